@@ -1,0 +1,497 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   D[M,N] = alpha * op(A) * op(B) + beta * C[M,N] (+ bias[N])        fp32 accumulate in TMEM
+//
+// Replaces the cuBLASLt dispatcher of the reference project
+// (helpers/matmul_dispatcher/src/dispatch.cpp:149-322) and its torch.matmul/addmm call sites.
+// Structure: persistent, one CTA per SM, warp-specialised
+//   warp 0    TMA producer   (cp.async.bulk.tensor 2-D, 128-byte swizzle, no multicast)
+//   warp 1    MMA issuer     (tcgen05.mma cta_group::1, 128 x BN x 16 per instruction)
+//   warps 2-5 epilogue       (tcgen05.ld 32x32b -> alpha/beta/bias -> global stores)
+// with a STAGES-deep shared-memory ring and two TMEM accumulators so the epilogue of tile i
+// overlaps the main loop of tile i+1.  Operands may each be K-major or MN-major, which covers
+// forward (x·Wᵀ), dgrad (dy·W) and wgrad (dyᵀ·x) with weights kept in (out, in) layout.
+//
+// A grouped variant (one launch for all experts of an MoE layer, tile list built on the device
+// from the expert offsets) shares the same pipeline; see ftb_grouped_gemm_bf16.
+#include "ptx.cuh"
+
+namespace ftb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 16;  // tile rasterisation: GROUP_M row-tiles share a sweep over N (L2 reuse)
+
+struct GemmParams {
+  int M, N, K;
+  int ldd, ldc;
+  float alpha, beta;
+  void* D;
+  const void* C;
+  const float* bias;
+  int d_fp32;        // output (and C) element type: 0 bf16, 1 fp32
+  // grouped mode (num_groups > 0): rows of A / D are expert-major, offsets[g]..offsets[g+1];
+  // B is (G, N, K) or (G, K, N) addressed through a 3-D tensor map.
+  int num_groups;
+  const int* offsets;
+  int max_tiles;     // grouped: upper bound of tiles the grid walks
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = GROUP_M * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gm = min(GROUP_M, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % gm;
+  tn = r / gm;
+}
+
+// Grouped tile lookup: tile index -> (group, row tile inside group). Linear walk over the
+// offsets (E <= 256, done by one thread per role per tile; cheap next to a 128xBNxK main loop).
+__device__ __forceinline__ bool grouped_tile(const int* __restrict__ offsets, int num_groups, int tiles_n, int tile,
+                                             int& g, int& row0, int& rows, int& tn) {
+  int acc = 0;
+  for (int e = 0; e < num_groups; ++e) {
+    const int a = offsets[e], b = offsets[e + 1];
+    const int tm_e = (b - a + BM - 1) / BM;
+    const int t_e = tm_e * tiles_n;
+    if (tile < acc + t_e) {
+      const int r = tile - acc;
+      g = e;
+      const int tm = r % tm_e;
+      tn = r / tm_e;
+      row0 = a + tm * BM;
+      rows = min(BM, b - row0);
+      return true;
+    }
+    acc += t_e;
+  }
+  return false;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool GROUPED>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int num_tiles = GROUPED ? p.max_tiles : tiles_m * tiles_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn, g = 0, row0, rows;
+        if constexpr (GROUPED) {
+          if (!grouped_tile(p.offsets, p.num_groups, tiles_n, tile, g, row0, rows, tn)) break;
+        } else {
+          tile_coords(tile, tiles_m, tiles_n, tm, tn);
+          row0 = tm * BM;
+        }
+        const int col0 = tn * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 10))) break;
+          uint8_t* sa = smem + stage * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (64 * BK * 2), &tmA, &full_bar[stage], row0 + j * 64, k0);
+          }
+          if constexpr (GROUPED) {
+            if constexpr (!B_MN) {
+              tma_load_3d(sb, &tmB, &full_bar[stage], k0, col0, g);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(sb + j * (64 * BK * 2), &tmB, &full_bar[stage], col0 + j * 64, k0, g);
+            }
+          } else {
+            if constexpr (!B_MN) {
+              tma_load_2d(sb, &tmB, &full_bar[stage], k0, col0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * (64 * BK * 2), &tmB, &full_bar[stage], col0 + j * 64, k0);
+            }
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      // Drain: wait until every load this thread issued has landed (the consumer may have
+      // aborted); bounded, so an unwinding CTA never exits with copies in flight.
+      if (!ok) {
+        for (int s = 0; s < STAGES; ++s)
+          for (uint32_t it = 0; it < (1u << 16); ++it)
+            if (mbar_try_wait(&full_bar[s], 0) || mbar_try_wait(&full_bar[s], 1)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if constexpr (GROUPED) {
+          int g, row0, rows, tn;
+          if (!grouped_tile(p.offsets, p.num_groups, tiles_n, tile, g, row0, rows, tn)) break;
+        }
+        if (!(ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, 20))) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag, 21))) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // K-major: step 32 B inside the 128 B swizzle row. MN-major: step 16 k-rows of 128 B.
+            const uint64_t ad = A_MN ? make_smem_desc(sa + kk * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                     : make_smem_desc(sa + kk * (UMMA_K * 2), 16, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc(sb + kk * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                     : make_smem_desc(sb + kk * (UMMA_K * 2), 16, 1024);
+            umma_f16(tmem_d, ad, bd, idesc, (kb | kk) != 0);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);  // accumulator complete -> epilogue
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ----------------------------------------------------------------- epilogue
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn, g = 0, row0, rows;
+      if constexpr (GROUPED) {
+        if (!grouped_tile(p.offsets, p.num_groups, tiles_n, tile, g, row0, rows, tn)) break;
+      } else {
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        row0 = tm * BM;
+        rows = min(BM, p.M - row0);
+      }
+      if (!(ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 30))) break;
+      tc_fence_after();
+      const int r_in = quad * 32 + lane;
+      const bool row_ok = r_in < rows;
+      const size_t row = static_cast<size_t>(row0 + r_in);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        const int col = tn * BN + c;
+        if (col >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col + i < p.N) v[i] += p.bias[col + i];
+          }
+          if (p.d_fp32) {
+            float* dptr = reinterpret_cast<float*>(p.D) + row * p.ldd + col;
+            const float* cptr = reinterpret_cast<const float*>(p.C) + row * p.ldc + col;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (col + i < p.N) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (p.beta != 0.f) {
+                  const float4 cc = *reinterpret_cast<const float4*>(cptr + i);
+                  o.x += p.beta * cc.x; o.y += p.beta * cc.y; o.z += p.beta * cc.z; o.w += p.beta * cc.w;
+                }
+                *reinterpret_cast<float4*>(dptr + i) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* dptr = reinterpret_cast<__nv_bfloat16*>(p.D) + row * p.ldd + col;
+            const __nv_bfloat16* cptr = reinterpret_cast<const __nv_bfloat16*>(p.C) + row * p.ldc + col;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col + i < p.N) {
+                if (p.beta != 0.f) {
+                  const uint4 cc = *reinterpret_cast<const uint4*>(cptr + i);
+                  const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&cc);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(c2[j]);
+                    v[i + 2 * j] += p.beta * f.x;
+                    v[i + 2 * j + 1] += p.beta * f.y;
+                  }
+                }
+                uint4 o;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(dptr + i) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Tensor map over a row-major bf16 tensor (dims innermost-first). box = {box0, box1[, 1]}.
+static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                     const uint32_t* box) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return -100;
+  cuuint64_t gdim[3];
+  cuuint64_t gstr[2];
+  cuuint32_t bx[3];
+  cuuint32_t es[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; }
+  for (int i = 0; i < rank - 1; ++i) gstr[i] = strides_bytes[i];
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstr, bx, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -200 - static_cast<int>(r);
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool GROUPED>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, GROUPED>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return -300 - static_cast<int>(e);
+    configured = true;
+  }
+  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
+}
+
+template <int BN, int STAGES, bool GROUPED>
+static int dispatch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                          int grid, cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch<BN, STAGES, false, false, GROUPED>(ta, tb, p, grid, s);
+  if (!a_mn && b_mn) return launch<BN, STAGES, false, true, GROUPED>(ta, tb, p, grid, s);
+  if (a_mn && !b_mn) return launch<BN, STAGES, true, false, GROUPED>(ta, tb, p, grid, s);
+  return launch<BN, STAGES, true, true, GROUPED>(ta, tb, p, grid, s);
+}
+
+}  // namespace ftb
+
+using namespace ftb;
+
+static int g_sm_count = 0;
+static int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_sm_count;
+}
+
+extern "C" {
+
+// D = alpha*op(A)*op(B) + beta*C + bias.   A, B bf16.  D/C bf16 (d_fp32=0) or fp32 (d_fp32=1).
+//   a_mn_major = 0: A stored (M, K) row-major, leading dim lda;  1: A stored (K, M), leading dim lda.
+//   b_mn_major = 0: B stored (N, K) row-major, leading dim ldb;  1: B stored (K, N), leading dim ldb.
+// Requirements: base pointers 16-byte aligned, lda/ldb multiples of 8, ldd/ldc multiples of 8 (bf16) or 4 (fp32),
+// N a multiple of 8.  Returns 0 or a negative error code.
+int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const float* bias, int M, int N, int K,
+                  int a_mn_major, int b_mn_major, int lda, int ldb, int ldd, int ldc, float alpha, float beta,
+                  int d_fp32, int bn, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -1;
+  if ((lda & 7) || (ldb & 7) || (N & 7) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(D) & 15))
+    return -2;
+  if (bn != 128 && bn != 256) bn = (N <= 128) ? 128 : 256;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn_major) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {BK, BM};
+    rc = make_tmap(&ta, A, 2, dims, str, box);
+  } else {
+    uint64_t dims[2] = {(uint64_t)M, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_tmap(&ta, A, 2, dims, str, box);
+  }
+  if (rc) return rc;
+  if (!b_mn_major) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {BK, (uint32_t)bn};
+    rc = make_tmap(&tb, B, 2, dims, str, box);
+  } else {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_tmap(&tb, B, 2, dims, str, box);
+  }
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = (C != nullptr) ? ldc : ldd;
+  p.alpha = alpha; p.beta = (C != nullptr) ? beta : 0.f;
+  p.D = D; p.C = (C != nullptr) ? C : D; p.bias = bias; p.d_fp32 = d_fp32;
+  p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
+  const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = tiles;
+  if (bn == 256) return dispatch_major<256, 4, false>(a_mn_major, b_mn_major, ta, tb, p, grid, stream);
+  return dispatch_major<128, 6, false>(a_mn_major, b_mn_major, ta, tb, p, grid, stream);
+}
+
+// Grouped GEMM over expert-major rows:  D[rows_g, :] = alpha * A[rows_g, :] * op(B[g]) + beta * C[rows_g, :].
+//   A (total_rows, K) row-major; B (G, N, K) if b_mn_major = 0, (G, K, N) if 1; offsets (G+1) int32 on device.
+//   max_tiles >= sum_g ceil(rows_g/128) * ceil(N/bn); the bound total_rows/128 + G row tiles always suffices.
+int ftb_grouped_gemm_bf16(const void* A, const void* B, void* D, const void* C, const int* offsets, int num_groups,
+                          int total_rows, int N, int K, int b_mn_major, int lda, int ldd, float alpha, float beta,
+                          int d_fp32, int max_ctas, cudaStream_t stream) {
+  if (total_rows <= 0 || N <= 0 || num_groups <= 0) return 0;
+  if ((lda & 7) || (N & 7) || (K & 7)) return -2;
+  const int bn = (N <= 128) ? 128 : 256;
+  CUtensorMap ta, tb;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)total_rows};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {BK, BM};
+    rc = make_tmap(&ta, A, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  if (!b_mn_major) {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)num_groups};
+    uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)K * N * 2};
+    uint32_t box[3] = {BK, (uint32_t)bn, 1};
+    rc = make_tmap(&tb, B, 3, dims, str, box);
+  } else {
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)num_groups};
+    uint64_t str[2] = {(uint64_t)N * 2, (uint64_t)K * N * 2};
+    uint32_t box[3] = {64, BK, 1};
+    rc = make_tmap(&tb, B, 3, dims, str, box);
+  }
+  if (rc) return rc;
+  GemmParams p;
+  p.M = total_rows; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldd;
+  p.alpha = alpha; p.beta = (C != nullptr) ? beta : 0.f;
+  p.D = D; p.C = (C != nullptr) ? C : D; p.bias = nullptr; p.d_fp32 = d_fp32;
+  p.num_groups = num_groups; p.offsets = offsets;
+  const int tiles_n = (N + bn - 1) / bn;
+  p.max_tiles = ((total_rows + BM - 1) / BM + num_groups) * tiles_n;
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (p.max_tiles < grid) grid = p.max_tiles;
+  if (bn == 256) return dispatch_major<256, 4, true>(0, b_mn_major, ta, tb, p, grid, stream);
+  return dispatch_major<128, 6, true>(0, b_mn_major, ta, tb, p, grid, stream);
+}
+
+// Reads and clears the library's device error word: returns code * 1000 + where (0 = no error).
+int ftb_gemm_error(void) {
+  int h[2] = {0, 0};
+  cudaMemcpyFromSymbol(&h[0], g_error_word, sizeof(int));
+  cudaMemcpyFromSymbol(&h[1], g_error_where, sizeof(int));
+  if (h[0] != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_error_word, &z, sizeof(int));
+    cudaMemcpyToSymbol(g_error_where, &z, sizeof(int));
+  }
+  return h[0] * 1000 + h[1];
+}
+
+}  // extern "C"

@@ -1,0 +1,510 @@
+"""ActiveModel: the training engine (flextrain/engine/active_model.py:138-2198).
+
+``fwd_bwd(seqs)``: split into rounds → per round pack chunks, plan save levels, then
+forward ``for layer: for chunk``, fused head forward+loss+backward per chunk, backward
+``for layer↓: for group↓: for chunk↓`` with recompute of the tiers that were not saved, embedding
+backward.  ``step()``: optimizer per layer.  No autograd graph exists anywhere.
+
+What differs from the reference, by design for an 8×B200 NVSwitch box:
+* state classes are GPU-resident by default; rings over pinned host memory are used only when the
+  planner says HBM is too small (n_gpu_layers / n_gpu_grads / n_gpu_opt_layers < n_layers);
+* loss bookkeeping stays on the device and is read once per ``fwd_bwd`` (the reference does a
+  blocking ``.item()`` per chunk, active_model.py:1307-1313);
+* a data-parallel hook fires as soon as a layer's gradients are final, so the fused
+  reduce-scatter of layer ``l`` overlaps the backward of layer ``l-1``.
+"""
+from __future__ import annotations
+
+import contextlib
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence as Seq
+
+import torch
+
+from ..core.activation_schema import ON_DEVICE, ActivationSlot, fetch_home, send_home
+from ..core.layer import ChunkMeta, LayerContext, LossStats
+from ..core.save_level import (HardwareCost, SaveLevelPlan, TransmissionScheduler, build_dp_tables,
+                               plan_from_solution)
+from ..core.working_set import WorkingSetConfig
+from ..io.sequence import Sequence
+from .buffers import BufferManager
+from .schedule import ChunkPolicy, prepare_training_chunks, split_sequences
+from .streams import EventBook, StreamBundle
+
+
+@dataclass
+class StepStats:
+    """What one ``fwd_bwd`` did (flextrain/engine/active_model.py:97-129)."""
+    loss_sum: float = 0.0
+    tokens: int = 0
+    active_tokens: int = 0
+    n_rounds: int = 0
+    n_chunks: int = 0
+    fwd_flops: float = 0.0
+    recompute_flops: float = 0.0
+    attn_fwd_flops: float = 0.0
+    host_act_bytes: int = 0
+    plan_hist: Dict[int, int] = field(default_factory=dict)
+    elapsed_s: float = 0.0
+
+    @property
+    def loss(self) -> float:
+        return self.loss_sum / max(self.active_tokens, 1)
+
+
+def _nvtx(name: str):
+    if torch.cuda.is_available():
+        return torch.cuda.nvtx.range(name)
+    return contextlib.nullcontext()
+
+
+class ActiveModel:
+    def __init__(self, *, embed, layers, head, optimizer, ws: WorkingSetConfig, device, hw_cost: HardwareCost = None,
+                 host_backend=None, dims: Optional[dict] = None, arch: str = "llama", hf_config: Optional[dict] = None,
+                 force_saved_act_level: Optional[int] = None, verbose: bool = False, dp=None, tp=None, ep=None,
+                 model_dir: Optional[str] = None):
+        self.embed, self.layers, self.head = embed, list(layers), head
+        self.optimizer = optimizer
+        self.ws = ws
+        self.device = torch.device(device)
+        self.hw = hw_cost or HardwareCost()
+        self.dims, self.arch, self.hf_config, self.model_dir = dims or {}, arch, hf_config, model_dir
+        self.force_level = force_saved_act_level
+        self.verbose = verbose
+        self.dp, self.tp, self.ep = dp, tp, ep
+        self.step_num = 0
+        self._zero_grad = True
+        self._pending_tokens = 0
+        self._grads_fresh: Dict[int, bool] = {}
+        attn_layers = [l for l in self.layers if getattr(l, "attn", None) is not None]
+        kvh = max((l.attn.cfg.n_kv_heads for l in attn_layers), default=0)
+        hd = max((l.attn.cfg.head_dim for l in attn_layers), default=0)
+        window = ws.max_seq_len if (attn_layers and ws.max_seq_len > ws.max_chunk_size) else 0
+        act_dtype = self.layers[0].cfg.dtype if self.layers else torch.bfloat16
+        self.buffers = BufferManager(
+            [l.param_spec for l in self.layers], embed.param_spec, head.param_spec, optimizer, device,
+            n_gpu_layers=ws.n_gpu_layers, n_gpu_grads=ws.n_gpu_grads, n_gpu_opt_layers=ws.n_gpu_opt_layers,
+            host_backend=host_backend, kv_window_tokens=window, kv_heads=kvh, head_dim=hd, act_dtype=act_dtype,
+            host_act_bytes=ws.host_act_buffer_size, verbose=verbose)
+        self.streams = StreamBundle.create(device, secondary=False)
+        self.events = EventBook(self.streams)
+        self._scheduler = None
+        self._last_plan: Optional[SaveLevelPlan] = None
+        self.is_causal = True
+        self.mrope = any(getattr(l, "attn", None) is not None and l.attn.cfg.rope.mrope_sections for l in self.layers)
+        if dp is not None:
+            dp.attach(self)
+
+    # ====================================================================== public API
+    def fwd_bwd(self, seqs: Seq[Sequence], loss_scale_factor: Optional[float] = None,
+                total_tokens_per_step: Optional[int] = None, loss_fn=None) -> StepStats:
+        """Forward + backward over ``seqs``; gradients accumulate until :meth:`step`."""
+        t0 = time.perf_counter()
+        ws = self.ws
+        if loss_scale_factor is None:
+            loss_scale_factor = 1.0 / max(sum(s.active_token_count for s in seqs), 1)
+        total_tokens_per_step = total_tokens_per_step or sum(len(s) for s in seqs)
+        rounds = split_sequences(seqs, target_round_tokens=ws.target_round_tokens, max_chunk_size=ws.max_chunk_size,
+                                 max_training_chunks=ws.max_training_chunks,
+                                 max_total_round_tokens=ws.max_total_round_tokens,
+                                 policy=ChunkPolicy.CAUSAL if self.is_causal else ChunkPolicy.NON_CAUSAL)
+        stats = StepStats(n_rounds=len(rounds))
+        loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
+        act_acc = torch.zeros((), dtype=torch.int64, device=self.device)
+        pending_losses = []
+        with _nvtx("Fwd+Bwd"):
+            for r, rseqs in enumerate(rounds):
+                with _nvtx(f"Round {r}"):
+                    last_round = r == len(rounds) - 1
+                    with _nvtx("Prepare Training Chunks"):
+                        metas = prepare_training_chunks(rseqs, ws.max_chunk_size, self.device, mrope=self.mrope)
+                    with _nvtx("Determine Saved Levels"):
+                        plan = self._plan_save_levels(metas)
+                    self._last_plan = plan
+                    stats.n_chunks += len(metas)
+                    stats.tokens += sum(m.num_tokens for m in metas)
+                    stats.host_act_bytes = max(stats.host_act_bytes, plan.host_bytes)
+                    for k, v in plan.histogram().items():
+                        stats.plan_hist[k] = stats.plan_hist.get(k, 0) + v
+                    if self._zero_grad:
+                        self._zero_all_grads()
+                        self._zero_grad = False
+                    ctx_base = dict(kv_window=self.buffers.kv_window, total_tokens_per_step=total_tokens_per_step,
+                                    tp=self.tp, ep=self.ep)
+                    with _nvtx("Setup Round"):
+                        transitions, slots = self._setup_round(metas)
+                    with _nvtx("Forward"):
+                        self._forward_pass(metas, plan, transitions, slots, ctx_base, stats)
+                    with _nvtx("Head"):
+                        for c, meta in enumerate(metas):
+                            ls = self.head.forward_backward(transitions[c], meta, self.buffers.head_params(),
+                                                            self.buffers.head_grads(), loss_fn, loss_scale_factor)
+                            loss_acc += ls.total_loss
+                            act_acc += ls.active_tokens
+                            pending_losses.append((rseqs, meta, ls.per_token_loss))
+                    with _nvtx("Backward"):
+                        self._backward_pass(metas, plan, transitions, slots, ctx_base, stats, last_round)
+                    with _nvtx("Embed Backward"):
+                        for c, meta in enumerate(metas):
+                            self.embed.backward(transitions[c], meta, self.buffers.embed_params(),
+                                                self.buffers.embed_grads())
+                    self.events.clear_per_round()
+        if self.dp is not None:
+            self.dp.on_embed_head_grads_ready()
+        # one host read for the whole call
+        stats.loss_sum = float(loss_acc)
+        stats.active_tokens = int(act_acc)
+        self._write_back_losses(pending_losses)
+        self._pending_tokens += stats.tokens
+        stats.elapsed_s = time.perf_counter() - t0
+        return stats
+
+    def step(self) -> int:
+        """Optimizer step over embed, head and every layer; returns 0, or the optimizer's error code."""
+        self.step_num += 1
+        with _nvtx("Step"):
+            if self.dp is not None:
+                rc = self.dp.step(self)
+            else:
+                rc = self._step_local()
+        for l, layer in enumerate(self.layers):
+            if self.buffers.params_resident:
+                layer.end_of_step(self.buffers.params(l))
+        self._zero_grad = True
+        self._pending_tokens = 0
+        return rc
+
+    # ================================================================= save-level planning
+    def _plan_save_levels(self, metas: List[ChunkMeta]) -> SaveLevelPlan:
+        nL, nC = len(self.layers), len(metas)
+        n_slots = self.ws.n_gpu_act_slots
+        if self.force_level is None and nL * nC <= n_slots:
+            return SaveLevelPlan.all_on_device(nL, nC)                    # fast path: everything stays in HBM
+        toks = [m.num_tokens for m in metas]
+        ctxs = [(m.total_k / max(len(m.seq_lens), 1)) / 2 + sum(m.prior_lens) / max(len(m.seq_lens), 1) / 2 for m in metas]
+        tables = build_dp_tables(self.layers, toks, self.hw, avg_ctx=ctxs)
+        if self.force_level is not None:
+            return plan_from_solution(tables, None, nL, nC, n_gpu_act_slots=0 if self.force_level >= 0 else nL * nC,
+                                      host_budget_bytes=None, force_level=self.force_level)
+        if self._scheduler is None:
+            self._scheduler = TransmissionScheduler()
+        T = len(tables.tasks)
+        pinned = [1 if t >= T - n_slots else 0 for t in range(T)]
+        sol, val = self._scheduler.solve(tables.compute_ms, tables.dur_ms, tables.value_ms, n_slots, pinned,
+                                         tables.valid_k)
+        plan = plan_from_solution(tables, sol, nL, nC, n_gpu_act_slots=n_slots,
+                                  host_budget_bytes=self.ws.host_act_buffer_size or None)
+        plan.solver_value = val
+        if self.verbose:
+            print(f"[Save Level Plan] tiers={plan.histogram()} host_bytes={plan.host_bytes / 2**30:.2f} GiB "
+                  f"feasible={plan.feasible}")
+        return plan
+
+    # ======================================================================= round set-up
+    def _setup_round(self, metas):
+        self.buffers.reset_host_act()
+        transitions = {}
+        ep = self.buffers.embed_params()
+        for c, meta in enumerate(metas):
+            transitions[c] = self.embed.forward(meta, ep)
+        return transitions, {}
+
+    def _ctx(self, base, **kw) -> LayerContext:
+        return LayerContext(**base, **kw)
+
+    # ============================================================================ forward
+    def _forward_pass(self, metas, plan: SaveLevelPlan, transitions, slots, ctx_base, stats: StepStats):
+        bm, st, ev = self.buffers, self.streams, self.events
+        nL = len(self.layers)
+        if not bm.params_resident:
+            # events of the previous round are stale; the ring may only be refilled once compute has left it
+            ev.weights_in.clear(); ev.layer_out.clear(); ev.grads_in.clear()
+            if st.is_cuda:
+                st.inbound.wait_stream(st.compute)
+            for l in range(min(bm.n_p, nL)):
+                self._prefetch_params(l)
+        elif not bm.grads_resident:
+            ev.layer_out.clear(); ev.grads_in.clear()
+        for l, layer in enumerate(self.layers):
+            with _nvtx(f"Layer {l}"):
+                if not bm.params_resident:
+                    ev.weights_in.wait(l, st.compute)
+                params = bm.params(l)
+                lin_state, lin_conv = {}, {}
+                for c, meta in enumerate(metas):
+                    slot = ActivationSlot(layer.activation_schema, meta.num_tokens, ON_DEVICE)
+                    ctx = self._ctx(ctx_base)
+                    if layer.gdn is not None and meta.has_prior:
+                        ctx.lin_state_in, ctx.lin_conv_in = lin_state.get(meta.seq_ids[0]), lin_conv.get(meta.seq_ids[0])
+                    x = layer.forward(transitions[c], meta, params, slot, ctx)
+                    if layer.gdn is not None and any(meta.has_more_chunks):
+                        lin_state[meta.seq_ids[0]] = ctx.out.get("lin_state")
+                        lin_conv[meta.seq_ids[0]] = ctx.out.get("lin_conv")
+                    transitions[c] = x
+                    cost = layer.compute_cost(meta.num_tokens, max(meta.total_k / max(len(meta.seq_lens), 1) / 2, 1))
+                    stats.fwd_flops += cost.total_fwd_flops
+                    stats.attn_fwd_flops += cost.attn_fwd_flops
+                    level = plan.level(l, c)
+                    if level == ON_DEVICE:
+                        slots[(l, c)] = slot
+                    else:
+                        stats.recompute_flops += (cost.avoided_recompute_flops[-1] - cost.avoided_recompute_flops[
+                            min(level, len(cost.avoided_recompute_flops) - 1)])
+                        slots[(l, c)] = self._offload_slot(slot, level, l, c)
+                if not bm.params_resident:
+                    ev.layer_out.record(l, st.compute)
+                    nxt = l + bm.n_p
+                    if nxt < nL:
+                        self._prefetch_params(nxt, after_layer=l)
+
+    def _offload_slot(self, slot: ActivationSlot, level: int, l: int, c: int):
+        """Send the fields with ``tier <= level`` to the host arena on the outbound stream; drop the rest."""
+        bm, st, ev = self.buffers, self.streams, self.events
+        if bm.host_act is None:
+            slot.demote(level)          # no host arena: keep the saved tiers in HBM, just drop the others
+            return slot
+        nbytes = slot.schema.home_size_bytes(slot.num_tokens, level)
+        hbuf = bm.host_act_slot(nbytes)
+        ev.act_computed.record((l, c), st.compute)
+        with st.use(st.outbound):
+            ev.act_computed.wait((l, c), st.outbound)
+            host = send_home(slot, hbuf, level)
+            ev.act_out.record((l, c), st.outbound)
+        if st.is_cuda:
+            for name in slot.names():
+                slot._t[name].record_stream(st.outbound)
+        return host
+
+    def _prefetch_params(self, l: int, after_layer: Optional[int] = None):
+        bm, st, ev = self.buffers, self.streams, self.events
+        with st.use(st.inbound):
+            if after_layer is not None:
+                ev.layer_out.wait(after_layer, st.inbound)      # ring slot is free once its previous tenant finished
+            bm.fetch_layer_params(l)
+            ev.weights_in.record(l, st.inbound)
+
+    # =========================================================================== backward
+    def _backward_pass(self, metas, plan, transitions, slots, ctx_base, stats, last_round: bool):
+        bm, st, ev = self.buffers, self.streams, self.events
+        nL = len(self.layers)
+        groups: Dict[int, List[int]] = {}
+        for c, m in enumerate(metas):
+            groups.setdefault(m.seq_group, []).append(c)
+        if not bm.params_resident:
+            # the forward pass left the last n_p layers in the ring; everything else is re-fetched backwards
+            pass
+        for l in range(nL - 1, -1, -1):
+            layer = self.layers[l]
+            with _nvtx(f"Layer {l}"):
+                if not bm.params_resident:
+                    if not ev.weights_in.has(("b", l)) and l + bm.n_p < nL:
+                        self._prefetch_params_bwd(l)
+                    if ev.weights_in.has(("b", l)):
+                        ev.weights_in.wait(("b", l), st.compute)
+                    else:
+                        ev.weights_in.wait(l, st.compute)
+                if not bm.grads_resident:
+                    self._prepare_ring_grads(l)
+                params, grads = bm.params(l), bm.grads(l)
+                for g in sorted(groups, reverse=True):
+                    chunk_ids = groups[g]
+                    spans = any(metas[c].has_prior or any(metas[c].has_more_chunks) for c in chunk_ids)
+                    if spans and layer.attn is not None:
+                        self._refresh_kv_window(l, chunk_ids, metas, slots)
+                    lin_d = {}
+                    for c in reversed(chunk_ids):
+                        meta = metas[c]
+                        slot = self._fetch_slot(slots.pop((l, c)), l, c)
+                        ctx = self._ctx(ctx_base)
+                        if layer.gdn is not None:
+                            if meta.has_prior:
+                                prev = self._peek_slot(slots[(l, c - 1)])
+                                ctx.lin_state_in = prev._t["lin_final_state"].to(self.device)
+                                ctx.lin_conv_in = prev._t["lin_conv_state"].to(self.device)
+                            if any(meta.has_more_chunks):
+                                ctx.lin_dstate_in, ctx.lin_dconv_in = lin_d.get("s"), lin_d.get("c")
+                        with _nvtx(f"Recompute: Chunk {c}"):
+                            layer.forward_recompute(meta, params, slot, ctx)
+                        with _nvtx(f"Backward: Chunk {c}"):
+                            transitions[c] = layer.backward(transitions[c], meta, params, grads, slot, ctx)
+                        if layer.gdn is not None:
+                            lin_d = {"s": ctx.out.get("lin_dstate"), "c": ctx.out.get("lin_dconv")}
+                        del slot
+                ev.grads_ready.record(l, st.compute)
+                if not bm.grads_resident:
+                    with st.use(st.outbound):
+                        ev.grads_ready.wait(l, st.outbound)
+                        bm.offload_layer_grads(l)
+                        ev.layer_out.record(("g", l), st.outbound)
+                if not bm.params_resident:
+                    ev.layer_out.record(("b", l), st.compute)
+                    nxt = l - bm.n_p
+                    if nxt >= 0:
+                        self._prefetch_params_bwd(nxt, after=("b", l))
+                if self.dp is not None and last_round:
+                    self.dp.on_layer_grads_ready(l)
+
+    def _prefetch_params_bwd(self, l: int, after=None):
+        bm, st, ev = self.buffers, self.streams, self.events
+        with st.use(st.inbound):
+            if after is not None:
+                ev.layer_out.wait(after, st.inbound)
+            bm.fetch_layer_params(l)
+            ev.weights_in.record(("b", l), st.inbound)
+
+    def _prepare_ring_grads(self, l: int):
+        """Ring-resident gradients: zero the slot on the first round of a step, else bring the partial sums back."""
+        bm, st, ev = self.buffers, self.streams, self.events
+        prev_tenant = l + bm.n_g
+        if ev.layer_out.has(("g", prev_tenant)):
+            ev.layer_out.wait(("g", prev_tenant), st.compute)
+        if self._grads_fresh.get(l, True):
+            bm.zero_layer_grads(l)
+            self._grads_fresh[l] = False
+        else:
+            with st.use(st.inbound):
+                if ev.layer_out.has(("g", prev_tenant)):
+                    ev.layer_out.wait(("g", prev_tenant), st.inbound)
+                bm.fetch_layer_grads(l)
+                ev.grads_in.record(l, st.inbound)
+            ev.grads_in.wait(l, st.compute)
+
+    def _peek_slot(self, slot):
+        return slot
+
+    def _fetch_slot(self, slot: ActivationSlot, l: int, c: int) -> ActivationSlot:
+        """Bring an offloaded slot back into HBM at its saved level (stale higher tiers stay invisible)."""
+        bm, st, ev = self.buffers, self.streams, self.events
+        if slot.buffer is None or slot.buffer.device == self.device:
+            return slot
+        with st.use(st.inbound):
+            ev.act_out.wait((l, c), st.inbound)
+            dev = fetch_home(slot, None, self.device)
+            ev.act_in.record((l, c), st.inbound)
+        ev.act_in.wait((l, c), st.compute)
+        return dev
+
+    def _refresh_kv_window(self, l: int, chunk_ids, metas, slots) -> None:
+        """Refill the rolling K/V window with layer ``l``'s saved K/V of every chunk of a multi-chunk sequence and
+        clear the dK/dV accumulators (flextrain/engine/active_model.py:1941-2034)."""
+        w = self.buffers.kv_window
+        st = self.streams
+        with st.use(st.inbound_fwd_context):
+            st.inbound_fwd_context.wait_stream(st.compute)
+            for c in chunk_ids:
+                m = metas[c]
+                if not (m.has_prior or any(m.has_more_chunks)):
+                    continue
+                P, L = m.prior_lens[0], m.seq_lens[0]
+                s = slots[(l, c)]
+                w.k[P:P + L].copy_(s._t["xk"], non_blocking=True)
+                w.v[P:P + L].copy_(s._t["xv"], non_blocking=True)
+            w.dk.zero_()
+            w.dv.zero_()
+        st.compute.wait_stream(st.inbound_fwd_context)
+
+    # =============================================================================== step
+    def _step_local(self) -> int:
+        bm, st, ev = self.buffers, self.streams, self.events
+        opt, rc = self.optimizer, 0
+        rc |= opt.step(self.embed.param_spec, bm.embed_params(), bm.embed_grads(), bm.embed_opt(), self.step_num)
+        rc |= opt.step(self.head.param_spec, bm.head_params(), bm.head_grads(), bm.head_opt(), self.step_num)
+        if rc:
+            return rc
+        nL = len(self.layers)
+        ringed = not (bm.params_resident and bm.grads_resident and bm.opt_resident)
+        if not ringed:
+            for l, layer in enumerate(self.layers):
+                rc |= opt.step(layer.param_spec, bm.params(l), bm.grads(l), bm.opt_state(l), self.step_num)
+                if rc:
+                    return rc
+            return rc
+        # ---- streamed step: prefetch k+depth on inbound, update on compute, write back on outbound
+        ring_n = [n for n, res in ((bm.n_p, bm.params_resident), (bm.n_g, bm.grads_resident),
+                                   (max(bm.n_o, 2), bm.opt_resident)) if not res]
+        depth = min(ring_n + [nL])
+
+        def fetch(k):
+            # a ring slot may be refilled once its previous tenant (k - n) has been written back
+            with st.use(st.inbound):
+                for n in ring_n:
+                    if k - n >= 0:
+                        ev.layer_out.wait(("s", k - n), st.inbound)
+                bm.fetch_layer_params(k); bm.fetch_layer_grads(k); bm.fetch_layer_opt(k)
+                ev.opt_in.record(k, st.inbound)
+
+        st.inbound.wait_stream(st.compute)
+        st.inbound.wait_stream(st.outbound)
+        for k in range(min(depth, nL)):
+            fetch(k)
+        for l, layer in enumerate(self.layers):
+            ev.opt_in.wait(l, st.compute)
+            rc |= opt.step(layer.param_spec, bm.params(l), bm.grads(l), bm.opt_state(l), self.step_num)
+            if rc:
+                break
+            layer.end_of_step(bm.params(l))
+            ev.layer_out.record(("c", l), st.compute)
+            with st.use(st.outbound):
+                ev.layer_out.wait(("c", l), st.outbound)
+                bm.offload_layer_params(l)
+                bm.offload_layer_opt(l)
+                ev.layer_out.record(("s", l), st.outbound)
+            if l + depth < nL:
+                fetch(l + depth)
+        st.synchronize_all()
+        ev.weights_in.clear(); ev.layer_out.clear(); ev.opt_in.clear()
+        self._grads_fresh = {}
+        return rc
+
+    # ============================================================================= helpers
+    def _zero_all_grads(self) -> None:
+        bm = self.buffers
+        bm.embed_g.zero_()
+        bm.head_g.zero_()
+        if bm.grads_resident:
+            for b in bm.gpu_g:
+                b.zero_()
+        self._grads_fresh = {}
+
+    def _write_back_losses(self, pending) -> None:
+        """Per-token losses back into each ``Sequence`` (flextrain/engine/active_model.py:1306-1312)."""
+        for rseqs, meta, per_tok in pending:
+            host = per_tok.detach().to("cpu")
+            off = 0
+            for i, start, n in meta.extra["pieces"]:
+                s = rseqs[i]
+                if s.per_token_loss is None:
+                    s.per_token_loss = torch.zeros(len(s), dtype=torch.float32)
+                s.per_token_loss[start:start + n] = host[off:off + n]
+                off += n
+
+    def synchronize(self) -> None:
+        self.streams.synchronize_all()
+
+    # --------------------------------------------------------------------- HF load / save
+    def load_hf(self, model_dir: str, strict: bool = False) -> None:
+        from ..io.hf_weights import load_hf_into_model
+        load_hf_into_model(self, model_dir, strict=strict)
+
+    def save_hf(self, out_dir: str, filename: str = "final.safetensors") -> str:
+        from ..io.hf_weights import export_model_safetensors
+        return export_model_safetensors(self, out_dir, filename)
+
+    def named_master_params(self):
+        """Yield ``(scope, layer_index, name, tensor)`` over every master tensor (embed, layers, head)."""
+        for n, t in self.buffers.embed_params().items():
+            yield "embed", -1, n, t
+        for l in range(len(self.layers)):
+            for n, t in self.buffers.host_params(l).items():
+                yield "layer", l, n, t
+        for n, t in self.buffers.head_params().items():
+            yield "head", -1, n, t
+
+    def push_masters_to_device(self) -> None:
+        """After editing host masters of a ringed model (load / init), nothing else is needed: layers are fetched
+        from the masters on demand.  Resident models are edited in place."""
+        return None
+
+    def destroy(self) -> None:
+        self.buffers.destroy()

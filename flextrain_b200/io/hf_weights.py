@@ -1,0 +1,183 @@
+"""Direct safetensors reader / writer for HF checkpoints (flextrain/io/hf_weights.py:81-530).
+
+No ``AutoModel``: an :class:`ArchSpec` lists, for the embedding, the head and each layer, which
+checkpoint tensors feed which engine tensor.  Linear weights need no transpose (both sides are
+``(out, in)``).  An entry may combine several checkpoint tensors (MoE expert stacks, bundled
+linear-attention projections) through ``combine`` / ``split`` callables, which replaces the
+reference's ``post_load_hook`` / ``pre_export_hook`` pair.  Loading is shard-index aware and strict:
+every non-optional entry must find at least one of its alternates.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+
+
+@dataclass
+class WeightMapEntry:
+    name: str                                   # engine tensor name (e.g. "w_q")
+    hf_names: Sequence[str]                     # checkpoint names (already formatted with the layer index)
+    optional: bool = False
+    alternates: Sequence[Sequence[str]] = ()    # other complete name sets that can satisfy this entry
+    combine: Optional[Callable[[List[torch.Tensor]], torch.Tensor]] = None
+    split: Optional[Callable[[torch.Tensor], List[torch.Tensor]]] = None
+    plus_one: bool = False                      # checkpoint stores gamma - 1
+    transpose: bool = False
+
+
+@dataclass
+class ArchSpec:
+    name: str
+    embed: Callable[[object], List[WeightMapEntry]]
+    head: Callable[[object], List[WeightMapEntry]]
+    layer: Callable[[int, object], List[WeightMapEntry]]
+    hf_architectures: Sequence[str] = ()
+
+
+class SafetensorsDir:
+    """Index-aware access to the tensors of an HF model directory."""
+
+    def __init__(self, model_dir: str):
+        from safetensors import safe_open
+        self.dir = model_dir
+        self._open = safe_open
+        self.where: Dict[str, str] = {}
+        idx = os.path.join(model_dir, "model.safetensors.index.json")
+        if os.path.exists(idx):
+            with open(idx) as f:
+                self.where = dict(json.load(f)["weight_map"])
+        else:
+            for fn in sorted(os.listdir(model_dir)):
+                if fn.endswith(".safetensors") and not fn.startswith("adapter_"):
+                    with safe_open(os.path.join(model_dir, fn), framework="pt") as sf:
+                        for k in sf.keys():
+                            self.where[k] = fn
+        self._handles: Dict[str, object] = {}
+        self.consumed = set()
+
+    def has(self, name: str) -> bool:
+        return name in self.where
+
+    def get(self, name: str) -> torch.Tensor:
+        fn = self.where[name]
+        if fn not in self._handles:
+            self._handles[fn] = self._open(os.path.join(self.dir, fn), framework="pt")
+        self.consumed.add(name)
+        return self._handles[fn].get_tensor(name)
+
+    def unconsumed(self) -> List[str]:
+        return sorted(set(self.where) - self.consumed)
+
+
+def _resolve(entry: WeightMapEntry, src: SafetensorsDir) -> Optional[List[torch.Tensor]]:
+    for names in (entry.hf_names, *entry.alternates):
+        if all(src.has(n) for n in names):
+            return [src.get(n) for n in names]
+    return None
+
+
+def _load_entries(entries: List[WeightMapEntry], dst: Dict[str, torch.Tensor], src: SafetensorsDir, where: str,
+                  strict: bool) -> None:
+    for e in entries:
+        if e.name not in dst:
+            if strict:
+                raise KeyError(f"{where}: engine has no tensor {e.name!r}")
+            continue
+        ts = _resolve(e, src)
+        if ts is None:
+            if e.optional:
+                continue
+            raise KeyError(f"{where}: none of {list(e.hf_names)[:3]}... found in checkpoint for {e.name!r}")
+        t = e.combine(ts) if e.combine is not None else ts[0]
+        if e.transpose:
+            t = t.t()
+        if e.plus_one:
+            t = t.to(torch.float32) + 1.0
+        d = dst[e.name]
+        if tuple(t.shape) != tuple(d.shape):
+            raise ValueError(f"{where}: shape mismatch for {e.name!r}: checkpoint {tuple(t.shape)} vs engine "
+                             f"{tuple(d.shape)}")
+        d.copy_(t.to(d.dtype))
+
+
+def load_hf_into_model(am, model_dir: str, strict: bool = False) -> None:
+    """Fill the engine's master tensors from an HF directory (flextrain/engine/active_model.py:700-793)."""
+    from .arch import select_arch_module
+    mc = am.model_config
+    spec: ArchSpec = select_arch_module(mc.arch).ARCH_SPEC
+    src = SafetensorsDir(model_dir)
+    bm = am.buffers
+    _load_entries(spec.embed(mc), bm.embed_params(), src, "embed", strict)
+    for i in range(len(am.layers)):
+        _load_entries(spec.layer(i, mc), bm.host_params(i), src, f"layer {i}", strict)
+    head_entries = spec.head(mc)
+    hp = bm.head_params()
+    tied_missing = False
+    for e in head_entries:
+        if e.name == "w_head_proj" and _peek(e, src) is None:
+            tied_missing = True
+    _load_entries([e for e in head_entries if not (e.name == "w_head_proj" and tied_missing)], hp, src, "head", strict)
+    if tied_missing or mc.tie_embeddings:
+        # tied embeddings: the head arrives empty and mirrors the embedding table (reference FINDING 10)
+        hp["w_head_proj"].copy_(bm.embed_params()["w_tok_embeddings"])
+        am.head.tied = True
+    if strict:
+        left = [n for n in src.unconsumed() if "rotary_emb.inv_freq" not in n and not n.startswith("visual.")]
+        if left:
+            raise KeyError(f"checkpoint tensors not consumed: {left[:8]} ... ({len(left)} total)")
+
+
+def _peek(entry: WeightMapEntry, src: SafetensorsDir):
+    for names in (entry.hf_names, *entry.alternates):
+        if all(src.has(n) for n in names):
+            return names
+    return None
+
+
+def collect_hf_state(am, lora_merge: bool = False) -> Dict[str, torch.Tensor]:
+    """Engine masters → ``{hf_name: cpu tensor}`` (inverse of the load map)."""
+    from .arch import select_arch_module
+    mc = am.model_config
+    spec: ArchSpec = select_arch_module(mc.arch).ARCH_SPEC
+    bm = am.buffers
+    out: Dict[str, torch.Tensor] = {}
+
+    def emit(entries: List[WeightMapEntry], params: Dict[str, torch.Tensor]):
+        for e in entries:
+            if e.name not in params:
+                continue
+            t = params[e.name].detach().to("cpu")
+            if lora_merge and (e.name + "_lora_a") in params:
+                from ..export._merged import merged_weight
+                t = merged_weight(params, e.name, am)
+            if e.plus_one:
+                t = (t.to(torch.float32) - 1.0).to(t.dtype)
+            if e.transpose:
+                t = t.t()
+            parts = e.split(t) if e.split is not None else [t]
+            for n, p in zip(e.hf_names, parts):
+                out[n] = p.contiguous()
+
+    emit(spec.embed(mc), bm.embed_params())
+    for i in range(len(am.layers)):
+        emit(spec.layer(i, mc), bm.host_params(i))
+    head_entries = spec.head(mc)
+    if am.head.tied or mc.tie_embeddings:
+        head_entries = [e for e in head_entries if e.name != "w_head_proj"]
+    emit(head_entries, bm.head_params())
+    return out
+
+
+def export_model_safetensors(am, out_dir: str, filename: str = "final.safetensors") -> str:
+    """Single-shard export in HF names (flextrain/io/hf_weights.py:491-530)."""
+    from safetensors.torch import save_file
+    os.makedirs(out_dir, exist_ok=True)
+    if torch.device(am.device).type == "cuda":
+        torch.cuda.synchronize()
+    path = os.path.join(out_dir, filename)
+    save_file(collect_hf_state(am), path, metadata={"format": "pt"})
+    return path

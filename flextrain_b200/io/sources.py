@@ -1,0 +1,301 @@
+"""Token sources (flextrain/io/sources.py:84-1245).
+
+``TokenSource`` protocol: ``get_sequences(max_token_count)`` returns whole sequences whose total
+length does not exceed the budget, ``iter_sequences()`` streams them, ``push_back(seqs)`` returns
+unconsumed sequences to the front of the queue (used by the short-tail-round spill in train.py).
+Adapters: synthetic uniform tokens, raw token lists, FineWeb-style ``uint16`` ``.bin`` shards, JSON /
+JSONL SFT records (background tokenizer thread, prompt masking), custom-schema records, and a
+streaming HuggingFace ``datasets`` adapter.
+"""
+from __future__ import annotations
+
+import collections
+import glob
+import json
+import os
+import queue
+import threading
+from typing import Callable, Deque, Dict, Iterable, Iterator, List, Optional, Protocol, Sequence as Seq
+
+import numpy as np
+import torch
+
+from .sequence import Sequence
+
+IGNORE = -100
+
+
+class TokenSource(Protocol):
+    def get_sequences(self, max_token_count: int) -> List[Sequence]: ...
+    def iter_sequences(self) -> Iterator[Sequence]: ...
+    def push_back(self, seqs: Seq[Sequence]) -> None: ...
+
+
+class _QueueMixin:
+    """Front queue shared by all sources: pushed-back sequences are served first, in order."""
+
+    def _init_queue(self):
+        self._front: Deque[Sequence] = collections.deque()
+
+    def push_back(self, seqs: Seq[Sequence]) -> None:
+        for s in reversed(list(seqs)):
+            self._front.appendleft(s)
+
+    def _next(self) -> Optional[Sequence]:
+        if self._front:
+            return self._front.popleft()
+        try:
+            return next(self._it)
+        except StopIteration:
+            return None
+
+    def get_sequences(self, max_token_count: int) -> List[Sequence]:
+        out, total = [], 0
+        while True:
+            s = self._next()
+            if s is None:
+                break
+            if total + len(s) > max_token_count:
+                if not out and len(s) > max_token_count:
+                    raise ValueError(f"sequence of {len(s)} tokens exceeds the step budget {max_token_count}")
+                self._front.appendleft(s)
+                break
+            out.append(s)
+            total += len(s)
+        return out
+
+    def iter_sequences(self) -> Iterator[Sequence]:
+        while True:
+            s = self._next()
+            if s is None:
+                return
+            yield s
+
+
+class SyntheticTokenSource(_QueueMixin):
+    """Uniform random tokens from a seed; fixed length or a cycle of lengths; infinite
+    (flextrain/io/sources.py:795-853). ``targets = roll(tokens, -1)``."""
+
+    def __init__(self, vocab_size: int, seq_len, seed: int = 0, pin: bool = False):
+        self.vocab_size = vocab_size
+        self.lengths = [int(seq_len)] if isinstance(seq_len, int) else [int(x) for x in seq_len]
+        self.gen = torch.Generator().manual_seed(seed)
+        self.pin = pin
+        self._count = 0
+        self._init_queue()
+        self._it = self._generate()
+
+    def _generate(self) -> Iterator[Sequence]:
+        while True:
+            n = self.lengths[self._count % len(self.lengths)]
+            toks = torch.randint(0, self.vocab_size, (n,), generator=self.gen, dtype=torch.int64)
+            if self.pin and torch.cuda.is_available():
+                toks = toks.pin_memory()
+            yield Sequence(toks, seq_id=self._count)
+            self._count += 1
+
+
+class RawTokenSource(_QueueMixin):
+    """Pre-tokenised sequences supplied by the caller (lists / tensors of ids)."""
+
+    def __init__(self, token_lists: Iterable, loop: bool = False):
+        self._data = [torch.as_tensor(t, dtype=torch.int64) for t in token_lists]
+        self.loop = loop
+        self._init_queue()
+        self._it = self._generate()
+
+    def _generate(self):
+        i = 0
+        while True:
+            for t in self._data:
+                yield Sequence(t.clone(), seq_id=i)
+                i += 1
+            if not self.loop:
+                return
+
+
+class ShardTokenSource(_QueueMixin):
+    """FineWeb-style shards: ``uint16`` token files, optionally with a 256-int32 header (magic 20240520);
+    documents are cut into ``seq_len`` windows (flextrain/io/sources.py:861)."""
+    MAGIC = 20240520
+
+    def __init__(self, pattern: str, seq_len: int, loop: bool = True, vocab_size: Optional[int] = None):
+        self.files = sorted(glob.glob(pattern)) if any(c in pattern for c in "*?[") else [pattern]
+        if not self.files:
+            raise FileNotFoundError(f"no shard matches {pattern!r}")
+        self.seq_len, self.loop, self.vocab_size = seq_len, loop, vocab_size
+        self._init_queue()
+        self._it = self._generate()
+
+    def _read(self, path: str) -> np.ndarray:
+        with open(path, "rb") as f:
+            head = np.frombuffer(f.read(1024), dtype=np.int32)
+        if head.size == 256 and head[0] == self.MAGIC:
+            return np.memmap(path, dtype=np.uint16, mode="r", offset=1024)
+        return np.memmap(path, dtype=np.uint16, mode="r")
+
+    def _generate(self):
+        sid = 0
+        while True:
+            for path in self.files:
+                arr = self._read(path)
+                for a in range(0, len(arr) - self.seq_len - 1, self.seq_len):
+                    win = torch.from_numpy(np.asarray(arr[a:a + self.seq_len + 1], dtype=np.int64))
+                    yield Sequence(win[:-1].clone(), targets=win[1:].clone(), seq_id=sid)
+                    sid += 1
+            if not self.loop:
+                return
+
+
+PROMPT_TEMPLATE = "Instruction:\n{instruction}\n\nResponse:\n"
+
+
+def normalise_sft_record(rec: dict) -> Optional[Dict[str, str]]:
+    """Accepts ``instruction/output``, ``prompt/completion``, ``question/answer`` or chat ``messages``."""
+    for a, b in (("instruction", "output"), ("prompt", "completion"), ("question", "answer"), ("input", "output"),
+                 ("instruction", "response")):
+        if a in rec and b in rec:
+            ins = rec[a]
+            if a == "instruction" and rec.get("input"):
+                ins = f"{ins}\n{rec['input']}"
+            return {"instruction": str(ins), "response": str(rec[b])}
+    msgs = rec.get("messages") or rec.get("conversations")
+    if msgs:
+        user = [m for m in msgs if m.get("role", m.get("from")) in ("user", "human")]
+        asst = [m for m in msgs if m.get("role", m.get("from")) in ("assistant", "gpt")]
+        if user and asst:
+            return {"instruction": str(user[0].get("content", user[0].get("value", ""))),
+                    "response": str(asst[0].get("content", asst[0].get("value", ""))), "messages": msgs}
+    return None
+
+
+class JsonSFTTokenSource(_QueueMixin):
+    """JSON / JSONL SFT records tokenised by a background thread; loss only on response tokens
+    (flextrain/io/sources.py:238-790).  Generic wrapper
+    ``"Instruction:\\n{instruction}\\n\\nResponse:\\n{response}<EOS>"`` with ``add_special_tokens=False``, or the
+    tokenizer's own chat template with ``apply_chat_template=True``.  Records longer than ``max_seq_len`` are
+    dropped, or have their response truncated with ``truncate_long=True``."""
+
+    def __init__(self, path: str, tokenizer, max_seq_len: int, *, apply_chat_template: bool = False,
+                 truncate_long: bool = False, loop: bool = True, prefetch: int = 256, shuffle_seed: Optional[int] = None):
+        self.path, self.tok, self.max_seq_len = path, tokenizer, max_seq_len
+        self.chat, self.truncate, self.loop = apply_chat_template, truncate_long, loop
+        self.records = self._load(path)
+        if shuffle_seed is not None:
+            rng = np.random.default_rng(shuffle_seed)
+            rng.shuffle(self.records)
+        self.dropped = 0
+        self._q: "queue.Queue" = queue.Queue(maxsize=prefetch)
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._producer, daemon=True)
+        self._thread.start()
+        self._init_queue()
+        self._it = self._consume()
+
+    @staticmethod
+    def _load(path: str) -> List[dict]:
+        with open(path) as f:
+            txt = f.read().strip()
+        if txt.startswith("["):
+            return json.loads(txt)
+        return [json.loads(line) for line in txt.splitlines() if line.strip()]
+
+    def encode(self, rec: dict) -> Optional[Sequence]:
+        r = normalise_sft_record(rec)
+        if r is None:
+            return None
+        eos = getattr(self.tok, "eos_token_id", None)
+        if self.chat and hasattr(self.tok, "apply_chat_template"):
+            msgs = r.get("messages") or [{"role": "user", "content": r["instruction"]},
+                                         {"role": "assistant", "content": r["response"]}]
+            full = self.tok.apply_chat_template(msgs, tokenize=True)
+            prompt = self.tok.apply_chat_template(msgs[:-1], tokenize=True, add_generation_prompt=True)
+            p_ids, f_ids = list(prompt), list(full)
+        else:
+            p_ids = self.tok.encode(PROMPT_TEMPLATE.format(instruction=r["instruction"]), add_special_tokens=False)
+            r_ids = self.tok.encode(r["response"], add_special_tokens=False)
+            f_ids = list(p_ids) + list(r_ids) + ([eos] if eos is not None else [])
+        if len(f_ids) > self.max_seq_len:
+            if not self.truncate or len(p_ids) >= self.max_seq_len:
+                return None
+            f_ids = f_ids[: self.max_seq_len]
+        toks = torch.tensor(f_ids, dtype=torch.int64)
+        tgt = torch.roll(toks, -1)
+        tgt[-1] = IGNORE
+        tgt[: max(len(p_ids) - 1, 0)] = IGNORE        # positions whose next token is still prompt
+        return Sequence(toks, targets=tgt)
+
+    def _producer(self):
+        sid = 0
+        while not self._stop.is_set():
+            for rec in self.records:
+                if self._stop.is_set():
+                    return
+                s = self.encode(rec)
+                if s is None:
+                    self.dropped += 1
+                    continue
+                s.seq_id = sid
+                sid += 1
+                self._q.put(s)
+            if not self.loop:
+                self._q.put(None)
+                return
+
+    def _consume(self):
+        while True:
+            s = self._q.get()
+            if s is None:
+                return
+            yield s
+
+    def close(self):
+        self._stop.set()
+
+
+class CustomSchemaTokenSource(_QueueMixin):
+    """Records mapped to ``(prompt_text, response_text)`` by a user function, then tokenised like SFT."""
+
+    def __init__(self, records: Iterable[dict], to_pair: Callable[[dict], tuple], tokenizer, max_seq_len: int):
+        self._sft = JsonSFTTokenSource.__new__(JsonSFTTokenSource)
+        self._sft.tok, self._sft.max_seq_len, self._sft.chat, self._sft.truncate = tokenizer, max_seq_len, False, False
+        self.records, self.to_pair = list(records), to_pair
+        self._init_queue()
+        self._it = self._generate()
+
+    def _generate(self):
+        sid = 0
+        for rec in self.records:
+            p, r = self.to_pair(rec)
+            s = self._sft.encode({"instruction": p, "output": r})
+            if s is not None:
+                s.seq_id = sid
+                sid += 1
+                yield s
+
+
+class HFTokenSource(_QueueMixin):
+    """Streaming HuggingFace ``datasets`` adapter: text column → tokens → ``seq_len`` windows
+    (flextrain/io/sources.py:1108). Needs the ``datasets`` package and network or a local cache."""
+
+    def __init__(self, dataset: str, tokenizer, seq_len: int, split: str = "train", text_column: str = "text",
+                 name: Optional[str] = None):
+        try:
+            import datasets
+        except ImportError as e:   # pragma: no cover
+            raise ImportError("HFTokenSource needs the `datasets` package") from e
+        self.ds = datasets.load_dataset(dataset, name, split=split, streaming=True)
+        self.tok, self.seq_len, self.col = tokenizer, seq_len, text_column
+        self._init_queue()
+        self._it = self._generate()
+
+    def _generate(self):
+        buf: List[int] = []
+        sid = 0
+        for row in self.ds:
+            buf += self.tok.encode(row[self.col]) + [self.tok.eos_token_id or 0]
+            while len(buf) > self.seq_len:
+                win = torch.tensor(buf[: self.seq_len + 1], dtype=torch.int64)
+                buf = buf[self.seq_len:]
+                yield Sequence(win[:-1].clone(), targets=win[1:].clone(), seq_id=sid)
+                sid += 1

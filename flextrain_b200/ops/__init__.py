@@ -1,0 +1,352 @@
+"""Op layer: one function per primitive, CUDA kernel on a B200, PyTorch fp32 oracle on CPU.
+
+The layers in ``flextrain_b200.nn`` call only these functions, so the same model code runs the
+CPU parity configuration and the sm_100a kernels.  Mirrors the role of the reference project's
+``flextrain/ops/__init__.py:77-120`` export list.
+
+Backends (``set_gemm_backend`` / ``set_attention_backend``):
+  * GEMM       ``tcgen05`` (hand-written kernel, default on CUDA) | ``library`` (torch.matmul → cuBLAS)
+  * attention  ``ftb`` (hand-written kernel) | ``library`` (torch's bundled flash kernels) | ``reference``
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from . import reference as ref
+
+_GEMM_BACKEND = os.environ.get("FTB_GEMM_BACKEND", "tcgen05")
+_ATTN_BACKEND = os.environ.get("FTB_ATTN_BACKEND", "auto")
+_launches = 0          # number of kernels of this package launched (bench.py reports it)
+
+
+def set_gemm_backend(name: str) -> None:
+    global _GEMM_BACKEND
+    assert name in ("tcgen05", "library")
+    _GEMM_BACKEND = name
+
+
+def set_attention_backend(name: str) -> None:
+    """``auto`` | ``ftb`` | ``library`` | ``reference`` (flextrain/ops/_kernels/attention.py:133)."""
+    global _ATTN_BACKEND
+    assert name in ("auto", "ftb", "library", "reference", "eager")
+    _ATTN_BACKEND = "reference" if name == "eager" else name
+
+
+def get_attention_backend() -> str:
+    return _ATTN_BACKEND
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def _count(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+def _cuda_bf16(*ts) -> bool:
+    return all(t is None or (t.is_cuda and t.dtype == torch.bfloat16) for t in ts) and ts[0].is_cuda
+
+
+def _kernels():
+    from . import cuda
+    return cuda
+
+
+# ------------------------------------------------------------------------------- GEMM
+def gemm(a, b, *, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, bias=None, out=None, out_dtype=None):
+    """``alpha * op(a) @ op(b) + beta * c (+ bias)``; fp32 accumulation; see ``reference.gemm``."""
+    if a.is_cuda:
+        od = out_dtype or (out.dtype if out is not None else a.dtype)
+        k = _kernels()
+        M = a.shape[1] if trans_a else a.shape[0]
+        N = b.shape[0] if trans_b else b.shape[1]
+        K = a.shape[0] if trans_a else a.shape[1]
+        if (_GEMM_BACKEND == "tcgen05" and k.gemm_supported(a, b, trans_a, trans_b, od) and N >= 64 and K >= 64
+                and M >= 1 and (out is None or (out.stride(-1) == 1 and out.data_ptr() % 16 == 0))
+                and (bias is None or bias.dtype == torch.float32)):
+            _count()
+            return k.gemm(a, b, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, c=c, bias=bias, out=out,
+                          out_dtype=od)
+        # library GEMM for shapes the tensor-core kernel does not take (tiny N / K, odd strides)
+        A = a.t() if trans_a else a
+        B = b.t() if trans_b else b
+        if od == a.dtype and b.dtype == a.dtype:
+            d = torch.matmul(A, B)
+            if alpha != 1.0:
+                d = d * alpha
+        else:
+            d = torch.matmul(A.to(torch.float32), B.to(torch.float32)) * alpha
+        if beta != 0.0:
+            src = c if c is not None else out
+            d = d.to(torch.float32) + beta * src.to(torch.float32)
+        if bias is not None:
+            d = d + bias
+        if out is not None:
+            out.copy_(d)
+            return out
+        return d.to(od)
+    return ref.gemm(a, b, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, c=c, bias=bias, out=out,
+                    out_dtype=out_dtype)
+
+
+def linear_fwd(x, w, *, bias=None, residual=None, out=None):
+    """``y = x @ w.T (+ bias) (+ residual)`` with ``w (out, in)``; residual add fused in the epilogue."""
+    if residual is not None:
+        return gemm(x, w, trans_b=True, beta=1.0, c=residual, bias=bias, out=out)
+    return gemm(x, w, trans_b=True, bias=bias, out=out)
+
+
+def linear_dgrad(dy, w, *, out=None, accumulate=False):
+    """``dx = dy @ w`` (``w (out, in)``), optionally accumulated into ``out``."""
+    return gemm(dy, w, beta=1.0 if accumulate else 0.0, out=out)
+
+
+def linear_wgrad(dy, x, gw, *, alpha=1.0, accumulate=True):
+    """``gw (out, in) (+)= alpha * dy.T @ x`` in the gradient's dtype (bf16 or fp32)."""
+    return gemm(dy, x, trans_a=True, alpha=alpha, beta=1.0 if accumulate else 0.0, out=gw)
+
+
+def bias_grad(dy, gb, *, alpha=1.0, accumulate=True):
+    s = dy.to(torch.float32).sum(0) * alpha
+    if accumulate:
+        gb.add_(s.to(gb.dtype))
+    else:
+        gb.copy_(s)
+
+
+# --------------------------------------------------------------------------- norms / rope / glu
+def rmsnorm_fwd(x, w, eps):
+    if _cuda_bf16(x) and (w is None or w.dtype == torch.float32):
+        _count()
+        return _kernels().rmsnorm_fwd(x.contiguous(), w, eps)
+    return ref.rmsnorm_fwd(x, w, eps)
+
+
+def rmsnorm_bwd(dy, x, w, rstd, *, dx_add=None, emit_y=False, dw_out=None):
+    """Returns ``(dx, y)``; ``dw`` is accumulated into ``dw_out`` (fp32 or grad dtype)."""
+    if _cuda_bf16(dy, x) and (w is None or w.dtype == torch.float32) and (dw_out is None or dw_out.dtype == torch.float32):
+        _count(2)
+        dx, _, y = _kernels().rmsnorm_bwd(dy.contiguous(), x.contiguous(), w, rstd.contiguous(), dx_add=dx_add,
+                                          emit_y=emit_y, dw_out=dw_out)
+        return dx, y
+    dx, dw = ref.rmsnorm_bwd(dy, x, w, rstd)
+    if dx_add is not None:
+        dx = (dx.to(torch.float32) + dx_add.to(torch.float32)).to(dx.dtype)
+    if dw_out is not None and dw is not None:
+        dw_out.add_(dw.reshape(dw_out.shape).to(dw_out.dtype))
+    y = ref.rmsnorm_fwd(x, w, 0.0)[0] if False else None
+    if emit_y:
+        xf = x.to(torch.float32) * rstd.unsqueeze(-1)
+        y = (xf * w.to(torch.float32) if w is not None else xf).to(x.dtype)
+    return dx, y
+
+
+def rope(x, positions, inv_freq, *, out=None, inverse=False, mrope_sections=None):
+    """RoPE on ``x (T,H,hd)`` (token-strided views allowed) written to ``out`` (in place when None)."""
+    if _cuda_bf16(x) and x.stride(2) == 1 and x.stride(1) == x.shape[2] and \
+            (out is None or (out.stride(2) == 1 and out.stride(1) == out.shape[2])):
+        _count()
+        return _kernels().rope(x, positions.to(torch.int32).contiguous(), inv_freq, out=out, inverse=inverse,
+                               mrope_sections=mrope_sections)
+    y = ref.rope_apply(x, positions, inv_freq, inverse=inverse, mrope_sections=mrope_sections)
+    if out is None:
+        x.copy_(y)
+        return x
+    out.copy_(y)
+    return out
+
+
+def glu_fwd(gate, up, kind="swiglu"):
+    if _cuda_bf16(gate, up):
+        _count()
+        return _kernels().glu_fwd(gate, up, kind)
+    return ref.glu_fwd(gate, up, kind)
+
+
+def glu_bwd(dact, gate, up, kind="swiglu", *, dgate=None, dup=None):
+    """Returns ``(dgate, dup, act)``."""
+    if _cuda_bf16(dact, gate, up):
+        _count()
+        return _kernels().glu_bwd(dact, gate, up, kind, dgate=dgate, dup=dup)
+    dg, du, act = ref.glu_bwd(dact, gate, up, kind)
+    if dgate is not None:
+        dgate.copy_(dg); dup.copy_(du)
+        return dgate, dup, act
+    return dg, du, act
+
+
+# -------------------------------------------------------------------------- attention
+def _attn_backend_for(q) -> str:
+    if not q.is_cuda or q.dtype not in (torch.bfloat16, torch.float16):
+        return "reference"
+    if _ATTN_BACKEND == "auto":
+        from . import cuda
+        return "ftb" if cuda.have("attention") and q.shape[-1] in (64, 128) else "library"
+    return _ATTN_BACKEND
+
+
+def attention_fwd(q, k, v, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, softcap=0.0):
+    """Varlen GQA attention, bottom-right aligned causal. Returns ``(out (Tq,H,hd), lse (H,Tq) fp32)``."""
+    be = _attn_backend_for(q)
+    if be == "ftb" and not softcap:
+        from . import attention_cuda
+        _count()
+        return attention_cuda.fwd(q, k, v, cu_q, cu_k, max_q, max_k, scale=scale, causal=causal, window=window)
+    if be in ("library", "ftb") and not softcap:
+        wl = (window - 1) if window and window > 0 else None
+        o, lse, _, _, _ = torch.ops.aten._flash_attention_forward(
+            q, k, v, cu_q.to(torch.int32), cu_k.to(torch.int32), max_q, max_k, 0.0, causal, False, scale=scale,
+            window_size_left=wl, window_size_right=0 if (wl is not None) else None)
+        return o, lse
+    return ref.attention_fwd(q, k, v, cu_q, cu_k, scale=scale, causal=causal, window=window, softcap=softcap)
+
+
+def attention_bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, softcap=0.0):
+    """Returns ``(dq, dk, dv)``; dk/dv span all visible keys."""
+    be = _attn_backend_for(q)
+    if be == "ftb" and not softcap:
+        from . import attention_cuda
+        _count(3)
+        return attention_cuda.bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, scale=scale, causal=causal,
+                                  window=window)
+    if be in ("library", "ftb") and not softcap:
+        wl = (window - 1) if window and window > 0 else None
+        rng = torch.zeros(2, dtype=torch.uint64, device=q.device)
+        unused = torch.empty(0, device=q.device)
+        dq, dk, dv = torch.ops.aten._flash_attention_backward(
+            dout, q, k, v, out, lse, cu_q.to(torch.int32), cu_k.to(torch.int32), max_q, max_k, 0.0, causal, rng, unused,
+            scale=scale, window_size_left=wl, window_size_right=0 if (wl is not None) else None)
+        return dq, dk, dv
+    return ref.attention_bwd(dout, q, k, v, out, lse, cu_q, cu_k, scale=scale, causal=causal, window=window,
+                             softcap=softcap)
+
+
+# ---------------------------------------------------------------------- loss / embed
+def softmax_ce_(logits, targets, *, grad_scale=1.0, softcap=0.0, loss_mask=None, ignore_index=-100):
+    """Fused softmax-CE: returns per-token loss; ``logits`` is overwritten with dlogits."""
+    if _cuda_bf16(logits) and logits.stride(1) == 1:
+        _count()
+        return _kernels().softmax_ce_(logits, targets.to(torch.int64), grad_scale=grad_scale, softcap=softcap,
+                                      loss_mask=loss_mask, ignore_index=ignore_index)
+    loss, dz = ref.softmax_ce_fwd_bwd(logits, targets, grad_scale=grad_scale, softcap=softcap, loss_mask=loss_mask,
+                                      ignore_index=ignore_index)
+    logits.copy_(dz)
+    return loss
+
+
+def embedding_fwd(tokens, table, scale=1.0):
+    if _cuda_bf16(table) and table.shape[1] % 8 == 0:
+        _count()
+        return _kernels().embedding_fwd(tokens.to(torch.int64).contiguous(), table, scale)
+    return ref.embedding_fwd(tokens, table, scale)
+
+
+def embedding_bwd(dy, tokens, grad_table, scale=1.0):
+    if dy.is_cuda and dy.dtype == torch.bfloat16 and grad_table.dtype in (torch.bfloat16, torch.float32) \
+            and grad_table.shape[1] % 8 == 0:
+        _count()
+        return _kernels().embedding_bwd(dy.contiguous(), tokens.to(torch.int64).contiguous(), grad_table, scale)
+    return ref.embedding_bwd(dy, tokens, grad_table, scale)
+
+
+# ------------------------------------------------------------------------- optimizers
+def adamw_multi(params, grads, ms, vs, *, lrs, wds, beta1, beta2, eps, step, grad_scale=1.0):
+    """Fused AdamW over a list of tensors (one launch per layer on CUDA)."""
+    ok = all(p.is_cuda and p.is_contiguous() and g.is_contiguous() and p.dtype in (torch.bfloat16, torch.float32)
+             and g.dtype in (torch.bfloat16, torch.float32) and m.dtype in (torch.bfloat16, torch.float32)
+             and m.dtype == v.dtype for p, g, m, v in zip(params, grads, ms, vs))
+    if ok and params:
+        _count((len(params) + 23) // 24)
+        return _kernels().adamw_multi(params, grads, ms, vs, lrs=list(lrs), wds=list(wds), beta1=beta1, beta2=beta2,
+                                      eps=eps, step=step, grad_scale=grad_scale)
+    for p, g, m, v, lr, wd in zip(params, grads, ms, vs, lrs, wds):
+        ref.adamw_step(p, g, m, v, lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=wd, step=step,
+                       grad_scale=grad_scale)
+
+
+def muon_step(p, g, mom, **kw):
+    return ref.muon_step(p, g, mom, **kw)
+
+
+# -------------------------------------------------------------------------------- MoE
+def topk_route(logits, k, mode="topk_then_softmax"):
+    if _cuda_bf16(logits) and logits.shape[1] <= 256 and k <= 16:
+        _count()
+        return _kernels().topk_route(logits, k, mode)
+    return ref.topk_route(logits, k, mode)
+
+
+topk_route_bwd = ref.topk_route_bwd
+moe_sort = ref.moe_sort
+
+
+def gather_rows(x, idx, weights=None, idx_div=1):
+    """``out[i] = x[idx[i] // idx_div] * weights[i]``."""
+    if _cuda_bf16(x) and x.shape[1] % 8 == 0 and x.is_contiguous():
+        _count()
+        return _kernels().gather_rows(x, idx.to(torch.int32).contiguous(), weights, idx_div)
+    src = idx.long()
+    y = x[(src.clamp(min=0) // idx_div)] * (src >= 0).unsqueeze(-1).to(x.dtype)
+    if weights is not None:
+        y = (y.to(torch.float32) * weights.unsqueeze(-1)).to(x.dtype)
+    return y
+
+
+def moe_combine(y, inv, weights, resid):
+    """``out[t] = resid[t] + sum_k weights[t,k] * y[inv[t,k]]`` in fp32."""
+    if _cuda_bf16(y) and y.shape[1] % 8 == 0 and y.is_contiguous():
+        _count()
+        return _kernels().moe_combine(y, inv.to(torch.int32).contiguous(), weights, resid)
+    g = y[inv.long()].to(torch.float32)                       # (T,K,D)
+    if weights is not None:
+        g = g * weights.unsqueeze(-1)
+    out = g.sum(1)
+    if resid is not None:
+        out = out + resid.to(torch.float32)
+    return out.to(y.dtype)
+
+
+def grouped_gemm(x, w, offsets, *, trans_w=True):
+    if _cuda_bf16(x, w) and _GEMM_BACKEND == "tcgen05" and x.shape[1] % 8 == 0 and w.is_contiguous() \
+            and (w.shape[1] if trans_w else w.shape[2]) % 8 == 0 and x.shape[1] >= 64:
+        _count()
+        return _kernels().grouped_gemm(x.contiguous(), w, offsets.to(torch.int32), trans_w=trans_w)
+    return ref.grouped_gemm(x, w, offsets, trans_w=trans_w)
+
+
+grouped_wgrad = ref.grouped_wgrad
+
+
+# ---------------------------------------------------------------------- linear attention
+def l2norm_fwd(x, eps=1e-6):
+    if _cuda_bf16(x) and x.is_contiguous():
+        _count()
+        return _kernels().l2norm_fwd(x, eps)
+    return ref.l2norm_fwd(x, eps)
+
+
+l2norm_bwd = ref.l2norm_bwd
+
+
+def gated_rmsnorm_fwd(o, z, w, eps):
+    if _cuda_bf16(o, z) and w.dtype == torch.float32 and o.is_contiguous() and z.is_contiguous():
+        _count()
+        return _kernels().gated_rmsnorm_fwd(o, z, w, eps)
+    return ref.gated_rmsnorm_fwd(o, z, w, eps)
+
+
+causal_conv1d_fwd = ref.causal_conv1d_fwd
+gated_delta_rule = ref.gated_delta_rule
+gated_delta_rule_chunked = ref.gated_delta_rule_chunked
+top_p_sample = ref.top_p_sample
+rope_inv_freq = ref.rope_inv_freq
