@@ -79,10 +79,13 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
     return am
 
 
-def _init_random_weights(am: ActiveModel, seed: int, std: float) -> None:
+def _init_random_weights(am: ActiveModel, seed: int, std: float, on_device: bool = False) -> None:
     """Deterministic init (flextrain/api.py:699-742): names containing ``norm`` → 1, biases → 0, LoRA skipped,
     everything else ``N(0, std)`` drawn in fp32 on a CPU generator in embed → head → layers order."""
     g = torch.Generator().manual_seed(seed)
+    dev_gen = None
+    if on_device and torch.device(am.device).type == "cuda":
+        dev_gen = torch.Generator(device=am.device).manual_seed(seed)
     specs = {}
     for n in am.embed.param_spec.tensors:
         specs[("embed", -1, n.name)] = n
@@ -101,6 +104,9 @@ def _init_random_weights(am: ActiveModel, seed: int, std: float) -> None:
             t.fill_(1.0)
         elif spec.init == "zeros" or name.startswith("b_"):
             t.zero_()
+        elif dev_gen is not None and t.is_cuda:
+            # large models: draw on the GPU (same distribution, different stream of numbers than the CPU generator)
+            t.normal_(0.0, std, generator=dev_gen)
         else:
             t.copy_((torch.randn(t.shape, generator=g, dtype=torch.float32) * std).to(t.dtype))
     if am.head.tied:
@@ -132,7 +138,7 @@ def from_dims(dims: Mapping, *, arch: str = "llama", optimizer, max_seq_len: int
               min_chunk_size: Optional[int] = None, max_chunk_size: Optional[int] = None, moe_backend=None,
               working_set: Optional[WorkingSetConfig] = None, world_size: int = 1, rank: int = 0,
               dp_shard: Optional[str] = None, tp: int = 1, ep: int = 1, process_group=None, host_backend=None,
-              init_weights: bool = True) -> ActiveModel:
+              init_weights: bool = True, init_on_device: bool = False) -> ActiveModel:
     """Build an :class:`ActiveModel` from a dims dict with deterministic random weights; bypasses HF entirely."""
     mod = select_arch_module(arch)
     hyper = dict(mod.default_hyperparams()) if hasattr(mod, "default_hyperparams") else {}
@@ -153,7 +159,7 @@ def from_dims(dims: Mapping, *, arch: str = "llama", optimizer, max_seq_len: int
                              host_backend=host_backend)
     am.dims = dict(dims)
     if init_weights:
-        _init_random_weights(am, init_seed, init_std)
+        _init_random_weights(am, init_seed, init_std, on_device=init_on_device)
     if lora is not None:
         _init_lora_params(am, lora_init_seed, lora_a_std)
     if am.dp is not None:

@@ -178,11 +178,16 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
     tier0_tok = sum(a[0] for a in mm.act_tier_per_token)
 
     best: Optional[Tuple[float, WorkingSetConfig]] = None
-    modes = [shard] if shard is not None else (SHARD_MODES if dp > 1 else ("none",))
+    # With dp > 1 the engine always reduce-scatters gradients into an fp32 shard and runs the optimizer on the
+    # shard ("opt+grad"); "opt+grad+param" additionally keeps only 1/dp of the parameters between uses.
+    modes = [shard] if shard is not None else (("opt+grad", "opt+grad+param") if dp > 1 else ("none",))
     for mode in modes:
         p = P / dp if mode == "opt+grad+param" else P
-        g = G / dp if mode in ("opt+grad", "opt+grad+param") else G
+        # local bf16 gradients stay full-size while rounds accumulate; the reduced fp32 shard is 2x bytes / dp
+        g = G + (2 * G / dp if (dp > 1 and mode != "none") else 0)
         o = O / dp if mode != "none" else O
+        # optimizer update traffic through HBM (params r/w, grads r, state r/w)
+        opt_ms = hw.bytes_to_ms((2 * P + G + 2 * O) / (dp if mode != "none" else 1), "hbm")
         # NVLink traffic per step and rank: gradient reduce-scatter (+ all-gather of the reduced grads when not
         # sharded), parameter all-gather after the sharded update, parameter all-gathers per pass when sharded
         nv = 0.0
@@ -252,7 +257,7 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
                 pcie_ms = hw.bytes_to_ms(pcie_total / 2, "pcie")      # both directions run concurrently
                 comp = compute_ms_step * (1 + recompute / 3)
                 # transfers overlap compute; what exceeds it is exposed
-                est = max(comp, pcie_ms, nv_ms) + 0.05 * (pcie_ms + nv_ms)
+                est = max(comp, pcie_ms, nv_ms) + 0.05 * (pcie_ms + nv_ms) + opt_ms + 2.0 * n_rounds
                 cfg = WorkingSetConfig(
                     target_round_tokens=round_tokens, max_chunk_size=chunk,
                     max_training_chunks=2 * math.ceil(round_tokens / chunk) + 2,

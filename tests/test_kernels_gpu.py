@@ -1,0 +1,229 @@
+"""sm_100a kernels against the plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from flextrain_b200 import ops
+from flextrain_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device=DEV) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (384, 1024, 320), (200, 264, 136), (1000, 72, 4096)])
+def test_gemm_layouts(ta, tb, M, N, K):
+    from flextrain_b200.ops import cuda as k
+    if (ta and M % 8) or ((not tb) and N % 8):
+        pytest.skip("leading dimension must be a multiple of 8")
+    a = _rand(K, M) if ta else _rand(M, K)
+    b = _rand(N, K) if tb else _rand(K, N)
+    out = k.gemm(a, b, trans_a=ta, trans_b=tb)
+    want = ref.gemm(a, b, trans_a=ta, trans_b=tb, out_dtype=torch.float32)
+    assert _rel(out, want) < 5e-3, (ta, tb, M, N, K, _rel(out, want))
+    assert k.device_error_words().get("gemm_tcgen05", 0) == 0
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_epilogue_alpha_beta_bias(out_dtype):
+    from flextrain_b200.ops import cuda as k
+    M, N, K = 512, 768, 1024
+    a, b = _rand(M, K), _rand(N, K)
+    c = _rand(M, N, dtype=out_dtype)
+    bias = torch.randn(N, device=DEV)
+    out = k.gemm(a, b, trans_b=True, alpha=0.5, beta=2.0, c=c, bias=bias, out_dtype=out_dtype)
+    want = 0.5 * (a.float() @ b.float().t()) + 2.0 * c.float() + bias
+    assert _rel(out, want) < 6e-3
+    # in-place accumulate (wgrad pattern)
+    acc = c.clone()
+    k.gemm(a, b, trans_b=True, beta=1.0, out=acc)
+    assert _rel(acc, a.float() @ b.float().t() + c.float()) < 6e-3
+
+
+def test_gemm_large_matches_cublas():
+    from flextrain_b200.ops import cuda as k
+    M, N, K = 4096, 4096, 4096
+    a, b = _rand(M, K), _rand(N, K)
+    out = k.gemm(a, b, trans_b=True)
+    want = a @ b.t()
+    assert _rel(out, want) < 3e-3
+    # strided A (a column slice of a wider buffer, as produced by a fused QKV projection)
+    wide = _rand(M, 2 * K)
+    out2 = k.gemm(wide[:, K:], b, trans_b=True)
+    assert _rel(out2, wide[:, K:].float() @ b.float().t()) < 5e-3
+
+
+def test_grouped_gemm():
+    from flextrain_b200.ops import cuda as k
+    E, K, N = 8, 256, 384
+    counts = [0, 128, 256, 0, 384, 128, 128, 256]
+    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    R = int(off[-1])
+    x = _rand(R, K)
+    w = _rand(E, N, K, scale=0.1)
+    y = k.grouped_gemm(x, w, off, trans_w=True)
+    want = ref.grouped_gemm(x, w, off, trans_w=True)
+    assert _rel(y, want) < 6e-3
+    w2 = _rand(E, K, N, scale=0.1)
+    y2 = k.grouped_gemm(x, w2, off, trans_w=False)
+    assert _rel(y2, ref.grouped_gemm(x, w2, off, trans_w=False)) < 6e-3
+
+
+@pytest.mark.parametrize("T,D", [(7, 256), (300, 4096), (64, 5120)])
+def test_rmsnorm(T, D):
+    x, w = _rand(T, D), torch.rand(D, device=DEV) + 0.5
+    y, r = ops.rmsnorm_fwd(x, w, 1e-5)
+    yw, rw = ref.rmsnorm_fwd(x, w, 1e-5)
+    assert _rel(y, yw) < 5e-3 and _rel(r, rw) < 1e-4
+    dy, res = _rand(T, D), _rand(T, D)
+    dw = torch.zeros(D, device=DEV)
+    dx, yy = ops.rmsnorm_bwd(dy, x, w, r, dx_add=res, emit_y=True, dw_out=dw)
+    dxw, dww = ref.rmsnorm_bwd(dy, x, w, rw)
+    assert _rel(dx, dxw.float() + res.float()) < 6e-3
+    assert _rel(dw, dww) < 5e-3 and _rel(yy, yw) < 5e-3
+
+
+def test_rmsnorm_per_head():
+    x, w = _rand(50, 8, 128), torch.rand(128, device=DEV) + 0.5
+    y, r = ops.rmsnorm_fwd(x, w, 1e-6)
+    yw, rw = ref.rmsnorm_fwd(x, w, 1e-6)
+    assert _rel(y, yw) < 5e-3 and r.shape == (50, 8)
+    dy = _rand(50, 8, 128)
+    dw = torch.zeros(128, device=DEV)
+    dx, _ = ops.rmsnorm_bwd(dy, x, w, r, dw_out=dw)
+    dxw, dww = ref.rmsnorm_bwd(dy, x, w, rw)
+    assert _rel(dx, dxw) < 6e-3 and _rel(dw, dww) < 5e-3
+
+
+@pytest.mark.parametrize("partial", [1.0, 0.25])
+def test_rope_strided_and_inverse(partial):
+    T, H, hd = 77, 8, 128
+    inv = ref.rope_inv_freq(hd, 5e5, rotary_dim=int(hd * partial)).to(DEV)
+    pos = torch.randint(0, 100000, (T,), device=DEV, dtype=torch.int32)
+    wide = _rand(T, 3 * H * hd)
+    x = wide[:, H * hd: 2 * H * hd].unflatten(1, (H, hd))
+    out = torch.empty(T, H, hd, device=DEV, dtype=torch.bfloat16)
+    ops.rope(x, pos, inv, out=out)
+    want = ref.rope_apply(x, pos, inv)
+    assert _rel(out, want) < 6e-3
+    back = ops.rope(out.clone(), pos, inv, inverse=True)
+    assert _rel(back, x) < 1.5e-2
+
+
+def test_rope_mrope():
+    T, H, hd = 40, 4, 128
+    inv = ref.rope_inv_freq(hd, 1e6).to(DEV)
+    pos = torch.randint(0, 500, (T, 3), device=DEV, dtype=torch.int32)
+    x = _rand(T, H, hd)
+    out = ops.rope(x.clone(), pos, inv, mrope_sections=(24, 20, 20))
+    want = ref.rope_apply(x, pos, inv, mrope_sections=(24, 20, 20))
+    assert _rel(out, want) < 6e-3
+
+
+@pytest.mark.parametrize("kind", ["swiglu", "geglu"])
+def test_glu(kind):
+    T, F = 333, 1024
+    x13 = _rand(T, 2 * F)
+    g, u = x13[:, :F], x13[:, F:]
+    act = ops.glu_fwd(g, u, kind)
+    assert _rel(act, ref.glu_fwd(g, u, kind)) < 5e-3
+    d = _rand(T, F)
+    dg, du, a2 = ops.glu_bwd(d, g, u, kind)
+    wg, wu, wa = ref.glu_bwd(d, g, u, kind)
+    assert _rel(dg, wg) < 6e-3 and _rel(du, wu) < 6e-3 and _rel(a2, wa) < 5e-3
+
+
+@pytest.mark.parametrize("softcap", [0.0, 30.0])
+def test_softmax_ce(softcap):
+    T, V = 65, 32008
+    z = _rand(T, V, scale=3.0)
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    tgt[3] = -100
+    mask = torch.ones(T, device=DEV)
+    mask[5] = 0
+    lw, dzw = ref.softmax_ce_fwd_bwd(z, tgt, grad_scale=0.01, softcap=softcap, loss_mask=mask)
+    zz = z.clone()
+    loss = ops.softmax_ce_(zz, tgt, grad_scale=0.01, softcap=softcap, loss_mask=mask)
+    assert _rel(loss, lw) < 2e-3
+    assert _rel(zz, dzw) < 1e-2
+    assert float(loss[3]) == 0.0 and float(zz[5].abs().max()) == 0.0
+
+
+def test_embedding():
+    V, D, T = 1000, 512, 4096
+    table = _rand(V, D)
+    tok = torch.randint(0, 50, (T,), device=DEV)       # heavy duplication
+    y = ops.embedding_fwd(tok, table, 2.0)
+    assert _rel(y, ref.embedding_fwd(tok, table, 2.0)) < 5e-3
+    dy = _rand(T, D)
+    g = torch.zeros(V, D, device=DEV, dtype=torch.float32)
+    ops.embedding_bwd(dy, tok, g, 2.0)
+    gw = torch.zeros(V, D, dtype=torch.float32, device=DEV)
+    ref.embedding_bwd(dy, tok, gw, 2.0)
+    assert _rel(g, gw) < 1e-4
+
+
+def test_adamw_multi():
+    shapes = [(300, 40), (4096,), (128, 128), (7,)]
+    P = [_rand(*s) for s in shapes]
+    G = [_rand(*s, scale=0.1) for s in shapes]
+    M = [torch.zeros(*s, device=DEV) for s in shapes]
+    V = [torch.zeros(*s, device=DEV) for s in shapes]
+    P2, M2, V2 = [p.clone() for p in P], [m.clone() for m in M], [v.clone() for v in V]
+    for step in (1, 2):
+        ops.adamw_multi(P, G, M, V, lrs=[1e-2] * 4, wds=[0.1, 0.0, 0.1, 0.0], beta1=0.9, beta2=0.95, eps=1e-8, step=step)
+        for p, g, m, v, wd in zip(P2, G, M2, V2, [0.1, 0.0, 0.1, 0.0]):
+            ref.adamw_step(p, g, m, v, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=wd, step=step)
+    for p, q, m, n in zip(P, P2, M, M2):
+        assert _rel(p, q) < 5e-3 and _rel(m, n) < 1e-5
+
+
+@pytest.mark.parametrize("mode", ["topk_then_softmax", "softmax_then_topk"])
+def test_topk_route(mode):
+    T, E, K = 500, 128, 8
+    z = _rand(T, E, scale=2.0)
+    w, idx = ops.topk_route(z, K, mode)
+    ww, wi = ref.topk_route(z, K, mode)
+    assert torch.equal(idx.long(), wi.long())
+    assert _rel(w, ww) < 1e-3
+
+
+def test_moe_gather_combine():
+    T, K, D, E = 300, 4, 256, 16
+    idx = torch.randint(0, E, (T, K), device=DEV, dtype=torch.int32)
+    plan = ref.moe_plan(idx, E, 128)
+    x = _rand(T, D)
+    xs = ops.gather_rows(x, plan.row_src, idx_div=K)
+    src = plan.row_src.long()
+    want = x[src.clamp(min=0) // K] * (src >= 0).unsqueeze(1)
+    assert torch.equal(xs, want)
+    w = torch.rand(T, K, device=DEV)
+    y = _rand(plan.rows, D)
+    out = ops.moe_combine(y, plan.inv, w, x)
+    ref_out = (y[plan.inv.long()].float() * w.unsqueeze(-1)).sum(1) + x.float()
+    assert _rel(out, ref_out) < 5e-3
+
+
+def test_attention_library_matches_reference():
+    H, KV, hd = 8, 2, 128
+    lens_q, lens_k = [100, 64, 37], [100, 200, 37]
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32, device=DEV)
+    q, k, v = _rand(sum(lens_q), H, hd), _rand(sum(lens_k), KV, hd), _rand(sum(lens_k), KV, hd)
+    o, lse = ops.attention_fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5)
+    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, scale=hd ** -0.5)
+    assert _rel(o, ow) < 1e-2
+    do = _rand(sum(lens_q), H, hd)
+    dq, dk, dv = ops.attention_bwd(do, q, k, v, o, lse, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5)
+    wq, wk, wv = ref.attention_bwd(do, q, k, v, ow, lw, cu_q, cu_k, scale=hd ** -0.5)
+    assert _rel(dq, wq) < 2e-2 and _rel(dk, wk) < 2e-2 and _rel(dv, wv) < 2e-2
