@@ -86,7 +86,7 @@ class ActiveModel:
             [l.param_spec for l in self.layers], embed.param_spec, head.param_spec, optimizer, device,
             n_gpu_layers=ws.n_gpu_layers, n_gpu_grads=ws.n_gpu_grads, n_gpu_opt_layers=ws.n_gpu_opt_layers,
             host_backend=host_backend, kv_window_tokens=window, kv_heads=kvh, head_dim=hd, act_dtype=act_dtype,
-            host_act_bytes=ws.host_act_buffer_size, verbose=verbose)
+            host_act_bytes=ws.host_act_buffer_size, verbose=verbose, **(dp.buffer_kwargs() if dp is not None else {}))
         self.streams = StreamBundle.create(device, secondary=False)
         self.events = EventBook(self.streams)
         self._scheduler = None

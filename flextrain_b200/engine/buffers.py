@@ -56,7 +56,7 @@ class BufferManager:
                  *, n_gpu_layers: Optional[int] = None, n_gpu_grads: Optional[int] = None,
                  n_gpu_opt_layers: Optional[int] = None, host_backend: Optional[HostMemoryBackend] = None,
                  kv_window_tokens: int = 0, kv_heads: int = 0, head_dim: int = 0, act_dtype=torch.bfloat16,
-                 host_act_bytes: int = 0, verbose: bool = False):
+                 host_act_bytes: int = 0, verbose: bool = False, device_alloc=None, shard_opt: bool = False):
         self.device = torch.device(device)
         self.host = host_backend or default_backend(device)
         L = len(layer_specs)
@@ -69,18 +69,47 @@ class BufferManager:
         self.head = LayerBuffers(head_spec, optimizer)
         dev = self.device
         u8 = lambda n: torch.zeros(max(n, 1), dtype=torch.uint8, device=dev)
-        # ---- resident embed / head (params + grads + opt state)
-        self.embed_p, self.embed_g, self.embed_o = u8(self.embed.p_bytes), u8(self.embed.g_bytes), u8(self.embed.o_bytes)
-        self.head_p, self.head_g, self.head_o = u8(self.head.p_bytes), u8(self.head.g_bytes), u8(self.head.o_bytes)
-        # ---- per-layer state: resident buffers or rings + pinned host masters
         self.params_resident = self.n_p >= L
         self.grads_resident = self.n_g >= L
         self.opt_resident = self.n_o >= L
         maxp = max(lb.p_bytes for lb in self.layers)
         maxg = max(lb.g_bytes for lb in self.layers)
         maxo = max(lb.o_bytes for lb in self.layers)
-        self.gpu_p = [u8(lb.p_bytes) for lb in self.layers] if self.params_resident else [u8(maxp) for _ in range(self.n_p)]
-        self.gpu_g = [u8(lb.g_bytes) for lb in self.layers] if self.grads_resident else [u8(maxg) for _ in range(self.n_g)]
+        # ---- parameters / gradients: one arena each when a data-parallel group needs them peer-mapped
+        #      (unit order: embed, layer 0..L-1, head), else one buffer per unit
+        self.param_arena = self.grad_arena = None
+        self.p_off: Dict[object, int] = {}
+        self.g_off: Dict[object, int] = {}
+        if device_alloc is not None:
+            if not (self.params_resident and self.grads_resident):
+                raise ValueError("peer-mapped parameter / gradient arenas need resident parameters and gradients")
+            units = [("embed", self.embed)] + [(i, lb) for i, lb in enumerate(self.layers)] + [("head", self.head)]
+            po = go = 0
+            for key, lb in units:
+                self.p_off[key], self.g_off[key] = po, go
+                po += align_up(max(lb.p_bytes, 1)); go += align_up(max(lb.g_bytes, 1))
+            self.param_arena, self.grad_arena = device_alloc(po, "params"), device_alloc(go, "grads")
+            pa, ga = self.param_arena.local, self.grad_arena.local
+            cut = lambda arena, off, n: arena[off:off + max(n, 1)]
+            self.embed_p, self.embed_g = cut(pa, self.p_off["embed"], self.embed.p_bytes), cut(ga, self.g_off["embed"], self.embed.g_bytes)
+            self.head_p, self.head_g = cut(pa, self.p_off["head"], self.head.p_bytes), cut(ga, self.g_off["head"], self.head.g_bytes)
+            self.gpu_p = [cut(pa, self.p_off[i], lb.p_bytes) for i, lb in enumerate(self.layers)]
+            self.gpu_g = [cut(ga, self.g_off[i], lb.g_bytes) for i, lb in enumerate(self.layers)]
+            self.embed_o, self.head_o = u8(0 if shard_opt else self.embed.o_bytes), u8(0 if shard_opt else self.head.o_bytes)
+        else:
+            # ---- resident embed / head (params + grads + opt state)
+            self.embed_p, self.embed_g, self.embed_o = u8(self.embed.p_bytes), u8(self.embed.g_bytes), u8(self.embed.o_bytes)
+            self.head_p, self.head_g, self.head_o = u8(self.head.p_bytes), u8(self.head.g_bytes), u8(self.head.o_bytes)
+            # ---- per-layer state: resident buffers or rings + pinned host masters
+            self.gpu_p = [u8(lb.p_bytes) for lb in self.layers] if self.params_resident else [u8(maxp) for _ in range(self.n_p)]
+            self.gpu_g = [u8(lb.g_bytes) for lb in self.layers] if self.grads_resident else [u8(maxg) for _ in range(self.n_g)]
+        if shard_opt:
+            # optimizer state lives in the data-parallel group's shards, not here
+            self.gpu_o = [u8(0) for _ in self.layers]
+            self.opt_resident = True
+            self.host_p = self.host_g = self.host_o = None
+            self._finish_init(kv_window_tokens, kv_heads, head_dim, act_dtype, host_act_bytes)
+            return
         if self.opt_resident:
             self.gpu_o = [u8(lb.o_bytes) for lb in self.layers]
         else:
@@ -88,6 +117,10 @@ class BufferManager:
         self.host_p = None if self.params_resident else [self.host.alloc(lb.m_bytes) for lb in self.layers]
         self.host_g = None if self.grads_resident else [self.host.alloc(lb.g_bytes) for lb in self.layers]
         self.host_o = None if self.opt_resident else [self.host.alloc(lb.o_bytes) for lb in self.layers]
+        self._finish_init(kv_window_tokens, kv_heads, head_dim, act_dtype, host_act_bytes)
+
+    def _finish_init(self, kv_window_tokens, kv_heads, head_dim, act_dtype, host_act_bytes) -> None:
+        dev = self.device
         self._view_cache: Dict[Tuple[str, int], Dict[str, torch.Tensor]] = {}
         # ---- context windows
         self.kv_window = None

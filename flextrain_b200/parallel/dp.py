@@ -1,0 +1,247 @@
+"""Data parallelism over one NVSwitch box with sharded gradients and optimizer state.
+
+Two interchangeable back ends behind the same engine hooks:
+
+``P2PDataParallel`` (the product, CUDA):  parameters and gradients of all ranks live in peer-mapped
+arenas.  As soon as a layer's backward has finished on the last accumulation round, a comm stream runs
+(1) a flag exchange — "my gradients of layer l are final" — with a bounded wait for all peers, and
+(2) the fused reduce-scatter kernel: each rank sums ITS element range of the W gradient buffers straight
+out of peer memory, casts bf16→fp32, applies the ``1/tokens`` scale and writes a local fp32 shard.  This
+overlaps the backward of layer l-1.  ``step()`` then runs the sharded AdamW kernel, whose store loop
+writes the new bf16 parameters into every rank's parameter arena (the all-gather is fused into the
+optimizer), and closes with one flag barrier.  No NCCL call is made on this path.
+
+``CollectiveDataParallel`` (the baseline, any backend incl. gloo on CPU):  ``all_reduce`` of each
+layer's gradients, then the ordinary local optimizer on replicated state.
+
+The reference project is single-GPU; its closest analogue is gradient accumulation across rounds
+(flextrain/engine/active_model.py:338-411) and a design note proposing ZeRO-1 by layer
+(docs/internal/NOTES.md:2340-2385).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_uint, c_void_p
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..core.layer import itemsize
+from .comm import PeerGroup, shard_range
+
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+@dataclass
+class Segment:
+    """A run of same-dtype, equally treated tensors inside a unit's parameter and gradient buffers."""
+    p_off: int          # byte offset in the parameter arena
+    g_off: int          # byte offset in the gradient arena
+    numel: int
+    p_dtype: torch.dtype
+    g_dtype: torch.dtype
+    decay: bool
+    begin: int = 0      # this rank's range
+    count: int = 0
+    shard_off: int = 0  # element offset in the rank's fp32 shard arrays
+
+
+def build_segments(lb, p_base: int, g_base: int, no_decay_1d: bool = True) -> List[Segment]:
+    """Merge tensors that are adjacent in both buffers and share dtypes / decay into segments."""
+    segs: List[Segment] = []
+    for t in lb.spec.trainable():
+        po, pn, _, pdt = lb.p_layout[t.name]
+        go, gn, _, gdt = lb.g_layout[t.grad_name]
+        decay = not (no_decay_1d and len(t.shape) == 1)
+        s = Segment(p_base + po, g_base + go, t.numel, pdt, gdt, decay)
+        if segs:
+            q = segs[-1]
+            if (q.p_dtype == pdt and q.g_dtype == gdt and q.decay == decay
+                    and q.p_off + q.numel * itemsize(pdt) == s.p_off and q.g_off + q.numel * itemsize(gdt) == s.g_off):
+                q.numel += t.numel
+                continue
+        segs.append(s)
+    return segs
+
+
+class _Base:
+    def __init__(self, rank: int, world: int, device, process_group=None):
+        self.rank, self.world, self.device, self.pg = rank, world, torch.device(device), process_group
+        self.am = None
+
+    def attach(self, am) -> None:
+        self.am = am
+
+    def buffer_kwargs(self) -> dict:
+        return {}
+
+    def after_weights_loaded(self, am) -> None:
+        """Make every rank start from rank 0's weights."""
+        import torch.distributed as dist
+        for _, _, _, t in am.named_master_params():
+            dist.broadcast(t, src=0, group=self.pg)
+
+    def on_layer_grads_ready(self, layer: int) -> None: ...
+    def on_embed_head_grads_ready(self) -> None: ...
+
+
+class CollectiveDataParallel(_Base):
+    """Baseline: library all-reduce of every unit's gradient buffer + replicated optimizer."""
+
+    def _allreduce(self, buf: torch.Tensor, layout) -> None:
+        import torch.distributed as dist
+        for name, (off, nb, shape, dt) in layout.items():
+            dist.all_reduce(buf[off:off + nb].view(dt), group=self.pg)
+
+    def on_layer_grads_ready(self, layer: int) -> None:
+        bm = self.am.buffers
+        self._allreduce(bm.grad_buffer(layer), bm.layers[layer].g_layout)
+
+    def on_embed_head_grads_ready(self) -> None:
+        bm = self.am.buffers
+        self._allreduce(bm.embed_g, bm.embed.g_layout)
+        self._allreduce(bm.head_g, bm.head.g_layout)
+
+    def step(self, am) -> int:
+        return am._step_local()
+
+
+class P2PDataParallel(_Base):
+    def __init__(self, rank: int, world: int, device, process_group=None, timeout_s: float = 60.0):
+        super().__init__(rank, world, device, process_group)
+        self.group = PeerGroup(rank, world, device, process_group, timeout_s=timeout_s)
+        self.lib = self.group.lib
+        self.units: Dict[object, List[Segment]] = {}
+        self.grad_shard = self.m = self.v = None
+        self._reduced_epoch = 0
+
+    # ------------------------------------------------------------------- set-up
+    def buffer_kwargs(self) -> dict:
+        return {"device_alloc": lambda nbytes, tag: self.group.alloc(nbytes), "shard_opt": True}
+
+    def attach(self, am) -> None:
+        from ..optim import AdamW
+        if not isinstance(am.optimizer, AdamW):
+            raise TypeError("the peer-memory data-parallel path implements sharded AdamW; use the collective "
+                            "backend for Muon / hybrid optimizers")
+        self.am = am
+        bm = am.buffers
+        nd = am.optimizer.no_decay_1d
+        off = 0
+        keys = ["embed"] + list(range(len(am.layers))) + ["head"]
+        lbs = {"embed": bm.embed, "head": bm.head, **{i: lb for i, lb in enumerate(bm.layers)}}
+        for key in keys:
+            segs = build_segments(lbs[key], bm.p_off[key], bm.g_off[key], nd)
+            for s in segs:
+                s.begin, s.count = shard_range(s.numel, self.rank, self.world)
+                s.shard_off = off
+                off += (s.count + 7) // 8 * 8
+            self.units[key] = segs
+        n = max(off, 8)
+        f32 = lambda: torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.grad_shard, self.m, self.v = f32(), f32(), f32()
+        self.slot = {k: i for i, k in enumerate(keys)}
+        self.barrier_slot = len(keys)
+        self.comm_stream = am.streams.comm
+        self._ev = {}
+
+    # ---------------------------------------------------------------- kernel calls
+    def _tables(self, segs: List[Segment], kind: str):
+        n = len(segs)
+        arr = lambda vals, ct=c_long: (ct * n)(*vals)
+        if kind == "grad":
+            return n, arr([s.g_off for s in segs]), arr([s.begin for s in segs]), arr([s.count for s in segs]), \
+                arr([s.shard_off for s in segs]), arr([_DT[s.g_dtype] for s in segs], c_int)
+        return n, arr([s.p_off for s in segs]), arr([s.begin for s in segs]), arr([s.count for s in segs]), \
+            arr([s.shard_off for s in segs]), arr([_DT[s.p_dtype] for s in segs], c_int)
+
+    def _reduce_unit(self, key, scale: float, stream) -> None:
+        from .. import ops
+        segs = self.units[key]
+        bm = self.am.buffers
+        for i0 in range(0, len(segs), 16):
+            n, boff, beg, cnt, ooff, dts = self._tables(segs[i0:i0 + 16], "grad")
+            rc = self.lib.ftb_comm_reduce_scatter(bm.grad_arena.c_ptrs, c_int(n), boff, beg, cnt, ooff, dts,
+                                                  c_void_p(self.grad_shard.data_ptr()), c_int(self.world),
+                                                  c_int(self.rank), c_float(scale), c_void_p(stream.cuda_stream))
+            if rc != 0:
+                raise RuntimeError(f"ftb_comm_reduce_scatter failed ({rc})")
+            ops._count()
+
+    def _reduce(self, key) -> None:
+        """Flag exchange + fused reduce-scatter of one unit on the comm stream, after compute produced its grads."""
+        st = self.am.streams
+        cs = self.comm_stream
+        ev = torch.cuda.Event()
+        ev.record(st.compute)
+        cs.wait_event(ev)
+        self.group.signal_wait(self.slot[key], self._epoch, cs)
+        self._reduce_unit(key, 1.0, cs)
+
+    def on_layer_grads_ready(self, layer: int) -> None:
+        if self._reduced_epoch != self.am.step_num + 1:
+            self._epoch = self.group.next_epoch()
+            self._reduced_epoch = self.am.step_num + 1
+        self._reduce(layer)
+
+    def on_embed_head_grads_ready(self) -> None:
+        if self._reduced_epoch != self.am.step_num + 1:
+            self._epoch = self.group.next_epoch()
+            self._reduced_epoch = self.am.step_num + 1
+        self._reduce("embed")
+        self._reduce("head")
+
+    def step(self, am) -> int:
+        from .. import ops
+        opt = am.optimizer
+        cs = self.comm_stream
+        bm = am.buffers
+        step = am.step_num
+        bc1, bc2 = 1.0 - opt.beta1 ** step, 1.0 - opt.beta2 ** step
+        for key, segs in self.units.items():
+            for i0 in range(0, len(segs), 16):
+                part = segs[i0:i0 + 16]
+                n, boff, beg, cnt, ooff, dts = self._tables(part, "param")
+                mask = sum((1 << i) for i, s in enumerate(part) if s.decay)
+                rc = self.lib.ftb_comm_adamw_push(bm.param_arena.c_ptrs, c_int(n), boff, beg, cnt, ooff, dts,
+                                                  c_void_p(self.grad_shard.data_ptr()), c_void_p(self.m.data_ptr()),
+                                                  c_void_p(self.v.data_ptr()), c_int(self.world), c_int(self.rank),
+                                                  c_float(opt.lr), c_float(opt.beta1), c_float(opt.beta2),
+                                                  c_float(opt.eps), c_float(opt.weight_decay), c_float(bc1),
+                                                  c_float(bc2), c_uint(mask), c_void_p(cs.cuda_stream))
+                if rc != 0:
+                    raise RuntimeError(f"ftb_comm_adamw_push failed ({rc})")
+                ops._count()
+        # every peer's stores into my parameters have landed, and every peer is done reading my gradients
+        self.group.signal_wait(self.barrier_slot, self.group.next_epoch(), cs)
+        am.streams.compute.wait_stream(cs)
+        return 0
+
+    def check(self) -> None:
+        self.group.check()
+
+
+def emulate_sharded_step(grad_bufs: List[torch.Tensor], param_bufs: List[torch.Tensor], segs_per_rank, states, *,
+                         lr, beta1, beta2, eps, wd, step: int, scale: float = 1.0) -> None:
+    """Single-process statement of what the two kernels do over ``W`` ranks' buffers (CPU test oracle):
+    rank r reduces its ranges of all ``grad_bufs`` and writes the AdamW result into all ``param_bufs``."""
+    W = len(grad_bufs)
+    bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
+    for r in range(W):
+        m, v = states[r]
+        for s in segs_per_rank[r]:
+            if s.count == 0:
+                continue
+            gsz, psz = itemsize(s.g_dtype), itemsize(s.p_dtype)
+            g = sum(gb[s.g_off: s.g_off + s.numel * gsz].view(s.g_dtype)[s.begin:s.begin + s.count].to(torch.float32)
+                    for gb in grad_bufs) * scale
+            pv = param_bufs[r][s.p_off: s.p_off + s.numel * psz].view(s.p_dtype)[s.begin:s.begin + s.count]
+            p = pv.to(torch.float32)
+            sl = slice(s.shard_off, s.shard_off + s.count)
+            p = p - lr * (wd if s.decay else 0.0) * p
+            m[sl] = beta1 * m[sl] + (1 - beta1) * g
+            v[sl] = beta2 * v[sl] + (1 - beta2) * g * g
+            p = p - lr * (m[sl] / bc1) / ((v[sl] / bc2).sqrt() + eps)
+            for pb in param_bufs:
+                pb[s.p_off: s.p_off + s.numel * psz].view(s.p_dtype)[s.begin:s.begin + s.count] = p.to(s.p_dtype)

@@ -1,0 +1,54 @@
+"""Worker run under ``torch.distributed.run`` by test_dp_gpu.py: trains a small Llama for a few steps with the
+chosen data-parallel backend and writes rank 0's parameters and losses to a file."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import flextrain_b200 as ft  # noqa: E402
+
+
+def main():
+    backend, out_path = sys.argv[1], sys.argv[2]
+    os.environ["FTB_DP_BACKEND"] = backend
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    dist.init_process_group("nccl", device_id=torch.device(dev))
+    dims = dict(vocab_size=2048, n_layers=3, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, expert_dim=1408,
+                num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+    gb = 4096
+    am = ft.from_dims(dims, arch="llama", optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32, weight_decay=0.01),
+                      max_seq_len=256, max_global_batch_tokens=gb, max_gpu_mem_bytes=16 << 30,
+                      max_host_mem_bytes=16 << 30, device=dev, world_size=world, rank=rank,
+                      working_set=ft.WorkingSetConfig.simple(max_seq_len=256, max_global_batch_tokens=gb // world,
+                                                             chunk=1024, round_tokens=1024, world_size=world,
+                                                             shard="opt+grad"))
+    src = ft.SyntheticTokenSource(2048, 256, seed=11)
+    losses = []
+    for step in range(3):
+        seqs = src.get_sequences(gb)[rank::world]
+        st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / gb, total_tokens_per_step=gb)
+        assert am.step() == 0
+        t = torch.tensor([st.loss_sum], device=dev)
+        dist.all_reduce(t)
+        losses.append(float(t) / gb)
+    torch.cuda.synchronize()
+    if hasattr(am.dp, "check"):
+        am.dp.check()
+    flat = torch.cat([t.flatten().float().cpu() for _, _, _, t in am.named_master_params()])
+    allflat = [None] * world
+    dist.all_gather_object(allflat, flat)
+    if rank == 0:
+        same = all(torch.equal(allflat[0], f) for f in allflat)
+        from flextrain_b200.ops import cuda as k
+        torch.save({"params": flat, "losses": losses, "ranks_identical": same, "errors": k.device_error_words(),
+                    "libs": sorted(k._libs)}, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

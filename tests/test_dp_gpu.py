@@ -1,0 +1,37 @@
+"""Peer-memory data parallelism on 2+ B200s: fused reduce-scatter + sharded AdamW with parameter push, checked
+against the library-collective baseline (NCCL all-reduce + replicated AdamW)."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(backend, out, n):
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "dp_worker.py"), backend, out]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return torch.load(out)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_p2p_matches_collective(tmp_path):
+    n = min(torch.cuda.device_count(), 4)
+    a = _run("p2p", str(tmp_path / "p2p.pt"), n)
+    b = _run("collective", str(tmp_path / "coll.pt"), n)
+    assert a["ranks_identical"] and b["ranks_identical"]
+    assert "comm" in a["libs"], "peer-memory kernels were not loaded"
+    assert all(v == 0 for v in a["errors"].values()), a["errors"]
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 2e-2, (a["losses"], b["losses"])
+    d = (a["params"] - b["params"]).abs()
+    # the sharded path keeps fp32 reduced gradients, the baseline rounds the all-reduce to bf16: tiny drift only
+    assert float(d.mean()) < 2e-4 and float(d.max()) < 2e-2, (float(d.mean()), float(d.max()))
