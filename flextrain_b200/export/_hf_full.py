@@ -1,0 +1,30 @@
+"""Full HF-directory export (flextrain/export/_hf_full.py:311): sharded safetensors in checkpoint names,
+``config.json`` and tokenizer files.  No Q/K permutation has to be undone (weights never left the checkpoint's
+rotate-half layout); (1+w) norms are written back as ``gamma - 1``; MoE stacks and bundled linear-attention
+projections are split by the arch map's ``split`` callables."""
+from __future__ import annotations
+
+import json
+import os
+from typing import Optional
+
+from ..io.arch import select_arch_module
+from ..io.hf_weights import collect_hf_state
+from ._common import copy_aux_files, write_sharded_safetensors
+
+
+def save_hf_full(am, out_dir: str, *, max_shard_bytes: int = 5 << 30, source_dir: Optional[str] = None,
+                 _merge_lora: bool = False) -> str:
+    state = collect_hf_state(am, lora_merge=_merge_lora)
+    write_sharded_safetensors(state, out_dir, max_shard_bytes)
+    src = source_dir or am.model_dir
+    cfg = None
+    if src and os.path.exists(os.path.join(src, "config.json")):
+        with open(os.path.join(src, "config.json")) as f:
+            cfg = json.load(f)
+    if cfg is None:
+        cfg = select_arch_module(am.model_config.arch).to_hf_config(am.model_config)
+    with open(os.path.join(out_dir, "config.json"), "w") as f:
+        json.dump(cfg, f, indent=2)
+    copy_aux_files(src, out_dir)
+    return out_dir

@@ -1,0 +1,86 @@
+"""Every architecture family on CPU in fp32: hand-written forward/backward against autograd on the naive model."""
+import pytest
+import torch
+
+import flextrain_b200 as ft
+from flextrain_b200.bench.naive import clone_params, naive_loss
+from conftest import build_tiny
+
+BASE = dict(vocab_size=512, n_layers=2, d_model=128, n_heads=4, n_kv_heads=2, head_dim=32, expert_dim=256, ffn_dim=256,
+            num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+MOE = dict(BASE, expert_dim=64, num_routed_experts=8, top_k=2)
+
+CASES = {
+    "llama": ("llama", BASE, {}),
+    "llama3_rope_scaling": ("llama", BASE, {"rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                             "high_freq_factor": 4.0,
+                                                             "original_max_position_embeddings": 64}}),
+    "mistral_sliding": ("mistral", BASE, {"sliding_window": 16, "layer_pattern": "S"}),
+    "qwen2_bias": ("qwen2", BASE, {}),
+    "qwen3_qknorm": ("qwen3", BASE, {}),
+    "qwen3_moe": ("qwen3_moe", MOE, {}),
+    "olmoe": ("olmoe", MOE, {}),
+    "gemma2": ("gemma2", BASE, {"sliding_window": 16, "layer_pattern": "SF", "attn_softcap": 50.0, "final_softcap": 30.0}),
+    "gemma3": ("gemma3", BASE, {"sliding_window": 16, "layer_pattern": "SF"}),
+    "qwen3_next": ("qwen3_next", dict(MOE, num_shared_experts=1, shared_dim=64),
+                   {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 4, "head_k_dim": 16, "head_v_dim": 16}}),
+    "qwen3_5_dense": ("qwen3_5", BASE,
+                      {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 2, "head_k_dim": 16, "head_v_dim": 32}}),
+}
+
+
+def _check(am, seqs, rtol=3e-4, atol=3e-6):
+    P = clone_params(am)
+    loss = naive_loss(am, P, seqs)
+    loss.backward()
+    st = am.fwd_bwd(seqs)
+    assert abs(st.loss - float(loss.detach())) < 2e-4, (st.loss, float(loss))
+    bm = am.buffers
+    n = 0
+    for (scope, l, name), p in P.items():
+        g = {"embed": bm.embed_grads(), "head": bm.head_grads()}.get(scope) or bm.grads(l)
+        gname = "g_" + name[2:] if name.startswith("w_") else "g_" + name
+        if gname not in g:
+            continue
+        want = p.grad if p.grad is not None else torch.zeros_like(p)
+        torch.testing.assert_close(g[gname].float(), want, rtol=rtol, atol=atol, msg=f"{scope}/{l}/{name}")
+        n += 1
+    assert n > 5
+
+
+@pytest.mark.parametrize("case", sorted(CASES))
+def test_family_gradients(case):
+    arch, dims, hyper = CASES[case]
+    am = build_tiny(arch=arch, dims=dims, hyper=hyper, max_seq_len=48, batch_tokens=96)
+    torch.manual_seed(0)
+    # perturb norm weights and biases so their gradients are exercised away from the init point
+    for scope, l, name, t in am.named_master_params():
+        if "norm" in name or name.startswith("b_") or "dt_bias" in name or "A_log" in name:
+            t.add_(torch.randn_like(t) * 0.1)
+    seqs = ft.SyntheticTokenSource(dims["vocab_size"], [48, 40], seed=2).get_sequences(96)
+    _check(am, seqs)
+
+
+def test_lora_gradients():
+    am = build_tiny(dims=BASE, max_seq_len=48, batch_tokens=96, lora_targets="all", lora_rank=4, lora_alpha=8.0,
+                    lora_adapter_compute_dtype=torch.float32, lora_adapter_master_dtype=torch.float32,
+                    lora_adapter_grad_dtype=torch.float32, lora_adapter_opt_state_dtype=torch.float32)
+    torch.manual_seed(0)
+    for scope, l, name, t in am.named_master_params():
+        if name.endswith("_lora_b"):
+            t.copy_(torch.randn_like(t) * 0.05)
+    seqs = ft.SyntheticTokenSource(512, 48, seed=3).get_sequences(96)
+    P = clone_params(am)
+    naive_loss(am, P, seqs).backward()
+    am.fwd_bwd(seqs)
+    checked = 0
+    for l in range(2):
+        g = am.buffers.grads(l)
+        assert "g_q" not in g, "base weights must be frozen under LoRA"
+        for name in ("w_q", "w_v", "w_o", "w_1", "w_2", "w_3", "w_k"):
+            for ab in ("_lora_a", "_lora_b"):
+                torch.testing.assert_close(g["g_" + name[2:] + ab].float(), P[("layer", l, name + ab)].grad,
+                                           rtol=3e-4, atol=3e-6, msg=f"{l}/{name}{ab}")
+                checked += 1
+    assert checked == 28
+    assert am.step() == 0

@@ -1,0 +1,256 @@
+"""End-to-end training CLI (same flags as the reference's train.py:372-630, plus the parallel layout).
+
+    python train.py --model <hf dir | dims:<name>> --mode {full,lora} --max-seq-len N --max-global-batch-tokens N
+    python -m torch.distributed.run --nproc-per-node 8 train.py ... --dp-shard opt+grad
+
+Per step: LR schedule (linear warm-up → constant → cosine to ``final``), ``source.get_sequences``, the
+short-tail-round spill (sequences that would open an extra, nearly empty round go back to the source),
+``am.fwd_bwd`` + ``am.step``, and a log line with loss / tok/s / effective and hardware TFLOPS / memory.
+``--save`` writes ``final.safetensors`` in HF names.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import flextrain_b200 as ft  # noqa: E402
+from flextrain_b200.core.flop_accounting import step_flops_breakdown  # noqa: E402
+from flextrain_b200.core.memory import get_available_gpu_memory, get_available_host_memory  # noqa: E402
+from flextrain_b200.engine.schedule import split_sequences  # noqa: E402
+
+_DT = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}
+
+
+def lr_schedule(step: int, *, max_lr: float, final_lr: float, warmup_steps: int, cooldown_start: int,
+                total_steps: int) -> float:
+    """``step`` is 1-based. Linear warm-up ``max*step/warmup`` → ``max`` → cosine to ``final`` from ``cooldown_start``."""
+    if warmup_steps > 0 and step <= warmup_steps:
+        return max_lr * step / warmup_steps
+    if step <= cooldown_start or total_steps <= cooldown_start:
+        return max_lr
+    t = (step - cooldown_start) / max(1, total_steps - cooldown_start)
+    return final_lr + 0.5 * (max_lr - final_lr) * (1 + math.cos(math.pi * min(t, 1.0)))
+
+
+def build_arg_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="train.py")
+    p.add_argument("--model", required=True, help="HF model directory, or dims:<name> for a random-init catalogue model")
+    p.add_argument("--mode", choices=("full", "lora"), required=True)
+    p.add_argument("--max-seq-len", type=int, required=True)
+    p.add_argument("--max-global-batch-tokens", type=int, required=True)
+    p.add_argument("--truncate-long", action="store_true")
+    p.add_argument("--apply-chat-template", action="store_true")
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--data-source", choices=("json_sft", "synthetic", "shards"), default="json_sft")
+    p.add_argument("--dataset", default=os.path.join(ROOT, "flextrain_b200/configs/examples/data/tiny_math_sft.json"))
+    p.add_argument("--synthetic-seq-len", type=int, default=None)
+    p.add_argument("--output-dir", default=None)
+    p.add_argument("--lr", type=float, default=None)
+    p.add_argument("--lr-warmup-pct", type=float, default=0.1)
+    p.add_argument("--lr-cooldown-start-pct", type=float, default=0.8)
+    p.add_argument("--lr-final-pct", type=float, default=0.1)
+    p.add_argument("--lora-rank", type=int, default=16)
+    p.add_argument("--lora-alpha", type=float, default=16.0)
+    p.add_argument("--moe-backend", default="flextrain", choices=["flextrain", "scattermoe", "sonicmoe"],
+                   help="kept for CLI compatibility; expert compute always runs on the built-in grouped tcgen05 GEMM")
+    p.add_argument("--attn-backend", default="auto", choices=["auto", "ftb", "library", "fa4", "fa3", "fa2", "eager"])
+    p.add_argument("--use-muon", action="store_true")
+    p.add_argument("--device-id", type=int, default=None)
+    p.add_argument("--max-gpu-mem-gib", type=float, default=None)
+    p.add_argument("--max-host-mem-gib", type=float, default=None)
+    p.add_argument("--leeway-gpu-mem-gib", type=float, default=5.0)
+    p.add_argument("--leeway-host-mem-gib", type=float, default=10.0)
+    p.add_argument("--profile-start-step", type=int, default=None)
+    p.add_argument("--profile-stop-step", type=int, default=None)
+    p.add_argument("--force-save-level", type=int, default=None, choices=[0, 1, 2, 3])
+    p.add_argument("--min-chunk-size", type=int, default=None)
+    p.add_argument("--max-chunk-size", type=int, default=None)
+    p.add_argument("--master-dtype", choices=tuple(_DT), default="bfloat16")
+    p.add_argument("--grad-dtype", choices=tuple(_DT), default="bfloat16")
+    p.add_argument("--opt-state-dtype", choices=tuple(_DT), default=None)
+    p.add_argument("--save", action="store_true")
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--verbose", action="store_true")
+    # parallel layout (new): ranks come from torch.distributed.run
+    p.add_argument("--dp-shard", default=None, choices=["opt+grad", "opt+grad+param"])
+    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--ep", type=int, default=1)
+    return p
+
+
+def _attn_backend(name: str) -> str:
+    return {"fa4": "ftb", "fa3": "library", "fa2": "library"}.get(name, name)
+
+
+def _resolve_model(args):
+    if args.model.startswith("dims:"):
+        with open(os.path.join(ROOT, "flextrain_b200/configs/model_dims.json")) as f:
+            cat = json.load(f)
+        name = args.model[5:]
+        if name not in cat:
+            raise SystemExit(f"unknown dims model {name!r}; known: {sorted(cat)}")
+        return "dims", cat[name]
+    if not os.path.isdir(args.model):
+        from flextrain_b200.io.download import maybe_download_hf_snapshot
+        args.model = maybe_download_hf_snapshot(args.model, os.environ.get("FLEXTRAIN_MODELS_DIR", "models"))
+    return "hf", args.model
+
+
+def main(argv=None) -> int:
+    args = build_arg_parser().parse_args(argv)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    use_cuda = torch.cuda.is_available()
+    dev_id = args.device_id if args.device_id is not None else local
+    device = f"cuda:{dev_id}" if use_cuda else "cpu"
+    if use_cuda:
+        torch.cuda.set_device(dev_id)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl" if use_cuda else "gloo",
+                                **({"device_id": torch.device(device)} if use_cuda else {}))
+    say = print if rank == 0 else (lambda *a, **k: None)
+    ft_ops = __import__("flextrain_b200.ops", fromlist=["set_attention_backend"])
+    ft_ops.set_attention_backend(_attn_backend(args.attn_backend))
+
+    # ---- optimizer (flextrain train.py:677-720)
+    lora = args.mode == "lora"
+    sd = _DT[args.opt_state_dtype] if args.opt_state_dtype else (torch.float32 if lora else torch.bfloat16)
+    if lora:
+        if args.use_muon:
+            raise SystemExit("--use-muon is for full fine-tuning only")
+        opt = ft.AdamW(lr=args.lr or 1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, state_dtype=sd)
+    elif args.use_muon:
+        lr = args.lr or 1e-3
+        opt = ft.HybridMuonAdamW(muon=ft.Muon(lr=lr), adamw=ft.AdamW(lr=lr, state_dtype=sd))
+    else:
+        opt = ft.AdamW(lr=args.lr or 3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, state_dtype=sd)
+
+    # ---- budgets
+    gpu_b = int(args.max_gpu_mem_gib * 2 ** 30) if args.max_gpu_mem_gib else get_available_gpu_memory(device)
+    env_cap = os.environ.get("FLEXTRAIN_MAX_GPU_MEM_GIB")
+    if env_cap:
+        gpu_b = min(gpu_b, int(float(env_cap) * 2 ** 30))
+    host_b = int(args.max_host_mem_gib * 2 ** 30) if args.max_host_mem_gib else get_available_host_memory() // max(world, 1)
+    say(f"[budget] gpu {gpu_b / 2**30:.1f} GiB, host {host_b / 2**30:.1f} GiB, world {world}")
+
+    kind, model = _resolve_model(args)
+    common = dict(optimizer=opt, max_seq_len=args.max_seq_len, max_global_batch_tokens=args.max_global_batch_tokens,
+                  max_gpu_mem_bytes=gpu_b, max_host_mem_bytes=host_b, device=device,
+                  leeway_gpu_mem_bytes=int(args.leeway_gpu_mem_gib * 2 ** 30),
+                  leeway_host_mem_bytes=int(args.leeway_host_mem_gib * 2 ** 30),
+                  compute_dtype=torch.bfloat16 if use_cuda else torch.float32,
+                  master_dtype=_DT[args.master_dtype] if use_cuda else torch.float32,
+                  grad_dtype=_DT[args.grad_dtype] if use_cuda else torch.float32,
+                  lora_targets="all" if lora else None, lora_rank=args.lora_rank, lora_alpha=args.lora_alpha,
+                  force_saved_act_level=args.force_save_level, min_chunk_size=args.min_chunk_size,
+                  max_chunk_size=args.max_chunk_size, verbose=args.verbose and rank == 0, world_size=world, rank=rank,
+                  dp_shard=args.dp_shard, tp=args.tp, ep=args.ep)
+    if kind == "dims":
+        arch = model.pop("arch", "llama")
+        hyper = model.pop("hyperparams", None)
+        am = ft.from_dims(model, arch=arch, hyperparams=hyper, init_on_device=use_cuda, **common)
+        vocab = model["vocab_size"]
+    else:
+        am = ft.from_pretrained(model, **common)
+        if os.environ.get("FLEXTRAIN_RANDOMIZE_WEIGHTS") == "1":
+            from flextrain_b200.api import _init_random_weights
+            _init_random_weights(am, int(os.environ.get("FLEXTRAIN_RANDOMIZE_WEIGHTS_SEED", "0")),
+                                 float(os.environ.get("FLEXTRAIN_RANDOMIZE_WEIGHTS_STD", "0.02")), on_device=use_cuda)
+        vocab = am.model_config.vocab_size
+
+    # ---- data
+    per_rank_tokens = args.max_global_batch_tokens // world
+    if args.data_source == "synthetic":
+        src = ft.SyntheticTokenSource(vocab, args.synthetic_seq_len or args.max_seq_len, seed=args.seed + rank, pin=use_cuda)
+    elif args.data_source == "shards":
+        src = ft.ShardTokenSource(args.dataset, args.max_seq_len)
+    else:
+        from transformers import AutoTokenizer
+        tok = AutoTokenizer.from_pretrained(model if kind == "hf" else args.model)
+        src = ft.JsonSFTTokenSource(args.dataset, tok, args.max_seq_len, apply_chat_template=args.apply_chat_template,
+                                    truncate_long=args.truncate_long)
+    out_dir = args.output_dir or os.path.join("runs", f"{os.path.basename(str(args.model).rstrip('/'))}_{args.mode}_sl{args.max_seq_len}")
+    os.makedirs(out_dir, exist_ok=True)
+    rc = run_training_loop(am, src, args, per_rank_tokens, world, say)
+    if args.save and rank == 0:
+        path = am.save_hf(out_dir, "final.safetensors")
+        say(f"[save] {path}")
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return rc
+
+
+def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> int:
+    total = args.steps
+    warm, cool = int(total * args.lr_warmup_pct), int(total * args.lr_cooldown_start_pct)
+    max_lr = am.optimizer.lr
+    final_lr = max_lr * args.lr_final_pct
+    ws = am.ws
+    ema, t_start, tok_total = None, time.time(), 0
+    profiling = False
+    for step in range(1, total + 1):
+        am.optimizer.lr = lr_schedule(step, max_lr=max_lr, final_lr=final_lr, warmup_steps=warm, cooldown_start=cool,
+                                      total_steps=total)
+        seqs = src.get_sequences(per_rank_tokens)
+        if not seqs:
+            say(f"[step {step}] data source exhausted")
+            break
+        # short-tail-round spill (flextrain train.py:221-250)
+        for _ in range(4):
+            rounds = split_sequences(seqs, target_round_tokens=ws.target_round_tokens, max_chunk_size=ws.max_chunk_size,
+                                     max_training_chunks=ws.max_training_chunks,
+                                     max_total_round_tokens=ws.max_total_round_tokens)
+            if len(rounds) <= ws.target_num_rounds or len(rounds[-1]) >= len(seqs):
+                break
+            src.push_back(rounds[-1])
+            seqs = seqs[: -len(rounds[-1])]
+        if args.profile_start_step is not None and step == args.profile_start_step and torch.cuda.is_available():
+            torch.cuda.synchronize(); torch.cuda.profiler.start(); profiling = True
+        step_tokens = sum(len(s) for s in seqs)
+        active = max(1, sum(s.active_token_count for s in seqs))
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([step_tokens, active], device=am.device, dtype=torch.int64)
+            dist.all_reduce(t)
+            g_tokens, g_active = int(t[0]), int(t[1])
+        else:
+            g_tokens, g_active = step_tokens, active
+        t0 = time.time()
+        st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / g_active, total_tokens_per_step=g_tokens)
+        rc = am.step()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        dt = time.time() - t0
+        stop = args.profile_stop_step if args.profile_stop_step is not None else (
+            args.profile_start_step + 2 if args.profile_start_step is not None else None)
+        if profiling and stop is not None and step == stop:
+            torch.cuda.profiler.stop(); profiling = False
+        if rc != 0:
+            say(f"[step {step}] optimizer reported non-finite gradients (code {rc}); update skipped")
+        loss = st.loss_sum / max(active, 1)
+        ema = loss if ema is None else 0.95 * ema + 0.05 * loss
+        eff, hw = step_flops_breakdown(am, st, mode=args.mode)
+        tok_total += g_tokens
+        mem = (torch.cuda.max_memory_allocated() / 2 ** 30, torch.cuda.max_memory_reserved() / 2 ** 30) \
+            if torch.cuda.is_available() else (0.0, 0.0)
+        say(f"[step {step:4d}] lr {am.optimizer.lr:.3e} loss {loss:.4f} ema {ema:.4f} tok/step {g_tokens} "
+            f"tok/s {g_tokens / dt:,.0f} TFLOPS_eff {eff * world / dt / 1e12:.1f} TFLOPS_hw {hw * world / dt / 1e12:.1f} "
+            f"max_alloc {mem[0]:.1f} GiB max_reserve {mem[1]:.1f} GiB step {dt * 1e3:.0f} ms "
+            f"elapsed {time.time() - t_start:.0f}s")
+    say(f"[done] {tok_total} tokens in {time.time() - t_start:.1f}s")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
