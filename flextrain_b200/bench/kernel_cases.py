@@ -1,0 +1,77 @@
+"""Small, self-terminating kernel cases for profiling one kernel at a time.
+
+    python -m flextrain_b200.bench.kernel_cases gemm_fwd|gemm_dgrad|gemm_wgrad|rmsnorm_bwd|softmax_ce|attn_fwd|attn_bwd
+
+Each case holds a few hundred MB on the device (inputs larger than the 126 MB L2), runs one warm-up launch and
+three timed launches with CUDA events, and prints achieved TFLOP/s or GB/s.  They are the commands behind the
+summaries in ``profiles/``.
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+
+def _time(fn, n=3):
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n
+
+
+def main(case: str) -> None:
+    from flextrain_b200 import ops
+    from flextrain_b200.ops import cuda as k
+    dev = "cuda"
+    bf = torch.bfloat16
+    if case.startswith("gemm"):
+        M, N, K = 8192, 8192, 4096
+        ta, tb = {"gemm_fwd": (False, True), "gemm_dgrad": (False, False), "gemm_wgrad": (True, False)}[case]
+        a = torch.randn((K, M) if ta else (M, K), device=dev, dtype=bf)
+        b = torch.randn((N, K) if tb else (K, N), device=dev, dtype=bf)
+        out = torch.empty(M, N, device=dev, dtype=bf)
+        ms = _time(lambda: k.gemm(a, b, trans_a=ta, trans_b=tb, out=out))
+        print(f"{case}: M={M} N={N} K={K}  {ms:.3f} ms  {2.0 * M * N * K / ms / 1e9:.0f} TFLOP/s")
+    elif case == "rmsnorm_bwd":
+        T, D = 16384, 4096
+        x, dy, res = (torch.randn(T, D, device=dev, dtype=bf) for _ in range(3))
+        w = torch.ones(D, device=dev)
+        _, r = k.rmsnorm_fwd(x, w, 1e-5)
+        dw = torch.zeros(D, device=dev)
+        ms = _time(lambda: k.rmsnorm_bwd(dy, x, w, r, dx_add=res, emit_y=True, dw_out=dw))
+        print(f"{case}: T={T} D={D}  {ms:.3f} ms  {5.0 * T * D * 2 / ms / 1e6:.0f} GB/s (3 reads + 2 writes)")
+    elif case == "softmax_ce":
+        T, V = 2048, 128256
+        z = torch.randn(T, V, device=dev, dtype=bf)
+        tgt = torch.randint(0, V, (T,), device=dev)
+        ms = _time(lambda: k.softmax_ce_(z, tgt, grad_scale=1e-3))
+        print(f"{case}: T={T} V={V}  {ms:.3f} ms  {3.0 * T * V * 2 / ms / 1e6:.0f} GB/s (2 reads + 1 write)")
+    elif case in ("attn_fwd", "attn_bwd"):
+        S, B, H, KV, hd = 1024, 16, 32, 8, 128
+        T = S * B
+        q = torch.randn(T, H, hd, device=dev, dtype=bf)
+        kk = torch.randn(T, KV, hd, device=dev, dtype=bf)
+        v = torch.randn(T, KV, hd, device=dev, dtype=bf)
+        cu = torch.arange(0, T + 1, S, device=dev, dtype=torch.int32)
+        fl = 4.0 * B * H * S * S * hd / 2
+        if case == "attn_fwd":
+            ms = _time(lambda: ops.attention_fwd(q, kk, v, cu, cu, S, S, scale=hd ** -0.5))
+            print(f"{case}: B={B} S={S} H={H} KV={KV} hd={hd}  {ms:.3f} ms  {fl / ms / 1e9:.0f} TFLOP/s (causal)")
+        else:
+            o, lse = ops.attention_fwd(q, kk, v, cu, cu, S, S, scale=hd ** -0.5)
+            do = torch.randn_like(o)
+            ms = _time(lambda: ops.attention_bwd(do, q, kk, v, o, lse, cu, cu, S, S, scale=hd ** -0.5))
+            print(f"{case}: B={B} S={S} H={H} KV={KV} hd={hd}  {ms:.3f} ms  {2.5 * fl / ms / 1e9:.0f} TFLOP/s (causal)")
+    else:
+        raise SystemExit(f"unknown case {case}")
+    print("device error words:", k.device_error_words())
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "gemm_fwd")

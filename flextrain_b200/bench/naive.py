@@ -100,10 +100,10 @@ def _ffn(layer, l, P, h):
     logits = h @ P[("layer", l, "w_router")].t()
     if c.routing == "softmax_then_topk":
         probs = torch.softmax(logits, -1)
-        w, idx = torch.sort(probs, -1, descending=True, stable=True)
+        w, idx = torch.sort(probs, dim=-1, descending=True, stable=True)
         w, idx = w[:, : c.top_k], idx[:, : c.top_k]
     else:
-        vals, idx = torch.sort(logits, -1, descending=True, stable=True)
+        vals, idx = torch.sort(logits, dim=-1, descending=True, stable=True)
         w, idx = torch.softmax(vals[:, : c.top_k], -1), idx[:, : c.top_k]
     up, down = P[("layer", l, "w_up")], P[("layer", l, "w_down")]
     out = torch.zeros_like(h)

@@ -1,0 +1,113 @@
+"""Engine scheduling paths forced by hand-built working sets (the reference's parity harness configs A-H,
+flextrain/bench/README.md:45-66): A all-on-device, B multi-chunk, C multi-round, D host offload at each tier,
+E weight ring, F grad ring, G opt ring, H a sequence that spans chunks.  The plan changes where tensors live,
+never what is computed, so losses and updated weights must agree with config A to fp32 round-off."""
+import pytest
+import torch
+
+import flextrain_b200 as ft
+from flextrain_b200.bench.naive import clone_params, naive_loss
+from conftest import build_tiny
+
+DIMS = dict(vocab_size=512, n_layers=4, d_model=128, n_heads=4, n_kv_heads=2, head_dim=32, expert_dim=256, ffn_dim=256,
+            num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+
+
+def _run(ws_kw=None, steps=2, seq_lens=(64, 48, 64, 80), force=None, arch="llama", dims=DIMS, hyper=None, max_seq=96):
+    ws = ft.WorkingSetConfig.simple(max_seq_len=max_seq, max_global_batch_tokens=256, **(ws_kw or {}))
+    am = build_tiny(arch=arch, dims=dims, hyper=hyper, ws=ws, max_seq_len=max_seq, batch_tokens=256,
+                    force_saved_act_level=force)
+    src = ft.SyntheticTokenSource(dims["vocab_size"], list(seq_lens), seed=4)
+    losses = []
+    for _ in range(steps):
+        seqs = src.get_sequences(256)
+        st = am.fwd_bwd(seqs)
+        assert am.step() == 0
+        losses.append(st.loss)
+    flat = torch.cat([t.flatten().float() for _, _, _, t in am.named_master_params()])
+    return losses, flat, am
+
+
+@pytest.fixture(scope="module")
+def base():
+    return _run()
+
+
+def _same(a, b, tol=2e-5):
+    for x, y in zip(a[0], b[0]):
+        assert abs(x - y) < 1e-4, (a[0], b[0])
+    d = (a[1] - b[1]).abs()
+    assert float(d.mean()) < tol and float(d.max()) < 2.5e-3, (float(d.mean()), float(d.max()))
+
+
+def test_B_multi_chunk(base):
+    _same(base, _run(dict(chunk=96)))
+
+
+def test_C_multi_round(base):
+    r = _run(dict(chunk=96, round_tokens=128))
+    assert r[2].ws.target_num_rounds >= 2
+    _same(base, r)
+
+
+@pytest.mark.parametrize("level", [0, 1, 2, 3])
+def test_D_forced_save_level_with_host_offload(base, level):
+    r = _run(dict(chunk=96, host_act_buffer_size=64 << 20), force=level)
+    assert set(r[2]._last_plan.histogram()) == {level}
+    _same(base, r)
+
+
+def test_D_solver_plan_with_few_device_slots(base):
+    r = _run(dict(chunk=96, host_act_buffer_size=64 << 20, n_gpu_act_slots=3))
+    hist = r[2]._last_plan.histogram()
+    assert any(k >= 0 for k in hist), hist
+    _same(base, r)
+
+
+def test_E_weight_ring(base):
+    _same(base, _run(dict(n_gpu_layers=2)))
+
+
+def test_F_grad_ring(base):
+    _same(base, _run(dict(n_gpu_grads=2, chunk=96, round_tokens=128)))
+
+
+def test_G_opt_ring(base):
+    _same(base, _run(dict(n_gpu_opt_layers=2)))
+
+
+def test_EFG_all_rings_multi_round(base):
+    _same(base, _run(dict(n_gpu_layers=2, n_gpu_grads=2, n_gpu_opt_layers=2, chunk=96, round_tokens=128)))
+
+
+def test_H_sequence_spans_chunks_matches_autograd():
+    ws = ft.WorkingSetConfig.simple(max_seq_len=160, max_global_batch_tokens=256, chunk=64)
+    am = build_tiny(dims=DIMS, ws=ws, max_seq_len=160, batch_tokens=256)
+    seqs = ft.SyntheticTokenSource(512, [150, 40, 66], seed=9).get_sequences(256)
+    P = clone_params(am)
+    loss = naive_loss(am, P, seqs)
+    loss.backward()
+    st = am.fwd_bwd(seqs)
+    assert st.n_chunks >= 5
+    assert abs(st.loss - float(loss.detach())) < 2e-4
+    for (scope, l, name), p in P.items():
+        g = {"embed": am.buffers.embed_grads(), "head": am.buffers.head_grads()}.get(scope) or am.buffers.grads(l)
+        torch.testing.assert_close(g["g_" + name[2:]].float(), p.grad, rtol=3e-4, atol=3e-6, msg=f"{scope}/{l}/{name}")
+
+
+def test_H_hybrid_linear_attention_spans_chunks():
+    dims = dict(DIMS, n_layers=2)
+    hyper = {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 2, "head_k_dim": 16, "head_v_dim": 32}}
+    ws = ft.WorkingSetConfig.simple(max_seq_len=100, max_global_batch_tokens=128, chunk=32)
+    am = build_tiny(arch="qwen3_5", dims=dims, hyper=hyper, ws=ws, max_seq_len=100, batch_tokens=128)
+    seqs = ft.SyntheticTokenSource(512, [90, 30], seed=10).get_sequences(128)
+    P = clone_params(am)
+    loss = naive_loss(am, P, seqs)
+    loss.backward()
+    st = am.fwd_bwd(seqs)
+    assert abs(st.loss - float(loss.detach())) < 2e-4, (st.loss, float(loss))
+    for (scope, l, name), p in P.items():
+        g = {"embed": am.buffers.embed_grads(), "head": am.buffers.head_grads()}.get(scope) or am.buffers.grads(l)
+        gname = "g_" + name[2:]
+        if gname in g:
+            torch.testing.assert_close(g[gname].float(), p.grad, rtol=5e-4, atol=5e-6, msg=f"{scope}/{l}/{name}")
