@@ -244,9 +244,21 @@ def run_reference(args):
         host_free = int(psutil.virtual_memory().available * 0.8) // max(world, 1)
         opt = AdamW(AdamWHyperparams(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0),
                     state_dtype=torch.float32)
-        am = ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len, max_global_batch_tokens=per_rank,
-                           max_gpu_mem_bytes=int(free), max_host_mem_bytes=host_free,
-                           hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5}, device=dev)
+        # The reference planner can reject its default chunk candidates on a 180 GB GPU and then advises a smaller
+        # --max-chunk-size; follow that advice through the public keyword until a plan exists.
+        am, plan_err = None, None
+        for mcs in (None, 16384, 8192, 4096):
+            try:
+                am = ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len,
+                                   max_global_batch_tokens=per_rank, max_gpu_mem_bytes=int(free),
+                                   max_host_mem_bytes=host_free, max_chunk_size=mcs,
+                                   hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5}, device=dev)
+                ref_chunk = mcs
+                break
+            except ValueError as e:
+                plan_err = e
+        if am is None:
+            raise plan_err
         src = SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234 + rank)
 
         def allreduce_grads():

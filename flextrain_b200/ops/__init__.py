@@ -214,7 +214,7 @@ def attention_fwd(q, k, v, cu_q, cu_k, max_q, max_k, *, scale, causal=True, wind
 def attention_bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, softcap=0.0):
     """Returns ``(dq, dk, dv)``; dk/dv span all visible keys."""
     be = _attn_backend_for(q)
-    if be == "ftb" and not softcap:
+    if be == "ftb" and not softcap and hasattr(_kernels().load("attention"), "ftb_attn_bwd"):
         from . import attention_cuda
         _count(3)
         return attention_cuda.bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, scale=scale, causal=causal,

@@ -227,3 +227,31 @@ def test_attention_library_matches_reference():
     dq, dk, dv = ops.attention_bwd(do, q, k, v, o, lse, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5)
     wq, wk, wv = ref.attention_bwd(do, q, k, v, ow, lw, cu_q, cu_k, scale=hd ** -0.5)
     assert _rel(dq, wq) < 2e-2 and _rel(dk, wk) < 2e-2 and _rel(dv, wv) < 2e-2
+
+
+@pytest.mark.parametrize("hd", [128, 64])
+@pytest.mark.parametrize("case", ["equal", "prior_ctx", "ragged", "window"])
+def test_attention_tcgen05_fwd(hd, case):
+    from flextrain_b200.ops import attention_cuda as fa
+    H, KV = 8, 2
+    window = 0
+    if case == "equal":
+        lens_q, lens_k = [256, 256, 256], [256, 256, 256]
+    elif case == "prior_ctx":
+        lens_q, lens_k = [128], [640]
+    elif case == "ragged":
+        lens_q, lens_k = [100, 37, 300, 1], [100, 200, 300, 129]
+    else:
+        lens_q, lens_k, window = [384, 200], [384, 456], 96
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32, device=DEV)
+    Tq, Tk = sum(lens_q), sum(lens_k)
+    wide = _rand(Tq, (H + 2 * KV) * hd)
+    q = wide[:, : H * hd].unflatten(1, (H, hd))            # strided view, as in the fused QKV buffer
+    k, v = _rand(Tk, KV, hd), _rand(Tk, KV, hd)
+    o, lse = fa.fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5, window=window)
+    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, scale=hd ** -0.5, window=window)
+    from flextrain_b200.ops import cuda as kk
+    assert kk.device_error_words().get("attention", 0) == 0
+    assert _rel(o, ow) < 1e-2, (case, hd, _rel(o, ow))
+    assert float((lse - lw).abs().max()) < 2e-2
