@@ -407,3 +407,347 @@ int ftb_attn_error(void) {
 }
 
 }  // extern "C"
+
+// =====================================================================================================
+// Backward
+// =====================================================================================================
+namespace ftb {
+
+struct BwdParams {
+  const int* cu_q;
+  const int* cu_k;
+  int num_seqs;
+  int H, KV;
+  float* dq_acc;            // (Tq, H, HD) fp32, zero-initialised by the caller
+  __nv_bfloat16* dk;        // (Tk, KV, HD) contiguous
+  __nv_bfloat16* dv;
+  const float* lse;         // (H, Tq)
+  const float* delta;       // (H, Tq)  rowsum(dO * O)
+  int total_q;
+  float scale;
+  int causal;
+  int window;
+};
+
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h).
+__global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ dout, long do_stride, const __nv_bfloat16* __restrict__ out,
+                                long o_stride, float* __restrict__ delta, int T, int H, int hd) {
+  const long w = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long)T * H) return;
+  const int t = (int)(w / H), h = (int)(w % H), lane = threadIdx.x & 31;
+  const __nv_bfloat16* a = dout + (size_t)t * do_stride + (size_t)h * hd;
+  const __nv_bfloat16* b = out + (size_t)t * o_stride + (size_t)h * hd;
+  float s = 0.f;
+  for (int i = lane * 2; i < hd; i += 64) {
+    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a + i));
+    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(b + i));
+    s += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) delta[(size_t)h * T + t] = s;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+              const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
+  constexpr int KB = HD / 64;
+  constexpr int T_BYTES = 128 * HD * 2;       // one Q / dO / K / V tile
+  constexpr int P_BYTES = 128 * 128 * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + T_BYTES;
+  uint8_t* sQ = sV + T_BYTES;
+  uint8_t* sDO = sQ + T_BYTES;
+  uint8_t* sP = sDO + T_BYTES;
+  uint8_t* sDS = sP + P_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + P_BYTES);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;
+  uint64_t* pds_full = bars + 4;
+  uint64_t* dq_full = bars + 5;
+  uint64_t* dq_empty = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.y;
+  const int rep = p.H / p.KV;
+  int seq = 0, k0 = 0;
+  if (!find_tile(p.cu_k, p.num_seqs, blockIdx.x, seq, k0)) return;
+  const int qs = p.cu_q[seq], len_q = p.cu_q[seq + 1] - qs;
+  const int ks = p.cu_k[seq], len_k = p.cu_k[seq + 1] - ks;
+  const int off = len_k - len_q;
+  const int kr = min(128, len_k - k0);
+  int i_lo = p.causal ? max(0, k0 - off) : 0;
+  int i_hi = (p.causal && p.window > 0) ? min(len_q, k0 + kr + p.window - 1 - off) : len_q;
+  i_lo = (i_lo / 128) * 128;
+  const int n_qt = i_hi > i_lo ? (i_hi - i_lo + 127) / 128 : 0;
+  const int n_iter = n_qt * rep;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(dq_empty, 4);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_S = tmem_base, tm_dP = tmem_base + 128, tm_dV = tmem_base + 256, tm_dK = tmem_base + 256 + HD;
+  const uint32_t tm_dQ = tm_S;   // dQ reuses the S columns once the softmax warps have consumed S
+
+  if (warp == 0) {
+    if (lane == 0 && n_iter > 0) {
+      mbar_expect_tx(kv_full, 2 * T_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb) {
+        tma_load_3d(sK + kb * (128 * 128), &tmK, kv_full, kb * 64, kvh, ks + k0);
+        tma_load_3d(sV + kb * (128 * 128), &tmV, kv_full, kb * 64, kvh, ks + k0);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int h = kvh * rep + it / n_qt;
+        const int qt = i_lo + (it % n_qt) * 128;
+        if (!mbar_wait(qdo_empty, (it & 1) ^ 1, abort_flag, 210)) break;
+        mbar_expect_tx(qdo_full, 2 * T_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_3d(sQ + kb * (128 * 128), &tmQ, qdo_full, kb * 64, h, qs + qt);
+          tma_load_3d(sDO + kb * (128 * 128), &tmDO, qdo_full, kb * 64, h, qs + qt);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t id_s = make_idesc_bf16(128, 128, 0, 0);       // S, dP: both operands K-major
+      constexpr uint32_t id_t = make_idesc_bf16(128, HD, 1, 1);        // dV, dK: transposed A, MN-major B
+      constexpr uint32_t id_q = make_idesc_bf16(128, HD, 0, 1);        // dQ: K-major A, MN-major B
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sDO);
+      const uint32_t aP = smem_u32(sP), aDS = smem_u32(sDS);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, 220);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const uint32_t ph = it & 1;
+        if (!(ok = mbar_wait(qdo_full, ph, abort_flag, 221))) break;
+        if (!(ok = mbar_wait(dq_empty, ph ^ 1, abort_flag, 222))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t o = kb * (128 * 128) + kk * 32;
+            umma_f16(tm_S, make_smem_desc(aQ + o, 16, 1024), make_smem_desc(aK + o, 16, 1024), id_s, (kb | kk) != 0);
+          }
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t o = kb * (128 * 128) + kk * 32;
+            umma_f16(tm_dP, make_smem_desc(aDO + o, 16, 1024), make_smem_desc(aV + o, 16, 1024), id_s, (kb | kk) != 0);
+          }
+        umma_commit(sdp_full);
+        if (!(ok = mbar_wait(pds_full, ph, abort_flag, 223))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {      // reduction over the 128 query rows, 16 per step
+          const uint32_t o = s * (16 * 128);
+          umma_f16(tm_dV, make_smem_desc(aP + o, 128 * 128, 1024), make_smem_desc(aDO + o, 128 * 128, 1024), id_t,
+                   (it | s) != 0);
+          umma_f16(tm_dK, make_smem_desc(aDS + o, 128 * 128, 1024), make_smem_desc(aQ + o, 128 * 128, 1024), id_t,
+                   (it | s) != 0);
+        }
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {      // reduction over the 128 keys
+          const uint64_t ad = make_smem_desc(aDS + (s >> 2) * (128 * 128) + (s & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(aK + s * (16 * 128), 128 * 128, 1024);
+          umma_f16(tm_dQ, ad, bd, id_q, s != 0);
+        }
+        umma_commit(dq_full);
+        umma_commit(qdo_empty);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const float c = p.scale * 1.4426950408889634f;
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const uint32_t ph = it & 1;
+      const int h = kvh * rep + it / n_qt;
+      const int qt = i_lo + (it % n_qt) * 128;
+      const int i = qt + r;
+      const bool vq = i < len_q;
+      const size_t grow = static_cast<size_t>(qs + (vq ? i : 0));
+      const float lse2 = vq ? p.lse[static_cast<size_t>(h) * p.total_q + grow] * 1.4426950408889634f : INFINITY;
+      const float dl = vq ? p.delta[static_cast<size_t>(h) * p.total_q + grow] : 0.f;
+      const int qi = i + off;
+      if (!(ok = mbar_wait(sdp_full, ph, abort_flag, 230))) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int cb = 0; cb < 128; cb += 32) {
+        uint32_t vs[32], vd[32];
+        tmem_ld_32x32(tm_S + lane_base + cb, vs);
+        tmem_ld_32x32(tm_dP + lane_base + cb, vd);
+        tmem_ld_wait();
+        float pr[32], ds[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int kj = k0 + cb + e;
+          bool keep = vq && kj < len_k;
+          if (p.causal) keep = keep && (kj <= qi) && (p.window <= 0 || kj > qi - p.window);
+          const float pe = keep ? exp2f(__uint_as_float(vs[e]) * c - lse2) : 0.f;
+          pr[e] = pe;
+          ds[e] = pe * (__uint_as_float(vd[e]) - dl) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 a, b;
+          __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&a);
+          __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            a2[e] = __floats2bfloat162_rn(pr[g * 8 + 2 * e], pr[g * 8 + 2 * e + 1]);
+            b2[e] = __floats2bfloat162_rn(ds[g * 8 + 2 * e], ds[g * 8 + 2 * e + 1]);
+          }
+          const uint32_t o = sw128_offset(r, cb + g * 8, 128);
+          *reinterpret_cast<uint4*>(sP + o) = a;
+          *reinterpret_cast<uint4*>(sDS + o) = b;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+      if (!(ok = mbar_wait(dq_full, ph, abort_flag, 231))) break;
+      tc_fence_after();
+      float* dq_row = p.dq_acc + (grow * p.H + h) * HD;
+#pragma unroll 1
+      for (int cb = 0; cb < HD; cb += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_dQ + lane_base + cb, v);
+        tmem_ld_wait();
+        if (vq) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) atomicAdd(dq_row + cb + e, __uint_as_float(v[e]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_empty);
+    }
+    // dK / dV of this key tile (thread = key row)
+    if (r < kr) {
+      const size_t row = static_cast<size_t>(ks + k0 + r);
+      __nv_bfloat16* dk_row = p.dk + (row * p.KV + kvh) * HD;
+      __nv_bfloat16* dv_row = p.dv + (row * p.KV + kvh) * HD;
+      if (n_iter == 0 || !ok) {
+        for (int cidx = 0; cidx < HD; cidx += 8) {
+          *reinterpret_cast<uint4*>(dk_row + cidx) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(dv_row + cidx) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+    if (n_iter > 0 && ok) {
+      tc_fence_after();
+      const size_t row = static_cast<size_t>(ks + k0 + min(r, kr - 1));
+      __nv_bfloat16* dk_row = p.dk + (row * p.KV + kvh) * HD;
+      __nv_bfloat16* dv_row = p.dv + (row * p.KV + kvh) * HD;
+#pragma unroll 1
+      for (int cb = 0; cb < HD; cb += 32) {
+        uint32_t a[32], b[32];
+        tmem_ld_32x32(tm_dV + lane_base + cb, a);
+        tmem_ld_32x32(tm_dK + lane_base + cb, b);
+        tmem_ld_wait();
+        if (r < kr) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 x, y;
+            __nv_bfloat162* x2 = reinterpret_cast<__nv_bfloat162*>(&x);
+            __nv_bfloat162* y2 = reinterpret_cast<__nv_bfloat162*>(&y);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              x2[e] = __floats2bfloat162_rn(__uint_as_float(a[g * 8 + 2 * e]), __uint_as_float(a[g * 8 + 2 * e + 1]));
+              y2[e] = __floats2bfloat162_rn(__uint_as_float(b[g * 8 + 2 * e]), __uint_as_float(b[g * 8 + 2 * e + 1]));
+            }
+            *reinterpret_cast<uint4*>(dv_row + cb + g * 8) = x;
+            *reinterpret_cast<uint4*>(dk_row + cb + g * 8) = y;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int HD>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv,
+                      const BwdParams& p, int tiles, cudaStream_t s) {
+  constexpr int SMEM = 4 * 128 * HD * 2 + 2 * 128 * 128 * 2 + 256 + 1024;
+  auto kern = fa_bwd_kernel<HD>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return -300 - static_cast<int>(e);
+    configured = true;
+  }
+  dim3 grid(tiles, p.KV);
+  kern<<<grid, FA_THREADS, SMEM, s>>>(tq, tdo, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
+}
+
+}  // namespace ftb
+
+extern "C" {
+
+// dout / q / out (Tq, H, hd), k / v (Tk, KV, hd) bf16 with token strides; lse (H, Tq) from the forward.
+// Workspaces supplied by the caller: delta (H, Tq) fp32, dq_acc (Tq, H, hd) fp32 ZEROED.
+// Outputs: dq (bf16, converted from dq_acc), dk, dv (Tk, KV, hd) bf16 contiguous, every row written.
+int ftb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse,
+                 float* delta, float* dq_acc, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k,
+                 int num_seqs, int total_q, int total_k, int H, int KV, int hd, long q_stride, long k_stride,
+                 long v_stride, long do_stride, long o_stride, float scale, int causal, int window, int max_tiles,
+                 cudaStream_t stream) {
+  if (total_q <= 0 || num_seqs <= 0) return 0;
+  if ((hd != 64 && hd != 128) || H % KV) return -2;
+  if ((q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (do_stride & 7)) return -2;
+  {
+    const long warps = (long)total_q * H;
+    fa_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)dout, do_stride,
+                                                                     (const __nv_bfloat16*)out, o_stride, delta,
+                                                                     total_q, H, hd);
+  }
+  CUtensorMap tq, tdo, tk, tv;
+  int rc = make_tmap_3d(&tq, q, hd, H, total_q, q_stride, 128);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tdo, dout, hd, H, total_q, do_stride, 128);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tk, k, hd, KV, total_k, k_stride, 128);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tv, v, hd, KV, total_k, v_stride, 128);
+  if (rc) return rc;
+  BwdParams p;
+  p.cu_q = cu_q; p.cu_k = cu_k; p.num_seqs = num_seqs; p.H = H; p.KV = KV;
+  p.dq_acc = dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.lse = lse; p.delta = delta;
+  p.total_q = total_q; p.scale = scale; p.causal = causal; p.window = window;
+  rc = (hd == 128) ? launch_bwd<128>(tq, tdo, tk, tv, p, max_tiles, stream)
+                   : launch_bwd<64>(tq, tdo, tk, tv, p, max_tiles, stream);
+  return rc;
+}
+
+}  // extern "C"

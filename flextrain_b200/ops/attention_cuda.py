@@ -62,4 +62,5 @@ def bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True
                           c_long(v.stride(0)), c_long(dout.stride(0)), c_long(out.stride(0)), c_float(scale),
                           c_int(1 if causal else 0), c_int(int(window or 0)), c_int(Tk // 128 + nseq), _stream())
     _check(rc, "ftb_attn_bwd")
+    dq.copy_(dq_acc)
     return dq, dk, dv

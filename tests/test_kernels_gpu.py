@@ -255,3 +255,33 @@ def test_attention_tcgen05_fwd(hd, case):
     assert kk.device_error_words().get("attention", 0) == 0
     assert _rel(o, ow) < 1e-2, (case, hd, _rel(o, ow))
     assert float((lse - lw).abs().max()) < 2e-2
+
+
+@pytest.mark.parametrize("hd", [128, 64])
+@pytest.mark.parametrize("case", ["equal", "prior_ctx", "ragged", "window"])
+def test_attention_tcgen05_bwd(hd, case):
+    from flextrain_b200.ops import attention_cuda as fa
+    from flextrain_b200.ops import cuda as kk
+    H, KV = 8, 2
+    window = 0
+    if case == "equal":
+        lens_q, lens_k = [256, 256], [256, 256]
+    elif case == "prior_ctx":
+        lens_q, lens_k = [128], [640]
+    elif case == "ragged":
+        lens_q, lens_k = [100, 37, 300, 1], [100, 200, 300, 129]
+    else:
+        lens_q, lens_k, window = [384, 200], [384, 456], 96
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32, device=DEV)
+    Tq, Tk = sum(lens_q), sum(lens_k)
+    q, k, v = _rand(Tq, H, hd), _rand(Tk, KV, hd), _rand(Tk, KV, hd)
+    do = _rand(Tq, H, hd)
+    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, scale=hd ** -0.5, window=window)
+    wq, wk, wv = ref.attention_bwd(do, q, k, v, ow, lw, cu_q, cu_k, scale=hd ** -0.5, window=window)
+    o, lse = fa.fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5, window=window)
+    dq, dk, dv = fa.bwd(do, q, k, v, o, lse, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5, window=window)
+    assert kk.device_error_words().get("attention", 0) == 0
+    assert _rel(dq, wq) < 2e-2, (case, hd, "dq", _rel(dq, wq))
+    assert _rel(dk, wk) < 2e-2, (case, hd, "dk", _rel(dk, wk))
+    assert _rel(dv, wv) < 2e-2, (case, hd, "dv", _rel(dv, wv))
