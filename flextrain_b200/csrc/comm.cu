@@ -266,6 +266,24 @@ __global__ void gather_rows_pull_kernel(PeerTable bufs, const int* __restrict__ 
   for (int c = threadIdx.x; c < (D >> 3); c += blockDim.x) dst[c] = src[c];
 }
 
+// out[i] = sum_r slots[r * slot_stride + i] (+ resid[i]); bf16 in / out, fp32 sum.  The tail of the GEMM -> reduce-scatter
+// path: `slots` is this rank's staging area holding one partial panel per source rank.
+__global__ void reduce_slots_kernel(const bf16* __restrict__ slots, long slot_stride, int world,
+                                    const bf16* __restrict__ resid, bf16* __restrict__ out, long n) {
+  const long n8 = n >> 3;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (resid) unpack8(reinterpret_cast<const uint4*>(resid)[i], acc);
+    for (int r = 0; r < world; ++r) {
+      float f[8];
+      unpack8(reinterpret_cast<const uint4*>(slots + (size_t)r * slot_stride)[i], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    reinterpret_cast<uint4*>(out)[i] = pack8(acc);
+  }
+}
+
 }  // namespace
 
 static int fill_table(SegTable& t, int n, const long* byte_off, const long* begin, const long* count,
@@ -374,6 +392,17 @@ int ftb_comm_gather_rows_pull(void* const* bufs, const int* src_rank, const int*
   for (int i = 0; i < world; ++i) t.ptr[i] = bufs[i];
   if (rows == 0) return 0;
   gather_rows_pull_kernel<<<(unsigned)rows, 128, 0, s>>>(t, src_rank, src_row, (bf16*)out, rows, D, byte_off);
+  CHECK_LAUNCH();
+}
+
+int ftb_comm_reduce_slots(const void* slots, long slot_stride, int world, const void* resid, void* out, long n,
+                          cudaStream_t s) {
+  if (n == 0) return 0;
+  if ((n & 7) || (slot_stride & 7)) return -2;
+  long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  reduce_slots_kernel<<<(unsigned)blocks, 256, 0, s>>>((const bf16*)slots, slot_stride, world, (const bf16*)resid,
+                                                       (bf16*)out, n);
   CHECK_LAUNCH();
 }
 

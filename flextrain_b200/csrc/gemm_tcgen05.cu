@@ -21,7 +21,8 @@ namespace ftb {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 256;   // warps 0-5: TMA / MMA / epilogue; warps 6-7: peer-panel pull (TP all-gather mode)
+constexpr int MAX_RANKS = 8;
 constexpr int GROUP_M = 16;  // tile rasterisation: GROUP_M row-tiles share a sweep over N (L2 reuse)
 
 struct GemmParams {
@@ -37,6 +38,20 @@ struct GemmParams {
   int num_groups;
   const int* offsets;
   int max_tiles;     // grouped: upper bound of tiles the grid walks
+  // ---- tensor-parallel fused modes (comm_mode != 0); rows are split into `world` panels of `panel_rows`
+  //  1  all-gather -> GEMM: A's row panel p lives on rank p.  Warps 6-7 of every CTA pull the remote panels
+  //     from the peers' staging buffers into the local one (plain peer loads, each byte crosses NVLink once),
+  //     publishing bytes-arrived per panel; the TMA producer starts on the local panel and waits per panel.
+  //  2  GEMM -> reduce-scatter: output panel p is owned by rank p.  The epilogue stores each partial tile
+  //     straight into the owner's staging slot for this rank (peer stores, tile by tile under the math);
+  //     a small reduce kernel on the owner then sums the `world` slots.
+  int comm_mode, world, rank, panel_rows;
+  const void* a_peer[MAX_RANKS];
+  void* a_local;
+  long panel_bytes;
+  unsigned long long* panel_counter;
+  void* d_peer[MAX_RANKS];
+  long d_slot_stride;
 };
 
 template <int BN, int STAGES>
@@ -56,6 +71,25 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   const int r = tile - g * per_group;
   tm = first_m + r % gm;
   tn = r / gm;
+}
+
+// Panel-ordered tiles for the tensor-parallel modes: panels are visited starting at `first`, each panel uses the
+// grouped rasterisation internally.
+__device__ __forceinline__ void panel_tile_coords(int tile, int tiles_n, int panel_rows, int world, int first,
+                                                  int& panel, int& row0, int& tn) {
+  const int tiles_m_panel = panel_rows / BM;
+  const int per_panel = tiles_m_panel * tiles_n;
+  const int pi = tile / per_panel;
+  panel = (first + pi) % world;
+  int tm;
+  tile_coords(tile - pi * per_panel, tiles_m_panel, tiles_n, tm, tn);
+  row0 = panel * panel_rows + tm * BM;
+}
+
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
 }
 
 // Grouped tile lookup: tile index -> (group, row tile inside group). Linear walk over the
@@ -81,7 +115,7 @@ __device__ __forceinline__ bool grouped_tile(const int* __restrict__ offsets, in
   return false;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool GROUPED>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool GROUPED, int COMM = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
@@ -134,6 +168,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         int tm, tn, g = 0, row0, rows;
         if constexpr (GROUPED) {
           if (!grouped_tile(p.offsets, p.num_groups, tiles_n, tile, g, row0, rows, tn)) break;
+        } else if constexpr (COMM != 0) {
+          int panel;
+          panel_tile_coords(tile, tiles_n, p.panel_rows, p.world, COMM == 1 ? p.rank : p.rank + 1, panel, row0, tn);
+          if constexpr (COMM == 1) {
+            if (panel != p.rank) {   // wait (bounded) until the pull warps have landed this panel in local memory
+              const unsigned long long need = static_cast<unsigned long long>(p.panel_bytes);
+              uint32_t it = 0;
+              while (ld_acquire_gpu_u64(p.panel_counter + panel) < need) {
+                if (++it > FTB_WAIT_LIMIT || *abort_flag) { *abort_flag = 1; set_error(2, 40 + panel); ok = false; break; }
+                __nanosleep(64);
+              }
+              if (!ok) break;
+              asm volatile("fence.proxy.async;" ::: "memory");
+            }
+          }
         } else {
           tile_coords(tile, tiles_m, tiles_n, tm, tn);
           row0 = tm * BM;
@@ -218,6 +267,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------- peer-panel pull (all-gather mode only)
+    if constexpr (COMM == 1) {
+      const int t = threadIdx.x - 192;                       // 0..63
+      const long stride = static_cast<long>(gridDim.x) * 64;
+      const long n16 = p.panel_bytes >> 4;
+      for (int i = 1; i < p.world; ++i) {
+        const int pn = (p.rank + i) % p.world;
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.a_peer[pn]) + pn * p.panel_bytes);
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.a_local) + pn * p.panel_bytes);
+        long moved = 0;
+        long idx = static_cast<long>(blockIdx.x) * 64 + t;
+        for (; idx + 3 * stride < n16; idx += 4 * stride) {   // four loads in flight per thread
+          const uint4 v0 = src[idx], v1 = src[idx + stride], v2 = src[idx + 2 * stride], v3 = src[idx + 3 * stride];
+          dst[idx] = v0; dst[idx + stride] = v1; dst[idx + 2 * stride] = v2; dst[idx + 3 * stride] = v3;
+          moved += 64;
+        }
+        for (; idx < n16; idx += stride) { dst[idx] = src[idx]; moved += 16; }
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) moved += __shfl_xor_sync(0xffffffffu, moved, o);
+        if (lane == 0 && moved) atomicAdd(p.panel_counter + pn, static_cast<unsigned long long>(moved));
+      }
+    }
   } else {
     // ----------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
@@ -226,8 +300,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tm, tn, g = 0, row0, rows;
+      char* d_base = reinterpret_cast<char*>(p.D);
+      long d_row_shift = 0;
       if constexpr (GROUPED) {
         if (!grouped_tile(p.offsets, p.num_groups, tiles_n, tile, g, row0, rows, tn)) break;
+      } else if constexpr (COMM != 0) {
+        int panel;
+        panel_tile_coords(tile, tiles_n, p.panel_rows, p.world, COMM == 1 ? p.rank : p.rank + 1, panel, row0, tn);
+        rows = BM;
+        if constexpr (COMM == 2) {   // partial tile goes to the owner's slot for this rank
+          d_base = reinterpret_cast<char*>(p.d_peer[panel]) +
+                   static_cast<size_t>(p.rank) * p.d_slot_stride * (p.d_fp32 ? 4 : 2);
+          d_row_shift = static_cast<long>(panel) * p.panel_rows;
+        }
       } else {
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
         row0 = tm * BM;
@@ -237,7 +322,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_after();
       const int r_in = quad * 32 + lane;
       const bool row_ok = r_in < rows;
-      const size_t row = static_cast<size_t>(row0 + r_in);
+      const size_t row = static_cast<size_t>(row0 + r_in - d_row_shift);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
@@ -256,7 +341,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               if (col + i < p.N) v[i] += p.bias[col + i];
           }
           if (p.d_fp32) {
-            float* dptr = reinterpret_cast<float*>(p.D) + row * p.ldd + col;
+            float* dptr = reinterpret_cast<float*>(d_base) + row * p.ldd + col;
             const float* cptr = reinterpret_cast<const float*>(p.C) + row * p.ldc + col;
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
@@ -270,7 +355,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               }
             }
           } else {
-            __nv_bfloat16* dptr = reinterpret_cast<__nv_bfloat16*>(p.D) + row * p.ldd + col;
+            __nv_bfloat16* dptr = reinterpret_cast<__nv_bfloat16*>(d_base) + row * p.ldd + col;
             const __nv_bfloat16* cptr = reinterpret_cast<const __nv_bfloat16*>(p.C) + row * p.ldc + col;
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
@@ -344,10 +429,10 @@ static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_
   return r == CUDA_SUCCESS ? 0 : -200 - static_cast<int>(r);
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool GROUPED>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool GROUPED, int COMM = 0>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
-  auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, GROUPED>;
+  auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, GROUPED, COMM>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -429,6 +514,7 @@ int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const fl
   p.alpha = alpha; p.beta = (C != nullptr) ? beta : 0.f;
   p.D = D; p.C = (C != nullptr) ? C : D; p.bias = bias; p.d_fp32 = d_fp32;
   p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0;
   const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
@@ -472,6 +558,7 @@ int ftb_grouped_gemm_bf16(const void* A, const void* B, void* D, const void* C, 
   p.alpha = alpha; p.beta = (C != nullptr) ? beta : 0.f;
   p.D = D; p.C = (C != nullptr) ? C : D; p.bias = nullptr; p.d_fp32 = d_fp32;
   p.num_groups = num_groups; p.offsets = offsets;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0;
   const int tiles_n = (N + bn - 1) / bn;
   p.max_tiles = ((total_rows + BM - 1) / BM + num_groups) * tiles_n;
   int grid = sm_count();
@@ -479,6 +566,72 @@ int ftb_grouped_gemm_bf16(const void* A, const void* B, void* D, const void* C, 
   if (p.max_tiles < grid) grid = p.max_tiles;
   if (bn == 256) return dispatch_major<256, 4, true>(0, b_mn_major, ta, tb, p, grid, stream);
   return dispatch_major<128, 6, true>(0, b_mn_major, ta, tb, p, grid, stream);
+}
+
+// Tensor-parallel fused GEMM.  A is (M, K) K-major with M = world * panel_rows.
+//  mode 1 (all-gather -> GEMM): `a_local` is this rank's staging buffer of the full (M, K) matrix whose own panel
+//    is already filled; `a_peer[r]` is rank r's staging buffer (same layout).  `panel_counter` (world x u64, device)
+//    must be zero at launch.  D (M, N) is local.
+//  mode 2 (GEMM -> reduce-scatter): A (M, K) is local; the partial output panel p is stored into
+//    d_peer[p] + rank * d_slot_stride (elements) as a (panel_rows, N) matrix with leading dimension ldd.
+// B as in ftb_gemm_bf16.  panel_rows must be a multiple of 128.
+int ftb_gemm_bf16_tp(int mode, const void* A, void* const* a_peer, unsigned long long* panel_counter, const void* B,
+                     void* D, void* const* d_peer, long d_slot_stride, int M, int N, int K, int b_mn_major, int lda,
+                     int ldb, int ldd, float alpha, int d_fp32, int world, int rank, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || M % world) return -2;
+  const int panel_rows = M / world;
+  if (panel_rows % BM || (lda & 7) || (ldb & 7) || (N & 7)) return -2;
+  const int bn = (N <= 128) ? 128 : 256;
+  CUtensorMap ta, tb;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {BK, BM};
+    rc = make_tmap(&ta, A, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  if (!b_mn_major) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {BK, (uint32_t)bn};
+    rc = make_tmap(&tb, B, 2, dims, str, box);
+  } else {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_tmap(&tb, B, 2, dims, str, box);
+  }
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldd; p.alpha = alpha; p.beta = 0.f;
+  p.D = D; p.C = D; p.bias = nullptr; p.d_fp32 = d_fp32;
+  p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
+  p.comm_mode = mode; p.world = world; p.rank = rank; p.panel_rows = panel_rows;
+  p.a_local = const_cast<void*>(A); p.panel_bytes = (long)panel_rows * lda * 2; p.panel_counter = panel_counter;
+  p.d_slot_stride = d_slot_stride;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    p.a_peer[i] = (mode == 1 && i < world) ? a_peer[i] : nullptr;
+    p.d_peer[i] = (mode == 2 && i < world) ? d_peer[i] : nullptr;
+  }
+  const int tiles = (M / BM) * ((N + bn - 1) / bn);
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = tiles;
+  if (mode == 1) {
+    if (bn == 256) return b_mn_major ? launch<256, 4, false, true, false, 1>(ta, tb, p, grid, stream)
+                                     : launch<256, 4, false, false, false, 1>(ta, tb, p, grid, stream);
+    return b_mn_major ? launch<128, 6, false, true, false, 1>(ta, tb, p, grid, stream)
+                      : launch<128, 6, false, false, false, 1>(ta, tb, p, grid, stream);
+  }
+  if (mode == 2) {
+    if (bn == 256) return b_mn_major ? launch<256, 4, false, true, false, 2>(ta, tb, p, grid, stream)
+                                     : launch<256, 4, false, false, false, 2>(ta, tb, p, grid, stream);
+    return b_mn_major ? launch<128, 6, false, true, false, 2>(ta, tb, p, grid, stream)
+                      : launch<128, 6, false, false, false, 2>(ta, tb, p, grid, stream);
+  }
+  return -2;
 }
 
 // Reads and clears the library's device error word: returns code * 1000 + where (0 = no error).

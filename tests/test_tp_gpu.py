@@ -1,0 +1,28 @@
+"""Fused tensor-parallel kernels on 2+ GPUs: all-gather->GEMM and GEMM->reduce-scatter vs NCCL + plain GEMM."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tp_gemms_match_nccl(tmp_path):
+    n = min(torch.cuda.device_count(), 4)
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "tp.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "tp_worker.py"), out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert all(v == 0 for v in res["errors"].values()), res["errors"]
+    for k, v in res.items():
+        if k.startswith(("ag_", "rs_")):
+            assert v < 1e-2, (k, v)
