@@ -115,7 +115,7 @@ __device__ __forceinline__ bool grouped_tile(const int* __restrict__ offsets, in
   return false;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool GROUPED, int COMM = 0>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int GROUPED, int COMM = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
@@ -132,8 +132,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int lane = threadIdx.x & 31;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int tiles_m = (p.M + BM - 1) / BM;
-  const int num_tiles = GROUPED ? p.max_tiles : tiles_m * tiles_n;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  const int num_tiles = GROUPED == 1 ? p.max_tiles : (GROUPED == 2 ? p.num_groups * tiles_m * tiles_n : tiles_m * tiles_n);
+  int k_blocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -166,8 +166,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn, g = 0, row0, rows;
-        if constexpr (GROUPED) {
+        int k_lo = 0;
+        if constexpr (GROUPED == 1) {
           if (!grouped_tile(p.offsets, p.num_groups, tiles_n, tile, g, row0, rows, tn)) break;
+        } else if constexpr (GROUPED == 2) {
+          // per-expert weight gradient: tile = (expert, tm, tn); the reduction runs over the expert's rows
+          g = tile / (tiles_m * tiles_n);
+          tile_coords(tile - g * tiles_m * tiles_n, tiles_m, tiles_n, tm, tn);
+          row0 = tm * BM;
+          k_lo = p.offsets[g];
+          k_blocks = (p.offsets[g + 1] - k_lo + BK - 1) / BK;
+          if (k_blocks == 0) continue;
         } else if constexpr (COMM != 0) {
           int panel;
           panel_tile_coords(tile, tiles_n, p.panel_rows, p.world, COMM == 1 ? p.rank : p.rank + 1, panel, row0, tn);
@@ -193,14 +202,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = k_lo + kb * BK;
           if constexpr (!A_MN) {
             tma_load_2d(sa, &tmA, &full_bar[stage], k0, row0);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (64 * BK * 2), &tmA, &full_bar[stage], row0 + j * 64, k0);
           }
-          if constexpr (GROUPED) {
+          if constexpr (GROUPED == 1) {
             if constexpr (!B_MN) {
               tma_load_3d(sb, &tmB, &full_bar[stage], k0, col0, g);
             } else {
@@ -238,9 +247,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if constexpr (GROUPED) {
+        if constexpr (GROUPED == 1) {
           int g, row0, rows, tn;
           if (!grouped_tile(p.offsets, p.num_groups, tiles_n, tile, g, row0, rows, tn)) break;
+        }
+        if constexpr (GROUPED == 2) {
+          const int g = tile / (tiles_m * tiles_n);
+          k_blocks = (p.offsets[g + 1] - p.offsets[g] + BK - 1) / BK;
+          if (k_blocks == 0) continue;
         }
         if (!(ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, 20))) break;
         tc_fence_after();
@@ -302,8 +316,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int tm, tn, g = 0, row0, rows;
       char* d_base = reinterpret_cast<char*>(p.D);
       long d_row_shift = 0;
-      if constexpr (GROUPED) {
+      if constexpr (GROUPED == 1) {
         if (!grouped_tile(p.offsets, p.num_groups, tiles_n, tile, g, row0, rows, tn)) break;
+      } else if constexpr (GROUPED == 2) {
+        g = tile / (tiles_m * tiles_n);
+        tile_coords(tile - g * tiles_m * tiles_n, tiles_m, tiles_n, tm, tn);
+        row0 = tm * BM;
+        rows = min(BM, p.M - row0);
+        if ((p.offsets[g + 1] - p.offsets[g] + BK - 1) / BK == 0) continue;   // empty expert: gradient unchanged
+        d_base = reinterpret_cast<char*>(p.D) + static_cast<size_t>(g) * p.M * p.ldd * (p.d_fp32 ? 4 : 2);
       } else if constexpr (COMM != 0) {
         int panel;
         panel_tile_coords(tile, tiles_n, p.panel_rows, p.world, COMM == 1 ? p.rank : p.rank + 1, panel, row0, tn);
@@ -342,7 +363,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           if (p.d_fp32) {
             float* dptr = reinterpret_cast<float*>(d_base) + row * p.ldd + col;
-            const float* cptr = reinterpret_cast<const float*>(p.C) + row * p.ldc + col;
+            const float* cptr = (GROUPED == 2 ? reinterpret_cast<const float*>(d_base) : reinterpret_cast<const float*>(p.C)) + row * p.ldc + col;
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
               if (col + i < p.N) {
@@ -356,7 +377,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           } else {
             __nv_bfloat16* dptr = reinterpret_cast<__nv_bfloat16*>(d_base) + row * p.ldd + col;
-            const __nv_bfloat16* cptr = reinterpret_cast<const __nv_bfloat16*>(p.C) + row * p.ldc + col;
+            const __nv_bfloat16* cptr = (GROUPED == 2 ? reinterpret_cast<const __nv_bfloat16*>(d_base) : reinterpret_cast<const __nv_bfloat16*>(p.C)) + row * p.ldc + col;
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               if (col + i < p.N) {
@@ -429,7 +450,7 @@ static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_
   return r == CUDA_SUCCESS ? 0 : -200 - static_cast<int>(r);
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool GROUPED, int COMM = 0>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int GROUPED, int COMM = 0>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, GROUPED, COMM>;
@@ -444,7 +465,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
 }
 
-template <int BN, int STAGES, bool GROUPED>
+template <int BN, int STAGES, int GROUPED>
 static int dispatch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                           int grid, cudaStream_t s) {
   if (!a_mn && !b_mn) return launch<BN, STAGES, false, false, GROUPED>(ta, tb, p, grid, s);
@@ -519,8 +540,8 @@ int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const fl
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
-  if (bn == 256) return dispatch_major<256, 4, false>(a_mn_major, b_mn_major, ta, tb, p, grid, stream);
-  return dispatch_major<128, 6, false>(a_mn_major, b_mn_major, ta, tb, p, grid, stream);
+  if (bn == 256) return dispatch_major<256, 4, 0>(a_mn_major, b_mn_major, ta, tb, p, grid, stream);
+  return dispatch_major<128, 6, 0>(a_mn_major, b_mn_major, ta, tb, p, grid, stream);
 }
 
 // Grouped GEMM over expert-major rows:  D[rows_g, :] = alpha * A[rows_g, :] * op(B[g]) + beta * C[rows_g, :].
@@ -564,8 +585,46 @@ int ftb_grouped_gemm_bf16(const void* A, const void* B, void* D, const void* C, 
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (p.max_tiles < grid) grid = p.max_tiles;
-  if (bn == 256) return dispatch_major<256, 4, true>(0, b_mn_major, ta, tb, p, grid, stream);
-  return dispatch_major<128, 6, true>(0, b_mn_major, ta, tb, p, grid, stream);
+  if (bn == 256) return dispatch_major<256, 4, 1>(0, b_mn_major, ta, tb, p, grid, stream);
+  return dispatch_major<128, 6, 1>(0, b_mn_major, ta, tb, p, grid, stream);
+}
+
+// Per-expert weight gradient in one launch:  G[g] (N, Kd) (+)= alpha * dY[rows_g, :N].T @ X[rows_g, :Kd]
+//   dY (total_rows, N) and X (total_rows, Kd) row-major, expert-major rows, offsets (G+1) int32 on device; each expert's
+//   row segment must start on a multiple of 64 and padding rows must be zero.  G is (num_groups, N, Kd) contiguous.
+int ftb_grouped_wgrad_bf16(const void* dY, const void* X, void* G, const int* offsets, int num_groups, int total_rows,
+                           int N, int Kd, int ldy, int ldx, float alpha, float beta, int g_fp32, int max_ctas,
+                           cudaStream_t stream) {
+  if (total_rows <= 0 || num_groups <= 0) return 0;
+  if ((ldy & 7) || (ldx & 7) || (N & 7) || (Kd & 7)) return -2;
+  const int bn = (Kd <= 128) ? 128 : 256;
+  CUtensorMap ta, tb;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)total_rows};
+    uint64_t str[1] = {(uint64_t)ldy * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_tmap(&ta, dY, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)Kd, (uint64_t)total_rows};
+    uint64_t str[1] = {(uint64_t)ldx * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_tmap(&tb, X, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  GemmParams p;
+  p.M = N; p.N = Kd; p.K = total_rows; p.ldd = Kd; p.ldc = Kd; p.alpha = alpha; p.beta = beta;
+  p.D = G; p.C = G; p.bias = nullptr; p.d_fp32 = g_fp32;
+  p.num_groups = num_groups; p.offsets = offsets; p.max_tiles = 0;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0;
+  const int tiles = num_groups * ((N + BM - 1) / BM) * ((Kd + bn - 1) / bn);
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = tiles;
+  if (bn == 256) return launch<256, 4, true, true, 2>(ta, tb, p, grid, stream);
+  return launch<128, 6, true, true, 2>(ta, tb, p, grid, stream);
 }
 
 // Tensor-parallel fused GEMM.  A is (M, K) K-major with M = world * panel_rows.
@@ -620,16 +679,16 @@ int ftb_gemm_bf16_tp(int mode, const void* A, void* const* a_peer, unsigned long
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
   if (mode == 1) {
-    if (bn == 256) return b_mn_major ? launch<256, 4, false, true, false, 1>(ta, tb, p, grid, stream)
-                                     : launch<256, 4, false, false, false, 1>(ta, tb, p, grid, stream);
-    return b_mn_major ? launch<128, 6, false, true, false, 1>(ta, tb, p, grid, stream)
-                      : launch<128, 6, false, false, false, 1>(ta, tb, p, grid, stream);
+    if (bn == 256) return b_mn_major ? launch<256, 4, false, true, 0, 1>(ta, tb, p, grid, stream)
+                                     : launch<256, 4, false, false, 0, 1>(ta, tb, p, grid, stream);
+    return b_mn_major ? launch<128, 6, false, true, 0, 1>(ta, tb, p, grid, stream)
+                      : launch<128, 6, false, false, 0, 1>(ta, tb, p, grid, stream);
   }
   if (mode == 2) {
-    if (bn == 256) return b_mn_major ? launch<256, 4, false, true, false, 2>(ta, tb, p, grid, stream)
-                                     : launch<256, 4, false, false, false, 2>(ta, tb, p, grid, stream);
-    return b_mn_major ? launch<128, 6, false, true, false, 2>(ta, tb, p, grid, stream)
-                      : launch<128, 6, false, false, false, 2>(ta, tb, p, grid, stream);
+    if (bn == 256) return b_mn_major ? launch<256, 4, false, true, 0, 2>(ta, tb, p, grid, stream)
+                                     : launch<256, 4, false, false, 0, 2>(ta, tb, p, grid, stream);
+    return b_mn_major ? launch<128, 6, false, true, 0, 2>(ta, tb, p, grid, stream)
+                      : launch<128, 6, false, false, 0, 2>(ta, tb, p, grid, stream);
   }
   return -2;
 }

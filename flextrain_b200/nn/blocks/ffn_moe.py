@@ -157,9 +157,9 @@ class MoEFFN:
             dw = ref.moe_rows_to_slots(dw_rows, plan, w.shape)
             if "g_down" in grads:
                 dyw = (dy_u.to(torch.float32) * wrow.unsqueeze(-1)).to(dy_u.dtype)
-                ops.grouped_wgrad(dyw, act, plan.offsets, grads["g_down"])
+                ops.grouped_wgrad(dyw, act, plan.offsets, grads["g_down"], pad=ROW_PAD)
             if "g_up" in grads:
-                ops.grouped_wgrad(dup, xs, plan.offsets, grads["g_up"])
+                ops.grouped_wgrad(dup, xs, plan.offsets, grads["g_up"], pad=ROW_PAD)
             dxs = ops.grouped_gemm(dup, params["w_up"], plan.offsets, trans_w=False)
             dh = ops.moe_combine(dxs, plan.inv, None, None)
         # router

@@ -324,7 +324,15 @@ def grouped_gemm(x, w, offsets, *, trans_w=True):
     return ref.grouped_gemm(x, w, offsets, trans_w=trans_w)
 
 
-grouped_wgrad = ref.grouped_wgrad
+def grouped_wgrad(dy, x, offsets, gw, *, alpha=1.0, pad: int = 1):
+    """``gw[e] += alpha * dy[rows_e].T @ x[rows_e]``. On CUDA one tcgen05 launch covers all experts; it needs every
+    expert's row segment padded to a multiple of 64 with zero rows (``pad``), which the MoE dispatch plan provides."""
+    if (_cuda_bf16(dy, x) and _GEMM_BACKEND == "tcgen05" and pad % 64 == 0 and gw.is_contiguous()
+            and gw.dtype in (torch.bfloat16, torch.float32) and dy.shape[1] % 8 == 0 and x.shape[1] % 8 == 0
+            and dy.stride(1) == 1 and x.stride(1) == 1 and dy.stride(0) % 8 == 0 and x.stride(0) % 8 == 0):
+        _count()
+        return _kernels().grouped_wgrad(dy, x, offsets.to(torch.int32), gw, alpha=alpha)
+    return ref.grouped_wgrad(dy, x, offsets, gw, alpha=alpha)
 
 
 # ---------------------------------------------------------------------- linear attention

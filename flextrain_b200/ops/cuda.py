@@ -133,6 +133,19 @@ def grouped_gemm(x, w, offsets, *, trans_w=True, out=None, alpha=1.0, beta=0.0):
     return out
 
 
+def grouped_wgrad(dy, x, offsets, gw, *, alpha=1.0, accumulate=True):
+    """``gw[e] (N, Kd) (+)= alpha * dy[rows_e].T @ x[rows_e]`` for all experts in one launch (rows padded to 64)."""
+    lib = load("gemm_tcgen05")
+    E, N, Kd = gw.shape
+    assert gw.is_contiguous() and dy.stride(1) == 1 and x.stride(1) == 1 and offsets.dtype == torch.int32
+    rc = lib.ftb_grouped_wgrad_bf16(_ptr(dy), _ptr(x), _ptr(gw), _ptr(offsets), c_int(E), c_int(dy.shape[0]), c_int(N),
+                                    c_int(Kd), c_int(dy.stride(0)), c_int(x.stride(0)), c_float(alpha),
+                                    c_float(1.0 if accumulate else 0.0), c_int(1 if gw.dtype == torch.float32 else 0),
+                                    c_int(GEMM_MAX_CTAS), _stream())
+    _check(rc, "ftb_grouped_wgrad_bf16")
+    return gw
+
+
 # ------------------------------------------------------------------------ elementwise
 def rmsnorm_fwd(x, w, eps):
     lib = load("elementwise")
