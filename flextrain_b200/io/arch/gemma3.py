@@ -19,6 +19,7 @@ def default_hyperparams() -> dict:
 def config_from_dims(dims, hyper):
     mc = _g.config_from_dims(dims, {**default_hyperparams(), **hyper})
     mc.arch = FAMILY
+    mc.rope_local = RopeConfig(theta=float(hyper.get("rope_local_theta", 10000.0)))   # sliding layers' own base
     return mc
 
 
