@@ -471,6 +471,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint64_t* pds_full = bars + 4;
   uint64_t* dq_full = bars + 5;
   uint64_t* dq_empty = bars + 6;
+  uint64_t* stage_bar = bars + 7;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -492,7 +493,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(dq_empty, 4);
+    mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(dq_empty, 4); mbar_init(stage_bar, 4);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
@@ -630,20 +631,33 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (lane == 0) mbar_arrive(pds_full);
       if (!(ok = mbar_wait(dq_full, ph, abort_flag, 231))) break;
       tc_fence_after();
-      float* dq_row = p.dq_acc + (grow * p.H + h) * HD;
+      // dQ tile: TMEM -> registers -> shared (XOR-swizzled so both the row-per-lane writes and the column-per-lane
+      // reads are conflict free) -> fp32 atomics that a warp issues on 32 consecutive addresses (one line each).
+      // The P / dS tiles are dead once dq_full has fired, so their 64 KB hold the fp32 tile.
+      float* sq = reinterpret_cast<float*>(sP);
 #pragma unroll 1
       for (int cb = 0; cb < HD; cb += 32) {
         uint32_t v[32];
         tmem_ld_32x32(tm_dQ + lane_base + cb, v);
         tmem_ld_wait();
-        if (vq) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) atomicAdd(dq_row + cb + e, __uint_as_float(v[e]));
-        }
+        for (int e = 0; e < 32; ++e) sq[r * HD + cb + (e ^ lane)] = __uint_as_float(v[e]);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(dq_empty);
+      if (lane == 0) mbar_arrive(dq_empty);       // TMEM columns are free: the next S / dP may be issued now
+      for (int rr = 0; rr < 32; ++rr) {
+        const int ii = qt + quad * 32 + rr;
+        if (ii >= len_q) break;
+        float* dq_row = p.dq_acc + ((static_cast<size_t>(qs + ii)) * p.H + h) * HD;
+        const float* srow = sq + (quad * 32 + rr) * HD;
+#pragma unroll
+        for (int cb = 0; cb < HD; cb += 32) atomicAdd(dq_row + cb + lane, srow[cb + (lane ^ rr)]);
+      }
+      // all four warps must be done with the staging area before anyone writes the next P / dS (bounded wait)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(stage_bar);
+      if (!(ok = mbar_wait(stage_bar, ph, abort_flag, 232))) break;
     }
     // dK / dV of this key tile (thread = key row)
     if (r < kr) {

@@ -66,6 +66,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 constexpr int RN_THREADS = 256;
 constexpr int RN_MAXV = 8;  // D <= 16384
 
+template <int MAXV>
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const bf16* __restrict__ x,
                                                                   const float* __restrict__ w, bf16* __restrict__ y,
                                                                   float* __restrict__ rstd_out, int T, int D,
@@ -74,10 +75,10 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const bf16* __r
   const int nv = D >> 3;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
-    uint4 v[RN_MAXV];
+    uint4 v[MAXV];
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < RN_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
       const int i = threadIdx.x + j * RN_THREADS;
       if (i < nv) {
         v[j] = xr[i];
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const bf16* __r
     if (threadIdx.x == 0 && rstd_out) rstd_out[row] = r;
     uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * D);
 #pragma unroll
-    for (int j = 0; j < RN_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
       const int i = threadIdx.x + j * RN_THREADS;
       if (i < nv) {
         float f[8];
@@ -115,6 +116,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const bf16* __r
 // dx = (g - xhat * mean(g . xhat)) * rstd, g = dy * w; optional dx += dx_add (residual gradient),
 // optional y_out = xhat * w (forward output re-emitted for the deferred weight-gradient GEMMs);
 // partial dw[blockIdx.x, :] = sum over this CTA's rows of dy * xhat (fp32), reduced by a second kernel.
+template <int MAXV>
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const bf16* __restrict__ dy,
                                                                   const bf16* __restrict__ x,
                                                                   const float* __restrict__ w,
@@ -124,9 +126,9 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const bf16* __r
                                                                   float* __restrict__ dw_partial, int T, int D) {
   __shared__ float sh[32];
   const int nv = D >> 3;
-  float dwacc[RN_MAXV][8];
+  float dwacc[MAXV][8];
 #pragma unroll
-  for (int j = 0; j < RN_MAXV; ++j)
+  for (int j = 0; j < MAXV; ++j)
 #pragma unroll
     for (int e = 0; e < 8; ++e) dwacc[j][e] = 0.f;
 
@@ -134,10 +136,10 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const bf16* __r
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + (size_t)row * D);
     const float r = rstd[row];
-    uint4 xv[RN_MAXV], gv[RN_MAXV];
+    uint4 xv[MAXV], gv[MAXV];
     float dot = 0.f;
 #pragma unroll
-    for (int j = 0; j < RN_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
       const int i = threadIdx.x + j * RN_THREADS;
       if (i < nv) {
         xv[j] = xr[i];
@@ -164,7 +166,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const bf16* __r
     dot = block_sum<RN_THREADS / 32>(dot, sh) / (float)D;
     uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * D);
 #pragma unroll
-    for (int j = 0; j < RN_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
       const int i = threadIdx.x + j * RN_THREADS;
       if (i < nv) {
         float xf[8], gf[8], wf[8], o[8];
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const bf16* __r
   }
   if (dw_partial) {
 #pragma unroll
-    for (int j = 0; j < RN_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
       const int i = threadIdx.x + j * RN_THREADS;
       if (i < nv) {
         float* o = dw_partial + (size_t)blockIdx.x * D + i * 8;
@@ -728,19 +730,31 @@ int ftb_rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd, int T, 
                     cudaStream_t s) {
   if (T == 0) return 0;
   if (D % 8 || D > 8 * RN_THREADS * RN_MAXV) return -2;
-  rmsnorm_fwd_kernel<<<grid_rows(T, 148 * 8), RN_THREADS, 0, s>>>((const bf16*)x, w, (bf16*)y, rstd, T, D, eps);
+  const int nv = D / 8;
+  if (nv <= 2 * RN_THREADS)
+    rmsnorm_fwd_kernel<2><<<grid_rows(T, 148 * 8), RN_THREADS, 0, s>>>((const bf16*)x, w, (bf16*)y, rstd, T, D, eps);
+  else if (nv <= 4 * RN_THREADS)
+    rmsnorm_fwd_kernel<4><<<grid_rows(T, 148 * 8), RN_THREADS, 0, s>>>((const bf16*)x, w, (bf16*)y, rstd, T, D, eps);
+  else
+    rmsnorm_fwd_kernel<8><<<grid_rows(T, 148 * 8), RN_THREADS, 0, s>>>((const bf16*)x, w, (bf16*)y, rstd, T, D, eps);
   CHECK_LAUNCH();
 }
 
 // dw_partial: fp32 workspace of (ftb_rmsnorm_bwd_blocks(T) * D); dw (fp32, D) accumulated if dw != null.
-int ftb_rmsnorm_bwd_blocks(int T) { return grid_rows(T, 148 * 2); }
+int ftb_rmsnorm_bwd_blocks(int T) { return grid_rows(T, 148 * 4); }
 int ftb_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dx_add, void* dx,
                     void* y_out, float* dw_partial, float* dw, int dw_accumulate, int T, int D, cudaStream_t s) {
   if (T == 0) return 0;
   if (D % 8 || D > 8 * RN_THREADS * RN_MAXV) return -2;
   const int blocks = ftb_rmsnorm_bwd_blocks(T);
-  rmsnorm_bwd_kernel<<<blocks, RN_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)x, w, rstd, (const bf16*)dx_add,
-                                                    (bf16*)dx, (bf16*)y_out, dw ? dw_partial : nullptr, T, D);
+  const int nv = D / 8;
+#define FTB_RN_BWD(MV)                                                                                              \
+  rmsnorm_bwd_kernel<MV><<<blocks, RN_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)x, w, rstd, (const bf16*)dx_add, \
+                                                       (bf16*)dx, (bf16*)y_out, dw ? dw_partial : nullptr, T, D)
+  if (nv <= 2 * RN_THREADS) FTB_RN_BWD(2);
+  else if (nv <= 4 * RN_THREADS) FTB_RN_BWD(4);
+  else FTB_RN_BWD(8);
+#undef FTB_RN_BWD
   if (dw) colsum_accum_kernel<<<(D + 255) / 256, 256, 0, s>>>(dw_partial, dw, blocks, D, dw_accumulate);
   CHECK_LAUNCH();
 }
