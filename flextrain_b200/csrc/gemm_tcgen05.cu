@@ -465,6 +465,225 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
 }
 
+
+// =====================================================================================================
+// Two-SM variant (tcgen05 cta_group::2): a cluster of two CTAs owns one 256 x 256 output tile.  Each CTA stages its
+// own 128 rows of A and HALF of the B tile (128 of the 256 N rows), so per 64-wide K block a CTA moves 32 KB instead
+// of 48 KB for twice the math per pair: a third less L2 -> SM and shared-memory traffic, which is what bounds the
+// one-SM kernel.  The leader CTA issues the MMAs for the pair; completion is multicast to both CTAs' barriers
+// (tcgen05.commit); loads are plain tiled TMA loads credited to the leader's barrier (no cluster multicast loads).
+// =====================================================================================================
+constexpr int BN2 = 256;
+constexpr int ST2 = 6;
+constexpr int STAGE2_BYTES = 2 * BM * BK * 2;   // A (128 x 64) + B half (128 x 64)
+constexpr int SMEM2_TOTAL = ST2 * STAGE2_BYTES + 256 + 1024;
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + ST2 * STAGE2_BYTES);
+  uint64_t* empty_bar = full_bar + ST2;
+  uint64_t* tfull_bar = empty_bar + ST2;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();
+  const bool leader = cta == 0;
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + BN2 - 1) / BN2;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < ST2; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(tmem_slot, 512);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int row0 = tm * 2 * BM + static_cast<int>(cta) * BM;      // this CTA's 128 rows of A
+        const int col0 = tn * BN2 + static_cast<int>(cta) * (BN2 / 2);  // this CTA's half of B's N rows
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 50))) break;
+          uint8_t* sa = smem + stage * STAGE2_BYTES;
+          uint8_t* sb = sa + BM * BK * 2;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE2_BYTES);
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d_2cta(sa, &tmA, &full_bar[stage], k0, row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_2cta(sa + j * (64 * BK * 2), &tmA, &full_bar[stage], row0 + j * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_2cta(sb, &tmB, &full_bar[stage], k0, col0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_2cta(sb + j * (64 * BK * 2), &tmB, &full_bar[stage], col0 + j * 64, k0);
+          }
+          if (++stage == ST2) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN2, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        if (!(ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, 60))) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN2;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag, 61))) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE2_BYTES);
+          const uint32_t sb = sa + BM * BK * 2;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t ad = A_MN ? make_smem_desc(sa + kk * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                     : make_smem_desc(sa + kk * (UMMA_K * 2), 16, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc(sb + kk * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                     : make_smem_desc(sb + kk * (UMMA_K * 2), 16, 1024);
+            umma_f16_2cta(tmem_d, ad, bd, idesc, (kb | kk) != 0);
+          }
+          umma_commit_2cta(&empty_bar[stage], 3);   // frees this stage in both CTAs
+          if (++stage == ST2) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_2cta(&tfull_bar[acc], 3);       // accumulator ready in both CTAs
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int row0 = tm * 2 * BM + static_cast<int>(cta) * BM;
+      const int rows = min(BM, p.M - row0);
+      if (!(ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 70))) break;
+      tc_fence_after();
+      const int r_in = quad * 32 + lane;
+      const bool row_ok = r_in < rows;
+      const size_t row = static_cast<size_t>(row0 + r_in);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN2;
+#pragma unroll 1
+      for (int c = 0; c < BN2; c += 32) {
+        const int col = tn * BN2 + c;
+        if (col >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col + i < p.N) v[i] += p.bias[col + i];
+          }
+          if (p.d_fp32) {
+            float* dptr = reinterpret_cast<float*>(p.D) + row * p.ldd + col;
+            const float* cptr = reinterpret_cast<const float*>(p.C) + row * p.ldc + col;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (col + i < p.N) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (p.beta != 0.f) {
+                  const float4 cc = *reinterpret_cast<const float4*>(cptr + i);
+                  o.x += p.beta * cc.x; o.y += p.beta * cc.y; o.z += p.beta * cc.z; o.w += p.beta * cc.w;
+                }
+                *reinterpret_cast<float4*>(dptr + i) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* dptr = reinterpret_cast<__nv_bfloat16*>(p.D) + row * p.ldd + col;
+            const __nv_bfloat16* cptr = reinterpret_cast<const __nv_bfloat16*>(p.C) + row * p.ldc + col;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col + i < p.N) {
+                if (p.beta != 0.f) {
+                  const uint4 cc = *reinterpret_cast<const uint4*>(cptr + i);
+                  const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&cc);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(c2[j]);
+                    v[i + 2 * j] += p.beta * f.x;
+                    v[i + 2 * j + 1] += p.beta * f.y;
+                  }
+                }
+                uint4 o;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(dptr + i) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tempty_bar[acc]);   // 4 warps x 2 CTAs release the accumulator
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();     // the leader's MMAs also write the peer's TMEM: nobody frees before both are done
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, 512);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  auto kern = gemm2_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_TOTAL);
+    if (e != cudaSuccess) return -300 - static_cast<int>(e);
+    configured = true;
+  }
+  kern<<<grid, 192, SMEM2_TOTAL, stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
+}
+
 template <int BN, int STAGES, int GROUPED>
 static int dispatch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                           int grid, cudaStream_t s) {
@@ -478,6 +697,7 @@ static int dispatch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUten
 
 using namespace ftb;
 
+static int g_use_2cta = 1;    // ftb_gemm_set_two_sm(0) falls back to the one-SM kernel for every shape
 static int g_sm_count = 0;
 static int sm_count() {
   if (g_sm_count == 0) {
@@ -503,6 +723,51 @@ int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const fl
   if ((lda & 7) || (ldb & 7) || (N & 7) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(D) & 15))
     return -2;
+  // bn == 512 selects the two-SM kernel (256 x 256 tile per CTA pair); bn == 0 picks it for large problems
+  const bool two_sm = (bn == 512) || (bn == 0 && g_use_2cta && M >= 512 && N >= 512);
+  if (two_sm) {
+    CUtensorMap ta2, tb2;
+    int rc2;
+    if (!a_mn_major) {
+      uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+      uint64_t str[1] = {(uint64_t)lda * 2};
+      uint32_t box[2] = {BK, BM};
+      rc2 = make_tmap(&ta2, A, 2, dims, str, box);
+    } else {
+      uint64_t dims[2] = {(uint64_t)M, (uint64_t)K};
+      uint64_t str[1] = {(uint64_t)lda * 2};
+      uint32_t box[2] = {64, BK};
+      rc2 = make_tmap(&ta2, A, 2, dims, str, box);
+    }
+    if (rc2) return rc2;
+    if (!b_mn_major) {
+      uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+      uint64_t str[1] = {(uint64_t)ldb * 2};
+      uint32_t box[2] = {BK, BM};                      // half of the 256-wide B tile per CTA
+      rc2 = make_tmap(&tb2, B, 2, dims, str, box);
+    } else {
+      uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+      uint64_t str[1] = {(uint64_t)ldb * 2};
+      uint32_t box[2] = {64, BK};
+      rc2 = make_tmap(&tb2, B, 2, dims, str, box);
+    }
+    if (rc2) return rc2;
+    GemmParams p2;
+    p2.M = M; p2.N = N; p2.K = K; p2.ldd = ldd; p2.ldc = (C != nullptr) ? ldc : ldd;
+    p2.alpha = alpha; p2.beta = (C != nullptr) ? beta : 0.f;
+    p2.D = D; p2.C = (C != nullptr) ? C : D; p2.bias = bias; p2.d_fp32 = d_fp32;
+    p2.num_groups = 0; p2.offsets = nullptr; p2.max_tiles = 0;
+    p2.comm_mode = 0; p2.world = 1; p2.rank = 0; p2.panel_rows = 0;
+    const int tiles2 = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN2 - 1) / BN2);
+    int grid2 = sm_count() & ~1;
+    if (max_ctas > 0 && max_ctas < grid2) grid2 = max_ctas & ~1;
+    if (2 * tiles2 < grid2) grid2 = 2 * tiles2;
+    if (grid2 < 2) grid2 = 2;
+    if (!a_mn_major && !b_mn_major) return launch2<false, false>(ta2, tb2, p2, grid2, stream);
+    if (!a_mn_major && b_mn_major) return launch2<false, true>(ta2, tb2, p2, grid2, stream);
+    if (a_mn_major && !b_mn_major) return launch2<true, false>(ta2, tb2, p2, grid2, stream);
+    return launch2<true, true>(ta2, tb2, p2, grid2, stream);
+  }
   if (bn != 128 && bn != 256) bn = (N <= 128) ? 128 : 256;
   CUtensorMap ta, tb;
   int rc;
@@ -543,6 +808,8 @@ int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const fl
   if (bn == 256) return dispatch_major<256, 4, 0>(a_mn_major, b_mn_major, ta, tb, p, grid, stream);
   return dispatch_major<128, 6, 0>(a_mn_major, b_mn_major, ta, tb, p, grid, stream);
 }
+
+void ftb_gemm_set_two_sm(int on) { g_use_2cta = on; }
 
 // Grouped GEMM over expert-major rows:  D[rows_g, :] = alpha * A[rows_g, :] * op(B[g]) + beta * C[rows_g, :].
 //   A (total_rows, K) row-major; B (G, N, K) if b_mn_major = 0, (G, K, N) if 1; offsets (G+1) int32 on device.

@@ -38,6 +38,8 @@ def load(name: str) -> ctypes.CDLL:
         raise NativeLibraryMissing(f"native library {path} is missing; run `python -m flextrain_b200.build`")
     lib = ctypes.CDLL(str(path))
     _libs[name] = lib
+    if name == "gemm_tcgen05" and os.environ.get("FTB_GEMM_TWO_SM", "1") == "0":
+        lib.ftb_gemm_set_two_sm(c_int(0))   # one-SM tiles for every shape (A/B comparisons)
     return lib
 
 

@@ -63,6 +63,34 @@ def test_gemm_large_matches_cublas():
     assert _rel(out2, wide[:, K:].float() @ b.float().t()) < 5e-3
 
 
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 512), (1000, 520, 320), (4096, 4096, 1024)])
+def test_gemm_two_sm_layouts(ta, tb, M, N, K):
+    """The cta_group::2 kernel (a CTA pair per 256 x 256 tile), forced with bn=512, against the fp32 reference."""
+    from flextrain_b200.ops import cuda as k
+    a = _rand(K, M) if ta else _rand(M, K)
+    b = _rand(N, K) if tb else _rand(K, N)
+    out = k.gemm(a, b, trans_a=ta, trans_b=tb, bn=512)
+    want = ref.gemm(a, b, trans_a=ta, trans_b=tb, out_dtype=torch.float32)
+    assert _rel(out, want) < 5e-3, (ta, tb, M, N, K, _rel(out, want))
+    assert k.device_error_words().get("gemm_tcgen05", 0) == 0
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_two_sm_epilogue(out_dtype):
+    from flextrain_b200.ops import cuda as k
+    M, N, K = 768, 1024, 512
+    a, b = _rand(M, K), _rand(N, K)
+    c = _rand(M, N, dtype=out_dtype)
+    bias = torch.randn(N, device=DEV)
+    out = k.gemm(a, b, trans_b=True, alpha=0.5, beta=2.0, c=c, bias=bias, out_dtype=out_dtype, bn=512)
+    want = 0.5 * (a.float() @ b.float().t()) + 2.0 * c.float() + bias
+    assert _rel(out, want) < 6e-3
+    acc = c.clone()
+    k.gemm(a, b, trans_b=True, beta=1.0, out=acc, bn=512)
+    assert _rel(acc, a.float() @ b.float().t() + c.float()) < 6e-3
+
+
 def test_grouped_gemm():
     from flextrain_b200.ops import cuda as k
     E, K, N = 8, 256, 384
