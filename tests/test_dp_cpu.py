@@ -36,7 +36,7 @@ def _worker(rank, world, port, out):
             am.step()
             losses.append(st.loss_sum)
         flat = torch.cat([t.flatten().float() for _, _, _, t in am.named_master_params()])
-        out.put((rank, losses, flat))
+        out.put((rank, losses, flat.numpy()))   # by value: a tensor would travel as a shared-memory handle that dies with the worker
     finally:
         dist.destroy_process_group()
 
@@ -50,6 +50,7 @@ def test_two_rank_collective_matches_single_process():
     for p in procs:
         p.start()
     res = sorted([q.get(timeout=300) for _ in range(world)], key=lambda x: x[0])
+    res = [(r, l, torch.from_numpy(f)) for r, l, f in res]
     for p in procs:
         p.join(60)
     # single process on the union of the data
