@@ -33,6 +33,32 @@ LLAMA31_8B = dict(vocab_size=128256, n_layers=32, d_model=4096, n_heads=32, n_kv
                   expert_dim=14336, ffn_dim=14336, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
 SEQ_LEN = 1024
 GLOBAL_BATCH = 524288
+# The other named configurations (``--config``); the headline stays llama8b.
+CONFIGS = {
+    "llama8b": dict(model="Llama-3.1-8B", arch="llama", dims=LLAMA31_8B, seq_len=SEQ_LEN, global_batch=GLOBAL_BATCH,
+                    hyper={"rope_theta": 500000.0, "norm_eps": 1e-5}, scaling="strong"),
+    # long-context dense 12B: one 32768-token sequence per GPU (weak scaling), chunked attention with a KV window
+    "longctx12b": dict(model="dense-12B long context", arch="llama",
+                       dims=dict(vocab_size=131072, n_layers=40, d_model=5120, n_heads=32, n_kv_heads=8, head_dim=128,
+                                 expert_dim=14336, ffn_dim=14336, num_routed_experts=0, num_shared_experts=0, top_k=0,
+                                 is_causal=True),
+                       seq_len=32768, per_gpu_batch=32768, hyper={"rope_theta": 1000000.0, "norm_eps": 1e-5},
+                       scaling="weak"),
+    # Qwen3-MoE 30B-A3B: experts sharded over all GPUs (expert parallel), the rest data parallel
+    "qwen3moe30b": dict(model="Qwen3-30B-A3B", arch="qwen3_moe",
+                        dims=dict(vocab_size=151936, n_layers=48, d_model=2048, n_heads=32, n_kv_heads=4, head_dim=128,
+                                  expert_dim=768, ffn_dim=768, num_routed_experts=128, num_shared_experts=0, top_k=8,
+                                  is_causal=True),
+                        seq_len=4096, global_batch=262144, hyper={"rope_theta": 1000000.0, "norm_eps": 1e-6},
+                        scaling="strong", ep="world"),
+    # Llama-3-70B architecture: tensor parallel over all GPUs
+    "llama70b": dict(model="Llama-3-70B", arch="llama",
+                     dims=dict(vocab_size=128256, n_layers=80, d_model=8192, n_heads=64, n_kv_heads=8, head_dim=128,
+                               expert_dim=28672, ffn_dim=28672, num_routed_experts=0, num_shared_experts=0, top_k=0,
+                               is_causal=True),
+                     seq_len=2048, global_batch=262144, hyper={"rope_theta": 500000.0, "norm_eps": 1e-5},
+                     scaling="strong", tp="world"),
+}
 PUBLISHED_TOK_S = 3733.0          # reference, RTX 5090, Llama-3.1-8B full FT (docs/verified_runs.md:160)
 METRIC = "train tokens/sec/box, Llama-3.1-8B full FT"
 
@@ -111,19 +137,22 @@ def run_ours(args):
     dev = f"cuda:{local}"
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device(dev))
-    dims = dict(LLAMA31_8B)
-    seq_len, gbatch = SEQ_LEN, GLOBAL_BATCH
+    cfg = CONFIGS[args.config]
+    dims = dict(cfg["dims"])
+    seq_len = cfg["seq_len"]
+    gbatch = cfg.get("global_batch") or cfg["per_gpu_batch"] * world
     if args.small:                          # debugging only; never used for a reported number
         dims.update(n_layers=4)
-        gbatch = 65536
+        gbatch = 65536 if "global_batch" in cfg else gbatch
     per_rank = gbatch // world
     free, total = torch.cuda.mem_get_info()
     opt = ft.AdamW(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, state_dtype=torch.float32)
-    am = ft.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len, max_global_batch_tokens=gbatch,
+    par = {k: (world if cfg.get(k) == "world" else 1) for k in ("tp", "ep")}
+    am = ft.from_dims(dims, arch=cfg["arch"], optimizer=opt, max_seq_len=seq_len, max_global_batch_tokens=gbatch,
                       max_gpu_mem_bytes=int(free), max_host_mem_bytes=args.host_gib << 30, device=dev,
-                      hyperparams={"rope_theta": 500000.0, "norm_eps": 1e-5}, world_size=world, rank=rank,
+                      hyperparams=cfg["hyper"], world_size=world, rank=rank,
                       dp_shard=args.shard, init_on_device=True, init_std=0.02, verbose=(rank == 0 and args.verbose),
-                      max_chunk_size=args.chunk, head_chunk_size=args.head_chunk)
+                      max_chunk_size=args.chunk, head_chunk_size=args.head_chunk, **par)
     src = ft.SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234 + rank, pin=True)
 
     def one_step(seqs):
@@ -175,8 +204,15 @@ def run_ours(args):
         ms_step = dev_ms / args.steps
         value = gbatch / (ms_step / 1e3)
         e2e_val = gbatch / (e2e_ms / args.steps / 1e3)
-        n_params = sum(t.numel() for _, _, _, t in am.named_master_params())
-        flops_tok = 6.0 * (n_params - dims["vocab_size"] * dims["d_model"]) + 6.0 * seq_len * dims["d_model"] * dims["n_layers"]
+        n_params = 0
+        for scope, l, name, t in am.named_master_params():
+            sp = am.spec_of(scope, l, name)
+            if sp.shard.ep_dim is not None:       # routed experts: only top_k of num_experts are active per token
+                n_params += t.numel() * par["ep"] * dims["top_k"] // dims["num_routed_experts"]
+            else:
+                n_params += t.numel() * (par["tp"] if sp.is_local_part else 1)
+        flops_tok = 6.0 * (n_params - dims["vocab_size"] * dims["d_model"]) \
+            + 6.0 * seq_len * dims["n_heads"] * dims["head_dim"] * dims["n_layers"]
         tflops_gpu = value * flops_tok / world / 1e12
         peaks = {}
         try:
@@ -186,11 +222,13 @@ def run_ours(args):
             pass
         sustained = peaks.get("bf16_tflops_sustained", 1400.0)
         _emit({
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": value / PUBLISHED_TOK_S, "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights",
-            "config": {"model": "Llama-3.1-8B" + (" (SMALL DEBUG)" if args.small else ""), "global_batch": gbatch,
-                       "seq_len": seq_len, "parallelism": f"dp{world}" + (f"-shard({am.ws.shard})" if world > 1 else ""),
+            "metric": METRIC if args.config == "llama8b" else f"train tokens/sec/box, {cfg['model']} full FT",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": cfg["scaling"],
+            "vs_baseline": value / PUBLISHED_TOK_S if args.config == "llama8b" else None, "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights",
+            "config": {"model": cfg["model"] + (" (SMALL DEBUG)" if args.small else ""), "global_batch": gbatch,
+                       "seq_len": seq_len, "parallelism": (f"tp{world}" if par["tp"] > 1 else f"dp{world}" + (f"+ep{world}" if par["ep"] > 1 else ""))
+                       + (f"-shard({am.ws.shard})" if world > 1 else ""),
                        "optimizer": "AdamW fp32 state", "round_tokens": am.ws.target_round_tokens,
                        "chunk": am.ws.max_chunk_size, "rounds_per_step": am.ws.target_num_rounds,
                        "l2": "inputs larger than L2 (each step streams >100 GB of weights/activations)",
@@ -326,7 +364,7 @@ def run_reference(args):
                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                "scaling": "strong", "vs_baseline": value / PUBLISHED_TOK_S, "dtype": "bf16",
                "data": "synthetic uniform tokens, random-init weights",
-               "config": {"model": "Llama-3.1-8B" + (" (SMALL DEBUG)" if args.small else ""), "global_batch": gbatch,
+               "config": {"model": cfg["model"] + (" (SMALL DEBUG)" if args.small else ""), "global_batch": gbatch,
                           "seq_len": seq_len,
                           "parallelism": f"dp{world}" + (" (constructed: one reference engine per GPU + NCCL "
                                                          "all-reduce of host gradients)" if world > 1 else "")},
@@ -344,6 +382,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--config", choices=sorted(CONFIGS), default="llama8b",
+                    help="named configuration; the headline number is llama8b")
     ap.add_argument("--shard", default=None, help="data-parallel shard mode (default: planner's choice)")
     ap.add_argument("--chunk", type=int, default=None)
     ap.add_argument("--head-chunk", type=int, default=4096)

@@ -54,9 +54,16 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
                         max_host_mem_bytes, device, leeway_gpu_mem_bytes, leeway_host_mem_bytes, dt: DTypePolicy,
                         lora, hw_cost, force_saved_act_level, head_chunk_size, verbose, min_chunk_size,
                         max_chunk_size, ws: Optional[WorkingSetConfig], world_size, rank, dp_shard, tp, ep,
-                        process_group, model_dir=None, arch_key=None, host_backend=None) -> ActiveModel:
+                        process_group, model_dir=None, arch_key=None, host_backend=None,
+                        plan_only: bool = False) -> ActiveModel:
     builder = _BLOCK_BUILDERS.get(arch_key) if arch_key else None
     embed, layers, head = build_model_parts(mc, dt, lora, head_chunk_size, builder)
+    if ep > 1:
+        # expert parallelism: every rank owns num_experts / ep experts of each MoE layer
+        for layer in layers:
+            for t in layer.param_spec.tensors:
+                if t.shard.ep_dim is not None:
+                    t.localize(t.shard.ep_dim, rank % ep, ep)
     hw = _hw_cost(hw_cost, device)
     if ws is None:
         ws = determine_working_set_config(
@@ -66,6 +73,8 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
             leeway_host_mem_bytes=leeway_host_mem_bytes, hw=hw, world_size=world_size, tp=tp, ep=ep, shard=dp_shard,
             min_chunk_size=min_chunk_size, max_chunk_size=max_chunk_size,
             force_saved_act_level=force_saved_act_level, verbose=verbose)
+    if plan_only:
+        return ws
     dp = tp_group = ep_group = None
     if world_size > 1:
         from .parallel import build_parallel
@@ -107,6 +116,11 @@ def _init_random_weights(am: ActiveModel, seed: int, std: float, on_device: bool
         elif dev_gen is not None and t.is_cuda:
             # large models: draw on the GPU (same distribution, different stream of numbers than the CPU generator)
             t.normal_(0.0, std, generator=dev_gen)
+        elif spec.is_local_part:
+            # same numbers as the unsharded model: draw the whole tensor, keep this rank's part
+            dim, a, b = spec.local_slice
+            full = torch.randn(spec.global_shape, generator=g, dtype=torch.float32) * std
+            t.copy_(full.narrow(dim, a, b - a).to(t.dtype))
         else:
             t.copy_((torch.randn(t.shape, generator=g, dtype=torch.float32) * std).to(t.dtype))
     if am.head.tied:
@@ -138,8 +152,11 @@ def from_dims(dims: Mapping, *, arch: str = "llama", optimizer, max_seq_len: int
               min_chunk_size: Optional[int] = None, max_chunk_size: Optional[int] = None, moe_backend=None,
               working_set: Optional[WorkingSetConfig] = None, world_size: int = 1, rank: int = 0,
               dp_shard: Optional[str] = None, tp: int = 1, ep: int = 1, process_group=None, host_backend=None,
-              init_weights: bool = True, init_on_device: bool = False) -> ActiveModel:
-    """Build an :class:`ActiveModel` from a dims dict with deterministic random weights; bypasses HF entirely."""
+              init_weights: bool = True, init_on_device: bool = False, plan_only: bool = False) -> ActiveModel:
+    """Build an :class:`ActiveModel` from a dims dict with deterministic random weights; bypasses HF entirely.
+
+    ``plan_only=True`` stops after the working-set planner and returns its :class:`WorkingSetConfig` (nothing is
+    allocated, no process group is needed): what the engine WOULD do for this model, budget and parallel layout."""
     mod = select_arch_module(arch)
     hyper = dict(mod.default_hyperparams()) if hasattr(mod, "default_hyperparams") else {}
     hyper.update(hyperparams or {})
@@ -156,7 +173,9 @@ def from_dims(dims: Mapping, *, arch: str = "llama", optimizer, max_seq_len: int
                              head_chunk_size=head_chunk_size, verbose=verbose, min_chunk_size=min_chunk_size,
                              max_chunk_size=max_chunk_size, ws=working_set, world_size=world_size, rank=rank,
                              dp_shard=dp_shard, tp=tp, ep=ep, process_group=process_group, arch_key=arch,
-                             host_backend=host_backend)
+                             host_backend=host_backend, plan_only=plan_only)
+    if plan_only:
+        return am
     am.dims = dict(dims)
     if init_weights:
         _init_random_weights(am, init_seed, init_std, on_device=init_on_device)

@@ -49,6 +49,8 @@ class TensorSpec:
     frozen: bool = False
     init: str = "normal"                   # "normal" | "ones" | "zeros"
     shard: ShardSpec = field(default_factory=ShardSpec)
+    global_shape: Optional[Tuple[int, ...]] = None          # set by localize(): the unsharded shape
+    local_slice: Optional[Tuple[int, int, int]] = None      # (dim, start, stop) of this rank's part
 
     def __post_init__(self):
         self.shape = tuple(int(s) for s in self.shape)
@@ -60,6 +62,22 @@ class TensorSpec:
     @property
     def numel(self) -> int:
         return int(math.prod(self.shape))
+
+    def localize(self, dim: int, index: int, count: int) -> "TensorSpec":
+        """Keep only part ``index`` of ``count`` along ``dim`` (tensor- or expert-parallel ownership).  Buffers,
+        gradients and optimizer state are then sized for the local part; loaders slice, exporters gather."""
+        g = self.global_shape or self.shape
+        if g[dim] % count:
+            raise ValueError(f"{self.name}: dim {dim} of {g} is not divisible by {count}")
+        n = g[dim] // count
+        self.global_shape = tuple(g)
+        self.local_slice = (dim, index * n, (index + 1) * n)
+        self.shape = tuple(g[:dim]) + (n,) + tuple(g[dim + 1:])
+        return self
+
+    @property
+    def is_local_part(self) -> bool:
+        return self.local_slice is not None
 
     @property
     def grad_name(self) -> str:

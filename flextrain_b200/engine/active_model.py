@@ -501,6 +501,11 @@ class ActiveModel:
         for n, t in self.buffers.head_params().items():
             yield "head", -1, n, t
 
+    def spec_of(self, scope: str, layer: int, name: str):
+        """The :class:`TensorSpec` behind one item of :meth:`named_master_params`."""
+        ps = {"embed": self.embed, "head": self.head}.get(scope) or self.layers[layer]
+        return ps.param_spec.get(name)
+
     def push_masters_to_device(self) -> None:
         """After editing host masters of a ringed model (load / init), nothing else is needed: layers are fetched
         from the masters on demand.  Resident models are edited in place."""

@@ -81,7 +81,7 @@ def _resolve(entry: WeightMapEntry, src: SafetensorsDir) -> Optional[List[torch.
 
 
 def _load_entries(entries: List[WeightMapEntry], dst: Dict[str, torch.Tensor], src: SafetensorsDir, where: str,
-                  strict: bool) -> None:
+                  strict: bool, specs=None) -> None:
     for e in entries:
         if e.name not in dst:
             if strict:
@@ -98,6 +98,10 @@ def _load_entries(entries: List[WeightMapEntry], dst: Dict[str, torch.Tensor], s
         if e.plus_one:
             t = t.to(torch.float32) + 1.0
         d = dst[e.name]
+        ts_spec = specs.get(e.name) if specs is not None else None
+        if ts_spec is not None and ts_spec.is_local_part:
+            dim, a, b = ts_spec.local_slice          # tensor / expert parallel: keep this rank's part
+            t = t.narrow(dim, a, b - a)
         if tuple(t.shape) != tuple(d.shape):
             raise ValueError(f"{where}: shape mismatch for {e.name!r}: checkpoint {tuple(t.shape)} vs engine "
                              f"{tuple(d.shape)}")
@@ -111,16 +115,19 @@ def load_hf_into_model(am, model_dir: str, strict: bool = False) -> None:
     spec: ArchSpec = select_arch_module(mc.arch).ARCH_SPEC
     src = SafetensorsDir(model_dir)
     bm = am.buffers
-    _load_entries(spec.embed(mc), bm.embed_params(), src, "embed", strict)
+    by_name = lambda ps: {t.name: t for t in ps.tensors}
+    _load_entries(spec.embed(mc), bm.embed_params(), src, "embed", strict, by_name(am.embed.param_spec))
     for i in range(len(am.layers)):
-        _load_entries(spec.layer(i, mc), bm.host_params(i), src, f"layer {i}", strict)
+        _load_entries(spec.layer(i, mc), bm.host_params(i), src, f"layer {i}", strict,
+                      by_name(am.layers[i].param_spec))
     head_entries = spec.head(mc)
     hp = bm.head_params()
     tied_missing = False
     for e in head_entries:
         if e.name == "w_head_proj" and _peek(e, src) is None:
             tied_missing = True
-    _load_entries([e for e in head_entries if not (e.name == "w_head_proj" and tied_missing)], hp, src, "head", strict)
+    _load_entries([e for e in head_entries if not (e.name == "w_head_proj" and tied_missing)], hp, src, "head", strict,
+                  by_name(am.head.param_spec))
     if tied_missing or mc.tie_embeddings:
         # tied embeddings: the head arrives empty and mirrors the embedding table (reference FINDING 10)
         hp["w_head_proj"].copy_(bm.embed_params()["w_tok_embeddings"])
@@ -146,11 +153,15 @@ def collect_hf_state(am, lora_merge: bool = False) -> Dict[str, torch.Tensor]:
     bm = am.buffers
     out: Dict[str, torch.Tensor] = {}
 
-    def emit(entries: List[WeightMapEntry], params: Dict[str, torch.Tensor]):
+    def emit(entries: List[WeightMapEntry], params: Dict[str, torch.Tensor], specs=None):
         for e in entries:
             if e.name not in params:
                 continue
-            t = params[e.name].detach().to("cpu")
+            t = params[e.name].detach()
+            ts_spec = specs.get(e.name) if specs is not None else None
+            if ts_spec is not None and ts_spec.is_local_part:
+                t = gather_local_parts(t, ts_spec, am)     # collective: every rank takes part in the export
+            t = t.to("cpu")
             if lora_merge and (e.name + "_lora_a") in params:
                 from ..export._merged import merged_weight
                 t = merged_weight(params, e.name, am)
@@ -162,14 +173,28 @@ def collect_hf_state(am, lora_merge: bool = False) -> Dict[str, torch.Tensor]:
             for n, p in zip(e.hf_names, parts):
                 out[n] = p.contiguous()
 
-    emit(spec.embed(mc), bm.embed_params())
+    by_name = lambda ps: {t.name: t for t in ps.tensors}
+    emit(spec.embed(mc), bm.embed_params(), by_name(am.embed.param_spec))
     for i in range(len(am.layers)):
-        emit(spec.layer(i, mc), bm.host_params(i))
+        emit(spec.layer(i, mc), bm.host_params(i), by_name(am.layers[i].param_spec))
     head_entries = spec.head(mc)
     if am.head.tied or mc.tie_embeddings:
         head_entries = [e for e in head_entries if e.name != "w_head_proj"]
-    emit(head_entries, bm.head_params())
+    emit(head_entries, bm.head_params(), by_name(am.head.param_spec))
     return out
+
+
+def gather_local_parts(t: torch.Tensor, spec, am) -> torch.Tensor:
+    """Reassemble a tensor- or expert-parallel tensor from the parts held by the ranks of its group."""
+    import torch.distributed as dist
+    dim, a, b = spec.local_slice
+    count = spec.global_shape[dim] // (b - a)
+    if count == 1 or not dist.is_initialized():
+        return t
+    group = getattr(am, "shard_group", None)
+    parts = [torch.empty_like(t) for _ in range(count)]
+    dist.all_gather(parts, t.contiguous(), group=group)
+    return torch.cat(parts, dim=dim)
 
 
 def export_model_safetensors(am, out_dir: str, filename: str = "final.safetensors") -> str:

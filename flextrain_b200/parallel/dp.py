@@ -51,6 +51,8 @@ def build_segments(lb, p_base: int, g_base: int, no_decay_1d: bool = True) -> Li
     """Merge tensors that are adjacent in both buffers and share dtypes / decay into segments."""
     segs: List[Segment] = []
     for t in lb.spec.trainable():
+        if t.is_local_part:
+            continue            # owned by this rank alone (expert / tensor parallel part): no reduction, local update
         po, pn, _, pdt = lb.p_layout[t.name]
         go, gn, _, gdt = lb.g_layout[t.grad_name]
         decay = not (no_decay_1d and len(t.shape) == 1)
@@ -79,8 +81,13 @@ class _Base:
     def after_weights_loaded(self, am) -> None:
         """Make every rank start from rank 0's weights."""
         import torch.distributed as dist
-        for _, _, _, t in am.named_master_params():
-            dist.broadcast(t, src=0, group=self.pg)
+        for scope, l, name, t in am.named_master_params():
+            if not am.spec_of(scope, l, name).is_local_part:
+                dist.broadcast(t, src=0, group=self.pg)
+
+    @staticmethod
+    def local_part_names(spec) -> List[str]:
+        return [t.name for t in spec.trainable() if t.is_local_part]
 
     def on_layer_grads_ready(self, layer: int) -> None: ...
     def on_embed_head_grads_ready(self) -> None: ...
@@ -89,19 +96,21 @@ class _Base:
 class CollectiveDataParallel(_Base):
     """Baseline: library all-reduce of every unit's gradient buffer + replicated optimizer."""
 
-    def _allreduce(self, buf: torch.Tensor, layout) -> None:
+    def _allreduce(self, buf: torch.Tensor, lb) -> None:
         import torch.distributed as dist
-        for name, (off, nb, shape, dt) in layout.items():
-            dist.all_reduce(buf[off:off + nb].view(dt), group=self.pg)
+        skip = {t.grad_name for t in lb.spec.trainable() if t.is_local_part}
+        for name, (off, nb, shape, dt) in lb.g_layout.items():
+            if name not in skip:
+                dist.all_reduce(buf[off:off + nb].view(dt), group=self.pg)
 
     def on_layer_grads_ready(self, layer: int) -> None:
         bm = self.am.buffers
-        self._allreduce(bm.grad_buffer(layer), bm.layers[layer].g_layout)
+        self._allreduce(bm.grad_buffer(layer), bm.layers[layer])
 
     def on_embed_head_grads_ready(self) -> None:
         bm = self.am.buffers
-        self._allreduce(bm.embed_g, bm.embed.g_layout)
-        self._allreduce(bm.head_g, bm.head.g_layout)
+        self._allreduce(bm.embed_g, bm.embed)
+        self._allreduce(bm.head_g, bm.head)
 
     def step(self, am) -> int:
         return am._step_local()
@@ -141,6 +150,16 @@ class P2PDataParallel(_Base):
         n = max(off, 8)
         f32 = lambda: torch.zeros(n, dtype=torch.float32, device=self.device)
         self.grad_shard, self.m, self.v = f32(), f32(), f32()
+        # tensors owned by this rank alone keep an ordinary local optimizer with fp32 state
+        self.local_names: Dict[object, List[str]] = {}
+        self.local_state: Dict[object, Dict[str, torch.Tensor]] = {}
+        for key in keys:
+            names = self.local_part_names(lbs[key].spec)
+            if names:
+                self.local_names[key] = names
+                self.local_state[key] = {
+                    s.key: torch.zeros(s.shape, dtype=torch.float32, device=self.device)
+                    for s in am.optimizer.state_specs(lbs[key].spec) if s.param in names}
         self.slot = {k: i for i, k in enumerate(keys)}
         self.barrier_slot = len(keys)
         self.comm_stream = am.streams.comm
@@ -213,6 +232,12 @@ class P2PDataParallel(_Base):
                 if rc != 0:
                     raise RuntimeError(f"ftb_comm_adamw_push failed ({rc})")
                 ops._count()
+        if self.local_names:
+            cs.wait_stream(am.streams.compute)
+            with torch.cuda.stream(cs):
+                for key, names in self.local_names.items():
+                    opt.step(bm.layers[key].spec, bm.params(key), bm.grads(key), self.local_state[key], step,
+                             only=set(names))
         # every peer's stores into my parameters have landed, and every peer is done reading my gradients
         self.group.signal_wait(self.barrier_slot, self.group.next_epoch(), cs)
         am.streams.compute.wait_stream(cs)
