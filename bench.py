@@ -144,16 +144,17 @@ def run_ours(args):
     if args.small:                          # debugging only; never used for a reported number
         dims.update(n_layers=4)
         gbatch = 65536 if "global_batch" in cfg else gbatch
-    per_rank = gbatch // world
+    par = {k: (world if cfg.get(k) == "world" else 1) for k in ("tp", "ep")}
+    # tensor parallel ranks work on the same tokens (each feeds the whole batch); data parallel ranks split it
+    per_rank = gbatch if par["tp"] > 1 else gbatch // world
     free, total = torch.cuda.mem_get_info()
     opt = ft.AdamW(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, state_dtype=torch.float32)
-    par = {k: (world if cfg.get(k) == "world" else 1) for k in ("tp", "ep")}
     am = ft.from_dims(dims, arch=cfg["arch"], optimizer=opt, max_seq_len=seq_len, max_global_batch_tokens=gbatch,
                       max_gpu_mem_bytes=int(free), max_host_mem_bytes=args.host_gib << 30, device=dev,
                       hyperparams=cfg["hyper"], world_size=world, rank=rank,
                       dp_shard=args.shard, init_on_device=True, init_std=0.02, verbose=(rank == 0 and args.verbose),
                       max_chunk_size=args.chunk, head_chunk_size=args.head_chunk, **par)
-    src = ft.SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234 + rank, pin=True)
+    src = ft.SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234 + (0 if par["tp"] > 1 else rank), pin=True)
 
     def one_step(seqs):
         st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / gbatch, total_tokens_per_step=gbatch)

@@ -57,7 +57,10 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
                         process_group, model_dir=None, arch_key=None, host_backend=None,
                         plan_only: bool = False) -> ActiveModel:
     builder = _BLOCK_BUILDERS.get(arch_key) if arch_key else None
-    embed, layers, head = build_model_parts(mc, dt, lora, head_chunk_size, builder)
+    if (tp > 1 and tp != world_size) or (ep > 1 and ep != world_size) or (tp > 1 and ep > 1):
+        raise NotImplementedError("tensor / expert parallel groups span the whole job: use tp == world_size or "
+                                  "ep == world_size (not both)")
+    embed, layers, head = build_model_parts(mc, dt, lora, head_chunk_size, builder, tp=tp, tp_rank=rank % max(tp, 1))
     if ep > 1:
         # expert parallelism: every rank owns num_experts / ep experts of each MoE layer
         for layer in layers:
@@ -71,6 +74,7 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
             max_global_batch_tokens=max_global_batch_tokens, max_gpu_mem_bytes=max_gpu_mem_bytes,
             max_host_mem_bytes=max_host_mem_bytes, leeway_gpu_mem_bytes=leeway_gpu_mem_bytes,
             leeway_host_mem_bytes=leeway_host_mem_bytes, hw=hw, world_size=world_size, tp=tp, ep=ep, shard=dp_shard,
+            layers_are_local=True,
             min_chunk_size=min_chunk_size, max_chunk_size=max_chunk_size,
             force_saved_act_level=force_saved_act_level, verbose=verbose)
     if plan_only:

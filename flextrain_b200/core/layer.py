@@ -75,6 +75,14 @@ class TensorSpec:
         self.shape = tuple(g[:dim]) + (n,) + tuple(g[dim + 1:])
         return self
 
+    def mark_local(self, dim: int, index: int, count: int) -> "TensorSpec":
+        """Like :meth:`localize` for a spec that was already built with its LOCAL shape (tensor parallelism builds
+        the blocks with ``heads / tp`` and ``ffn / tp``): records the global shape and this rank's slice."""
+        n = self.shape[dim]
+        self.global_shape = tuple(self.shape[:dim]) + (n * count,) + tuple(self.shape[dim + 1:])
+        self.local_slice = (dim, index * n, (index + 1) * n)
+        return self
+
     @property
     def is_local_part(self) -> bool:
         return self.local_slice is not None

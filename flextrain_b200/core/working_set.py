@@ -137,7 +137,7 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
                                  hw: Optional[HardwareCost] = None, world_size: int = 1, tp: int = 1, ep: int = 1,
                                  shard: Optional[str] = None, min_chunk_size: Optional[int] = None,
                                  max_chunk_size: Optional[int] = None, force_saved_act_level: Optional[int] = None,
-                                 verbose: bool = False) -> WorkingSetConfig:
+                                 verbose: bool = False, layers_are_local: bool = False) -> WorkingSetConfig:
     hw = hw or HardwareCost()
     log: List[str] = []
 
@@ -159,6 +159,9 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
     # 2. model memory
     mm = baseline_model_memory(layers, embed, head, optimizer)
     L = mm.n_layers
+    tp_group = tp
+    if layers_are_local:
+        tp = 1          # the layers already describe one rank's part: sizes and FLOPs below are per rank as they are
     P, G, O = sum(mm.layer_param) // tp, sum(mm.layer_grad) // tp, sum(mm.layer_opt) // tp
     say(f"model: {L} layers, params {P / GiB:.2f} GiB, grads {G / GiB:.2f} GiB, opt {O / GiB:.2f} GiB per TP rank, "
         f"embed+head resident {mm.embed_head_resident / GiB:.2f} GiB")
@@ -264,7 +267,7 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
                     max_total_round_tokens=max(round_tokens, max_seq_len), target_num_rounds=n_rounds,
                     n_gpu_layers=n_p, n_gpu_grads=n_g, n_gpu_opt_layers=n_o, n_gpu_act_slots=n_slots,
                     gpu_act_buffer_size=int(room), host_act_buffer_size=host_act, max_seq_len=max_seq_len,
-                    max_global_batch_tokens=max_global_batch_tokens, world_size=world_size, shard=mode, tp=tp, ep=ep,
+                    max_global_batch_tokens=max_global_batch_tokens, world_size=world_size, shard=mode, tp=tp_group, ep=ep,
                     est_step_ms=est, est_compute_ms=comp, est_pcie_ms=pcie_ms, est_nvlink_ms=nv_ms,
                     healthy=(n_slots >= 2))
                 say(f"[{mode}/{resid}] chunk {chunk} round {round_tokens} x{n_rounds} slots "

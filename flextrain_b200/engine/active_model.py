@@ -15,6 +15,8 @@ What differs from the reference, by design for an 8×B200 NVSwitch box:
 """
 from __future__ import annotations
 
+import dataclasses
+
 import contextlib
 import time
 from dataclasses import dataclass, field
@@ -73,6 +75,9 @@ class ActiveModel:
         self.force_level = force_saved_act_level
         self.verbose = verbose
         self.dp, self.tp, self.ep = dp, tp, ep
+        for layer in self.layers:
+            if tp is not None:
+                layer.bind_tp(tp)
         self.step_num = 0
         self._zero_grad = True
         self._pending_tokens = 0
@@ -138,8 +143,9 @@ class ActiveModel:
                         self._forward_pass(metas, plan, transitions, slots, ctx_base, stats)
                     with _nvtx("Head"):
                         for c, meta in enumerate(metas):
-                            ls = self.head.forward_backward(transitions[c], meta, self.buffers.head_params(),
-                                                            self.buffers.head_grads(), loss_fn, loss_scale_factor)
+                            ls = self.head.forward_backward(transitions[c], self._token_shard(meta),
+                                                            self.buffers.head_params(), self.buffers.head_grads(),
+                                                            loss_fn, loss_scale_factor)
                             loss_acc += ls.total_loss
                             act_acc += ls.active_tokens
                             pending_losses.append((rseqs, meta, ls.per_token_loss))
@@ -147,8 +153,8 @@ class ActiveModel:
                         self._backward_pass(metas, plan, transitions, slots, ctx_base, stats, last_round)
                     with _nvtx("Embed Backward"):
                         for c, meta in enumerate(metas):
-                            self.embed.backward(transitions[c], meta, self.buffers.embed_params(),
-                                                self.buffers.embed_grads())
+                            self.embed.backward(transitions[c], self._token_shard(meta),
+                                                self.buffers.embed_params(), self.buffers.embed_grads())
                     self.events.clear_per_round()
         if self.dp is not None:
             self.dp.on_embed_head_grads_ready()
@@ -207,8 +213,31 @@ class ActiveModel:
         transitions = {}
         ep = self.buffers.embed_params()
         for c, meta in enumerate(metas):
-            transitions[c] = self.embed.forward(meta, ep)
+            transitions[c] = self.embed.forward(self._token_shard(meta), ep)
         return transitions, {}
+
+    def _token_shard(self, meta: ChunkMeta) -> ChunkMeta:
+        """Under tensor parallelism the residual stream is token-sharded: the embedding, the head and the loss see
+        rows ``[rank * T/tp, (rank+1) * T/tp)`` of the chunk; the layers keep the full chunk's packing metadata."""
+        tp = self.tp
+        if tp is None:
+            return meta
+        key = ("_shard", tp.rank)
+        cached = meta.extra.get(key)
+        if cached is not None:
+            return cached
+        T, W = meta.num_tokens, tp.world
+        if T % (W * 128):
+            raise ValueError(f"tensor parallelism needs chunk token counts that are multiples of {W * 128}; got {T} "
+                             f"(use sequence lengths / chunk sizes that are multiples of it)")
+        a, b = tp.rank * (T // W), (tp.rank + 1) * (T // W)
+        cut = lambda t: None if t is None else t[a:b]
+        extra = {k: (v[a:b] if k in ("advantages", "ref_logprobs") and v is not None else v)
+                 for k, v in meta.extra.items() if not (isinstance(k, tuple) and k[0] == "_shard")}
+        sh = dataclasses.replace(meta, tokens=cut(meta.tokens), targets=cut(meta.targets),
+                                 loss_mask=cut(meta.loss_mask), extra=extra)
+        meta.extra[key] = sh
+        return sh
 
     def _ctx(self, base, **kw) -> LayerContext:
         return LayerContext(**base, **kw)
@@ -470,6 +499,8 @@ class ActiveModel:
     def _write_back_losses(self, pending) -> None:
         """Per-token losses back into each ``Sequence`` (flextrain/engine/active_model.py:1306-1312)."""
         for rseqs, meta, per_tok in pending:
+            if self.tp is not None:
+                per_tok = self.tp.all_gather(per_tok)          # each rank computed the losses of its token shard
             host = per_tok.detach().to("cpu")
             off = 0
             for i, start, n in meta.extra["pieces"]:

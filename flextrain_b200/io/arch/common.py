@@ -115,6 +115,22 @@ def resolve_lora(lora_targets, rank: int, alpha: float, compute, master, grad, o
                       opt_state_dtype=opt or torch.bfloat16)
 
 
+TP_COL_TENSORS = ("w_q", "w_k", "w_v", "b_q", "b_k", "b_v", "w_1", "w_3")     # split along dim 0 (output features)
+TP_ROW_TENSORS = ("w_o", "w_2")                                              # split along dim 1 (input features)
+
+
+def localize_for_tp(mc: ModelConfig, tp: int) -> ModelConfig:
+    """The per-rank model of a ``tp``-way tensor-parallel layout: heads and FFN width divided by ``tp``."""
+    if tp <= 1:
+        return mc
+    if mc.n_heads % tp or mc.n_kv_heads % tp or mc.ffn_dim % tp:
+        raise ValueError(f"tensor parallel degree {tp} must divide n_heads {mc.n_heads}, n_kv_heads {mc.n_kv_heads} "
+                         f"and ffn_dim {mc.ffn_dim}")
+    if mc.num_experts > 0 or mc.gdn is not None or mc.qk_norm == "row" or mc.post_norms:
+        raise NotImplementedError("tensor parallelism covers dense pre-norm attention + gated-FFN models")
+    return replace(mc, n_heads=mc.n_heads // tp, n_kv_heads=mc.n_kv_heads // tp, ffn_dim=mc.ffn_dim // tp)
+
+
 def build_decoder_config(mc: ModelConfig, i: int, dt: DTypePolicy, lora: Optional[LoRAConfig]) -> DecoderConfig:
     lt = mc.layer_type(i)
     attn = gdn = None
@@ -141,9 +157,10 @@ def build_decoder_config(mc: ModelConfig, i: int, dt: DTypePolicy, lora: Optiona
 
 
 def build_model_parts(mc: ModelConfig, dt: DTypePolicy, lora: Optional[LoRAConfig], head_chunk_size: int = 4096,
-                      block_builder=None):
+                      block_builder=None, tp: int = 1, tp_rank: int = 0):
     """Returns ``(embed, layers, head)``; under LoRA the embedding and head are frozen
-    (flextrain/api.py:568-582)."""
+    (flextrain/api.py:568-582).  With ``tp > 1`` the layers are this rank's part of a tensor-parallel model."""
+    mc = localize_for_tp(mc, tp)
     frozen = lora is not None
     embed = TokenEmbedLayer(mc.vocab_size, mc.d_model, dtype=dt.compute, grad_dtype=dt.grad, master_dtype=dt.master,
                             scale=mc.embed_scale, frozen=frozen)
@@ -153,7 +170,16 @@ def build_model_parts(mc: ModelConfig, dt: DTypePolicy, lora: Optional[LoRAConfi
     layers = []
     for i in range(mc.n_layers):
         cfg = build_decoder_config(mc, i, dt, lora)
-        layers.append(block_builder(i, cfg, mc) if block_builder is not None else DecoderLayer(cfg, i))
+        if tp > 1:
+            cfg.seq_parallel = tp
+        layer = block_builder(i, cfg, mc) if block_builder is not None else DecoderLayer(cfg, i)
+        if tp > 1:
+            for t in layer.param_spec.tensors:
+                if t.name in TP_COL_TENSORS:
+                    t.mark_local(0, tp_rank, tp)
+                elif t.name in TP_ROW_TENSORS:
+                    t.mark_local(1, tp_rank, tp)
+        layers.append(layer)
     return embed, layers, head
 
 

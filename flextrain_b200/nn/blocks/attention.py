@@ -60,6 +60,7 @@ class GQAAttentionBlock:
         bias = ["b_q", "b_k", "b_v"] if cfg.qkv_bias else []
         self.qkv = LinearGroup(["w_q", "w_k", "w_v"], lora, bias)
         self.o = LinearGroup(["w_o"], lora)
+        self.qkv.tp_mode, self.o.tp_mode = "col", "row"      # used only when a tensor-parallel handle is bound
         self.inv_freq_cache: Dict[str, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ declarations
@@ -106,8 +107,8 @@ class GQAAttentionBlock:
     def _project_qkv(self, h, params):
         """QKV projection (one GEMM) -> pre-norm, pre-RoPE ``(q, gate, k, v)`` views of one buffer."""
         c = self.cfg
-        T = h.shape[0]
         qkv = self.qkv.fwd(h, params)
+        T = qkv.shape[0]                 # all tokens of the chunk (h holds T/tp of them under tensor parallelism)
         if c.gated:
             # w_q rows are per-head [query(hd) ‖ gate(hd)] (HF Qwen3-Next layout)
             qg = qkv[:, : 2 * c.q_dim].reshape(T, c.n_heads, 2 * c.head_dim)
@@ -212,16 +213,16 @@ class GQAAttentionBlock:
         it calls ``self.qkv.wgrad(dqkv, h, ...)`` once the norm backward has re-emitted ``h``.
         """
         c = self.cfg
-        T = dxo.shape[0]
         t = slot._t
         attn_raw = t["attn_result"]
+        T = attn_raw.shape[0]
         if c.gated:
             sg = torch.sigmoid(t["xgate"].to(torch.float32))
             attn_in = (attn_raw.to(torch.float32) * sg).to(attn_raw.dtype)
         else:
             attn_in = attn_raw
-        self.o.wgrad(dxo, attn_in, params, grads)
         dattn = self.o.dgrad(dxo, params)                                        # (T, q_dim)
+        self.o.wgrad(dxo, attn_in, params, grads)
         dgate = None
         if c.gated:
             df = dattn.to(torch.float32)

@@ -31,6 +31,7 @@ class GatedFFN:
         self.dtype = dtype
         self.up = LinearGroup(["w_1", "w_3"], lora)
         self.down = LinearGroup(["w_2"], lora)
+        self.up.tp_mode, self.down.tp_mode = "col", "row"    # used only when a tensor-parallel handle is bound
 
     def tensor_specs(self):
         c, dt = self.cfg, self.dtype

@@ -9,6 +9,11 @@
   and the rank-r gradients come from the captured ``(x, dy)``:
   ``gA += s * (dy @ B).T @ x``,  ``gB += s * dy.T @ (x @ A.T)``
   (flextrain/nn/layers/lora_wrapper.py:106-148, 429, 602, 840).
+* **Tensor parallelism** (no counterpart in the reference).  With a bound ``tp`` handle the activations between
+  blocks are token-sharded ``(T/tp, d)``.  A ``"col"`` group holds ``out/tp`` rows of each weight: forward is the
+  fused all-gather→GEMM, dgrad the fused GEMM→reduce-scatter, wgrad gathers its input.  A ``"row"`` group holds
+  ``in/tp`` columns: forward is GEMM→reduce-scatter (+ local residual), dgrad all-gather→GEMM; the gathered ``dy``
+  is kept for the weight gradient.
 """
 from __future__ import annotations
 
@@ -63,6 +68,9 @@ class LinearGroup:
         self.bias_names = list(bias_names)
         self.lora = lora
         self.lora_names = [n for n in self.names if lora is not None and n in lora.targets]
+        self.tp = None                 # TensorParallel handle, bound by the layer when tensor parallelism is on
+        self.tp_mode: Optional[str] = None      # "col" | "row"
+        self._dy_full = None           # (data_ptr of the local dy, gathered dy) kept between dgrad and wgrad
 
     # -- effective weight ---------------------------------------------------------
     def weight(self, params: Dict[str, torch.Tensor]) -> torch.Tensor:
@@ -96,13 +104,62 @@ class LinearGroup:
 
     # -- passes -------------------------------------------------------------------
     def fwd(self, x, params, *, residual=None, out=None):
+        if self.tp is not None:
+            return self._tp_fwd(x, params, residual, out)
         return ops.linear_fwd(x, self.weight(params), bias=self.bias(params), residual=residual, out=out)
 
     def dgrad(self, dy, params, *, out=None, accumulate=False):
+        if self.tp is not None:
+            return self._tp_dgrad(dy, params, out, accumulate)
         return ops.linear_dgrad(dy, self.weight(params), out=out, accumulate=accumulate)
+
+    # -- tensor-parallel passes -----------------------------------------------------
+    def _tp_fwd(self, x, params, residual, out):
+        w = self.weight(params)
+        if self.tp_mode == "col":
+            y = self.tp.ag_gemm(x, w)                                   # (T, out/tp) from (T/tp, in)
+            b = self.bias(params)
+            if b is not None:
+                y += b.to(y.dtype)
+            if residual is not None:
+                y += residual
+        else:
+            y = self.tp.gemm_rs(x, w, residual_local=residual)          # (T/tp, out) from (T, in/tp)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def _tp_dgrad(self, dy, params, out, accumulate):
+        w = self.weight(params)
+        if self.tp_mode == "col":
+            dx = self.tp.gemm_rs(dy, w, trans_w=False)                  # (T/tp, in)
+        else:
+            dx = self.tp.ag_gemm(dy, w, trans_w=False)                  # (T, in/tp); dy gathered on the way
+            self._dy_full = (dy.data_ptr(), self.tp.last_gathered)
+        if out is not None:
+            if accumulate:
+                out += dx
+            else:
+                out.copy_(dx)
+            return out
+        return dx
+
+    def _tp_wgrad_operands(self, dy, x):
+        """Full-token operands of the weight gradient: gather whichever side is token-sharded."""
+        if self.tp_mode == "col":
+            return dy, self.tp.all_gather(x)
+        if self._dy_full is not None and self._dy_full[0] == dy.data_ptr():
+            dyf = self._dy_full[1]
+        else:
+            dyf = self.tp.all_gather(dy)
+        self._dy_full = None
+        return dyf, x
 
     def wgrad(self, dy, x, params, grads, *, alpha: float = 1.0) -> None:
         """Accumulate weight (and bias / LoRA) gradients of every member from ``(x, dy)``."""
+        if self.tp is not None:
+            dy, x = self._tp_wgrad_operands(dy, x)
         gnames = ["g_" + n[2:] for n in self.names]
         trainable = [g in grads for g in gnames]
         if all(trainable) and not self.lora_names:

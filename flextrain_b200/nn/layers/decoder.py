@@ -47,6 +47,7 @@ class DecoderConfig:
     master_dtype: Optional[torch.dtype] = None
     lora: Optional[LoRAConfig] = None
     family: str = "llama"
+    seq_parallel: int = 1            # tensor-parallel degree: the residual stream and norm statistics hold T / seq_parallel tokens
 
 
 class DecoderLayer:
@@ -102,11 +103,12 @@ class DecoderLayer:
     def _build_schema(self) -> ActivationSchema:
         c, d, dt = self.cfg, self.cfg.d_model, self.cfg.dtype
         f32 = torch.float32
-        fields = [ActivationField("x_inp", lambda t: (t, d), dt, 0),
-                  ActivationField("attn_norm_rstd", lambda t: (t,), f32, 0),
-                  ActivationField("ffn_norm_rstd", lambda t: (t,), f32, 0)]
+        sp = max(1, c.seq_parallel)
+        fields = [ActivationField("x_inp", lambda t: (t // sp, d), dt, 0),
+                  ActivationField("attn_norm_rstd", lambda t: (t // sp,), f32, 0),
+                  ActivationField("ffn_norm_rstd", lambda t: (t // sp,), f32, 0)]
         fields += (self.attn or self.gdn).activation_fields()
-        fields.append(ActivationField("xo", lambda t: (t, d), dt, 2))
+        fields.append(ActivationField("xo", lambda t: (t // sp, d), dt, 2))
         fields += (self.ffn or self.moe).activation_fields()
         if c.post_norms:
             fields += [ActivationField("post_attn_rstd", lambda t: (t,), f32, 0),
@@ -240,6 +242,15 @@ class DecoderLayer:
 
     def end_of_step(self, params) -> None:
         clear_effective_weights(params)
+
+    def bind_tp(self, tp) -> None:
+        """Route the projections through the tensor-parallel handle (fused all-gather→GEMM / GEMM→reduce-scatter)."""
+        if tp is None:
+            return
+        if self.attn is None or self.ffn is None or self.cfg.post_norms or self.cfg.lora is not None:
+            raise NotImplementedError("tensor parallelism covers dense attention + gated-FFN layers without LoRA")
+        for g in (self.attn.qkv, self.attn.o, self.ffn.up, self.ffn.down):
+            g.tp = tp
 
     # ------------------------------------------------------------------------ cost
     def compute_cost(self, num_tokens: int, avg_ctx: float) -> ComputeCost:

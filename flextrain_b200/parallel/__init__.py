@@ -24,7 +24,9 @@ def build_parallel(*, world_size: int, rank: int, shard: str, tp: int, ep: int, 
     if ep > 1:
         from .ep import ExpertParallel
         ep_group = ExpertParallel(rank % ep, ep, dev, process_group, backend=backend)
-    if dp_size > 1:
+    if dp_size > 1 or tp > 1:
+        # under tensor parallelism the ranks still hold replicated tensors (embedding, head, norm weights) whose
+        # gradients come from different token shards: the data-parallel machinery reduces and updates exactly those
         from .dp import CollectiveDataParallel, P2PDataParallel
         if backend == "p2p":
             dp = P2PDataParallel(rank, world_size, dev, process_group)

@@ -64,6 +64,7 @@ class TensorParallel:
             import torch.distributed as dist
             full = torch.empty(W * Tl, K, dtype=x_local.dtype, device=x_local.device)
             dist.all_gather_into_tensor(full, x_local.contiguous(), group=self.pg)
+            self.last_gathered = full
             return ops.gemm(full, w_local, trans_b=trans_w)
         assert Tl % 128 == 0 and x_local.dtype == torch.bfloat16
         bufs = self._ag_stage(W * Tl, K)
@@ -128,6 +129,33 @@ class TensorParallel:
             raise RuntimeError(f"ftb_comm_reduce_slots failed ({rc})")
         ops._count()
         return out
+
+    def all_gather(self, x_local: torch.Tensor) -> torch.Tensor:
+        """Token all-gather ``(T/tp, ...) -> (T, ...)`` (rank-major) for the operands of weight gradients and for
+        per-token results.  Peer path: each rank stores its part into every peer's staging buffer."""
+        W = self.world
+        x_local = x_local.contiguous()
+        if self.backend != "p2p":
+            import torch.distributed as dist
+            full = torch.empty((W * x_local.shape[0],) + tuple(x_local.shape[1:]), dtype=x_local.dtype,
+                               device=x_local.device)
+            dist.all_gather_into_tensor(full, x_local, group=self.pg)
+            return full
+        nb = x_local.numel() * x_local.element_size()
+        assert nb % 16 == 0, "token all-gather moves 16-byte units"
+        bufs = self._ag_stage(W * nb // 2, 1)              # staging is sized in bf16 elements
+        buf = bufs[self._calls % 2]
+        stage = buf.local[: W * nb]
+        stage[self.rank * nb:(self.rank + 1) * nb].copy_(x_local.view(-1).view(torch.uint8))
+        self._sync()                                     # previous readers of this staging buffer are done
+        from ..ops.cuda import _stream
+        rc = self.group.lib.ftb_comm_allgather_push(buf.c_ptrs, c_long(self.rank * nb), c_long(nb), c_int(W),
+                                                    c_int(self.rank), _stream())
+        if rc != 0:
+            raise RuntimeError(f"ftb_comm_allgather_push failed ({rc})")
+        ops._count()
+        self._sync()                                     # every rank's part has landed here
+        return stage.view(x_local.dtype).view((W * x_local.shape[0],) + tuple(x_local.shape[1:]))
 
     def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
         """Small replicated-gradient reduction (norm weights under sequence parallelism); library call."""

@@ -1,0 +1,96 @@
+"""Worker for the engine-level expert- and tensor-parallel tests (run under ``torch.distributed.run``).
+
+``ep``: every rank builds the same small Qwen3-MoE model with ``ep = world`` (experts sharded over the ranks, the rest
+data parallel) and trains on its share of the batch.  ``tp``: a small Llama with ``tp = world`` (heads and FFN width
+sharded, token-sharded residual stream); every rank feeds the whole batch.  After a few steps the parameters are
+gathered back through the HF exporter; rank 0 also trains the unsharded model on the whole batch in the same process
+and reports the differences.
+"""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import flextrain_b200 as ft  # noqa: E402
+from flextrain_b200.io.hf_weights import collect_hf_state  # noqa: E402
+
+MOE_DIMS = dict(vocab_size=512, n_layers=2, d_model=128, n_heads=4, n_kv_heads=2, head_dim=32, expert_dim=64,
+                ffn_dim=64, num_routed_experts=8, num_shared_experts=0, top_k=2, is_causal=True)
+DENSE_DIMS = dict(vocab_size=512, n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, expert_dim=512,
+                  ffn_dim=512, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+GB, SEQ, STEPS = 1024, 128, 2
+
+
+def build(dev, dtype, world, rank, mode, backend):
+    from flextrain_b200.engine.host_memory import UnpinnedHostBackend
+    os.environ["FTB_DP_BACKEND"] = backend
+    per_rank = GB if mode == "tp" else GB // world
+    ws = ft.WorkingSetConfig.simple(max_seq_len=SEQ, max_global_batch_tokens=per_rank, chunk=512,
+                                    round_tokens=per_rank, world_size=world,
+                                    shard="opt+grad" if world > 1 else "none")
+    par = {"ep": world} if mode == "ep" else {"tp": world}
+    return ft.from_dims(MOE_DIMS if mode == "ep" else DENSE_DIMS, arch="qwen3_moe" if mode == "ep" else "llama",
+                        optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32),
+                        max_seq_len=SEQ, max_global_batch_tokens=GB, max_gpu_mem_bytes=8 << 30,
+                        max_host_mem_bytes=8 << 30, device=dev, compute_dtype=dtype, master_dtype=dtype,
+                        grad_dtype=dtype, working_set=ws, world_size=world, rank=rank,
+                        host_backend=UnpinnedHostBackend() if dev == "cpu" else None, **(par if world > 1 else {}))
+
+
+def train(am, rank, world, dev, mode):
+    src = ft.SyntheticTokenSource(512, SEQ, seed=5)
+    losses = []
+    for _ in range(STEPS):
+        seqs = src.get_sequences(GB)
+        if mode == "ep":
+            seqs = seqs[rank::world]                  # data parallel: each rank takes its share of the batch
+        st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / GB, total_tokens_per_step=GB)
+        assert am.step() == 0
+        t = torch.tensor([st.loss_sum], device=dev, dtype=torch.float64 if dev == "cpu" else torch.float32)
+        if world > 1:
+            dist.all_reduce(t)
+        losses.append(float(t) / GB)
+    return losses
+
+
+def main():
+    backend, mode, out_path = sys.argv[1], sys.argv[2], sys.argv[3]
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    if backend == "p2p":
+        torch.cuda.set_device(local)
+        dev, dtype = f"cuda:{local}", torch.bfloat16
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    else:
+        dev, dtype = "cpu", torch.float32
+        dist.init_process_group("gloo")
+    am = build(dev, dtype, world, rank, mode, backend)
+    local_rows = am.buffers.params(0)["w_up" if mode == "ep" else "w_1"].shape[0]
+    losses = train(am, rank, world, dev, mode)
+    if am.ep is not None:
+        am.ep.check()
+    state = collect_hf_state(am)                  # collective: gathers the expert shards
+    res = None
+    if rank == 0:
+        full = build(dev, dtype, 1, 0, mode, backend)
+        ref_losses = train(full, 0, 1, dev, mode)
+        ref_state = collect_hf_state(full)
+        worst = 0.0
+        for k, v in ref_state.items():
+            d = float((state[k].float() - v.float()).abs().max())
+            worst = max(worst, d)
+        res = {"local_rows": int(local_rows), "loss_diff": max(abs(a - b) for a, b in zip(losses, ref_losses)),
+               "param_diff": worst, "losses": losses, "keys": len(ref_state)}
+        if backend == "p2p":
+            from flextrain_b200.ops import cuda as k
+            res["errors"] = k.device_error_words()
+        with open(out_path, "w") as f:
+            json.dump(res, f)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

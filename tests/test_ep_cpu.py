@@ -27,9 +27,9 @@ def test_engine_expert_parallel_matches_unsharded(tmp_path):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     out = str(tmp_path / "epe.json")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "ep_engine_worker.py"), "collective", out]
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective", "ep", out]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     res = json.load(open(out))
-    assert res["local_experts"] == 4
+    assert res["local_rows"] == 4
     assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res

@@ -34,10 +34,10 @@ def test_engine_expert_parallel_p2p(tmp_path):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     out = str(tmp_path / "epe.json")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "ep_engine_worker.py"), "p2p", out]
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "p2p", "ep", out]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     res = json.load(open(out))
     assert all(v == 0 for v in res.pop("errors").values())
-    assert res["local_experts"] == 4
+    assert res["local_rows"] == 4
     assert res["loss_diff"] < 2e-2 and res["param_diff"] < 2e-2, res

@@ -26,3 +26,20 @@ def test_fused_tp_gemms_match_nccl(tmp_path):
     for k, v in res.items():
         if k.startswith(("ag_", "rs_")):
             assert v < 1e-2, (k, v)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_engine_tensor_parallel_p2p(tmp_path):
+    """A small Llama trained with 2-way tensor parallelism through the fused all-gather→GEMM / GEMM→reduce-scatter
+    kernels against the unsharded model on one GPU."""
+    import json
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "tpe.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "p2p", "tp", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert all(v == 0 for v in res.pop("errors").values())
+    assert res["local_rows"] == 256
+    assert res["loss_diff"] < 2e-2 and res["param_diff"] < 2e-2, res
