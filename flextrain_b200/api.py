@@ -67,6 +67,10 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
             for t in layer.param_spec.tensors:
                 if t.shard.ep_dim is not None:
                     t.localize(t.shard.ep_dim, rank % ep, ep)
+            if getattr(layer, "moe", None) is not None:
+                from .parallel.ep import DEFAULT_CAPACITY_FACTOR
+                layer.moe.ep_world, layer.moe.ep_capacity_factor = ep, DEFAULT_CAPACITY_FACTOR
+                layer.activation_schema = layer._build_schema()
     hw = _hw_cost(hw_cost, device)
     if ws is None:
         ws = determine_working_set_config(

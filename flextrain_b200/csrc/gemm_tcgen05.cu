@@ -63,6 +63,9 @@ struct SmemLayout {
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
 };
 
+// Reduce-scatter epilogue staging: 4 epilogue warps x (32 rows x 128 bf16 columns).
+constexpr int RS_STAGE_BYTES = 4 * 32 * 256;
+
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int per_group = GROUP_M * tiles_n;
   const int g = tile / per_group;
@@ -345,6 +348,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool row_ok = r_in < rows;
       const size_t row = static_cast<size_t>(row0 + r_in - d_row_shift);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      if constexpr (COMM == 2) {
+        // Peer stores: a lane-per-row store puts 16 B per row on the wire per instruction.  Stage 32 rows x 128
+        // columns per warp in shared memory (16-byte chunks XOR-swizzled by row) and write whole 256-byte row
+        // segments, 16 lanes per row, so every NVLink write request carries a full segment.
+        if (!p.d_fp32) {
+          uint8_t* stg = smem + L::BAR_OFFSET + 256 + quad * (RS_STAGE_BYTES / 4);
+          __nv_bfloat16* dmat = reinterpret_cast<__nv_bfloat16*>(d_base);
+#pragma unroll 1
+          for (int half = 0; half < BN; half += 128) {
+            const int col_h = tn * BN + half;
+            if (col_h >= p.N) break;
+#pragma unroll 1
+            for (int c = half; c < half + 128; c += 32) {
+              if (tn * BN + c >= p.N) break;
+              uint32_t r[32];
+              tmem_ld_32x32(taddr + c, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  o2[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]) * p.alpha,
+                                                __uint_as_float(r[8 * j + 2 * e + 1]) * p.alpha);
+                const int chunk = ((c - half) >> 3) + j;
+                *reinterpret_cast<uint4*>(stg + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
+              }
+            }
+            __syncwarp();
+            const int chunks_valid = min(128, p.N - col_h) >> 3;
+            const int ch = lane & 15;
+#pragma unroll 4
+            for (int i = 0; i < 16; ++i) {
+              const int rr = 2 * i + (lane >> 4);
+              if (quad * 32 + rr < rows && ch < chunks_valid) {
+                const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((ch ^ (rr & 15)) << 4));
+                const size_t orow = static_cast<size_t>(row0 + quad * 32 + rr - d_row_shift);
+                *reinterpret_cast<uint4*>(dmat + orow * p.ldd + col_h + ch * 8) = v;
+              }
+            }
+            __syncwarp();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         const int col = tn * BN + c;
@@ -454,13 +507,14 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, int GROUPED, int COMM = 0>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, GROUPED, COMM>;
+  constexpr int SMEM = L::TOTAL + (COMM == 2 ? RS_STAGE_BYTES : 0);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return -300 - static_cast<int>(e);
     configured = true;
   }
-  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, p);
+  kern<<<grid, NUM_THREADS, SMEM, stream>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
 }

@@ -70,8 +70,15 @@ class MoEFFN:
                 specs.append(TensorSpec("w_shared_gate", (1, c.d_model), dt, optimizer="adamw"))
         return specs
 
+    ep_world = 1                   # set by the API under expert parallelism (with the receive capacity factor)
+    ep_capacity_factor = 1.0
+
     def rows_bound(self, T: int) -> int:
         c = self.cfg
+        if self.ep_world > 1:
+            # rows this rank may RECEIVE for its experts from all ranks' chunks of T tokens
+            from ...parallel.ep import ep_capacity
+            return ep_capacity(T, c.top_k, c.num_experts, self.ep_world, self.ep_capacity_factor)
         return ref.moe_rows_bound(T, c.top_k, c.num_experts, ROW_PAD)
 
     def activation_fields(self):

@@ -316,12 +316,16 @@ def moe_combine(y, inv, weights, resid):
     return out.to(y.dtype)
 
 
-def grouped_gemm(x, w, offsets, *, trans_w=True):
+def grouped_gemm(x, w, offsets, *, trans_w=True, out=None):
     if _cuda_bf16(x, w) and _GEMM_BACKEND == "tcgen05" and x.shape[1] % 8 == 0 and w.is_contiguous() \
             and (w.shape[1] if trans_w else w.shape[2]) % 8 == 0 and x.shape[1] >= 64:
         _count()
-        return _kernels().grouped_gemm(x.contiguous(), w, offsets.to(torch.int32), trans_w=trans_w)
-    return ref.grouped_gemm(x, w, offsets, trans_w=trans_w)
+        return _kernels().grouped_gemm(x.contiguous(), w, offsets.to(torch.int32), trans_w=trans_w, out=out)
+    y = ref.grouped_gemm(x, w, offsets, trans_w=trans_w)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
 
 
 def grouped_wgrad(dy, x, offsets, gw, *, alpha=1.0, pad: int = 1):

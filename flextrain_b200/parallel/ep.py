@@ -18,6 +18,7 @@ The reference project has no expert parallelism; its single-GPU MoE path is flex
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_long, c_void_p
 from dataclasses import dataclass
 from typing import Optional
@@ -27,6 +28,14 @@ import torch
 from .. import ops
 
 PAD = 128
+DEFAULT_CAPACITY_FACTOR = float(os.environ.get("FTB_EP_CAPACITY", "1.5"))
+
+
+def ep_capacity(T: int, K: int, E: int, world: int, factor: float) -> int:
+    """Rows of one rank's expert-major receive buffer for chunks of ``T`` tokens per rank: ``factor`` times the
+    balanced share ``T*K`` plus tile padding per local expert.  Exceeding it is reported, never written past."""
+    rows = int(factor * T * K) + (E // world) * (PAD - 1)
+    return (rows + PAD - 1) // PAD * PAD
 
 
 @dataclass
@@ -43,7 +52,7 @@ class EPPlan:
 
 class ExpertParallel:
     def __init__(self, rank: int, world: int, device, process_group=None, backend: str = "p2p", group=None,
-                 capacity_factor: float = 2.0):
+                 capacity_factor: float = DEFAULT_CAPACITY_FACTOR):
         self.rank, self.world, self.device, self.pg, self.backend = rank, world, torch.device(device), process_group, backend
         self.capacity_factor = capacity_factor
         self.group = group
@@ -60,8 +69,7 @@ class ExpertParallel:
 
     # ------------------------------------------------------------------ helpers
     def capacity(self, T: int, K: int, E: int) -> int:
-        rows = int(self.capacity_factor * T * K) + (E // self.world) * (PAD - 1)
-        return (rows + PAD - 1) // PAD * PAD
+        return ep_capacity(T, K, E, self.world, self.capacity_factor)
 
     def _sync(self) -> None:
         if self.backend == "p2p":
@@ -237,8 +245,10 @@ class ExpertParallel:
         cap = self.capacity(T, c.top_k, c.num_experts)
         plan = self.plan(idx, w, c.num_experts)
         xs, _ = self.dispatch(h, plan, cap, "recv_a")
-        up = ops.grouped_gemm(xs, params["w_up"], plan.offsets)
-        slot._t["x_up"] = up
+        sized = moe.ep_world == self.world and moe.ep_capacity_factor == self.capacity_factor
+        up = ops.grouped_gemm(xs, params["w_up"], plan.offsets, out=slot.out("x_up", h.device) if sized else None)
+        if not sized:                      # block used outside the engine: the slot was not sized for this group
+            slot._t["x_up"] = up
         slot._t["_ep_plan"] = plan
         act = ops.glu_fwd(up[:, F:], up[:, :F], c.kind)
         y = ops.grouped_gemm(act, params["w_down"], plan.offsets)
