@@ -43,6 +43,29 @@ def load(name: str) -> ctypes.CDLL:
     return lib
 
 
+_fast = None
+
+
+def fastcall():
+    """The CPython fast-call module for GEMM launches (``csrc/fastcall.cpp``), bound to the kernel library; ``None``
+    if it was not built.  ``FTB_FASTCALL=0`` keeps the ctypes path."""
+    global _fast
+    if _fast is None:
+        _fast = False
+        if os.environ.get("FTB_FASTCALL", "1") != "0":
+            import importlib.util
+            import sysconfig
+            path = lib_path("x").parent / f"_ftb_fastcall{sysconfig.get_config_var('EXT_SUFFIX')}"
+            if path.exists():
+                load("gemm_tcgen05")
+                spec = importlib.util.spec_from_file_location("_ftb_fastcall", str(path))
+                mod = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(mod)
+                mod.bind(str(lib_path("gemm_tcgen05")))
+                _fast = mod
+    return _fast or None
+
+
 def have(name: str) -> bool:
     return lib_path(name).exists()
 
@@ -109,6 +132,15 @@ def gemm(a, b, *, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, bia
         assert c.dtype == out.dtype and c.stride(1) == 1
     if bias is not None:
         assert bias.dtype == torch.float32
+    fast = fastcall()
+    if fast is not None:
+        rc = fast.gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), None if c is None else c.data_ptr(),
+                       None if bias is None else bias.data_ptr(), M, N, K, 1 if trans_a else 0, 0 if trans_b else 1,
+                       a.stride(0), b.stride(0), out.stride(0), c.stride(0) if c is not None else 0, float(alpha),
+                       float(beta), 1 if out.dtype == torch.float32 else 0, bn, GEMM_MAX_CTAS,
+                       torch.cuda.current_stream().cuda_stream)
+        _check(rc, "ftb_gemm_bf16")
+        return out
     rc = lib.ftb_gemm_bf16(_ptr(a), _ptr(b), _ptr(out), _ptr(c), _ptr(bias), c_int(M), c_int(N), c_int(K),
                            c_int(1 if trans_a else 0), c_int(0 if trans_b else 1), c_int(a.stride(0)),
                            c_int(b.stride(0)), c_int(out.stride(0)), c_int(c.stride(0) if c is not None else 0),

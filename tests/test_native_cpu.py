@@ -112,3 +112,23 @@ def test_planner_decisions_for_the_headline_model():
     assert small.n_gpu_opt_layers is not None
     with pytest.raises(ValueError):
         ft.determine_working_set_config(max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=16 << 30, **kw)
+
+
+def test_fastcall_module_binds_and_calls():
+    """The CPython fast-call GEMM entry: argument checking, binding to the kernel library, and a call that the
+    library answers without touching a device (an empty problem returns 0 at once)."""
+    import pytest
+    from flextrain_b200.build import build_all, lib_path
+    from flextrain_b200.ops import cuda as k
+    build_all()
+    k._fast = None
+    mod = k.fastcall()
+    assert mod is not None, "fastcall extension was not built"
+    with pytest.raises(TypeError):
+        mod.gemm(1, 2, 3)
+    n0 = mod.calls()
+    rc = mod.gemm(0, 0, 0, None, None, 0, 0, 64, 0, 0, 64, 64, 64, 0, 1.0, 0.0, 0, 0, 0, 0)
+    assert rc == 0 and mod.calls() == n0 + 1
+    with pytest.raises(OSError):
+        mod.bind("/nonexistent/libnothing.so")
+    mod.bind(str(lib_path("gemm_tcgen05")))
