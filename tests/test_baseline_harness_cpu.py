@@ -1,0 +1,68 @@
+"""Comparison harness: spec merging / templating, command construction for every backend, step-throughput
+extraction, and a dry-run sweep (no GPU, nothing is launched)."""
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from baseline.baseline_harness.backends import BACKENDS, format_command, get_backend  # noqa: E402
+from baseline.baseline_harness.spec import RunSpec, load_sweep, spec_from_sections, substitute  # noqa: E402
+from baseline.scripts.sweep import extract_step_throughput, main as sweep_main  # noqa: E402
+
+
+def test_template_substitution_and_merge():
+    assert substitute("${NUM_GPUS}", {"NUM_GPUS": 8}) == 8
+    assert substitute("dp${NUM_GPUS}x", {"NUM_GPUS": 4}) == "dp4x"
+    assert substitute({"a": ["${NUM_GPUS}", 2]}, {"NUM_GPUS": 2}) == {"a": [2, 2]}
+    spec = spec_from_sections("flextrain_b200", {"seq_length": 2048, "num_steps": 3, "num_gpus": "${NUM_GPUS}"},
+                              {"dp_shard": "opt+grad", "micro_batch_size": 4}, {"num_steps": 1}, num_gpus=8)
+    assert (spec.seq_length, spec.num_steps, spec.num_gpus, spec.micro_batch_size) == (2048, 1, 8, 4)
+    assert spec.extra == {"dp_shard": "opt+grad"} and spec.tokens_per_step == 2048 * 4 * 8
+    with pytest.raises(ValueError):
+        RunSpec(backend="x", num_steps=0).validate()
+
+
+def test_every_backend_builds_a_command(tmp_path):
+    for name, b in BACKENDS.items():
+        spec = RunSpec(backend=name, model_path=str(tmp_path), num_gpus=2, seq_length=512, micro_batch_size=2,
+                       gradient_accumulation_steps=4, extra={"zero_stage": 3, "dp_shard": "opt+grad"})
+        cmd, env = b.command(spec)
+        line = format_command(cmd, env)
+        assert "torch.distributed.run" in line and "--nproc-per-node=2" in line and "127.0.0.1" in line, name
+        assert ROOT in env["PYTHONPATH"]
+    cmd, env = get_backend("nccl_library").command(RunSpec(backend="nccl_library"))
+    assert env["FTB_DP_BACKEND"] == "collective" and env["FTB_GEMM_BACKEND"] == "library"
+    assert cmd[1].endswith("train.py") and "dims:llama3_1_8B" in cmd
+    with pytest.raises(KeyError):
+        get_backend("nope")
+    ok, why = get_backend("megatron").available()
+    assert ok or "not installed" in why
+
+
+def test_extract_step_throughput_formats():
+    log = "\n".join([
+        "[step    2] lr 3.000e-05 loss 11.7612 ema 11.80 tok/step 524288 tok/s 21,950 TFLOPS_eff 1005.1",
+        "warmup 0: loss 12.1  900.0 ms  100.0 tok/s",
+        "step 1: loss 11.9021  812.0 ms  20177.3 tok/s  max_alloc 71.2 GiB",
+        '{"metric": "train tokens/sec/box", "value": 22050.5, "loss": 12.5}',
+        "unrelated line",
+    ])
+    rows = extract_step_throughput(log)
+    assert [r["step"] for r in rows] == [2, 1, -1]
+    assert rows[0]["tok_s"] == 21950.0 and rows[1]["tok_s"] == 20177.3 and rows[2]["tok_s"] == 22050.5
+
+
+def test_dry_run_sweep_of_the_shipped_configs(capsys):
+    for cfg in ("llama3_8b_b200.toml", "llama3_128k_maxmem.toml"):
+        path = os.path.join(ROOT, "baseline", "configs", cfg)
+        data = load_sweep(path)
+        assert "common" in data and len(data) >= 4
+        common = dict(data["common"])
+        if "model_path" in common:              # the model directory is not on this machine
+            continue
+        assert sweep_main([path, "--dry-run", "--num-gpus", "8", "--num-steps", "1"]) == 0
+        out = capsys.readouterr().out
+        assert "train.py" in out and "hf_fsdp2.py" in out and "--nproc-per-node=8" in out
