@@ -20,7 +20,7 @@ LIB = PKG / "_lib"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 CUDA_HOME = Path(NVCC).resolve().parent.parent
 
-CUDA_SOURCES = ["gemm_tcgen05", "elementwise", "attention", "comm", "moe", "noalloc"]
+CUDA_SOURCES = ["gemm_tcgen05", "elementwise", "attention", "comm", "moe", "noalloc", "gdn", "seqmix"]
 CPP_SOURCES = ["dp_solver", "copy_engine"]
 PYEXT_SOURCES = ["fastcall"]
 

@@ -202,7 +202,9 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
                 nv += 2 * P * f                           # fwd + bwd gathers
         nv_ms = hw.bytes_to_ms(nv, "nvlink")
         # ---- residency search: all resident, else offload opt → grads → params (least-touched first)
-        for resid in ("all", "opt_host", "opt_grad_host", "all_host"):
+        # Host residency of model states is the single-GPU mechanism; with more than one rank the states are sharded /
+        # partitioned over the ranks instead and stay in HBM (only activations may still go to the host).
+        for resid in (("all", "opt_host", "opt_grad_host", "all_host") if world_size == 1 else ("all",)):
             n_p = n_g = n_o = None
             host_state = 0.0
             pcie = 0.0
@@ -232,7 +234,10 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
                 # rounds that fit entirely on the device at full tier
                 r_dev = int(room // max(full_tok, 1))
                 rounds_pcie = 0.0
-                if r_dev >= min(batch_per_rank, max(chunk, tokens_compute_bound if resid == "all_host" else chunk)):
+                # a sequence is never split across rounds: a round holds at least one whole (longest) sequence
+                seq_floor = min(batch_per_rank, math.ceil(max_seq_len / chunk) * chunk)
+                if r_dev >= max(seq_floor, min(batch_per_rank, max(chunk, tokens_compute_bound if resid == "all_host"
+                                                                  else chunk))):
                     round_tokens = _round_down_to_multiple(min(r_dev, batch_per_rank), chunk, batch_per_rank)
                     n_slots = 1 << 30
                     host_act = 0
@@ -242,7 +247,7 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
                     host_room = host_budget - host_state
                     r_host = int(host_room // max(tier0_tok, 1))
                     round_tokens = _round_down_to_multiple(min(batch_per_rank, max(r_host, 0)), chunk, batch_per_rank)
-                    if round_tokens < chunk:
+                    if round_tokens < max(chunk, seq_floor):
                         continue
                     n_slots = int(room // max(full_tok * chunk / max(L, 1), 1))
                     if n_slots < 2:

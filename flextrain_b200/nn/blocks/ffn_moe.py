@@ -76,9 +76,10 @@ class MoEFFN:
     def rows_bound(self, T: int) -> int:
         c = self.cfg
         if self.ep_world > 1:
-            # rows this rank may RECEIVE for its experts from all ranks' chunks of T tokens
-            from ...parallel.ep import ep_capacity
-            return ep_capacity(T, c.top_k, c.num_experts, self.ep_world, self.ep_capacity_factor)
+            # rows this rank is PLANNED to receive for its experts from all ranks' chunks of T tokens (the saved
+            # x_up is sized by what actually arrives; the receive buffers by the worst case)
+            from ...parallel.ep import PLANNING_FACTOR, ep_capacity
+            return ep_capacity(T, c.top_k, c.num_experts, self.ep_world, PLANNING_FACTOR)
         return ref.moe_rows_bound(T, c.top_k, c.num_experts, ROW_PAD)
 
     def activation_fields(self):

@@ -9,12 +9,21 @@ Cross-chunk state: the recurrent state ``(HV, dk, dv)`` fp32 and the conv tail `
 the end of a chunk are tier-0 fields; the engine threads them (and their gradients, in reverse)
 between the chunks of one sequence through ``LayerContext``.
 
-Backward re-runs the block's forward under autograd on the saved input (an activation-
-recompute backward): the only tensors kept per chunk are the boundary states, which is the
-reference's tier-0 footprint (``lin_final_state``, ``lin_conv_state``).
+The only tensors kept per chunk are the boundary states, which is the reference's tier-0 footprint
+(``lin_final_state``, ``lin_conv_state``); backward recomputes the block from its input.
+
+Two implementations of the same math:
+
+* **CUDA (bf16)**: hand-written forward and backward, no autograd: tcgen05 GEMMs for the projections, the conv1d /
+  L2-norm / gated-RMSNorm kernels of ``csrc/seqmix.cu`` and the recurrent delta-rule kernels of ``csrc/gdn.cu``
+  (forward pass; backward = one reverse pass for the state adjoint + one forward-direction pass for the
+  state-dependent terms; the gate gradient is a suffix sum of per-token scalars).
+* **Reference (any device / dtype)**: the fp32 PyTorch formulation under autograd; it is the CPU path and the oracle
+  the CUDA path is tested against.  ``FTB_GDN_BACKEND=reference`` forces it.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -103,8 +112,101 @@ class GatedDeltaNetBlock:
             out = out + x_resid.to(f32)
         return out, fin, conv_fin
 
+    # ------------------------------------------------------------------- CUDA path
+    def _use_cuda(self, h) -> bool:
+        from ...ops import linattn_cuda as la
+        c = self.cfg
+        return (h.is_cuda and h.dtype == torch.bfloat16 and os.environ.get("FTB_GDN_BACKEND", "cuda") != "reference"
+                and la.gdn_supported(c.head_k_dim, c.head_v_dim) and c.conv_width <= 8)
+
+    def _cuda_forward(self, h, meta: ChunkMeta, p, state_in, conv_in, want_r: bool):
+        """Everything up to the gated norm; returns the intermediates the backward needs."""
+        from ...ops import linattn_cuda as la
+        c = self.cfg
+        T = h.shape[0]
+        f32 = torch.float32
+        cu = meta.cu_seqlens_q
+        qkvz = ops.gemm(h, p["w_lin_qkvz"], trans_b=True)
+        ba = ops.gemm(h, p["w_lin_ba"], trans_b=True).to(f32)
+        qkv, z2d = qkvz[:, : c.conv_dim], qkvz[:, c.conv_dim:]
+        qkv_c, conv_fin = la.conv1d_fwd(qkv, p["w_lin_conv"], cu, conv_in, activation=True)
+        qn, q_rn = la.l2norm_heads_fwd(qkv_c[:, : c.key_dim], c.n_k_heads, c.head_k_dim)
+        kn, k_rn = la.l2norm_heads_fwd(qkv_c[:, c.key_dim: 2 * c.key_dim], c.n_k_heads, c.head_k_dim)
+        v = qkv_c[:, 2 * c.key_dim:].contiguous().view(T, c.n_v_heads, c.head_v_dim)
+        a_pre = ba[:, c.n_v_heads:] + p["w_lin_dt_bias"].to(f32)
+        beta = torch.sigmoid(ba[:, : c.n_v_heads]).contiguous()
+        g = (-torch.exp(p["w_lin_A_log"].to(f32)) * F.softplus(a_pre)).contiguous()
+        o, fin, r = la.gdn_fwd(qn, kn, v, g, beta, cu, state_in, want_r=want_r)
+        z = z2d.contiguous().view(T * c.n_v_heads, c.head_v_dim)
+        on = ops.gated_rmsnorm_fwd(o.view(T * c.n_v_heads, c.head_v_dim), z, p["w_lin_norm"].to(f32), c.norm_eps)
+        return dict(qkvz=qkvz, qkv_c=qkv_c, conv_fin=conv_fin, qn=qn, kn=kn, q_rn=q_rn, k_rn=k_rn, v=v, a_pre=a_pre,
+                    beta=beta, g=g, o=o, fin=fin, r=r, on=on.view(T, c.value_dim))
+
+    def _fwd_cuda(self, h, x_resid, meta, params, slot, ctx):
+        s = self._cuda_forward(h, meta, params, ctx.lin_state_in, ctx.lin_conv_in, want_r=False)
+        out = ops.linear_fwd(s["on"], params["w_lin_out"], residual=x_resid)
+        if not ctx.lin_attn_recompute_only:
+            slot.put("lin_final_state", s["fin"][:1])
+            slot.put("lin_conv_state", s["conv_fin"][:1].to(self.dtype))
+            ctx.out["lin_state"], ctx.out["lin_conv"] = s["fin"], s["conv_fin"].to(self.dtype)
+        return out
+
+    def _bwd_cuda(self, dx, h, meta, params, grads, slot, ctx):
+        from ...ops import linattn_cuda as la
+        c = self.cfg
+        T = h.shape[0]
+        f32 = torch.float32
+        cu = meta.cu_seqlens_q
+        s = self._cuda_forward(h, meta, params, ctx.lin_state_in, ctx.lin_conv_in, want_r=True)
+        acc = lambda name, val: grads[name].add_(val.to(grads[name].dtype)) if name in grads else None
+        # ---- out-projection and gated norm
+        d_on = ops.linear_dgrad(dx, params["w_lin_out"])
+        if "g_lin_out" in grads:
+            ops.linear_wgrad(dx, s["on"], grads["g_lin_out"])
+        dqkvz = torch.empty_like(s["qkvz"])
+        dwn = torch.zeros(c.head_v_dim, dtype=f32, device=h.device)
+        d_o = la.gated_rmsnorm_bwd(d_on.view(T, c.n_v_heads, c.head_v_dim), s["o"], s["qkvz"][:, c.conv_dim:],
+                                   params["w_lin_norm"].to(f32), dqkvz[:, c.conv_dim:], dwn, c.n_v_heads,
+                                   c.head_v_dim, c.norm_eps)
+        acc("g_lin_norm", dwn)
+        # ---- recurrence
+        dq, dk, dv, dg, dbeta, dstate_in = la.gdn_bwd(s["qn"], s["kn"], s["v"], s["g"], s["beta"], cu, ctx.lin_state_in,
+                                                      s["fin"], s["r"], d_o, dstate_final=ctx.lin_dstate_in)
+        # ---- L2 norms and conv
+        dqkv_c = torch.empty(T, c.conv_dim, dtype=h.dtype, device=h.device)
+        la.l2norm_heads_bwd(dq.contiguous(), s["qkv_c"][:, : c.key_dim], s["q_rn"], dqkv_c[:, : c.key_dim],
+                            c.n_k_heads, c.head_k_dim)
+        la.l2norm_heads_bwd(dk.contiguous(), s["qkv_c"][:, c.key_dim: 2 * c.key_dim], s["k_rn"],
+                            dqkv_c[:, c.key_dim: 2 * c.key_dim], c.n_k_heads, c.head_k_dim)
+        dqkv_c[:, 2 * c.key_dim:].copy_(dv.view(T, c.value_dim))
+        dwc = torch.zeros(c.conv_dim, c.conv_width, dtype=f32, device=h.device)
+        dconv_in = la.conv1d_bwd(s["qkvz"][:, : c.conv_dim], params["w_lin_conv"], cu, ctx.lin_conv_in, dqkv_c,
+                                 ctx.lin_dconv_in, dqkvz[:, : c.conv_dim], dwc, want_dinit=ctx.lin_conv_in is not None)
+        acc("g_lin_conv", dwc)
+        # ---- gates:  beta = sigmoid(b);  g = -exp(A_log) * softplus(a + dt_bias)
+        beta, a_pre = s["beta"], s["a_pre"]
+        db = dbeta * beta * (1.0 - beta)
+        da = dg * (-torch.exp(params["w_lin_A_log"].to(f32))) * torch.sigmoid(a_pre)
+        acc("g_lin_A_log", (dg * s["g"]).sum(0))
+        acc("g_lin_dt_bias", da.sum(0))
+        dba = torch.cat([db, da], 1).to(h.dtype)
+        # ---- input projections
+        dh = ops.linear_dgrad(dqkvz, params["w_lin_qkvz"])
+        dh = ops.linear_dgrad(dba, params["w_lin_ba"], out=dh, accumulate=True)
+        if "g_lin_qkvz" in grads:
+            ops.linear_wgrad(dqkvz, h, grads["g_lin_qkvz"])
+        if "g_lin_ba" in grads:
+            ops.linear_wgrad(dba, h, grads["g_lin_ba"])
+        if ctx.lin_state_in is not None:
+            ctx.out["lin_dstate"] = dstate_in
+        if ctx.lin_conv_in is not None:
+            ctx.out["lin_dconv"] = dconv_in
+        return dh
+
     # --------------------------------------------------------------------- forward
     def fwd(self, h, x_resid, meta: ChunkMeta, params, slot, ctx: LayerContext):
+        if self._use_cuda(h):
+            return self._fwd_cuda(h, x_resid, meta, params, slot, ctx)
         with torch.no_grad():
             out, fin, conv_fin = self._core(h, x_resid, meta, params, ctx.lin_state_in, ctx.lin_conv_in)
         if not ctx.lin_attn_recompute_only:
@@ -119,6 +221,8 @@ class GatedDeltaNetBlock:
     # -------------------------------------------------------------------- backward
     def bwd(self, dx, h, meta: ChunkMeta, params, grads, slot, ctx: LayerContext):
         """Returns ``dh``; accumulates all parameter gradients; hands back state gradients via ``ctx.out``."""
+        if self._use_cuda(h):
+            return self._bwd_cuda(dx, h, meta, params, grads, slot, ctx)
         names = [n for n in self.PARAMS]
         leaf = {n: params[n].detach().to(torch.float32).requires_grad_("g_" + n[2:] in grads) for n in names}
         hh = h.detach().to(torch.float32).requires_grad_(True)

@@ -28,13 +28,19 @@ import torch
 from .. import ops
 
 PAD = 128
-DEFAULT_CAPACITY_FACTOR = float(os.environ.get("FTB_EP_CAPACITY", "1.5"))
+# Receive-buffer capacity as a multiple of the balanced share.  0 (default) = dropless: the buffers hold the worst
+# case (every slot of every rank routed to one rank), so no routing skew can overflow them.  Saved activations are
+# sized by the rows a rank actually receives, not by this bound.
+DEFAULT_CAPACITY_FACTOR = float(os.environ.get("FTB_EP_CAPACITY", "0"))
+PLANNING_FACTOR = 1.25          # what the planner assumes a rank receives, relative to the balanced share
 
 
 def ep_capacity(T: int, K: int, E: int, world: int, factor: float) -> int:
     """Rows of one rank's expert-major receive buffer for chunks of ``T`` tokens per rank: ``factor`` times the
     balanced share ``T*K`` plus tile padding per local expert.  Exceeding it is reported, never written past."""
-    rows = int(factor * T * K) + (E // world) * (PAD - 1)
+    if factor <= 0:
+        factor = float(world)
+    rows = int(min(factor, float(world)) * T * K) + (E // world) * (PAD - 1)
     return (rows + PAD - 1) // PAD * PAD
 
 
@@ -46,8 +52,9 @@ class EPPlan:
     dest_row: torch.Tensor       # (n,) int32
     slot_rank: torch.Tensor      # (T, K) int32
     slot_row: torch.Tensor       # (T, K) int32
-    offsets: torch.Tensor        # (E_local + 1,) int32 rows of my experts (padded segments)
+    offsets: torch.Tensor        # (E_local + 1,) int32 rows of my experts (padded segments), clamped to the capacity
     w_sorted: torch.Tensor       # (n,) fp32 router weight of each sorted slot
+    rows: int = 0                # padded rows this rank received (host value: one device read per plan)
 
 
 class ExpertParallel:
@@ -130,8 +137,11 @@ class ExpertParallel:
         cap = self.capacity(T, K, E)
         over = (dest_row >= cap).any()
         self.overflow = over if self.overflow is None else (self.overflow | over)
+        # rows past the capacity are never written (the push skips them); the expert GEMMs must not touch them either
+        offsets.clamp_(max=cap)
+        rows = int(offsets[-1])             # host read: sizes this layer's expert activations by what really arrived
         return EPPlan(order, (order // K).to(torch.int32), dest_rank, dest_row, slot_rank.view(T, K),
-                      slot_row.view(T, K), offsets, w.reshape(-1).to(torch.float32)[order].contiguous())
+                      slot_row.view(T, K), offsets, w.reshape(-1).to(torch.float32)[order].contiguous(), rows)
 
     # ------------------------------------------------------------- dispatch / combine
     def dispatch(self, x: torch.Tensor, plan: EPPlan, cap: int, name: str, with_scalar: bool = False):
@@ -189,6 +199,8 @@ class ExpertParallel:
         D = y.shape[1]
         if self.backend != "p2p":
             import torch.distributed as dist
+            if y.shape[0] < cap:            # ranks receive different row counts; the library gather wants equal shapes
+                y = torch.cat([y, y.new_zeros(cap - y.shape[0], D)])
             ys = [torch.empty_like(y) for _ in range(self.world)]
             dist.all_gather(ys, y.contiguous(), group=self.pg)
             Y = torch.stack(ys)                                           # (W, cap, D)
@@ -202,7 +214,7 @@ class ExpertParallel:
         buf = self._buf(name, cap * D * 2)
         ysym = buf.local.view(torch.bfloat16)[: cap * D].view(cap, D)
         if ysym.data_ptr() != y.data_ptr():
-            ysym.copy_(y)
+            ysym[: y.shape[0]].copy_(y)
         self._sync()                       # all owners' outputs are complete
         out = torch.empty(T, D, dtype=torch.bfloat16, device=y.device)
         from ..ops.cuda import _stream
@@ -222,12 +234,14 @@ class ExpertParallel:
         T, K = plan.slot_rank.shape
         if self.backend != "p2p":
             import torch.distributed as dist
+            if v.shape[0] < cap:
+                v = torch.cat([v, v.new_zeros(cap - v.shape[0])])
             vs = [torch.empty_like(v) for _ in range(self.world)]
             dist.all_gather(vs, v.contiguous(), group=self.pg)
             return torch.stack(vs)[plan.slot_rank.long(), plan.slot_row.long()]
         buf = self._buf(name, cap * 4)
         vsym = buf.local.view(torch.float32)[:cap]
-        vsym.copy_(v)
+        vsym[: v.shape[0]].copy_(v)
         self._sync()
         out = torch.empty(T, K, dtype=torch.float32, device=v.device)
         from ..ops.cuda import _stream
@@ -245,10 +259,9 @@ class ExpertParallel:
         cap = self.capacity(T, c.top_k, c.num_experts)
         plan = self.plan(idx, w, c.num_experts)
         xs, _ = self.dispatch(h, plan, cap, "recv_a")
-        sized = moe.ep_world == self.world and moe.ep_capacity_factor == self.capacity_factor
-        up = ops.grouped_gemm(xs, params["w_up"], plan.offsets, out=slot.out("x_up", h.device) if sized else None)
-        if not sized:                      # block used outside the engine: the slot was not sized for this group
-            slot._t["x_up"] = up
+        R = max(plan.rows, PAD)
+        up = ops.grouped_gemm(xs[:R], params["w_up"], plan.offsets)
+        slot._t["x_up"] = up               # sized by the rows that arrived, not by the receive capacity
         slot._t["_ep_plan"] = plan
         act = ops.glu_fwd(up[:, F:], up[:, :F], c.kind)
         y = ops.grouped_gemm(act, params["w_down"], plan.offsets)
@@ -259,8 +272,10 @@ class ExpertParallel:
         F, T, K = c.expert_dim, h.shape[0], c.top_k
         cap = self.capacity(T, K, c.num_experts)
         plan = slot._t.get("_ep_plan") or self.plan(idx, w, c.num_experts)
+        R = max(plan.rows, PAD)
         xs, _ = self.dispatch(h, plan, cap, "recv_a")
         dy_u, wrow = self.dispatch(dx, plan, cap, "recv_b", with_scalar=True)
+        xs, dy_u, wrow = xs[:R], dy_u[:R], wrow[:R]
         up = slot._t.get("x_up")
         if up is None:
             up = ops.grouped_gemm(xs, params["w_up"], plan.offsets)
