@@ -1,6 +1,7 @@
 """Small, self-terminating kernel cases for profiling one kernel at a time.
 
-    python -m flextrain_b200.bench.kernel_cases gemm_fwd|gemm_dgrad|gemm_wgrad|rmsnorm_bwd|softmax_ce|attn_fwd|attn_bwd
+    python -m flextrain_b200.bench.kernel_cases gemm_fwd|gemm_dgrad|gemm_wgrad|rmsnorm_bwd|softmax_ce|attn_fwd|attn_bwd|
+                                                  gdn_fwd|gdn_bwd|gdn_long_fwd
 
 Each case holds a few hundred MB on the device (inputs larger than the 126 MB L2), runs one warm-up launch and
 three timed launches with CUDA events, and prints achieved TFLOP/s or GB/s.  They are the commands behind the
@@ -52,6 +53,29 @@ def main(case: str) -> None:
         tgt = torch.randint(0, V, (T,), device=dev)
         ms = _time(lambda: k.softmax_ce_(z, tgt, grad_scale=1e-3))
         print(f"{case}: T={T} V={V}  {ms:.3f} ms  {3.0 * T * V * 2 / ms / 1e6:.0f} GB/s (2 reads + 1 write)")
+    elif case in ("gdn_fwd", "gdn_bwd", "gdn_long_fwd"):
+        import torch.nn.functional as F
+        from flextrain_b200.ops import linattn_cuda as la
+        # Qwen3.5-9B linear-attention shape: 16 key heads, 32 value heads, 128 x 128 state per head
+        HK, HV, dk, dv = 16, 32, 128, 128
+        S, L = (1, 16384) if case == "gdn_long_fwd" else (16, 1024)
+        T = S * L
+        q = F.normalize(torch.randn(T, HK, dk, device=dev), dim=-1).to(bf)
+        kk = F.normalize(torch.randn(T, HK, dk, device=dev), dim=-1).to(bf)
+        v = (torch.randn(T, HV, dv, device=dev) * 0.5).to(bf)
+        g = (-torch.rand(T, HV, device=dev) * 0.3).contiguous()
+        beta = (torch.rand(T, HV, device=dev) * 0.9 + 0.05).contiguous()
+        cu = torch.arange(0, T + 1, L, device=dev, dtype=torch.int32)
+        fl = 2.0 * T * HV * dk * dv * 3          # decay+predict, update, read-out: 3 multiply-adds per state element
+        if case != "gdn_bwd":
+            ms = _time(lambda: la.gdn_fwd(q, kk, v, g, beta, cu, None, want_r=True))
+            print(f"{case}: {S} x {L} tokens, HV={HV} dk={dk} dv={dv}  {ms:.3f} ms  {fl / ms / 1e9:.1f} TFLOP/s fp32 "
+                  f"(state recurrence on CUDA cores)")
+        else:
+            o, fin, r = la.gdn_fwd(q, kk, v, g, beta, cu, None, want_r=True)
+            d_o = torch.randn_like(o)
+            ms = _time(lambda: la.gdn_bwd(q, kk, v, g, beta, cu, None, fin, r, d_o))
+            print(f"{case}: {S} x {L} tokens, HV={HV} dk={dk} dv={dv}  {ms:.3f} ms  {2.2 * fl / ms / 1e9:.1f} TFLOP/s fp32")
     elif case in ("attn_fwd", "attn_bwd"):
         S, B, H, KV, hd = 1024, 16, 32, 8, 128
         T = S * B

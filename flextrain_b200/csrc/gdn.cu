@@ -17,8 +17,8 @@
 //     dk_t = dS' e  +  S^ dr;         dq_t = scale S_t dO_t;          dS_{t-1} = exp(g_t) (dS' + k_t dr^T)
 //     dg_t = sum_{u >= t} ( q_u.dq_u - k_u.(dS'_u e_u) + k_u.(S^_u dr_u) )  (+ <dS_final, S_final>)
 // The terms that need the state itself (dq, S^ dr) are produced by re-running the forward recurrence ("pass F") with
-// de from the reverse pass ("pass R"); the dg suffix sums are formed by the caller from dq / dk, which are written per
-// value head in fp32.
+// de from the reverse pass ("pass R").  Both passes add their part of the per-token scalar q.dq - k.(dS' e) + k.(S^ dr)
+// into `sacc`; the caller turns it into dg with a suffix sum per sequence.  dq / dk are written per value head in fp32.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -46,6 +46,7 @@ struct GdnArgs {
   float* dbeta;        // (T, HV)            pass R (atomic over column blocks)
   float* dq;           // (T, HV, DK) fp32   pass F (atomic over column blocks)
   float* dk;           // (T, HV, DK) fp32   pass R adds dS' e, pass F adds S^ dr (atomic)
+  float* sacc;         // (T, HV) fp32       per-token scalar of the gate gradient: q.dq - k.(dS' e) + k.(S^ dr)
   int HK, HV, DV;
   float scale;
 };
@@ -56,6 +57,13 @@ __device__ __forceinline__ float half_warp_sum(float x) {   // over the 16 lanes
   x += __shfl_xor_sync(0xffffffffu, x, 2);
   x += __shfl_xor_sync(0xffffffffu, x, 1);
   return x;
+}
+
+// Sum over the lanes that hold one token's DK consecutive elements (DK lanes for DK = 16, the whole warp otherwise).
+template <int DK>
+__device__ __forceinline__ float segment_sum(float x) {
+  if (DK >= 32) x += __shfl_xor_sync(0xffffffffu, x, 16);
+  return half_warp_sum(x);
 }
 
 // MODE 0: forward (o, r, final state).  MODE 1: pass F of the backward (dq, dk += S^ dr).
@@ -155,12 +163,24 @@ __global__ void __launch_bounds__(NT) gdn_forward_kernel(const GdnArgs a) {
     }
     if (MODE == 1) {
       __syncthreads();
-      for (int idx = tid; idx < nt * DK; idx += NT) {
+      if (tid < TB) a_s[tid] = 0.f;           // reused as the per-token scalar accumulator of this block
+      __syncthreads();
+      for (int idx = tid; idx < TB * DK; idx += NT) {           // uniform trip count: the shuffles need full warps
         const int t = idx / DK, i = idx - t * DK;
-        const size_t off = ((size_t)(tb + t) * a.HV + hv) * DK + i;
-        atomicAdd(a.dq + off, acc_q[0][t][i] + acc_q[1][t][i] + acc_q[2][t][i] + acc_q[3][t][i]);
-        atomicAdd(a.dk + off, acc_k[0][t][i] + acc_k[1][t][i] + acc_k[2][t][i] + acc_k[3][t][i]);
+        float sc = 0.f;
+        if (t < nt) {
+          const size_t off = ((size_t)(tb + t) * a.HV + hv) * DK + i;
+          const float vq = acc_q[0][t][i] + acc_q[1][t][i] + acc_q[2][t][i] + acc_q[3][t][i];
+          const float vk = acc_k[0][t][i] + acc_k[1][t][i] + acc_k[2][t][i] + acc_k[3][t][i];
+          atomicAdd(a.dq + off, vq);
+          atomicAdd(a.dk + off, vk);
+          sc = q_s[t][i] * vq / a.scale + k_s[t][i] * vk;
+        }
+        sc = segment_sum<DK>(sc);
+        if ((idx & (DK < 32 ? DK - 1 : 31)) == 0 && t < nt) atomicAdd(&a_s[t], sc);
       }
+      __syncthreads();
+      if (tid < nt) atomicAdd(a.sacc + (size_t)(tb + tid) * a.HV + hv, a_s[tid]);
     }
   }
   if (MODE == 0 && a.state_out) {
@@ -257,13 +277,24 @@ __global__ void __launch_bounds__(NT) gdn_reverse_kernel(const GdnArgs a) {
       }
     }
     __syncthreads();
-    for (int idx = tid; idx < nt * DK; idx += NT) {
+    if (tid < TB) a_s[tid] = 0.f;             // reused as the per-token scalar accumulator of this block
+    __syncthreads();
+    for (int idx = tid; idx < TB * DK; idx += NT) {             // uniform trip count: the shuffles need full warps
       const int t = idx / DK, i = idx - t * DK;
-      atomicAdd(a.dk + ((size_t)(tb + t) * a.HV + hv) * DK + i,
-                acc_k[0][t][i] + acc_k[1][t][i] + acc_k[2][t][i] + acc_k[3][t][i]);
+      float sc = 0.f;
+      if (t < nt) {
+        const float vk = acc_k[0][t][i] + acc_k[1][t][i] + acc_k[2][t][i] + acc_k[3][t][i];
+        atomicAdd(a.dk + ((size_t)(tb + t) * a.HV + hv) * DK + i, vk);
+        sc = -k_s[t][i] * vk;
+      }
+      sc = segment_sum<DK>(sc);
+      if ((idx & (DK < 32 ? DK - 1 : 31)) == 0 && t < nt) atomicAdd(&a_s[t], sc);
     }
-    if (tid < nt)
+    __syncthreads();
+    if (tid < nt) {
       atomicAdd(a.dbeta + (size_t)(tb + tid) * a.HV + hv, acc_b[0][tid] + acc_b[1][tid] + acc_b[2][tid] + acc_b[3][tid]);
+      atomicAdd(a.sacc + (size_t)(tb + tid) * a.HV + hv, a_s[tid]);
+    }
   }
   if (a.state_out) {
 #pragma unroll
@@ -286,10 +317,14 @@ int launch_all(int pass, const GdnArgs& a, int nseq, cudaStream_t s) {
   return e == cudaSuccess ? 0 : -400 - (int)e;
 }
 
+// Column block per CTA: 32 columns when that already gives two CTAs per SM, otherwise 16 or 8 so that one long
+// sequence still spreads over the whole GPU (the recurrence is latency-bound per CTA).
 template <int RPT>
 int launch_cols(int pass, const GdnArgs& a, int nseq, cudaStream_t s) {
-  if (a.DV % 32 == 0) return launch_all<RPT, 4>(pass, a, nseq, s);
-  if (a.DV % 16 == 0) return launch_all<RPT, 2>(pass, a, nseq, s);
+  const long heads = (long)nseq * a.HV;
+  if (a.DV % 32 == 0 && heads * (a.DV / 32) >= 296) return launch_all<RPT, 4>(pass, a, nseq, s);
+  if (a.DV % 16 == 0 && heads * (a.DV / 16) >= 296) return launch_all<RPT, 2>(pass, a, nseq, s);
+  if (a.DV % 8 == 0) return launch_all<RPT, 1>(pass, a, nseq, s);
   return -2;
 }
 
@@ -297,16 +332,17 @@ int launch_cols(int pass, const GdnArgs& a, int nseq, cudaStream_t s) {
 
 extern "C" {
 
-// pass: 0 forward, 1 backward reverse pass, 2 backward forward-direction pass.  DK in {16, 32, 64, 128}, DV % 16 == 0.
+// pass: 0 forward, 1 backward reverse pass, 2 backward forward-direction pass.  DK in {16, 32, 64, 128}, DV % 8 == 0.
 int ftb_gdn(int pass, const void* q, const void* k, const void* v, const float* g, const float* beta, const int* cu,
             int nseq, const float* state_in, float* state_out, void* o, float* r, const void* d_o, float* de, void* dv,
-            float* dbeta, float* dq, float* dk, int HK, int HV, int DK, int DV, float scale, cudaStream_t s) {
+            float* dbeta, float* dq, float* dk, float* sacc, int HK, int HV, int DK, int DV, float scale,
+            cudaStream_t s) {
   if (nseq <= 0) return 0;
   if (HV % HK) return -2;
   GdnArgs a;
   a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.g = g; a.beta = beta; a.cu = cu;
   a.state_in = state_in; a.state_out = state_out; a.o = (bf16*)o; a.r = r; a.d_o = (const bf16*)d_o; a.de = de;
-  a.dv = (bf16*)dv; a.dbeta = dbeta; a.dq = dq; a.dk = dk; a.HK = HK; a.HV = HV; a.DV = DV; a.scale = scale;
+  a.dv = (bf16*)dv; a.dbeta = dbeta; a.dq = dq; a.dk = dk; a.sacc = sacc; a.HK = HK; a.HV = HV; a.DV = DV; a.scale = scale;
   switch (DK) {
     case 16: return launch_cols<1>(pass, a, nseq, s);
     case 32: return launch_cols<2>(pass, a, nseq, s);

@@ -100,16 +100,16 @@ def gated_rmsnorm_bwd(dy: torch.Tensor, o: torch.Tensor, z2d: torch.Tensor, w: t
 
 # ------------------------------------------------------------------------------------------ gated delta rule
 def gdn_supported(dk: int, dv: int) -> bool:
-    return dk in (16, 32, 64, 128) and dv % 16 == 0
+    return dk in (16, 32, 64, 128) and dv % 8 == 0
 
 
-def _gdn(pass_, q, k, v, g, beta, cu, state_in, state_out, o, r, d_o, de, dv, dbeta, dq, dk, scale):
+def _gdn(pass_, q, k, v, g, beta, cu, state_in, state_out, o, r, d_o, de, dv, dbeta, dq, dk, sacc, scale):
     lib = load("gdn")
     T, HK, DK = q.shape
     HV, DV = v.shape[1], v.shape[2]
     rc = lib.ftb_gdn(c_int(pass_), _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(cu), c_int(cu.numel() - 1),
                      _ptr(state_in), _ptr(state_out), _ptr(o), _ptr(r), _ptr(d_o), _ptr(de), _ptr(dv), _ptr(dbeta),
-                     _ptr(dq), _ptr(dk), c_int(HK), c_int(HV), c_int(DK), c_int(DV), c_float(scale), _stream())
+                     _ptr(dq), _ptr(dk), _ptr(sacc), c_int(HK), c_int(HV), c_int(DK), c_int(DV), c_float(scale), _stream())
     _check(rc, f"ftb_gdn(pass {pass_})")
 
 
@@ -124,7 +124,7 @@ def gdn_fwd(q, k, v, g, beta, cu, state_in=None, scale=None, want_r=False):
     fin = torch.empty(S, HV, DK, DV, dtype=F32, device=q.device)
     r = torch.empty(T, HV, DV, dtype=F32, device=q.device) if want_r else None
     sin = state_in.to(F32).contiguous() if state_in is not None else None
-    _gdn(0, q, k, v, g, beta, cu, sin, fin, o, r, None, None, None, None, None, None, scale)
+    _gdn(0, q, k, v, g, beta, cu, sin, fin, o, r, None, None, None, None, None, None, None, scale)
     return o, fin, r
 
 
@@ -140,19 +140,17 @@ def gdn_bwd(q, k, v, g, beta, cu, state_in, final_state, r, d_o, dstate_final=No
     de = torch.empty(T, HV, DV, dtype=F32, device=dev)
     dv = torch.empty(T, HV, DV, dtype=BF, device=dev)
     dbeta = torch.zeros(T, HV, dtype=F32, device=dev)
-    dk1 = torch.zeros(T, HV, DK, dtype=F32, device=dev)
+    dk_hv = torch.zeros(T, HV, DK, dtype=F32, device=dev)
+    s = torch.zeros(T, HV, dtype=F32, device=dev)
     dstate_in = torch.empty(S, HV, DK, DV, dtype=F32, device=dev)
     dsf = dstate_final.to(F32).contiguous() if dstate_final is not None else None
     d_o = d_o.contiguous()
-    _gdn(1, q, k, v, g, beta, cu, dsf, dstate_in, None, r, d_o, de, dv, dbeta, None, dk1, scale)
+    _gdn(1, q, k, v, g, beta, cu, dsf, dstate_in, None, r, d_o, de, dv, dbeta, None, dk_hv, s, scale)
     dq_hv = torch.zeros(T, HV, DK, dtype=F32, device=dev)
-    dk2 = torch.zeros(T, HV, DK, dtype=F32, device=dev)
     sin = state_in.to(F32).contiguous() if state_in is not None else None
-    _gdn(2, q, k, v, g, beta, cu, sin, None, None, None, d_o, de, None, None, dq_hv, dk2, scale)
-    # dg_t = sum_{u >= t, same sequence} ( q_u.dq_u - k_u.dk1_u + k_u.dk2_u )  (+ <dS_final, S_final>)
-    qf = q.to(F32).repeat_interleave(rep, 1) if rep > 1 else q.to(F32)
-    kf = k.to(F32).repeat_interleave(rep, 1) if rep > 1 else k.to(F32)
-    s = (qf * dq_hv).sum(-1) + (kf * (dk2 - dk1)).sum(-1)                 # (T, HV)
+    _gdn(2, q, k, v, g, beta, cu, sin, None, None, None, d_o, de, None, None, dq_hv, dk_hv, s, scale)
+    # dg_t = sum_{u >= t, same sequence} s_u  (+ <dS_final, S_final>), with the per-token scalar
+    # s_u = q_u.dq_u - k_u.(dS'_u e_u) + k_u.(S^_u dr_u) accumulated by the two passes
     csum = torch.flip(torch.cumsum(torch.flip(s, [0]), 0), [0])            # suffix sums over the whole chunk
     ends = cu[1:].long()                                                    # first token AFTER each sequence
     tail = torch.cat([csum, torch.zeros(1, HV, dtype=F32, device=dev)], 0)[ends]       # (S, HV) mass past the end
@@ -160,7 +158,6 @@ def gdn_bwd(q, k, v, g, beta, cu, state_in, final_state, r, d_o, dstate_final=No
         tail = tail - (dsf * final_state.to(F32)).sum((-1, -2))
     lens = (cu[1:] - cu[:-1]).long()
     dg = csum - torch.repeat_interleave(tail, lens, dim=0)
-    dk_hv = dk1 + dk2
     if rep > 1:
         dq = dq_hv.view(T, HK, rep, DK).sum(2)
         dk = dk_hv.view(T, HK, rep, DK).sum(2)

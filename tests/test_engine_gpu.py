@@ -63,3 +63,27 @@ def test_gradients_bf16_vs_autograd():
 def test_smoke_entry():
     import __graft_entry__ as ge
     ge.smoke()
+
+
+@pytest.mark.parametrize("seq_len,chunk", [(128, 256), (512, 128)])
+def test_hybrid_gated_deltanet_bf16_tracks_fp32(seq_len, chunk):
+    """Qwen3.5-style hybrid (linear-attention + full-attention layers) through the hand-written Gated DeltaNet CUDA
+    kernels, single-chunk and with the recurrent / conv state carried across the chunks of one sequence."""
+    dims = dict(vocab_size=1024, n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, expert_dim=512,
+                ffn_dim=512, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+    hyper = {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 4, "head_k_dim": 64, "head_v_dim": 64}}
+    kw = dict(arch="qwen3_5", dims=dims, hyper=hyper, max_seq_len=seq_len, batch_tokens=512,
+              ws=ft.WorkingSetConfig.simple(max_seq_len=seq_len, max_global_batch_tokens=512, chunk=chunk,
+                                            round_tokens=512))
+    cpu = build_tiny(**kw)
+    gpu = build_tiny(device="cuda:0", dtype=torch.bfloat16, optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32),
+                     **kw)
+    _copy_weights(cpu, gpu)
+    src = ft.SyntheticTokenSource(1024, seq_len, seed=9)
+    for step in range(3):
+        seqs = src.get_sequences(512)
+        a = cpu.fwd_bwd(seqs); cpu.step()
+        b = gpu.fwd_bwd(seqs); gpu.step()
+        assert abs(a.loss - b.loss) < 0.04, (step, a.loss, b.loss)
+    from flextrain_b200.ops import cuda as k
+    assert "gdn" in k._libs and "seqmix" in k._libs, "Gated DeltaNet CUDA kernels were not used"
