@@ -250,33 +250,56 @@ __global__ void rmsnorm_small_fwd_kernel(const bf16* __restrict__ x, const float
 __global__ void rmsnorm_small_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                                          const float* __restrict__ w, const float* __restrict__ rstd,
                                          bf16* __restrict__ dx, float* __restrict__ dw, long rows, int D) {
-  // dw (D,) accumulated with fp32 atomics from per-warp partials (D is small).
-  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const bf16* xr = x + row * D;
-  const bf16* gr = dy + row * D;
-  const float r = rstd[row];
-  float dot = 0.f;
-  for (int i = lane * 2; i < D; i += 64) {
-    const float2 xv = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + i));
-    const float2 gv = __bfloat1622float2(*reinterpret_cast<const bf162*>(gr + i));
-    const float w0 = w ? w[i] : 1.f, w1 = w ? w[i + 1] : 1.f;
-    dot += gv.x * w0 * xv.x * r + gv.y * w1 * xv.y * r;
-  }
-  dot = warp_sum(dot) / (float)D;
-  bf16* dxr = dx + row * D;
-  for (int i = lane * 2; i < D; i += 64) {
-    const float2 xv = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + i));
-    const float2 gv = __bfloat1622float2(*reinterpret_cast<const bf162*>(gr + i));
-    const float w0 = w ? w[i] : 1.f, w1 = w ? w[i + 1] : 1.f;
-    const float o0 = (gv.x * w0 - xv.x * r * dot) * r;
-    const float o1 = (gv.y * w1 - xv.y * r * dot) * r;
-    *reinterpret_cast<bf162*>(dxr + i) = __floats2bfloat162_rn(o0, o1);
-    if (dw) {
-      atomicAdd(dw + i, gv.x * xv.x * r);
-      atomicAdd(dw + i + 1, gv.y * xv.y * r);
+  // One warp per row, grid-stride over rows.  dw (D,) partial sums stay in registers while a warp walks its rows
+  // (D <= 512: 8 pairs per lane), are combined across the CTA's warps in shared memory and leave with ONE atomic per
+  // element per CTA; a per-row atomic on D hot addresses serialises the whole grid.
+  constexpr int MAXP = 8;
+  extern __shared__ float dw_sh[];                 // D floats
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  float2 acc[MAXP];
+#pragma unroll
+  for (int p = 0; p < MAXP; ++p) acc[p] = make_float2(0.f, 0.f);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) dw_sh[i] = 0.f;
+  __syncthreads();
+  for (long row = (long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += (long)gridDim.x * wpb) {
+    const bf16* xr = x + row * D;
+    const bf16* gr = dy + row * D;
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = lane * 2; i < D; i += 64) {
+      const float2 xv = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + i));
+      const float2 gv = __bfloat1622float2(*reinterpret_cast<const bf162*>(gr + i));
+      const float w0 = w ? w[i] : 1.f, w1 = w ? w[i + 1] : 1.f;
+      dot += gv.x * w0 * xv.x * r + gv.y * w1 * xv.y * r;
     }
+    dot = warp_sum(dot) / (float)D;
+    bf16* dxr = dx + row * D;
+#pragma unroll
+    for (int p = 0; p < MAXP; ++p) {
+      const int i = lane * 2 + p * 64;
+      if (i < D) {
+        const float2 xv = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + i));
+        const float2 gv = __bfloat1622float2(*reinterpret_cast<const bf162*>(gr + i));
+        const float w0 = w ? w[i] : 1.f, w1 = w ? w[i + 1] : 1.f;
+        const float o0 = (gv.x * w0 - xv.x * r * dot) * r;
+        const float o1 = (gv.y * w1 - xv.y * r * dot) * r;
+        *reinterpret_cast<bf162*>(dxr + i) = __floats2bfloat162_rn(o0, o1);
+        acc[p].x += gv.x * xv.x * r;
+        acc[p].y += gv.y * xv.y * r;
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int p = 0; p < MAXP; ++p) {
+      const int i = lane * 2 + p * 64;
+      if (i < D) {
+        atomicAdd(&dw_sh[i], acc[p].x);
+        atomicAdd(&dw_sh[i + 1], acc[p].y);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(dw + i, dw_sh[i]);
   }
 }
 
@@ -374,6 +397,48 @@ __global__ void glu_bwd_kernel(const bf16* __restrict__ dact, const bf16* __rest
     *reinterpret_cast<uint4*>(dgate + t * ld_d + c) = pack8(og);
     *reinterpret_cast<uint4*>(dup + t * ld_d + c) = pack8(ou);
     if (act_out) *reinterpret_cast<uint4*>(act_out + t * ld_act + c) = pack8(oa);
+  }
+}
+
+// MoE expert backward through the gated activation with the router weight folded in, one CTA per expert-major row
+// (the reference's swiglu_bwd_weighted kernel, flextrain/ops/_kernels/moe.py:77-145):
+//   act = glu(gate, up);  d = w_row * dact_u;  dgate, dup from d;  act_w = w_row * act (left operand of the down-proj
+//   weight gradient, so dy needs no separate scaling pass);  dw_row = sum_c dact_u * act (router-weight gradient).
+__global__ void glu_bwd_weighted_kernel(const bf16* __restrict__ dact, const bf16* __restrict__ gate,
+                                        const bf16* __restrict__ up, const float* __restrict__ w_row,
+                                        bf16* __restrict__ dgate, bf16* __restrict__ dup, bf16* __restrict__ act_w,
+                                        float* __restrict__ dw_row, int F, int ld_in, int ld_d, int kind) {
+  __shared__ float red[32];
+  const long t = blockIdx.x;
+  const float wr = w_row[t];
+  float dot = 0.f;
+  for (int c = threadIdx.x << 3; c < F; c += blockDim.x << 3) {
+    float g[8], u[8], d[8], og[8], ou[8], oa[8];
+    unpack8(*reinterpret_cast<const uint4*>(gate + t * ld_in + c), g);
+    unpack8(*reinterpret_cast<const uint4*>(up + t * ld_in + c), u);
+    unpack8(*reinterpret_cast<const uint4*>(dact + t * (long)F + c), d);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float a, da;
+      act_and_grad(g[e], kind, a, da);
+      const float act = a * u[e];
+      dot += d[e] * act;
+      const float dd = d[e] * wr;
+      og[e] = dd * u[e] * da;
+      ou[e] = dd * a;
+      oa[e] = act * wr;
+    }
+    *reinterpret_cast<uint4*>(dgate + t * ld_d + c) = pack8(og);
+    *reinterpret_cast<uint4*>(dup + t * ld_d + c) = pack8(ou);
+    *reinterpret_cast<uint4*>(act_w + t * (long)F + c) = pack8(oa);
+  }
+  dot = warp_sum(dot);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) dw_row[t] = v;
   }
 }
 
@@ -770,9 +835,11 @@ int ftb_rmsnorm_small_fwd(const void* x, const float* w, void* y, float* rstd, l
 int ftb_rmsnorm_small_bwd(const void* dy, const void* x, const float* w, const float* rstd, void* dx, float* dw,
                           long rows, int D, cudaStream_t s) {
   if (rows == 0) return 0;
-  if (D % 2) return -2;
-  rmsnorm_small_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const bf16*)dy, (const bf16*)x, w, rstd,
-                                                                       (bf16*)dx, dw, rows, D);
+  if (D % 2 || D > 512) return -2;
+  long blocks = (rows + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  rmsnorm_small_bwd_kernel<<<(unsigned)blocks, 256, D * sizeof(float), s>>>((const bf16*)dy, (const bf16*)x, w, rstd,
+                                                                            (bf16*)dx, dw, rows, D);
   CHECK_LAUNCH();
 }
 
@@ -804,6 +871,15 @@ int ftb_glu_bwd(const void* dact, const void* gate, const void* up, void* dgate,
   const int blocks = (int)((nvec + 255) / 256 < 148 * 16 ? (nvec + 255) / 256 : 148 * 16);
   glu_bwd_kernel<<<blocks, 256, 0, s>>>((const bf16*)dact, (const bf16*)gate, (const bf16*)up, (bf16*)dgate,
                                         (bf16*)dup, (bf16*)act_out, T, F, ld_in, ld_d, ld_act, kind);
+  CHECK_LAUNCH();
+}
+
+int ftb_glu_bwd_weighted(const void* dact, const void* gate, const void* up, const float* w_row, void* dgate, void* dup,
+                         void* act_w, float* dw_row, long T, int F, int ld_in, int ld_d, int kind, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (F % 8 || ld_in % 8 || ld_d % 8) return -2;
+  glu_bwd_weighted_kernel<<<(unsigned)T, 128, 0, s>>>((const bf16*)dact, (const bf16*)gate, (const bf16*)up, w_row,
+                                                      (bf16*)dgate, (bf16*)dup, (bf16*)act_w, dw_row, F, ld_in, ld_d, kind);
   CHECK_LAUNCH();
 }
 

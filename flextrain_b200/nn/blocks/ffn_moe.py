@@ -159,13 +159,11 @@ class MoEFFN:
             # activation (re-emitted), router-weight gradient and weighted dact in one pass
             wrow = ref.moe_row_weights(w, plan)
             dup = torch.empty_like(up)
-            dactw = (dact_u.to(torch.float32) * wrow.unsqueeze(-1)).to(dact_u.dtype)
-            _, _, act = ops.glu_bwd(dactw, up[:, F:], up[:, :F], c.kind, dgate=dup[:, F:], dup=dup[:, :F])
-            dw_rows = (dact_u.to(torch.float32) * act.to(torch.float32)).sum(-1)       # (R,)
+            act_w, dw_rows = ops.glu_bwd_weighted(dact_u, up[:, F:], up[:, :F], wrow, c.kind, dgate=dup[:, F:],
+                                                  dup=dup[:, :F])
             dw = ref.moe_rows_to_slots(dw_rows, plan, w.shape)
-            if "g_down" in grads:
-                dyw = (dy_u.to(torch.float32) * wrow.unsqueeze(-1)).to(dy_u.dtype)
-                ops.grouped_wgrad(dyw, act, plan.offsets, grads["g_down"], pad=ROW_PAD)
+            if "g_down" in grads:       # g_down += dy^T (w * act): the router weight rides on the activation
+                ops.grouped_wgrad(dy_u, act_w, plan.offsets, grads["g_down"], pad=ROW_PAD)
             if "g_up" in grads:
                 ops.grouped_wgrad(dup, xs, plan.offsets, grads["g_up"], pad=ROW_PAD)
             dxs = ops.grouped_gemm(dup, params["w_up"], plan.offsets, trans_w=False)

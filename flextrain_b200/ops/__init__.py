@@ -185,6 +185,20 @@ def glu_bwd(dact, gate, up, kind="swiglu", *, dgate=None, dup=None):
     return dg, du, act
 
 
+def glu_bwd_weighted(dact_u, gate, up, w_row, kind="swiglu", *, dgate, dup):
+    """Expert backward through the gated activation with the router weight folded in (one pass):
+    ``dgate, dup`` from ``w_row * dact_u``; returns ``(act_w = w_row * act, dw_row = sum(dact_u * act, -1))``."""
+    if _cuda_bf16(dact_u, gate, up) and dact_u.is_contiguous():
+        _count()
+        return _kernels().glu_bwd_weighted(dact_u, gate, up, w_row.to(torch.float32).contiguous(), kind,
+                                           dgate=dgate, dup=dup)
+    wcol = w_row.to(torch.float32).unsqueeze(-1)
+    dactw = (dact_u.to(torch.float32) * wcol).to(dact_u.dtype)
+    _, _, act = glu_bwd(dactw, gate, up, kind, dgate=dgate, dup=dup)
+    dw_row = (dact_u.to(torch.float32) * act.to(torch.float32)).sum(-1)
+    return (act.to(torch.float32) * wcol).to(act.dtype), dw_row
+
+
 # -------------------------------------------------------------------------- attention
 def _attn_backend_for(q) -> str:
     if not q.is_cuda or q.dtype not in (torch.bfloat16, torch.float16):

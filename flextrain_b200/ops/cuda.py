@@ -280,6 +280,21 @@ def glu_bwd(dact, gate, up, kind="swiglu", *, dgate=None, dup=None, emit_act=Tru
     return dgate, dup, act
 
 
+def glu_bwd_weighted(dact_u, gate, up, w_row, kind="swiglu", *, dgate, dup):
+    """MoE expert backward through the gated activation with the per-row router weight folded in.
+    Returns ``(act_w (T,F) = w_row * act, dw_row (T,) = sum(dact_u * act))``; writes ``dgate / dup``."""
+    lib = load("elementwise")
+    T, F = gate.shape
+    assert dact_u.is_contiguous() and w_row.dtype == torch.float32 and dgate.stride(0) == dup.stride(0)
+    act_w = torch.empty(T, F, dtype=gate.dtype, device=gate.device)
+    dw_row = torch.empty(T, dtype=torch.float32, device=gate.device)
+    rc = lib.ftb_glu_bwd_weighted(_ptr(dact_u), _ptr(gate), _ptr(up), _ptr(w_row), _ptr(dgate), _ptr(dup), _ptr(act_w),
+                                  _ptr(dw_row), c_long(T), c_int(F), c_int(gate.stride(0)), c_int(dgate.stride(0)),
+                                  c_int(_KIND[kind]), _stream())
+    _check(rc, "ftb_glu_bwd_weighted")
+    return act_w, dw_row
+
+
 def softmax_ce_(logits, targets, *, grad_scale=1.0, softcap=0.0, loss_mask=None, ignore_index=-100):
     """In place: ``logits`` becomes dlogits. Returns per-token loss (fp32)."""
     lib = load("elementwise")

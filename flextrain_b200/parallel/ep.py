@@ -172,12 +172,13 @@ class ExpertParallel:
             return recv, sc
         buf = self._buf(name, cap * D * 2)
         recv = buf.local.view(torch.bfloat16)[: cap * D].view(cap, D)
-        recv.zero_()
+        R = max(plan.rows, PAD)
+        recv[:R].zero_()                   # padding rows inside the used range must read as zero; the rest is never read
         sbuf = sc = None
         if with_scalar:
             sbuf = self._buf(name + "_s", cap * 4)
             sc = sbuf.local.view(torch.float32)[:cap]
-            sc.zero_()
+            sc[:R].zero_()
         self._sync()                       # all receive buffers are clean and no one still reads the old contents
         from ..ops.cuda import _stream
         n = plan.src_tok.numel()
@@ -281,12 +282,10 @@ class ExpertParallel:
             up = ops.grouped_gemm(xs, params["w_up"], plan.offsets)
         dact_u = ops.grouped_gemm(dy_u, params["w_down"], plan.offsets, trans_w=False)
         dup = torch.empty_like(up)
-        dactw = (dact_u.to(torch.float32) * wrow.unsqueeze(-1)).to(dact_u.dtype)
-        _, _, act = ops.glu_bwd(dactw, up[:, F:], up[:, :F], c.kind, dgate=dup[:, F:], dup=dup[:, :F])
-        dw_rows = (dact_u.to(torch.float32) * act.to(torch.float32)).sum(-1)
-        if "g_down" in grads:
-            dyw = (dy_u.to(torch.float32) * wrow.unsqueeze(-1)).to(dy_u.dtype)
-            ops.grouped_wgrad(dyw, act, plan.offsets, grads["g_down"], pad=PAD)
+        act_w, dw_rows = ops.glu_bwd_weighted(dact_u, up[:, F:], up[:, :F], wrow, c.kind, dgate=dup[:, F:],
+                                              dup=dup[:, :F])
+        if "g_down" in grads:           # g_down += dy^T (w * act): the router weight rides on the activation
+            ops.grouped_wgrad(dy_u, act_w, plan.offsets, grads["g_down"], pad=PAD)
         if "g_up" in grads:
             ops.grouped_wgrad(dup, xs, plan.offsets, grads["g_up"], pad=PAD)
         dxs = ops.grouped_gemm(dup, params["w_up"], plan.offsets, trans_w=False)
