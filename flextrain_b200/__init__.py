@@ -13,6 +13,7 @@ from .io.sequence import Sequence
 from .io.sources import (CustomSchemaTokenSource, HFTokenSource, JsonSFTTokenSource, RawTokenSource,
                          ShardTokenSource, SyntheticTokenSource, TokenSource)
 from .optim import AdamW, HybridMuonAdamW, Muon
+from . import export  # noqa: E402  (``flextrain_b200.export.save_hf_full`` / ``save_lora_adapter`` / ``save_hf_merged``)
 
 __version__ = "0.1.0"
 

@@ -940,6 +940,65 @@ int ftb_l2norm_fwd(const void* x, void* y, float* rnorm, long rows, int D, float
   CHECK_LAUNCH();
 }
 
+// Router backward (one warp per token, E <= 256): dlogits (T, E) fp32 from the gradient of the K routing weights.
+//   mode 0 (softmax over the K picks):  dl[e_k] = w_k (dw_k - sum_j w_j dw_j), 0 elsewhere
+//   mode 1 (softmax over E, then pick): dl = p * (dp - sum p dp) with dp = dw scattered to the picks
+// (flextrain/ops/_kernels/moe.py:360-458).
+__global__ void topk_route_bwd_kernel(const float* __restrict__ dw, const bf16* __restrict__ logits,
+                                      const float* __restrict__ w, const int* __restrict__ experts,
+                                      float* __restrict__ dl, int T, int E, int K, int mode) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int lane = threadIdx.x & 31;
+  float* out = dl + (size_t)t * E;
+  const float* dwt = dw + (size_t)t * K;
+  const int* et = experts + (size_t)t * K;
+  if (mode == 0) {
+    const float* wt = w + (size_t)t * K;
+    float dot = 0.f;
+    for (int k = 0; k < K; ++k) dot += wt[k] * dwt[k];
+    for (int e = lane; e < E; e += 32) out[e] = 0.f;
+    __syncwarp();
+    if (lane < K) out[et[lane]] = wt[lane] * (dwt[lane] - dot);
+    return;
+  }
+  float v[8], dp[8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = lane + j * 32;
+    v[j] = e < E ? __bfloat162float(logits[(size_t)t * E + e]) : -INFINITY;
+    dp[j] = 0.f;
+    mx = fmaxf(mx, v[j]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { v[j] = (lane + j * 32 < E) ? __expf(v[j] - mx) : 0.f; sum += v[j]; }
+  sum = warp_sum(sum);
+  for (int k = 0; k < K; ++k) {
+    const int e = et[k];
+    if ((e & 31) == lane) dp[e >> 5] = dwt[k];
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { v[j] /= sum; dot += v[j] * dp[j]; }
+  dot = warp_sum(dot);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = lane + j * 32;
+    if (e < E) out[e] = v[j] * (dp[j] - dot);
+  }
+}
+
+int ftb_topk_route_bwd(const float* dw, const void* logits, const float* w, const int* experts, float* dl, int T, int E,
+                       int K, int mode, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (E > 256 || K > 32) return -2;
+  topk_route_bwd_kernel<<<(T + 7) / 8, 256, 0, s>>>(dw, (const bf16*)logits, w, experts, dl, T, E, K, mode);
+  CHECK_LAUNCH();
+}
+
 int ftb_topk_route(const void* logits, float* weights, int* experts, int T, int E, int K, int mode, cudaStream_t s) {
   if (T == 0) return 0;
   if (E > 256 || K > 16) return -2;

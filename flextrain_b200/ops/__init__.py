@@ -10,6 +10,7 @@ Backends (``set_gemm_backend`` / ``set_attention_backend``):
 """
 from __future__ import annotations
 
+import math
 import os
 from typing import Optional
 
@@ -288,8 +289,42 @@ def adamw_multi(params, grads, ms, vs, *, lrs, wds, beta1, beta2, eps, step, gra
                        grad_scale=grad_scale)
 
 
-def muon_step(p, g, mom, **kw):
-    return ref.muon_step(p, g, mom, **kw)
+def newton_schulz_bf16(u: torch.Tensor, iters: int = 5) -> torch.Tensor:
+    """Quintic Newton-Schulz orthogonalisation of one matrix on the tcgen05 GEMM, bf16 iterates with fp32
+    accumulation: per iteration ``A = X Xᵀ``, ``B = bA + cA²`` (epilogue ``alpha=c, beta=b``), ``X = aX + BX``
+    (epilogue ``beta=a``) — three launches, no elementwise pass (flextrain/ops/_kernels/muon.py:53-61 issues
+    mm / addmm through cuBLAS).  A tall matrix is iterated as ``AᵀA`` on the right, so nothing is transposed."""
+    a, b, c = ref.NS_COEFFS
+    x = (u / (u.norm() + 1e-7)).to(torch.bfloat16).contiguous()
+    tall = x.shape[0] > x.shape[1]
+    for _ in range(iters):
+        if not tall:
+            A = gemm(x, x, trans_b=True)                       # (m, m)
+            B = gemm(A, A, alpha=c, beta=b, c=A)
+            x = gemm(B, x, beta=a, c=x)
+        else:
+            A = gemm(x, x, trans_a=True)                       # (n, n) = XᵀX
+            B = gemm(A, A, alpha=c, beta=b, c=A)
+            x = gemm(x, B, beta=a, c=x)
+    return x
+
+
+def muon_step(p, g, mom, *, lr, beta=0.95, weight_decay=0.0, ns_iters=5, nesterov=True, grad_scale=1.0):
+    """Muon update (flextrain/ops/_kernels/muon.py:16-75).  On CUDA bf16 the Newton-Schulz GEMMs run on the
+    tcgen05 kernel; 3-D tensors (stacked experts) are updated matrix by matrix."""
+    if not (_cuda_bf16(p) and _GEMM_BACKEND == "tcgen05" and p.dim() in (2, 3) and min(p.shape[-2:]) >= 64
+            and p.shape[-1] % 8 == 0 and p.shape[-2] % 8 == 0):
+        return ref.muon_step(p, g, mom, lr=lr, beta=beta, weight_decay=weight_decay, ns_iters=ns_iters,
+                             nesterov=nesterov, grad_scale=grad_scale)
+    gf = g.to(torch.float32) * grad_scale
+    mf = beta * mom.to(torch.float32) + gf
+    mom.copy_(mf.to(mom.dtype))
+    u = gf + beta * mf if nesterov else mf
+    scale = 0.2 * math.sqrt(max(p.shape[-2], p.shape[-1]))
+    mats = [(p, u)] if p.dim() == 2 else [(p[i], u[i]) for i in range(p.shape[0])]
+    for pm, um in mats:
+        x = newton_schulz_bf16(um, ns_iters)
+        pm.copy_((pm.to(torch.float32) * (1.0 - lr * weight_decay) - (lr * scale) * x.to(torch.float32)).to(pm.dtype))
 
 
 # -------------------------------------------------------------------------------- MoE
@@ -300,7 +335,14 @@ def topk_route(logits, k, mode="topk_then_softmax"):
     return ref.topk_route(logits, k, mode)
 
 
-topk_route_bwd = ref.topk_route_bwd
+def topk_route_bwd(dw, logits, w, experts, mode="topk_then_softmax"):
+    """dlogits (T, E) fp32 from the gradient of the selected routing weights."""
+    if _cuda_bf16(logits) and logits.shape[1] <= 256 and experts.shape[1] <= 32:
+        _count()
+        return _kernels().topk_route_bwd(dw, logits, w, experts, mode)
+    return ref.topk_route_bwd(dw, logits, w, experts, mode)
+
+
 moe_sort = ref.moe_sort
 
 
@@ -374,5 +416,13 @@ def gated_rmsnorm_fwd(o, z, w, eps):
 causal_conv1d_fwd = ref.causal_conv1d_fwd
 gated_delta_rule = ref.gated_delta_rule
 gated_delta_rule_chunked = ref.gated_delta_rule_chunked
-top_p_sample = ref.top_p_sample
+def top_p_sample(logits, top_p, temperature, generator=None):
+    """Nucleus sampling per row (flextrain/ops/_kernels/sample_top_p.py:7-150)."""
+    if _cuda_bf16(logits):
+        from . import linattn_cuda
+        _count()
+        return linattn_cuda.top_p_sample(logits, top_p, temperature, generator=generator)
+    return ref.top_p_sample(logits, top_p, temperature, generator=generator)
+
+
 rope_inv_freq = ref.rope_inv_freq

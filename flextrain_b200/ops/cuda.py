@@ -280,6 +280,19 @@ def glu_bwd(dact, gate, up, kind="swiglu", *, dgate=None, dup=None, emit_act=Tru
     return dgate, dup, act
 
 
+def topk_route_bwd(dw, logits, w, experts, mode="topk_then_softmax"):
+    lib = load("elementwise")
+    T, E = logits.shape
+    K = experts.shape[1]
+    dl = torch.empty(T, E, dtype=torch.float32, device=logits.device)
+    rc = lib.ftb_topk_route_bwd(_ptr(dw.to(torch.float32).contiguous()), _ptr(logits.contiguous()),
+                                _ptr(w.to(torch.float32).contiguous()), _ptr(experts.to(torch.int32).contiguous()),
+                                _ptr(dl), c_int(T), c_int(E), c_int(K), c_int(0 if mode == "topk_then_softmax" else 1),
+                                _stream())
+    _check(rc, "ftb_topk_route_bwd")
+    return dl
+
+
 def glu_bwd_weighted(dact_u, gate, up, w_row, kind="swiglu", *, dgate, dup):
     """MoE expert backward through the gated activation with the per-row router weight folded in.
     Returns ``(act_w (T,F) = w_row * act, dw_row (T,) = sum(dact_u * act))``; writes ``dgate / dup``."""

@@ -224,6 +224,13 @@ def test_topk_route(mode):
     ww, wi = ref.topk_route(z, K, mode)
     assert torch.equal(idx.long(), wi.long())
     assert _rel(w, ww) < 1e-3
+    # backward: dlogits from the gradient of the routing weights, against autograd through the fp32 reference
+    dw = torch.randn(T, K, device=DEV)
+    zr = z.float().clone().requires_grad_(True)
+    wr, _ = ref.topk_route(zr, K, mode)
+    (want,) = torch.autograd.grad(wr, zr, dw)
+    got = ops.topk_route_bwd(dw, z, w, idx, mode)
+    assert _rel(got, want) < 2e-3, _rel(got, want)
 
 
 def test_moe_gather_combine():
@@ -313,3 +320,23 @@ def test_attention_tcgen05_bwd(hd, case):
     assert _rel(dq, wq) < 2e-2, (case, hd, "dq", _rel(dq, wq))
     assert _rel(dk, wk) < 2e-2, (case, hd, "dk", _rel(dk, wk))
     assert _rel(dv, wv) < 2e-2, (case, hd, "dv", _rel(dv, wv))
+
+
+@pytest.mark.parametrize("shape", [(256, 512), (768, 256), (3, 128, 256)])
+def test_muon_newton_schulz_on_tcgen05(shape):
+    """Muon step whose Newton-Schulz GEMMs run on the tcgen05 kernel (bf16 iterates) against the fp32 reference."""
+    from flextrain_b200 import ops
+    torch.manual_seed(0)
+    p = (torch.randn(*shape, device=DEV) * 0.05).to(torch.bfloat16)
+    g = (torch.randn(*shape, device=DEV) * 0.01).to(torch.bfloat16)
+    mom = torch.zeros(*shape, device=DEV, dtype=torch.bfloat16)
+    p_ref, mom_ref = p.float().clone(), mom.float().clone()
+    ref.muon_step(p_ref, g.float(), mom_ref, lr=0.02, beta=0.95, weight_decay=0.01)
+    ops.muon_step(p, g, mom, lr=0.02, beta=0.95, weight_decay=0.01)
+    assert _rel(mom, mom_ref) < 1e-2
+    torch.manual_seed(0)
+    start = (torch.randn(*shape, device=DEV) * 0.05).to(torch.bfloat16).float()
+    step, step_ref = p.float() - start, p_ref - start
+    cos = torch.nn.functional.cosine_similarity(step.flatten(), step_ref.flatten(), dim=0)
+    assert float(cos) > 0.98, float(cos)
+    assert _rel(p, p_ref) < 2e-2, _rel(p, p_ref)
