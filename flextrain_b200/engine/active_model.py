@@ -15,6 +15,7 @@ What differs from the reference, by design for an 8×B200 NVSwitch box:
 """
 from __future__ import annotations
 
+import ctypes
 import dataclasses
 
 import contextlib
@@ -94,6 +95,8 @@ class ActiveModel:
             host_act_bytes=ws.host_act_buffer_size, verbose=verbose, **(dp.buffer_kwargs() if dp is not None else {}))
         self.streams = StreamBundle.create(device, secondary=False)
         self.events = EventBook(self.streams)
+        self._ce = None                 # C++ copy engine, created on first host<->device transfer
+        self._ce_key = 0
         self._scheduler = None
         self._last_plan: Optional[SaveLevelPlan] = None
         self.is_causal = True
@@ -287,6 +290,39 @@ class ActiveModel:
                     if nxt < nL:
                         self._prefetch_params(nxt, after_layer=l)
 
+    # ======================================================================= copy engine
+    def _engine_copies(self, pairs, kind: int) -> None:
+        """Run ``(dst, src)`` copies through the C++ copy engine, ordered inside the CURRENT stream: the engine's
+        worker thread issues one ``cudaMemcpyAsync`` per pair on its own stream after everything queued on the current
+        stream so far, and the current stream resumes when the last one has finished.  One Python call per batch
+        instead of one ``copy_`` per tensor (flextrain/engine/buffers.py:1088-1164 and
+        flextrain/core/activation_schema.py:483-519 issue a ``copy_`` per tensor / field from Python).
+        ``FTB_COPY_ENGINE=0`` falls back to ``Tensor.copy_``."""
+        if not pairs:
+            return
+        import os
+        if os.environ.get("FTB_COPY_ENGINE", "1") == "0":
+            for d, s_ in pairs:
+                d.copy_(s_, non_blocking=True)
+            return
+        if self._ce is None:
+            from .copy_engine import CopyEngine
+            self._ce = CopyEngine(self.device)
+        cur = ev = None
+        if self.streams.is_cuda:
+            cur = torch.cuda.current_stream(self.device)
+            ev = torch.cuda.Event()
+            ev.record(cur)
+        self._ce_key += 1
+        key = self._ce_key
+        jobs = [(d, s_, kind, 0, ev, key if i == len(pairs) - 1 else 0) for i, (d, s_) in enumerate(pairs)]
+        ticket = self._ce.submit(jobs)
+        self._ce.stream_wait(key, ticket, cur)
+        self._ce.lib.ftb_ce_forget(self._ce.h, ctypes.c_uint64(key))
+
+    def _ring_copier(self, kind: int):
+        return lambda dst, src: self._engine_copies([(dst, src)], kind)
+
     def _offload_slot(self, slot: ActivationSlot, level: int, l: int, c: int):
         """Send the fields with ``tier <= level`` to the host arena on the outbound stream; drop the rest."""
         bm, st, ev = self.buffers, self.streams, self.events
@@ -298,7 +334,9 @@ class ActiveModel:
         ev.act_computed.record((l, c), st.compute)
         with st.use(st.outbound):
             ev.act_computed.wait((l, c), st.outbound)
-            host = send_home(slot, hbuf, level)
+            pairs = []
+            host = send_home(slot, hbuf, level, copy_fn=lambda d, s_: pairs.append((d, s_)))
+            self._engine_copies(pairs, 1)
             ev.act_out.record((l, c), st.outbound)
         if st.is_cuda:
             for name in slot.names():
@@ -310,7 +348,7 @@ class ActiveModel:
         with st.use(st.inbound):
             if after_layer is not None:
                 ev.layer_out.wait(after_layer, st.inbound)      # ring slot is free once its previous tenant finished
-            bm.fetch_layer_params(l)
+            bm.fetch_layer_params(l, self._ring_copier(0))
             ev.weights_in.record(l, st.inbound)
 
     # =========================================================================== backward
@@ -364,7 +402,7 @@ class ActiveModel:
                 if not bm.grads_resident:
                     with st.use(st.outbound):
                         ev.grads_ready.wait(l, st.outbound)
-                        bm.offload_layer_grads(l)
+                        bm.offload_layer_grads(l, self._ring_copier(1))
                         ev.layer_out.record(("g", l), st.outbound)
                 if not bm.params_resident:
                     ev.layer_out.record(("b", l), st.compute)
@@ -379,7 +417,7 @@ class ActiveModel:
         with st.use(st.inbound):
             if after is not None:
                 ev.layer_out.wait(after, st.inbound)
-            bm.fetch_layer_params(l)
+            bm.fetch_layer_params(l, self._ring_copier(0))
             ev.weights_in.record(("b", l), st.inbound)
 
     def _prepare_ring_grads(self, l: int):
@@ -395,7 +433,7 @@ class ActiveModel:
             with st.use(st.inbound):
                 if ev.layer_out.has(("g", prev_tenant)):
                     ev.layer_out.wait(("g", prev_tenant), st.inbound)
-                bm.fetch_layer_grads(l)
+                bm.fetch_layer_grads(l, self._ring_copier(0))
                 ev.grads_in.record(l, st.inbound)
             ev.grads_in.wait(l, st.compute)
 
@@ -409,7 +447,9 @@ class ActiveModel:
             return slot
         with st.use(st.inbound):
             ev.act_out.wait((l, c), st.inbound)
-            dev = fetch_home(slot, None, self.device)
+            pairs = []
+            dev = fetch_home(slot, None, self.device, copy_fn=lambda d, s_: pairs.append((d, s_)))
+            self._engine_copies(pairs, 0)
             ev.act_in.record((l, c), st.inbound)
         ev.act_in.wait((l, c), st.compute)
         return dev
@@ -460,7 +500,8 @@ class ActiveModel:
                 for n in ring_n:
                     if k - n >= 0:
                         ev.layer_out.wait(("s", k - n), st.inbound)
-                bm.fetch_layer_params(k); bm.fetch_layer_grads(k); bm.fetch_layer_opt(k)
+                cp = self._ring_copier(0)
+                bm.fetch_layer_params(k, cp); bm.fetch_layer_grads(k, cp); bm.fetch_layer_opt(k, cp)
                 ev.opt_in.record(k, st.inbound)
 
         st.inbound.wait_stream(st.compute)
@@ -476,8 +517,8 @@ class ActiveModel:
             ev.layer_out.record(("c", l), st.compute)
             with st.use(st.outbound):
                 ev.layer_out.wait(("c", l), st.outbound)
-                bm.offload_layer_params(l)
-                bm.offload_layer_opt(l)
+                bm.offload_layer_params(l, self._ring_copier(1))
+                bm.offload_layer_opt(l, self._ring_copier(1))
                 ev.layer_out.record(("s", l), st.outbound)
             if l + depth < nL:
                 fetch(l + depth)
@@ -543,4 +584,8 @@ class ActiveModel:
         return None
 
     def destroy(self) -> None:
+        if self._ce is not None:
+            self._ce.synchronize()
+            self._ce.close()
+            self._ce = None
         self.buffers.destroy()

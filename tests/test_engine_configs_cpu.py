@@ -77,7 +77,20 @@ def test_G_opt_ring(base):
 
 
 def test_EFG_all_rings_multi_round(base):
-    _same(base, _run(dict(n_gpu_layers=2, n_gpu_grads=2, n_gpu_opt_layers=2, chunk=96, round_tokens=128)))
+    r = _run(dict(n_gpu_layers=2, n_gpu_grads=2, n_gpu_opt_layers=2, chunk=96, round_tokens=128))
+    _same(base, r)
+    nbytes, ncopies = r[2]._ce.stats()          # the ring transfers went through the C++ copy engine
+    assert ncopies > 0 and nbytes > 0
+
+
+def test_copy_engine_can_be_switched_off(base, monkeypatch):
+    monkeypatch.setenv("FTB_COPY_ENGINE", "0")
+    r = _run(dict(n_gpu_layers=2, chunk=96, host_act_buffer_size=64 << 20), force=1)
+    assert r[2]._ce is None
+    monkeypatch.delenv("FTB_COPY_ENGINE")
+    r2 = _run(dict(n_gpu_layers=2, chunk=96, host_act_buffer_size=64 << 20), force=1)
+    assert r2[2]._ce is not None and r2[2]._ce.stats()[1] > 0
+    _same(r, r2)
 
 
 def test_H_sequence_spans_chunks_matches_autograd():
