@@ -452,6 +452,11 @@ class ActiveModel:
             self._engine_copies(pairs, 0)
             ev.act_in.record((l, c), st.inbound)
         ev.act_in.wait((l, c), st.compute)
+        if st.is_cuda:
+            # allocated while the inbound stream was current, consumed on the compute stream: the allocator must not
+            # hand this memory to the next inbound allocation before compute is done with it
+            for name in dev.names():
+                dev._t[name].record_stream(st.compute)
         return dev
 
     def _refresh_kv_window(self, l: int, chunk_ids, metas, slots) -> None:
@@ -467,6 +472,8 @@ class ActiveModel:
                     continue
                 P, L = m.prior_lens[0], m.seq_lens[0]
                 s = slots[(l, c)]
+                if self.events.act_out.has((l, c)):       # saved K/V live in the host arena: wait for their arrival
+                    self.events.act_out.wait((l, c), st.inbound_fwd_context)
                 w.k[P:P + L].copy_(s._t["xk"], non_blocking=True)
                 w.v[P:P + L].copy_(s._t["xv"], non_blocking=True)
             w.dk.zero_()

@@ -87,3 +87,29 @@ def test_hybrid_gated_deltanet_bf16_tracks_fp32(seq_len, chunk):
         assert abs(a.loss - b.loss) < 0.04, (step, a.loss, b.loss)
     from flextrain_b200.ops import cuda as k
     assert "gdn" in k._libs and "seqmix" in k._libs, "Gated DeltaNet CUDA kernels were not used"
+
+
+@pytest.mark.parametrize("ws_kw,force", [
+    (dict(chunk=128, host_act_buffer_size=256 << 20, n_gpu_act_slots=3), None),     # DP-solver tiers, host arena
+    (dict(chunk=128, host_act_buffer_size=256 << 20), 0),                           # everything offloaded at tier 0
+    (dict(chunk=128, n_gpu_layers=2, n_gpu_grads=2, n_gpu_opt_layers=2), None),     # weight / grad / opt rings
+])
+def test_long_sequence_with_host_offload_bf16_tracks_fp32(ws_kw, force):
+    """One sequence spanning four chunks (rolling KV window) with activations and states streamed through pinned host
+    memory on the side streams: the bf16 GPU run must follow the fp32 CPU run (a stream-ordering bug shows as NaN or
+    drift here, not on the CPU where everything is synchronous)."""
+    dims = dict(vocab_size=1024, n_layers=4, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, expert_dim=704,
+                ffn_dim=704, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+    mk = lambda **kw: build_tiny(dims=dims, max_seq_len=512, batch_tokens=1024, force_saved_act_level=force,
+                                 ws=ft.WorkingSetConfig.simple(max_seq_len=512, max_global_batch_tokens=1024,
+                                                               round_tokens=1024, **ws_kw), **kw)
+    cpu = mk()
+    gpu = mk(device="cuda:0", dtype=torch.bfloat16, optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32))
+    _copy_weights(cpu, gpu)
+    src = ft.SyntheticTokenSource(1024, 512, seed=13)
+    for step in range(4):
+        seqs = src.get_sequences(1024)
+        a = cpu.fwd_bwd(seqs); cpu.step()
+        b = gpu.fwd_bwd(seqs); gpu.step()
+        assert abs(a.loss - b.loss) < 0.04, (step, a.loss, b.loss)
+    gpu.destroy()
