@@ -189,16 +189,40 @@ __global__ void __launch_bounds__(RS_THREADS) adamw_push_kernel(PeerTable params
     float p[8];
     if (vec) unpack8(*reinterpret_cast<const uint4*>(mine), p);
     else for (int e = 0; e < n; ++e) p[e] = __bfloat162float(mine[e]);
-    for (int e = 0; e < n; ++e) {
-      const long si = sg.out_off + i0 + e;
-      const float g = grad[si];
-      float mm = m[si], vv = v[si];
-      p[e] -= h.lr * wd * p[e];
-      mm = h.beta1 * mm + (1.f - h.beta1) * g;
-      vv = h.beta2 * vv + (1.f - h.beta2) * g * g;
-      p[e] -= h.lr * (mm / h.bc1) / (sqrtf(vv / h.bc2) + h.eps);
-      m[si] = mm;
-      v[si] = vv;
+    const long s0 = sg.out_off + i0;
+    if (vec && ((s0 & 3) == 0)) {
+      // 16-byte accesses to the fp32 shard arrays: a lane-per-8-elements layout read with scalar loads touches every
+      // 32-byte sector eight times
+      float g8[8], m8[8], v8[8];
+      *reinterpret_cast<float4*>(g8) = *reinterpret_cast<const float4*>(grad + s0);
+      *reinterpret_cast<float4*>(g8 + 4) = *reinterpret_cast<const float4*>(grad + s0 + 4);
+      *reinterpret_cast<float4*>(m8) = *reinterpret_cast<const float4*>(m + s0);
+      *reinterpret_cast<float4*>(m8 + 4) = *reinterpret_cast<const float4*>(m + s0 + 4);
+      *reinterpret_cast<float4*>(v8) = *reinterpret_cast<const float4*>(v + s0);
+      *reinterpret_cast<float4*>(v8 + 4) = *reinterpret_cast<const float4*>(v + s0 + 4);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        p[e] -= h.lr * wd * p[e];
+        m8[e] = h.beta1 * m8[e] + (1.f - h.beta1) * g8[e];
+        v8[e] = h.beta2 * v8[e] + (1.f - h.beta2) * g8[e] * g8[e];
+        p[e] -= h.lr * (m8[e] / h.bc1) / (sqrtf(v8[e] / h.bc2) + h.eps);
+      }
+      *reinterpret_cast<float4*>(m + s0) = *reinterpret_cast<const float4*>(m8);
+      *reinterpret_cast<float4*>(m + s0 + 4) = *reinterpret_cast<const float4*>(m8 + 4);
+      *reinterpret_cast<float4*>(v + s0) = *reinterpret_cast<const float4*>(v8);
+      *reinterpret_cast<float4*>(v + s0 + 4) = *reinterpret_cast<const float4*>(v8 + 4);
+    } else {
+      for (int e = 0; e < n; ++e) {
+        const long si = s0 + e;
+        const float g = grad[si];
+        float mm = m[si], vv = v[si];
+        p[e] -= h.lr * wd * p[e];
+        mm = h.beta1 * mm + (1.f - h.beta1) * g;
+        vv = h.beta2 * vv + (1.f - h.beta2) * g * g;
+        p[e] -= h.lr * (mm / h.bc1) / (sqrtf(vv / h.bc2) + h.eps);
+        m[si] = mm;
+        v[si] = vv;
+      }
     }
     if (vec) {
       const uint4 packed = pack8(p);
