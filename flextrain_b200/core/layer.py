@@ -229,6 +229,8 @@ class LayerContext:
     training: bool = True
     tp: Any = None                                     # TensorParallel group handle, or None
     ep: Any = None                                     # ExpertParallel group handle, or None
+    param_gather: Any = None                           # data parallel with deferred parameter all-gather: callable
+                                                       # (layer_id, x, w) -> x @ w.T or None (see parallel/dp.py)
     out: Dict[str, Any] = field(default_factory=dict)  # values a layer hands back (state gradients, ...)
 
 

@@ -185,7 +185,9 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
     # shard ("opt+grad"); "opt+grad+param" additionally keeps only 1/dp of the parameters between uses.
     modes = [shard] if shard is not None else (("opt+grad", "opt+grad+param") if dp > 1 else ("none",))
     for mode in modes:
-        p = P / dp if mode == "opt+grad+param" else P
+        # "opt+grad+param" defers the parameter all-gather to the first GEMM that uses a layer (it overlaps the forward
+        # pass instead of closing the optimizer step); the arena stays full size, so memory equals "opt+grad"
+        p = P
         # local bf16 gradients stay full-size while rounds accumulate; the reduced fp32 shard is 2x bytes / dp
         g = G + (2 * G / dp if (dp > 1 and mode != "none") else 0)
         o = O / dp if mode != "none" else O
@@ -199,7 +201,7 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
             nv += G * f                                   # reduce-scatter
             nv += (G * f) if mode == "none" else (P * f)  # all-gather grads, or updated params
             if mode == "opt+grad+param":
-                nv += 2 * P * f                           # fwd + bwd gathers
+                nv += 0.0                                 # same bytes as the eager push, moved under the forward pass
         nv_ms = hw.bytes_to_ms(nv, "nvlink")
         # ---- residency search: all resident, else offload opt → grads → params (least-touched first)
         # Host residency of model states is the single-GPU mechanism; with more than one rank the states are sharded /

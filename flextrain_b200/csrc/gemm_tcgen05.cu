@@ -52,7 +52,17 @@ struct GemmParams {
   unsigned long long* panel_counter;
   void* d_peer[MAX_RANKS];
   long d_slot_stride;
+  //  3  parameter all-gather -> GEMM (data parallel with the parameter all-gather deferred to first use): B lies in
+  //     this rank's parameter arena `a_local`; after the sharded optimizer step only rank r's element range of every
+  //     segment is current in r's arena `a_peer[r]`.  Warps 6-7 pull the other ranks' ranges of up to MAX_PULL
+  //     segments (the whole layer) into the local arena; `panel_counter[r]` counts the bytes of segment 0 (the one
+  //     that holds B) arrived from rank r, and the TMA producer waits for the ranks whose ranges a B tile touches.
+  int n_pull, tn_first;
+  long pull_off[4], pull_numel[4], pull_per[4];   // byte offset in the arena, elements, elements per rank
+  int pull_es[4];                                 // element size in bytes
+  long gate_lo;                                   // byte offset of B's first row inside segment 0
 };
+constexpr int MAX_PULL = 4;
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -180,6 +190,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           k_lo = p.offsets[g];
           k_blocks = (p.offsets[g + 1] - k_lo + BK - 1) / BK;
           if (k_blocks == 0) continue;
+        } else if constexpr (COMM == 3) {
+          tile_coords(tile, tiles_m, tiles_n, tm, tn);
+          tn = (tn + p.tn_first) % tiles_n;          // start the sweep over N at the rows this rank owns
+          row0 = tm * BM;
+          // ranks whose ranges of segment 0 this B tile touches: wait (bounded) for their bytes
+          const long rb = p.pull_per[0] * p.pull_es[0];                      // bytes per rank
+          const long lo = p.gate_lo + static_cast<long>(tn) * BN * p.K * 2;
+          const long hi = min(lo + static_cast<long>(BN) * p.K * 2, p.gate_lo + static_cast<long>(p.N) * p.K * 2);
+          for (int r = static_cast<int>(lo / rb); r <= static_cast<int>((hi - 1) / rb) && r < p.world && ok; ++r) {
+            if (r == p.rank) continue;
+            const long cnt = min(p.pull_numel[0], (r + 1) * p.pull_per[0]) - min(p.pull_numel[0], r * p.pull_per[0]);
+            const unsigned long long need = static_cast<unsigned long long>(cnt * p.pull_es[0]);
+            uint32_t it = 0;
+            while (ld_acquire_gpu_u64(p.panel_counter + r) < need) {
+              if (++it > FTB_WAIT_LIMIT || *abort_flag) { *abort_flag = 1; set_error(2, 50 + r); ok = false; break; }
+              __nanosleep(64);
+            }
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
         } else if constexpr (COMM != 0) {
           int panel;
           panel_tile_coords(tile, tiles_n, p.panel_rows, p.world, COMM == 1 ? p.rank : p.rank + 1, panel, row0, tn);
@@ -285,7 +315,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
   } else if (warp >= 6) {
-    // ------------------------------------------------------- peer-panel pull (all-gather mode only)
+    // ------------------------------------------------------- peer pulls (all-gather modes only)
+    if constexpr (COMM == 3) {
+      const int t = threadIdx.x - 192;                       // 0..63
+      const long stride = static_cast<long>(gridDim.x) * 64;
+      for (int sgi = 0; sgi < p.n_pull; ++sgi) {
+        const long es = p.pull_es[sgi];
+        for (int i = 1; i < p.world; ++i) {
+          const int r = (p.rank + i) % p.world;
+          const long beg = min(p.pull_numel[sgi], r * p.pull_per[sgi]);
+          const long cnt = min(p.pull_numel[sgi], (r + 1) * p.pull_per[sgi]) - beg;
+          if (cnt <= 0) continue;
+          const long off = p.pull_off[sgi] + beg * es;
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.a_peer[r]) + off);
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.a_local) + off);
+          const long n16 = (cnt * es) >> 4;
+          long moved = 0;
+          long idx = static_cast<long>(blockIdx.x) * 64 + t;
+          for (; idx + 3 * stride < n16; idx += 4 * stride) {   // four loads in flight per thread
+            const uint4 v0 = src[idx], v1 = src[idx + stride], v2 = src[idx + 2 * stride], v3 = src[idx + 3 * stride];
+            dst[idx] = v0; dst[idx + stride] = v1; dst[idx + 2 * stride] = v2; dst[idx + 3 * stride] = v3;
+            moved += 64;
+          }
+          for (; idx < n16; idx += stride) { dst[idx] = src[idx]; moved += 16; }
+          if (sgi == 0) {
+            asm volatile("fence.proxy.async;" ::: "memory");
+            __threadfence();
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) moved += __shfl_xor_sync(0xffffffffu, moved, o);
+            if (lane == 0 && moved) atomicAdd(p.panel_counter + r, static_cast<unsigned long long>(moved));
+          }
+        }
+      }
+    }
     if constexpr (COMM == 1) {
       const int t = threadIdx.x - 192;                       // 0..63
       const long stride = static_cast<long>(gridDim.x) * 64;
@@ -328,6 +390,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         rows = min(BM, p.M - row0);
         if ((p.offsets[g + 1] - p.offsets[g] + BK - 1) / BK == 0) continue;   // empty expert: gradient unchanged
         d_base = reinterpret_cast<char*>(p.D) + static_cast<size_t>(g) * p.M * p.ldd * (p.d_fp32 ? 4 : 2);
+      } else if constexpr (COMM == 3) {
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        tn = (tn + p.tn_first) % tiles_n;
+        row0 = tm * BM;
+        rows = min(BM, p.M - row0);
       } else if constexpr (COMM != 0) {
         int panel;
         panel_tile_coords(tile, tiles_n, p.panel_rows, p.world, COMM == 1 ? p.rank : p.rank + 1, panel, row0, tn);
@@ -1012,6 +1079,68 @@ int ftb_gemm_bf16_tp(int mode, const void* A, void* const* a_peer, unsigned long
                       : launch<128, 6, false, false, 0, 2>(ta, tb, p, grid, stream);
   }
   return -2;
+}
+
+// Parameter all-gather fused into the first GEMM that consumes the gathered weights (comm mode 3).
+//   D (M, N) = alpha * A (M, K) @ B (N, K)^T with B inside segment 0 of this rank's parameter arena `arena[rank]`.
+//   Every segment s < nseg (byte offset seg_off[s], seg_numel[s] elements of seg_es[s] bytes) is sharded over the ranks
+//   in element ranges of seg_per[s] elements; the kernel pulls the other ranks' ranges from `arena[r]` into the local
+//   arena while it computes, so on return the whole layer is current.  `counters` (world x u64, device) must be zero.
+//   Ranges must be multiples of 16 bytes.
+int ftb_gemm_bf16_wgather(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldd, float alpha,
+                          void* const* arena, int nseg, const long* seg_off, const long* seg_numel, const int* seg_es,
+                          const long* seg_per, unsigned long long* counters, int world, int rank, int max_ctas,
+                          cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || nseg < 1 || nseg > MAX_PULL) return -2;
+  if ((lda & 7) || (N & 7) || (K & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -2;
+  for (int s2 = 0; s2 < nseg; ++s2)
+    if (((seg_per[s2] * seg_es[s2]) & 15) || ((seg_numel[s2] * seg_es[s2]) & 15) || (seg_off[s2] & 15)) return -2;
+  const long gate_lo = static_cast<long>(reinterpret_cast<const char*>(B) - reinterpret_cast<const char*>(arena[rank])) -
+                       seg_off[0];
+  if (gate_lo < 0 || gate_lo + static_cast<long>(N) * K * 2 > seg_numel[0] * seg_es[0]) return -2;
+  const int bn = (N <= 128) ? 128 : 256;
+  CUtensorMap ta, tb;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {BK, BM};
+    rc = make_tmap(&ta, A, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)K * 2};
+    uint32_t box[2] = {BK, (uint32_t)bn};
+    rc = make_tmap(&tb, B, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldd; p.alpha = alpha; p.beta = 0.f;
+  p.D = D; p.C = D; p.bias = nullptr; p.d_fp32 = 0;
+  p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
+  p.comm_mode = 3; p.world = world; p.rank = rank; p.panel_rows = 0;
+  p.a_local = arena[rank]; p.panel_bytes = 0; p.panel_counter = counters; p.d_slot_stride = 0;
+  for (int i = 0; i < MAX_RANKS; ++i) { p.a_peer[i] = i < world ? arena[i] : nullptr; p.d_peer[i] = nullptr; }
+  p.n_pull = nseg;
+  for (int s2 = 0; s2 < MAX_PULL; ++s2) {
+    p.pull_off[s2] = s2 < nseg ? seg_off[s2] : 0; p.pull_numel[s2] = s2 < nseg ? seg_numel[s2] : 0;
+    p.pull_per[s2] = s2 < nseg ? seg_per[s2] : 1; p.pull_es[s2] = s2 < nseg ? seg_es[s2] : 2;
+  }
+  p.gate_lo = gate_lo;
+  const int tiles_n = (N + bn - 1) / bn;
+  const long my_lo = min(seg_numel[0], rank * seg_per[0]) * seg_es[0];        // first byte of my range in segment 0
+  long first = (my_lo - gate_lo) / (static_cast<long>(bn) * K * 2);
+  if (my_lo <= gate_lo) first = 0;
+  p.tn_first = static_cast<int>(first >= tiles_n ? 0 : first);
+  const int tiles = ((M + BM - 1) / BM) * tiles_n;
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = tiles;
+  if (bn == 256) return launch<256, 4, false, false, 0, 3>(ta, tb, p, grid, stream);
+  return launch<128, 6, false, false, 0, 3>(ta, tb, p, grid, stream);
 }
 
 // Reads and clears the library's device error word: returns code * 1000 + where (0 = no error).

@@ -139,7 +139,8 @@ class ActiveModel:
                         self._zero_all_grads()
                         self._zero_grad = False
                     ctx_base = dict(kv_window=self.buffers.kv_window, total_tokens_per_step=total_tokens_per_step,
-                                    tp=self.tp, ep=self.ep)
+                                    tp=self.tp, ep=self.ep,
+                                    param_gather=(self.dp.first_gemm if getattr(self.dp, "defer", False) else None))
                     with _nvtx("Setup Round"):
                         transitions, slots = self._setup_round(metas)
                     with _nvtx("Forward"):

@@ -152,6 +152,8 @@ def collect_hf_state(am, lora_merge: bool = False) -> Dict[str, torch.Tensor]:
     spec: ArchSpec = select_arch_module(mc.arch).ARCH_SPEC
     bm = am.buffers
     out: Dict[str, torch.Tensor] = {}
+    if getattr(am, "dp", None) is not None and hasattr(am.dp, "finish_param_gather"):
+        am.dp.finish_param_gather()         # deferred parameter all-gather: make every rank's copy current first
 
     def emit(entries: List[WeightMapEntry], params: Dict[str, torch.Tensor], specs=None):
         for e in entries:

@@ -104,10 +104,14 @@ class GQAAttentionBlock:
             self.inv_freq_cache[key] = self.cfg.rope.inv_freq(self.cfg.head_dim).to(device)
         return self.inv_freq_cache[key]
 
-    def _project_qkv(self, h, params):
-        """QKV projection (one GEMM) -> pre-norm, pre-RoPE ``(q, gate, k, v)`` views of one buffer."""
+    def _project_qkv(self, h, params, qkv=None):
+        """QKV projection (one GEMM) -> pre-norm, pre-RoPE ``(q, gate, k, v)`` views of one buffer.  ``qkv`` may carry
+        a projection that was already computed (without bias) by a fused gather-GEMM."""
         c = self.cfg
-        qkv = self.qkv.fwd(h, params)
+        if qkv is None:
+            qkv = self.qkv.fwd(h, params)
+        elif self.qkv.bias_names:
+            qkv += self.qkv.bias(params).to(qkv.dtype)
         T = qkv.shape[0]                 # all tokens of the chunk (h holds T/tp of them under tensor parallelism)
         if c.gated:
             # w_q rows are per-head [query(hd) ‖ gate(hd)] (HF Qwen3-Next layout)
@@ -134,10 +138,10 @@ class GQAAttentionBlock:
             qn, kn = qn.view(T, c.n_heads, c.head_dim), kn.view(T, c.n_kv_heads, c.head_dim)
         return qn, qr, kn, kr
 
-    def _qkv_post(self, h, meta: ChunkMeta, params, slot, *, want_q=True):
+    def _qkv_post(self, h, meta: ChunkMeta, params, slot, *, want_q=True, qkv=None):
         """Compute post-norm, post-RoPE q / k / v (+gate) from the normed input and store them in the slot."""
         c = self.cfg
-        q, gate, k, v = self._project_qkv(h, params)
+        q, gate, k, v = self._project_qkv(h, params, qkv)
         if c.qk_norm:
             q, qr, k, kr = self._qk_norm_fwd(q, k, params)
             slot.put("q_rstd", qr)
@@ -173,10 +177,10 @@ class GQAAttentionBlock:
                                  scale=self.scale, causal=c.causal, window=c.window, softcap=c.softcap)
 
     # --------------------------------------------------------------------- forward
-    def fwd(self, h, x_resid, meta: ChunkMeta, params, slot, ctx: LayerContext) -> torch.Tensor:
+    def fwd(self, h, x_resid, meta: ChunkMeta, params, slot, ctx: LayerContext, qkv=None) -> torch.Tensor:
         """``h`` = normed input, ``x_resid`` = residual stream. Returns ``x_resid + attn(h) @ w_o.T``."""
         c = self.cfg
-        xq, xk, xv = self._qkv_post(h, meta, params, slot)
+        xq, xk, xv = self._qkv_post(h, meta, params, slot, qkv=qkv)
         K, V = self._kv_for_attention(meta, xk, xv, ctx, write=True)
         out, lse = self._attend(xq, K, V, meta)
         out2 = out.reshape(out.shape[0], c.q_dim)

@@ -120,7 +120,11 @@ class DecoderLayer:
     # --------------------------------------------------------------------- forward
     def _mixer_fwd(self, h1, resid, meta, params, slot, ctx):
         if self.attn is not None:
-            return self.attn.fwd(h1, resid, meta, params, slot, ctx)
+            qkv = None
+            if ctx.param_gather is not None:
+                # first use of this layer's weights in the step: the QKV projection also gathers the layer's parameters
+                qkv = ctx.param_gather(self.layer_id, h1, self.attn.qkv.weight(params))
+            return self.attn.fwd(h1, resid, meta, params, slot, ctx, qkv=qkv)
         return self.gdn.fwd(h1, resid, meta, params, slot, ctx)
 
     def _ffn_fwd(self, h2, resid, params, slot, ctx):

@@ -11,6 +11,11 @@ overlaps the backward of layer l-1.  ``step()`` then runs the sharded AdamW kern
 writes the new bf16 parameters into every rank's parameter arena (the all-gather is fused into the
 optimizer), and closes with one flag barrier.  No NCCL call is made on this path.
 
+With ``shard="opt+grad+param"`` the parameter all-gather of the large (bf16) segments of attention layers is
+deferred: the optimizer writes only the rank's own range, and the FIRST GEMM that consumes the layer's weights in the
+next forward (the QKV projection) pulls the other ranks' ranges of the whole layer out of peer memory while it computes
+(``ftb_gemm_bf16_wgather``, comm mode 3 of the tcgen05 GEMM), gating each weight tile on the arrival of its bytes.
+
 ``CollectiveDataParallel`` (the baseline, any backend incl. gloo on CPU):  ``all_reduce`` of each
 layer's gradients, then the ordinary local optimizer on replicated state.
 
@@ -160,6 +165,18 @@ class P2PDataParallel(_Base):
                 self.local_state[key] = {
                     s.key: torch.zeros(s.shape, dtype=torch.float32, device=self.device)
                     for s in am.optimizer.state_specs(lbs[key].spec) if s.param in names}
+        # deferred parameter all-gather ("opt+grad+param"): bf16 segments of attention layers are gathered by the
+        # layer's first GEMM; everything else (norm weights, embedding, head, other layer kinds) is pushed eagerly
+        self.defer = getattr(am.ws, "shard", "") == "opt+grad+param"
+        self.deferred_keys = set()
+        if self.defer:
+            for i, layer in enumerate(am.layers):
+                big = [s for s in self.units[i] if s.p_dtype == torch.bfloat16]
+                if getattr(layer, "attn", None) is not None and getattr(layer.cfg, "lora", None) is None \
+                        and 1 <= len(big) <= 4 and all((s.numel * 2) % 16 == 0 for s in big):
+                    self.deferred_keys.add(i)
+        self._stale = set()
+        self._gather_counter = torch.zeros(8, dtype=torch.int64, device=self.device)
         self.slot = {k: i for i, k in enumerate(keys)}
         self.barrier_slot = len(keys)
         self.comm_stream = am.streams.comm
@@ -218,20 +235,28 @@ class P2PDataParallel(_Base):
         bm = am.buffers
         step = am.step_num
         bc1, bc2 = 1.0 - opt.beta1 ** step, 1.0 - opt.beta2 ** step
+        own_only = (c_void_p * 1)(bm.param_arena.c_ptrs[self.rank])       # a one-rank "group": no peer stores
         for key, segs in self.units.items():
-            for i0 in range(0, len(segs), 16):
-                part = segs[i0:i0 + 16]
-                n, boff, beg, cnt, ooff, dts = self._tables(part, "param")
-                mask = sum((1 << i) for i, s in enumerate(part) if s.decay)
-                rc = self.lib.ftb_comm_adamw_push(bm.param_arena.c_ptrs, c_int(n), boff, beg, cnt, ooff, dts,
-                                                  c_void_p(self.grad_shard.data_ptr()), c_void_p(self.m.data_ptr()),
-                                                  c_void_p(self.v.data_ptr()), c_int(self.world), c_int(self.rank),
-                                                  c_float(opt.lr), c_float(opt.beta1), c_float(opt.beta2),
-                                                  c_float(opt.eps), c_float(opt.weight_decay), c_float(bc1),
-                                                  c_float(bc2), c_uint(mask), c_void_p(cs.cuda_stream))
-                if rc != 0:
-                    raise RuntimeError(f"ftb_comm_adamw_push failed ({rc})")
-                ops._count()
+            deferred = key in self.deferred_keys
+            groups = [([s for s in segs if not (deferred and s.p_dtype == torch.bfloat16)], False),
+                      ([s for s in segs if deferred and s.p_dtype == torch.bfloat16], True)]
+            for glist, local in groups:
+                for i0 in range(0, len(glist), 16):
+                    part = glist[i0:i0 + 16]
+                    n, boff, beg, cnt, ooff, dts = self._tables(part, "param")
+                    mask = sum((1 << i) for i, s in enumerate(part) if s.decay)
+                    rc = self.lib.ftb_comm_adamw_push(own_only if local else bm.param_arena.c_ptrs, c_int(n), boff, beg,
+                                                      cnt, ooff, dts, c_void_p(self.grad_shard.data_ptr()),
+                                                      c_void_p(self.m.data_ptr()), c_void_p(self.v.data_ptr()),
+                                                      c_int(1 if local else self.world), c_int(0 if local else self.rank),
+                                                      c_float(opt.lr), c_float(opt.beta1), c_float(opt.beta2),
+                                                      c_float(opt.eps), c_float(opt.weight_decay), c_float(bc1),
+                                                      c_float(bc2), c_uint(mask), c_void_p(cs.cuda_stream))
+                    if rc != 0:
+                        raise RuntimeError(f"ftb_comm_adamw_push failed ({rc})")
+                    ops._count()
+            if deferred:
+                self._stale.add(key)
         if self.local_names:
             cs.wait_stream(am.streams.compute)
             with torch.cuda.stream(cs):
@@ -242,6 +267,63 @@ class P2PDataParallel(_Base):
         self.group.signal_wait(self.barrier_slot, self.group.next_epoch(), cs)
         am.streams.compute.wait_stream(cs)
         return 0
+
+    def first_gemm(self, layer: int, x: torch.Tensor, w: torch.Tensor):
+        """``x @ w.T`` for the first projection of ``layer`` in a step, fused with the all-gather of the layer's
+        deferred parameter segments (peer pulls inside the GEMM kernel).  Returns ``None`` when the layer's parameters
+        are already current (later rounds of the step, recompute, layers that are pushed eagerly)."""
+        if layer not in self._stale:
+            return None
+        from .. import ops
+        from ..ops.cuda import load, _stream
+        bm = self.am.buffers
+        segs = [s for s in self.units[layer] if s.p_dtype == torch.bfloat16]
+        base = bm.param_arena.ptrs[self.rank]
+        rel = w.data_ptr() - base
+        first = [s for s in segs if s.p_off <= rel and rel + w.numel() * 2 <= s.p_off + s.numel * 2]
+        if not first or x.dtype != torch.bfloat16 or not w.is_contiguous() or x.stride(1) != 1:
+            raise RuntimeError("deferred parameter gather: the first projection's weight is not inside one bf16 segment")
+        order = first + [s for s in segs if s is not first[0]]
+        n = len(order)
+        W = self.world
+        per = lambda s: (s.numel + 8 * W - 1) // (8 * W) * 8
+        arr = lambda vals, ct=c_long: (ct * n)(*vals)
+        self._gather_counter.zero_()
+        M, K = x.shape
+        N = w.shape[0]
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        rc = load("gemm_tcgen05").ftb_gemm_bf16_wgather(
+            c_void_p(x.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
+            c_int(x.stride(0)), c_int(N), c_float(1.0), bm.param_arena.c_ptrs, c_int(n),
+            arr([s.p_off for s in order]), arr([s.numel for s in order]), arr([2] * n, c_int),
+            arr([per(s) for s in order]), c_void_p(self._gather_counter.data_ptr()), c_int(W), c_int(self.rank),
+            c_int(0), _stream())
+        if rc != 0:
+            raise RuntimeError(f"ftb_gemm_bf16_wgather failed ({rc})")
+        ops._count()
+        self._stale.discard(layer)
+        return out
+
+    def finish_param_gather(self) -> None:
+        """Complete the deferred all-gather of every layer that has not run a forward since the last optimizer step
+        (before exporting, evaluating a single rank's copy, or comparing ranks): each rank pushes its own ranges."""
+        if not self._stale:
+            return
+        bm = self.am.buffers
+        cs = self.comm_stream
+        cs.wait_stream(self.am.streams.compute)
+        for key in sorted(self._stale):
+            for s in self.units[key]:
+                if s.p_dtype != torch.bfloat16 or s.count == 0:
+                    continue
+                rc = self.lib.ftb_comm_allgather_push(bm.param_arena.c_ptrs, c_long(s.p_off + s.begin * 2),
+                                                      c_long(s.count * 2), c_int(self.world), c_int(self.rank),
+                                                      c_void_p(cs.cuda_stream))
+                if rc != 0:
+                    raise RuntimeError(f"ftb_comm_allgather_push failed ({rc})")
+        self.group.signal_wait(self.barrier_slot, self.group.next_epoch(), cs)
+        self.am.streams.compute.wait_stream(cs)
+        self._stale.clear()
 
     def check(self) -> None:
         self.group.check()

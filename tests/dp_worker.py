@@ -12,6 +12,9 @@ import flextrain_b200 as ft  # noqa: E402
 
 def main():
     backend, out_path = sys.argv[1], sys.argv[2]
+    shard = "opt+grad"
+    if backend == "p2p_param":              # peer-memory path with the parameter all-gather deferred into the QKV GEMM
+        backend, shard = "p2p", "opt+grad+param"
     os.environ["FTB_DP_BACKEND"] = backend
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -25,7 +28,7 @@ def main():
                       max_host_mem_bytes=16 << 30, device=dev, world_size=world, rank=rank,
                       working_set=ft.WorkingSetConfig.simple(max_seq_len=256, max_global_batch_tokens=gb // world,
                                                              chunk=1024, round_tokens=1024, world_size=world,
-                                                             shard="opt+grad"))
+                                                             shard=shard))
     src = ft.SyntheticTokenSource(2048, 256, seed=11)
     losses = []
     for step in range(3):
@@ -35,6 +38,11 @@ def main():
         t = torch.tensor([st.loss_sum], device=dev)
         dist.all_reduce(t)
         losses.append(float(t) / gb)
+    if hasattr(am.dp, "finish_param_gather"):
+        deferred = sorted(am.dp._stale)
+        am.dp.finish_param_gather()
+    else:
+        deferred = []
     torch.cuda.synchronize()
     if hasattr(am.dp, "check"):
         am.dp.check()
@@ -45,7 +53,7 @@ def main():
         same = all(torch.equal(allflat[0], f) for f in allflat)
         from flextrain_b200.ops import cuda as k
         torch.save({"params": flat, "losses": losses, "ranks_identical": same, "errors": k.device_error_words(),
-                    "libs": sorted(k._libs)}, out_path)
+                    "libs": sorted(k._libs), "deferred_layers": deferred}, out_path)
     dist.barrier()
     dist.destroy_process_group()
 
