@@ -8,6 +8,7 @@ max over ranks, 3 warm-up + 10 timed calls each):
 
   dp_reduce_scatter   fused gradient reduce-scatter + bf16->fp32 cast/scale over peer memory   vs  NCCL reduce_scatter + cast
   dp_adamw_push       sharded AdamW whose stores are the parameter all-gather                  vs  local AdamW + NCCL all_gather
+  dp_param_gather_gemm parameter all-gather of a layer fused into its QKV projection            vs  NCCL all_gather x2 + GEMM
   tp_ag_gemm          all-gather -> GEMM in one kernel                                          vs  NCCL all_gather + GEMM
   tp_gemm_rs          GEMM -> reduce-scatter (peer-store epilogue + slot sum)                   vs  GEMM + NCCL reduce_scatter
   ep_dispatch         MoE token dispatch (peer stores into the owners' expert-major buffers)    vs  NCCL all_to_all (equal splits)
@@ -136,6 +137,44 @@ def main() -> None:
     link = (world - 1) * Tl * K * 2
     record("tp_ag_gemm", timeit(lambda: tp.ag_gemm(x, w)), timeit(lambda: base.ag_gemm(x, w)), fl, link)
     record("tp_gemm_rs", timeit(lambda: tp.gemm_rs(xa, w2)), timeit(lambda: base.gemm_rs(xa, w2)), fl, link)
+
+    # ------------------------------------------------------------------ (b) parameter all-gather -> first GEMM
+    # Llama-3.1-8B layer: the QKV projection (6144 x 4096) sits at the start of the 10240 x 4096 [q|k|v|o] segment; the
+    # kernel also gathers the FFN segment (3 x 14336 x 4096) of the layer while it computes.
+    from flextrain_b200.ops.cuda import load as _load
+    gl = _load("gemm_tcgen05")
+    Kd, Nq, n0, n1 = 4096, 6144, 10240 * 4096, 3 * 14336 * 4096
+    arena = group.alloc((n0 + n1) * 2)
+    arena.local.view(torch.bfloat16)[: n0 + n1].normal_(0, 0.02)
+    xq = (torch.randn(16384, Kd, device=dev) * 0.5).to(torch.bfloat16)
+    wq = arena.local.view(torch.bfloat16)[: Nq * Kd].view(Nq, Kd)
+    outq = torch.empty(16384, Nq, dtype=torch.bfloat16, device=dev)
+    cnt8 = torch.zeros(8, dtype=torch.int64, device=dev)
+    per_ = lambda nel: (nel + 8 * world - 1) // (8 * world) * 8
+    arr2 = lambda vals, ct=c_long: (ct * 2)(*vals)
+
+    def fused_wgather():
+        group.signal_wait(120 + slot[0] % 8, group.next_epoch()); slot[0] += 1      # everyone's ranges are final
+        cnt8.zero_()
+        rc = gl.ftb_gemm_bf16_wgather(c_void_p(xq.data_ptr()), c_void_p(wq.data_ptr()), c_void_p(outq.data_ptr()),
+                                      c_int(16384), c_int(Nq), c_int(Kd), c_int(Kd), c_int(Nq), c_float(1.0),
+                                      arena.c_ptrs, c_int(2), arr2([0, n0 * 2]), arr2([n0, n1]), arr2([2, 2], c_int),
+                                      arr2([per_(n0), per_(n1)]), c_void_p(cnt8.data_ptr()), c_int(world), c_int(rank),
+                                      c_int(0), stream())
+        assert rc == 0, rc
+
+    flat = arena.local.view(torch.bfloat16)[: n0 + n1]
+    sh0, sh1 = flat[:n0][rank * per_(n0):(rank + 1) * per_(n0)].clone(), flat[n0:][rank * per_(n1):(rank + 1) * per_(n1)].clone()
+    full0 = torch.empty(world * sh0.numel(), dtype=torch.bfloat16, device=dev)
+    full1 = torch.empty(world * sh1.numel(), dtype=torch.bfloat16, device=dev)
+
+    def nccl_wgather():
+        dist.all_gather_into_tensor(full0, sh0)
+        dist.all_gather_into_tensor(full1, sh1)
+        ops.gemm(xq, full0[: Nq * Kd].view(Nq, Kd), trans_b=True, out=outq)
+
+    record("dp_param_gather_gemm", timeit(fused_wgather), timeit(nccl_wgather), 2.0 * 16384 * Nq * Kd,
+           (n0 + n1) * 2 * (world - 1) / world)
 
     # ------------------------------------------------------------------ (d) expert-parallel dispatch / combine
     T, Kt, D, E = 16384, 8, 2048, 128
