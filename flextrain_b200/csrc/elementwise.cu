@@ -132,18 +132,39 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const bf16* __r
 #pragma unroll
     for (int e = 0; e < 8; ++e) dwacc[j][e] = 0.f;
 
+  // The next row's operands are requested before the current row's block-wide reduction, so its DRAM latency hides
+  // behind the two barriers and the arithmetic of this row (the kernel is latency-bound otherwise: one row in flight
+  // per CTA).
+  uint4 nx[MAXV], ng[MAXV], na[MAXV];
+  float nr = 0.f;
+  auto prefetch = [&](int rw) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)rw * D);
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + (size_t)rw * D);
+    nr = rstd[rw];
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int i = threadIdx.x + j * RN_THREADS;
+      if (i < nv) {
+        nx[j] = xr[i];
+        ng[j] = dyr[i];
+        if (dx_add) na[j] = reinterpret_cast<const uint4*>(dx_add + (size_t)rw * D)[i];
+      }
+    }
+  };
+  constexpr bool AHEAD = MAXV <= 2;          // wider rows would halve the CTAs per SM with two rows in registers
+  if (AHEAD && blockIdx.x < T) prefetch(blockIdx.x);
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
-    const uint4* dyr = reinterpret_cast<const uint4*>(dy + (size_t)row * D);
-    const float r = rstd[row];
-    uint4 xv[MAXV], gv[MAXV];
+    if (!AHEAD) prefetch(row);
+    const float r = nr;
+    uint4 xv[MAXV], gv[MAXV], av[MAXV];
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) { xv[j] = nx[j]; gv[j] = ng[j]; av[j] = na[j]; }
+    if (AHEAD && row + (int)gridDim.x < T) prefetch(row + gridDim.x);
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
       const int i = threadIdx.x + j * RN_THREADS;
       if (i < nv) {
-        xv[j] = xr[i];
-        gv[j] = dyr[i];
         float xf[8], gf[8], wf[8];
         unpack8(xv[j], xf);
         unpack8(gv[j], gf);
@@ -184,8 +205,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const bf16* __r
         for (int e = 0; e < 8; ++e) o[e] = (gf[e] * wf[e] - xf[e] * r * dot) * r;
         if (dx_add) {
           float a[8];
-          const uint4 av = reinterpret_cast<const uint4*>(dx_add + (size_t)row * D)[i];
-          unpack8(av, a);
+          unpack8(av[j], a);
 #pragma unroll
           for (int e = 0; e < 8; ++e) o[e] += a[e];
         }
