@@ -59,6 +59,27 @@ __device__ __forceinline__ float half_warp_sum(float x) {   // over the 16 lanes
   return x;
 }
 
+// Four per-column partial sums reduced over the 16 lanes of a half warp in 5 shuffles instead of 16: each exchange
+// halves the number of columns a lane is responsible for (reduce-scatter), so after the xor-8 and xor-4 steps a lane
+// carries one column, c = 2 * bit3(lane) + bit2(lane), and the xor-2 / xor-1 steps finish its sum.
+__device__ __forceinline__ float reduce_scatter4(float p0, float p1, float p2, float p3, int lane) {
+  const bool hi8 = lane & 8;
+  float k0 = hi8 ? p2 : p0, k1 = hi8 ? p3 : p1;
+  k0 += __shfl_xor_sync(0xffffffffu, hi8 ? p0 : p2, 8);
+  k1 += __shfl_xor_sync(0xffffffffu, hi8 ? p1 : p3, 8);
+  const bool hi4 = lane & 4;
+  float k = hi4 ? k1 : k0;
+  k += __shfl_xor_sync(0xffffffffu, hi4 ? k0 : k1, 4);
+  k += __shfl_xor_sync(0xffffffffu, k, 2);
+  k += __shfl_xor_sync(0xffffffffu, k, 1);
+  return k;
+}
+// ... and handed back to every lane of the half warp (4 more shuffles).
+__device__ __forceinline__ void all_gather4(float k, int lane, float (&out)[4]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) out[c] = __shfl_sync(0xffffffffu, k, (lane & 0x13) | (c << 2));
+}
+
 // Sum over the lanes that hold one token's DK consecutive elements (DK lanes for DK = 16, the whole warp otherwise).
 template <int DK>
 __device__ __forceinline__ float segment_sum(float x) {
@@ -114,12 +135,21 @@ __global__ void __launch_bounds__(NT) gdn_forward_kernel(const GdnArgs a) {
       float kr[RPT], qr[RPT], rj[CPT];
 #pragma unroll
       for (int rr = 0; rr < RPT; ++rr) { kr[rr] = k_s[t][ti + 16 * rr]; qr[rr] = q_s[t][ti + 16 * rr]; }
+      {
+        float pp[CPT];
 #pragma unroll
-      for (int cc = 0; cc < CPT; ++cc) {
-        float p = 0.f;
+        for (int cc = 0; cc < CPT; ++cc) {
+          float p = 0.f;
 #pragma unroll
-        for (int rr = 0; rr < RPT; ++rr) { S[rr][cc] *= at; p += kr[rr] * S[rr][cc]; }
-        rj[cc] = half_warp_sum(p);
+          for (int rr = 0; rr < RPT; ++rr) { S[rr][cc] *= at; p += kr[rr] * S[rr][cc]; }
+          pp[cc] = p;
+        }
+        if constexpr (CPT == 4) {
+          all_gather4(reduce_scatter4(pp[0], pp[1], pp[2], pp[3], tid & 31), tid & 31, rj);
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < CPT; ++cc) rj[cc] = half_warp_sum(pp[cc]);
+        }
       }
       if (MODE == 1) {   // dk += S^ dr  with dr = -beta de   (S holds S^ here)
 #pragma unroll
@@ -138,16 +168,31 @@ __global__ void __launch_bounds__(NT) gdn_forward_kernel(const GdnArgs a) {
         for (int rr = 0; rr < RPT; ++rr) S[rr][cc] += kr[rr] * e;
       }
       if (MODE == 0) {
+        float pp[CPT];
 #pragma unroll
         for (int cc = 0; cc < CPT; ++cc) {
           float p = 0.f;
 #pragma unroll
           for (int rr = 0; rr < RPT; ++rr) p += qr[rr] * S[rr][cc];
-          p = half_warp_sum(p);
-          if (ti == 0) {
+          pp[cc] = p;
+        }
+        if constexpr (CPT == 4) {
+          const float tot = reduce_scatter4(pp[0], pp[1], pp[2], pp[3], tid & 31);
+          if ((ti & 3) == 0) {                     // lanes 0, 4, 8, 12 of the half warp hold columns 0..3
+            const int cc = ti >> 2;
             const size_t off = ((size_t)(tb + t) * a.HV + hv) * a.DV + col0 + tj * CPT + cc;
-            a.o[off] = __float2bfloat16(p);
+            a.o[off] = __float2bfloat16(tot);
             if (a.r) a.r[off] = rj[cc];
+          }
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < CPT; ++cc) {
+            const float p = half_warp_sum(pp[cc]);
+            if (ti == 0) {
+              const size_t off = ((size_t)(tb + t) * a.HV + hv) * a.DV + col0 + tj * CPT + cc;
+              a.o[off] = __float2bfloat16(p);
+              if (a.r) a.r[off] = rj[cc];
+            }
           }
         }
       } else {            // dq = scale S_t dO
@@ -243,13 +288,25 @@ __global__ void __launch_bounds__(NT) gdn_reverse_kernel(const GdnArgs a) {
 #pragma unroll
       for (int rr = 0; rr < RPT; ++rr) { kr[rr] = k_s[t][ti + 16 * rr]; qr[rr] = q_s[t][ti + 16 * rr]; }
       float db = 0.f;
+      {
+        float pp[CPT];
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          const float dO = x_s[t][tj * CPT + cc];
+          float p = 0.f;
+#pragma unroll
+          for (int rr = 0; rr < RPT; ++rr) { dS[rr][cc] += qr[rr] * dO; p += kr[rr] * dS[rr][cc]; }
+          pp[cc] = p;
+        }
+        if constexpr (CPT == 4) {
+          all_gather4(reduce_scatter4(pp[0], pp[1], pp[2], pp[3], tid & 31), tid & 31, de);
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < CPT; ++cc) de[cc] = half_warp_sum(pp[cc]);
+        }
+      }
 #pragma unroll
       for (int cc = 0; cc < CPT; ++cc) {
-        const float dO = x_s[t][tj * CPT + cc];
-        float p = 0.f;
-#pragma unroll
-        for (int rr = 0; rr < RPT; ++rr) { dS[rr][cc] += qr[rr] * dO; p += kr[rr] * dS[rr][cc]; }
-        de[cc] = half_warp_sum(p);
         const float diff = v_s[t][tj * CPT + cc] - r_s[t][tj * CPT + cc];
         ej[cc] = bt * diff;
         db += de[cc] * diff;
@@ -319,13 +376,22 @@ int launch_all(int pass, const GdnArgs& a, int nseq, cudaStream_t s) {
 
 // Column block per CTA: 32 columns when that already gives two CTAs per SM, otherwise 16 or 8 so that one long
 // sequence still spreads over the whole GPU (the recurrence is latency-bound per CTA).
+int cols_per_thread(int nseq, int HV, int DV) {
+  const long heads = (long)nseq * HV;
+  if (DV % 32 == 0 && heads * (DV / 32) >= 296) return 4;
+  if (DV % 16 == 0 && heads * (DV / 16) >= 296) return 2;
+  if (DV % 8 == 0) return 1;
+  return 0;
+}
+
 template <int RPT>
 int launch_cols(int pass, const GdnArgs& a, int nseq, cudaStream_t s) {
-  const long heads = (long)nseq * a.HV;
-  if (a.DV % 32 == 0 && heads * (a.DV / 32) >= 296) return launch_all<RPT, 4>(pass, a, nseq, s);
-  if (a.DV % 16 == 0 && heads * (a.DV / 16) >= 296) return launch_all<RPT, 2>(pass, a, nseq, s);
-  if (a.DV % 8 == 0) return launch_all<RPT, 1>(pass, a, nseq, s);
-  return -2;
+  switch (cols_per_thread(nseq, a.HV, a.DV)) {
+    case 4: return launch_all<RPT, 4>(pass, a, nseq, s);
+    case 2: return launch_all<RPT, 2>(pass, a, nseq, s);
+    case 1: return launch_all<RPT, 1>(pass, a, nseq, s);
+    default: return -2;
+  }
 }
 
 }  // namespace
@@ -333,6 +399,12 @@ int launch_cols(int pass, const GdnArgs& a, int nseq, cudaStream_t s) {
 extern "C" {
 
 // pass: 0 forward, 1 backward reverse pass, 2 backward forward-direction pass.  DK in {16, 32, 64, 128}, DV % 8 == 0.
+// Number of column blocks (CTAs per head) the kernels will use: the leading dimension of the dq / dk partial buffers.
+int ftb_gdn_col_blocks(int nseq, int HV, int DV) {
+  const int cpt = cols_per_thread(nseq, HV, DV);
+  return cpt ? DV / (8 * cpt) : 0;
+}
+
 int ftb_gdn(int pass, const void* q, const void* k, const void* v, const float* g, const float* beta, const int* cu,
             int nseq, const float* state_in, float* state_out, void* o, float* r, const void* d_o, float* de, void* dv,
             float* dbeta, float* dq, float* dk, float* sacc, int HK, int HV, int DK, int DV, float scale,
