@@ -332,10 +332,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const long n16 = (cnt * es) >> 4;
           long moved = 0;
           long idx = static_cast<long>(blockIdx.x) * 64 + t;
-          for (; idx + 3 * stride < n16; idx += 4 * stride) {   // four loads in flight per thread
-            const uint4 v0 = src[idx], v1 = src[idx + stride], v2 = src[idx + 2 * stride], v3 = src[idx + 3 * stride];
-            dst[idx] = v0; dst[idx + stride] = v1; dst[idx + 2 * stride] = v2; dst[idx + 3 * stride] = v3;
-            moved += 64;
+          for (; idx + 7 * stride < n16; idx += 8 * stride) {   // eight loads in flight per thread
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = src[idx + u * stride];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) dst[idx + u * stride] = v[u];
+            moved += 128;
           }
           for (; idx < n16; idx += stride) { dst[idx] = src[idx]; moved += 16; }
           if (sgi == 0) {
@@ -358,10 +361,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.a_local) + pn * p.panel_bytes);
         long moved = 0;
         long idx = static_cast<long>(blockIdx.x) * 64 + t;
-        for (; idx + 3 * stride < n16; idx += 4 * stride) {   // four loads in flight per thread
-          const uint4 v0 = src[idx], v1 = src[idx + stride], v2 = src[idx + 2 * stride], v3 = src[idx + 3 * stride];
-          dst[idx] = v0; dst[idx + stride] = v1; dst[idx + 2 * stride] = v2; dst[idx + 3 * stride] = v3;
-          moved += 64;
+        for (; idx + 7 * stride < n16; idx += 8 * stride) {   // eight loads in flight per thread
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = src[idx + u * stride];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) dst[idx + u * stride] = v[u];
+          moved += 128;
         }
         for (; idx < n16; idx += stride) { dst[idx] = src[idx]; moved += 16; }
         asm volatile("fence.proxy.async;" ::: "memory");
