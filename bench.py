@@ -365,7 +365,7 @@ def run_reference(args):
                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                "scaling": "strong", "vs_baseline": value / PUBLISHED_TOK_S, "dtype": "bf16",
                "data": "synthetic uniform tokens, random-init weights",
-               "config": {"model": cfg["model"] + (" (SMALL DEBUG)" if args.small else ""), "global_batch": gbatch,
+               "config": {"model": "Llama-3.1-8B" + (" (SMALL DEBUG)" if args.small else ""), "global_batch": gbatch,
                           "seq_len": seq_len,
                           "parallelism": f"dp{world}" + (" (constructed: one reference engine per GPU + NCCL "
                                                          "all-reduce of host gradients)" if world > 1 else "")},
