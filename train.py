@@ -82,6 +82,9 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--verbose", action="store_true")
     # parallel layout (new): ranks come from torch.distributed.run
     p.add_argument("--dp-shard", default=None, choices=["opt+grad", "opt+grad+param"])
+    p.add_argument("--heartbeat-s", type=float, default=0.0,
+                   help="multi-rank runs: raise on every rank when a peer has not finished a step for this many "
+                        "seconds or has left (0 = off)")
     p.add_argument("--tp", type=int, default=1)
     p.add_argument("--ep", type=int, default=1)
     return p
@@ -199,7 +202,16 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
     ws = am.ws
     ema, t_start, tok_total = None, time.time(), 0
     profiling = False
+    hb = None
+    if world > 1 and getattr(args, "heartbeat_s", 0) > 0:
+        # ranks learn of a lost peer on the host, between steps, instead of inside a kernel's bounded wait
+        import torch.distributed as dist
+        from flextrain_b200.parallel.health import Heartbeat
+        hb = Heartbeat(dist.distributed_c10d._get_default_store(), dist.get_rank(), world, stale_s=args.heartbeat_s)
+        hb.beat(0)
     for step in range(1, total + 1):
+        if hb is not None:
+            hb.check(grace_s=args.heartbeat_s)
         am.optimizer.lr = lr_schedule(step, max_lr=max_lr, final_lr=final_lr, warmup_steps=warm, cooldown_start=cool,
                                       total_steps=total)
         seqs = src.get_sequences(per_rank_tokens)
@@ -232,6 +244,8 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
         if torch.cuda.is_available():
             torch.cuda.synchronize()
         dt = time.time() - t0
+        if hb is not None:
+            hb.beat(step)
         stop = args.profile_stop_step if args.profile_stop_step is not None else (
             args.profile_start_step + 2 if args.profile_start_step is not None else None)
         if profiling and stop is not None and step == stop:
