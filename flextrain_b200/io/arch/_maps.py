@@ -65,6 +65,8 @@ def moe_entries(i: int, mc, *, prefix="model.", router="mlp.gate", experts="mlp.
         down_names.append(f"{p}{experts}.{e}.down_proj.weight")
 
     def comb_up(ts):       # (E, 2F, d) with the 2F axis [up ‖ gate]
+        if len(ts) == 1:   # stacked checkpoint (transformers >= 5 writes experts.gate_up_proj as [gate ‖ up])
+            return torch.cat([ts[0][:, F:], ts[0][:, :F]], 1)
         return torch.stack([torch.cat([ts[2 * e], ts[2 * e + 1]], 0) for e in range(n)], 0)
 
     def split_up(t):
@@ -74,8 +76,9 @@ def moe_entries(i: int, mc, *, prefix="model.", router="mlp.gate", experts="mlp.
         return out
 
     out = [E("w_router", [f"{p}{router}.weight"]),
-           E("w_up", up_names, combine=comb_up, split=split_up),
-           E("w_down", down_names, combine=lambda ts: torch.stack(ts, 0), split=lambda t: list(t.unbind(0)))]
+           E("w_up", up_names, combine=comb_up, split=split_up, alternates=[[f"{p}{experts}.gate_up_proj"]]),
+           E("w_down", down_names, combine=lambda ts: ts[0] if len(ts) == 1 else torch.stack(ts, 0),
+             split=lambda t: list(t.unbind(0)), alternates=[[f"{p}{experts}.down_proj"]])]
     if mc.shared_dim > 0:
         out += [E("w_shared_1", [f"{p}{shared}.gate_proj.weight"]), E("w_shared_3", [f"{p}{shared}.up_proj.weight"]),
                 E("w_shared_2", [f"{p}{shared}.down_proj.weight"])]

@@ -20,7 +20,7 @@ def config_from_dims(dims, hyper):
 def config_from_hf(hf: dict) -> ModelConfig:
     mc = _l.config_from_hf(hf)
     mc.arch, mc.qk_norm = FAMILY, "row"
-    mc.num_experts, mc.top_k = int(hf["num_experts"]), int(hf["num_experts_per_tok"])
+    mc.num_experts, mc.top_k = int(hf.get("num_experts", hf.get("num_local_experts"))), int(hf["num_experts_per_tok"])
     mc.expert_dim = int(hf["intermediate_size"])
     mc.routing = "topk_then_softmax" if hf.get("norm_topk_prob", False) else "softmax_then_topk"
     mc.aux_loss_alpha = float(hf.get("router_aux_loss_coef", 0.0)) if hf.get("output_router_logits") else 0.0

@@ -22,7 +22,7 @@ def config_from_dims(dims, hyper):
 def config_from_hf(hf: dict) -> ModelConfig:
     mc = _q.config_from_hf(hf)
     mc.arch = FAMILY
-    mc.num_experts, mc.top_k = int(hf["num_experts"]), int(hf["num_experts_per_tok"])
+    mc.num_experts, mc.top_k = int(hf.get("num_experts", hf.get("num_local_experts"))), int(hf["num_experts_per_tok"])
     mc.expert_dim = int(hf["moe_intermediate_size"])
     mc.routing = "topk_then_softmax" if hf.get("norm_topk_prob", True) else "softmax_then_topk"
     mc.aux_loss_alpha = 0.0
