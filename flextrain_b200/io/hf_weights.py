@@ -73,8 +73,21 @@ class SafetensorsDir:
         return sorted(set(self.where) - self.consumed)
 
 
+# multimodal wrappers (and text-only saves of families that have one) nest the decoder under another prefix
+_NESTED_PREFIXES = ("model.language_model.", "language_model.model.")
+
+
+def _name_sets(entry: WeightMapEntry):
+    sets = [list(entry.hf_names), *[list(a) for a in entry.alternates]]
+    yield from sets
+    for names in sets:
+        if all(n.startswith("model.") for n in names):
+            for pre in _NESTED_PREFIXES:
+                yield [pre + n[len("model."):] for n in names]
+
+
 def _resolve(entry: WeightMapEntry, src: SafetensorsDir) -> Optional[List[torch.Tensor]]:
-    for names in (entry.hf_names, *entry.alternates):
+    for names in _name_sets(entry):
         if all(src.has(n) for n in names):
             return [src.get(n) for n in names]
     return None
@@ -139,7 +152,7 @@ def load_hf_into_model(am, model_dir: str, strict: bool = False) -> None:
 
 
 def _peek(entry: WeightMapEntry, src: SafetensorsDir):
-    for names in (entry.hf_names, *entry.alternates):
+    for names in _name_sets(entry):
         if all(src.has(n) for n in names):
             return names
     return None

@@ -30,6 +30,23 @@ CASES = {
     "qwen3_moe": ("Qwen3MoeConfig", dict(COMMON, rope_theta=10000.0, head_dim=16, num_experts=8, num_experts_per_tok=2,
                                          moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
                                          mlp_only_layers=[])),
+    "qwen3_next": ("Qwen3NextConfig", dict(COMMON, head_dim=16, num_hidden_layers=4, linear_conv_kernel_dim=4,
+                                           linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2,
+                                           linear_num_value_heads=4, num_experts=8, num_experts_per_tok=2,
+                                           moe_intermediate_size=48, shared_expert_intermediate_size=48,
+                                           norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
+                                           layer_types=["linear_attention", "full_attention"] * 2)),
+    "qwen3_5": ("Qwen3_5TextConfig", dict(COMMON, head_dim=16, num_hidden_layers=4, linear_conv_kernel_dim=4,
+                                          linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2,
+                                          linear_num_value_heads=4,
+                                          layer_types=["linear_attention", "full_attention"] * 2)),
+    "qwen3_5_moe": ("Qwen3_5MoeTextConfig", dict({k: v for k, v in COMMON.items() if k != "intermediate_size"},
+                                                 head_dim=16, num_hidden_layers=4, linear_conv_kernel_dim=4,
+                                                 linear_key_head_dim=16, linear_value_head_dim=16,
+                                                 linear_num_key_heads=2, linear_num_value_heads=4, num_experts=8,
+                                                 num_experts_per_tok=2, moe_intermediate_size=48,
+                                                 shared_expert_intermediate_size=48,
+                                                 layer_types=["linear_attention", "full_attention"] * 2)),
     "olmoe": ("OlmoeConfig", dict(COMMON, rope_theta=10000.0, num_experts=8, num_experts_per_tok=2,
                                   norm_topk_prob=False)),
 }
@@ -45,6 +62,8 @@ def _hf_model(name):
         for n, p in model.named_parameters():
             if "norm" in n:
                 p.add_(torch.randn_like(p) * 0.1)
+            if n.endswith("A_log"):            # default init decays the state within a token: gradients would be noise
+                p.uniform_(-1.0, 0.5)
     return model
 
 
@@ -85,12 +104,16 @@ def test_loss_and_gradients_match_transformers(name, tmp_path):
         tied_total = bm.embed_grads()["g_tok_embeddings"].float() + bm.head_grads()["g_head_proj"].float()
     pairs = [(bm.embed_params(), bm.embed_grads())] + [(bm.host_params(i), bm.grads(i)) for i in range(len(am.layers))] \
         + [(bm.head_params(), bm.head_grads())]
+    for P, _ in pairs:                        # what the export map adds on its own (-1 on (1 + w) norm weights)
+        for p in P.values():
+            p.zero_()
+    offsets = {n: t.clone() for n, t in collect_hf_state(am).items()}
     for P, G in pairs:
         for n, p in P.items():
             g = G.get("g_" + n[2:] if n.startswith("w_") else "g_" + n)
             if g is not None:
                 p.copy_(g.to(p.dtype))
-    hf_named = collect_hf_state(am)
+    hf_named = {n: t.float() - offsets[n].float() for n, t in collect_hf_state(am).items()}
     checked = 0
     for n, g in hf_grads.items():
         if n.endswith("mlp.experts.gate_up_proj"):        # stacked experts (transformers >= 5): [gate ‖ up] per expert
@@ -111,8 +134,6 @@ def test_loss_and_gradients_match_transformers(name, tmp_path):
             # the reference project) treats the pad id as an ordinary token
             got = got.clone()
             got[pad] = g[pad]
-        if "norm" in n and got.shape == g.shape and name in ("gemma2", "gemma3"):
-            got = got + 1.0                   # the exporter subtracts 1 from (1 + w) norm weights; gradients have no offset
         cos = torch.nn.functional.cosine_similarity(got.flatten(), g.flatten(), dim=0)
         rel = (got - g).norm() / (g.norm() + 1e-12)
         assert cos > 0.9999 and rel < 2e-3, (name, n, float(cos), float(rel))
