@@ -62,6 +62,8 @@ def _attention(layer, l, P, h, pos):
     if c.qk_norm == "head":
         q = _rms(q, P[("layer", l, "w_q_norm")], c.norm_eps)
         k = _rms(k, P[("layer", l, "w_k_norm")], c.norm_eps)
+    if c.v_norm:
+        v = _rms(v, torch.ones(c.head_dim, dtype=v.dtype), c.norm_eps)
     inv = c.rope.inv_freq(c.head_dim)
     q, k = _rope(q, pos, inv, c.rope.mrope_sections), _rope(k, pos, inv, c.rope.mrope_sections)
     rep = c.n_heads // c.n_kv_heads
@@ -141,6 +143,8 @@ def naive_forward(am, P, tokens: torch.Tensor, positions: Optional[torch.Tensor]
         if c.post_norms:
             f = _rms(f, P[("layer", l, "w_post_ffn_norm")], c.norm_eps)
         x = x + f
+        if c.layer_scalar:
+            x = x * P[("layer", l, "w_layer_scalar")]
     h = _rms(x, P[("head", -1, "w_final_norm")], am.head.norm_eps)
     z = h @ P[("head", -1, "w_head_proj")].t()
     if am.head.final_softcap:

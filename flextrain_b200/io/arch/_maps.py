@@ -114,14 +114,21 @@ def gdn_entries(i: int, mc, prefix="model.") -> List[E]:
 
     pq, pb = perm_qkvz(), perm_ba()
     iq, ib = torch.argsort(pq), torch.argsort(pb)
-    # separate-projection checkpoints (in_proj_qkv + in_proj_z, in_proj_b + in_proj_a) are already flat
+    # Qwen3-Next bundles the projections per key-head group; Qwen3.5 stores them separately and already flat.  Either
+    # form loads; export writes the family's own.
+    bundled_qkvz, bundled_ba = [f"{p}in_proj_qkvz.weight"], [f"{p}in_proj_ba.weight"]
+    flat_qkvz, flat_ba = [f"{p}in_proj_qkv.weight", f"{p}in_proj_z.weight"], [f"{p}in_proj_b.weight", f"{p}in_proj_a.weight"]
+    n_qkv, n_b = 2 * g.n_k_heads * hk + g.n_v_heads * hv, g.n_v_heads
+    flat = mc.arch in ("qwen3_5", "qwen3_5_moe")
     return [
-        E("w_lin_qkvz", [f"{p}in_proj_qkvz.weight"],
-          combine=lambda ts: torch.cat(ts, 0) if len(ts) == 2 else ts[0][pq], split=lambda t: [t[iq]],
-          alternates=[[f"{p}in_proj_qkv.weight", f"{p}in_proj_z.weight"]]),
-        E("w_lin_ba", [f"{p}in_proj_ba.weight"],
-          combine=lambda ts: torch.cat(ts, 0) if len(ts) == 2 else ts[0][pb], split=lambda t: [t[ib]],
-          alternates=[[f"{p}in_proj_b.weight", f"{p}in_proj_a.weight"]]),
+        E("w_lin_qkvz", flat_qkvz if flat else bundled_qkvz,
+          combine=lambda ts: torch.cat(ts, 0) if len(ts) == 2 else ts[0][pq],
+          split=(lambda t: [t[:n_qkv], t[n_qkv:]]) if flat else (lambda t: [t[iq]]),
+          alternates=[bundled_qkvz if flat else flat_qkvz]),
+        E("w_lin_ba", flat_ba if flat else bundled_ba,
+          combine=lambda ts: torch.cat(ts, 0) if len(ts) == 2 else ts[0][pb],
+          split=(lambda t: [t[:n_b], t[n_b:]]) if flat else (lambda t: [t[ib]]),
+          alternates=[bundled_ba if flat else flat_ba]),
         E("w_lin_conv", [f"{p}conv1d.weight"], combine=lambda ts: ts[0].reshape(ts[0].shape[0], -1),
           split=lambda t: [t.unsqueeze(1)]),
         E("w_lin_dt_bias", [f"{p}dt_bias"]), E("w_lin_A_log", [f"{p}A_log"]),

@@ -63,6 +63,8 @@ class ModelConfig:
     tie_embeddings: bool = False
     norm_plus_one: bool = False                      # checkpoint stores gamma - 1 (Gemma, Qwen3.5/Next)
     is_causal: bool = True
+    v_norm: bool = False                             # Gemma 4: scale-free per-head RMSNorm of V
+    layer_scalar: bool = False                       # Gemma 4: stored per-layer output multiplier
     mrope_sections: Optional[Tuple[int, int, int]] = None
     hf: Optional[dict] = None
 
@@ -143,7 +145,7 @@ def build_decoder_config(mc: ModelConfig, i: int, dt: DTypePolicy, lora: Optiona
         attn = AttentionConfig(d_model=mc.d_model, n_heads=mc.n_heads, n_kv_heads=mc.n_kv_heads, head_dim=mc.head_dim,
                                rope=rope, qkv_bias=mc.qkv_bias, qk_norm=mc.qk_norm, norm_eps=mc.norm_eps,
                                softcap=mc.attn_softcap, window=mc.sliding_window if lt == "sliding" else 0,
-                               scale=mc.attn_scale, gated=mc.gated_attn, causal=mc.is_causal)
+                               scale=mc.attn_scale, gated=mc.gated_attn, causal=mc.is_causal, v_norm=mc.v_norm)
     ffn = moe = None
     if mc.is_moe_layer(i):
         moe = MoEConfig(d_model=mc.d_model, num_experts=mc.num_experts, top_k=mc.top_k, expert_dim=mc.expert_dim,
@@ -153,7 +155,8 @@ def build_decoder_config(mc: ModelConfig, i: int, dt: DTypePolicy, lora: Optiona
         ffn = DenseFFNConfig(mc.d_model, mc.ffn_dim, mc.ffn_kind)
     return DecoderConfig(d_model=mc.d_model, attn=attn, gdn=gdn, ffn=ffn, moe=moe, norm_eps=mc.norm_eps,
                          post_norms=mc.post_norms, dtype=dt.compute, norm_dtype=dt.norm, grad_dtype=dt.grad,
-                         norm_grad_dtype=dt.norm_grad, master_dtype=dt.master, lora=lora, family=mc.arch)
+                         norm_grad_dtype=dt.norm_grad, master_dtype=dt.master, lora=lora, family=mc.arch,
+                         layer_scalar=mc.layer_scalar)
 
 
 def build_model_parts(mc: ModelConfig, dt: DTypePolicy, lora: Optional[LoRAConfig], head_chunk_size: int = 4096,
@@ -199,7 +202,8 @@ def config_from_dims(dims: dict, arch: str, hyper: Optional[dict] = None) -> Mod
             dims.get("num_shared_experts", 0) or 0) if E > 0 else 0,
         is_causal=bool(dims.get("is_causal", True)))
     for k in ("qkv_bias", "qk_norm", "attn_softcap", "final_softcap", "sliding_window", "routing", "ffn_kind",
-              "post_norms", "embed_scale", "gated_attn", "shared_gate", "aux_loss_alpha", "tie_embeddings"):
+              "post_norms", "embed_scale", "gated_attn", "shared_gate", "aux_loss_alpha", "tie_embeddings", "v_norm",
+              "layer_scalar", "attn_scale"):
         if k in h:
             setattr(mc, k, h[k])
     if "layer_pattern" in h:

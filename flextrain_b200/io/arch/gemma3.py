@@ -35,6 +35,10 @@ def config_from_hf(hf: dict) -> ModelConfig:
         pat = int(txt.get("sliding_window_pattern", 6))
         mc.layer_types = ["full" if (i + 1) % pat == 0 else "sliding" for i in range(mc.n_layers)]
     mc.rope_local = RopeConfig(theta=float(txt.get("rope_local_base_freq", 10000.0)))
+    rp = txt.get("rope_parameters") or {}
+    if "full_attention" in rp or "sliding_attention" in rp:       # transformers >= 5: one parameter set per layer type
+        mc.rope = RopeConfig.from_hf({"rope_parameters": rp.get("full_attention", {})}, mc.head_dim)
+        mc.rope_local = RopeConfig.from_hf({"rope_parameters": rp.get("sliding_attention", {})}, mc.head_dim)
     return mc
 
 

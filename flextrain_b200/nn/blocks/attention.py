@@ -40,6 +40,7 @@ class AttentionConfig:
     scale: Optional[float] = None            # default head_dim ** -0.5
     gated: bool = False                      # Qwen3-Next / Qwen3.5 output gate
     causal: bool = True
+    v_norm: bool = False                     # Gemma 4: per-head RMSNorm of V without a learned scale
 
     @property
     def q_dim(self) -> int:
@@ -95,6 +96,8 @@ class GQAAttentionBlock:
         elif c.qk_norm == "row":
             f += [ActivationField("q_rstd", lambda t: (t,), torch.float32, 0),
                   ActivationField("k_rstd", lambda t: (t,), torch.float32, 0)]
+        if c.v_norm:
+            f.append(ActivationField("v_rstd", lambda t: (t, c.n_kv_heads), torch.float32, 0))
         return f
 
     # --------------------------------------------------------------------- helpers
@@ -102,6 +105,13 @@ class GQAAttentionBlock:
         key = str(device)
         if key not in self.inv_freq_cache:
             self.inv_freq_cache[key] = self.cfg.rope.inv_freq(self.cfg.head_dim).to(device)
+        return self.inv_freq_cache[key]
+
+    def _unit_gain(self, device) -> torch.Tensor:
+        """The all-ones gain of the scale-free V norm (the norm kernels take a gain operand)."""
+        key = "ones:" + str(device)
+        if key not in self.inv_freq_cache:
+            self.inv_freq_cache[key] = torch.ones(self.cfg.head_dim, dtype=self.norm_dtype, device=device)
         return self.inv_freq_cache[key]
 
     def _project_qkv(self, h, params, qkv=None):
@@ -150,7 +160,12 @@ class GQAAttentionBlock:
         pos, sec = meta.positions, c.rope.mrope_sections
         xk = ops.rope(k, pos, inv, out=slot.out("xk", h.device), mrope_sections=sec)
         xv = slot.out("xv", h.device)
-        xv.copy_(v)
+        if c.v_norm:
+            vn, vr = ops.rmsnorm_fwd(v.contiguous(), self._unit_gain(h.device), c.norm_eps)
+            slot.put("v_rstd", vr)
+            xv.copy_(vn)
+        else:
+            xv.copy_(v)
         xq = None
         if want_q:
             xq = ops.rope(q, pos, inv, out=slot.out("xq", h.device), mrope_sections=sec)
@@ -252,7 +267,12 @@ class GQAAttentionBlock:
             dq_dst = dqkv[:, :qrows].unflatten(1, (c.n_heads, c.head_dim))
         dk_dst = dqkv[:, qrows: qrows + c.kv_dim].unflatten(1, (c.n_kv_heads, c.head_dim))
         dv_dst = dqkv[:, qrows + c.kv_dim:].unflatten(1, (c.n_kv_heads, c.head_dim))
-        dv_dst.copy_(dv)
+        pre = self._project_qkv(h_fn(), params) if (c.qk_norm or c.v_norm) else None   # pre-norm recompute (one GEMM)
+        if c.v_norm:
+            dvp, _ = ops.rmsnorm_bwd(dv.contiguous(), pre[3].contiguous(), self._unit_gain(dxo.device), t["v_rstd"])
+            dv_dst.copy_(dvp.view(T, c.n_kv_heads, c.head_dim))
+        else:
+            dv_dst.copy_(dv)
         if not c.qk_norm:
             if c.gated:
                 dq_dst.copy_(ops.rope(dq.contiguous(), pos, inv, inverse=True, mrope_sections=sec))
@@ -262,7 +282,7 @@ class GQAAttentionBlock:
         else:
             dqn = ops.rope(dq.contiguous(), pos, inv, inverse=True, mrope_sections=sec)
             dkn = ops.rope(dk.contiguous(), pos, inv, inverse=True, mrope_sections=sec)
-            q_pre, _, k_pre, _ = self._project_qkv(h_fn(), params)               # pre-norm recompute (one GEMM)
+            q_pre, _, k_pre, _ = pre
             if c.qk_norm == "head":
                 dqp, _ = ops.rmsnorm_bwd(dqn, q_pre.contiguous(), params["w_q_norm"], t["q_rstd"],
                                          dw_out=grads.get("g_q_norm"))

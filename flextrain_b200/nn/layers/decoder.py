@@ -47,6 +47,7 @@ class DecoderConfig:
     master_dtype: Optional[torch.dtype] = None
     lora: Optional[LoRAConfig] = None
     family: str = "llama"
+    layer_scalar: bool = False       # Gemma 4: the layer's output is multiplied by a stored, untrained scalar
     seq_parallel: int = 1            # tensor-parallel degree: the residual stream and norm statistics hold T / seq_parallel tokens
 
 
@@ -76,6 +77,9 @@ class DecoderLayer:
         specs += (self.ffn or self.moe).tensor_specs()
         if c.post_norms:
             specs.append(norm("w_post_ffn_norm"))
+        if c.layer_scalar:
+            specs.append(TensorSpec("w_layer_scalar", (1,), torch.float32, master_dtype=torch.float32, init="ones",
+                                    frozen=True))
         for s in specs:
             if "norm" in s.name:
                 s.grad_dtype = c.norm_grad_dtype
@@ -133,6 +137,12 @@ class DecoderLayer:
         return self.moe.fwd(h2, resid, params, slot, ctx)
 
     def forward(self, x, meta: ChunkMeta, params: Dict[str, torch.Tensor], slot, ctx: LayerContext):
+        out = self._forward(x, meta, params, slot, ctx)
+        if self.cfg.layer_scalar:
+            out = (out * params["w_layer_scalar"]).to(out.dtype)
+        return out
+
+    def _forward(self, x, meta: ChunkMeta, params: Dict[str, torch.Tensor], slot, ctx: LayerContext):
         c = self.cfg
         x = slot.put("x_inp", x)
         h1, r1 = ops.rmsnorm_fwd(x, params["w_attn_norm"], c.norm_eps)
@@ -205,6 +215,8 @@ class DecoderLayer:
         c = self.cfg
         t = slot._t
         x, xo = t["x_inp"], t["xo"]
+        if c.layer_scalar:
+            dx = (dx * params["w_layer_scalar"]).to(dx.dtype)
         # ---- FFN half
         d_branch = dx
         if c.post_norms:

@@ -22,6 +22,9 @@ CASES = {
     "olmoe": ("olmoe", MOE, {}),
     "gemma2": ("gemma2", BASE, {"sliding_window": 16, "layer_pattern": "SF", "attn_softcap": 50.0, "final_softcap": 30.0}),
     "gemma3": ("gemma3", BASE, {"sliding_window": 16, "layer_pattern": "SF"}),
+    "gemma4": ("gemma4", BASE, {"sliding_window": 16, "layer_pattern": "SF"}),
+    "qwen3_5_moe": ("qwen3_5_moe", dict(MOE, num_shared_experts=1, shared_dim=64),
+                    {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 4, "head_k_dim": 16, "head_v_dim": 16}}),
     "qwen3_next": ("qwen3_next", dict(MOE, num_shared_experts=1, shared_dim=64),
                    {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 4, "head_k_dim": 16, "head_v_dim": 16}}),
     "qwen3_5_dense": ("qwen3_5", BASE,
@@ -55,7 +58,7 @@ def test_family_gradients(case):
     torch.manual_seed(0)
     # perturb norm weights and biases so their gradients are exercised away from the init point
     for scope, l, name, t in am.named_master_params():
-        if "norm" in name or name.startswith("b_") or "dt_bias" in name or "A_log" in name:
+        if "norm" in name or name.startswith("b_") or "dt_bias" in name or "A_log" in name or "scalar" in name:
             t.add_(torch.randn_like(t) * 0.1)
     seqs = ft.SyntheticTokenSource(dims["vocab_size"], [48, 40], seed=2).get_sequences(96)
     _check(am, seqs)

@@ -25,7 +25,11 @@ CASES = {
                                     attn_logit_softcapping=50.0, final_logit_softcapping=30.0,
                                     hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)),
     "gemma3": ("Gemma3TextConfig", dict(COMMON, head_dim=16, query_pre_attn_scalar=16, sliding_window=16,
-                                        sliding_window_pattern=2, rope_theta=10000.0, rope_local_base_freq=10000.0,
+                                        sliding_window_pattern=2, rope_theta=1000000.0, rope_local_base_freq=10000.0,
+                                        hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)),
+    "gemma4": ("Gemma4TextConfig", dict(COMMON, head_dim=16, global_head_dim=16, sliding_window=16,
+                                        layer_types=["sliding_attention", "full_attention"],
+                                        hidden_size_per_layer_input=0, vocab_size_per_layer_input=320,
                                         hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)),
     "qwen3_moe": ("Qwen3MoeConfig", dict(COMMON, rope_theta=10000.0, head_dim=16, num_experts=8, num_experts_per_tok=2,
                                          moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
@@ -64,6 +68,9 @@ def _hf_model(name):
                 p.add_(torch.randn_like(p) * 0.1)
             if n.endswith("A_log"):            # default init decays the state within a token: gradients would be noise
                 p.uniform_(-1.0, 0.5)
+        for n, b in model.named_buffers():
+            if n.endswith("layer_scalar"):     # stored, untrained per-layer multiplier (Gemma 4)
+                b.fill_(0.5 + 0.25 * int(n.split(".")[2]))
     return model
 
 

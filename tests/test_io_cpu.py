@@ -27,13 +27,16 @@ def _reload(path, **kw):
 @pytest.mark.parametrize("arch,dims,hyper", [
     ("llama", BASE, {}), ("qwen2", BASE, {}), ("qwen3", BASE, {}), ("qwen3_moe", MOE, {}), ("olmoe", MOE, {}),
     ("gemma2", BASE, {"sliding_window": 16, "layer_pattern": "SF"}), ("gemma3", BASE, {"sliding_window": 16, "layer_pattern": "SF"}),
+    ("gemma4", BASE, {"sliding_window": 16, "layer_pattern": "SF"}),
+    ("qwen3_5", BASE, {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 2, "head_k_dim": 16, "head_v_dim": 32}}),
+    ("qwen3_5_moe", NEXT, {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 4, "head_k_dim": 16, "head_v_dim": 16}}),
     ("qwen3_next", NEXT, {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 4, "head_k_dim": 16, "head_v_dim": 16}}),
 ])
 def test_export_reload_roundtrip(tmp_path, arch, dims, hyper):
     am = build_tiny(arch=arch, dims=dims, hyper=hyper, max_seq_len=64, batch_tokens=128)
     torch.manual_seed(1)
     for _, _, name, t in am.named_master_params():
-        if "norm" in name:
+        if "norm" in name or "scalar" in name:
             t.add_(torch.randn_like(t) * 0.1)
     out = str(tmp_path / arch)
     save_hf_full(am, out)
