@@ -89,6 +89,29 @@ def test_hybrid_gated_deltanet_bf16_tracks_fp32(seq_len, chunk):
     assert "gdn" in k._libs and "seqmix" in k._libs, "Gated DeltaNet CUDA kernels were not used"
 
 
+@pytest.mark.parametrize("arch", ["gemma3", "gemma4"])
+def test_gemma_family_bf16_tracks_fp32(arch):
+    """Sandwich norms, per-head QK-norm, sliding + global layers with their own RoPE bases, GeGLU, tied scaled
+    embedding; Gemma 4 adds the scale-free V norm, unit attention scale, proportional RoPE and the layer scalar."""
+    dims = dict(vocab_size=1024, n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, expert_dim=704,
+                ffn_dim=704, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+    kw = dict(arch=arch, dims=dims, hyper={"sliding_window": 32, "layer_pattern": "SF"})
+    cpu = build_tiny(**kw)
+    gpu = build_tiny(device="cuda:0", dtype=torch.bfloat16, optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32),
+                     **kw)
+    torch.manual_seed(4)
+    for _, _, name, t in cpu.named_master_params():
+        if "norm" in name or "scalar" in name:
+            t.add_(torch.randn_like(t) * 0.1)
+    _copy_weights(cpu, gpu)
+    src = ft.SyntheticTokenSource(1024, 128, seed=17)
+    for step in range(3):
+        seqs = src.get_sequences(256)
+        a = cpu.fwd_bwd(seqs); cpu.step()
+        b = gpu.fwd_bwd(seqs); gpu.step()
+        assert abs(a.loss - b.loss) < 0.04, (step, a.loss, b.loss)
+
+
 @pytest.mark.parametrize("ws_kw,force", [
     (dict(chunk=128, host_act_buffer_size=256 << 20, n_gpu_act_slots=3), None),     # DP-solver tiers, host arena
     (dict(chunk=128, host_act_buffer_size=256 << 20), 0),                           # everything offloaded at tier 0
