@@ -31,9 +31,16 @@ struct FwdParams {
   float* lse;             // (H, Tq)
   int total_q;
   float scale;
+  float softcap;          // 0 = none; else scores become softcap * tanh(scale * s / softcap) (Gemma 2)
   int causal;
   int window;             // 0 = unlimited
 };
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ bool find_tile(const int* cu_q, int num_seqs, int tile, int& seq, int& q0) {
   int acc = 0;
@@ -196,6 +203,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int r = quad * 32 + lane;                 // query row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const float c = p.scale * 1.4426950408889634f;  // scores are kept in log2 units
+    const bool capped = p.softcap > 0.f;
+    const float cap2 = p.softcap * 1.4426950408889634f;            // soft-cap in log2 units
+    const float soc = capped ? p.scale / p.softcap : 0.f;
     float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
     float o[HD];
 #pragma unroll
@@ -224,7 +234,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (keep) mx = fmaxf(mx, __uint_as_float(v[i]));
         }
       }
-      const float m_new = fmaxf(m, mx * c);
+      // tanh is monotonic: the capped maximum is the cap of the maximum
+      const float mx2 = (capped && mx != -INFINITY) ? cap2 * tanh_fast(mx * soc) : mx * c;
+      const float m_new = fmaxf(m, mx2);
       const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
       // fold the previous tile's P·V into the running output (this also means the P tile is free again)
       if (j > 0) {
@@ -256,7 +268,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           const int kj = key0 + cb + i;
           bool keep = kj < len_k;
           if (p.causal) keep = keep && (kj <= qi) && (p.window <= 0 || kj > qi - p.window);
-          pr[i] = keep ? exp2f(__uint_as_float(v[i]) * c - mref) : 0.f;
+          const float raw = __uint_as_float(v[i]);
+          const float s2 = capped ? cap2 * tanh_fast(raw * soc) : raw * c;
+          pr[i] = keep ? exp2f(s2 - mref) : 0.f;
           sum += pr[i];
         }
 #pragma unroll
@@ -375,7 +389,8 @@ extern "C" {
 // max_tiles >= sum over sequences of ceil(len_q / 128); Tq / 128 + num_seqs always suffices.
 int ftb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q, const int* cu_k,
                  int num_seqs, int total_q, int total_k, int H, int KV, int hd, long q_stride, long k_stride,
-                 long v_stride, float scale, int causal, int window, int max_tiles, cudaStream_t stream) {
+                 long v_stride, float scale, float softcap, int causal, int window, int max_tiles,
+                 cudaStream_t stream) {
   if (total_q <= 0 || num_seqs <= 0) return 0;
   if ((hd != 64 && hd != 128) || H % KV) return -2;
   if ((q_stride & 7) || (k_stride & 7) || (v_stride & 7)) return -2;
@@ -389,7 +404,7 @@ int ftb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* 
   FwdParams p;
   p.cu_q = cu_q; p.cu_k = cu_k; p.num_seqs = num_seqs; p.H = H; p.KV = KV;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.total_q = total_q;
-  p.scale = scale; p.causal = causal; p.window = window;
+  p.scale = scale; p.softcap = softcap; p.causal = causal; p.window = window;
   if (hd == 128) return launch_fwd<128>(tq, tk, tv, p, max_tiles, stream);
   return launch_fwd<64>(tq, tk, tv, p, max_tiles, stream);
 }
@@ -425,6 +440,7 @@ struct BwdParams {
   const float* delta;       // (H, Tq)  rowsum(dO * O)
   int total_q;
   float scale;
+  float softcap;
   int causal;
   int window;
 };
@@ -581,6 +597,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int r = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const float c = p.scale * 1.4426950408889634f;
+    const bool capped = p.softcap > 0.f;
+    const float cap2 = p.softcap * 1.4426950408889634f;
+    const float soc = capped ? p.scale / p.softcap : 0.f;
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const uint32_t ph = it & 1;
@@ -606,9 +625,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           const int kj = k0 + cb + e;
           bool keep = vq && kj < len_k;
           if (p.causal) keep = keep && (kj <= qi) && (p.window <= 0 || kj > qi - p.window);
-          const float pe = keep ? exp2f(__uint_as_float(vs[e]) * c - lse2) : 0.f;
+          const float raw = __uint_as_float(vs[e]);
+          const float th = capped ? tanh_fast(raw * soc) : 0.f;
+          const float pe = keep ? exp2f((capped ? cap2 * th : raw * c) - lse2) : 0.f;
           pr[e] = pe;
-          ds[e] = pe * (__uint_as_float(vd[e]) - dl) * p.scale;
+          // d(cap * tanh(scale * s / cap)) / ds = scale * (1 - tanh^2)
+          ds[e] = pe * (__uint_as_float(vd[e]) - dl) * p.scale * (1.f - th * th);
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -735,8 +757,8 @@ extern "C" {
 int ftb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse,
                  float* delta, float* dq_acc, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k,
                  int num_seqs, int total_q, int total_k, int H, int KV, int hd, long q_stride, long k_stride,
-                 long v_stride, long do_stride, long o_stride, float scale, int causal, int window, int max_tiles,
-                 cudaStream_t stream) {
+                 long v_stride, long do_stride, long o_stride, float scale, float softcap, int causal, int window,
+                 int max_tiles, cudaStream_t stream) {
   if (total_q <= 0 || num_seqs <= 0) return 0;
   if ((hd != 64 && hd != 128) || H % KV) return -2;
   if ((q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (do_stride & 7)) return -2;
@@ -758,7 +780,7 @@ int ftb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, 
   BwdParams p;
   p.cu_q = cu_q; p.cu_k = cu_k; p.num_seqs = num_seqs; p.H = H; p.KV = KV;
   p.dq_acc = dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.lse = lse; p.delta = delta;
-  p.total_q = total_q; p.scale = scale; p.causal = causal; p.window = window;
+  p.total_q = total_q; p.scale = scale; p.softcap = softcap; p.causal = causal; p.window = window;
   rc = (hd == 128) ? launch_bwd<128>(tq, tdo, tk, tv, p, max_tiles, stream)
                    : launch_bwd<64>(tq, tdo, tk, tv, p, max_tiles, stream);
   return rc;

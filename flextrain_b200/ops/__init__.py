@@ -213,10 +213,11 @@ def _attn_backend_for(q) -> str:
 def attention_fwd(q, k, v, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, softcap=0.0):
     """Varlen GQA attention, bottom-right aligned causal. Returns ``(out (Tq,H,hd), lse (H,Tq) fp32)``."""
     be = _attn_backend_for(q)
-    if be == "ftb" and not softcap:
+    if be == "ftb":
         from . import attention_cuda
         _count()
-        return attention_cuda.fwd(q, k, v, cu_q, cu_k, max_q, max_k, scale=scale, causal=causal, window=window)
+        return attention_cuda.fwd(q, k, v, cu_q, cu_k, max_q, max_k, scale=scale, causal=causal, window=window,
+                                  softcap=softcap)
     if be in ("library", "ftb") and not softcap:
         wl = (window - 1) if window and window > 0 else None
         o, lse, _, _, _ = torch.ops.aten._flash_attention_forward(
@@ -229,11 +230,11 @@ def attention_fwd(q, k, v, cu_q, cu_k, max_q, max_k, *, scale, causal=True, wind
 def attention_bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, softcap=0.0):
     """Returns ``(dq, dk, dv)``; dk/dv span all visible keys."""
     be = _attn_backend_for(q)
-    if be == "ftb" and not softcap and hasattr(_kernels().load("attention"), "ftb_attn_bwd"):
+    if be == "ftb" and hasattr(_kernels().load("attention"), "ftb_attn_bwd"):
         from . import attention_cuda
         _count(3)
         return attention_cuda.bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, scale=scale, causal=causal,
-                                  window=window)
+                                  window=window, softcap=softcap)
     if be in ("library", "ftb") and not softcap:
         wl = (window - 1) if window and window > 0 else None
         rng = torch.zeros(2, dtype=torch.uint64, device=q.device)

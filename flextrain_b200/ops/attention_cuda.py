@@ -12,7 +12,7 @@ def _strided_ok(t: torch.Tensor) -> bool:
     return t.stride(2) == 1 and t.stride(1) == t.shape[2] and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
 
 
-def fwd(q, k, v, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0):
+def fwd(q, k, v, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, softcap=0.0):
     """``q (Tq,H,hd)``, ``k,v (Tk,KV,hd)`` bf16 (token-strided views allowed). Returns ``(out, lse (H,Tq) fp32)``."""
     lib = load("attention")
     if not _strided_ok(q):
@@ -30,13 +30,13 @@ def fwd(q, k, v, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0):
     cu_k = cu_k.to(torch.int32)
     rc = lib.ftb_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), _ptr(cu_q), _ptr(cu_k), c_int(nseq),
                           c_int(Tq), c_int(Tk), c_int(H), c_int(KV), c_int(hd), c_long(q.stride(0)),
-                          c_long(k.stride(0)), c_long(v.stride(0)), c_float(scale), c_int(1 if causal else 0),
-                          c_int(int(window or 0)), c_int(Tq // 128 + nseq), _stream())
+                          c_long(k.stride(0)), c_long(v.stride(0)), c_float(scale), c_float(float(softcap or 0.0)),
+                          c_int(1 if causal else 0), c_int(int(window or 0)), c_int(Tq // 128 + nseq), _stream())
     _check(rc, "ftb_attn_fwd")
     return out, lse
 
 
-def bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0):
+def bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, softcap=0.0):
     """Returns ``(dq, dk, dv)``; dk / dv cover all keys."""
     lib = load("attention")
     if not hasattr(lib, "ftb_attn_bwd"):
@@ -60,7 +60,8 @@ def bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True
                           _ptr(dq), _ptr(dk), _ptr(dv), _ptr(cu_q), _ptr(cu_k), c_int(nseq), c_int(Tq), c_int(Tk),
                           c_int(H), c_int(KV), c_int(hd), c_long(q.stride(0)), c_long(k.stride(0)),
                           c_long(v.stride(0)), c_long(dout.stride(0)), c_long(out.stride(0)), c_float(scale),
-                          c_int(1 if causal else 0), c_int(int(window or 0)), c_int(Tk // 128 + nseq), _stream())
+                          c_float(float(softcap or 0.0)), c_int(1 if causal else 0), c_int(int(window or 0)),
+                          c_int(Tk // 128 + nseq), _stream())
     _check(rc, "ftb_attn_bwd")
     dq.copy_(dq_acc)
     return dq, dk, dv

@@ -89,9 +89,9 @@ def test_hybrid_gated_deltanet_bf16_tracks_fp32(seq_len, chunk):
     assert "gdn" in k._libs and "seqmix" in k._libs, "Gated DeltaNet CUDA kernels were not used"
 
 
-@pytest.mark.parametrize("arch", ["gemma3", "gemma4"])
+@pytest.mark.parametrize("arch", ["gemma2", "gemma3", "gemma4"])
 def test_gemma_family_bf16_tracks_fp32(arch):
-    """Sandwich norms, per-head QK-norm, sliding + global layers with their own RoPE bases, GeGLU, tied scaled
+    """Gemma 2: attention and final-logit soft-caps.  Gemma 3: sandwich norms, per-head QK-norm, sliding + global layers with their own RoPE bases, GeGLU, tied scaled
     embedding; Gemma 4 adds the scale-free V norm, unit attention scale, proportional RoPE and the layer scalar."""
     dims = dict(vocab_size=1024, n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, expert_dim=704,
                 ffn_dim=704, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)

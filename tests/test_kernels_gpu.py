@@ -265,17 +265,19 @@ def test_attention_library_matches_reference():
 
 
 @pytest.mark.parametrize("hd", [128, 64])
-@pytest.mark.parametrize("case", ["equal", "prior_ctx", "ragged", "window"])
+@pytest.mark.parametrize("case", ["equal", "prior_ctx", "ragged", "window", "softcap"])
 def test_attention_tcgen05_fwd(hd, case):
     from flextrain_b200.ops import attention_cuda as fa
     H, KV = 8, 2
-    window = 0
+    window, softcap = 0, 0.0
     if case == "equal":
         lens_q, lens_k = [256, 256, 256], [256, 256, 256]
     elif case == "prior_ctx":
         lens_q, lens_k = [128], [640]
     elif case == "ragged":
         lens_q, lens_k = [100, 37, 300, 1], [100, 200, 300, 129]
+    elif case == "softcap":                                # Gemma-2 logit soft-cap, deep in the tanh's curved range
+        lens_q, lens_k, window, softcap = [100, 37, 300], [100, 200, 300], 160, 2.0
     else:
         lens_q, lens_k, window = [384, 200], [384, 456], 96
     cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=DEV)
@@ -284,8 +286,8 @@ def test_attention_tcgen05_fwd(hd, case):
     wide = _rand(Tq, (H + 2 * KV) * hd)
     q = wide[:, : H * hd].unflatten(1, (H, hd))            # strided view, as in the fused QKV buffer
     k, v = _rand(Tk, KV, hd), _rand(Tk, KV, hd)
-    o, lse = fa.fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5, window=window)
-    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, scale=hd ** -0.5, window=window)
+    o, lse = fa.fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5, window=window, softcap=softcap)
+    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, scale=hd ** -0.5, window=window, softcap=softcap)
     from flextrain_b200.ops import cuda as kk
     assert kk.device_error_words().get("attention", 0) == 0
     assert _rel(o, ow) < 1e-2, (case, hd, _rel(o, ow))
@@ -293,18 +295,20 @@ def test_attention_tcgen05_fwd(hd, case):
 
 
 @pytest.mark.parametrize("hd", [128, 64])
-@pytest.mark.parametrize("case", ["equal", "prior_ctx", "ragged", "window"])
+@pytest.mark.parametrize("case", ["equal", "prior_ctx", "ragged", "window", "softcap"])
 def test_attention_tcgen05_bwd(hd, case):
     from flextrain_b200.ops import attention_cuda as fa
     from flextrain_b200.ops import cuda as kk
     H, KV = 8, 2
-    window = 0
+    window, softcap = 0, 0.0
     if case == "equal":
         lens_q, lens_k = [256, 256], [256, 256]
     elif case == "prior_ctx":
         lens_q, lens_k = [128], [640]
     elif case == "ragged":
         lens_q, lens_k = [100, 37, 300, 1], [100, 200, 300, 129]
+    elif case == "softcap":
+        lens_q, lens_k, window, softcap = [100, 37, 300], [100, 200, 300], 160, 2.0
     else:
         lens_q, lens_k, window = [384, 200], [384, 456], 96
     cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=DEV)
@@ -312,10 +316,11 @@ def test_attention_tcgen05_bwd(hd, case):
     Tq, Tk = sum(lens_q), sum(lens_k)
     q, k, v = _rand(Tq, H, hd), _rand(Tk, KV, hd), _rand(Tk, KV, hd)
     do = _rand(Tq, H, hd)
-    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, scale=hd ** -0.5, window=window)
-    wq, wk, wv = ref.attention_bwd(do, q, k, v, ow, lw, cu_q, cu_k, scale=hd ** -0.5, window=window)
-    o, lse = fa.fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5, window=window)
-    dq, dk, dv = fa.bwd(do, q, k, v, o, lse, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5, window=window)
+    kw = dict(scale=hd ** -0.5, window=window, softcap=softcap)
+    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, **kw)
+    wq, wk, wv = ref.attention_bwd(do, q, k, v, ow, lw, cu_q, cu_k, **kw)
+    o, lse = fa.fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), **kw)
+    dq, dk, dv = fa.bwd(do, q, k, v, o, lse, cu_q, cu_k, max(lens_q), max(lens_k), **kw)
     assert kk.device_error_words().get("attention", 0) == 0
     assert _rel(dq, wq) < 2e-2, (case, hd, "dq", _rel(dq, wq))
     assert _rel(dk, wk) < 2e-2, (case, hd, "dk", _rel(dk, wk))
