@@ -3,8 +3,8 @@
     python -m flextrain_b200.bench.kernel_cases gemm_fwd|gemm_dgrad|gemm_wgrad|rmsnorm_bwd|softmax_ce|attn_fwd|attn_bwd|
                                                   gdn_fwd|gdn_bwd|gdn_long_fwd
 
-Each case holds a few hundred MB on the device (inputs larger than the 126 MB L2), runs one warm-up launch and
-three timed launches with CUDA events, and prints achieved TFLOP/s or GB/s.  They are the commands behind the
+Each case holds a few hundred MB on the device (inputs larger than the 126 MB L2), runs three warm-up launches and
+ten timed launches with CUDA events, and prints achieved TFLOP/s or GB/s.  They are the commands behind the
 summaries in ``profiles/``.
 """
 from __future__ import annotations
@@ -14,8 +14,9 @@ import sys
 import torch
 
 
-def _time(fn, n=3):
-    fn()
+def _time(fn, n=10, warmup=3):
+    for _ in range(warmup):
+        fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()

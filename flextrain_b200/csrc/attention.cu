@@ -64,7 +64,7 @@ __device__ __forceinline__ uint32_t sw128_offset(int row, int col, int rows) {
   return static_cast<uint32_t>(kb * rows * 128 + row * 128 + chunk * 16 + (c & 7) * 2);
 }
 
-template <int HD>
+template <int HD, bool CAP>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -203,7 +203,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int r = quad * 32 + lane;                 // query row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const float c = p.scale * 1.4426950408889634f;  // scores are kept in log2 units
-    const bool capped = p.softcap > 0.f;
+    constexpr bool capped = CAP;   // soft-cap is a template parameter: the plain path carries no extra work
     const float cap2 = p.softcap * 1.4426950408889634f;            // soft-cap in log2 units
     const float soc = capped ? p.scale / p.softcap : 0.f;
     float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
@@ -235,8 +235,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
       }
       // tanh is monotonic: the capped maximum is the cap of the maximum
-      const float mx2 = (capped && mx != -INFINITY) ? cap2 * tanh_fast(mx * soc) : mx * c;
-      const float m_new = fmaxf(m, mx2);
+      float m_new;
+      if constexpr (CAP) m_new = fmaxf(m, mx == -INFINITY ? mx : cap2 * tanh_fast(mx * soc));
+      else m_new = fmaxf(m, mx * c);
       const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
       // fold the previous tile's P·V into the running output (this also means the P tile is free again)
       if (j > 0) {
@@ -268,9 +269,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           const int kj = key0 + cb + i;
           bool keep = kj < len_k;
           if (p.causal) keep = keep && (kj <= qi) && (p.window <= 0 || kj > qi - p.window);
-          const float raw = __uint_as_float(v[i]);
-          const float s2 = capped ? cap2 * tanh_fast(raw * soc) : raw * c;
-          pr[i] = keep ? exp2f(s2 - mref) : 0.f;
+          // two textually separate forms: the plain one must stay a single multiply-add feeding the exponential
+          if constexpr (CAP) pr[i] = keep ? exp2f(cap2 * tanh_fast(__uint_as_float(v[i]) * soc) - mref) : 0.f;
+          else pr[i] = keep ? exp2f(__uint_as_float(v[i]) * c - mref) : 0.f;
           sum += pr[i];
         }
 #pragma unroll
@@ -361,11 +362,11 @@ static int make_tmap_3d(CUtensorMap* out, const void* base, int hd, int heads, l
   return r == CUDA_SUCCESS ? 0 : -200 - static_cast<int>(r);
 }
 
-template <int HD>
+template <int HD, bool CAP>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                       int tiles, cudaStream_t s) {
   constexpr int SMEM = TQ * HD * 2 + 4 * TK * HD * 2 + TQ * TK * 2 + 256 + 1024;
-  auto kern = fa_fwd_kernel<HD>;
+  auto kern = fa_fwd_kernel<HD, CAP>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -405,8 +406,11 @@ int ftb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* 
   p.cu_q = cu_q; p.cu_k = cu_k; p.num_seqs = num_seqs; p.H = H; p.KV = KV;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.total_q = total_q;
   p.scale = scale; p.softcap = softcap; p.causal = causal; p.window = window;
-  if (hd == 128) return launch_fwd<128>(tq, tk, tv, p, max_tiles, stream);
-  return launch_fwd<64>(tq, tk, tv, p, max_tiles, stream);
+  if (softcap > 0.f)
+    return hd == 128 ? launch_fwd<128, true>(tq, tk, tv, p, max_tiles, stream)
+                     : launch_fwd<64, true>(tq, tk, tv, p, max_tiles, stream);
+  return hd == 128 ? launch_fwd<128, false>(tq, tk, tv, p, max_tiles, stream)
+                   : launch_fwd<64, false>(tq, tk, tv, p, max_tiles, stream);
 }
 
 int ftb_attn_error(void) {
@@ -464,7 +468,7 @@ __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ dout, long do_
   if (lane == 0) delta[(size_t)h * T + t] = s;
 }
 
-template <int HD>
+template <int HD, bool CAP>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
@@ -597,7 +601,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int r = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const float c = p.scale * 1.4426950408889634f;
-    const bool capped = p.softcap > 0.f;
+    constexpr bool capped = CAP;   // soft-cap is a template parameter: the plain path carries no extra work
     const float cap2 = p.softcap * 1.4426950408889634f;
     const float soc = capped ? p.scale / p.softcap : 0.f;
     bool ok = true;
@@ -730,11 +734,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   }
 }
 
-template <int HD>
+template <int HD, bool CAP>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv,
                       const BwdParams& p, int tiles, cudaStream_t s) {
   constexpr int SMEM = 4 * 128 * HD * 2 + 2 * 128 * 128 * 2 + 256 + 1024;
-  auto kern = fa_bwd_kernel<HD>;
+  auto kern = fa_bwd_kernel<HD, CAP>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -781,8 +785,12 @@ int ftb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, 
   p.cu_q = cu_q; p.cu_k = cu_k; p.num_seqs = num_seqs; p.H = H; p.KV = KV;
   p.dq_acc = dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.lse = lse; p.delta = delta;
   p.total_q = total_q; p.scale = scale; p.softcap = softcap; p.causal = causal; p.window = window;
-  rc = (hd == 128) ? launch_bwd<128>(tq, tdo, tk, tv, p, max_tiles, stream)
-                   : launch_bwd<64>(tq, tdo, tk, tv, p, max_tiles, stream);
+  if (softcap > 0.f)
+    rc = (hd == 128) ? launch_bwd<128, true>(tq, tdo, tk, tv, p, max_tiles, stream)
+                     : launch_bwd<64, true>(tq, tdo, tk, tv, p, max_tiles, stream);
+  else
+    rc = (hd == 128) ? launch_bwd<128, false>(tq, tdo, tk, tv, p, max_tiles, stream)
+                     : launch_bwd<64, false>(tq, tdo, tk, tv, p, max_tiles, stream);
   return rc;
 }
 
