@@ -142,6 +142,8 @@ class ActiveModel:
                                     tp=self.tp, ep=self.ep,
                                     param_gather=(self.dp.first_gemm if getattr(self.dp, "defer", False) else None))
                     with _nvtx("Setup Round"):
+                        if hasattr(self.embed, "setup_round"):           # multimodal: encode the round's images once
+                            self.embed.setup_round(rseqs, metas, self.device)
                         transitions, slots = self._setup_round(metas)
                     with _nvtx("Forward"):
                         self._forward_pass(metas, plan, transitions, slots, ctx_base, stats)
@@ -159,6 +161,8 @@ class ActiveModel:
                         for c, meta in enumerate(metas):
                             self.embed.backward(transitions[c], self._token_shard(meta),
                                                 self.buffers.embed_params(), self.buffers.embed_grads())
+                    if hasattr(self.embed, "finalize_round"):
+                        self.embed.finalize_round()
                     self.events.clear_per_round()
         if self.dp is not None:
             self.dp.on_embed_head_grads_ready()

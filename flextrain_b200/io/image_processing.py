@@ -1,45 +1,234 @@
-"""Image pre-processing for multimodal SFT (flextrain/io/image_processing.py:40-278): resize to a multiple of
-``patch * merge``, normalise, cut into ``temporal x patch x patch`` patches, and build a :class:`Sequence` whose
-text holds one placeholder token per merged patch."""
+"""Image pre-processing for multimodal SFT (flextrain/io/image_processing.py:40-278).
+
+The reference wraps HuggingFace's ``AutoImageProcessor``; here the Qwen-VL family's pre-processing is written out in
+torch (so a training job needs neither PIL nor the processor classes on its hot path) and is checked against
+``transformers``' ``Qwen2VLImageProcessor`` in the tests:
+
+1. *smart resize*: both sides become multiples of ``patch * merge``, the area is kept inside
+   ``[min_pixels, max_pixels]`` and the aspect ratio is preserved as well as that allows (bicubic, anti-aliased,
+   rounded back to 8-bit levels as an 8-bit image pipeline does);
+2. rescale to ``[0, 1]`` and normalise per channel;
+3. a still image is repeated to fill the temporal patch; frames of a video are grouped ``temporal_patch`` at a time;
+4. the result is cut into ``temporal_patch x patch x patch`` blocks, flattened channel-major, and ordered
+   merge-block-major: the ``merge x merge`` patches that the vision tower's merger concatenates are consecutive rows.
+
+:class:`MultimodalProcessorBundle` reads the geometry and the special token ids from a model directory
+(``preprocessor_config.json`` / ``config.json``) and, when a tokenizer is there, turns chat-style rows with images
+into multimodal :class:`Sequence` objects; :func:`build_multimodal_sequence` does the token-level assembly."""
 from __future__ import annotations
 
-from typing import List, Sequence as Seq, Tuple
+import json
+import math
+import os
+from dataclasses import dataclass, field
+from typing import Any, List, Optional, Sequence as Seq, Tuple
 
 import torch
 
 from ..core.modality import ImageInputCPU
 from .sequence import Sequence
 
-MEAN = (0.48145466, 0.4578275, 0.40821073)
-STD = (0.26862954, 0.26130258, 0.27577711)
+CLIP_MEAN = (0.48145466, 0.4578275, 0.40821073)
+CLIP_STD = (0.26862954, 0.26130258, 0.27577711)
 
 
-def patchify(img: torch.Tensor, patch: int = 14, temporal_patch: int = 2, merge: int = 2) -> ImageInputCPU:
-    """``img (3, H, W)`` float in [0, 1] → ``ImageInputCPU`` with rows ordered (merge-block-major) like the HF processor."""
-    c, H, W = img.shape
-    q = patch * merge
-    Hn, Wn = max(q, round(H / q) * q), max(q, round(W / q) * q)
-    if (Hn, Wn) != (H, W):
-        img = torch.nn.functional.interpolate(img[None], size=(Hn, Wn), mode="bicubic", align_corners=False)[0]
-    mean, std = torch.tensor(MEAN).view(3, 1, 1), torch.tensor(STD).view(3, 1, 1)
-    img = (img - mean) / std
-    frames = img[None].repeat(temporal_patch, 1, 1, 1)                       # a still image fills the temporal patch
-    gh, gw = Hn // patch, Wn // patch
-    x = frames.view(temporal_patch, c, gh // merge, merge, patch, gw // merge, merge, patch)
-    x = x.permute(2, 5, 3, 6, 1, 0, 4, 7).reshape(gh * gw, c * temporal_patch * patch * patch)
-    return ImageInputCPU(pixel_values=x.contiguous(), grid_thw=(1, gh, gw))
+def smart_resize(height: int, width: int, factor: int, min_pixels: int, max_pixels: int) -> Tuple[int, int]:
+    """Target size: multiples of ``factor``, area within ``[min_pixels, max_pixels]``, aspect ratio kept."""
+    if max(height, width) / max(min(height, width), 1) > 200:
+        raise ValueError(f"aspect ratio of a {height}x{width} image is beyond 200")
+    h = round(height / factor) * factor
+    w = round(width / factor) * factor
+    if h * w > max_pixels:
+        beta = math.sqrt(height * width / max_pixels)
+        h = max(factor, math.floor(height / beta / factor) * factor)
+        w = max(factor, math.floor(width / beta / factor) * factor)
+    elif h * w < min_pixels:
+        beta = math.sqrt(min_pixels / (height * width))
+        h = math.ceil(height * beta / factor) * factor
+        w = math.ceil(width * beta / factor) * factor
+    return max(h, factor), max(w, factor)
 
 
-def build_multimodal_sequence(text_ids_before: Seq[int], image: ImageInputCPU, text_ids_after: Seq[int],
-                              placeholder_id: int, merge: int = 2, seq_id: int = 0) -> Sequence:
-    t, gh, gw = image.grid_thw
-    n_ph = t * (gh // merge) * (gw // merge)
-    ids = list(text_ids_before) + [placeholder_id] * n_ph + list(text_ids_after)
+def _to_uint8_chw(img: Any) -> torch.Tensor:
+    """PIL image, ``(H, W, 3)`` uint8 array, or ``(3, H, W)`` tensor (uint8, or float in [0, 1]) -> ``(3, H, W)`` float
+    tensor holding 8-bit levels."""
+    if isinstance(img, torch.Tensor):
+        t = img
+        if t.dim() == 3 and t.shape[0] not in (1, 3) and t.shape[-1] in (1, 3):
+            t = t.permute(2, 0, 1)
+        t = t.to(torch.float32) * (255.0 if t.dtype.is_floating_point else 1.0)
+    else:
+        import numpy as np
+        if hasattr(img, "convert"):                    # PIL
+            img = img.convert("RGB")
+        a = np.asarray(img)
+        if a.ndim == 2:
+            a = a[:, :, None].repeat(3, axis=2)
+        t = torch.from_numpy(a.copy()).permute(2, 0, 1).to(torch.float32)
+    if t.shape[0] == 1:
+        t = t.expand(3, -1, -1)
+    return t
+
+
+@dataclass
+class ImageGeometry:
+    patch: int = 16
+    temporal_patch: int = 2
+    merge: int = 2
+    min_pixels: int = 64 * 64
+    max_pixels: int = 16 * 16 * 4 * 4096
+    mean: Tuple[float, float, float] = (0.5, 0.5, 0.5)
+    std: Tuple[float, float, float] = (0.5, 0.5, 0.5)
+
+    @property
+    def patch_dim(self) -> int:
+        return 3 * self.temporal_patch * self.patch * self.patch
+
+
+def preprocess_frames(frames: Seq[Any], g: ImageGeometry, resize: bool = True) -> ImageInputCPU:
+    """One image (a single frame) or one video clip (several frames of equal size) -> :class:`ImageInputCPU`."""
+    ts = [_to_uint8_chw(f) for f in frames]
+    H, W = ts[0].shape[-2:]
+    x = torch.stack(ts, 0)                                                     # (F, 3, H, W), 8-bit levels
+    q = g.patch * g.merge
+    if resize:
+        Hn, Wn = smart_resize(H, W, q, g.min_pixels, g.max_pixels)
+        if (Hn, Wn) != (H, W):
+            # on 8-bit data, as an image library does it (the two separable passes each saturate to 8 bits)
+            x8 = x.round().clamp_(0, 255).to(torch.uint8)
+            x = torch.nn.functional.interpolate(x8, size=(Hn, Wn), mode="bicubic", align_corners=False,
+                                                antialias=True).to(torch.float32)
+            H, W = Hn, Wn
+    elif H % q or W % q:
+        raise ValueError(f"a {H}x{W} image is not a multiple of patch*merge = {q}; pass resize=True")
+    mean, std = torch.tensor(g.mean).view(1, 3, 1, 1), torch.tensor(g.std).view(1, 3, 1, 1)
+    x = (x / 255.0 - mean) / std
+    tp = g.temporal_patch
+    if x.shape[0] % tp:
+        x = torch.cat([x, x[-1:].expand(tp - x.shape[0] % tp, -1, -1, -1)], 0)
+    gt, gh, gw = x.shape[0] // tp, H // g.patch, W // g.patch
+    m, p = g.merge, g.patch
+    x = x.view(gt, tp, 3, gh // m, m, p, gw // m, m, p)
+    x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8).reshape(gt * gh * gw, 3 * tp * p * p)
+    return ImageInputCPU(pixel_values=x.contiguous(), grid_thw=(gt, gh, gw), kind="image" if len(frames) == 1 else "video")
+
+
+def preprocess_images(images: Seq[Any], g: Optional[ImageGeometry] = None, resize: bool = True) -> List[ImageInputCPU]:
+    g = g or ImageGeometry()
+    return [preprocess_frames([im], g, resize=resize) for im in images]
+
+
+def patchify(img: torch.Tensor, patch: int = 16, temporal_patch: int = 2, merge: int = 2) -> ImageInputCPU:
+    """``img (3, H, W)`` float in [0, 1] with the default geometry otherwise; kept for callers of the first API."""
+    return preprocess_frames([img], ImageGeometry(patch=patch, temporal_patch=temporal_patch, merge=merge))
+
+
+def build_multimodal_sequence(segments: Seq[Any], image_token_id: int, merge: int = 2, seq_id: int = 0,
+                              vision_start_token_id: Optional[int] = None, vision_end_token_id: Optional[int] = None,
+                              train_on: Optional[Seq[bool]] = None) -> Sequence:
+    """Assemble token ids and images into one training sequence.
+
+    ``segments`` alternates freely between lists of token ids and :class:`ImageInputCPU` objects; every image expands
+    to ``[vision_start] + image_token * n + [vision_end]`` with ``n`` its merged patch count.  ``train_on[i]`` says
+    whether the tokens of text segment ``i`` (counting all segments) are targets; image tokens never are, and the
+    token before an image never predicts it."""
+    ids: List[int] = []
+    learn: List[bool] = []
+    images: List[ImageInputCPU] = []
+    spans = []
+    for si, seg in enumerate(segments):
+        if isinstance(seg, ImageInputCPU):
+            t, gh, gw = seg.grid_thw
+            n = seg.num_placeholders(merge)
+            if vision_start_token_id is not None:
+                ids.append(vision_start_token_id); learn.append(False)
+            seg.first_token = len(ids)
+            spans.append((len(ids), t, gh // merge, gw // merge))
+            ids += [image_token_id] * n
+            learn += [False] * n
+            if vision_end_token_id is not None:
+                ids.append(vision_end_token_id); learn.append(False)
+            images.append(seg)
+        else:
+            seg = [int(v) for v in seg]
+            ids += seg
+            learn += [True if train_on is None else bool(train_on[si])] * len(seg)
     toks = torch.tensor(ids, dtype=torch.int64)
     tgt = torch.roll(toks, -1)
     tgt[-1] = -100
-    first = len(text_ids_before)
-    tgt[max(first - 1, 0): first + n_ph] = -100                              # never predict placeholder tokens
-    return Sequence(toks, targets=tgt, seq_id=seq_id,
-                    modality_inputs={"pixel_values": image.pixel_values, "grid_thw": [image.grid_thw],
-                                     "image_spans": [(first, t, gh // merge, gw // merge)]})
+    keep = torch.tensor(learn[1:] + [False])                 # position i predicts token i + 1
+    tgt[~keep] = -100
+    mi = None
+    if images:
+        mi = {"pixel_values": torch.cat([im.pixel_values for im in images], 0),
+              "grid_thw": [tuple(im.grid_thw) for im in images], "image_spans": spans, "images": images}
+    return Sequence(toks, targets=tgt, seq_id=seq_id, modality_inputs=mi)
+
+
+@dataclass
+class MultimodalProcessorBundle:
+    """Geometry + special token ids of one model directory, and its tokenizer when ``transformers`` can load one."""
+    model_path: str
+    geometry: ImageGeometry
+    image_token_id: int
+    vision_start_token_id: Optional[int] = None
+    vision_end_token_id: Optional[int] = None
+    video_token_id: Optional[int] = None
+    tokenizer: Any = None
+    image_placeholder: str = "<|image_pad|>"
+    extra: dict = field(default_factory=dict)
+
+    @classmethod
+    def from_pretrained(cls, model_path: str, load_tokenizer: bool = True) -> "MultimodalProcessorBundle":
+        with open(os.path.join(model_path, "config.json")) as f:
+            cfg = json.load(f)
+        vc = cfg.get("vision_config") or {}
+        g = ImageGeometry(patch=int(vc.get("patch_size", 16)), temporal_patch=int(vc.get("temporal_patch_size", 2)),
+                          merge=int(vc.get("spatial_merge_size", 2)))
+        pp = os.path.join(model_path, "preprocessor_config.json")
+        if os.path.exists(pp):
+            with open(pp) as f:
+                pc = json.load(f)
+            g.patch = int(pc.get("patch_size", g.patch))
+            g.temporal_patch = int(pc.get("temporal_patch_size", g.temporal_patch))
+            g.merge = int(pc.get("merge_size", g.merge))
+            size = pc.get("size") or {}
+            g.min_pixels = int(pc.get("min_pixels", size.get("shortest_edge", g.min_pixels)))
+            g.max_pixels = int(pc.get("max_pixels", size.get("longest_edge", g.max_pixels)))
+            if pc.get("image_mean"):
+                g.mean = tuple(float(v) for v in pc["image_mean"])
+            if pc.get("image_std"):
+                g.std = tuple(float(v) for v in pc["image_std"])
+        tok = None
+        if load_tokenizer:
+            try:
+                from transformers import AutoTokenizer
+                tok = AutoTokenizer.from_pretrained(model_path)
+            except Exception:                                  # no tokenizer files: token-id level API only
+                tok = None
+        return cls(model_path=model_path, geometry=g, image_token_id=int(cfg.get("image_token_id", -1)),
+                   vision_start_token_id=cfg.get("vision_start_token_id"),
+                   vision_end_token_id=cfg.get("vision_end_token_id"), video_token_id=cfg.get("video_token_id"),
+                   tokenizer=tok)
+
+    def process_images(self, images: Seq[Any]) -> List[ImageInputCPU]:
+        return preprocess_images(images, self.geometry)
+
+    def build(self, texts: Seq[str], images: Seq[Any], seq_id: int = 0, train_on: Optional[Seq[bool]] = None) -> Sequence:
+        """``texts`` has one more entry than ``images``: text, image, text, image, ..., text.  ``train_on`` flags the
+        text pieces (default: only the last one, the answer)."""
+        if self.tokenizer is None:
+            raise RuntimeError("this model directory has no tokenizer; use build_multimodal_sequence with token ids")
+        if len(texts) != len(images) + 1:
+            raise ValueError("need len(texts) == len(images) + 1")
+        ims = self.process_images(images)
+        segs: List[Any] = []
+        flags: List[bool] = []
+        for i, t in enumerate(texts):
+            segs.append(self.tokenizer(t, add_special_tokens=False)["input_ids"])
+            flags.append((i == len(texts) - 1) if train_on is None else bool(train_on[i]))
+            if i < len(ims):
+                segs.append(ims[i])
+                flags.append(False)
+        return build_multimodal_sequence(segs, self.image_token_id, self.geometry.merge, seq_id,
+                                         self.vision_start_token_id, self.vision_end_token_id, flags)

@@ -38,7 +38,8 @@ class RopeConfig:
     def from_hf(cfg: dict, head_dim: int) -> "RopeConfig":
         """Read ``rope_theta`` / ``rope_scaling`` / ``partial_rotary_factor`` / ``mrope_section`` from an HF config."""
         rs = cfg.get("rope_scaling") or cfg.get("rope_parameters") or None
-        theta = float(cfg.get("rope_theta", (rs or {}).get("rope_theta", 10000.0)))
+        # the nested parameter set is what transformers >= 5 reads; top-level keys are the older spelling
+        theta = float((rs or {}).get("rope_theta", cfg.get("rope_theta", 10000.0)))
         sections = None
         scaling = None
         if rs:
@@ -47,5 +48,5 @@ class RopeConfig:
             kind = rs.get("rope_type", rs.get("type", "default"))
             if kind not in ("default", "mrope", None):
                 scaling = dict(rs)
-        prf = float(cfg.get("partial_rotary_factor", (rs or {}).get("partial_rotary_factor", 1.0)))
+        prf = float((rs or {}).get("partial_rotary_factor", cfg.get("partial_rotary_factor", 1.0)))
         return RopeConfig(theta=theta, scaling=scaling, partial_rotary_factor=prf, mrope_sections=sections)

@@ -1,0 +1,207 @@
+"""Multimodal path on CPU against ``transformers``: image pre-processing, the vision tower, MRoPE position ids, and
+the whole model (image + text -> loss and gradients) for a tiny random Qwen3.5 vision-language checkpoint
+(the reference's analogues: tests/test_qwen_vl_vit_forward.py, tests/test_mrope_position_ids.py,
+tests/test_concat_splice.py, tests/test_qwen3_5_mm_*.py)."""
+import json
+import os
+
+import pytest
+import torch
+
+import flextrain_b200 as ft
+from flextrain_b200.core.modality import ImageInputCPU
+from flextrain_b200.engine.host_memory import UnpinnedHostBackend
+from flextrain_b200.engine.schedule import compute_mrope_position_ids
+from flextrain_b200.io.image_processing import (ImageGeometry, MultimodalProcessorBundle, build_multimodal_sequence,
+                                                preprocess_frames, smart_resize)
+from flextrain_b200.nn.encoders.qwen_vl_vit import QwenVLViT, ViTConfig
+from flextrain_b200.nn.splices.concat import build_splice_maps, splice_backward, splice_forward
+
+transformers = pytest.importorskip("transformers")
+
+IMG, VID, VSTART, VEND = 300, 301, 302, 303
+TEXT = dict(vocab_size=320, hidden_size=64, intermediate_size=112, num_hidden_layers=4, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=16, max_position_embeddings=512, rms_norm_eps=1e-5,
+            tie_word_embeddings=False, linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16,
+            linear_num_key_heads=2, linear_num_value_heads=4, layer_types=["linear_attention", "full_attention"] * 2,
+            rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5,
+                             "mrope_section": [2, 1, 1], "mrope_interleaved": True})
+VISION = dict(depth=2, hidden_size=32, num_heads=2, intermediate_size=64, patch_size=4, temporal_patch_size=2,
+              in_channels=3, spatial_merge_size=2, out_hidden_size=64, num_position_embeddings=64,
+              hidden_act="gelu_pytorch_tanh")
+
+
+def _hf_vl_model():
+    cfg = transformers.Qwen3_5Config(text_config=dict(TEXT), vision_config=dict(VISION), image_token_id=IMG,
+                                     video_token_id=VID, vision_start_token_id=VSTART, vision_end_token_id=VEND,
+                                     tie_word_embeddings=False)
+    cfg._attn_implementation = "eager"
+    cfg.text_config._attn_implementation = "eager"
+    cfg.vision_config._attn_implementation = "eager"
+    torch.manual_seed(0)
+    model = transformers.Qwen3_5ForConditionalGeneration(cfg).to(torch.float32)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "norm" in n or n.endswith("bias"):
+                p.add_(torch.randn_like(p) * 0.1)
+            if n.endswith("A_log"):
+                p.uniform_(-1.0, 0.5)
+    return model
+
+
+def _save_hub_layout(model, path):
+    """Write the checkpoint with the hub's tensor names (``model.visual.*``, ``model.language_model.*``)."""
+    from safetensors.torch import save_file
+    os.makedirs(path, exist_ok=True)
+    save_file({k: v.detach().contiguous() for k, v in model.state_dict().items()},
+              os.path.join(path, "model.safetensors"))
+    cfg = model.config.to_dict()
+    cfg["architectures"] = ["Qwen3_5ForConditionalGeneration"]
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    with open(os.path.join(path, "preprocessor_config.json"), "w") as f:
+        json.dump({"patch_size": 4, "temporal_patch_size": 2, "merge_size": 2, "image_mean": [0.5, 0.5, 0.5],
+                   "image_std": [0.5, 0.5, 0.5], "size": {"shortest_edge": 64, "longest_edge": 4096}}, f)
+
+
+def test_image_preprocessing_matches_transformers():
+    g = ImageGeometry(patch=4, temporal_patch=2, merge=2, min_pixels=64, max_pixels=4096)
+    proc = transformers.Qwen2VLImageProcessor(patch_size=4, temporal_patch_size=2, merge_size=2,
+                                              image_mean=[0.5] * 3, image_std=[0.5] * 3,
+                                              size={"shortest_edge": 64, "longest_edge": 4096})
+    torch.manual_seed(0)
+    for H, W in [(32, 48), (24, 24), (50, 37), (90, 120)]:
+        img = torch.randint(0, 256, (3, H, W), dtype=torch.uint8)
+        want = proc(images=[img], return_tensors="pt")
+        got = preprocess_frames([img], g)
+        assert list(got.grid_thw) == want["image_grid_thw"][0].tolist(), (H, W)
+        assert tuple(got.grid_thw[1:]) == tuple(s // 4 for s in smart_resize(H, W, 8, 64, 4096))
+        # identical when no resize happens; within one 8-bit level of the torchvision bicubic otherwise
+        tol = 1e-6 if (H % 8 == 0 and W % 8 == 0 and 64 <= H * W <= 4096) else 2.5 / 255 / 0.5
+        assert float((got.pixel_values - want["pixel_values"]).abs().max()) <= tol, (H, W)
+
+
+def test_vision_tower_matches_transformers():
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5VisionConfig
+    from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5VisionModel
+    vc = Qwen3_5VisionConfig(**VISION)
+    vc._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = Qwen3_5VisionModel(vc).float().eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.add_(torch.randn_like(p) * 0.05)
+    vit = QwenVLViT(ViTConfig.from_hf(vc.to_dict()))
+    vit.load_state(dict(hf.state_dict()))
+    grids = [(1, 4, 6), (2, 8, 4), (1, 2, 2)]                  # two stills and a two-frame clip
+    px = torch.randn(sum(t * h * w for t, h, w in grids), vit.cfg.patch_dim)
+    with torch.no_grad():
+        out = hf(px, torch.tensor(grids))
+    mine, hidden = vit.encode(px, grids, return_hidden=True)
+    assert float((hidden - out.last_hidden_state).norm() / out.last_hidden_state.norm()) < 1e-5
+    assert float((mine - out.pooler_output).norm() / out.pooler_output.norm()) < 1e-5
+    assert mine.shape == (sum(vit.rows_per_image(grids)), 64)
+
+
+def _mm_sequence(seq_id, grids, seed, text_lens):
+    """text, image, text, image, ..., text with random pixels; returns the Sequence."""
+    g = torch.Generator().manual_seed(seed)
+    segs = []
+    for i, n in enumerate(text_lens):
+        segs.append(torch.randint(0, 290, (n,), generator=g).tolist())
+        if i < len(grids):
+            t, h, w = grids[i]
+            segs.append(ImageInputCPU(torch.randn(t * h * w, 3 * 2 * 4 * 4, generator=g), (t, h, w)))
+    return build_multimodal_sequence(segs, IMG, merge=2, seq_id=seq_id, vision_start_token_id=VSTART,
+                                     vision_end_token_id=VEND, train_on=[True] * len(segs))
+
+
+def test_mrope_position_ids_match_transformers():
+    model = _hf_vl_model()
+    seq = _mm_sequence(0, [(1, 4, 6), (1, 8, 4)], 3, [5, 7, 9])
+    ids = seq.tokens[None]
+    types = (ids == IMG).to(torch.int32)
+    want, _ = model.model.get_rope_index(ids, mm_token_type_ids=types,
+                                         image_grid_thw=torch.tensor(seq.modality_inputs["grid_thw"]))
+    got = compute_mrope_position_ids(seq, 0, len(seq))
+    assert torch.equal(got.to(torch.int64).t(), want[:, 0])
+    # a slice of the sequence (a chunk that starts inside the first image) sees the same positions
+    assert torch.equal(compute_mrope_position_ids(seq, 9, 20), got[9:29])
+
+
+def test_concat_splice_maps_and_gradients():
+    a = _mm_sequence(0, [(1, 4, 4)], 1, [3, 2])                # 3 text, start, 4 placeholders, end, 2 text
+    b = _mm_sequence(1, [], 2, [6])
+    seqs = [a, b]
+    # chunk 0: first 6 tokens of a (2 placeholders); chunk 1: rest of a, then b
+    pieces = [[(0, 0, 6)], [(0, 6, len(a) - 6), (1, 0, 6)]]
+    maps = build_splice_maps(seqs, pieces, [IMG], {0: 10})
+    assert maps[0][0].tolist() == [4, 5] and maps[0][1].tolist() == [10, 11]
+    assert maps[1][0].tolist() == [0, 1] and maps[1][1].tolist() == [12, 13]
+    x = torch.zeros(6, 8)
+    enc = torch.arange(14 * 8, dtype=torch.float32).view(14, 8)
+    y = splice_forward(x, maps[0][0], enc[maps[0][1]])
+    assert torch.equal(y[4], enc[10]) and torch.equal(y[5], enc[11]) and float(y[:4].abs().sum()) == 0
+    dx = torch.ones(6, 8)
+    dx, d_enc = splice_backward(dx, maps[0][0], want_encoder_grad=True)
+    assert float(dx[4:].abs().sum()) == 0 and float(dx[:4].sum()) == 32 and d_enc.shape == (2, 8)
+
+
+@pytest.mark.parametrize("chunk", [256, 32])
+def test_vision_language_model_matches_transformers(tmp_path, chunk):
+    """Loss and text-side gradients of image + text sequences; ``chunk=32`` cuts sequences (and images) across
+    chunks, so the rolling KV window, the recurrent state and the splice maps all cross chunk borders."""
+    model = _hf_vl_model()
+    _save_hub_layout(model, str(tmp_path))
+    seqs = [_mm_sequence(0, [(1, 4, 6), (1, 8, 4)], 3, [5, 7, 9]), _mm_sequence(1, [(1, 4, 4)], 4, [11, 6]),
+            _mm_sequence(2, [], 5, [40])]
+    # ---- transformers
+    model.zero_grad()
+    total = 0.0
+    for s in seqs:
+        ids = s.tokens[None]
+        kw = {}
+        if s.modality_inputs:
+            kw = dict(pixel_values=s.modality_inputs["pixel_values"],
+                      image_grid_thw=torch.tensor(s.modality_inputs["grid_thw"]),
+                      mm_token_type_ids=(ids == IMG).to(torch.int32))
+        logits = model(input_ids=ids, **kw).logits[0].float()
+        total = total + torch.nn.functional.cross_entropy(logits, s.targets, ignore_index=-100, reduction="sum")
+    total.backward()
+    # ---- engine
+    am = ft.from_pretrained(str(tmp_path), optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32), max_seq_len=128,
+                            max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
+                            device="cpu", compute_dtype=torch.float32, master_dtype=torch.float32,
+                            grad_dtype=torch.float32, host_backend=UnpinnedHostBackend(), enable_multimodal=True,
+                            working_set=ft.WorkingSetConfig.simple(max_seq_len=128, max_global_batch_tokens=256,
+                                                                   chunk=chunk, round_tokens=256))
+    assert am.embed.num_vision_layers() == 2
+    st = am.fwd_bwd(seqs, loss_scale_factor=1.0)
+    assert abs(st.loss_sum - float(total)) / float(total) < 2e-4, (st.loss_sum, float(total))
+    assert am.embed.last_summary.n_images == 3 and am.embed.last_summary.n_image_tokens == 6 + 8 + 4
+    sd = dict(model.named_parameters())
+    g_embed = am.buffers.embed_grads()["g_tok_embeddings"]
+    want = sd["model.language_model.embed_tokens.weight"].grad
+    assert float((g_embed - want).norm() / want.norm()) < 2e-3
+    assert float(g_embed[IMG].abs().max()) == 0.0              # placeholder rows never reach the embedding table
+    g_head = am.buffers.head_grads()["g_head_proj"]
+    assert float((g_head - sd["lm_head.weight"].grad).norm() / sd["lm_head.weight"].grad.norm()) < 2e-3
+    g_o = am.buffers.grads(1)["g_o"]
+    want = sd["model.language_model.layers.1.self_attn.o_proj.weight"].grad
+    assert float((g_o - want).norm() / want.norm()) < 2e-3
+
+
+def test_processor_bundle_reads_geometry_and_ids(tmp_path):
+    model = _hf_vl_model()
+    _save_hub_layout(model, str(tmp_path))
+    b = MultimodalProcessorBundle.from_pretrained(str(tmp_path), load_tokenizer=False)
+    assert (b.geometry.patch, b.geometry.temporal_patch, b.geometry.merge) == (4, 2, 2)
+    assert (b.geometry.min_pixels, b.geometry.max_pixels) == (64, 4096)
+    assert (b.image_token_id, b.vision_start_token_id, b.vision_end_token_id) == (IMG, VSTART, VEND)
+    ims = b.process_images([torch.randint(0, 256, (3, 32, 48), dtype=torch.uint8)])
+    assert ims[0].grid_thw == (1, 8, 12) and ims[0].pixel_values.shape == (96, 96)
+    s = build_multimodal_sequence([[1, 2, 3], ims[0], [4, 5]], b.image_token_id, b.geometry.merge, 0,
+                                  b.vision_start_token_id, b.vision_end_token_id, train_on=[False, False, True])
+    assert len(s) == 3 + 1 + 24 + 1 + 2
+    assert s.modality_inputs["image_spans"] == [(4, 1, 4, 6)]
+    assert (s.targets != -100).sum() == 1 + 1                  # vision_end predicts 4, 4 predicts 5
