@@ -136,3 +136,28 @@ def test_long_sequence_with_host_offload_bf16_tracks_fp32(ws_kw, force):
         b = gpu.fwd_bwd(seqs); gpu.step()
         assert abs(a.loss - b.loss) < 0.04, (step, a.loss, b.loss)
     gpu.destroy()
+
+
+def test_multimodal_bf16_tracks_fp32(tmp_path):
+    """Image + text sequences on the GPU (vision tower in bf16 through SDPA, MRoPE through the RoPE kernel, splice by
+    index copy) against the fp32 CPU engine on the same tiny random vision-language checkpoint."""
+    pytest.importorskip("transformers")
+    from flextrain_b200.engine.host_memory import UnpinnedHostBackend
+    from test_multimodal_cpu import _hf_vl_model, _mm_sequence, _save_hub_layout
+    _save_hub_layout(_hf_vl_model(), str(tmp_path))
+    common = dict(max_seq_len=128, max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
+                  enable_multimodal=True,
+                  working_set=ft.WorkingSetConfig.simple(max_seq_len=128, max_global_batch_tokens=256, chunk=64,
+                                                         round_tokens=256))
+    cpu = ft.from_pretrained(str(tmp_path), optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32), device="cpu",
+                             compute_dtype=torch.float32, master_dtype=torch.float32, grad_dtype=torch.float32,
+                             host_backend=UnpinnedHostBackend(), **common)
+    gpu = ft.from_pretrained(str(tmp_path), optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32), device="cuda:0",
+                             **common)
+    seqs = [_mm_sequence(0, [(1, 4, 6), (1, 8, 4)], 3, [5, 7, 60]), _mm_sequence(1, [(1, 4, 4)], 4, [11, 70]),
+            _mm_sequence(2, [], 5, [40])]
+    for step in range(3):
+        a = cpu.fwd_bwd(seqs); cpu.step()
+        b = gpu.fwd_bwd(seqs); gpu.step()
+        assert abs(a.loss - b.loss) < 0.05, (step, a.loss, b.loss)
+    assert gpu.embed.last_summary.n_images == 3

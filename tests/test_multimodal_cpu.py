@@ -205,3 +205,44 @@ def test_processor_bundle_reads_geometry_and_ids(tmp_path):
     assert len(s) == 3 + 1 + 24 + 1 + 2
     assert s.modality_inputs["image_spans"] == [(4, 1, 4, 6)]
     assert (s.targets != -100).sum() == 1 + 1                  # vision_end predicts 4, 4 predicts 5
+
+
+def test_multimodal_training_follows_transformers_forward(tmp_path):
+    """The engine owns the loop (vision tower frozen); before every step its current language-model weights are
+    copied into the ``transformers`` model, which must give the same loss on the same batch.  The loss must also go
+    down on the repeated batch (the reference's analogue: tests/test_qwen3_5_mm_train_parity.py)."""
+    from flextrain_b200.io.hf_weights import collect_hf_state
+    model = _hf_vl_model()
+    _save_hub_layout(model, str(tmp_path))
+    am = ft.from_pretrained(str(tmp_path), optimizer=ft.AdamW(lr=2e-3, state_dtype=torch.float32), max_seq_len=128,
+                            max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
+                            device="cpu", compute_dtype=torch.float32, master_dtype=torch.float32,
+                            grad_dtype=torch.float32, host_backend=UnpinnedHostBackend(), enable_multimodal=True,
+                            working_set=ft.WorkingSetConfig.simple(max_seq_len=128, max_global_batch_tokens=256))
+    seqs = [_mm_sequence(0, [(1, 4, 6)], 3, [5, 30]), _mm_sequence(1, [(1, 4, 4), (1, 2, 2)], 4, [8, 6, 20])]
+    visual_before = {n: p.detach().clone() for n, p in model.named_parameters() if ".visual." in n}
+    losses = []
+    for step in range(4):
+        state = collect_hf_state(am)                           # text-model names: model.layers..., lm_head.weight
+        remap = {(k.replace("model.", "model.language_model.", 1) if k.startswith("model.") else k): v
+                 for k, v in state.items()}
+        missing = model.load_state_dict(remap, strict=False).missing_keys
+        assert all(".visual." in k for k in missing), missing
+        total = 0.0
+        with torch.no_grad():
+            for s in seqs:
+                ids = s.tokens[None]
+                logits = model(input_ids=ids, pixel_values=s.modality_inputs["pixel_values"],
+                               image_grid_thw=torch.tensor(s.modality_inputs["grid_thw"]),
+                               mm_token_type_ids=(ids == IMG).to(torch.int32)).logits[0].float()
+                total += float(torch.nn.functional.cross_entropy(logits, s.targets, ignore_index=-100,
+                                                                 reduction="sum"))
+        st = am.fwd_bwd(seqs)
+        am.step()
+        assert abs(st.loss_sum - total) / total < 3e-4, (step, st.loss_sum, total)
+        losses.append(st.loss)
+    assert losses[-1] < losses[0] - 0.05, losses
+    vit = am.embed.encoders["image"]
+    for n, p in visual_before.items():                         # the frozen tower did not move
+        mine = vit.w[n.split(".visual.", 1)[1]]
+        assert torch.equal(mine.reshape(-1), p.reshape(-1)), n
