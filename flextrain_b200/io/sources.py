@@ -119,8 +119,11 @@ class ShardTokenSource(_QueueMixin):
     documents are cut into ``seq_len`` windows (flextrain/io/sources.py:861)."""
     MAGIC = 20240520
 
-    def __init__(self, pattern: str, seq_len: int, loop: bool = True, vocab_size: Optional[int] = None):
-        self.files = sorted(glob.glob(pattern)) if any(c in pattern for c in "*?[") else [pattern]
+    def __init__(self, pattern, seq_len: int, loop: bool = True, vocab_size: Optional[int] = None):
+        if isinstance(pattern, (list, tuple)):                 # explicit shard list, kept in the given order
+            self.files = [str(p) for p in pattern]
+        else:
+            self.files = sorted(glob.glob(pattern)) if any(c in pattern for c in "*?[") else [pattern]
         if not self.files:
             raise FileNotFoundError(f"no shard matches {pattern!r}")
         self.seq_len, self.loop, self.vocab_size = seq_len, loop, vocab_size

@@ -1,0 +1,103 @@
+"""Command-line entry points on CPU with tiny models: ``python -m flextrain_b200 {info, init, pretrain}`` with the
+reference's flag spellings (flextrain/scripts/pretrain.py:518-571, flextrain/scripts/init_hf.py) and this
+package's shorter aliases."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from flextrain_b200.scripts.pretrain import lr_at, parse_count, resolve_shards
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(*argv, timeout=600):
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, "-m", "flextrain_b200", *argv], capture_output=True, text=True, env=env,
+                       timeout=timeout, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    return r.stdout
+
+
+def _write_shards(d, vocab=200):
+    rng = np.random.default_rng(0)
+    os.makedirs(d, exist_ok=True)
+    for kind, idx in (("train", 1), ("train", 2), ("val", 0)):
+        toks = rng.integers(0, vocab, size=6000, dtype=np.uint16)
+        head = np.zeros(256, dtype=np.int32)
+        head[0], head[1], head[2] = 20240520, 1, toks.size
+        with open(os.path.join(d, f"fineweb_{kind}_{idx:06d}.bin"), "wb") as f:
+            f.write(head.tobytes())
+            f.write(toks.tobytes())
+
+
+def test_helpers(tmp_path):
+    assert parse_count("1B") == 10 ** 9 and parse_count("250M") == 250_000_000 and parse_count("16384") == 16384
+    assert parse_count("2.5e3") == 2500 and parse_count("3k") == 3000
+    assert lr_at(1, 100, 1.0, 0.1) == pytest.approx(0.1) and lr_at(10, 100, 1.0, 0.1) == pytest.approx(1.0)
+    assert lr_at(100, 100, 1.0, 0.1) == pytest.approx(0.1)
+    d = str(tmp_path / "data")
+    _write_shards(d)
+    assert [os.path.basename(p) for p in resolve_shards(d, "1-99", "train")] == ["fineweb_train_000001.bin",
+                                                                                  "fineweb_train_000002.bin"]
+    assert len(resolve_shards(d, "0", "val")) == 1
+    assert len(resolve_shards(None, os.path.join(d, "fineweb_train_*.bin"), "train")) == 2
+    with pytest.raises(FileNotFoundError):
+        resolve_shards(d, "7-9", "train")
+
+
+def test_info_lists_architectures():
+    out = _run("info")
+    assert "architectures:" in out and "gemma4" in out and "qwen3_5_moe" in out
+
+
+def test_pretrain_with_reference_flags_then_skip(tmp_path):
+    d, out = str(tmp_path / "data"), str(tmp_path / "run")
+    _write_shards(d)
+    argv = ["pretrain", "--arch", "llama", "--d-model", "64", "--n-layers", "2", "--vocab-size", "200", "--head-dim", "16",
+            "--n-kv-heads", "2", "--total-tokens", "2K", "--batch-tokens", "256", "--max-seq-len", "64",
+            "--data-dir", d, "--train-shards", "1-99", "--val-shard", "0", "--out", out, "--peak-lr", "3e-3",
+            "--warmup-frac", "0.25", "--weight-decay", "0.0", "--init-seed", "7", "--eval-every", "4",
+            "--eval-tokens", "256", "--log-every", "2", "--max-gpu-gib", "4", "--max-host-gib", "4"]
+    _run(*argv)
+    meta = json.load(open(os.path.join(out, "meta.json")))
+    assert meta["total_steps"] == 8 and meta["dims"]["n_heads"] == 4 and meta["dims"]["expert_dim"] == 176
+    train = [json.loads(l) for l in open(os.path.join(out, "train.jsonl"))]
+    assert [r["step"] for r in train] == [1, 2, 4, 6, 8] and all(r["tok_per_s"] > 0 for r in train)
+    assert train[0]["lr"] == pytest.approx(3e-3 / 2)
+    ev = [json.loads(l) for l in open(os.path.join(out, "eval.jsonl"))]
+    assert [r["step"] for r in ev] == [4, 8] and ev[0]["val_ppl"] == pytest.approx(np.exp(ev[0]["val_loss"]), rel=1e-6)
+    fin = json.load(open(os.path.join(out, "final.json")))
+    assert fin["steps"] == 8 and fin["tokens"] == 8 * 256 and fin["val_loss"] is not None
+    assert "nothing to do" in _run(*argv)                       # final.json exists: the run is skipped
+
+
+def test_pretrain_flop_budget_and_named_dims(tmp_path):
+    d, out = str(tmp_path / "data"), str(tmp_path / "run")
+    _write_shards(d)
+    dims = {"tiny": {"arch": "qwen3", "vocab_size": 200, "n_layers": 2, "d_model": 64, "n_heads": 4, "n_kv_heads": 2,
+                     "head_dim": 16, "expert_dim": 128, "ffn_dim": 128, "num_routed_experts": 0, "top_k": 0,
+                     "num_shared_experts": 0, "is_causal": True}}
+    dj = str(tmp_path / "dims.json")
+    json.dump(dims, open(dj, "w"))
+    _run("pretrain", "--dims-json", dj, "--model-name", "tiny", "--total-flops", "6e8", "--batch-tokens", "256",
+         "--max-seq-len", "64", "--train-shards", os.path.join(d, "fineweb_train_*.bin"), "--out", out,
+         "--log-every", "1", "--use-muon")
+    meta = json.load(open(os.path.join(out, "meta.json")))
+    assert meta["arch"] == "qwen3" and meta["optimizer"] == "muon+adamw"
+    assert meta["total_tokens"] == int(np.ceil(6e8 / (6.0 * meta["n_params"])))
+    fin = json.load(open(os.path.join(out, "final.json")))
+    assert fin["val_loss"] is None and fin["steps"] == meta["total_steps"]
+
+
+def test_init_writes_a_loadable_hf_directory(tmp_path):
+    out = str(tmp_path / "m")
+    _run("init", "--arch", "gemma3", "--d-model", "64", "--n-layers", "2", "--vocab-size", "200", "--head-dim", "16",
+         "--layer-pattern", "SF", "--out", out, "--dtype", "float32")
+    cfg = json.load(open(os.path.join(out, "config.json")))
+    assert cfg["model_type"] == "gemma3_text" and cfg["num_hidden_layers"] == 2
+    assert cfg["layer_types"] == ["sliding_attention", "full_attention"]
+    assert os.path.exists(os.path.join(out, "model.safetensors"))
