@@ -8,7 +8,66 @@ import json
 import os
 from typing import Iterable, Optional
 
-from .sources import normalise_sft_record
+DEFAULT_PATTERNS = ["*.json", "*.safetensors", "*.model", "*.txt", "*.jinja", "*.tiktoken"]
+
+
+def _looks_complete(target: str) -> bool:
+    """A model directory is usable when it has a config and every shard its index (if any) names."""
+    if not os.path.exists(os.path.join(target, "config.json")):
+        return False
+    idx = os.path.join(target, "model.safetensors.index.json")
+    if os.path.exists(idx):
+        with open(idx) as f:
+            shards = set(json.load(f).get("weight_map", {}).values())
+        return all(os.path.exists(os.path.join(target, s)) for s in shards)
+    return any(n.endswith(".safetensors") for n in os.listdir(target))
+
+
+def download_model(repo_id: str, target: str, revision: Optional[str] = None,
+                   allow_patterns: Optional[Iterable[str]] = None, force: bool = False) -> str:
+    """Mirror an HF model repository into ``target`` (explicit path, created if needed).  A target that already looks
+    complete is left alone unless ``force``."""
+    if not force and os.path.isdir(target) and _looks_complete(target):
+        return target
+    try:
+        from huggingface_hub import snapshot_download
+    except ImportError as e:
+        raise FileNotFoundError(f"{target} is incomplete and huggingface_hub is not installed") from e
+    os.makedirs(target, exist_ok=True)
+    try:
+        snapshot_download(repo_id, local_dir=target, revision=revision,
+                          allow_patterns=list(allow_patterns) if allow_patterns else DEFAULT_PATTERNS)
+    except Exception as e:
+        raise FileNotFoundError(f"could not download {repo_id!r} (offline?): {e}") from e
+    return target
+
+
+def download_dataset(spec: str, target: str, split: str = "train", config: Optional[str] = None,
+                     force: bool = False, limit: Optional[int] = None) -> str:
+    """Write an SFT dataset (local JSON / JSONL file, or HF dataset id) as normalised JSONL at ``target``."""
+    if force and os.path.exists(target):
+        os.remove(target)
+    return materialize_sft_dataset(spec if os.path.exists(spec) or ":" in spec else f"{spec}:{split}", target, limit,
+                                   config=config)
+
+
+def normalise_sft_record(rec: dict) -> Optional[dict]:
+    """Accepts ``instruction/output``, ``prompt/completion``, ``question/answer`` or chat ``messages``."""
+    for a, b in (("instruction", "output"), ("prompt", "completion"), ("question", "answer"), ("input", "output"),
+                 ("instruction", "response")):
+        if a in rec and b in rec:
+            ins = rec[a]
+            if a == "instruction" and rec.get("input"):
+                ins = f"{ins}\n{rec['input']}"
+            return {"instruction": str(ins), "response": str(rec[b])}
+    msgs = rec.get("messages") or rec.get("conversations")
+    if msgs:
+        user = [m for m in msgs if m.get("role", m.get("from")) in ("user", "human")]
+        asst = [m for m in msgs if m.get("role", m.get("from")) in ("assistant", "gpt")]
+        if user and asst:
+            return {"instruction": str(user[0].get("content", user[0].get("value", ""))),
+                    "response": str(asst[0].get("content", asst[0].get("value", ""))), "messages": msgs}
+    return None
 
 
 def maybe_download_hf_snapshot(repo_id: str, models_dir: str = "models") -> str:
@@ -28,7 +87,7 @@ def maybe_download_hf_snapshot(repo_id: str, models_dir: str = "models") -> str:
         raise FileNotFoundError(f"could not download {repo_id!r} (offline?): {e}") from e
 
 
-def materialize_sft_dataset(spec: str, out_path: str, limit: Optional[int] = None) -> str:
+def materialize_sft_dataset(spec: str, out_path: str, limit: Optional[int] = None, config: Optional[str] = None) -> str:
     """Normalise a dataset to JSONL records ``{"instruction", "response"}``.
 
     ``spec`` is a local JSON / JSONL file or an HF dataset id (``name`` or ``name:split``).  Accepted schemas:
@@ -46,7 +105,7 @@ def materialize_sft_dataset(spec: str, out_path: str, limit: Optional[int] = Non
         except ImportError as e:
             raise FileNotFoundError(f"{spec!r} is not a file and the `datasets` package is not installed") from e
         name, _, split = spec.partition(":")
-        records = datasets.load_dataset(name, split=split or "train")
+        records = datasets.load_dataset(name, config, split=split or "train")
     os.makedirs(os.path.dirname(out_path) or ".", exist_ok=True)
     n = 0
     with open(out_path, "w") as f:

@@ -153,23 +153,7 @@ class ShardTokenSource(_QueueMixin):
 PROMPT_TEMPLATE = "Instruction:\n{instruction}\n\nResponse:\n"
 
 
-def normalise_sft_record(rec: dict) -> Optional[Dict[str, str]]:
-    """Accepts ``instruction/output``, ``prompt/completion``, ``question/answer`` or chat ``messages``."""
-    for a, b in (("instruction", "output"), ("prompt", "completion"), ("question", "answer"), ("input", "output"),
-                 ("instruction", "response")):
-        if a in rec and b in rec:
-            ins = rec[a]
-            if a == "instruction" and rec.get("input"):
-                ins = f"{ins}\n{rec['input']}"
-            return {"instruction": str(ins), "response": str(rec[b])}
-    msgs = rec.get("messages") or rec.get("conversations")
-    if msgs:
-        user = [m for m in msgs if m.get("role", m.get("from")) in ("user", "human")]
-        asst = [m for m in msgs if m.get("role", m.get("from")) in ("assistant", "gpt")]
-        if user and asst:
-            return {"instruction": str(user[0].get("content", user[0].get("value", ""))),
-                    "response": str(asst[0].get("content", asst[0].get("value", ""))), "messages": msgs}
-    return None
+from .download import normalise_sft_record  # noqa: E402  (pure Python; lives where login-node tools can load it)
 
 
 class JsonSFTTokenSource(_QueueMixin):

@@ -101,3 +101,25 @@ def test_init_writes_a_loadable_hf_directory(tmp_path):
     assert cfg["model_type"] == "gemma3_text" and cfg["num_hidden_layers"] == 2
     assert cfg["layer_types"] == ["sliding_attention", "full_attention"]
     assert os.path.exists(os.path.join(out, "model.safetensors"))
+
+
+def test_download_cli_stages_local_dataset_and_keeps_complete_models(tmp_path):
+    """``download.py`` runs without importing the package; a local dataset is normalised to JSONL, and a model target
+    that is already complete is left alone (no network is touched)."""
+    src = tmp_path / "raw.json"
+    json.dump([{"prompt": "2+2?", "completion": "4"}, {"messages": [{"role": "user", "content": "hi"},
+                                                                   {"role": "assistant", "content": "hello"}]},
+               {"unrelated": 1}], open(src, "w"))
+    tgt = tmp_path / "out" / "sft.jsonl"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "download.py"), "dataset", str(src), "--target", str(tgt)],
+                       capture_output=True, text=True, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = [json.loads(l) for l in open(tgt)]
+    assert rows[0] == {"instruction": "2+2?", "response": "4"} and len(rows) == 2
+    model = tmp_path / "m"
+    model.mkdir()
+    json.dump({}, open(model / "config.json", "w"))
+    (model / "model.safetensors").write_bytes(b"")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "download.py"), "model", "org/name", "--target", str(model)],
+                       capture_output=True, text=True, cwd=str(tmp_path))
+    assert r.returncode == 0 and r.stdout.strip() == str(model), r.stderr[-2000:]
