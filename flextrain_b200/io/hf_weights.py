@@ -36,6 +36,9 @@ class ArchSpec:
     head: Callable[[object], List[WeightMapEntry]]
     layer: Callable[[int, object], List[WeightMapEntry]]
     hf_architectures: Sequence[str] = ()
+    # optional: ``export_hook(state, model_config) -> state`` runs on the collected ``{hf_name: tensor}`` dict, for
+    # checkpoints that fuse several engine tensors into one (the reference's ``pre_export_hook``)
+    export_hook: Optional[Callable[[Dict[str, torch.Tensor], object], Dict[str, torch.Tensor]]] = None
 
 
 class SafetensorsDir:
@@ -196,6 +199,8 @@ def collect_hf_state(am, lora_merge: bool = False) -> Dict[str, torch.Tensor]:
     if am.head.tied or mc.tie_embeddings:
         head_entries = [e for e in head_entries if e.name != "w_head_proj"]
     emit(head_entries, bm.head_params(), by_name(am.head.param_spec))
+    if spec.export_hook is not None:
+        out = spec.export_hook(out, mc)
     return out
 
 
