@@ -132,3 +132,37 @@ def test_fastcall_module_binds_and_calls():
     with pytest.raises(OSError):
         mod.bind("/nonexistent/libnothing.so")
     mod.bind(str(lib_path("gemm_tcgen05")))
+
+
+def _catalogue():
+    import json
+    import os
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(here, "flextrain_b200", "configs", "model_dims.json")) as f:
+        return json.load(f)
+
+
+@pytest.mark.parametrize("name", sorted(_catalogue()))
+def test_every_packaged_model_plans(name):
+    """Every entry of the packaged catalogue resolves to its family and gets a plan for one and for eight 180 GB GPUs
+    (``plan_only``: nothing is allocated); models that cannot fit one GPU must say so with an error, not a crash."""
+    from flextrain_b200.core.sizing import model_param_count
+    dims = dict(_catalogue()[name])
+    arch, hyper = dims.pop("arch"), dims.pop("hyperparams", None)
+    kw = dict(arch=arch, hyperparams=hyper, optimizer=ft.AdamW(state_dtype=torch.float32), max_seq_len=1024,
+              max_global_batch_tokens=65536, max_gpu_mem_bytes=178 << 30, max_host_mem_bytes=512 << 30,
+              device="cpu", plan_only=True)
+    n = model_param_count({"n_kv_heads": dims.get("n_heads"), **dims})
+    assert n > 0
+    try:
+        ws8 = ft.from_dims(dims, world_size=8, rank=0, **kw)
+    except ValueError:            # too large for replicated bf16 weights + gradients: shard the model itself
+        split = {"ep": 8} if dims.get("num_routed_experts") else {"tp": 8}
+        ws8 = ft.from_dims(dims, world_size=8, rank=0, **split, **kw)
+        assert n > 30e9, (name, n)
+    assert ws8.world_size == 8 and ws8.max_chunk_size >= 1024 and ws8.est_step_ms > 0
+    try:
+        ws1 = ft.from_dims(dims, **kw)
+        assert ws1.target_round_tokens * ws1.target_num_rounds >= 65536 or ws1.target_num_rounds >= 1
+    except ValueError as e:                                    # e.g. the 70B / 80B entries on one GPU
+        assert "fit" in str(e).lower() or "memory" in str(e).lower() or "budget" in str(e).lower(), str(e)
