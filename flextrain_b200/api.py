@@ -93,6 +93,7 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
                      verbose=verbose, dp=dp, tp=tp_group, ep=ep_group, model_dir=model_dir, host_backend=host_backend)
     am.model_config = mc
     am.is_causal = mc.is_causal
+    am.rank, am.world_size = rank, world_size
     return am
 
 

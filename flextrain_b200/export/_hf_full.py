@@ -9,13 +9,15 @@ import os
 from typing import Optional
 
 from ..io.arch import select_arch_module
-from ..io.hf_weights import collect_hf_state
+from ..io.hf_weights import collect_hf_state, is_export_writer
 from ._common import copy_aux_files, write_sharded_safetensors
 
 
 def save_hf_full(am, out_dir: str, *, max_shard_bytes: int = 5 << 30, source_dir: Optional[str] = None,
                  _merge_lora: bool = False) -> str:
-    state = collect_hf_state(am, lora_merge=_merge_lora)
+    state = collect_hf_state(am, lora_merge=_merge_lora)          # collective under tensor / expert parallelism
+    if not is_export_writer(am):
+        return out_dir
     write_sharded_safetensors(state, out_dir, max_shard_bytes)
     src = source_dir or am.model_dir
     cfg = None

@@ -161,8 +161,15 @@ def _peek(entry: WeightMapEntry, src: SafetensorsDir):
     return None
 
 
+def is_export_writer(am) -> bool:
+    """Rank 0 writes export files; the other ranks only take part in gathering tensor- / expert-parallel parts."""
+    return int(getattr(am, "rank", 0) or 0) == 0
+
+
 def collect_hf_state(am, lora_merge: bool = False) -> Dict[str, torch.Tensor]:
-    """Engine masters → ``{hf_name: cpu tensor}`` (inverse of the load map)."""
+    """Engine masters → ``{hf_name: cpu tensor}`` (inverse of the load map).  Under tensor / expert parallelism this is
+    a collective: every rank calls it; ranks other than the writer skip the tensors they hold completely and return
+    only what they helped to gather."""
     from .arch import select_arch_module
     mc = am.model_config
     spec: ArchSpec = select_arch_module(mc.arch).ARCH_SPEC
@@ -171,12 +178,16 @@ def collect_hf_state(am, lora_merge: bool = False) -> Dict[str, torch.Tensor]:
     if getattr(am, "dp", None) is not None and hasattr(am.dp, "finish_param_gather"):
         am.dp.finish_param_gather()         # deferred parameter all-gather: make every rank's copy current first
 
+    writer = is_export_writer(am)
+
     def emit(entries: List[WeightMapEntry], params: Dict[str, torch.Tensor], specs=None):
         for e in entries:
             if e.name not in params:
                 continue
             t = params[e.name].detach()
             ts_spec = specs.get(e.name) if specs is not None else None
+            if not writer and not (ts_spec is not None and ts_spec.is_local_part):
+                continue
             if ts_spec is not None and ts_spec.is_local_part:
                 t = gather_local_parts(t, ts_spec, am)     # collective: every rank takes part in the export
             t = t.to("cpu")
@@ -199,7 +210,7 @@ def collect_hf_state(am, lora_merge: bool = False) -> Dict[str, torch.Tensor]:
     if am.head.tied or mc.tie_embeddings:
         head_entries = [e for e in head_entries if e.name != "w_head_proj"]
     emit(head_entries, bm.head_params(), by_name(am.head.param_spec))
-    if spec.export_hook is not None:
+    if spec.export_hook is not None and writer:
         out = spec.export_hook(out, mc)
     return out
 
@@ -224,5 +235,7 @@ def export_model_safetensors(am, out_dir: str, filename: str = "final.safetensor
     if torch.device(am.device).type == "cuda":
         torch.cuda.synchronize()
     path = os.path.join(out_dir, filename)
-    save_file(collect_hf_state(am), path, metadata={"format": "pt"})
+    state = collect_hf_state(am)
+    if is_export_writer(am):
+        save_file(state, path, metadata={"format": "pt"})
     return path

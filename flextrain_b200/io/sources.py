@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import collections
 import glob
+import itertools
 import json
 import os
 import queue
@@ -70,6 +71,18 @@ class _QueueMixin:
             if s is None:
                 return
             yield s
+
+
+class RankStridedSource(_QueueMixin):
+    """Data-parallel view of a source: rank ``r`` of ``n`` sees sequences ``r, r + n, r + 2n, ...`` of the wrapped
+    source, so ranks that read the same files train on disjoint data."""
+
+    def __init__(self, source, rank: int, world: int):
+        if not 0 <= rank < world:
+            raise ValueError(f"rank {rank} outside world {world}")
+        self.source, self.rank, self.world = source, rank, world
+        self._init_queue()
+        self._it = itertools.islice(source.iter_sequences(), rank, None, world)
 
 
 class SyntheticTokenSource(_QueueMixin):

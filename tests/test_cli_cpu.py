@@ -123,3 +123,43 @@ def test_download_cli_stages_local_dataset_and_keeps_complete_models(tmp_path):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "download.py"), "model", "org/name", "--target", str(model)],
                        capture_output=True, text=True, cwd=str(tmp_path))
     assert r.returncode == 0 and r.stdout.strip() == str(model), r.stderr[-2000:]
+
+
+def _steps(out):
+    import re
+    return [float(m) for m in re.findall(r"\[step\s+\d+\].*? loss ([\d.]+)", out)]
+
+
+def test_train_tensor_parallel_matches_single_rank_and_saves(tmp_path):
+    """``train.py --tp 2`` (two gloo ranks on CPU): the ranks of a tensor-parallel group read the same batch, the
+    reported loss is the whole batch's, and ``--save`` (a collective gather of the parts) completes and writes one
+    file that holds the unsharded tensors."""
+    from safetensors import safe_open
+    common = ["--model", "dims:tiny_llama", "--mode", "full", "--data-source", "synthetic", "--max-seq-len", "128",
+              "--max-global-batch-tokens", "512", "--steps", "3", "--lr", "1e-3"]
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
+    one = subprocess.run([sys.executable, os.path.join(ROOT, "train.py"), *common, "--output-dir", str(tmp_path / "a")],
+                         capture_output=True, text=True, env=env, timeout=600, cwd=str(tmp_path))
+    assert one.returncode == 0, one.stderr[-3000:]
+    two = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29641", os.path.join(ROOT, "train.py"),
+                          *common, "--tp", "2", "--save", "--output-dir", str(tmp_path / "b")],
+                         capture_output=True, text=True, env=env, timeout=600, cwd=str(tmp_path))
+    assert two.returncode == 0, two.stderr[-3000:]
+    a, b = _steps(one.stdout), _steps(two.stdout)
+    assert len(a) == 3 and len(b) == 3 and max(abs(x - y) for x, y in zip(a, b)) < 2e-4, (a, b)
+    with safe_open(str(tmp_path / "b" / "final.safetensors"), framework="pt") as f:
+        assert f.get_tensor("model.layers.0.mlp.gate_proj.weight").shape == (688, 256)      # gathered, not a shard
+        assert f.get_tensor("model.layers.1.self_attn.o_proj.weight").shape == (256, 256)
+
+
+def test_rank_strided_source_partitions_the_stream():
+    import flextrain_b200 as ft
+    base = lambda: ft.SyntheticTokenSource(100, 16, seed=3)
+    whole = [s.tokens.tolist() for s in base().get_sequences(16 * 8)]
+    parts = [[s.tokens.tolist() for s in ft.RankStridedSource(base(), r, 2).get_sequences(16 * 4)] for r in range(2)]
+    assert parts[0] == whole[0::2] and parts[1] == whole[1::2]
+    src = ft.RankStridedSource(base(), 1, 2)
+    first = src.get_sequences(32)
+    src.push_back(first)
+    assert [s.tokens.tolist() for s in src.get_sequences(32)] == [s.tokens.tolist() for s in first]

@@ -172,9 +172,13 @@ def main(argv=None) -> int:
         vocab = am.model_config.vocab_size
 
     # ---- data
-    per_rank_tokens = args.max_global_batch_tokens // world
+    # data-parallel ranks (also under expert parallelism) each take their share of the batch; the ranks of a
+    # tensor-parallel group work on the SAME sequences, so they read identical data
+    data_ranks, data_rank = (1, 0) if args.tp > 1 else (world, rank)
+    per_rank_tokens = args.max_global_batch_tokens // data_ranks
     if args.data_source == "synthetic":
-        src = ft.SyntheticTokenSource(vocab, args.synthetic_seq_len or args.max_seq_len, seed=args.seed + rank, pin=use_cuda)
+        src = ft.SyntheticTokenSource(vocab, args.synthetic_seq_len or args.max_seq_len, seed=args.seed + data_rank,
+                                      pin=use_cuda)
     elif args.data_source == "shards":
         src = ft.ShardTokenSource(args.dataset, args.max_seq_len)
     else:
@@ -182,10 +186,13 @@ def main(argv=None) -> int:
         tok = AutoTokenizer.from_pretrained(model if kind == "hf" else args.model)
         src = ft.JsonSFTTokenSource(args.dataset, tok, args.max_seq_len, apply_chat_template=args.apply_chat_template,
                                     truncate_long=args.truncate_long)
+    if data_ranks > 1 and args.data_source != "synthetic":
+        src = ft.RankStridedSource(src, data_rank, data_ranks)       # every rank opened the same files
     out_dir = args.output_dir or os.path.join("runs", f"{os.path.basename(str(args.model).rstrip('/'))}_{args.mode}_sl{args.max_seq_len}")
     os.makedirs(out_dir, exist_ok=True)
     rc = run_training_loop(am, src, args, per_rank_tokens, world, say)
-    if args.save and rank == 0:
+    if args.save and (rank == 0 or am.tp is not None or am.ep is not None):
+        # gathering tensor- / expert-parallel parts is a collective: every rank takes part, rank 0 writes
         path = am.save_hf(out_dir, "final.safetensors")
         say(f"[save] {path}")
     if world > 1:
@@ -231,7 +238,8 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
             torch.cuda.synchronize(); torch.cuda.profiler.start(); profiling = True
         step_tokens = sum(len(s) for s in seqs)
         active = max(1, sum(s.active_token_count for s in seqs))
-        if world > 1:
+        shared_batch = am.tp is not None                      # tensor parallel: every rank holds the whole batch
+        if world > 1 and not shared_batch:
             import torch.distributed as dist
             t = torch.tensor([step_tokens, active], device=am.device, dtype=torch.int64)
             dist.all_reduce(t)
@@ -252,7 +260,13 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
             torch.cuda.profiler.stop(); profiling = False
         if rc != 0:
             say(f"[step {step}] optimizer reported non-finite gradients (code {rc}); update skipped")
-        loss = st.loss_sum / max(active, 1)
+        loss_sum = st.loss_sum
+        if shared_batch:                                      # each rank scored its token shard of the same batch
+            import torch.distributed as dist
+            t = torch.tensor([loss_sum], device=am.device, dtype=torch.float64 if am.device.type == "cpu" else torch.float32)
+            dist.all_reduce(t)
+            loss_sum = float(t)
+        loss = loss_sum / max(active, 1)
         ema = loss if ema is None else 0.95 * ema + 0.05 * loss
         eff, hw = step_flops_breakdown(am, st, mode=args.mode)
         tok_total += g_tokens
