@@ -163,3 +163,35 @@ def test_rank_strided_source_partitions_the_stream():
     first = src.get_sequences(32)
     src.push_back(first)
     assert [s.tokens.tolist() for s in src.get_sequences(32)] == [s.tokens.tolist() for s in first]
+
+
+def _tiny_hf_dir_with_tokenizer(path):
+    """A two-layer random Llama in HF layout with a character-level tokenizer (digits, operators, letters)."""
+    transformers = pytest.importorskip("transformers")
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    chars = ["<unk>", "</s>", "<pad>"] + [chr(c) for c in range(32, 127)] + ["\n"]
+    tok = Tokenizer(models.WordLevel({c: i for i, c in enumerate(chars)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Split("", behavior="isolated")
+    fast = transformers.PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", eos_token="</s>",
+                                                pad_token="<pad>")
+    _run("init", "--arch", "llama", "--d-model", "64", "--n-layers", "2", "--vocab-size", str(len(chars)), "--head-dim",
+         "16", "--n-kv-heads", "2", "--out", path, "--dtype", "float32")
+    fast.save_pretrained(path)
+    return len(chars)
+
+
+def test_train_lora_sft_on_an_hf_directory_learns_and_saves(tmp_path):
+    """``train.py --mode lora`` on an HF directory with its tokenizer and the bundled toy arithmetic set: the prompt is
+    masked, the loss falls, ``--save`` writes the weights, and ``--truncate-long`` / chat-template flags parse."""
+    model = str(tmp_path / "model")
+    _tiny_hf_dir_with_tokenizer(model)
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
+    out = str(tmp_path / "run")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "train.py"), "--model", model, "--mode", "lora",
+                        "--lora-rank", "8", "--lora-alpha", "16", "--max-seq-len", "96", "--max-global-batch-tokens",
+                        "768", "--steps", "12", "--lr", "2e-2", "--truncate-long", "--save", "--output-dir", out],
+                       capture_output=True, text=True, env=env, timeout=900, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr[-3000:]
+    losses = _steps(r.stdout)
+    assert len(losses) == 12 and losses[-1] < losses[0] - 0.3, losses
+    assert os.path.exists(os.path.join(out, "final.safetensors"))
