@@ -87,6 +87,8 @@ class ActiveModel:
         kvh = max((l.attn.cfg.n_kv_heads for l in attn_layers), default=0)
         hd = max((l.attn.cfg.head_dim for l in attn_layers), default=0)
         window = ws.max_seq_len if (attn_layers and ws.max_seq_len > ws.max_chunk_size) else 0
+        if window and tp is not None:
+            window += 128 * tp.world        # a sequence's last chunk may carry filler tokens up to the shard multiple
         act_dtype = self.layers[0].cfg.dtype if self.layers else torch.bfloat16
         self.buffers = BufferManager(
             [l.param_spec for l in self.layers], embed.param_spec, head.param_spec, optimizer, device,
@@ -126,12 +128,13 @@ class ActiveModel:
                 with _nvtx(f"Round {r}"):
                     last_round = r == len(rounds) - 1
                     with _nvtx("Prepare Training Chunks"):
-                        metas = prepare_training_chunks(rseqs, ws.max_chunk_size, self.device, mrope=self.mrope)
+                        metas = prepare_training_chunks(rseqs, ws.max_chunk_size, self.device, mrope=self.mrope,
+                                                        pad_multiple=128 * self.tp.world if self.tp is not None else 1)
                     with _nvtx("Determine Saved Levels"):
                         plan = self._plan_save_levels(metas)
                     self._last_plan = plan
                     stats.n_chunks += len(metas)
-                    stats.tokens += sum(m.num_tokens for m in metas)
+                    stats.tokens += sum(m.num_tokens - m.extra.get("pad_tokens", 0) for m in metas)
                     stats.host_act_bytes = max(stats.host_act_bytes, plan.host_bytes)
                     for k, v in plan.histogram().items():
                         stats.plan_hist[k] = stats.plan_hist.get(k, 0) + v

@@ -95,14 +95,27 @@ def pack_sequences(seqs: Seq[Sequence], max_chunk_size: int) -> List[ChunkPlan]:
 
 
 def prepare_training_chunks(seqs: Seq[Sequence], max_chunk_size: int, device, *, staging=None,
-                            mrope: bool = False) -> List[ChunkMeta]:
-    """Pack ``seqs`` into chunks and upload ids / targets / masks (one H2D copy per chunk)."""
+                            mrope: bool = False, pad_multiple: int = 1) -> List[ChunkMeta]:
+    """Pack ``seqs`` into chunks and upload ids / targets / masks (one H2D copy per chunk).
+
+    ``pad_multiple > 1`` (tensor parallelism shards a chunk's tokens in 128-row tiles per rank) rounds a chunk's token
+    count up by extending its LAST piece with unscored filler tokens.  That piece must end its sequence: the filler
+    then sits after every real token of a causal model, so no real token sees it, it carries no loss and it feeds no
+    later chunk.  A chunk that ends inside a sequence has exactly ``max_chunk_size`` tokens, which therefore has to be
+    a multiple of ``pad_multiple`` itself.  ``meta.extra["pad_tokens"]`` records the filler count."""
     plans = pack_sequences(seqs, max_chunk_size)
     metas: List[ChunkMeta] = []
     dev = torch.device(device)
     for cid, plan in enumerate(plans):
-        T = plan.num_tokens
-        any_mask = any(seqs[i].loss_mask is not None for i, _, _ in plan.pieces)
+        Tr = plan.num_tokens
+        pad = (-Tr) % pad_multiple if pad_multiple > 1 else 0
+        if pad:
+            li, ls, ln = plan.pieces[-1]
+            if ls + ln < len(seqs[li]):
+                raise ValueError(f"a chunk of {Tr} tokens ends inside a sequence and cannot be padded to a multiple of "
+                                 f"{pad_multiple}: make max_chunk_size ({max_chunk_size}) a multiple of it")
+        T = Tr + pad
+        any_mask = any(seqs[i].loss_mask is not None for i, _, _ in plan.pieces) or pad > 0
         any_adv = any(seqs[i].advantages is not None for i, _, _ in plan.pieces)
         rows = 2 + (1 if any_mask else 0)
         host = torch.empty(rows, T, dtype=torch.int64, pin_memory=(dev.type == "cuda"))
@@ -116,21 +129,31 @@ def prepare_training_chunks(seqs: Seq[Sequence], max_chunk_size: int, device, *,
                 host[2, off:off + n] = (s.loss_mask[start:start + n] > 0).to(torch.int64) if s.loss_mask is not None else 1
             off += n
             seq_ids.append(s.seq_id); lens.append(n); priors.append(start); more.append(start + n < len(s))
+        if pad:
+            host[0, Tr:] = host[0, Tr - 1]                     # any valid token id
+            host[1, Tr:] = -100
+            host[2, Tr:] = 0
+            lens[-1] += pad
         devbuf = host.to(dev, non_blocking=True)
         mask = devbuf[2].to(torch.float32) if any_mask else None
         meta = ChunkMeta.build(cid, seq_ids, lens, priors, more, dev, tokens=devbuf[0], targets=devbuf[1],
                                loss_mask=mask, seq_group=plan.seq_group)
         meta.extra["pieces"] = plan.pieces
+        meta.extra["pad_tokens"] = pad
+        tail = lambda t, fill: torch.cat([t, torch.full((pad,), fill, dtype=t.dtype)]) if pad else t
         if any_adv:
             adv = torch.cat([(seqs[i].advantages[st:st + n] if seqs[i].advantages is not None else torch.ones(n))
-                             for i, st, n in plan.pieces]).to(dev, non_blocking=True)
-            meta.extra["advantages"] = adv
+                             for i, st, n in plan.pieces])
+            meta.extra["advantages"] = tail(adv, 0.0).to(dev, non_blocking=True)
             if any(seqs[i].ref_logprobs is not None for i, _, _ in plan.pieces):
-                meta.extra["ref_logprobs"] = torch.cat(
-                    [(seqs[i].ref_logprobs[st:st + n] if seqs[i].ref_logprobs is not None else torch.zeros(n))
-                     for i, st, n in plan.pieces]).to(dev, non_blocking=True)
+                ref = torch.cat([(seqs[i].ref_logprobs[st:st + n] if seqs[i].ref_logprobs is not None else torch.zeros(n))
+                                 for i, st, n in plan.pieces])
+                meta.extra["ref_logprobs"] = tail(ref, 0.0).to(dev, non_blocking=True)
         if mrope:
             pos = [compute_mrope_position_ids(seqs[i], start, n) for i, start, n in plan.pieces]
+            if pad:                                            # filler continues after the sequence's last position
+                nxt = int(pos[-1].max()) + 1 if pos[-1].numel() else 0
+                pos.append((nxt + torch.arange(pad, dtype=torch.int32)).unsqueeze(1).expand(pad, 3))
             meta.positions = torch.cat(pos, 0).to(dev)
         metas.append(meta)
     return metas

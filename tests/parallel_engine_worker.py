@@ -4,7 +4,8 @@
 data parallel) and trains on its share of the batch.  ``tp``: a small Llama with ``tp = world`` (heads and FFN width
 sharded, token-sharded residual stream); every rank feeds the whole batch.  After a few steps the parameters are
 gathered back through the HF exporter; rank 0 also trains the unsharded model on the whole batch in the same process
-and reports the differences.
+and reports the differences.  ``tp_ragged``: as ``tp`` with sequences of uneven lengths (one of them longer than a
+chunk), so chunk token counts are not multiples of the shard width and the scheduler has to pad them.
 """
 import json
 import os
@@ -22,29 +23,32 @@ MOE_DIMS = dict(vocab_size=512, n_layers=2, d_model=128, n_heads=4, n_kv_heads=2
 DENSE_DIMS = dict(vocab_size=512, n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, expert_dim=512,
                   ffn_dim=512, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
 GB, SEQ, STEPS = 1024, 128, 2
+RAGGED = [100, 37, 300, 77, 41, 131, 65, 29, 200]      # 980 tokens; the 300-token one spans two 256-token chunks
 
 
 def build(dev, dtype, world, rank, mode, backend):
     from flextrain_b200.engine.host_memory import UnpinnedHostBackend
     os.environ["FTB_DP_BACKEND"] = backend
-    per_rank = GB if mode == "tp" else GB // world
-    ws = ft.WorkingSetConfig.simple(max_seq_len=SEQ, max_global_batch_tokens=per_rank, chunk=512,
+    per_rank = GB if mode.startswith("tp") else GB // world
+    seq = 512 if mode == "tp_ragged" else SEQ
+    ws = ft.WorkingSetConfig.simple(max_seq_len=seq, max_global_batch_tokens=per_rank,
+                                    chunk=256 if mode == "tp_ragged" else 512,
                                     round_tokens=per_rank, world_size=world,
                                     shard="opt+grad" if world > 1 else "none")
     par = {"ep": world} if mode == "ep" else {"tp": world}
     return ft.from_dims(MOE_DIMS if mode == "ep" else DENSE_DIMS, arch="qwen3_moe" if mode == "ep" else "llama",
                         optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32),
-                        max_seq_len=SEQ, max_global_batch_tokens=GB, max_gpu_mem_bytes=8 << 30,
+                        max_seq_len=seq, max_global_batch_tokens=GB, max_gpu_mem_bytes=8 << 30,
                         max_host_mem_bytes=8 << 30, device=dev, compute_dtype=dtype, master_dtype=dtype,
                         grad_dtype=dtype, working_set=ws, world_size=world, rank=rank,
                         host_backend=UnpinnedHostBackend() if dev == "cpu" else None, **(par if world > 1 else {}))
 
 
 def train(am, rank, world, dev, mode):
-    src = ft.SyntheticTokenSource(512, SEQ, seed=5)
+    src = ft.SyntheticTokenSource(512, RAGGED if mode == "tp_ragged" else SEQ, seed=5)
     losses = []
     for _ in range(STEPS):
-        seqs = src.get_sequences(GB)
+        seqs = src.get_sequences(sum(RAGGED) if mode == "tp_ragged" else GB)
         if mode == "ep":
             seqs = seqs[rank::world]                  # data parallel: each rank takes its share of the batch
         st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / GB, total_tokens_per_step=GB)
@@ -68,6 +72,11 @@ def main():
         dist.init_process_group("gloo")
     am = build(dev, dtype, world, rank, mode, backend)
     local_rows = am.buffers.params(0)["w_up" if mode == "ep" else "w_1"].shape[0]
+    if mode == "tp_ragged" and world > 1:
+        from flextrain_b200.engine.schedule import prepare_training_chunks
+        probe = ft.SyntheticTokenSource(512, RAGGED, seed=5).get_sequences(sum(RAGGED))
+        metas = prepare_training_chunks(probe, 256, dev, pad_multiple=128 * world)
+        assert all(m.num_tokens % (128 * world) == 0 for m in metas) and sum(m.extra["pad_tokens"] for m in metas) > 0
     losses = train(am, rank, world, dev, mode)
     if am.ep is not None:
         am.ep.check()

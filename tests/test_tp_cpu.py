@@ -22,6 +22,21 @@ def test_engine_tensor_parallel_matches_unsharded(tmp_path):
     assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
 
 
+def test_engine_tensor_parallel_pads_ragged_chunks(tmp_path):
+    """Sequences of uneven lengths (one longer than a chunk): chunk token counts are rounded up to the shard multiple
+    with unscored filler after the last real token; losses, per-token write-back and the trained parameters still
+    match the unsharded, unpadded run."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "tpr.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective",
+           "tp_ragged", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
+
+
 def test_tensor_spec_localisation():
     import torch
     from flextrain_b200.core.layer import TensorSpec
