@@ -166,3 +166,28 @@ def test_every_packaged_model_plans(name):
         assert ws1.target_round_tokens * ws1.target_num_rounds >= 65536 or ws1.target_num_rounds >= 1
     except ValueError as e:                                    # e.g. the 70B / 80B entries on one GPU
         assert "fit" in str(e).lower() or "memory" in str(e).lower() or "budget" in str(e).lower(), str(e)
+
+
+def test_chunk_padding_rules():
+    """Padding to a shard multiple: filler goes after the chunk's last real token, is unscored and masked, extends the
+    last sequence's length and positions, and is refused when the chunk ends inside a sequence."""
+    from flextrain_b200.engine.schedule import prepare_training_chunks
+    seqs = ft.SyntheticTokenSource(100, [100, 37, 300], seed=1).get_sequences(437)
+    for i, s in enumerate(seqs):
+        s.advantages = torch.full((len(s),), float(i + 1))
+    metas = prepare_training_chunks(seqs, 512, "cpu", pad_multiple=256)
+    assert [m.num_tokens for m in metas] == [512] and metas[0].extra["pad_tokens"] == 75
+    m = metas[0]
+    assert m.seq_lens == [100, 37, 375] and m.extra["pieces"] == [(0, 0, 100), (1, 0, 37), (2, 0, 300)]
+    assert bool((m.targets[437:] == -100).all()) and float(m.loss_mask[437:].sum()) == 0 and float(m.loss_mask[:437].min()) == 1
+    assert m.positions[436:440].tolist() == [299, 300, 301, 302]
+    assert float(m.extra["advantages"][437:].abs().sum()) == 0 and float(m.extra["advantages"][436]) == 3.0
+    same = prepare_training_chunks(seqs, 512, "cpu")            # no padding asked for: nothing changes
+    assert same[0].num_tokens == 437 and same[0].extra["pad_tokens"] == 0 and same[0].loss_mask is None
+    # a 300-token sequence over 256-token chunks: the first chunk ends inside it (exactly the chunk size, no filler
+    # needed), the last one is padded; with a chunk size that is not a multiple the split cannot be padded
+    long = prepare_training_chunks(seqs[2:], 256, "cpu", pad_multiple=256)
+    assert [x.num_tokens for x in long] == [256, 256] and [x.extra["pad_tokens"] for x in long] == [0, 212]
+    assert long[1].prior_lens == [256] and long[1].seq_lens == [256]
+    with pytest.raises(ValueError, match="ends inside a sequence"):
+        prepare_training_chunks(seqs[2:], 200, "cpu", pad_multiple=256)
