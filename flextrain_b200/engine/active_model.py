@@ -578,6 +578,15 @@ class ActiveModel:
         from ..io.hf_weights import export_model_safetensors
         return export_model_safetensors(self, out_dir, filename)
 
+    def save_training_state(self, out_dir: str, extra: Optional[dict] = None) -> str:
+        """Weights + optimizer state + step counter (every rank calls it); see ``io/training_state.py``."""
+        from ..io.training_state import save_training_state
+        return save_training_state(self, out_dir, extra)
+
+    def load_training_state(self, src_dir: str, strict: bool = True) -> dict:
+        from ..io.training_state import load_training_state
+        return load_training_state(self, src_dir, strict)
+
     def named_master_params(self):
         """Yield ``(scope, layer_index, name, tensor)`` over every master tensor (embed, layers, head)."""
         for n, t in self.buffers.embed_params().items():

@@ -183,6 +183,12 @@ class BufferManager:
             return self.params(layer)
         return _views(self.host_p[layer], self.layers[layer].m_layout)
 
+    def master_opt_state(self, layer: int) -> Dict[str, torch.Tensor]:
+        """Optimizer state of a layer where it lives between steps (host views when ringed, GPU views when resident)."""
+        if self.opt_resident or self.host_o is None:
+            return self.opt_state(layer)
+        return _views(self.host_o[layer], self.layers[layer].o_layout)
+
     # ------------------------------------------------------------------ fetch / offload
     def _copy(self, dst: torch.Tensor, src: torch.Tensor, copier=None):
         if copier is not None:

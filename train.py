@@ -78,6 +78,14 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--grad-dtype", choices=tuple(_DT), default="bfloat16")
     p.add_argument("--opt-state-dtype", choices=tuple(_DT), default=None)
     p.add_argument("--save", action="store_true")
+    p.add_argument("--save-state-every", type=int, default=0,
+                   help="every N steps (and at the end) write a full training state (weights, optimizer state, step) "
+                        "to <output-dir>/state; 0 = never")
+    p.add_argument("--stop-after", type=int, default=None,
+                   help="leave the loop after this step (the schedule still spans --steps): a run that will be resumed")
+    p.add_argument("--resume-state", default=None,
+                   help="directory written by --save-state-every: restore it and continue from its step (same model, "
+                        "world size and layout; the data source is advanced past the batches already consumed)")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--verbose", action="store_true")
     # parallel layout (new): ranks come from torch.distributed.run
@@ -190,6 +198,14 @@ def main(argv=None) -> int:
         src = ft.RankStridedSource(src, data_rank, data_ranks)       # every rank opened the same files
     out_dir = args.output_dir or os.path.join("runs", f"{os.path.basename(str(args.model).rstrip('/'))}_{args.mode}_sl{args.max_seq_len}")
     os.makedirs(out_dir, exist_ok=True)
+    first_step = 1
+    if args.resume_state:
+        info = am.load_training_state(args.resume_state)
+        first_step = info["step"] + 1
+        for _ in range(info["step"]):                          # the batches the saved run already consumed
+            src.get_sequences(per_rank_tokens)
+        say(f"[resume] {args.resume_state}: continuing at step {first_step}")
+    args._first_step, args._state_dir = first_step, os.path.join(out_dir, "state")
     rc = run_training_loop(am, src, args, per_rank_tokens, world, say)
     if args.save and (rank == 0 or am.tp is not None or am.ep is not None):
         # gathering tensor- / expert-parallel parts is a collective: every rank takes part, rank 0 writes
@@ -216,7 +232,11 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
         from flextrain_b200.parallel.health import Heartbeat
         hb = Heartbeat(dist.distributed_c10d._get_default_store(), dist.get_rank(), world, stale_s=args.heartbeat_s)
         hb.beat(0)
-    for step in range(1, total + 1):
+    first = getattr(args, "_first_step", 1)
+    if hb is not None and first > 1:
+        hb.beat(first - 1)
+    last = min(total, args.stop_after) if getattr(args, "stop_after", None) else total
+    for step in range(first, last + 1):
         if hb is not None:
             hb.check(grace_s=args.heartbeat_s)
         am.optimizer.lr = lr_schedule(step, max_lr=max_lr, final_lr=final_lr, warmup_steps=warm, cooldown_start=cool,
@@ -276,6 +296,10 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
             f"tok/s {g_tokens / dt:,.0f} TFLOPS_eff {eff * world / dt / 1e12:.1f} TFLOPS_hw {hw * world / dt / 1e12:.1f} "
             f"max_alloc {mem[0]:.1f} GiB max_reserve {mem[1]:.1f} GiB step {dt * 1e3:.0f} ms "
             f"elapsed {time.time() - t_start:.0f}s")
+        every = getattr(args, "save_state_every", 0)
+        if every and (step % every == 0 or step == last):
+            am.save_training_state(args._state_dir, extra={"tokens_seen": tok_total, "ema": ema})
+            say(f"[state] step {step} -> {args._state_dir}")
     say(f"[done] {tok_total} tokens in {time.time() - t_start:.1f}s")
     return 0
 
