@@ -69,8 +69,10 @@ class DataConfig:
 class IOConfig:
     output_dir: str = "runs/default"
     save: bool = False
-    resume_from: Optional[str] = None
+    resume_from: Optional[str] = None          # weights only: an exported HF directory becomes the model to load
     log_every: int = 1
+    save_state_every: int = 0                  # full training state (weights, optimizer state, step) every N steps
+    resume_state: Optional[str] = None         # continue exactly from a directory written by save_state_every
 
 
 @dataclass(frozen=True)

@@ -195,3 +195,17 @@ def test_train_lora_sft_on_an_hf_directory_learns_and_saves(tmp_path):
     losses = _steps(r.stdout)
     assert len(losses) == 12 and losses[-1] < losses[0] - 0.3, losses
     assert os.path.exists(os.path.join(out, "final.safetensors"))
+
+
+def test_train_from_yaml_with_state_checkpoint(tmp_path):
+    """``python -m flextrain_b200 train <yaml>``: the YAML front end drives the same loop as ``train.py``; the run
+    writes a training state that a second YAML resumes."""
+    y1, y2 = tmp_path / "a.yaml", tmp_path / "b.yaml"
+    body = ("model: {dims: tiny_llama, mode: full}\noptimizer: {name: adamw, lr: 1.0e-3, state_dtype: float32}\n"
+            "train: {steps: 4, max_seq_len: 128, max_global_batch_tokens: 512}\ndata: {source: synthetic}\n")
+    y1.write_text(body + f"io: {{output_dir: {tmp_path}/r1, save_state_every: 2}}\n")
+    out = _run("train", str(y1))
+    assert len(_steps(out)) == 4 and out.count("[state]") == 2
+    y2.write_text(body.replace("steps: 4", "steps: 6") + f"io: {{output_dir: {tmp_path}/r2, resume_state: {tmp_path}/r1/state}}\n")
+    out2 = _run("train", str(y2))
+    assert "continuing at step 5" in out2 and len(_steps(out2)) == 2
