@@ -206,6 +206,9 @@ def test_train_from_yaml_with_state_checkpoint(tmp_path):
     y1.write_text(body + f"io: {{output_dir: {tmp_path}/r1, save_state_every: 2}}\n")
     out = _run("train", str(y1))
     assert len(_steps(out)) == 4 and out.count("[state]") == 2
+    rows = [json.loads(l) for l in open(tmp_path / "r1" / "metrics.jsonl")]
+    assert [r["step"] for r in rows] == [1, 2, 3, 4] and rows[0]["tokens"] == 512 and rows[0]["tok_per_s"] > 0
+    assert abs(rows[2]["loss"] - _steps(out)[2]) < 1e-3 and rows[0]["chunks"] >= 1 and rows[0]["optimizer_rc"] == 0
     y2.write_text(body.replace("steps: 4", "steps: 6") + f"io: {{output_dir: {tmp_path}/r2, resume_state: {tmp_path}/r1/state}}\n")
     out2 = _run("train", str(y2))
     assert "continuing at step 5" in out2 and len(_steps(out2)) == 2

@@ -81,6 +81,9 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--save-state-every", type=int, default=0,
                    help="every N steps (and at the end) write a full training state (weights, optimizer state, step) "
                         "to <output-dir>/state; 0 = never")
+    p.add_argument("--metrics-jsonl", default=None,
+                   help="append one JSON object per step (rank 0): step, loss, ema, lr, tokens, tok/s, TFLOPS, memory, "
+                        "rounds / chunks, save-tier histogram; default <output-dir>/metrics.jsonl, 'none' disables")
     p.add_argument("--stop-after", type=int, default=None,
                    help="leave the loop after this step (the schedule still spans --steps): a run that will be resumed")
     p.add_argument("--resume-state", default=None,
@@ -206,6 +209,8 @@ def main(argv=None) -> int:
             src.get_sequences(per_rank_tokens)
         say(f"[resume] {args.resume_state}: continuing at step {first_step}")
     args._first_step, args._state_dir = first_step, os.path.join(out_dir, "state")
+    mj = args.metrics_jsonl or os.path.join(out_dir, "metrics.jsonl")
+    args._metrics_path = None if (rank != 0 or str(mj).lower() == "none") else mj
     rc = run_training_loop(am, src, args, per_rank_tokens, world, say)
     if args.save and (rank == 0 or am.tp is not None or am.ep is not None):
         # gathering tensor- / expert-parallel parts is a collective: every rank takes part, rank 0 writes
@@ -296,6 +301,17 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
             f"tok/s {g_tokens / dt:,.0f} TFLOPS_eff {eff * world / dt / 1e12:.1f} TFLOPS_hw {hw * world / dt / 1e12:.1f} "
             f"max_alloc {mem[0]:.1f} GiB max_reserve {mem[1]:.1f} GiB step {dt * 1e3:.0f} ms "
             f"elapsed {time.time() - t_start:.0f}s")
+        mj = getattr(args, "_metrics_path", None)
+        if mj:
+            import json
+            with open(mj, "a") as f:
+                f.write(json.dumps({"step": step, "loss": loss, "ema": ema, "lr": am.optimizer.lr, "tokens": g_tokens,
+                                    "tokens_total": tok_total, "tok_per_s": g_tokens / dt, "step_ms": dt * 1e3,
+                                    "tflops_eff": eff * world / dt / 1e12, "tflops_hw": hw * world / dt / 1e12,
+                                    "max_alloc_gib": mem[0], "max_reserved_gib": mem[1], "rounds": st.n_rounds,
+                                    "chunks": st.n_chunks, "save_tiers": {str(k): v for k, v in st.plan_hist.items()},
+                                    "host_act_bytes": st.host_act_bytes, "optimizer_rc": rc,
+                                    "wall_s": time.time() - t_start}) + "\n")
         every = getattr(args, "save_state_every", 0)
         if every and (step % every == 0 or step == last):
             am.save_training_state(args._state_dir, extra={"tokens_seen": tok_total, "ema": ema})
