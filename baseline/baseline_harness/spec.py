@@ -12,7 +12,7 @@ import os
 import re
 import subprocess
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Mapping, Optional
+from typing import Any, Dict, Mapping, Optional
 
 _TEMPLATE = re.compile(r"\$\{([A-Z_]+)\}")
 

@@ -7,7 +7,7 @@ against ``torch.autograd`` + ``torch.optim.AdamW`` on CPU in fp32.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Optional
 
 import torch
 import torch.nn.functional as F

@@ -6,7 +6,7 @@ documented workflow)."""
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional
+from typing import Optional
 
 
 @dataclass(frozen=True)

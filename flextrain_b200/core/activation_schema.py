@@ -10,7 +10,7 @@ A slot is either *dynamic* (fields are ordinary tensors, used when everything st
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Tuple
 
 import torch

@@ -7,7 +7,7 @@ Mirrors flextrain/core/save_level.py (SaveLevel :57-80, HardwareCost :88-132, bu
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np

@@ -19,10 +19,10 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Tuple
 
 from .save_level import HardwareCost
-from .sizing import divisors, prev_high_div
+from .sizing import divisors
 
 GiB = 1 << 30
 SHARD_MODES = ("none", "opt", "opt+grad", "opt+grad+param")

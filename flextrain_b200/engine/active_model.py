@@ -21,12 +21,12 @@ import dataclasses
 import contextlib
 import time
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Sequence as Seq
+from typing import Dict, List, Optional, Sequence as Seq
 
 import torch
 
 from ..core.activation_schema import ON_DEVICE, ActivationSlot, fetch_home, send_home
-from ..core.layer import ChunkMeta, LayerContext, LossStats
+from ..core.layer import ChunkMeta, LayerContext
 from ..core.save_level import (HardwareCost, SaveLevelPlan, TransmissionScheduler, build_dp_tables,
                                plan_from_solution)
 from ..core.working_set import WorkingSetConfig

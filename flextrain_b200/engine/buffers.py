@@ -11,13 +11,12 @@ gradient / state bytes and are skipped when a layer is written back.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
 import torch
 
 from ..core.activation_schema import align_up
-from ..core.layer import KVContextWindow, ParamSpec, TensorSpec, itemsize
+from ..core.layer import KVContextWindow, ParamSpec, itemsize
 from .host_memory import HostMemoryBackend, default_backend
 
 

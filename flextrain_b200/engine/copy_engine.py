@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_int, c_uint64, c_void_p
-from typing import List, Optional, Sequence, Tuple
+from typing import Sequence, Tuple
 
 import torch
 

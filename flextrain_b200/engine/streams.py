@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Generic, Hashable, Optional, Tuple, TypeVar
 
 import torch

@@ -9,7 +9,7 @@ per-arch ``hf_config_to_flextrain`` / ``hf_config_to_hyperparams`` / ``expand_di
 from __future__ import annotations
 
 from dataclasses import dataclass, field, replace
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 

@@ -6,7 +6,7 @@ from ...nn.blocks.rope import RopeConfig
 from ..hf_weights import ArchSpec
 from . import _maps as M
 from . import gemma2 as _g
-from .common import ModelConfig, config_from_dims as _cfd
+from .common import ModelConfig
 
 FAMILY = "gemma3"
 

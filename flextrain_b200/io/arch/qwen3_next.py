@@ -8,7 +8,7 @@ from ...nn.blocks.linear_attn import GDNConfig
 from ...nn.blocks.rope import RopeConfig
 from ..hf_weights import ArchSpec
 from . import _maps as M
-from .common import ModelConfig, config_from_dims as _cfd, expand_layer_pattern
+from .common import ModelConfig, config_from_dims as _cfd
 
 FAMILY = "qwen3_next"
 

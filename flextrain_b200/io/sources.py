@@ -13,10 +13,9 @@ import collections
 import glob
 import itertools
 import json
-import os
 import queue
 import threading
-from typing import Callable, Deque, Dict, Iterable, Iterator, List, Optional, Protocol, Sequence as Seq
+from typing import Callable, Deque, Iterable, Iterator, List, Optional, Protocol, Sequence as Seq
 
 import numpy as np
 import torch

@@ -14,7 +14,7 @@ accumulated in the window and each chunk collects (then clears) its own slice
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Optional, Sequence, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 

@@ -8,7 +8,7 @@ MRoPE with (t, h, w) sections.  Channel pairing is rotate-half ``(i, i + rot/2)`
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Sequence, Tuple
+from typing import Optional, Tuple
 
 import torch
 

@@ -6,7 +6,6 @@ buffer is overwritten with ``dx``.  ``(T, V)`` is never materialised beyond one 
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 

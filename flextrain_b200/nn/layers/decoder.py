@@ -16,7 +16,7 @@ Llama-shaped layer (flextrain/nn/layers/llama.py:98-104): 0 ``x_inp, rstd's, xk,
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Optional
 
 import torch

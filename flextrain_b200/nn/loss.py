@@ -7,7 +7,7 @@ A loss receives the logits of one micro-chunk and turns them *in place* into ``d
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Protocol, Tuple
+from typing import Optional, Protocol
 
 import torch
 

@@ -1,7 +1,7 @@
 """Bindings to the tcgen05 flash-attention kernels (``csrc/attention.cu``)."""
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_long, c_void_p
+from ctypes import c_float, c_int, c_long
 
 import torch
 

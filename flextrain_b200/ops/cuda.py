@@ -13,7 +13,7 @@ from typing import Optional
 
 import torch
 
-from ..build import LIB, lib_path
+from ..build import lib_path
 
 _libs: dict = {}
 

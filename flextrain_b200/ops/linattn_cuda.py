@@ -5,7 +5,7 @@ All tensors are bf16 unless noted; ``cu`` is the int32 cumulative sequence-lengt
 """
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_long, c_void_p
+from ctypes import c_float, c_int, c_long
 from typing import Optional, Tuple
 
 import torch

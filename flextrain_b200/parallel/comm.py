@@ -10,8 +10,8 @@ The reference project has no communication layer (single GPU); its only analogue
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_double, c_int, c_long, c_void_p
-from typing import List, Optional
+from ctypes import c_double, c_int, c_void_p
+from typing import List
 
 import torch
 

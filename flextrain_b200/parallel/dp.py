@@ -25,10 +25,9 @@ The reference project is single-GPU; its closest analogue is gradient accumulati
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_long, c_uint, c_void_p
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List
 
 import torch
 

@@ -17,7 +17,6 @@ The reference project has no expert parallelism; its single-GPU MoE path is flex
 """
 from __future__ import annotations
 
-import ctypes
 import os
 from ctypes import c_int, c_long, c_void_p
 from dataclasses import dataclass

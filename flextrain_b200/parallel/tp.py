@@ -16,7 +16,6 @@ plain GEMM) and the CPU path.  The reference project has no tensor parallelism.
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_long, c_void_p
 from typing import Dict, Optional, Tuple
 

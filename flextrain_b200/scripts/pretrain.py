@@ -25,7 +25,6 @@ import glob
 import json
 import math
 import os
-import sys
 import time
 from typing import List, Optional
 

@@ -1,9 +1,7 @@
 """Data-parallel host logic on CPU: gloo ranks for the collective path, and a single-process emulation of the
 peer-memory kernels' shard arithmetic."""
-import os
 import socket
 
-import pytest
 import torch
 import torch.multiprocessing as mp
 

@@ -1,5 +1,4 @@
 """sm_100a kernels against the plain PyTorch fp32 reference of the same op."""
-import math
 
 import pytest
 import torch

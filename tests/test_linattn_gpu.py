@@ -1,6 +1,5 @@
 """Gated DeltaNet kernels (csrc/gdn.cu, csrc/seqmix.cu) against plain PyTorch fp32 references (autograd for the
 backward passes)."""
-import os
 
 import pytest
 import torch

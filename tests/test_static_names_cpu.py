@@ -16,7 +16,9 @@ def _undefined_in(path):
     module_names = {s.get_name() for s in top.get_symbols() if s.is_assigned() or s.is_imported() or s.is_namespace()}
     if "*" in src and "import *" in src:
         return []
-    bad = []
+    bad = [f"{os.path.relpath(path, ROOT)}:<module>:{s.get_name()}" for s in top.get_symbols()
+           if s.is_referenced() and not (s.is_assigned() or s.is_imported() or s.is_namespace())
+           and not hasattr(builtins, s.get_name()) and s.get_name() not in ("__file__", "__name__", "__doc__")]
 
     def walk(table):
         for child in table.get_children():
@@ -35,7 +37,7 @@ def _undefined_in(path):
 def test_no_undefined_names_in_sources():
     files = [os.path.join(ROOT, f) for f in ("bench.py", "train.py", "download.py", "__graft_entry__.py")]
     for base in ("flextrain_b200", "baseline/baseline_harness", "baseline/scripts", "baseline/backends", "experiments",
-                 "examples"):
+                 "examples", "tests"):
         for d, _, names in os.walk(os.path.join(ROOT, base)):
             files += [os.path.join(d, n) for n in names if n.endswith(".py")]
     files.append(os.path.join(ROOT, "baseline", "run_baseline.py"))

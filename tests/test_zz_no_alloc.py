@@ -9,7 +9,7 @@ the regular entry point, ``ftb_rmsnorm_bwd``, which takes a caller-allocated wor
 The file name sorts last so that a run that stops at the first failure has already run every other test.
 """
 import ctypes
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_int, c_void_p
 
 import pytest
 import torch
