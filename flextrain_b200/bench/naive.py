@@ -92,7 +92,7 @@ def _gdn(layer, l, P, h):
     return out
 
 
-def _ffn(layer, l, P, h):
+def _ffn(layer, l, P, h, aux=None):
     ls = layer.cfg.lora.scale if layer.cfg.lora is not None else None
     if layer.ffn is not None:
         g, u = _lin(P, l, "w_1", h, ls), _lin(P, l, "w_3", h, ls)
@@ -107,6 +107,12 @@ def _ffn(layer, l, P, h):
     else:
         vals, idx = torch.sort(logits, dim=-1, descending=True, stable=True)
         w, idx = torch.softmax(vals[:, : c.top_k], -1), idx[:, : c.top_k]
+    if aux is not None and c.aux_loss_alpha > 0:
+        # load-balance term of this layer over these tokens: alpha * E * sum_e f_e * sum_t p_te, with the routed
+        # fraction f_e a constant; the caller divides by the step's token count
+        E = logits.shape[-1]
+        f = torch.bincount(idx.reshape(-1), minlength=E).to(logits.dtype) / idx.numel()
+        aux.append(c.aux_loss_alpha * E * (f.detach() * torch.softmax(logits, -1).sum(0)).sum())
     up, down = P[("layer", l, "w_up")], P[("layer", l, "w_down")]
     out = torch.zeros_like(h)
     for k in range(c.top_k):
@@ -126,8 +132,9 @@ def _ffn(layer, l, P, h):
     return out
 
 
-def naive_forward(am, P, tokens: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Logits ``(T, V)`` of one sequence through plain autograd ops."""
+def naive_forward(am, P, tokens: torch.Tensor, positions: Optional[torch.Tensor] = None, aux=None) -> torch.Tensor:
+    """Logits ``(T, V)`` of one sequence through plain autograd ops; ``aux`` (a list) collects the MoE layers'
+    un-normalised load-balance terms."""
     T = tokens.numel()
     pos = positions if positions is not None else torch.arange(T)
     x = P[("embed", -1, "w_tok_embeddings")][tokens.long()] * am.embed.scale
@@ -139,7 +146,7 @@ def naive_forward(am, P, tokens: torch.Tensor, positions: Optional[torch.Tensor]
             a = _rms(a, P[("layer", l, "w_post_attn_norm")], c.norm_eps)
         x = x + a
         h = _rms(x, P[("layer", l, "w_ffn_norm")], c.norm_eps)
-        f = _ffn(layer, l, P, h)
+        f = _ffn(layer, l, P, h, aux)
         if c.post_norms:
             f = _rms(f, P[("layer", l, "w_post_ffn_norm")], c.norm_eps)
         x = x + f

@@ -25,7 +25,8 @@ def config_from_hf(hf: dict) -> ModelConfig:
     mc.num_experts, mc.top_k = int(hf.get("num_experts", hf.get("num_local_experts"))), int(hf["num_experts_per_tok"])
     mc.expert_dim = int(hf["moe_intermediate_size"])
     mc.routing = "topk_then_softmax" if hf.get("norm_topk_prob", True) else "softmax_then_topk"
-    mc.aux_loss_alpha = 0.0
+    # the checkpoint's load-balance coefficient applies only when the config asks for router losses (HF semantics)
+    mc.aux_loss_alpha = float(hf.get("router_aux_loss_coef", 0.0)) if hf.get("output_router_logits") else 0.0
     step = int(hf.get("decoder_sparse_step", 1) or 1)
     only_mlp = set(hf.get("mlp_only_layers", []) or [])
     mc.moe_layers = [((i + 1) % step == 0) and i not in only_mlp for i in range(mc.n_layers)]

@@ -87,3 +87,45 @@ def test_lora_gradients():
                 checked += 1
     assert checked == 28
     assert am.step() == 0
+
+
+@pytest.mark.parametrize("arch", ["qwen3_moe", "olmoe"])
+def test_moe_load_balance_gradient(arch):
+    """The auxiliary load-balance loss ``alpha * E * sum_e f_e * mean_t p_te`` (routed fractions ``f`` held constant,
+    flextrain/nn/blocks/ffn_moe.py:95-110) only exists as a gradient in the engine; with one sequence per chunk it must
+    equal autograd's gradient of cross-entropy + that term on the naive model."""
+    am = build_tiny(arch=arch, dims=MOE, hyper={"aux_loss_alpha": 0.05}, max_seq_len=48, batch_tokens=96,
+                    ws=ft.WorkingSetConfig.simple(max_seq_len=48, max_global_batch_tokens=96, chunk=48))
+    assert am.layers[0].moe.cfg.aux_loss_alpha == 0.05
+    torch.manual_seed(0)
+    for scope, l, name, t in am.named_master_params():
+        if "norm" in name or "router" in name:
+            t.add_(torch.randn_like(t) * 0.1)
+    seqs = ft.SyntheticTokenSource(512, 48, seed=2).get_sequences(96)
+    P = clone_params(am)
+    total, active, aux = 0.0, 0, []
+    from flextrain_b200.bench.naive import naive_forward
+    for s in seqs:
+        z = naive_forward(am, P, s.tokens, aux=aux)
+        total = total + torch.nn.functional.cross_entropy(z, s.targets, ignore_index=-100, reduction="sum")
+        active += int((s.targets != -100).sum())
+    n_tokens = sum(len(s) for s in seqs)
+    assert len(aux) == 2 * len(seqs)
+    loss = total / active + sum(aux) / n_tokens
+    loss.backward()
+    st = am.fwd_bwd(seqs)
+    assert abs(st.loss - float(total.detach()) / active) < 2e-4          # the reported loss is the cross-entropy
+    bm = am.buffers
+    for l in range(2):
+        for gname, pname in (("g_router", "w_router"), ("g_up", "w_up"), ("g_q", "w_q")):
+            want = P[("layer", l, pname)].grad
+            torch.testing.assert_close(bm.grads(l)[gname].float(), want, rtol=3e-4, atol=3e-6, msg=f"{l}/{pname}")
+    # and the term matters: without it the router gradient differs
+    P2 = clone_params(am)
+    tot2 = 0.0
+    for s in seqs:
+        tot2 = tot2 + torch.nn.functional.cross_entropy(naive_forward(am, P2, s.tokens), s.targets, ignore_index=-100,
+                                                        reduction="sum")
+    (tot2 / active).backward()
+    d = (P2[("layer", 0, "w_router")].grad - P[("layer", 0, "w_router")].grad).norm()
+    assert float(d) > 1e-5
