@@ -19,6 +19,16 @@ COMMON = dict(vocab_size=320, hidden_size=64, intermediate_size=112, num_hidden_
 CASES = {
     "llama": ("LlamaConfig", dict(COMMON, rope_theta=10000.0, head_dim=16)),
     "mistral": ("MistralConfig", dict(COMMON, rope_theta=10000.0, head_dim=16, sliding_window=None)),
+    "mistral_window": ("MistralConfig", dict(COMMON, rope_theta=10000.0, head_dim=16, sliding_window=16)),
+    "llama_tied": ("LlamaConfig", dict(COMMON, rope_theta=10000.0, head_dim=16, tie_word_embeddings=True)),
+    "llama3_scaling": ("LlamaConfig", dict(COMMON, head_dim=16, rope_parameters={
+        "rope_type": "llama3", "rope_theta": 10000.0, "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+        "original_max_position_embeddings": 32})),
+    "llama_chunked": ("LlamaConfig", dict(COMMON, rope_theta=10000.0, head_dim=16)),
+    "qwen3_5_chunked": ("Qwen3_5TextConfig", dict(COMMON, head_dim=16, num_hidden_layers=4, linear_conv_kernel_dim=4,
+                                                  linear_key_head_dim=16, linear_value_head_dim=16,
+                                                  linear_num_key_heads=2, linear_num_value_heads=4,
+                                                  layer_types=["linear_attention", "full_attention"] * 2)),
     "qwen2": ("Qwen2Config", dict(COMMON, rope_theta=10000.0)),
     "qwen3": ("Qwen3Config", dict(COMMON, rope_theta=10000.0, head_dim=16)),
     "gemma2": ("Gemma2Config", dict(COMMON, head_dim=16, query_pre_attn_scalar=16, sliding_window=16,
@@ -31,6 +41,14 @@ CASES = {
                                         layer_types=["sliding_attention", "full_attention"],
                                         hidden_size_per_layer_input=0, vocab_size_per_layer_input=320,
                                         hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)),
+    "gemma3_linear_rope": ("Gemma3TextConfig", dict(
+        COMMON, head_dim=16, query_pre_attn_scalar=16, sliding_window=16, sliding_window_pattern=2,
+        hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True,
+        rope_parameters={"full_attention": {"rope_type": "linear", "factor": 8.0, "rope_theta": 1000000.0},
+                         "sliding_attention": {"rope_type": "default", "rope_theta": 10000.0}})),
+    "qwen3_sliding": ("Qwen3Config", dict(COMMON, rope_theta=10000.0, head_dim=16, use_sliding_window=True,
+                                          sliding_window=16, max_window_layers=1,
+                                          layer_types=["full_attention", "sliding_attention"])),
     "qwen3_moe": ("Qwen3MoeConfig", dict(COMMON, rope_theta=10000.0, head_dim=16, num_experts=8, num_experts_per_tok=2,
                                          moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
                                          mlp_only_layers=[])),
@@ -94,7 +112,8 @@ def test_loss_and_gradients_match_transformers(name, tmp_path):
                             max_global_batch_tokens=128, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
                             device="cpu", compute_dtype=torch.float32, master_dtype=torch.float32,
                             grad_dtype=torch.float32, host_backend=UnpinnedHostBackend(),
-                            working_set=ft.WorkingSetConfig.simple(max_seq_len=64, max_global_batch_tokens=128))
+                            working_set=ft.WorkingSetConfig.simple(max_seq_len=64, max_global_batch_tokens=128,
+                                                                   chunk=32 if name.endswith("_chunked") else None))
     seqs = []
     for i, t in enumerate(seqs_tok):
         tgt = torch.roll(t, -1)
