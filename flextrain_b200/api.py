@@ -57,9 +57,10 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
                         process_group, model_dir=None, arch_key=None, host_backend=None,
                         plan_only: bool = False) -> ActiveModel:
     builder = _BLOCK_BUILDERS.get(arch_key) if arch_key else None
-    if (tp > 1 and tp != world_size) or (ep > 1 and ep != world_size) or (tp > 1 and ep > 1):
-        raise NotImplementedError("tensor / expert parallel groups span the whole job: use tp == world_size or "
-                                  "ep == world_size (not both)")
+    if tp > 1 and ep > 1:
+        raise NotImplementedError("tensor and expert parallelism cannot be combined")
+    if (tp > 1 and world_size % tp) or (ep > 1 and world_size % ep):
+        raise ValueError(f"world size {world_size} is not a multiple of tp={tp} / ep={ep}")
     embed, layers, head = build_model_parts(mc, dt, lora, head_chunk_size, builder, tp=tp, tp_rank=rank % max(tp, 1))
     if ep > 1:
         # expert parallelism: every rank owns num_experts / ep experts of each MoE layer
@@ -94,6 +95,8 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
     am.model_config = mc
     am.is_causal = mc.is_causal
     am.rank, am.world_size = rank, world_size
+    mp = tp_group or ep_group
+    am.shard_group = getattr(mp, "group_pg", None) if mp is not None else None
     return am
 
 

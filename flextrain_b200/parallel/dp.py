@@ -75,6 +75,8 @@ class _Base:
     def __init__(self, rank: int, world: int, device, process_group=None):
         self.rank, self.world, self.device, self.pg = rank, world, torch.device(device), process_group
         self.am = None
+        # hybrid grids: the group of ranks that hold the same tensor- / expert-parallel part, and its first rank
+        self.replica_pg, self.replica_src = None, 0
 
     def attach(self, am) -> None:
         self.am = am
@@ -88,6 +90,8 @@ class _Base:
         for scope, l, name, t in am.named_master_params():
             if not am.spec_of(scope, l, name).is_local_part:
                 dist.broadcast(t, src=0, group=self.pg)
+            elif self.replica_pg is not None:
+                dist.broadcast(t, src=self.replica_src, group=self.replica_pg)
 
     @staticmethod
     def local_part_names(spec) -> List[str]:
@@ -102,10 +106,12 @@ class CollectiveDataParallel(_Base):
 
     def _allreduce(self, buf: torch.Tensor, lb) -> None:
         import torch.distributed as dist
-        skip = {t.grad_name for t in lb.spec.trainable() if t.is_local_part}
+        part = {t.grad_name for t in lb.spec.trainable() if t.is_local_part}
         for name, (off, nb, shape, dt) in lb.g_layout.items():
-            if name not in skip:
+            if name not in part:
                 dist.all_reduce(buf[off:off + nb].view(dt), group=self.pg)
+            elif self.replica_pg is not None:        # the same part on other model-parallel groups saw other data
+                dist.all_reduce(buf[off:off + nb].view(dt), group=self.replica_pg)
 
     def on_layer_grads_ready(self, layer: int) -> None:
         bm = self.am.buffers

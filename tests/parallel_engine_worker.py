@@ -6,6 +6,8 @@ sharded, token-sharded residual stream); every rank feeds the whole batch.  Afte
 gathered back through the HF exporter; rank 0 also trains the unsharded model on the whole batch in the same process
 and reports the differences.  ``tp_ragged``: as ``tp`` with sequences of uneven lengths (one of them longer than a
 chunk), so chunk token counts are not multiples of the shard width and the scheduler has to pad them.
+``tp_grid`` / ``ep_grid``: model-parallel groups of two ranks inside a larger job (a ``dp x tp`` / ``dp x ep`` grid over
+library collectives); every group trains on its share of the batch.
 """
 import json
 import os
@@ -29,14 +31,16 @@ RAGGED = [100, 37, 300, 77, 41, 131, 65, 29, 200]      # 980 tokens; the 300-tok
 def build(dev, dtype, world, rank, mode, backend):
     from flextrain_b200.engine.host_memory import UnpinnedHostBackend
     os.environ["FTB_DP_BACKEND"] = backend
-    per_rank = GB if mode.startswith("tp") else GB // world
+    mp = 2 if mode.endswith("_grid") else world                # model-parallel group size
+    per_rank = GB // max(world // mp, 1) if mode.startswith("tp") else GB // world
     seq = 512 if mode == "tp_ragged" else SEQ
     ws = ft.WorkingSetConfig.simple(max_seq_len=seq, max_global_batch_tokens=per_rank,
                                     chunk=256 if mode == "tp_ragged" else 512,
                                     round_tokens=per_rank, world_size=world,
                                     shard="opt+grad" if world > 1 else "none")
-    par = {"ep": world} if mode == "ep" else {"tp": world}
-    return ft.from_dims(MOE_DIMS if mode == "ep" else DENSE_DIMS, arch="qwen3_moe" if mode == "ep" else "llama",
+    par = {"ep": mp} if mode.startswith("ep") else {"tp": mp}
+    return ft.from_dims(MOE_DIMS if mode.startswith("ep") else DENSE_DIMS,
+                        arch="qwen3_moe" if mode.startswith("ep") else "llama",
                         optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32),
                         max_seq_len=seq, max_global_batch_tokens=GB, max_gpu_mem_bytes=8 << 30,
                         max_host_mem_bytes=8 << 30, device=dev, compute_dtype=dtype, master_dtype=dtype,
@@ -49,8 +53,10 @@ def train(am, rank, world, dev, mode):
     losses = []
     for _ in range(STEPS):
         seqs = src.get_sequences(sum(RAGGED) if mode == "tp_ragged" else GB)
-        if mode == "ep":
+        if mode.startswith("ep"):
             seqs = seqs[rank::world]                  # data parallel: each rank takes its share of the batch
+        elif mode == "tp_grid" and world > 1:
+            seqs = seqs[rank // 2::world // 2]        # each tensor-parallel pair takes its share
         st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / GB, total_tokens_per_step=GB)
         assert am.step() == 0
         t = torch.tensor([st.loss_sum], device=dev, dtype=torch.float64 if dev == "cpu" else torch.float32)
@@ -71,7 +77,7 @@ def main():
         dev, dtype = "cpu", torch.float32
         dist.init_process_group("gloo")
     am = build(dev, dtype, world, rank, mode, backend)
-    local_rows = am.buffers.params(0)["w_up" if mode == "ep" else "w_1"].shape[0]
+    local_rows = am.buffers.params(0)["w_up" if mode.startswith("ep") else "w_1"].shape[0]
     if mode == "tp_ragged" and world > 1:
         from flextrain_b200.engine.schedule import prepare_training_chunks
         probe = ft.SyntheticTokenSource(512, RAGGED, seed=5).get_sequences(sum(RAGGED))

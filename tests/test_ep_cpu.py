@@ -33,3 +33,18 @@ def test_engine_expert_parallel_matches_unsharded(tmp_path):
     res = json.load(open(out))
     assert res["local_rows"] == 4
     assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
+
+
+def test_engine_grid_of_expert_parallel_pairs(tmp_path):
+    """Four gloo ranks as two expert-parallel pairs (each pair holds all experts once): tokens are dispatched inside a
+    pair, expert gradients are reduced between the pairs' replicas, everything else over the job."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "epgrid.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective",
+           "ep_grid", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert res["local_rows"] == 4
+    assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res

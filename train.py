@@ -185,7 +185,7 @@ def main(argv=None) -> int:
     # ---- data
     # data-parallel ranks (also under expert parallelism) each take their share of the batch; the ranks of a
     # tensor-parallel group work on the SAME sequences, so they read identical data
-    data_ranks, data_rank = (1, 0) if args.tp > 1 else (world, rank)
+    data_ranks, data_rank = (world // args.tp, rank // args.tp) if args.tp > 1 else (world, rank)
     per_rank_tokens = args.max_global_batch_tokens // data_ranks
     if args.data_source == "synthetic":
         src = ft.SyntheticTokenSource(vocab, args.synthetic_seq_len or args.max_seq_len, seed=args.seed + data_rank,
@@ -263,12 +263,13 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
             torch.cuda.synchronize(); torch.cuda.profiler.start(); profiling = True
         step_tokens = sum(len(s) for s in seqs)
         active = max(1, sum(s.active_token_count for s in seqs))
-        shared_batch = am.tp is not None                      # tensor parallel: every rank holds the whole batch
-        if world > 1 and not shared_batch:
+        shared_batch = am.tp is not None                      # the ranks of a tensor-parallel group hold one batch
+        group_size = am.tp.world if shared_batch else 1
+        if world > group_size:
             import torch.distributed as dist
             t = torch.tensor([step_tokens, active], device=am.device, dtype=torch.int64)
-            dist.all_reduce(t)
-            g_tokens, g_active = int(t[0]), int(t[1])
+            dist.all_reduce(t)                                # every member of a group reports the group's batch
+            g_tokens, g_active = int(t[0]) // group_size, int(t[1]) // group_size
         else:
             g_tokens, g_active = step_tokens, active
         t0 = time.time()
@@ -289,7 +290,7 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
         if shared_batch:                                      # each rank scored its token shard of the same batch
             import torch.distributed as dist
             t = torch.tensor([loss_sum], device=am.device, dtype=torch.float64 if am.device.type == "cpu" else torch.float32)
-            dist.all_reduce(t)
+            dist.all_reduce(t, group=am.tp.pg)
             loss_sum = float(t)
         loss = loss_sum / max(active, 1)
         ema = loss if ema is None else 0.95 * ema + 0.05 * loss
