@@ -307,7 +307,7 @@ def run_reference(args):
             b = am.buffers
             for d in (getattr(b, "host_grads", None) or []):
                 bufs += list(d.values()) if isinstance(d, dict) else [d]
-            for name in ("embed_grads", "head_grads"):
+            for name in ("gpu_embed_grads", "gpu_head_grads"):        # device-resident dicts in the reference engine
                 d = getattr(b, name, None)
                 if isinstance(d, dict):
                     bufs += list(d.values())
