@@ -10,7 +10,7 @@ from .core.save_level import HardwareCost, SaveLevelPlan
 from .core.working_set import WorkingSetConfig, determine_working_set_config
 from .engine.active_model import ActiveModel, StepStats
 from .io.sequence import Sequence
-from .io.sources import (CustomSchemaTokenSource, HFTokenSource, JsonSFTTokenSource, RankStridedSource, RawTokenSource,
+from .io.sources import (CustomSchemaTokenSource, HFTokenSource, JsonSFTTokenSource, MultimodalJsonSource, RankStridedSource, RawTokenSource,
                          ShardTokenSource, SyntheticTokenSource, TokenSource)
 from .optim import AdamW, HybridMuonAdamW, Muon
 from . import export  # noqa: E402  (``flextrain_b200.export.save_hf_full`` / ``save_lora_adapter`` / ``save_hf_merged``)
@@ -20,7 +20,7 @@ __version__ = "0.1.0"
 __all__ = [
     "from_pretrained", "from_dims", "register_block_builder", "BuildContext", "ActiveModel", "StepStats",
     "AdamW", "Muon", "HybridMuonAdamW", "Sequence", "TokenSource", "SyntheticTokenSource", "RawTokenSource",
-    "ShardTokenSource", "JsonSFTTokenSource", "CustomSchemaTokenSource", "HFTokenSource", "RankStridedSource",
+    "ShardTokenSource", "JsonSFTTokenSource", "CustomSchemaTokenSource", "HFTokenSource", "RankStridedSource", "MultimodalJsonSource",
     "HardwareCost",
     "SaveLevelPlan", "WorkingSetConfig", "determine_working_set_config",
 ]

@@ -232,3 +232,59 @@ class MultimodalProcessorBundle:
                 flags.append(False)
         return build_multimodal_sequence(segs, self.image_token_id, self.geometry.merge, seq_id,
                                          self.vision_start_token_id, self.vision_end_token_id, flags)
+
+    def build_from_messages(self, messages: Seq[dict], images: Seq[Any], seq_id: int = 0,
+                            max_seq_len: Optional[int] = None) -> Optional[Sequence]:
+        """Chat-style row -> multimodal sequence, through the tokenizer's own chat template.
+
+        ``messages`` is the usual list of ``{"role", "content"}`` dicts whose ``content`` is a string or a list of
+        ``{"type": "text", "text": ...}`` / ``{"type": "image"}`` parts; the template must render every image part as
+        one image placeholder token, which is expanded here to the image's merged patch count.  Only the LAST
+        assistant message is trained on (everything the template renders before it is prompt).  Returns ``None`` when
+        ``max_seq_len`` is given and the result is longer."""
+        if self.tokenizer is None or not hasattr(self.tokenizer, "apply_chat_template"):
+            raise RuntimeError("this model directory has no tokenizer with a chat template")
+        if not messages or messages[-1].get("role") != "assistant":
+            raise ValueError("the last message must be the assistant's answer")
+        ids_of = lambda msgs, gen: self._flat_ids(self.tokenizer.apply_chat_template(msgs, tokenize=True,
+                                                                                    add_generation_prompt=gen))
+        full, prompt = ids_of(list(messages), False), ids_of(list(messages[:-1]), True)
+        if full[: len(prompt)] != prompt:
+            raise ValueError("the chat template does not render the prompt as a prefix of the whole conversation")
+        ims = self.process_images(images)
+        n_ph = sum(1 for t in full if t == self.image_token_id)
+        if n_ph != len(ims):
+            raise ValueError(f"the template rendered {n_ph} image placeholders for {len(ims)} images")
+        segs: List[Any] = []
+        flags: List[bool] = []
+        cur: List[int] = []
+        cur_start, k = 0, 0
+        for pos, t in enumerate(full):
+            if t == self.image_token_id:
+                if cur:
+                    segs.append(cur); flags.append(cur_start >= len(prompt))
+                segs.append(ims[k]); flags.append(False)
+                k += 1
+                cur, cur_start = [], pos + 1
+            else:
+                if cur and (cur_start < len(prompt)) != (pos < len(prompt)):      # prompt / answer border
+                    segs.append(cur); flags.append(cur_start >= len(prompt))
+                    cur, cur_start = [], pos
+                if not cur:
+                    cur_start = pos
+                cur.append(int(t))
+        if cur:
+            segs.append(cur); flags.append(cur_start >= len(prompt))
+        # the template already wrote the vision start / end tokens around each placeholder
+        seq = build_multimodal_sequence(segs, self.image_token_id, self.geometry.merge, seq_id, None, None, flags)
+        if max_seq_len is not None and len(seq) > max_seq_len:
+            return None
+        return seq
+
+    @staticmethod
+    def _flat_ids(out) -> List[int]:
+        if isinstance(out, dict) or hasattr(out, "input_ids"):
+            out = out["input_ids"]
+        if out and isinstance(out[0], (list, tuple)):
+            out = out[0]
+        return [int(t) for t in out]

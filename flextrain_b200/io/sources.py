@@ -13,6 +13,7 @@ import collections
 import glob
 import itertools
 import json
+import os
 import queue
 import threading
 from typing import Callable, Deque, Iterable, Iterator, List, Optional, Protocol, Sequence as Seq
@@ -82,6 +83,42 @@ class RankStridedSource(_QueueMixin):
         self.source, self.rank, self.world = source, rank, world
         self._init_queue()
         self._it = itertools.islice(source.iter_sequences(), rank, None, world)
+
+
+class MultimodalJsonSource(_QueueMixin):
+    """JSON / JSONL rows ``{"messages": [...], "images": [path, ...]}`` (chat parts of type ``image`` mark where each
+    image goes) -> multimodal sequences through a :class:`MultimodalProcessorBundle`; image paths are relative to the
+    file.  Rows that fail to load or exceed ``max_seq_len`` are skipped and counted in ``skipped``."""
+
+    def __init__(self, path: str, bundle, max_seq_len: int, loop: bool = True):
+        self.path, self.bundle, self.max_seq_len, self.loop = path, bundle, max_seq_len, loop
+        with open(path) as f:
+            txt = f.read().strip()
+        self.records = json.loads(txt) if txt.startswith("[") else [json.loads(l) for l in txt.splitlines() if l.strip()]
+        self.skipped = 0
+        self._init_queue()
+        self._it = self._generate()
+
+    def _generate(self) -> Iterator[Sequence]:
+        from PIL import Image
+        base, sid = os.path.dirname(os.path.abspath(self.path)), 0
+        while True:
+            emitted = 0
+            for r in self.records:
+                try:
+                    ims = [Image.open(p if os.path.isabs(p) else os.path.join(base, p)).convert("RGB")
+                           for p in r.get("images", [])]
+                    seq = self.bundle.build_from_messages(r["messages"], ims, seq_id=sid, max_seq_len=self.max_seq_len)
+                except (OSError, ValueError, KeyError):
+                    seq = None
+                if seq is None:
+                    self.skipped += 1
+                    continue
+                sid += 1
+                emitted += 1
+                yield seq
+            if not self.loop or emitted == 0:
+                return
 
 
 class SyntheticTokenSource(_QueueMixin):

@@ -246,3 +246,71 @@ def test_multimodal_training_follows_transformers_forward(tmp_path):
     for n, p in visual_before.items():                         # the frozen tower did not move
         mine = vit.w[n.split(".visual.", 1)[1]]
         assert torch.equal(mine.reshape(-1), p.reshape(-1)), n
+
+
+def _chat_tokenizer(path):
+    """Character-level tokenizer with vision special tokens and a chat template that renders image parts as
+    ``<|vision_start|><|image_pad|><|vision_end|>`` (the shape of the Qwen-VL templates)."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    specials = ["<unk>", "</s>", "<|im_start|>", "<|im_end|>", "<|vision_start|>", "<|image_pad|>", "<|vision_end|>"]
+    chars = specials + [chr(c) for c in range(32, 127)] + ["\n"]
+    tok = Tokenizer(models.WordLevel({c: i for i, c in enumerate(chars)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Split("", behavior="isolated")
+    tok.add_special_tokens(specials)
+    fast = transformers.PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", eos_token="</s>")
+    fast.chat_template = (
+        "{% for m in messages %}<|im_start|>{{ m['role'] }}\n"
+        "{% if m['content'] is string %}{{ m['content'] }}{% else %}{% for p in m['content'] %}"
+        "{% if p['type'] == 'image' %}<|vision_start|><|image_pad|><|vision_end|>{% else %}{{ p['text'] }}{% endif %}"
+        "{% endfor %}{% endif %}<|im_end|>\n{% endfor %}"
+        "{% if add_generation_prompt %}<|im_start|>assistant\n{% endif %}")
+    fast.save_pretrained(path)
+    return fast, {s: fast.convert_tokens_to_ids(s) for s in specials}
+
+
+def test_chat_rows_with_images_become_sequences(tmp_path):
+    """Chat rows -> multimodal sequences through the tokenizer's template: every image part expands to its merged
+    patch count between the template's vision tokens, MRoPE spans are recorded, and only the last answer is scored;
+    the JSON source reads image files relative to the data file."""
+    from PIL import Image
+    import numpy as np
+    d = str(tmp_path)
+    fast, ids = _chat_tokenizer(d)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump({"image_token_id": ids["<|image_pad|>"], "vision_start_token_id": ids["<|vision_start|>"],
+                   "vision_end_token_id": ids["<|vision_end|>"],
+                   "vision_config": {"patch_size": 4, "temporal_patch_size": 2, "spatial_merge_size": 2}}, f)
+    with open(os.path.join(d, "preprocessor_config.json"), "w") as f:
+        json.dump({"patch_size": 4, "temporal_patch_size": 2, "merge_size": 2, "image_mean": [0.5] * 3,
+                   "image_std": [0.5] * 3, "size": {"shortest_edge": 64, "longest_edge": 4096}}, f)
+    b = MultimodalProcessorBundle.from_pretrained(d)
+    assert b.tokenizer is not None and b.image_token_id == ids["<|image_pad|>"]
+    rng = np.random.default_rng(0)
+    Image.fromarray(rng.integers(0, 255, (32, 48, 3), dtype=np.uint8)).save(os.path.join(d, "a.png"))
+    Image.fromarray(rng.integers(0, 255, (16, 16, 3), dtype=np.uint8)).save(os.path.join(d, "b.png"))
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "compare "}, {"type": "image"},
+                                         {"type": "text", "text": " and "}, {"type": "image"}]},
+            {"role": "assistant", "content": "first is wider"}]
+    seq = b.build_from_messages(msgs, [Image.open(os.path.join(d, "a.png")), Image.open(os.path.join(d, "b.png"))])
+    toks = seq.tokens.tolist()
+    assert toks.count(ids["<|image_pad|>"]) == 4 * 6 + 2 * 2 and toks.count(ids["<|vision_start|>"]) == 2
+    (s0, t0, h0, w0), (s1, t1, h1, w1) = seq.modality_inputs["image_spans"]
+    assert (t0, h0, w0) == (1, 4, 6) and (t1, h1, w1) == (1, 2, 2)
+    assert toks[s0 - 1] == ids["<|vision_start|>"] and toks[s0 + 24] == ids["<|vision_end|>"]
+    assert toks[s1 - 1] == ids["<|vision_start|>"] and toks[s1 + 4] == ids["<|vision_end|>"]
+    assert seq.modality_inputs["pixel_values"].shape == (8 * 12 + 4 * 4, 96)
+    # scored targets are exactly the answer and what the template closes it with
+    scored = [int(t) for t in seq.targets.tolist() if t != -100]
+    answer = fast("first is wider", add_special_tokens=False)["input_ids"]
+    assert scored[: len(answer)] == answer and len(scored) <= len(answer) + 2
+    assert compute_mrope_position_ids(seq, 0, len(seq)).shape == (len(seq), 3)
+    # the JSON source
+    rows = [{"messages": msgs, "images": ["a.png", "b.png"]},
+            {"messages": msgs, "images": ["missing.png", "b.png"]},                       # skipped: unreadable
+            {"messages": [{"role": "user", "content": "no image here"}, {"role": "assistant", "content": "ok"}]}]
+    with open(os.path.join(d, "mm.jsonl"), "w") as f:
+        f.write("\n".join(json.dumps(r) for r in rows))
+    src = ft.MultimodalJsonSource(os.path.join(d, "mm.jsonl"), b, max_seq_len=512, loop=False)
+    got = list(src.iter_sequences())
+    assert len(got) == 2 and src.skipped == 1 and got[1].modality_inputs is None
+    assert torch.equal(got[0].tokens, seq.tokens)
