@@ -50,7 +50,8 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--truncate-long", action="store_true")
     p.add_argument("--apply-chat-template", action="store_true")
     p.add_argument("--steps", type=int, default=20)
-    p.add_argument("--data-source", choices=("json_sft", "synthetic", "shards"), default="json_sft")
+    p.add_argument("--data-source", choices=("json_sft", "synthetic", "shards", "mm_json"), default="json_sft",
+                   help="mm_json: chat rows with image files for a vision-language checkpoint (MultimodalJsonSource)")
     p.add_argument("--dataset", default=os.path.join(ROOT, "flextrain_b200/configs/examples/data/tiny_math_sft.json"))
     p.add_argument("--synthetic-seq-len", type=int, default=None)
     p.add_argument("--output-dir", default=None)
@@ -192,6 +193,11 @@ def main(argv=None) -> int:
                                       pin=use_cuda)
     elif args.data_source == "shards":
         src = ft.ShardTokenSource(args.dataset, args.max_seq_len)
+    elif args.data_source == "mm_json":
+        if kind != "hf":
+            raise SystemExit("--data-source mm_json needs an HF vision-language model directory (tokenizer, geometry)")
+        from flextrain_b200.io.image_processing import MultimodalProcessorBundle
+        src = ft.MultimodalJsonSource(args.dataset, MultimodalProcessorBundle.from_pretrained(model), args.max_seq_len)
     else:
         from transformers import AutoTokenizer
         tok = AutoTokenizer.from_pretrained(model if kind == "hf" else args.model)
