@@ -167,6 +167,7 @@ class ActiveModel:
                     if hasattr(self.embed, "finalize_round"):
                         self.embed.finalize_round()
                     self.events.clear_per_round()
+        self._fold_tied_head_grad()
         if self.dp is not None:
             self.dp.on_embed_head_grads_ready()
         # one host read for the whole call
@@ -177,6 +178,19 @@ class ActiveModel:
         stats.elapsed_s = time.perf_counter() - t0
         return stats
 
+    def _fold_tied_head_grad(self) -> None:
+        """Tied embeddings are ONE parameter used twice: the head's share of its gradient is added to the embedding's
+        before any reduction or update, and the head mirror is refreshed from the embedding after every step
+        (:meth:`step`).  Training the mirror separately would untie the model, and an export — which writes the
+        embedding only — would lose what the head learnt."""
+        if not getattr(self.head, "tied", False):
+            return
+        ge = self.buffers.embed_grads().get("g_tok_embeddings")
+        gh = self.buffers.head_grads().get("g_head_proj")
+        if ge is not None and gh is not None:
+            ge.add_(gh)
+            gh.zero_()
+
     def step(self) -> int:
         """Optimizer step over embed, head and every layer; returns 0, or the optimizer's error code."""
         self.step_num += 1
@@ -185,6 +199,8 @@ class ActiveModel:
                 rc = self.dp.step(self)
             else:
                 rc = self._step_local()
+            if getattr(self.head, "tied", False) and "g_tok_embeddings" in self.buffers.embed_grads():
+                self.buffers.head_params()["w_head_proj"].copy_(self.buffers.embed_params()["w_tok_embeddings"])
         for l, layer in enumerate(self.layers):
             if self.buffers.params_resident:
                 layer.end_of_step(self.buffers.params(l))
