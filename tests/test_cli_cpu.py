@@ -11,6 +11,15 @@ import pytest
 
 from flextrain_b200.scripts.pretrain import lr_at, parse_count, resolve_shards
 
+def _free_port():
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -142,7 +151,7 @@ def test_train_tensor_parallel_matches_single_rank_and_saves(tmp_path):
                          capture_output=True, text=True, env=env, timeout=600, cwd=str(tmp_path))
     assert one.returncode == 0, one.stderr[-3000:]
     two = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                          "--master-addr", "127.0.0.1", "--master-port", "29641", os.path.join(ROOT, "train.py"),
+                          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(ROOT, "train.py"),
                           *common, "--tp", "2", "--save", "--output-dir", str(tmp_path / "b")],
                          capture_output=True, text=True, env=env, timeout=600, cwd=str(tmp_path))
     assert two.returncode == 0, two.stderr[-3000:]

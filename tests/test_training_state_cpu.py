@@ -12,6 +12,15 @@ import torch
 import flextrain_b200 as ft
 from conftest import build_tiny
 
+def _free_port():
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DIMS = dict(vocab_size=256, n_layers=3, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, expert_dim=128, ffn_dim=128,
             num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
@@ -72,7 +81,7 @@ def test_train_py_resume(launch, tmp_path):
     env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
     base = [sys.executable] if launch == "single" else \
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-         "127.0.0.1", "--master-port", "29671"]
+         "127.0.0.1", "--master-port", str(_free_port())]
     common = [os.path.join(ROOT, "train.py"), "--model", "dims:tiny_moe" if launch == "ep2" else "dims:tiny_llama",
               "--mode", "full", "--data-source",
               "synthetic", "--max-seq-len", "128", "--max-global-batch-tokens", "512", "--lr", "1e-3", "--steps", "5"] + \
