@@ -31,15 +31,23 @@ VISION = dict(depth=2, hidden_size=32, num_heads=2, intermediate_size=64, patch_
               hidden_act="gelu_pytorch_tanh")
 
 
-def _hf_vl_model():
-    cfg = transformers.Qwen3_5Config(text_config=dict(TEXT), vision_config=dict(VISION), image_token_id=IMG,
-                                     video_token_id=VID, vision_start_token_id=VSTART, vision_end_token_id=VEND,
-                                     tie_word_embeddings=False)
+def _hf_vl_model(moe: bool = False):
+    if moe:
+        text = {k: v for k, v in TEXT.items() if k != "intermediate_size"}
+        text.update(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=48, shared_expert_intermediate_size=48)
+        cfg = transformers.Qwen3_5MoeConfig(text_config=text, vision_config=dict(VISION), image_token_id=IMG,
+                                            video_token_id=VID, vision_start_token_id=VSTART,
+                                            vision_end_token_id=VEND, tie_word_embeddings=False)
+    else:
+        cfg = transformers.Qwen3_5Config(text_config=dict(TEXT), vision_config=dict(VISION), image_token_id=IMG,
+                                         video_token_id=VID, vision_start_token_id=VSTART, vision_end_token_id=VEND,
+                                         tie_word_embeddings=False)
     cfg._attn_implementation = "eager"
     cfg.text_config._attn_implementation = "eager"
     cfg.vision_config._attn_implementation = "eager"
     torch.manual_seed(0)
-    model = transformers.Qwen3_5ForConditionalGeneration(cfg).to(torch.float32)
+    cls = transformers.Qwen3_5MoeForConditionalGeneration if moe else transformers.Qwen3_5ForConditionalGeneration
+    model = cls(cfg).to(torch.float32)
     with torch.no_grad():
         for n, p in model.named_parameters():
             if "norm" in n or n.endswith("bias"):
@@ -56,7 +64,7 @@ def _save_hub_layout(model, path):
     save_file({k: v.detach().contiguous() for k, v in model.state_dict().items()},
               os.path.join(path, "model.safetensors"))
     cfg = model.config.to_dict()
-    cfg["architectures"] = ["Qwen3_5ForConditionalGeneration"]
+    cfg["architectures"] = [type(model).__name__]
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(cfg, f)
     with open(os.path.join(path, "preprocessor_config.json"), "w") as f:
@@ -147,11 +155,11 @@ def test_concat_splice_maps_and_gradients():
     assert float(dx[4:].abs().sum()) == 0 and float(dx[:4].sum()) == 32 and d_enc.shape == (2, 8)
 
 
-@pytest.mark.parametrize("chunk", [256, 32])
-def test_vision_language_model_matches_transformers(tmp_path, chunk):
+@pytest.mark.parametrize("chunk,moe", [(256, False), (32, False), (256, True)])
+def test_vision_language_model_matches_transformers(tmp_path, chunk, moe):
     """Loss and text-side gradients of image + text sequences; ``chunk=32`` cuts sequences (and images) across
     chunks, so the rolling KV window, the recurrent state and the splice maps all cross chunk borders."""
-    model = _hf_vl_model()
+    model = _hf_vl_model(moe)
     _save_hub_layout(model, str(tmp_path))
     seqs = [_mm_sequence(0, [(1, 4, 6), (1, 8, 4)], 3, [5, 7, 9]), _mm_sequence(1, [(1, 4, 4)], 4, [11, 6]),
             _mm_sequence(2, [], 5, [40])]
