@@ -220,3 +220,37 @@ def test_training_curve_matches_transformers_with_torch_adamw(name, tmp_path):
             total_el += d.numel()
             worst = max(worst, float(d.max()))
     assert off <= 5e-3 * total_el and worst < 5 * lr, (name, off, total_el, worst)
+
+
+@pytest.mark.parametrize("name,arch,prefix", [("gemma3", "Gemma3ForConditionalGeneration", "model.language_model."),
+                                              ("gemma4", "Gemma4ForConditionalGeneration", "model.language_model."),
+                                              ("gemma3", "Gemma3ForConditionalGeneration", "language_model.model.")])
+def test_text_tower_of_a_multimodal_checkpoint_loads(name, arch, prefix, tmp_path):
+    """Multimodal wrappers nest the decoder (``text_config`` in the config, another prefix on the tensors, in two
+    historical spellings); ``from_pretrained`` trains the text tower of such a checkpoint like the plain model."""
+    import json
+    import os
+    from safetensors.torch import save_file
+    model = _hf_model(name)
+    os.makedirs(str(tmp_path), exist_ok=True)
+    state = {}
+    for k, v in model.state_dict().items():
+        if k == "lm_head.weight":
+            continue                                            # tied: the wrapper stores the embedding only
+        state[(prefix + k[len("model."):]) if k.startswith("model.") else k] = v.detach().contiguous()
+    save_file(state, os.path.join(str(tmp_path), "model.safetensors"))
+    with open(os.path.join(str(tmp_path), "config.json"), "w") as f:
+        json.dump({"architectures": [arch], "model_type": name, "text_config": model.config.to_dict()}, f)
+    am = ft.from_pretrained(str(tmp_path), optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32), max_seq_len=64,
+                            max_global_batch_tokens=128, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
+                            device="cpu", compute_dtype=torch.float32, master_dtype=torch.float32,
+                            grad_dtype=torch.float32, host_backend=UnpinnedHostBackend(), strict=True,
+                            working_set=ft.WorkingSetConfig.simple(max_seq_len=64, max_global_batch_tokens=128))
+    seqs = ft.SyntheticTokenSource(model.config.vocab_size, 64, seed=4).get_sequences(128)
+    total = 0.0
+    with torch.no_grad():
+        for s in seqs:
+            z = model(input_ids=s.tokens[None]).logits[0].float()
+            total += float(torch.nn.functional.cross_entropy(z, s.targets, ignore_index=-100, reduction="sum"))
+    st = am.fwd_bwd(seqs, loss_scale_factor=1.0)
+    assert abs(st.loss_sum - total) / total < 2e-4
