@@ -1,6 +1,7 @@
 """Tiny Llama on CPU in fp32: the engine's hand-written forward/backward/optimizer against
 ``torch.autograd`` + ``torch.optim.AdamW`` (2 layers, hidden 256, 4 query / 2 KV heads, head_dim 64,
 SwiGLU 688, vocab 1024, seq 128, batch 2, 3 AdamW steps at lr 1e-3)."""
+import pytest
 import torch
 
 import flextrain_b200 as ft
@@ -58,3 +59,29 @@ def test_per_token_loss_written_back():
     tot = sum(float(s.per_token_loss.sum()) for s in seqs)
     assert abs(tot - st.loss_sum) < 1e-2
     assert st.active_tokens == 256 and st.tokens == 256
+
+
+@pytest.mark.parametrize("tied", [False, True])
+def test_gradient_accumulation_over_calls_equals_one_call(tied):
+    """Gradients accumulate over ``fwd_bwd`` calls until ``step``: two calls with half the batch each (and the whole
+    batch's scale factor) leave the same weights as one call with everything — also for tied embeddings, whose
+    head share is folded into the embedding gradient at the end of every call."""
+    import flextrain_b200 as ft
+    from conftest import build_tiny
+    dims = dict(vocab_size=256, n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, expert_dim=128,
+                ffn_dim=128, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+    mk = lambda: build_tiny(dims=dims, hyper={"tie_embeddings": tied}, max_seq_len=64, batch_tokens=256,
+                            optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32))
+    seqs = ft.SyntheticTokenSource(256, 64, seed=7).get_sequences(256)
+    n_active = sum(s.active_token_count for s in seqs)
+    a, b = mk(), mk()
+    assert a.head.tied == tied
+    a.fwd_bwd(seqs, loss_scale_factor=1.0 / n_active)
+    a.step()
+    b.fwd_bwd(seqs[:2], loss_scale_factor=1.0 / n_active)
+    b.fwd_bwd(seqs[2:], loss_scale_factor=1.0 / n_active)
+    b.step()
+    for (s, l, n, t), (_, _, _, u) in zip(a.named_master_params(), b.named_master_params()):
+        torch.testing.assert_close(t, u, rtol=0, atol=2e-6, msg=f"{s}/{l}/{n}")
+    if tied:
+        assert torch.equal(a.buffers.head_params()["w_head_proj"], a.buffers.embed_params()["w_tok_embeddings"])
