@@ -128,8 +128,10 @@ def localize_for_tp(mc: ModelConfig, tp: int) -> ModelConfig:
     if mc.n_heads % tp or mc.n_kv_heads % tp or mc.ffn_dim % tp:
         raise ValueError(f"tensor parallel degree {tp} must divide n_heads {mc.n_heads}, n_kv_heads {mc.n_kv_heads} "
                          f"and ffn_dim {mc.ffn_dim}")
-    if mc.num_experts > 0 or mc.gdn is not None or mc.qk_norm == "row" or mc.post_norms:
-        raise NotImplementedError("tensor parallelism covers dense pre-norm attention + gated-FFN models")
+    if mc.num_experts > 0 or mc.gdn is not None or mc.qk_norm == "row":
+        raise NotImplementedError("tensor parallelism covers dense attention + gated-FFN models (per-head QK-norm, "
+                                  "sandwich norms, windows and soft-caps included; no MoE, linear attention or "
+                                  "full-row QK-norm)")
     return replace(mc, n_heads=mc.n_heads // tp, n_kv_heads=mc.n_kv_heads // tp, ffn_dim=mc.ffn_dim // tp)
 
 

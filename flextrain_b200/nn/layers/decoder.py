@@ -115,10 +115,11 @@ class DecoderLayer:
         fields.append(ActivationField("xo", lambda t: (t // sp, d), dt, 2))
         fields += (self.ffn or self.moe).activation_fields()
         if c.post_norms:
-            fields += [ActivationField("post_attn_rstd", lambda t: (t,), f32, 0),
-                       ActivationField("post_ffn_rstd", lambda t: (t,), f32, 0),
-                       ActivationField("attn_branch", lambda t: (t, d), dt, 2),
-                       ActivationField("ffn_branch", lambda t: (t, d), dt, 3)]
+            # the branch outputs come out of the row-parallel projections, i.e. already token-sharded
+            fields += [ActivationField("post_attn_rstd", lambda t: (t // sp,), f32, 0),
+                       ActivationField("post_ffn_rstd", lambda t: (t // sp,), f32, 0),
+                       ActivationField("attn_branch", lambda t: (t // sp, d), dt, 2),
+                       ActivationField("ffn_branch", lambda t: (t // sp, d), dt, 3)]
         return ActivationSchema(fields, max_tier=3)
 
     # --------------------------------------------------------------------- forward
@@ -263,7 +264,7 @@ class DecoderLayer:
         """Route the projections through the tensor-parallel handle (fused all-gather→GEMM / GEMM→reduce-scatter)."""
         if tp is None:
             return
-        if self.attn is None or self.ffn is None or self.cfg.post_norms or self.cfg.lora is not None:
+        if self.attn is None or self.ffn is None or self.cfg.lora is not None:
             raise NotImplementedError("tensor parallelism covers dense attention + gated-FFN layers without LoRA")
         for g in (self.attn.qkv, self.attn.o, self.ffn.up, self.ffn.down):
             g.tp = tp

@@ -39,8 +39,10 @@ def build(dev, dtype, world, rank, mode, backend):
                                     round_tokens=per_rank, world_size=world,
                                     shard="opt+grad" if world > 1 else "none")
     par = {"ep": mp} if mode.startswith("ep") else {"tp": mp}
+    gemma = mode == "tp_gemma"          # sandwich norms, per-head QK-norm, sliding + global layers, tied scaled embedding
     return ft.from_dims(MOE_DIMS if mode.startswith("ep") else DENSE_DIMS,
-                        arch="qwen3_moe" if mode.startswith("ep") else "llama",
+                        arch="qwen3_moe" if mode.startswith("ep") else ("gemma3" if gemma else "llama"),
+                        hyperparams={"sliding_window": 64, "layer_pattern": "SF"} if gemma else None,
                         optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32),
                         max_seq_len=seq, max_global_batch_tokens=GB, max_gpu_mem_bytes=8 << 30,
                         max_host_mem_bytes=8 << 30, device=dev, compute_dtype=dtype, master_dtype=dtype,

@@ -37,6 +37,20 @@ def test_engine_tensor_parallel_pads_ragged_chunks(tmp_path):
     assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
 
 
+def test_engine_tensor_parallel_gemma_layer_shape(tmp_path):
+    """Sandwich (pre + post) norms on the token-sharded branch outputs, per-head QK-norm whose replicated gains see
+    different heads per rank, sliding and global layers, tied scaled embedding: two ranks match the unsharded run."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "tpg.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective",
+           "tp_gemma", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
+
+
 def test_engine_grid_of_tensor_parallel_pairs(tmp_path):
     """Four ranks as a 2 x 2 grid (two tensor-parallel pairs, data parallel across the pairs) over library collectives:
     replicated tensors are reduced over the job, each pair's parts over their replicas; losses and the re-gathered
