@@ -144,7 +144,13 @@ def _init_lora_params(am: ActiveModel, seed: int, a_std: float) -> None:
     g = torch.Generator().manual_seed(seed)
     for scope, l, name, t in am.named_master_params():
         if name.endswith("_lora_a"):
-            t.copy_((torch.randn(t.shape, generator=g, dtype=torch.float32) * a_std).to(t.dtype))
+            spec = am.spec_of(scope, l, name)
+            if spec.is_local_part:                             # draw the unsharded tensor, keep this rank's slice
+                dim, a, b = spec.local_slice
+                full = torch.randn(spec.global_shape, generator=g, dtype=torch.float32) * a_std
+                t.copy_(full.narrow(dim, a, b - a).to(t.dtype))
+            else:
+                t.copy_((torch.randn(t.shape, generator=g, dtype=torch.float32) * a_std).to(t.dtype))
         elif name.endswith("_lora_b"):
             t.zero_()
 

@@ -184,6 +184,13 @@ def build_model_parts(mc: ModelConfig, dt: DTypePolicy, lora: Optional[LoRAConfi
                     t.mark_local(0, tp_rank, tp)
                 elif t.name in TP_ROW_TENSORS:
                     t.mark_local(1, tp_rank, tp)
+                # LoRA on a sharded weight W (out, in): W + s * B @ A stays local when the adapter on the sharded side
+                # is sharded with it (B rows for column-parallel W, A columns for row-parallel W); the other adapter is
+                # replicated and its gradient, a partial sum on every rank, goes through the data-parallel reduction
+                elif t.name.endswith("_lora_b") and t.name[: -len("_lora_b")] in TP_COL_TENSORS:
+                    t.mark_local(0, tp_rank, tp)
+                elif t.name.endswith("_lora_a") and t.name[: -len("_lora_a")] in TP_ROW_TENSORS:
+                    t.mark_local(1, tp_rank, tp)
         layers.append(layer)
     return embed, layers, head
 

@@ -188,12 +188,12 @@ def collect_hf_state(am, lora_merge: bool = False) -> Dict[str, torch.Tensor]:
             ts_spec = specs.get(e.name) if specs is not None else None
             if not writer and not (ts_spec is not None and ts_spec.is_local_part):
                 continue
+            if lora_merge and (e.name + "_lora_a") in params:
+                from ..export._merged import merged_weight
+                t = merged_weight(params, e.name, am).to(t.device)      # merged locally, gathered below
             if ts_spec is not None and ts_spec.is_local_part:
                 t = gather_local_parts(t, ts_spec, am)     # collective: every rank takes part in the export
             t = t.to("cpu")
-            if lora_merge and (e.name + "_lora_a") in params:
-                from ..export._merged import merged_weight
-                t = merged_weight(params, e.name, am)
             if e.plus_one:
                 t = (t.to(torch.float32) - 1.0).to(t.dtype)
             if e.transpose:

@@ -264,8 +264,8 @@ class DecoderLayer:
         """Route the projections through the tensor-parallel handle (fused all-gather→GEMM / GEMM→reduce-scatter)."""
         if tp is None:
             return
-        if self.attn is None or self.ffn is None or self.cfg.lora is not None:
-            raise NotImplementedError("tensor parallelism covers dense attention + gated-FFN layers without LoRA")
+        if self.attn is None or self.ffn is None:
+            raise NotImplementedError("tensor parallelism covers dense attention + gated-FFN layers")
         for g in (self.attn.qkv, self.attn.o, self.ffn.up, self.ffn.down):
             g.tp = tp
 

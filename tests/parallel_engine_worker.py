@@ -39,6 +39,9 @@ def build(dev, dtype, world, rank, mode, backend):
                                     round_tokens=per_rank, world_size=world,
                                     shard="opt+grad" if world > 1 else "none")
     par = {"ep": mp} if mode.startswith("ep") else {"tp": mp}
+    lora = dict(lora_targets="all", lora_rank=4, lora_alpha=8.0, lora_adapter_compute_dtype=dtype,
+                lora_adapter_master_dtype=dtype, lora_adapter_grad_dtype=dtype,
+                lora_adapter_opt_state_dtype=torch.float32) if mode == "tp_lora" else {}
     gemma = mode == "tp_gemma"          # sandwich norms, per-head QK-norm, sliding + global layers, tied scaled embedding
     return ft.from_dims(MOE_DIMS if mode.startswith("ep") else DENSE_DIMS,
                         arch="qwen3_moe" if mode.startswith("ep") else ("gemma3" if gemma else "llama"),
@@ -47,13 +50,14 @@ def build(dev, dtype, world, rank, mode, backend):
                         max_seq_len=seq, max_global_batch_tokens=GB, max_gpu_mem_bytes=8 << 30,
                         max_host_mem_bytes=8 << 30, device=dev, compute_dtype=dtype, master_dtype=dtype,
                         grad_dtype=dtype, working_set=ws, world_size=world, rank=rank,
-                        host_backend=UnpinnedHostBackend() if dev == "cpu" else None, **(par if world > 1 else {}))
+                        host_backend=UnpinnedHostBackend() if dev == "cpu" else None, **lora,
+                        **(par if world > 1 else {}))
 
 
 def train(am, rank, world, dev, mode):
     src = ft.SyntheticTokenSource(512, RAGGED if mode == "tp_ragged" else SEQ, seed=5)
     losses = []
-    for _ in range(STEPS):
+    for _ in range(4 if mode == "tp_lora" else STEPS):      # LoRA: B starts at zero, A only moves from step 2 on
         seqs = src.get_sequences(sum(RAGGED) if mode == "tp_ragged" else GB)
         if mode.startswith("ep"):
             seqs = seqs[rank::world]                  # data parallel: each rank takes its share of the batch
@@ -88,18 +92,36 @@ def main():
     losses = train(am, rank, world, dev, mode)
     if am.ep is not None:
         am.ep.check()
-    state = collect_hf_state(am)                  # collective: gathers the expert shards
+    merge = mode == "tp_lora"                     # compare base + adapters, merged: the adapters are what trained
+    state = collect_hf_state(am, lora_merge=merge)      # collective: gathers the tensor- / expert-parallel parts
+    adapters = {}
+    if mode == "tp_lora":                         # gather every adapter (collective) for a direct comparison
+        from flextrain_b200.io.hf_weights import gather_local_parts
+        for l, layer in enumerate(am.layers):
+            for n, t in am.buffers.host_params(l).items():
+                if "_lora_" in n:
+                    spec = layer.param_spec.get(n)
+                    adapters[(l, n)] = (gather_local_parts(t.detach(), spec, am) if spec.is_local_part else t.detach()).float().cpu()
     res = None
     if rank == 0:
         full = build(dev, dtype, 1, 0, mode, backend)
         ref_losses = train(full, 0, 1, dev, mode)
-        ref_state = collect_hf_state(full)
+        ref_state = collect_hf_state(full, lora_merge=merge)
         worst = 0.0
         for k, v in ref_state.items():
             d = float((state[k].float() - v.float()).abs().max())
             worst = max(worst, d)
         res = {"local_rows": int(local_rows), "loss_diff": max(abs(a - b) for a, b in zip(losses, ref_losses)),
                "param_diff": worst, "losses": losses, "keys": len(ref_state)}
+        if adapters:
+            worst_a, moved = 0.0, 0.0
+            for l in range(len(full.layers)):
+                for n, t in full.buffers.host_params(l).items():
+                    if "_lora_" in n:
+                        worst_a = max(worst_a, float((adapters[(l, n)] - t.detach().float().cpu()).abs().max()))
+                        if n.endswith("_lora_b"):
+                            moved = max(moved, float(t.detach().abs().max()))
+            res["adapter_diff"], res["adapter_moved"] = worst_a, moved
         if backend == "p2p":
             from flextrain_b200.ops import cuda as k
             res["errors"] = k.device_error_words()

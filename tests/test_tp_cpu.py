@@ -51,6 +51,22 @@ def test_engine_tensor_parallel_gemma_layer_shape(tmp_path):
     assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
 
 
+def test_engine_tensor_parallel_lora(tmp_path):
+    """LoRA on sharded weights: the adapter on a weight's sharded side is sharded with it, the other one is replicated
+    and its partial gradients are summed by the data-parallel reduction; four steps (both adapters move) match the
+    unsharded LoRA run, compared through the merged weights."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "tpl.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective",
+           "tp_lora", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-4, res
+    assert res["adapter_moved"] > 1e-3 and res["adapter_diff"] < 1e-2 * res["adapter_moved"], res
+
+
 def test_engine_grid_of_tensor_parallel_pairs(tmp_path):
     """Four ranks as a 2 x 2 grid (two tensor-parallel pairs, data parallel across the pairs) over library collectives:
     replicated tensors are reduced over the job, each pair's parts over their replicas; losses and the re-gathered
