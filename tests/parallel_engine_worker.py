@@ -42,10 +42,16 @@ def build(dev, dtype, world, rank, mode, backend):
     lora = dict(lora_targets="all", lora_rank=4, lora_alpha=8.0, lora_adapter_compute_dtype=dtype,
                 lora_adapter_master_dtype=dtype, lora_adapter_grad_dtype=dtype,
                 lora_adapter_opt_state_dtype=torch.float32) if mode == "tp_lora" else {}
+    hybrid = mode == "ep_hybrid"        # Gated DeltaNet + gated attention layers, routed + shared experts
     gemma = mode == "tp_gemma"          # sandwich norms, per-head QK-norm, sliding + global layers, tied scaled embedding
-    return ft.from_dims(MOE_DIMS if mode.startswith("ep") else DENSE_DIMS,
-                        arch="qwen3_moe" if mode.startswith("ep") else ("gemma3" if gemma else "llama"),
-                        hyperparams={"sliding_window": 64, "layer_pattern": "SF"} if gemma else None,
+    hyper = {"sliding_window": 64, "layer_pattern": "SF"} if gemma else None
+    dims = MOE_DIMS if mode.startswith("ep") else DENSE_DIMS
+    if hybrid:
+        dims = dict(MOE_DIMS, num_shared_experts=1, shared_dim=64)
+        hyper = {"layer_pattern": "1L1F", "gdn": {"n_k_heads": 2, "n_v_heads": 4, "head_k_dim": 16, "head_v_dim": 16}}
+    return ft.from_dims(dims,
+                        arch="qwen3_5_moe" if hybrid else "qwen3_moe" if mode.startswith("ep") else ("gemma3" if gemma else "llama"),
+                        hyperparams=hyper,
                         optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32),
                         max_seq_len=seq, max_global_batch_tokens=GB, max_gpu_mem_bytes=8 << 30,
                         max_host_mem_bytes=8 << 30, device=dev, compute_dtype=dtype, master_dtype=dtype,

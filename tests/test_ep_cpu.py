@@ -48,3 +48,17 @@ def test_engine_grid_of_expert_parallel_pairs(tmp_path):
     res = json.load(open(out))
     assert res["local_rows"] == 4
     assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
+
+
+def test_engine_expert_parallel_hybrid_with_shared_expert(tmp_path):
+    """Qwen3.5-MoE layer shapes under ep=2: Gated DeltaNet and gated-attention mixers stay data parallel, routed experts
+    are sharded, the sigmoid-gated shared expert is replicated; matches the unsharded run."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "eph.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective",
+           "ep_hybrid", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert res["local_rows"] == 4 and res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
