@@ -59,6 +59,9 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
     builder = _BLOCK_BUILDERS.get(arch_key) if arch_key else None
     if tp > 1 and ep > 1:
         raise NotImplementedError("tensor and expert parallelism cannot be combined")
+    if tp > 1 and type(optimizer).__name__ in ("Muon", "HybridMuonAdamW"):
+        raise NotImplementedError("Muon orthogonalises whole weight matrices; a tensor-parallel rank holds a slice of "
+                                  "each, and the slice's orthogonalisation is a different update: use AdamW with --tp")
     if (tp > 1 and world_size % tp) or (ep > 1 and world_size % ep):
         raise ValueError(f"world size {world_size} is not a multiple of tp={tp} / ep={ep}")
     embed, layers, head = build_model_parts(mc, dt, lora, head_chunk_size, builder, tp=tp, tp_rank=rank % max(tp, 1))

@@ -90,3 +90,15 @@ def test_tensor_spec_localisation():
     u = TensorSpec("w_o", (16, 4), torch.float32).mark_local(1, 2, 4)
     assert u.shape == (16, 4) and u.global_shape == (16, 16) and u.local_slice == (1, 8, 12)
     assert not TensorSpec("w_attn_norm", (16,), torch.float32).is_local_part
+
+
+def test_muon_is_refused_under_tensor_parallelism():
+    import pytest
+    import torch
+    import flextrain_b200 as ft
+    dims = dict(vocab_size=512, n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, expert_dim=512,
+                ffn_dim=512, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+    with pytest.raises(NotImplementedError, match="Muon"):
+        ft.from_dims(dims, optimizer=ft.HybridMuonAdamW(), max_seq_len=128, max_global_batch_tokens=512,
+                     max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30, device="cpu", world_size=2, rank=0, tp=2,
+                     plan_only=True)
