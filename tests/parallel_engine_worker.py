@@ -108,6 +108,10 @@ def main():
                 if "_lora_" in n:
                     spec = layer.param_spec.get(n)
                     adapters[(l, n)] = (gather_local_parts(t.detach(), spec, am) if spec.is_local_part else t.detach()).float().cpu()
+    adapter_dir = out_path + ".adapter"
+    if mode == "tp_lora":
+        from flextrain_b200.export import save_lora_adapter
+        save_lora_adapter(am, adapter_dir)        # collective gather of the sharded adapters; rank 0 writes
     res = None
     if rank == 0:
         full = build(dev, dtype, 1, 0, mode, backend)
@@ -128,6 +132,9 @@ def main():
                         if n.endswith("_lora_b"):
                             moved = max(moved, float(t.detach().abs().max()))
             res["adapter_diff"], res["adapter_moved"] = worst_a, moved
+            from safetensors import safe_open
+            with safe_open(os.path.join(adapter_dir, "adapter_model.safetensors"), framework="pt") as f:
+                res["adapter_file_shapes"] = {k: list(f.get_tensor(k).shape) for k in f.keys() if "layers.0." in k}
         if backend == "p2p":
             from flextrain_b200.ops import cuda as k
             res["errors"] = k.device_error_words()

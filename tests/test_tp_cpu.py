@@ -65,6 +65,10 @@ def test_engine_tensor_parallel_lora(tmp_path):
     res = json.load(open(out))
     assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-4, res
     assert res["adapter_moved"] > 1e-3 and res["adapter_diff"] < 1e-2 * res["adapter_moved"], res
+    shapes = res["adapter_file_shapes"]                        # the PEFT file holds whole adapters, not shards
+    assert shapes["base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight"] == [256, 4]
+    assert shapes["base_model.model.model.layers.0.self_attn.o_proj.lora_A.weight"] == [4, 256]
+    assert shapes["base_model.model.model.layers.0.mlp.down_proj.lora_A.weight"] == [4, 512]
 
 
 def test_engine_grid_of_tensor_parallel_pairs(tmp_path):
