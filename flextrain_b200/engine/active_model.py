@@ -108,8 +108,9 @@ class ActiveModel:
 
     # ====================================================================== public API
     def fwd_bwd(self, seqs: Seq[Sequence], loss_scale_factor: Optional[float] = None,
-                total_tokens_per_step: Optional[int] = None, loss_fn=None) -> StepStats:
-        """Forward + backward over ``seqs``; gradients accumulate until :meth:`step`."""
+                total_tokens_per_step: Optional[int] = None, loss_fn=None, forward_only: bool = False) -> StepStats:
+        """Forward + backward over ``seqs``; gradients accumulate until :meth:`step`.  ``forward_only`` stops after the
+        loss (see :meth:`evaluate`): no gradient buffer is read or written."""
         t0 = time.perf_counter()
         ws = self.ws
         if loss_scale_factor is None:
@@ -138,7 +139,7 @@ class ActiveModel:
                     stats.host_act_bytes = max(stats.host_act_bytes, plan.host_bytes)
                     for k, v in plan.histogram().items():
                         stats.plan_hist[k] = stats.plan_hist.get(k, 0) + v
-                    if self._zero_grad:
+                    if self._zero_grad and not forward_only:
                         self._zero_all_grads()
                         self._zero_grad = False
                     ctx_base = dict(kv_window=self.buffers.kv_window, total_tokens_per_step=total_tokens_per_step,
@@ -153,30 +154,42 @@ class ActiveModel:
                     with _nvtx("Head"):
                         for c, meta in enumerate(metas):
                             ls = self.head.forward_backward(transitions[c], self._token_shard(meta),
-                                                            self.buffers.head_params(), self.buffers.head_grads(),
-                                                            loss_fn, loss_scale_factor)
+                                                            self.buffers.head_params(),
+                                                            {} if forward_only else self.buffers.head_grads(),
+                                                            loss_fn, loss_scale_factor, want_dx=not forward_only)
                             loss_acc += ls.total_loss
                             act_acc += ls.active_tokens
                             pending_losses.append((rseqs, meta, ls.per_token_loss))
-                    with _nvtx("Backward"):
-                        self._backward_pass(metas, plan, transitions, slots, ctx_base, stats, last_round)
-                    with _nvtx("Embed Backward"):
-                        for c, meta in enumerate(metas):
-                            self.embed.backward(transitions[c], self._token_shard(meta),
-                                                self.buffers.embed_params(), self.buffers.embed_grads())
+                    if forward_only:
+                        self.streams.synchronize_all()      # saved activations are dropped: let their copies finish
+                    else:
+                        with _nvtx("Backward"):
+                            self._backward_pass(metas, plan, transitions, slots, ctx_base, stats, last_round)
+                        with _nvtx("Embed Backward"):
+                            for c, meta in enumerate(metas):
+                                self.embed.backward(transitions[c], self._token_shard(meta),
+                                                    self.buffers.embed_params(), self.buffers.embed_grads())
                     if hasattr(self.embed, "finalize_round"):
                         self.embed.finalize_round()
                     self.events.clear_per_round()
-        self._fold_tied_head_grad()
-        if self.dp is not None:
-            self.dp.on_embed_head_grads_ready()
+        if not forward_only:
+            self._fold_tied_head_grad()
+            if self.dp is not None:
+                self.dp.on_embed_head_grads_ready()
         # one host read for the whole call
         stats.loss_sum = float(loss_acc)
         stats.active_tokens = int(act_acc)
         self._write_back_losses(pending_losses)
-        self._pending_tokens += stats.tokens
+        if not forward_only:
+            self._pending_tokens += stats.tokens
         stats.elapsed_s = time.perf_counter() - t0
         return stats
+
+    def evaluate(self, seqs: Seq[Sequence], loss_fn=None) -> StepStats:
+        """Loss of ``seqs`` under the current weights, forward only: gradients accumulated so far, optimizer state and
+        the step counter are untouched (``stats.loss`` is the mean over active tokens; per-token losses are written
+        back to the sequences)."""
+        return self.fwd_bwd(seqs, loss_scale_factor=1.0, loss_fn=loss_fn, forward_only=True)
 
     def _fold_tied_head_grad(self) -> None:
         """Tied embeddings are ONE parameter used twice: the head's share of its gradient is added to the embedding's

@@ -255,15 +255,13 @@ def run(args) -> int:
 
 
 def evaluate(am, source, eval_tokens: int, batch_tokens: int) -> float:
-    """Mean loss over ``eval_tokens`` without touching the weights: forward+backward is run and the gradients
-    are discarded (the engine's head computes the loss inside its fused forward/backward)."""
+    """Mean loss over ``eval_tokens`` under the current weights (forward only; nothing of the training state moves)."""
     tot, n = 0.0, 0
     while n < eval_tokens:
         seqs = source.get_sequences(min(batch_tokens, eval_tokens - n) or batch_tokens)
         if not seqs:
             break
-        st = am.fwd_bwd(seqs)
-        am._zero_grad = True
+        st = am.evaluate(seqs)
         tot += st.loss_sum
         n += st.active_tokens
     return tot / max(n, 1)

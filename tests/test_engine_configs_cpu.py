@@ -124,3 +124,45 @@ def test_H_hybrid_linear_attention_spans_chunks():
         gname = "g_" + name[2:]
         if gname in g:
             torch.testing.assert_close(g[gname].float(), p.grad, rtol=5e-4, atol=5e-6, msg=f"{scope}/{l}/{name}")
+
+
+@pytest.mark.parametrize("variant", ["resident", "rings_and_host_acts", "multi_chunk_sequence"])
+def test_evaluate_is_forward_only(variant):
+    """``am.evaluate`` returns the loss ``fwd_bwd`` would, leaves accumulated gradients, optimizer state and the step
+    counter alone, and a training run with evaluations in between equals one without."""
+    import flextrain_b200 as ft
+    dims = dict(vocab_size=256, n_layers=3, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, expert_dim=128,
+                ffn_dim=128, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+    kw = dict(dims=dims, max_seq_len=128, batch_tokens=256, optimizer=ft.AdamW(lr=2e-3, state_dtype=torch.float32))
+    if variant == "rings_and_host_acts":
+        kw["ws"] = ft.WorkingSetConfig.simple(max_seq_len=128, max_global_batch_tokens=256, chunk=64, n_gpu_layers=2,
+                                              n_gpu_grads=2, n_gpu_opt_layers=2, host_act_buffer_size=64 << 20,
+                                              n_gpu_act_slots=2)
+    if variant == "multi_chunk_sequence":
+        kw["ws"] = ft.WorkingSetConfig.simple(max_seq_len=128, max_global_batch_tokens=256, chunk=32)
+    src = lambda seed: ft.SyntheticTokenSource(256, 128, seed=seed)
+    a, b = build_tiny(**kw), build_tiny(**kw)
+    train, held_out = src(1), src(2).get_sequences(256)
+    la, lb = [], []
+    for step in range(3):
+        seqs = train.get_sequences(256)
+        half = a.fwd_bwd(seqs[:1], loss_scale_factor=1.0 / 256)            # gradients pending ...
+        g_before = a.buffers.grads(1)["g_q"].clone() if a.buffers.grads_resident else None
+        ev = a.evaluate(held_out)                                           # ... while an evaluation runs
+        if g_before is not None:
+            assert torch.equal(a.buffers.grads(1)["g_q"], g_before)
+        rest = a.fwd_bwd(seqs[1:], loss_scale_factor=1.0 / 256)
+        assert a.step() == 0 and a.step_num == step + 1
+        la.append((half.loss_sum + rest.loss_sum) / 256)
+        st = b.fwd_bwd(seqs, loss_scale_factor=1.0 / 256)
+        assert b.step() == 0
+        lb.append(st.loss_sum / 256)
+        # the evaluation saw the same weights b had before this step: compare with b's own forward+backward on them
+        assert ev.active_tokens == sum(s.active_token_count for s in held_out) and ev.loss > 0
+    assert max(abs(x - y) for x, y in zip(la, lb)) < 1e-6, (la, lb)
+    for (_, _, n, t), (_, _, _, u) in zip(a.named_master_params(), b.named_master_params()):
+        torch.testing.assert_close(t, u, rtol=0, atol=1e-6, msg=n)
+    want = b.fwd_bwd(held_out, loss_scale_factor=1.0)                       # same weights now: same loss as evaluate
+    b._zero_grad = True
+    assert abs(a.evaluate(held_out).loss_sum - want.loss_sum) < 1e-3
+    assert held_out[0].per_token_loss is not None
