@@ -48,7 +48,9 @@ def _train_argv(cfg) -> List[str]:
     for flag, val in (("--max-gpu-mem-gib", h.max_gpu_mem_gib), ("--max-host-mem-gib", h.max_host_mem_gib),
                       ("--force-save-level", t.force_save_level), ("--min-chunk-size", t.min_chunk_size),
                       ("--max-chunk-size", t.max_chunk_size), ("--dp-shard", h.dp_shard),
-                      ("--save-state-every", io.save_state_every or None), ("--resume-state", io.resume_state)):
+                      ("--save-state-every", io.save_state_every or None), ("--resume-state", io.resume_state),
+                      ("--eval-every", io.eval_every or None), ("--eval-tokens", io.eval_tokens if io.eval_every else None),
+                      ("--eval-dataset", d.eval_path)):
         if val is not None:
             argv += [flag, str(val)]
     for flag, on in (("--save", io.save), ("--apply-chat-template", d.apply_chat_template),

@@ -58,8 +58,9 @@ class HardwareConfig:
 
 @dataclass(frozen=True)
 class DataConfig:
-    source: str = "synthetic"             # "synthetic" | "json_sft" | "shards"
+    source: str = "synthetic"             # "synthetic" | "json_sft" | "shards" | "mm_json"
     path: Optional[str] = None
+    eval_path: Optional[str] = None       # validation file(s) of the same kind
     synthetic_seq_len: Optional[int] = None
     apply_chat_template: bool = False
     truncate_long: bool = False
@@ -71,6 +72,8 @@ class IOConfig:
     save: bool = False
     resume_from: Optional[str] = None          # weights only: an exported HF directory becomes the model to load
     log_every: int = 1
+    eval_every: int = 0                        # validation loss every N steps (needs data.eval_path unless synthetic)
+    eval_tokens: int = 65536
     save_state_every: int = 0                  # full training state (weights, optimizer state, step) every N steps
     resume_state: Optional[str] = None         # continue exactly from a directory written by save_state_every
 

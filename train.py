@@ -82,6 +82,9 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--save-state-every", type=int, default=0,
                    help="every N steps (and at the end) write a full training state (weights, optimizer state, step) "
                         "to <output-dir>/state; 0 = never")
+    p.add_argument("--eval-every", type=int, default=0, help="every N steps: validation loss (forward only); 0 = never")
+    p.add_argument("--eval-dataset", default=None, help="validation file(s), same kind as --dataset")
+    p.add_argument("--eval-tokens", type=int, default=65536, help="validation tokens per evaluation, over all ranks")
     p.add_argument("--metrics-jsonl", default=None,
                    help="append one JSON object per step (rank 0): step, loss, ema, lr, tokens, tok/s, TFLOPS, memory, "
                         "rounds / chunks, save-tier histogram; default <output-dir>/metrics.jsonl, 'none' disables")
@@ -188,23 +191,31 @@ def main(argv=None) -> int:
     # tensor-parallel group work on the SAME sequences, so they read identical data
     data_ranks, data_rank = (world // args.tp, rank // args.tp) if args.tp > 1 else (world, rank)
     per_rank_tokens = args.max_global_batch_tokens // data_ranks
-    if args.data_source == "synthetic":
-        src = ft.SyntheticTokenSource(vocab, args.synthetic_seq_len or args.max_seq_len, seed=args.seed + data_rank,
-                                      pin=use_cuda)
-    elif args.data_source == "shards":
-        src = ft.ShardTokenSource(args.dataset, args.max_seq_len)
-    elif args.data_source == "mm_json":
-        if kind != "hf":
-            raise SystemExit("--data-source mm_json needs an HF vision-language model directory (tokenizer, geometry)")
-        from flextrain_b200.io.image_processing import MultimodalProcessorBundle
-        src = ft.MultimodalJsonSource(args.dataset, MultimodalProcessorBundle.from_pretrained(model), args.max_seq_len)
-    else:
-        from transformers import AutoTokenizer
-        tok = AutoTokenizer.from_pretrained(model if kind == "hf" else args.model)
-        src = ft.JsonSFTTokenSource(args.dataset, tok, args.max_seq_len, apply_chat_template=args.apply_chat_template,
-                                    truncate_long=args.truncate_long)
-    if data_ranks > 1 and args.data_source != "synthetic":
-        src = ft.RankStridedSource(src, data_rank, data_ranks)       # every rank opened the same files
+    def make_source(path, seed, loop=True):
+        if args.data_source == "synthetic":
+            return ft.SyntheticTokenSource(vocab, args.synthetic_seq_len or args.max_seq_len, seed=seed + data_rank,
+                                           pin=use_cuda)
+        if args.data_source == "shards":
+            s = ft.ShardTokenSource(path, args.max_seq_len, loop=loop)
+        elif args.data_source == "mm_json":
+            if kind != "hf":
+                raise SystemExit("--data-source mm_json needs an HF vision-language model directory (tokenizer, geometry)")
+            from flextrain_b200.io.image_processing import MultimodalProcessorBundle
+            s = ft.MultimodalJsonSource(path, MultimodalProcessorBundle.from_pretrained(model), args.max_seq_len, loop=loop)
+        else:
+            from transformers import AutoTokenizer
+            tok = AutoTokenizer.from_pretrained(model if kind == "hf" else args.model)
+            s = ft.JsonSFTTokenSource(path, tok, args.max_seq_len, apply_chat_template=args.apply_chat_template,
+                                      truncate_long=args.truncate_long, loop=loop)
+        # every rank opened the same files: data-parallel ranks each take every data_ranks-th sequence
+        return ft.RankStridedSource(s, data_rank, data_ranks) if data_ranks > 1 else s
+
+    src = make_source(args.dataset, args.seed)
+    args._eval = None
+    if args.eval_every > 0:
+        if args.data_source != "synthetic" and not args.eval_dataset:
+            raise SystemExit("--eval-every needs --eval-dataset (except with synthetic data)")
+        args._eval = lambda: make_source(args.eval_dataset, args.seed + 7919, loop=False)
     out_dir = args.output_dir or os.path.join("runs", f"{os.path.basename(str(args.model).rstrip('/'))}_{args.mode}_sl{args.max_seq_len}")
     os.makedirs(out_dir, exist_ok=True)
     first_step = 1
@@ -226,6 +237,31 @@ def main(argv=None) -> int:
         import torch.distributed as dist
         dist.destroy_process_group()
     return rc
+
+
+def validation_loss(am, source, rank_tokens: int, batch_tokens: int, world: int):
+    """Mean loss over up to ``rank_tokens`` tokens of this rank's share of ``source`` (forward only), averaged over the
+    job; every rank runs the same number of evaluation batches so that collectives inside the model stay matched."""
+    import torch
+    n_batches = max(1, -(-rank_tokens // batch_tokens))
+    tot, cnt = 0.0, 0
+    for _ in range(n_batches):
+        seqs = source.get_sequences(min(batch_tokens, rank_tokens))
+        if am.tp is None and am.ep is None and not seqs:
+            break
+        if not seqs:
+            raise RuntimeError("the validation set ran out on this rank while model-parallel peers still evaluate; "
+                               "use a larger --eval-dataset or fewer --eval-tokens")
+        st = am.evaluate(seqs)
+        tot += st.loss_sum
+        cnt += st.active_tokens
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([tot, float(cnt)], dtype=torch.float64 if am.device.type == "cpu" else torch.float32,
+                         device=am.device)
+        dist.all_reduce(t)
+        tot, cnt = float(t[0]), int(t[1])      # tensor-parallel peers each scored (and counted) their token shard
+    return tot / max(cnt, 1), cnt
 
 
 def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> int:
@@ -310,7 +346,6 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
             f"elapsed {time.time() - t_start:.0f}s")
         mj = getattr(args, "_metrics_path", None)
         if mj:
-            import json
             with open(mj, "a") as f:
                 f.write(json.dumps({"step": step, "loss": loss, "ema": ema, "lr": am.optimizer.lr, "tokens": g_tokens,
                                     "tokens_total": tok_total, "tok_per_s": g_tokens / dt, "step_ms": dt * 1e3,
@@ -319,6 +354,13 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
                                     "chunks": st.n_chunks, "save_tiers": {str(k): v for k, v in st.plan_hist.items()},
                                     "host_act_bytes": st.host_act_bytes, "optimizer_rc": rc,
                                     "wall_s": time.time() - t_start}) + "\n")
+        if getattr(args, "_eval", None) is not None and (step % args.eval_every == 0 or step == last):
+            vl, vn = validation_loss(am, args._eval(), args.eval_tokens // max(world // (am.tp.world if am.tp else 1), 1),
+                                     per_rank_tokens, world)
+            say(f"[eval {step:4d}] loss {vl:.4f} over {vn} tokens")
+            if mj:
+                with open(mj, "a") as f:
+                    f.write(json.dumps({"step": step, "eval_loss": vl, "eval_tokens": vn}) + "\n")
         every = getattr(args, "save_state_every", 0)
         if every and (step % every == 0 or step == last):
             am.save_training_state(args._state_dir, extra={"tokens_seen": tok_total, "ema": ema})
