@@ -50,7 +50,7 @@ def _train_argv(cfg) -> List[str]:
                       ("--max-chunk-size", t.max_chunk_size), ("--dp-shard", h.dp_shard),
                       ("--save-state-every", io.save_state_every or None), ("--resume-state", io.resume_state),
                       ("--eval-every", io.eval_every or None), ("--eval-tokens", io.eval_tokens if io.eval_every else None),
-                      ("--eval-dataset", d.eval_path)):
+                      ("--eval-dataset", d.eval_path), ("--max-grad-norm", o.max_grad_norm)):
         if val is not None:
             argv += [flag, str(val)]
     for flag, on in (("--save", io.save), ("--apply-chat-template", d.apply_chat_template),

@@ -31,6 +31,7 @@ class OptimizerConfig:
     warmup_pct: float = 0.1
     cooldown_start_pct: float = 0.8
     final_pct: float = 0.1
+    max_grad_norm: Optional[float] = None  # clip the global gradient norm before every update
 
 
 @dataclass(frozen=True)

@@ -82,6 +82,7 @@ class ActiveModel:
         self.step_num = 0
         self._zero_grad = True
         self._pending_tokens = 0
+        self.last_grad_norm: Optional[float] = None
         self._grads_fresh: Dict[int, bool] = {}
         attn_layers = [l for l in self.layers if getattr(l, "attn", None) is not None]
         kvh = max((l.attn.cfg.n_kv_heads for l in attn_layers), default=0)
@@ -204,14 +205,54 @@ class ActiveModel:
             ge.add_(gh)
             gh.zero_()
 
-    def step(self) -> int:
-        """Optimizer step over embed, head and every layer; returns 0, or the optimizer's error code."""
+    def grad_norm(self) -> float:
+        """Global L2 norm of the accumulated gradients (one host read).  Replicated tensors count once; the parts of
+        tensor- / expert-parallel tensors are summed over their group."""
+        from .buffers import _views
+        bm = self.buffers
+        self.streams.synchronize_all()
+        dev = self.device
+        rep = torch.zeros((), dtype=torch.float32, device=dev)
+        part = torch.zeros((), dtype=torch.float32, device=dev)
+        units = [(self.embed.param_spec, bm.embed_grads()), (self.head.param_spec, bm.head_grads())]
+        for l, layer in enumerate(self.layers):
+            g = bm.grads(l) if bm.grads_resident else _views(bm.host_g[l], bm.layers[l].g_layout)
+            units.append((layer.param_spec, g))
+        for spec, grads in units:
+            for t in spec.trainable():
+                g = grads.get(t.grad_name)
+                if g is None:
+                    continue
+                sq = g.to(torch.float32).pow(2).sum().to(dev)
+                if t.is_local_part:
+                    part += sq
+                else:
+                    rep += sq
+        group = self.tp or self.ep
+        if group is not None:
+            import torch.distributed as dist
+            dist.all_reduce(part, group=group.pg)
+        return float((rep + part).sqrt())
+
+    def step(self, max_grad_norm: Optional[float] = None) -> int:
+        """Optimizer step over embed, head and every layer; returns 0, or the optimizer's error code.
+        ``max_grad_norm`` scales the gradients down when their global norm exceeds it (``last_grad_norm`` keeps the
+        norm before scaling)."""
         self.step_num += 1
+        grad_scale = 1.0
+        if max_grad_norm is not None:
+            if self.dp is not None and getattr(self.dp, "m", None) is not None:
+                raise NotImplementedError("gradient clipping needs the whole gradient on every rank: use "
+                                          "FTB_DP_BACKEND=collective (the peer-memory path keeps reduced gradients "
+                                          "as shards)")
+            self.last_grad_norm = self.grad_norm()
+            if self.last_grad_norm > max_grad_norm:
+                grad_scale = max_grad_norm / (self.last_grad_norm + 1e-6)
         with _nvtx("Step"):
             if self.dp is not None:
-                rc = self.dp.step(self)
+                rc = self.dp.step(self) if grad_scale == 1.0 else self._step_local(grad_scale)
             else:
-                rc = self._step_local()
+                rc = self._step_local(grad_scale)
             if getattr(self.head, "tied", False) and "g_tok_embeddings" in self.buffers.embed_grads():
                 self.buffers.head_params()["w_head_proj"].copy_(self.buffers.embed_params()["w_tok_embeddings"])
         for l, layer in enumerate(self.layers):
@@ -518,18 +559,20 @@ class ActiveModel:
         st.compute.wait_stream(st.inbound_fwd_context)
 
     # =============================================================================== step
-    def _step_local(self) -> int:
+    def _step_local(self, grad_scale: float = 1.0) -> int:
         bm, st, ev = self.buffers, self.streams, self.events
         opt, rc = self.optimizer, 0
-        rc |= opt.step(self.embed.param_spec, bm.embed_params(), bm.embed_grads(), bm.embed_opt(), self.step_num)
-        rc |= opt.step(self.head.param_spec, bm.head_params(), bm.head_grads(), bm.head_opt(), self.step_num)
+        rc |= opt.step(self.embed.param_spec, bm.embed_params(), bm.embed_grads(), bm.embed_opt(), self.step_num,
+                       grad_scale)
+        rc |= opt.step(self.head.param_spec, bm.head_params(), bm.head_grads(), bm.head_opt(), self.step_num,
+                       grad_scale)
         if rc:
             return rc
         nL = len(self.layers)
         ringed = not (bm.params_resident and bm.grads_resident and bm.opt_resident)
         if not ringed:
             for l, layer in enumerate(self.layers):
-                rc |= opt.step(layer.param_spec, bm.params(l), bm.grads(l), bm.opt_state(l), self.step_num)
+                rc |= opt.step(layer.param_spec, bm.params(l), bm.grads(l), bm.opt_state(l), self.step_num, grad_scale)
                 if rc:
                     return rc
             return rc
@@ -554,7 +597,7 @@ class ActiveModel:
             fetch(k)
         for l, layer in enumerate(self.layers):
             ev.opt_in.wait(l, st.compute)
-            rc |= opt.step(layer.param_spec, bm.params(l), bm.grads(l), bm.opt_state(l), self.step_num)
+            rc |= opt.step(layer.param_spec, bm.params(l), bm.grads(l), bm.opt_state(l), self.step_num, grad_scale)
             if rc:
                 break
             layer.end_of_step(bm.params(l))

@@ -146,7 +146,7 @@ def test_train_tensor_parallel_matches_single_rank_and_saves(tmp_path):
     from safetensors import safe_open
     common = ["--model", "dims:tiny_llama", "--mode", "full", "--data-source", "synthetic", "--max-seq-len", "128",
               "--max-global-batch-tokens", "512", "--steps", "3", "--lr", "1e-3", "--eval-every", "2",
-              "--eval-tokens", "1024"]
+              "--eval-tokens", "1024", "--max-grad-norm", "0.5"]
     env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
     one = subprocess.run([sys.executable, os.path.join(ROOT, "train.py"), *common, "--output-dir", str(tmp_path / "a")],
                          capture_output=True, text=True, env=env, timeout=600, cwd=str(tmp_path))
@@ -162,6 +162,9 @@ def test_train_tensor_parallel_matches_single_rank_and_saves(tmp_path):
     ev = lambda out: [(int(s), float(l), int(n)) for s, l, n in re.findall(r"\[eval\s+(\d+)\] loss ([\d.]+) over (\d+)", out)]
     assert [e[0] for e in ev(one.stdout)] == [2, 3] and all(e[2] == 1024 for e in ev(one.stdout))     # validation, forward only
     assert max(abs(x[1] - y[1]) for x, y in zip(ev(one.stdout), ev(two.stdout))) < 2e-4
+    gn = lambda out: [float(v) for v in re.findall(r"gnorm ([\d.]+)", out)]
+    assert len(gn(one.stdout)) == 3 and min(gn(one.stdout)) > 0.5                      # clipped every step
+    assert max(abs(x - y) for x, y in zip(gn(one.stdout), gn(two.stdout))) < 2e-4      # parts summed over the group
     with safe_open(str(tmp_path / "b" / "final.safetensors"), framework="pt") as f:
         assert f.get_tensor("model.layers.0.mlp.gate_proj.weight").shape == (688, 256)      # gathered, not a shard
         assert f.get_tensor("model.layers.1.self_attn.o_proj.weight").shape == (256, 256)

@@ -85,3 +85,33 @@ def test_gradient_accumulation_over_calls_equals_one_call(tied):
         torch.testing.assert_close(t, u, rtol=0, atol=2e-6, msg=f"{s}/{l}/{n}")
     if tied:
         assert torch.equal(a.buffers.head_params()["w_head_proj"], a.buffers.embed_params()["w_tok_embeddings"])
+
+
+@pytest.mark.parametrize("rings", [False, True])
+def test_gradient_clipping_tracks_torch(rings):
+    """``am.step(max_grad_norm=c)``: the reported global norm equals ``torch.nn.utils.clip_grad_norm_``'s and three
+    clipped AdamW steps follow torch's (resident state, and with weight / gradient / optimizer rings)."""
+    kw = {}
+    if rings:
+        kw["ws"] = ft.WorkingSetConfig.simple(max_seq_len=128, max_global_batch_tokens=256, n_gpu_layers=1, n_gpu_grads=1,
+                                              n_gpu_opt_layers=1)
+    am = build_tiny(**kw)
+    P = clone_params(am)
+    opt = torch.optim.AdamW(list(P.values()), lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0)
+    src = ft.SyntheticTokenSource(1024, 128, seed=1)
+    clip = 0.3
+    for step in range(3):
+        seqs = src.get_sequences(256)
+        opt.zero_grad()
+        loss = naive_loss(am, P, seqs)
+        loss.backward()
+        want_norm = float(torch.nn.utils.clip_grad_norm_(list(P.values()), clip))
+        opt.step()
+        st = am.fwd_bwd(seqs)
+        assert am.step(max_grad_norm=clip) == 0
+        assert want_norm > clip                                             # the clip is active
+        assert abs(am.last_grad_norm - want_norm) < 1e-4 * want_norm, (step, am.last_grad_norm, want_norm)
+        assert abs(st.loss - float(loss)) < 2e-4, (step, st.loss, float(loss))
+    for scope, l, name, t in am.named_master_params():
+        d = (t.float() - P[(scope, l, name)].detach()).abs()
+        assert float(d.max()) < 2.5e-3 and float(d.mean()) < 2e-6, (scope, l, name, float(d.max()), float(d.mean()))

@@ -82,6 +82,9 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--save-state-every", type=int, default=0,
                    help="every N steps (and at the end) write a full training state (weights, optimizer state, step) "
                         "to <output-dir>/state; 0 = never")
+    p.add_argument("--max-grad-norm", type=float, default=None,
+                   help="clip the global gradient norm to this value before every update (library-collective or "
+                        "single-GPU runs; the norm is logged as gnorm)")
     p.add_argument("--eval-every", type=int, default=0, help="every N steps: validation loss (forward only); 0 = never")
     p.add_argument("--eval-dataset", default=None, help="validation file(s), same kind as --dataset")
     p.add_argument("--eval-tokens", type=int, default=65536, help="validation tokens per evaluation, over all ranks")
@@ -316,7 +319,7 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
             g_tokens, g_active = step_tokens, active
         t0 = time.time()
         st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / g_active, total_tokens_per_step=g_tokens)
-        rc = am.step()
+        rc = am.step(max_grad_norm=args.max_grad_norm) if getattr(args, "max_grad_norm", None) else am.step()
         if torch.cuda.is_available():
             torch.cuda.synchronize()
         dt = time.time() - t0
@@ -343,7 +346,8 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
         say(f"[step {step:4d}] lr {am.optimizer.lr:.3e} loss {loss:.4f} ema {ema:.4f} tok/step {g_tokens} "
             f"tok/s {g_tokens / dt:,.0f} TFLOPS_eff {eff * world / dt / 1e12:.1f} TFLOPS_hw {hw * world / dt / 1e12:.1f} "
             f"max_alloc {mem[0]:.1f} GiB max_reserve {mem[1]:.1f} GiB step {dt * 1e3:.0f} ms "
-            f"elapsed {time.time() - t_start:.0f}s")
+            f"elapsed {time.time() - t_start:.0f}s"
+            + (f" gnorm {am.last_grad_norm:.4f}" if getattr(args, "max_grad_norm", None) else ""))
         mj = getattr(args, "_metrics_path", None)
         if mj:
             with open(mj, "a") as f:
@@ -353,6 +357,7 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
                                     "max_alloc_gib": mem[0], "max_reserved_gib": mem[1], "rounds": st.n_rounds,
                                     "chunks": st.n_chunks, "save_tiers": {str(k): v for k, v in st.plan_hist.items()},
                                     "host_act_bytes": st.host_act_bytes, "optimizer_rc": rc,
+                                    "grad_norm": am.last_grad_norm if getattr(args, "max_grad_norm", None) else None,
                                     "wall_s": time.time() - t_start}) + "\n")
         if getattr(args, "_eval", None) is not None and (step % args.eval_every == 0 or step == last):
             vl, vn = validation_loss(am, args._eval(), args.eval_tokens // max(world // (am.tp.world if am.tp else 1), 1),
