@@ -120,6 +120,7 @@ def add_subparser(sub) -> None:
     p.add_argument("--peak-lr", "--lr", dest="peak_lr", type=float, default=3.0e-4)
     p.add_argument("--warmup-frac", "--warmup-pct", dest="warmup_frac", type=float, default=0.02)
     p.add_argument("--weight-decay", type=float, default=0.1)
+    p.add_argument("--grad-clip", type=float, default=None, help="clip the global gradient norm (off by default)")
     p.add_argument("--eval-every", type=int, default=200)
     p.add_argument("--eval-tokens", type=int, default=200_000)
     p.add_argument("--log-every", type=int, default=20)
@@ -231,7 +232,7 @@ def run(args) -> int:
             lr = lr_at(step, steps, args.peak_lr, args.warmup_frac)
             am.optimizer.lr = lr
             st = am.fwd_bwd(train.get_sequences(args.batch_tokens))
-            am.step()
+            am.step(max_grad_norm=args.grad_clip) if args.grad_clip else am.step()
             tokens += st.tokens
             window = (window + [st.loss])[-20:]
             if step % args.log_every == 0 or step == steps or step == 1:
