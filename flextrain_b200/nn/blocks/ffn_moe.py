@@ -24,6 +24,7 @@ import torch
 from ... import ops
 from ...core.activation_schema import ActivationField
 from ...core.layer import LayerContext, TensorSpec
+from ...ops import moe_dump
 from ...ops import reference as ref
 from .ffn_dense import DenseFFNConfig, GatedFFN
 from .linear import LinearGroup, LoRAConfig
@@ -132,6 +133,8 @@ class MoEFFN:
         if self.shared is not None:
             ys, g = self._shared_fwd(h, params, slot)
             out = (out.to(torch.float32) + (ys.to(torch.float32) * g if g is not None else ys.to(torch.float32))).to(out.dtype)
+        if moe_dump.DUMP_DIR is not None:
+            moe_dump.dump(router_logits=logits, router_weights=w, chosen_experts=idx, output=out)
         return out
 
     def recompute(self, h, params, slot) -> None:

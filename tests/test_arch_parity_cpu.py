@@ -133,3 +133,30 @@ def test_moe_load_balance_gradient(arch):
     (tot2 / active).backward()
     d = (P2[("layer", 0, "w_router")].grad - P[("layer", 0, "w_router")].grad).norm()
     assert float(d) > 1e-5
+
+
+def test_moe_dump_and_diff(tmp_path, monkeypatch):
+    """``FTB_MOE_DUMP_DIR`` diagnostics: every MoE forward is written out; two identical runs diff to zero, a run with
+    a perturbed router shows which calls and tensors moved."""
+    from flextrain_b200.ops import moe_dump
+
+    def run(d, perturb):
+        monkeypatch.setattr(moe_dump, "DUMP_DIR", str(d))
+        monkeypatch.setattr(moe_dump, "_calls", 0)
+        am = build_tiny(arch="qwen3_moe", dims=MOE, max_seq_len=48, batch_tokens=96)
+        if perturb:
+            am.buffers.params(1)["w_router"].add_(0.5)
+        am.fwd_bwd(ft.SyntheticTokenSource(512, 48, seed=2).get_sequences(96))
+
+    run(tmp_path / "a", False)
+    run(tmp_path / "b", False)
+    run(tmp_path / "c", True)
+    monkeypatch.setattr(moe_dump, "DUMP_DIR", None)
+    same = moe_dump.diff_dumps(str(tmp_path / "a"), str(tmp_path / "b"))
+    assert len(same) == 2 * 2 * 4 and all(          # 2 layers x 2 chunks, 4 tensors each
+        r.get("max_abs", 0.0) == 0.0 and r.get("rows_with_other_experts", 0.0) == 0.0 for r in same)
+    moved = moe_dump.diff_dumps(str(tmp_path / "a"), str(tmp_path / "c"))
+    first = [r for r in moved if r["call"] == "call000000.pt"]
+    assert all(r.get("max_abs", 0.0) == 0.0 for r in first if "max_abs" in r)          # layer 0 is untouched
+    logits = [r["max_abs"] for r in moved if r["tensor"] == "router_logits"]
+    assert sum(v > 0.1 for v in logits) == 2 and sum(v == 0.0 for v in logits) == 2     # layer 1's router moved, both chunks
