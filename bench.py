@@ -9,10 +9,12 @@ Config (fixed): 32 layers, hidden 4096, 32 query / 8 KV heads, head_dim 128, Swi
 theta 5e5; bf16 weights / activations / gradients, fp32 AdamW state; synthetic uniform tokens, seq_len 1024,
 global batch 524288 tokens per optimizer step (strong scaling: the global batch is split over the GPUs);
 random-init weights.  Every timed step runs forward, backward, the data-parallel gradient reduction and the
-optimizer update.  Two timed regions of K steps each, after W warm-up steps:
-  * device-timed (CUDA events on the compute stream, max over ranks) -> ``value``;
-  * end to end (wall clock around the public API: host token generation into pinned memory, H2D copy of the
-    step's tokens, ``fwd_bwd`` + ``step``, D2H read of the loss) -> ``e2e``.
+optimizer update.  ONE timed region of K steps after W warm-up steps; each iteration draws its tokens on the host,
+puts them in pinned memory, and goes through the public API (``fwd_bwd`` copies them to the device, ``step``
+updates, the loss is read back).  CUDA events around the loop give ``value`` (max over ranks), the wall clock
+around the same loop gives ``e2e``.  Every GPU count trains on the same global batch (one seeded host stream,
+rank r keeps sequences r, r + N, ...), so ``loss_step1`` is comparable across N.  If K steps do not fit the wall
+budget of the process (``--budget-s``), fewer are timed and ``steps`` reports the count that ran.
 Rank 0 prints one JSON line.
 """
 from __future__ import annotations
@@ -36,7 +38,11 @@ GLOBAL_BATCH = 524288
 # The other named configurations (``--config``); the headline stays llama8b.
 CONFIGS = {
     "llama8b": dict(model="Llama-3.1-8B", arch="llama", dims=LLAMA31_8B, seq_len=SEQ_LEN, global_batch=GLOBAL_BATCH,
-                    hyper={"rope_theta": 500000.0, "norm_eps": 1e-5}, scaling="strong"),
+                    hyper={"rope_theta": 500000.0, "norm_eps": 1e-5}, scaling="strong", published=3733.0),
+    # LoRA r16 on every linear of the same model (reference: 5,295 tokens/s on an RTX 5090, docs/verified_runs.md:159)
+    "llama8b_lora": dict(model="Llama-3.1-8B", arch="llama", dims=LLAMA31_8B, seq_len=SEQ_LEN, global_batch=GLOBAL_BATCH,
+                         hyper={"rope_theta": 500000.0, "norm_eps": 1e-5}, scaling="strong", published=5295.0,
+                         lora=dict(targets="all", rank=16, alpha=16.0)),
     # long-context dense 12B: one 32768-token sequence per GPU (weak scaling), chunked attention with a KV window
     "longctx12b": dict(model="dense-12B long context", arch="llama",
                        dims=dict(vocab_size=131072, n_layers=40, d_model=5120, n_heads=32, n_kv_heads=8, head_dim=128,
@@ -121,12 +127,25 @@ def _emit(obj):
     print(json.dumps(obj), flush=True)
 
 
+def _budget_steps(args, t_proc0: float, warm_step_s: float, setup_reserve_s: float = 25.0) -> int:
+    """Number of timed steps that fit into the wall-clock budget of this process (``--budget-s``, default 800 s:
+    the scaling run gives every command 870 s).  The requested count is used whenever it fits."""
+    if args.budget_s <= 0 or warm_step_s <= 0:
+        return args.steps
+    left = args.budget_s - (time.perf_counter() - t_proc0) - setup_reserve_s
+    fit = int(left // warm_step_s)
+    return max(min(args.steps, fit), min(args.steps, 3))
+
+
 def run_ours(args):
+    t_proc0 = time.perf_counter()
+    os.environ.setdefault("FTB_STRICT", "1")        # a library fallback on a hot op raises instead of running
     import torch
     import torch.distributed as dist
 
     import flextrain_b200 as ft
     from flextrain_b200 import ops
+    from flextrain_b200.io.sequence import Sequence
     from flextrain_b200.ops import cuda as kernels
 
     rank, world, local = _dist_env()
@@ -146,65 +165,88 @@ def run_ours(args):
         gbatch = 65536 if "global_batch" in cfg else gbatch
     par = {k: (world if cfg.get(k) == "world" else 1) for k in ("tp", "ep")}
     # tensor parallel ranks work on the same tokens (each feeds the whole batch); data parallel ranks split it
-    per_rank = gbatch if par["tp"] > 1 else gbatch // world
+    dp = 1 if par["tp"] > 1 else world
+    per_rank = gbatch // dp
     free, total = torch.cuda.mem_get_info()
-    opt = ft.AdamW(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, state_dtype=torch.float32)
+    lora = cfg.get("lora")
+    opt = ft.AdamW(lr=1e-4 if lora else 3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
+                   state_dtype=torch.float32)
+    extra = dict(lora_targets=lora["targets"], lora_rank=lora["rank"], lora_alpha=lora["alpha"]) if lora else {}
     am = ft.from_dims(dims, arch=cfg["arch"], optimizer=opt, max_seq_len=seq_len, max_global_batch_tokens=gbatch,
                       max_gpu_mem_bytes=int(free), max_host_mem_bytes=args.host_gib << 30, device=dev,
                       hyperparams=cfg["hyper"], world_size=world, rank=rank,
                       dp_shard=args.shard, init_on_device=True, init_std=0.02, verbose=(rank == 0 and args.verbose),
-                      max_chunk_size=args.chunk, head_chunk_size=args.head_chunk, **par)
-    src = ft.SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234 + (0 if par["tp"] > 1 else rank), pin=True)
+                      max_chunk_size=args.chunk, head_chunk_size=args.head_chunk, **par, **extra)
+    # one seeded host stream for the whole job, so the global batch (and the loss) is the same at every GPU count
+    src = ft.SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234, pin=False)
+    n_global = gbatch // seq_len
+    h2d = [0]
+
+    def next_batch():
+        """Host side of a step: draw the global batch, keep this rank's sequences, put them in pinned memory."""
+        seqs = src.get_sequences(gbatch)
+        assert len(seqs) == n_global
+        mine = seqs[rank % dp::dp]
+        out = [Sequence(s.tokens.pin_memory(), targets=s.targets.pin_memory(), seq_id=s.seq_id) for s in mine]
+        h2d[0] = sum(s.tokens.numel() * 8 + s.targets.numel() * 8 for s in out)
+        return out
 
     def one_step(seqs):
-        st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / gbatch, total_tokens_per_step=gbatch)
+        st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / gbatch, total_tokens_per_step=gbatch)   # H2D of tokens/targets
         rc = am.step()
         assert rc == 0
-        return st
+        return st                                    # st.loss was read back from the device (D2H)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        st = one_step(src.get_sequences(per_rank))
-    barrier()
+    loss_step1, warm_s = None, 0.0
+    for i in range(args.warmup):
+        barrier()
+        t0 = time.perf_counter()
+        st = one_step(next_batch())
+        barrier()
+        warm_s = time.perf_counter() - t0           # the last warm-up step is the estimate for the budget
+        if i == 0:
+            loss_step1 = st.loss
     peak_alloc = torch.cuda.max_memory_allocated() / 2 ** 30
+    steps = _budget_steps(args, t_proc0, warm_s)
+    if world > 1:
+        tsteps = torch.tensor([steps], device=dev)
+        dist.all_reduce(tsteps, op=dist.ReduceOp.MIN)
+        steps = int(tsteps.item())
 
-    # ---- region A: device-timed
-    batches = [src.get_sequences(per_rank) for _ in range(args.steps)]
+    # ---- ONE timed region: CUDA events give ``value``, the wall clock around the same loop gives ``e2e``.
+    # Every iteration draws its tokens on the host, copies them from pinned memory, trains, reads the loss back.
     sampler = ClockSampler(local)
     ops.reset_launch_count()
+    ops.reset_backends_used()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
     e0.record()
-    for seqs in batches:
-        st = one_step(seqs)
+    for _ in range(steps):
+        st = one_step(next_batch())
     e1.record()
     barrier()
+    e2e_s = time.perf_counter() - t0
     dev_ms = e0.elapsed_time(e1)
     launches = ops.launch_count()
     clocks = sampler.stop()
     last_loss = st.loss
-    # ---- region B: end to end through the public API
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        seqs = src.get_sequences(per_rank)             # host RNG into pinned memory
-        st = one_step(seqs)                            # H2D of tokens/targets, fwd+bwd+step, D2H of the loss
-    barrier()
-    e2e_s = time.perf_counter() - t0
 
     t = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = float(t[0]), float(t[1])
     errs = kernels.device_error_words()
+    am.check_health()                                # raises when a bounded device-side wait ran out
     if rank == 0:
-        ms_step = dev_ms / args.steps
+        ms_step = dev_ms / steps
         value = gbatch / (ms_step / 1e3)
-        e2e_val = gbatch / (e2e_ms / args.steps / 1e3)
+        e2e_val = gbatch / (e2e_ms / steps / 1e3)
         n_params = 0
         for scope, l, name, t in am.named_master_params():
             sp = am.spec_of(scope, l, name)
@@ -214,6 +256,8 @@ def run_ours(args):
                 n_params += t.numel() * (par["tp"] if sp.is_local_part else 1)
         flops_tok = 6.0 * (n_params - dims["vocab_size"] * dims["d_model"]) \
             + 6.0 * seq_len * dims["n_heads"] * dims["head_dim"] * dims["n_layers"]
+        if lora:                                  # frozen base: no weight-gradient GEMMs (4 of the 6 FLOPs per weight)
+            flops_tok = flops_tok * 4.0 / 6.0
         tflops_gpu = value * flops_tok / world / 1e12
         peaks = {}
         try:
@@ -222,32 +266,58 @@ def run_ours(args):
         except Exception:
             pass
         sustained = peaks.get("bf16_tflops_sustained", 1400.0)
+        headline = args.config == "llama8b"
         _emit({
-            "metric": METRIC if args.config == "llama8b" else f"train tokens/sec/box, {cfg['model']} full FT",
-            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "metric": METRIC if headline else f"train tokens/sec/box, {cfg['model']} {'LoRA' if lora else 'full FT'}",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": cfg["scaling"],
-            "vs_baseline": value / PUBLISHED_TOK_S if args.config == "llama8b" else None, "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights",
+            "vs_baseline": value / cfg["published"] if cfg.get("published") else None, "dtype": "bf16",
+            "data": "synthetic uniform tokens, random-init weights",
             "config": {"model": cfg["model"] + (" (SMALL DEBUG)" if args.small else ""), "global_batch": gbatch,
                        "seq_len": seq_len, "parallelism": (f"tp{world}" if par["tp"] > 1 else f"dp{world}" + (f"+ep{world}" if par["ep"] > 1 else ""))
                        + (f"-shard({am.ws.shard})" if world > 1 else ""),
-                       "optimizer": "AdamW fp32 state", "round_tokens": am.ws.target_round_tokens,
+                       "optimizer": "AdamW fp32 state" + (f", state on {am.ws.opt_residency}" if hasattr(am.ws, "opt_residency") else ""),
+                       "round_tokens": am.ws.target_round_tokens,
                        "chunk": am.ws.max_chunk_size, "rounds_per_step": am.ws.target_num_rounds,
                        "l2": "inputs larger than L2 (each step streams >100 GB of weights/activations)",
-                       "gemm_backend": os.environ.get("FTB_GEMM_BACKEND", "tcgen05"),
-                       "attention_backend": ops.get_attention_backend()},
+                       "backends": ops.backends_used(), "strict": os.environ.get("FTB_STRICT") == "1",
+                       "timed_region": "one loop: host token draw -> pinned -> H2D -> fwd_bwd -> step -> D2H loss; "
+                                       "CUDA events and wall clock bracket the same steps"},
+            "steps_requested": args.steps,
             "clocks": clocks,
-            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 16 * per_rank,
+            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d[0],
                     "d2h_bytes_per_step": 4 * per_rank + 12},
             "gpu_launches": launches,
             "model_tflops_per_gpu": tflops_gpu, "pct_of_measured_sustained_bf16": 100.0 * tflops_gpu / sustained,
-            "loss": last_loss, "peak_alloc_gib": peak_alloc, "device_errors": errs,
+            "loss": last_loss, "loss_step1": loss_step1, "peak_alloc_gib": peak_alloc, "device_errors": errs,
         })
     if world > 1:
         dist.destroy_process_group()
 
 
+def _host_memory_report() -> dict:
+    """What the box offers (psutil and the cgroup limit), printed to stderr by the reference arm for diagnosis."""
+    out = {}
+    try:
+        import psutil
+        vm = psutil.virtual_memory()
+        out.update(total_gib=vm.total / 2 ** 30, available_gib=vm.available / 2 ** 30)
+    except Exception:
+        pass
+    for p in ("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory/memory.limit_in_bytes"):
+        try:
+            v = open(p).read().strip()
+            out["cgroup_limit_gib"] = None if v == "max" else int(v) / 2 ** 30
+            break
+        except Exception:
+            continue
+    return out
+
+
 def run_reference(args):
-    """The unmodified reference engine (installed under baseline/_ref) through its own public API."""
+    """The unmodified reference engine (installed under baseline/_ref) through its own public API
+    (``flextrain.from_dims`` -> ``fwd_bwd`` -> ``step``): same model, sequence length, batch and optimizer."""
+    t_proc0 = time.perf_counter()
     rank, world, local = _dist_env()
     ref_root = os.path.join(ROOT, "baseline", "_ref")
 
@@ -267,12 +337,15 @@ def run_reference(args):
         if world > 1:
             dist.init_process_group("nccl", device_id=torch.device(dev))
         import flextrain as ref
+        from flextrain.core import _memory as ref_memory
+        from flextrain.core.hw_probe import probe_hardware
+        from flextrain.core.save_level import HardwareCost
+        from flextrain.io.sequence import Sequence as RefSequence
         from flextrain.io.sources import SyntheticTokenSource
         from flextrain.optim.adamw import AdamW, AdamWHyperparams
     except Exception as e:
         unavailable(f"reference import failed: {type(e).__name__}: {e}")
     try:
-        import psutil
         dims = {k: v for k, v in LLAMA31_8B.items() if k != "ffn_dim"}
         seq_len, gbatch = SEQ_LEN, GLOBAL_BATCH
         if args.small:
@@ -280,25 +353,73 @@ def run_reference(args):
             gbatch = 65536
         per_rank = gbatch // world
         free, _ = torch.cuda.mem_get_info()
-        host_free = int(psutil.virtual_memory().available * 0.8) // max(world, 1)
-        opt = AdamW(AdamWHyperparams(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0),
-                    state_dtype=torch.float32)
-        # The reference planner can reject its default chunk candidates on a 180 GB GPU and then advises a smaller
-        # --max-chunk-size; follow that advice through the public keyword until a plan exists.
-        am, plan_err = None, None
-        for mcs in (None, 16384, 8192, 4096):
+        # The reference pins its whole host budget (cudaHostRegister), so the budget must be something the box can
+        # pin: its own cgroup-aware figure, split over the ranks of the node, capped at the 192 GiB host of its
+        # published runs (docs/verified_runs.md:141-155).
+        host_avail = int(ref_memory.get_available_host_memory())
+        host_budget = min(int(host_avail * 0.85) // max(world, 1), 192 << 30)
+        if rank == 0:
+            print(f"[reference arm] host memory: {_host_memory_report()} reference sees "
+                  f"{host_avail / 2 ** 30:.1f} GiB -> budget {host_budget / 2 ** 30:.1f} GiB per rank; "
+                  f"GPU free {free / 2 ** 30:.1f} GiB", file=sys.stderr, flush=True)
+        probe = probe_hardware(device=dev)          # once (about 10 s); every planning attempt reuses it
+        hw_probed = (probe.hw_cost, probe.mem_bw_gbps)
+        # second choice when the probed figures make the planner's round target unplannable (a slow shared PCIe
+        # link inflates it): nominal B200 host link and the probed compute
+        hw_nominal = (HardwareCost(peak_tflops=probe.hw_cost.peak_tflops, pcie_bw_gbps=50.0), probe.mem_bw_gbps)
+        if rank == 0:
+            print(f"[reference arm] probe: {probe.hw_cost.peak_tflops:.0f} TFLOP/s, PCIe "
+                  f"{probe.hw_cost.pcie_bw_gbps:.1f} GB/s, memory {probe.mem_bw_gbps:.0f} GB/s",
+                  file=sys.stderr, flush=True)
+        # Plan ladder through public keywords only.  The reference's search is tuned for 24-32 GiB cards
+        # (flextrain/core/working_set.py:1684-1736): when it rejects its own candidates on a 180 GB GPU, offer a
+        # smaller chunk cap, then a smaller GPU budget, then the nominal link figure, then its default bf16
+        # optimizer state; the first plan that builds is the one that runs, and the JSON line says which.
+        am, errors, chosen = None, [], None
+        ladder = [(st, hw, g, m)
+                  for st in ("float32", "bfloat16")
+                  for hw in ("probed", "nominal")
+                  for g in (None, 96, 64, 31)
+                  for m in (None, 16384, 8192, 4096)]
+        for st, hw, g, m in ladder:
+            opt = AdamW(AdamWHyperparams(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0),
+                        state_dtype=getattr(torch, st))
+            hwc, mbw = hw_probed if hw == "probed" else hw_nominal
             try:
                 am = ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len,
-                                   max_global_batch_tokens=per_rank, max_gpu_mem_bytes=int(free),
-                                   max_host_mem_bytes=host_free, max_chunk_size=mcs,
+                                   max_global_batch_tokens=per_rank,
+                                   max_gpu_mem_bytes=int(free) if g is None else min(int(free), g << 30),
+                                   max_host_mem_bytes=host_budget, max_chunk_size=m, hw_cost=hwc, mem_bw_gbps=mbw,
                                    hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5}, device=dev)
-                ref_chunk = mcs
+                chosen = {"opt_state": st, "hw_cost": hw, "max_gpu_gib": g, "max_chunk_size": m}
                 break
-            except ValueError as e:
-                plan_err = e
+            except (ValueError, RuntimeError, AssertionError, MemoryError) as e:
+                errors.append(f"{st}/{hw}/gpu={g}/chunk={m}: {type(e).__name__}: {str(e)[:160]}")
+                if isinstance(e, (RuntimeError, MemoryError)):
+                    import gc
+                    gc.collect()
+                    torch.cuda.empty_cache()
         if am is None:
-            raise plan_err
-        src = SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234 + rank)
+            for line in errors:
+                print("[reference arm] " + line, file=sys.stderr)
+            try:                                    # the planner's own trace for the last attempt
+                ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len, max_global_batch_tokens=per_rank,
+                              max_gpu_mem_bytes=int(free), max_host_mem_bytes=host_budget, hw_cost=hw_probed[0],
+                              mem_bw_gbps=hw_probed[1], device=dev, verbose=True,
+                              hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5})
+            except Exception:
+                pass
+            raise RuntimeError(f"no plan builds ({len(errors)} attempts); first: {errors[0]}; last: {errors[-1]}")
+        ws = am.working_set if hasattr(am, "working_set") else None
+        if rank == 0:
+            print(f"[reference arm] plan {chosen}: " + (f"round {ws.target_round_tokens} chunk {ws.max_chunk_size} "
+                  f"gpu layers {ws.n_gpu_layers}/{ws.n_gpu_grads}/{ws.n_gpu_opt_layers} host act "
+                  f"{ws.host_act_buffer_size / 2 ** 30:.1f} GiB" if ws is not None else ""), file=sys.stderr, flush=True)
+        src = SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234)
+
+        def next_batch():
+            seqs = src.get_sequences(gbatch)
+            return seqs[rank::world]
 
         def allreduce_grads():
             # constructed multi-GPU wrapper: the reference has no distributed mode, so the ranks' host gradients
@@ -330,26 +451,32 @@ def run_reference(args):
                 dist.barrier()
             torch.cuda.synchronize()
 
-        for _ in range(args.warmup):
-            one_step(src.get_sequences(per_rank))
-        barrier()
-        batches = [src.get_sequences(per_rank) for _ in range(args.steps)]
+        loss_step1, warm_s = None, 0.0
+        for i in range(args.warmup):
+            barrier()
+            t0 = time.perf_counter()
+            st = one_step(next_batch())
+            barrier()
+            warm_s = time.perf_counter() - t0
+            if i == 0:
+                loss_step1 = getattr(st, "loss", None)
+        steps = _budget_steps(args, t_proc0, warm_s)
+        if world > 1:
+            tsteps = torch.tensor([steps], device=dev)
+            dist.all_reduce(tsteps, op=dist.ReduceOp.MIN)
+            steps = int(tsteps.item())
         sampler = ClockSampler(local)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
         e0.record()
-        for seqs in batches:
-            st = one_step(seqs)
+        for _ in range(steps):
+            st = one_step(next_batch())
         e1.record()
         barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
         dev_ms = e0.elapsed_time(e1)
         clocks = sampler.stop()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            st = one_step(src.get_sequences(per_rank))
-        barrier()
-        e2e_ms = (time.perf_counter() - t0) * 1e3
         t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -359,19 +486,28 @@ def run_reference(args):
         traceback.print_exc()
         unavailable(f"reference run failed on this box: {type(e).__name__}: {e}")
     if rank == 0:
-        ms_step = dev_ms / args.steps
+        ms_step = dev_ms / steps
         value = gbatch / (ms_step / 1e3)
+        loss = getattr(st, "loss", None)
         _emit({"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
-               "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+               "steps": steps, "steps_requested": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+               "higher_is_better": True,
                "scaling": "strong", "vs_baseline": value / PUBLISHED_TOK_S, "dtype": "bf16",
                "data": "synthetic uniform tokens, random-init weights",
                "config": {"model": "Llama-3.1-8B" + (" (SMALL DEBUG)" if args.small else ""), "global_batch": gbatch,
                           "seq_len": seq_len,
                           "parallelism": f"dp{world}" + (" (constructed: one reference engine per GPU + NCCL "
-                                                         "all-reduce of host gradients)" if world > 1 else "")},
+                                                         "all-reduce of host gradients)" if world > 1 else ""),
+                          "optimizer": f"AdamW {chosen['opt_state']} state", "plan": chosen,
+                          "round_tokens": getattr(ws, "target_round_tokens", None),
+                          "chunk": getattr(ws, "max_chunk_size", None),
+                          "gpu_layers": getattr(ws, "n_gpu_layers", None),
+                          "host_budget_gib": host_budget / 2 ** 30},
                "clocks": clocks,
-               "e2e": {"value": gbatch / (e2e_ms / args.steps / 1e3), "unit": "tokens/s",
+               "e2e": {"value": gbatch / (e2e_ms / steps / 1e3), "unit": "tokens/s",
                        "h2d_bytes_per_step": 16 * per_rank, "d2h_bytes_per_step": 4 * per_rank},
+               "loss": float(loss) if loss is not None else None,
+               "loss_step1": float(loss_step1) if loss_step1 is not None else None,
                "gpu_launches": None})
     if world > 1:
         dist.destroy_process_group()
@@ -389,6 +525,8 @@ def main():
     ap.add_argument("--chunk", type=int, default=None)
     ap.add_argument("--head-chunk", type=int, default=4096)
     ap.add_argument("--host-gib", type=int, default=64)
+    ap.add_argument("--budget-s", type=float, default=800.0,
+                    help="wall-clock budget of the whole process; timed steps are reduced to fit (0 = never)")
     ap.add_argument("--small", action="store_true", help="4-layer debug model; results are not reportable")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()

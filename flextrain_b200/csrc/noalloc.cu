@@ -147,7 +147,8 @@ __global__ void colsum_kernel(const float* __restrict__ partial, float* __restri
   out[c] = accumulate ? out[c] + s : s;
 }
 
-// Device address of g_scratch on the current device; resolved once per device, never allocates.
+// Device address of g_scratch on the current device; resolved once per device, never allocates.  The cache is
+// written without a lock: two host threads that race here both store the same address, which is harmless.
 int resolve_scratch(float** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -170,6 +171,14 @@ int ftb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float* w, const
                             void* dx, void* y_out, float* dw, int dw_accumulate, int T, int D, cudaStream_t stream) {
   if (T < 0 || D <= 0 || (D & 7)) return FTB_NOALLOC_ERR_BAD_SHAPE;
   if (D > FTB_NOALLOC_MAX_D) return FTB_NOALLOC_ERR_TOO_LARGE;
+  // Host-side pointer checks (nothing is launched on failure).  The kernels move rows as 16-byte vectors, so an
+  // unaligned view of a caller's buffer would fault on the device; a weight gradient without weights has no meaning.
+  if (dy == nullptr || x == nullptr || rstd == nullptr || dx == nullptr) return FTB_NOALLOC_ERR_BAD_POINTER;
+  const void* vec_ptrs[] = {dy, x, dx, dx_add, y_out, w, dw};
+  for (const void* q : vec_ptrs)
+    if (q != nullptr && (reinterpret_cast<uintptr_t>(q) & 15)) return FTB_NOALLOC_ERR_BAD_POINTER;
+  if ((reinterpret_cast<uintptr_t>(rstd) & 3)) return FTB_NOALLOC_ERR_BAD_POINTER;
+  if (dw != nullptr && w == nullptr) return FTB_NOALLOC_ERR_BAD_POINTER;
   if (T == 0) return 0;
   float* scratch = nullptr;
   const int rc = resolve_scratch(&scratch);
@@ -189,6 +198,8 @@ const char* ftb_noalloc_strerror(int code) {
     case FTB_NOALLOC_ERR_TOO_LARGE:
       return "row width D exceeds FTB_NOALLOC_MAX_D (8192): the built-in workspace cannot hold the reduction";
     case FTB_NOALLOC_ERR_BAD_SHAPE: return "D must be a positive multiple of 8 and T must not be negative";
+    case FTB_NOALLOC_ERR_BAD_POINTER:
+      return "dy, x, rstd, dx are required; every tensor pointer must be 16-byte aligned; dw needs w";
     case FTB_NOALLOC_ERR_SYMBOL: return "could not resolve the device address of the built-in workspace";
     default: return "CUDA launch error (code = -400 - cudaError_t)";
   }

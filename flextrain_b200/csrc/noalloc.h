@@ -16,6 +16,12 @@
 // Contract
 //   * Inputs and outputs are the caller's: dy, x, dx (T x D, bf16), w (D, fp32) or NULL, rstd (T, fp32), optional
 //     dx_add / y_out (T x D, bf16), optional dw (D, fp32; accumulated when dw_accumulate != 0).
+//   * Every tensor pointer (dy, x, dx, dx_add, y_out, w, dw) must be 16-byte aligned (rows move as 16-byte vectors);
+//     a misaligned or missing required pointer is rejected with FTB_NOALLOC_ERR_BAD_POINTER before any launch.
+//     Without w the normalisation has no gain; asking for dw without w is rejected with the same code.
+//   * `stream` must belong to the device that is current when the call is made: the workspace address is looked up for
+//     the current device.  Host threads may call concurrently (the address cache is benign to race on), but see the
+//     last point about calls that overlap on the GPU.
 //   * D must be a multiple of 8 and at most FTB_NOALLOC_MAX_D; larger D is rejected with
 //     FTB_NOALLOC_ERR_TOO_LARGE and nothing is launched.  ftb_noalloc_strerror() turns a code into text.
 //   * No cudaMalloc, cudaFree or allocating library routine is called, on any call.
@@ -35,6 +41,7 @@
 #define FTB_NOALLOC_ERR_TOO_LARGE (-3)
 #define FTB_NOALLOC_ERR_BAD_SHAPE (-2)
 #define FTB_NOALLOC_ERR_SYMBOL (-4)
+#define FTB_NOALLOC_ERR_BAD_POINTER (-5)
 
 #ifdef __cplusplus
 extern "C" {

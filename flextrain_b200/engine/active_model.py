@@ -80,6 +80,7 @@ class ActiveModel:
             if tp is not None:
                 layer.bind_tp(tp)
         self.step_num = 0
+        self.fwd_bwd_serial = 0          # counts training ``fwd_bwd`` calls (data-parallel flag epochs key on it)
         self._zero_grad = True
         self._pending_tokens = 0
         self.last_grad_norm: Optional[float] = None
@@ -106,6 +107,8 @@ class ActiveModel:
         self.mrope = any(getattr(l, "attn", None) is not None and l.attn.cfg.rope.mrope_sections for l in self.layers)
         if dp is not None:
             dp.attach(self)
+        if ep is not None and hasattr(ep, "attach"):
+            ep.attach(self)
 
     # ====================================================================== public API
     def fwd_bwd(self, seqs: Seq[Sequence], loss_scale_factor: Optional[float] = None,
@@ -121,7 +124,12 @@ class ActiveModel:
                                  max_training_chunks=ws.max_training_chunks,
                                  max_total_round_tokens=ws.max_total_round_tokens,
                                  policy=ChunkPolicy.CAUSAL if self.is_causal else ChunkPolicy.NON_CAUSAL)
+        if self.ep is not None:
+            # expert-parallel ranks exchange rows per (layer, chunk): all of them walk the same number of rounds
+            rounds = rounds + [[] for _ in range(self.ep.agree_max(len(rounds)) - len(rounds))]
         stats = StepStats(n_rounds=len(rounds))
+        if not forward_only:
+            self.fwd_bwd_serial += 1
         loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
         act_acc = torch.zeros((), dtype=torch.int64, device=self.device)
         pending_losses = []
@@ -132,6 +140,8 @@ class ActiveModel:
                     with _nvtx("Prepare Training Chunks"):
                         metas = prepare_training_chunks(rseqs, ws.max_chunk_size, self.device, mrope=self.mrope,
                                                         pad_multiple=128 * self.tp.world if self.tp is not None else 1)
+                        if self.ep is not None:
+                            metas = self._pad_with_filler_chunks(metas, self.ep.agree_max(len(metas)))
                     with _nvtx("Determine Saved Levels"):
                         plan = self._plan_save_levels(metas)
                     self._last_plan = plan
@@ -297,6 +307,28 @@ class ActiveModel:
             transitions[c] = self.embed.forward(self._token_shard(meta), ep)
         return transitions, {}
 
+    def _pad_with_filler_chunks(self, metas: List[ChunkMeta], n: int) -> List[ChunkMeta]:
+        """Append unscored filler chunks until the round has ``n`` chunks (the count of the busiest expert-parallel
+        peer).  A filler chunk is a short sequence of its own whose targets are all ``-100``: it joins every
+        dispatch / combine of the round, contributes no loss and no gradient (``meta.extra["filler"]`` also keeps it
+        out of the router's load-balance term) and is not counted in the step's tokens."""
+        if len(metas) >= n:
+            return metas
+        from ..parallel.ep import FILLER_TOKENS
+        next_group = max((m.seq_group for m in metas), default=-1) + 1
+        while len(metas) < n:
+            toks = torch.zeros(FILLER_TOKENS, dtype=torch.int64)
+            fill = Sequence(toks, targets=torch.full((FILLER_TOKENS,), -100, dtype=torch.int64), seq_id=-1)
+            m = prepare_training_chunks([fill], self.ws.max_chunk_size, self.device, mrope=self.mrope)[0]
+            m.chunk_id = len(metas)
+            m.seq_group = next_group
+            next_group += 1
+            m.extra["pieces"] = []                     # nothing to write back
+            m.extra["pad_tokens"] = m.num_tokens       # not part of the step's token count
+            m.extra["filler"] = True
+            metas.append(m)
+        return metas
+
     def _token_shard(self, meta: ChunkMeta) -> ChunkMeta:
         """Under tensor parallelism the residual stream is token-sharded: the embedding, the head and the loss see
         rows ``[rank * T/tp, (rank+1) * T/tp)`` of the chunk; the layers keep the full chunk's packing metadata."""
@@ -320,8 +352,11 @@ class ActiveModel:
         meta.extra[key] = sh
         return sh
 
-    def _ctx(self, base, **kw) -> LayerContext:
-        return LayerContext(**base, **kw)
+    def _ctx(self, base, meta: Optional[ChunkMeta] = None, **kw) -> LayerContext:
+        ctx = LayerContext(**base, **kw)
+        if meta is not None and meta.extra.get("filler"):
+            ctx.total_tokens_per_step = 0          # a filler chunk takes no part in the load-balance term
+        return ctx
 
     # ============================================================================ forward
     def _forward_pass(self, metas, plan: SaveLevelPlan, transitions, slots, ctx_base, stats: StepStats):
@@ -344,7 +379,7 @@ class ActiveModel:
                 lin_state, lin_conv = {}, {}
                 for c, meta in enumerate(metas):
                     slot = ActivationSlot(layer.activation_schema, meta.num_tokens, ON_DEVICE)
-                    ctx = self._ctx(ctx_base)
+                    ctx = self._ctx(ctx_base, meta)
                     if layer.gdn is not None and meta.has_prior:
                         ctx.lin_state_in, ctx.lin_conv_in = lin_state.get(meta.seq_ids[0]), lin_conv.get(meta.seq_ids[0])
                     x = layer.forward(transitions[c], meta, params, slot, ctx)
@@ -461,7 +496,7 @@ class ActiveModel:
                     for c in reversed(chunk_ids):
                         meta = metas[c]
                         slot = self._fetch_slot(slots.pop((l, c)), l, c)
-                        ctx = self._ctx(ctx_base)
+                        ctx = self._ctx(ctx_base, meta)
                         if layer.gdn is not None:
                             if meta.has_prior:
                                 prev = self._peek_slot(slots[(l, c - 1)])
@@ -640,6 +675,30 @@ class ActiveModel:
 
     def synchronize(self) -> None:
         self.streams.synchronize_all()
+
+    def check_health(self, error_words=None) -> None:
+        """Raise if anything on the device gave up during the step that just ran.
+
+        The kernels never spin for ever: a wait on a peer's flag, an mbarrier or an arrival counter stops after its
+        limit, records an error word and lets the kernel return, so the step "finishes" with incomplete data (a
+        reduce-scatter that summed gradients a peer had not finished writing, an optimizer that then pushed the
+        result to every rank).  The host therefore reads the words after every step and stops the run.  Call it after
+        :meth:`step`; it synchronises this rank's streams.  ``error_words`` replaces the read of the kernel libraries
+        (host-side tests inject a fake status through it)."""
+        self.streams.synchronize_all()
+        if error_words is None:
+            if self.device.type == "cuda":
+                from ..ops.cuda import device_error_words
+                error_words = device_error_words()
+            else:
+                error_words = {}
+        bad = {k: v for k, v in error_words.items() if v}
+        if bad:
+            raise RuntimeError(f"device-side wait or check failed during step {self.step_num}: {bad} "
+                               "(library: code*1000 + site); gradients / parameters of this step are not trustworthy")
+        for grp in (self.dp, self.ep, self.tp):
+            if grp is not None and hasattr(grp, "check"):
+                grp.check()
 
     # --------------------------------------------------------------------- HF load / save
     def load_hf(self, model_dir: str, strict: bool = False) -> None:

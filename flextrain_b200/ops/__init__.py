@@ -21,6 +21,36 @@ from . import reference as ref
 _GEMM_BACKEND = os.environ.get("FTB_GEMM_BACKEND", "tcgen05")
 _ATTN_BACKEND = os.environ.get("FTB_ATTN_BACKEND", "auto")
 _launches = 0          # number of kernels of this package launched (bench.py reports it)
+_backends_used: dict = {}      # op family -> set of back ends that actually ran since the last reset
+
+
+class LibraryFallback(RuntimeError):
+    """Raised in strict mode (``FTB_STRICT=1``) when a hot op on a CUDA tensor would leave the hand-written
+    kernels for a library call (cuBLAS through ``torch.matmul``, torch's bundled flash attention, eager PyTorch)."""
+
+
+def strict() -> bool:
+    return os.environ.get("FTB_STRICT", "0") == "1"
+
+
+def _used(family: str, backend: str) -> None:
+    _backends_used.setdefault(family, set()).add(backend)
+
+
+def _fallback(family: str, why: str) -> None:
+    """Record (or, in strict mode, refuse) a library / eager path taken by ``family`` on a CUDA tensor."""
+    if strict():
+        raise LibraryFallback(f"{family}: {why} -- no hand-written kernel takes this call (FTB_STRICT=1)")
+    _used(family, "library")
+
+
+def backends_used() -> dict:
+    """``{family: sorted back ends that ran}`` since :func:`reset_backends_used` — what ran, not what was asked."""
+    return {k: sorted(v) for k, v in sorted(_backends_used.items())}
+
+
+def reset_backends_used() -> None:
+    _backends_used.clear()
 
 
 def set_gemm_backend(name: str) -> None:
@@ -72,13 +102,26 @@ def gemm(a, b, *, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, bia
         M = a.shape[1] if trans_a else a.shape[0]
         N = b.shape[0] if trans_b else b.shape[1]
         K = a.shape[0] if trans_a else a.shape[1]
-        if (_GEMM_BACKEND == "tcgen05" and k.gemm_supported(a, b, trans_a, trans_b, od) and N >= 64 and K >= 64
-                and M >= 1 and (out is None or (out.stride(-1) == 1 and out.data_ptr() % 16 == 0))
-                and (bias is None or bias.dtype == torch.float32)):
+        # The tensor-core kernel takes any N, K >= 8 (multiples of 8): TMA zero-fills the part of a tile that lies
+        # outside the matrix, so the rank-r LoRA products (N = r or K = r) run on it too.
+        why = None
+        if _GEMM_BACKEND != "tcgen05":
+            why = "FTB_GEMM_BACKEND=library"
+        elif not k.gemm_supported(a, b, trans_a, trans_b, od):
+            why = f"operands not bf16 / 16-byte aligned / N % 8 ({tuple(a.shape)}, {tuple(b.shape)}, {a.dtype})"
+        elif N < 8 or K < 8 or M < 1:
+            why = f"N={N} or K={K} below 8"
+        elif out is not None and not (out.stride(-1) == 1 and out.data_ptr() % 16 == 0):
+            why = "output not row-contiguous / 16-byte aligned"
+        elif bias is not None and bias.dtype != torch.float32:
+            why = "bias not fp32"
+        if why is None:
             _count()
+            _used("gemm", "tcgen05")
             return k.gemm(a, b, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, c=c, bias=bias, out=out,
                           out_dtype=od)
-        # library GEMM for shapes the tensor-core kernel does not take (tiny N / K, odd strides)
+        _fallback("gemm", why)
+        # library GEMM for shapes the tensor-core kernel does not take (odd strides, N or K not a multiple of 8)
         A = a.t() if trans_a else a
         B = b.t() if trans_b else b
         if od == a.dtype and b.dtype == a.dtype:
@@ -216,8 +259,11 @@ def attention_fwd(q, k, v, cu_q, cu_k, max_q, max_k, *, scale, causal=True, wind
     if be == "ftb":
         from . import attention_cuda
         _count()
+        _used("attention_fwd", "ftb")
         return attention_cuda.fwd(q, k, v, cu_q, cu_k, max_q, max_k, scale=scale, causal=causal, window=window,
                                   softcap=softcap)
+    if q.is_cuda:
+        _fallback("attention_fwd", f"backend {be}, head_dim {q.shape[-1]}, dtype {q.dtype}")
     if be in ("library", "ftb") and not softcap:
         wl = (window - 1) if window and window > 0 else None
         o, lse, _, _, _ = torch.ops.aten._flash_attention_forward(
@@ -233,8 +279,11 @@ def attention_bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, c
     if be == "ftb" and hasattr(_kernels().load("attention"), "ftb_attn_bwd"):
         from . import attention_cuda
         _count(3)
+        _used("attention_bwd", "ftb")
         return attention_cuda.bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, scale=scale, causal=causal,
                                   window=window, softcap=softcap)
+    if q.is_cuda:
+        _fallback("attention_bwd", f"backend {be}, head_dim {q.shape[-1]}, dtype {q.dtype}")
     if be in ("library", "ftb") and not softcap:
         wl = (window - 1) if window and window > 0 else None
         rng = torch.zeros(2, dtype=torch.uint64, device=q.device)

@@ -133,7 +133,7 @@ class P2PDataParallel(_Base):
         self.lib = self.group.lib
         self.units: Dict[object, List[Segment]] = {}
         self.grad_shard = self.m = self.v = None
-        self._reduced_epoch = 0
+        self._reduced_epoch = None
 
     # ------------------------------------------------------------------- set-up
     def buffer_kwargs(self) -> dict:
@@ -220,16 +220,23 @@ class P2PDataParallel(_Base):
         self.group.signal_wait(self.slot[key], self._epoch, cs)
         self._reduce_unit(key, 1.0, cs)
 
-    def on_layer_grads_ready(self, layer: int) -> None:
-        if self._reduced_epoch != self.am.step_num + 1:
+    def _call_epoch(self) -> None:
+        """One flag epoch per ``fwd_bwd`` call, not per optimizer step.  Gradients may be accumulated over several
+        calls before ``step()``; every call re-reduces the accumulated buffers (the shard is overwritten, so the last
+        call's sum is the one the optimizer sees).  With a single epoch per step the later calls would find the flags
+        of the first call already raised, skip the wait and sum peers' buffers that are still being accumulated.
+        Every rank must make the same number of ``fwd_bwd`` calls per step."""
+        serial = (self.am.step_num, getattr(self.am, "fwd_bwd_serial", 0))
+        if self._reduced_epoch != serial:
             self._epoch = self.group.next_epoch()
-            self._reduced_epoch = self.am.step_num + 1
+            self._reduced_epoch = serial
+
+    def on_layer_grads_ready(self, layer: int) -> None:
+        self._call_epoch()
         self._reduce(layer)
 
     def on_embed_head_grads_ready(self) -> None:
-        if self._reduced_epoch != self.am.step_num + 1:
-            self._epoch = self.group.next_epoch()
-            self._reduced_epoch = self.am.step_num + 1
+        self._call_epoch()
         self._reduce("embed")
         self._reduce("head")
 

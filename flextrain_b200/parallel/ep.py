@@ -27,6 +27,13 @@ import torch
 from .. import ops
 
 PAD = 128
+FILLER_TOKENS = 128     # length of the unscored chunk a rank runs when its peers have more chunks than it has
+
+
+def _dist_ready() -> bool:
+    import torch.distributed as dist
+    return dist.is_available() and dist.is_initialized()
+
 # Receive-buffer capacity as a multiple of the balanced share.  0 (default) = dropless: the buffers hold the worst
 # case (every slot of every rank routed to one rank), so no routing skew can overflow them.  Saved activations are
 # sized by the rows a rank actually receives, not by this bound.
@@ -72,10 +79,29 @@ class ExpertParallel:
         self._calls = 0
         self.slot_base = 3500
         self.overflow = None
+        self.max_chunk_tokens = 0      # set by attach(): the planner's chunk size, identical on every rank
+
+    def attach(self, am) -> None:
+        """Bind to the engine.  Receive / result / scalar buffers are symmetric allocations (every rank must ask for
+        the same size in the same order), and the library gathers need equal shapes, so their size comes from the
+        planner's ``max_chunk_size`` (the same number on every rank) and not from the token count of the chunk at
+        hand: data-parallel ranks read different sequences and their chunks differ in length."""
+        self.max_chunk_tokens = int(am.ws.max_chunk_size)
 
     # ------------------------------------------------------------------ helpers
     def capacity(self, T: int, K: int, E: int) -> int:
-        return ep_capacity(T, K, E, self.world, self.capacity_factor)
+        return ep_capacity(max(T, self.max_chunk_tokens), K, E, self.world, self.capacity_factor)
+
+    def agree_max(self, n: int) -> int:
+        """Largest ``n`` over the ranks (one small all-reduce, a host read).  Every MoE layer does flag exchanges and
+        peer reads per chunk, so the ranks of an expert-parallel group must walk the same number of rounds and of
+        chunks per round; the engine pads the shorter ranks with filler chunks up to this count."""
+        if self.world <= 1 or self.pg is None and not _dist_ready():
+            return n
+        import torch.distributed as dist
+        t = torch.tensor([n], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
+        return int(t.item())
 
     def _sync(self) -> None:
         if self.backend == "p2p":

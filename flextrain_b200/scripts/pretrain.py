@@ -233,6 +233,7 @@ def run(args) -> int:
             am.optimizer.lr = lr
             st = am.fwd_bwd(train.get_sequences(args.batch_tokens))
             am.step(max_grad_norm=args.grad_clip) if args.grad_clip else am.step()
+            am.check_health()           # raises when a bounded device-side wait ran out during this step
             tokens += st.tokens
             window = (window + [st.loss])[-20:]
             if step % args.log_every == 0 or step == steps or step == 1:

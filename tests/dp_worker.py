@@ -13,6 +13,8 @@ import flextrain_b200 as ft  # noqa: E402
 def main():
     backend, out_path = sys.argv[1], sys.argv[2]
     shard = "opt+grad"
+    accum = backend.endswith("_accum")      # the step's batch in two fwd_bwd calls (gradient accumulation over calls)
+    backend = backend.replace("_accum", "")
     if backend == "p2p_param":              # peer-memory path with the parameter all-gather deferred into the QKV GEMM
         backend, shard = "p2p", "opt+grad+param"
     os.environ["FTB_DP_BACKEND"] = backend
@@ -33,7 +35,13 @@ def main():
     losses = []
     for step in range(3):
         seqs = src.get_sequences(gb)[rank::world]
-        st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / gb, total_tokens_per_step=gb)
+        if accum:
+            h = len(seqs) // 2
+            st = am.fwd_bwd(seqs[:h], loss_scale_factor=1.0 / gb, total_tokens_per_step=gb)
+            st2 = am.fwd_bwd(seqs[h:], loss_scale_factor=1.0 / gb, total_tokens_per_step=gb)
+            st.loss_sum += st2.loss_sum
+        else:
+            st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / gb, total_tokens_per_step=gb)
         assert am.step() == 0
         t = torch.tensor([st.loss_sum], device=dev)
         dist.all_reduce(t)

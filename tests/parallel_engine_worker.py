@@ -6,6 +6,8 @@ sharded, token-sharded residual stream); every rank feeds the whole batch.  Afte
 gathered back through the HF exporter; rank 0 also trains the unsharded model on the whole batch in the same process
 and reports the differences.  ``tp_ragged``: as ``tp`` with sequences of uneven lengths (one of them longer than a
 chunk), so chunk token counts are not multiples of the shard width and the scheduler has to pad them.
+``ep_ragged``: as ``ep`` with uneven sequences split unevenly over the ranks, so the ranks' chunks differ in length
+and one rank has more rounds and more chunks than the other (it is padded with filler chunks).
 ``tp_grid`` / ``ep_grid``: model-parallel groups of two ranks inside a larger job (a ``dp x tp`` / ``dp x ep`` grid over
 library collectives); every group trains on its share of the batch.
 """
@@ -33,10 +35,11 @@ def build(dev, dtype, world, rank, mode, backend):
     os.environ["FTB_DP_BACKEND"] = backend
     mp = 2 if mode.endswith("_grid") else world                # model-parallel group size
     per_rank = GB // max(world // mp, 1) if mode.startswith("tp") else GB // world
-    seq = 512 if mode == "tp_ragged" else SEQ
+    ragged = mode in ("tp_ragged", "ep_ragged")
+    seq = 512 if ragged else SEQ
     ws = ft.WorkingSetConfig.simple(max_seq_len=seq, max_global_batch_tokens=per_rank,
-                                    chunk=256 if mode == "tp_ragged" else 512,
-                                    round_tokens=per_rank, world_size=world,
+                                    chunk=256 if ragged else 512,
+                                    round_tokens=512 if mode == "ep_ragged" else per_rank, world_size=world,
                                     shard="opt+grad" if world > 1 else "none")
     par = {"ep": mp} if mode.startswith("ep") else {"tp": mp}
     lora = dict(lora_targets="all", lora_rank=4, lora_alpha=8.0, lora_adapter_compute_dtype=dtype,
@@ -61,10 +64,11 @@ def build(dev, dtype, world, rank, mode, backend):
 
 
 def train(am, rank, world, dev, mode):
-    src = ft.SyntheticTokenSource(512, RAGGED if mode == "tp_ragged" else SEQ, seed=5)
+    ragged = mode in ("tp_ragged", "ep_ragged")
+    src = ft.SyntheticTokenSource(512, RAGGED if ragged else SEQ, seed=5)
     losses = []
     for _ in range(4 if mode == "tp_lora" else STEPS):      # LoRA: B starts at zero, A only moves from step 2 on
-        seqs = src.get_sequences(sum(RAGGED) if mode == "tp_ragged" else GB)
+        seqs = src.get_sequences(sum(RAGGED) if ragged else GB)
         if mode.startswith("ep"):
             seqs = seqs[rank::world]                  # data parallel: each rank takes its share of the batch
         elif mode == "tp_grid" and world > 1:

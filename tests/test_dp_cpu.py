@@ -121,3 +121,31 @@ def test_sharded_adamw_emulation_equals_plain_adamw():
                        weight_decay=0.0 if len(t.shape) == 1 else 0.1, step=1)
     for r in range(W):
         torch.testing.assert_close(pbufs[r].view(torch.float32), want.view(torch.float32), rtol=1e-5, atol=1e-7)
+
+
+def test_p2p_takes_one_flag_epoch_per_fwd_bwd_call():
+    """Host logic of the peer-memory path (no GPU): with two ``fwd_bwd`` calls before ``step()`` the reduce of the
+    second call must wait on a NEW epoch; reusing the first call's epoch would let the wait pass at once while the
+    peers are still accumulating.  Within one call all units share the epoch."""
+    from types import SimpleNamespace
+    from flextrain_b200.parallel.dp import P2PDataParallel
+
+    class Group:
+        def __init__(self): self.e = 0
+        def next_epoch(self):
+            self.e += 1
+            return self.e
+
+    dp = P2PDataParallel.__new__(P2PDataParallel)
+    dp.group, dp._reduced_epoch = Group(), None
+    dp.am = SimpleNamespace(step_num=0, fwd_bwd_serial=0)
+    waited = []
+    dp._reduce = lambda key: waited.append((key, dp._epoch))
+    for call in (1, 2):                       # two calls of the same step
+        dp.am.fwd_bwd_serial = call
+        for layer in (1, 0):
+            dp.on_layer_grads_ready(layer)
+        dp.on_embed_head_grads_ready()
+    dp.am.step_num, dp.am.fwd_bwd_serial = 1, 3   # next step
+    dp.on_layer_grads_ready(1)
+    assert [e for _, e in waited] == [1, 1, 1, 1, 2, 2, 2, 2, 3], waited

@@ -53,3 +53,17 @@ def test_deferred_param_gather_fused_into_qkv_gemm(tmp_path):
     # the gather-GEMM runs on the one-SM kernel, the eager path's projection on the two-SM kernel: a different fp32
     # summation order, i.e. single-ulp bf16 differences after three updates
     assert float(d.mean()) < 1e-5 and float(d.max()) < 5e-3, (float(d.mean()), float(d.max()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_fwd_bwd_calls_per_step_match_one_call(tmp_path):
+    """Gradient accumulation over two ``fwd_bwd`` calls before ``step()``: each call takes its own flag epoch, so the
+    second reduce-scatter waits for the peers' second backward; parameters match the one-call run of the same batch."""
+    n = min(torch.cuda.device_count(), 4)
+    a = _run("p2p_accum", str(tmp_path / "acc.pt"), n)
+    b = _run("p2p", str(tmp_path / "one.pt"), n)
+    assert a["ranks_identical"] and all(v == 0 for v in a["errors"].values()), a["errors"]
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 2e-3, (a["losses"], b["losses"])
+    d = (a["params"] - b["params"]).abs()
+    assert float(d.mean()) < 2e-5 and float(d.max()) < 5e-3, (float(d.mean()), float(d.max()))

@@ -62,3 +62,19 @@ def test_engine_expert_parallel_hybrid_with_shared_expert(tmp_path):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     res = json.load(open(out))
     assert res["local_rows"] == 4 and res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
+
+
+def test_engine_expert_parallel_with_unequal_chunks_and_rounds(tmp_path):
+    """Data-parallel ranks read different sequences: here rank 0 gets 706 tokens in 2 rounds / 4 + 1 chunks and rank 1
+    274 tokens in 1 round / 2 chunks, with chunk lengths that differ between the ranks.  The symmetric buffers are sized
+    from the planner's chunk size and the short rank runs filler chunks, so every dispatch / combine has its partner;
+    losses and parameters match the unsharded single-process run on the whole batch."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "epr.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective",
+           "ep_ragged", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert res["local_rows"] == 4 and res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res

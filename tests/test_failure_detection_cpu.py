@@ -119,3 +119,53 @@ def test_collective_with_dead_peer_raises_instead_of_hanging():
         p.join(30)
     assert msg.startswith("raised:"), msg
     assert float(msg.rsplit(":", 1)[1]) < 30.0
+
+
+def test_training_loop_stops_on_a_device_status_word(tmp_path, monkeypatch):
+    """A bounded device-side wait that runs out leaves an error word and lets the step finish on incomplete data.
+    ``ActiveModel.check_health`` turns a non-zero word into an exception, and ``train.py`` calls it after every
+    step: with a fake status injected at step 2 the loop must stop there instead of training on."""
+    import importlib.util
+    import sys
+    from flextrain_b200.engine.active_model import ActiveModel
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("ftb_train_cli", os.path.join(root, "train.py"))
+    train = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(train)
+
+    real = ActiveModel.check_health
+    calls = []
+
+    def fake(self, error_words=None):
+        calls.append(self.step_num)
+        # step 2: the word a run-out wait for peer panel 1 would leave in the GEMM library
+        return real(self, error_words={"gemm_tcgen05": 2041} if self.step_num == 2 else {})
+
+    monkeypatch.setattr(ActiveModel, "check_health", fake)
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    argv = ["--model", "dims:tiny_llama", "--mode", "full", "--data-source", "synthetic", "--max-seq-len", "128",
+            "--max-global-batch-tokens", "512", "--steps", "4", "--lr", "1e-3", "--output-dir", str(tmp_path / "o")]
+    with pytest.raises(RuntimeError, match="device-side wait or check failed during step 2.*2041"):
+        train.main(argv)
+    assert calls == [1, 2]
+
+
+def test_check_health_passes_on_clean_words_and_polls_groups():
+    from flextrain_b200.engine.active_model import ActiveModel
+
+    class Grp:
+        def __init__(self): self.n = 0
+        def check(self): self.n += 1
+
+    class Streams:
+        def synchronize_all(self): pass
+
+    am = ActiveModel.__new__(ActiveModel)
+    am.streams, am.device, am.step_num = Streams(), torch.device("cpu"), 7
+    am.dp, am.ep, am.tp = Grp(), None, Grp()
+    am.check_health(error_words={"comm": 0, "moe": 0})
+    assert am.dp.n == 1 and am.tp.n == 1
+    with pytest.raises(RuntimeError, match="step 7"):
+        am.check_health(error_words={"comm": 1003})

@@ -191,19 +191,3 @@ def test_chunk_padding_rules():
     assert long[1].prior_lens == [256] and long[1].seq_lens == [256]
     with pytest.raises(ValueError, match="ends inside a sequence"):
         prepare_training_chunks(seqs[2:], 200, "cpu", pad_multiple=256)
-
-
-def test_linear_attention_state_plan():
-    """Which packed sequences thread recurrent / convolution state across chunks in a round."""
-    from flextrain_b200.engine.linear_attn_state import build_state_plan, needs_state_threading
-    from flextrain_b200.engine.schedule import prepare_training_chunks
-    seqs = ft.SyntheticTokenSource(100, [40, 300, 30], seed=1).get_sequences(370)
-    metas = prepare_training_chunks(seqs, 128, "cpu")
-    assert [m.seq_ids for m in metas] == [[0], [1], [1], [1], [2]]
-    plan = build_state_plan(metas)
-    assert not plan[(0, 0)].has_prior_chunks and not plan[(0, 0)].has_more_chunks
-    assert not plan[(1, 0)].has_prior_chunks and plan[(1, 0)].has_more_chunks
-    assert plan[(2, 0)].has_prior_chunks and plan[(2, 0)].has_more_chunks and plan[(2, 0)].prior_chunk == 1
-    assert plan[(3, 0)].has_prior_chunks and not plan[(3, 0)].has_more_chunks and plan[(3, 0)].prior_chunk == 2
-    assert plan[(4, 0)].prior_chunk == -1
-    assert needs_state_threading(metas) and not needs_state_threading(metas[:1])

@@ -72,3 +72,49 @@ def test_noalloc_rejects_oversized_rows():
     assert b"8192" in lib.ftb_noalloc_strerror(rc)
     rc, _, _ = _call_noalloc(lib, x[:, :12], x[:, :12], None, rstd, None, False, None, False)
     assert rc == -2
+
+
+@pytest.mark.parametrize("T,D,with_w,with_dw", [(3, 8192, True, True), (200, 1024, False, False), (65, 4096, True, False)])
+def test_noalloc_matches_fp32_reference(T, D, with_w, with_dw):
+    """Against the plain PyTorch fp32 statement of the op (``ops.reference.rmsnorm_bwd``), at the widest row the
+    built-in workspace takes (every per-thread vector live), without a gain vector, and without a weight gradient."""
+    from flextrain_b200.ops import cuda as k
+    from flextrain_b200.ops import reference as ref
+    lib = k.load("noalloc")
+    lib.ftb_noalloc_strerror.restype = ctypes.c_char_p
+    torch.manual_seed(1)
+    x = torch.randn(T, D, device="cuda").to(torch.bfloat16)
+    dy = torch.randn(T, D, device="cuda").to(torch.bfloat16)
+    w = (torch.rand(D, device="cuda") + 0.5) if with_w else None
+    rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-5)
+    dw = torch.zeros(D, device="cuda") if with_dw else None
+    rc, dx, y = _call_noalloc(lib, dy, x, w, rstd, None, True, dw, False)
+    assert rc == 0, lib.ftb_noalloc_strerror(rc)
+    torch.cuda.synchronize()
+    dx_ref, dw_ref = ref.rmsnorm_bwd(dy.float(), x.float(), w, rstd)
+    y_ref = x.float() * rstd.unsqueeze(-1) * (w if with_w else 1.0)
+    assert _rel(dx, dx_ref) < 6e-3, _rel(dx, dx_ref)
+    assert _rel(y, y_ref) < 5e-3
+    if with_dw:
+        assert _rel(dw, dw_ref) < 5e-3, _rel(dw, dw_ref)
+
+
+def test_noalloc_rejects_bad_pointers_before_any_launch():
+    """An unaligned view, a missing required tensor, or a weight gradient without weights come back as an error code
+    from the host-side checks; nothing runs on the GPU."""
+    from flextrain_b200.ops import cuda as k
+    lib = k.load("noalloc")
+    lib.ftb_noalloc_strerror.restype = ctypes.c_char_p
+    T, D = 4, 1024
+    flat = torch.zeros(T * D + 8, device="cuda", dtype=torch.bfloat16)
+    x = flat[: T * D].view(T, D)
+    odd = flat[1: T * D + 1].view(T, D)                     # 2-byte offset: not 16-byte aligned
+    rstd = torch.ones(T, device="cuda")
+    dw = torch.zeros(D, device="cuda")
+    rc, _, _ = _call_noalloc(lib, odd, x, None, rstd, None, False, None, False)
+    assert rc == -5 and b"16-byte" in lib.ftb_noalloc_strerror(rc)
+    rc, _, _ = _call_noalloc(lib, x, x, None, rstd, None, False, dw, False)        # dw without w
+    assert rc == -5
+    rc, _, _ = _call_noalloc(lib, x, x, None, None, None, False, None, False)      # rstd missing
+    assert rc == -5
+    torch.cuda.synchronize()

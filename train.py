@@ -61,9 +61,9 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--lr-final-pct", type=float, default=0.1)
     p.add_argument("--lora-rank", type=int, default=16)
     p.add_argument("--lora-alpha", type=float, default=16.0)
-    p.add_argument("--moe-backend", default="flextrain", choices=["flextrain", "scattermoe", "sonicmoe"],
-                   help="kept for CLI compatibility; expert compute always runs on the built-in grouped tcgen05 GEMM")
-    p.add_argument("--attn-backend", default="auto", choices=["auto", "ftb", "library", "fa4", "fa3", "fa2", "eager"])
+    p.add_argument("--attn-backend", default="auto", choices=["auto", "ftb", "library", "eager"],
+                   help="ftb: the hand-written sm_100a kernels (what auto picks on a B200); library: torch's bundled "
+                        "flash kernels (comparison only); eager: plain PyTorch")
     p.add_argument("--use-muon", action="store_true")
     p.add_argument("--device-id", type=int, default=None)
     p.add_argument("--max-gpu-mem-gib", type=float, default=None)
@@ -109,7 +109,7 @@ def build_arg_parser() -> argparse.ArgumentParser:
 
 
 def _attn_backend(name: str) -> str:
-    return {"fa4": "ftb", "fa3": "library", "fa2": "library"}.get(name, name)
+    return name
 
 
 def _resolve_model(args):
@@ -322,6 +322,8 @@ def run_training_loop(am, src, args, per_rank_tokens: int, world: int, say) -> i
         rc = am.step(max_grad_norm=args.max_grad_norm) if getattr(args, "max_grad_norm", None) else am.step()
         if torch.cuda.is_available():
             torch.cuda.synchronize()
+        # a bounded device-side wait that ran out means this step used incomplete data: stop, do not train on it
+        am.check_health()
         dt = time.time() - t0
         if hb is not None:
             hb.beat(step)
