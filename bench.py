@@ -50,6 +50,14 @@ CONFIGS = {
                                  is_causal=True),
                        seq_len=32768, per_gpu_batch=32768, hyper={"rope_theta": 1000000.0, "norm_eps": 1e-5},
                        scaling="weak"),
+    # OLMoE-1B-7B on one GPU: 64 experts, top-8 (reference: 13,346 tokens/s full FT on an RTX 5090,
+    # docs/verified_runs.md:161); the single-GPU MoE path (device-side routing plan, grouped tcgen05 GEMMs)
+    "olmoe1b7b": dict(model="OLMoE-1B-7B", arch="olmoe",
+                      dims=dict(vocab_size=50304, n_layers=16, d_model=2048, n_heads=16, n_kv_heads=16, head_dim=128,
+                                expert_dim=1024, ffn_dim=1024, num_routed_experts=64, num_shared_experts=0, top_k=8,
+                                is_causal=True),
+                      seq_len=2048, global_batch=262144, hyper={"rope_theta": 10000.0, "norm_eps": 1e-5},
+                      scaling="strong", published=13346.0),
     # Qwen3-MoE 30B-A3B: experts sharded over all GPUs (expert parallel), the rest data parallel
     "qwen3moe30b": dict(model="Qwen3-30B-A3B", arch="qwen3_moe",
                         dims=dict(vocab_size=151936, n_layers=48, d_model=2048, n_heads=32, n_kv_heads=4, head_dim=128,
@@ -223,6 +231,9 @@ def run_ours(args):
     sampler = ClockSampler(local)
     ops.reset_launch_count()
     ops.reset_backends_used()
+    if args.op_timing:
+        ops.enable_op_timing()
+        ops.reset_op_timing()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
@@ -241,6 +252,11 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = float(t[0]), float(t[1])
+    if args.op_timing and rank == 0:
+        rows = ops.timing_report()
+        with open(args.op_timing, "w") as f:
+            json.dump({"steps": steps, "device_ms": dev_ms, "ops_ms": sum(r["total_ms"] for r in rows), "rows": rows}, f,
+                      indent=1)
     errs = kernels.device_error_words()
     am.check_health()                                # raises when a bounded device-side wait ran out
     if rank == 0:
@@ -283,7 +299,7 @@ def run_ours(args):
                        "backends": ops.backends_used(), "strict": os.environ.get("FTB_STRICT") == "1",
                        "timed_region": "one loop: host token draw -> pinned -> H2D -> fwd_bwd -> step -> D2H loss; "
                                        "CUDA events and wall clock bracket the same steps"},
-            "steps_requested": args.steps,
+            "steps_requested": args.steps, "diagnostic_op_timing": bool(args.op_timing),
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d[0],
                     "d2h_bytes_per_step": 4 * per_rank + 12},
@@ -527,6 +543,9 @@ def main():
     ap.add_argument("--host-gib", type=int, default=64)
     ap.add_argument("--budget-s", type=float, default=800.0,
                     help="wall-clock budget of the whole process; timed steps are reduced to fit (0 = never)")
+    ap.add_argument("--op-timing", default=None, metavar="FILE",
+                    help="bracket every op with CUDA events and write the per-op time table of the timed steps to FILE "
+                         "(diagnostic run: the throughput it prints is not a benchmark value)")
     ap.add_argument("--small", action="store_true", help="4-layer debug model; results are not reportable")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()

@@ -114,6 +114,9 @@ def _ffn(layer, l, P, h, aux=None):
         f = torch.bincount(idx.reshape(-1), minlength=E).to(logits.dtype) / idx.numel()
         aux.append(c.aux_loss_alpha * E * (f.detach() * torch.softmax(logits, -1).sum(0)).sum())
     up, down = P[("layer", l, "w_up")], P[("layer", l, "w_down")]
+    if ls is not None and ("layer", l, "w_up_lora_a") in P:        # per-expert adapters: W'[e] = W[e] + s B[e] A[e]
+        up = up + ls * torch.bmm(P[("layer", l, "w_up_lora_b")], P[("layer", l, "w_up_lora_a")])
+        down = down + ls * torch.bmm(P[("layer", l, "w_down_lora_b")], P[("layer", l, "w_down_lora_a")])
     out = torch.zeros_like(h)
     for k in range(c.top_k):
         e = idx[:, k]

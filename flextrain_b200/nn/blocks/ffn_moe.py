@@ -49,6 +49,8 @@ class MoEFFN:
     def __init__(self, cfg: MoEConfig, *, dtype=torch.bfloat16, lora: Optional[LoRAConfig] = None):
         self.cfg = cfg
         self.dtype = dtype
+        # per-expert LoRA on the routed stacks (flextrain/nn/layers/lora_wrapper.py:656-838)
+        self.lora = lora if (lora is not None and any(t in lora.targets for t in ("w_up", "w_down"))) else None
         self.shared = None
         if cfg.shared_dim > 0:
             self.shared = GatedFFN(DenseFFNConfig(cfg.d_model, cfg.shared_dim, cfg.kind), dtype=dtype, lora=None)
@@ -92,6 +94,42 @@ class MoEFFN:
             f.append(ActivationField("x13_shared", lambda t: (t, 2 * c.shared_dim), dt, 3))
         return f
 
+    # ------------------------------------------------------------------ per-expert LoRA
+    def weight(self, params, name: str) -> torch.Tensor:
+        """Effective expert stack ``W'[e] = W[e] + s * B[e] @ A[e]`` (cached in ``params`` until the optimizer step).
+        The merge is ONE grouped GEMM with K = r over the stacked ``B`` rows (expert e owns rows ``e*out .. (e+1)*out``),
+        accumulated in place into a copy of the base stack."""
+        w = params[name]
+        a = params.get(name + "_lora_a")
+        if self.lora is None or a is None:
+            return w
+        key = "_eff_" + name
+        eff = params.get(key)
+        if eff is None:
+            b = params[name + "_lora_b"]
+            n_e, out_f, in_f = w.shape
+            eff = w.clone()
+            offs = torch.arange(n_e + 1, dtype=torch.int32, device=w.device) * out_f
+            ops.grouped_gemm(b.to(w.dtype).reshape(n_e * out_f, -1), a.to(w.dtype).contiguous(), offs, trans_w=False,
+                             out=eff.view(n_e * out_f, in_f), alpha=self.lora.scale, beta=1.0)
+            params[key] = eff
+        return eff
+
+    def lora_wgrad(self, name: str, dy, x, offsets, params, grads, pad: int) -> None:
+        """Rank-r gradients of one expert stack from the expert-major rows ``x (R, in)`` / ``dy (R, out)``:
+        ``gB[e] += s * dy_e^T (x_e A_e^T)``, ``gA[e] += s * (dy_e B_e)^T x_e`` -- two grouped GEMMs with N = r and two
+        grouped weight-gradient launches, for all experts at once."""
+        ga = grads.get("g_" + name[2:] + "_lora_a")
+        if self.lora is None or ga is None:
+            return
+        gb = grads["g_" + name[2:] + "_lora_b"]
+        s = self.lora.scale
+        a, b = params[name + "_lora_a"].to(x.dtype), params[name + "_lora_b"].to(x.dtype)
+        xa = ops.grouped_gemm(x, a, offsets, trans_w=True)               # (R, r)
+        ops.grouped_wgrad(dy, xa, offsets, gb, alpha=s, pad=pad)
+        dyb = ops.grouped_gemm(dy, b, offsets, trans_w=False)            # (R, r)
+        ops.grouped_wgrad(dyb, x, offsets, ga, alpha=s, pad=pad)
+
     # --------------------------------------------------------------------- helpers
     def _route(self, h, params):
         c = self.cfg
@@ -102,7 +140,7 @@ class MoEFFN:
     def _experts_fwd(self, h, params, plan, x_up_out=None):
         F = self.cfg.expert_dim
         xs = ops.gather_rows(h, plan.row_src, idx_div=self.cfg.top_k)
-        up = ops.grouped_gemm(xs, params["w_up"], plan.offsets)
+        up = ops.grouped_gemm(xs, self.weight(params, "w_up"), plan.offsets)
         if x_up_out is not None and x_up_out.data_ptr() != up.data_ptr():
             x_up_out.copy_(up)
             up = x_up_out
@@ -126,9 +164,9 @@ class MoEFFN:
         if ctx.ep is not None:
             out = ctx.ep.moe_forward(self, h, x_resid, w, idx, params, slot)
         else:
-            plan = ref.moe_plan(idx, c.num_experts, ROW_PAD)
+            plan = ops.moe_plan(idx, c.num_experts, ROW_PAD)
             _, up, act = self._experts_fwd(h, params, plan, slot.out("x_up", h.device))
-            y = ops.grouped_gemm(act, params["w_down"], plan.offsets)
+            y = ops.grouped_gemm(act, self.weight(params, "w_down"), plan.offsets)
             out = ops.moe_combine(y, plan.inv, w, x_resid)
         if self.shared is not None:
             ys, g = self._shared_fwd(h, params, slot)
@@ -139,7 +177,7 @@ class MoEFFN:
 
     def recompute(self, h, params, slot) -> None:
         if not slot.has("x_up"):
-            plan = ref.moe_plan(slot._t["chosen_experts"], self.cfg.num_experts, ROW_PAD)
+            plan = ops.moe_plan(slot._t["chosen_experts"], self.cfg.num_experts, ROW_PAD)
             _, up, _ = self._experts_fwd(h, params, plan)
             slot._t["x_up"] = up
         if self.shared is not None and not slot.has("x13_shared"):
@@ -154,11 +192,11 @@ class MoEFFN:
         if ctx.ep is not None:
             dh, dw = ctx.ep.moe_backward(self, dx, h, w, idx, params, grads, slot)
         else:
-            plan = ref.moe_plan(idx, E, ROW_PAD)
+            plan = ops.moe_plan(idx, E, ROW_PAD)
             up = slot._t["x_up"]
             xs = ops.gather_rows(h, plan.row_src, idx_div=K)
             dy_u = ops.gather_rows(dx, plan.row_src, idx_div=K)                         # unweighted dL/dy rows
-            dact_u = ops.grouped_gemm(dy_u, params["w_down"], plan.offsets, trans_w=False)
+            dact_u = ops.grouped_gemm(dy_u, self.weight(params, "w_down"), plan.offsets, trans_w=False)
             # activation (re-emitted), router-weight gradient and weighted dact in one pass
             wrow = ref.moe_row_weights(w, plan)
             dup = torch.empty_like(up)
@@ -169,7 +207,9 @@ class MoEFFN:
                 ops.grouped_wgrad(dy_u, act_w, plan.offsets, grads["g_down"], pad=ROW_PAD)
             if "g_up" in grads:
                 ops.grouped_wgrad(dup, xs, plan.offsets, grads["g_up"], pad=ROW_PAD)
-            dxs = ops.grouped_gemm(dup, params["w_up"], plan.offsets, trans_w=False)
+            self.lora_wgrad("w_down", dy_u, act_w, plan.offsets, params, grads, ROW_PAD)
+            self.lora_wgrad("w_up", dup, xs, plan.offsets, params, grads, ROW_PAD)
+            dxs = ops.grouped_gemm(dup, self.weight(params, "w_up"), plan.offsets, trans_w=False)
             dh = ops.moe_combine(dxs, plan.inv, None, None)
         # router
         logits = ops.gemm(h, params["w_router"], trans_b=True)

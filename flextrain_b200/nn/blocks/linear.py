@@ -24,7 +24,10 @@ import torch
 
 from ... import ops
 
-LORA_ALL_TARGETS = ("w_q", "w_k", "w_v", "w_o", "w_1", "w_2", "w_3")
+# "all": every dense projection plus the routed-expert stacks of MoE layers (one rank-r pair per expert), as the
+# reference's lora_targets="all" (flextrain/nn/layers/lora_wrapper.py:197-255); routers, shared experts and the
+# bundled linear-attention projections are left out there too.
+LORA_ALL_TARGETS = ("w_q", "w_k", "w_v", "w_o", "w_1", "w_2", "w_3", "w_up", "w_down")
 
 
 @dataclass

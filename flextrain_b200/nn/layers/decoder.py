@@ -101,6 +101,16 @@ class DecoderLayer:
                     extra.append(TensorSpec(s.name + "_lora_b", (out_f, lo.rank), lo.compute_dtype,
                                             master_dtype=lo.master_dtype, grad_dtype=lo.grad_dtype,
                                             opt_state_dtype=lo.opt_state_dtype, optimizer="adamw", init="zeros"))
+                elif s.name in lo.targets and len(s.shape) == 3 and s.shard.ep_dim == 0:
+                    # routed-expert stack (E, out, in): one rank-r pair per expert, sharded with the experts
+                    n_e, out_f, in_f = s.shape
+                    for suffix, shape, init in (("_lora_a", (n_e, lo.rank, in_f), None),
+                                                ("_lora_b", (n_e, out_f, lo.rank), "zeros")):
+                        t = TensorSpec(s.name + suffix, shape, lo.compute_dtype, master_dtype=lo.master_dtype,
+                                       grad_dtype=lo.grad_dtype, opt_state_dtype=lo.opt_state_dtype, optimizer="adamw",
+                                       **({"init": init} if init else {}))
+                        t.shard = type(s.shard)(ep_dim=0)
+                        extra.append(t)
             specs += extra
         return ParamSpec(specs)
 

@@ -396,6 +396,23 @@ def topk_route_bwd(dw, logits, w, experts, mode="topk_then_softmax"):
 moe_sort = ref.moe_sort
 
 
+def moe_plan(experts, num_experts: int, pad: int = 1):
+    """Expert-major row layout of one chunk's routed slots (``reference.MoEPlan``): a stable counting sort by expert
+    with every expert's segment padded to ``pad`` rows.  On CUDA three small kernels build it without a host read
+    and without the library sort (flextrain/ops/_kernels/moe.py:318-357,461-505 plus the host sync of
+    flextrain/ops/full_moe.py:134-148 in the reference)."""
+    if experts.is_cuda and num_experts <= 1024:
+        T, K = experts.shape
+        R = ref.moe_rows_bound(T, K, num_experts, pad)
+        _count(3)
+        _used("moe_plan", "ftb")
+        row_src, inv, offsets, _ = _kernels().moe_plan(experts, num_experts, pad, R)
+        return ref.MoEPlan(row_src, inv, offsets, R)
+    if experts.is_cuda:
+        _fallback("moe_plan", f"{num_experts} experts (the plan kernels take up to 1024)")
+    return ref.moe_plan(experts, num_experts, pad)
+
+
 def gather_rows(x, idx, weights=None, idx_div=1):
     """``out[i] = x[idx[i] // idx_div] * weights[i]``."""
     if _cuda_bf16(x) and x.shape[1] % 8 == 0 and x.is_contiguous():
@@ -422,14 +439,29 @@ def moe_combine(y, inv, weights, resid):
     return out.to(y.dtype)
 
 
-def grouped_gemm(x, w, offsets, *, trans_w=True, out=None):
-    if _cuda_bf16(x, w) and _GEMM_BACKEND == "tcgen05" and x.shape[1] % 8 == 0 and w.is_contiguous() \
-            and (w.shape[1] if trans_w else w.shape[2]) % 8 == 0 and x.shape[1] >= 64:
-        _count()
-        return _kernels().grouped_gemm(x.contiguous(), w, offsets.to(torch.int32), trans_w=trans_w, out=out)
+def grouped_gemm(x, w, offsets, *, trans_w=True, out=None, alpha=1.0, beta=0.0):
+    """``out[rows_e] = alpha * x[rows_e] @ op(w[e]) + beta * out[rows_e]`` for every expert in one launch."""
+    if x.is_cuda:
+        why = None
+        if not (_cuda_bf16(x, w) and _GEMM_BACKEND == "tcgen05"):
+            why = "operands not bf16 or FTB_GEMM_BACKEND=library"
+        elif x.shape[1] % 8 or x.shape[1] < 8 or not w.is_contiguous() or (w.shape[1] if trans_w else w.shape[2]) % 8:
+            why = f"K or N not a multiple of 8 ({tuple(x.shape)}, {tuple(w.shape)})"
+        if why is None:
+            _count()
+            _used("grouped_gemm", "tcgen05")
+            return _kernels().grouped_gemm(x if x.stride(1) == 1 else x.contiguous(), w, offsets.to(torch.int32),
+                                           trans_w=trans_w, out=out, alpha=alpha, beta=beta)
+        _fallback("grouped_gemm", why)
     y = ref.grouped_gemm(x, w, offsets, trans_w=trans_w)
+    if alpha != 1.0:
+        y = (y.to(torch.float32) * alpha).to(y.dtype)
     if out is not None:
-        out.copy_(y)
+        if beta != 0.0:
+            rows = int(offsets[-1])
+            out[:rows] = (beta * out[:rows].to(torch.float32) + y[:rows].to(torch.float32)).to(out.dtype)
+        else:
+            out.copy_(y)
         return out
     return y
 
@@ -441,7 +473,10 @@ def grouped_wgrad(dy, x, offsets, gw, *, alpha=1.0, pad: int = 1):
             and gw.dtype in (torch.bfloat16, torch.float32) and dy.shape[1] % 8 == 0 and x.shape[1] % 8 == 0
             and dy.stride(1) == 1 and x.stride(1) == 1 and dy.stride(0) % 8 == 0 and x.stride(0) % 8 == 0):
         _count()
+        _used("grouped_wgrad", "tcgen05")
         return _kernels().grouped_wgrad(dy, x, offsets.to(torch.int32), gw, alpha=alpha)
+    if dy.is_cuda:
+        _fallback("grouped_wgrad", f"dtype / stride / padding not supported ({tuple(dy.shape)}, {tuple(x.shape)}, pad {pad})")
     return ref.grouped_wgrad(dy, x, offsets, gw, alpha=alpha)
 
 
@@ -476,3 +511,82 @@ def top_p_sample(logits, top_p, temperature, generator=None):
 
 
 rope_inv_freq = ref.rope_inv_freq
+
+
+# ------------------------------------------------------------------ per-op device timing
+# ``FTB_OP_TIMING=1`` brackets every leaf op of this module with CUDA events on the current stream and
+# ``timing_report()`` aggregates them by (op, shape): the per-kernel time table of a training step without a
+# profiler attached.  The events add host work, so a throughput number taken with it on is not a benchmark value.
+_TIMED_OPS = ("gemm", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "glu_fwd", "glu_bwd", "glu_bwd_weighted", "attention_fwd",
+              "attention_bwd", "softmax_ce_", "embedding_fwd", "embedding_bwd", "adamw_multi", "topk_route",
+              "topk_route_bwd", "gather_rows", "moe_combine", "grouped_gemm", "grouped_wgrad", "l2norm_fwd",
+              "gated_rmsnorm_fwd", "bias_grad")
+_timing_events: list = []
+
+
+def _timing_key(name, args, kwargs):
+    if name == "gemm":
+        a, b = args[0], args[1]
+        ta, tb = kwargs.get("trans_a", False), kwargs.get("trans_b", False)
+        M = a.shape[1] if ta else a.shape[0]
+        K = a.shape[0] if ta else a.shape[1]
+        N = b.shape[0] if tb else b.shape[1]
+        lay = ("T" if ta else "N") + ("T" if tb else "N")
+        od = kwargs.get("out_dtype") or (kwargs["out"].dtype if kwargs.get("out") is not None else a.dtype)
+        return f"{M}x{N}x{K} {lay}" + (" +C" if kwargs.get("beta", 0.0) else "") + (" f32" if od == torch.float32 else "")
+    for v in list(args) + list(kwargs.values()):
+        if isinstance(v, torch.Tensor):
+            return "x".join(str(s) for s in v.shape)
+        if isinstance(v, (list, tuple)) and v and isinstance(v[0], torch.Tensor):
+            return f"{len(v)} tensors, {sum(t.numel() for t in v)} elements"
+    return ""
+
+
+def _timed(name, fn):
+    def wrapper(*args, **kwargs):
+        first = next((v for v in args if isinstance(v, torch.Tensor)), None)
+        if first is None and args and isinstance(args[0], (list, tuple)) and args[0]:
+            first = args[0][0]
+        if first is None or not first.is_cuda:
+            return fn(*args, **kwargs)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn(*args, **kwargs)
+        e1.record()
+        _timing_events.append((name, _timing_key(name, args, kwargs), e0, e1))
+        return out
+    wrapper.__name__ = fn.__name__
+    wrapper.__doc__ = fn.__doc__
+    return wrapper
+
+
+def enable_op_timing() -> None:
+    g = globals()
+    for n in _TIMED_OPS:
+        if not getattr(g[n], "_ftb_timed", False):
+            g[n] = _timed(n, g[n])
+            g[n]._ftb_timed = True
+
+
+def reset_op_timing() -> None:
+    _timing_events.clear()
+
+
+def timing_report() -> list:
+    """``[{op, shape, calls, total_ms, mean_us, share}]`` sorted by total time; synchronises the device."""
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    agg: dict = {}
+    for name, key, e0, e1 in _timing_events:
+        ms = e0.elapsed_time(e1)
+        c = agg.setdefault((name, key), [0, 0.0])
+        c[0] += 1
+        c[1] += ms
+    total = sum(v[1] for v in agg.values()) or 1.0
+    rows = [{"op": k[0], "shape": k[1], "calls": v[0], "total_ms": v[1], "mean_us": 1e3 * v[1] / v[0],
+             "share": v[1] / total} for k, v in agg.items()]
+    return sorted(rows, key=lambda r: -r["total_ms"])
+
+
+if os.environ.get("FTB_OP_TIMING", "0") == "1":
+    enable_op_timing()

@@ -370,6 +370,61 @@ def topk_route(logits, k, mode):
     return w, idx
 
 
+PLAN_CHUNK = 2048          # slots per block of the routing-plan kernels (csrc/moe.cu)
+
+
+def moe_plan(experts: torch.Tensor, num_experts: int, pad: int, rows: int):
+    """Routing plan of one chunk on the device (three launches, no host read): returns
+    ``(row_src (rows,), inv (T,K), offsets (E+1,), counts (E,))``, all int32 (csrc/moe.cu ``ftb_moe_plan``)."""
+    lib = load("moe")
+    T, K = experts.shape
+    n = T * K
+    dev = experts.device
+    ex = experts if (experts.dtype == torch.int32 and experts.is_contiguous()) else experts.to(torch.int32).contiguous()
+    nb = max((n + PLAN_CHUNK - 1) // PLAN_CHUNK, 1)
+    work = torch.empty(nb * num_experts, dtype=torch.int32, device=dev)
+    counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    inv = torch.empty(T, K, dtype=torch.int32, device=dev)
+    row_src = torch.empty(rows, dtype=torch.int32, device=dev)
+    rc = lib.ftb_moe_plan(_ptr(ex), c_long(n), c_int(num_experts), c_int(pad), c_long(rows), _ptr(work), _ptr(counts),
+                          _ptr(offsets), _ptr(inv), _ptr(row_src), _stream())
+    _check(rc, "ftb_moe_plan")
+    return row_src, inv, offsets, counts
+
+
+def ep_plan_count(experts: torch.Tensor, num_experts: int):
+    """First half of the expert-parallel plan: ``(counts (E,) int32, work)`` of this rank's slots."""
+    lib = load("moe")
+    n = experts.numel()
+    ex = experts if (experts.dtype == torch.int32 and experts.is_contiguous()) else experts.to(torch.int32).contiguous()
+    nb = max((n + PLAN_CHUNK - 1) // PLAN_CHUNK, 1)
+    work = torch.empty(nb * num_experts, dtype=torch.int32, device=experts.device)
+    counts = torch.empty(num_experts, dtype=torch.int32, device=experts.device)
+    rc = lib.ftb_ep_plan_count(_ptr(ex), c_long(n), c_int(num_experts), _ptr(work), _ptr(counts), _stream())
+    _check(rc, "ftb_ep_plan_count")
+    return counts, work, ex
+
+
+def ep_plan_map(ex: torch.Tensor, shape, num_experts: int, table: torch.Tensor, world: int, rank: int, pad: int,
+                capacity: int, work: torch.Tensor, overflow: torch.Tensor):
+    """Second half: ``(slot_rank (T,K), slot_row (T,K), my_offsets (E/W+1,))`` from the all-gathered ``(W, E)`` int32
+    count table; sets ``overflow`` (int32 scalar tensor) when a destination row exceeds ``capacity``."""
+    lib = load("moe")
+    T, K = shape
+    dev = ex.device
+    assert table.dtype == torch.int32 and table.is_contiguous() and overflow.dtype == torch.int32
+    start = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    offs = torch.empty(num_experts // world + 1, dtype=torch.int32, device=dev)
+    slot_rank = torch.empty(T, K, dtype=torch.int32, device=dev)
+    slot_row = torch.empty(T, K, dtype=torch.int32, device=dev)
+    rc = lib.ftb_ep_plan_map(_ptr(ex), c_long(T * K), c_int(num_experts), _ptr(table), c_int(world), c_int(rank),
+                             c_int(pad), c_long(capacity), _ptr(work), _ptr(start), _ptr(offs), _ptr(slot_rank),
+                             _ptr(slot_row), _ptr(overflow), _stream())
+    _check(rc, "ftb_ep_plan_map")
+    return slot_rank, slot_row, offs
+
+
 def gather_rows(x, idx, weights=None, idx_div=1):
     lib = load("elementwise")
     R, D = idx.numel(), x.shape[1]

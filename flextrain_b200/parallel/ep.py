@@ -79,6 +79,7 @@ class ExpertParallel:
         self._calls = 0
         self.slot_base = 3500
         self.overflow = None
+        self._overflow_dev = None
         self.max_chunk_tokens = 0      # set by attach(): the planner's chunk size, identical on every rank
 
     def attach(self, am) -> None:
@@ -114,7 +115,7 @@ class ExpertParallel:
             self._bufs[key] = self.group.alloc(nbytes)
         return self._bufs[key]
 
-    def _gather_counts(self, counts: torch.Tensor) -> torch.Tensor:
+    def _gather_counts(self, counts: torch.Tensor, as_int32: bool = False) -> torch.Tensor:
         W, E = self.world, counts.numel()
         if self.backend != "p2p":
             import torch.distributed as dist
@@ -131,9 +132,41 @@ class ExpertParallel:
         if rc != 0:
             raise RuntimeError(f"ftb_comm_allgather_push failed ({rc})")
         self._sync()
-        return table.clone().long()
+        return table.clone() if as_int32 else table.clone().long()
 
     def plan(self, idx: torch.Tensor, w: torch.Tensor, E: int) -> EPPlan:
+        if self.backend == "p2p" and idx.is_cuda and E <= 1024:
+            return self._plan_device(idx, w, E)
+        T, K = idx.shape
+        dev = idx.device
+        flat = idx.reshape(-1).long()
+        n = flat.numel()
+        counts = torch.zeros(E, dtype=torch.long, device=dev).index_add_(0, flat, torch.ones(n, dtype=torch.long, device=dev))
+        table = self._gather_counts(counts).long()                      # (W, E)
+        return self.plan_from_table(idx, w, E, table)
+
+    def _plan_device(self, idx: torch.Tensor, w: torch.Tensor, E: int) -> EPPlan:
+        """The plan on the device: count kernel -> all-gather of the count table over peer memory -> scan + map
+        kernels (``csrc/moe.cu``).  No library sort and no eager index arithmetic; the only host read left is the
+        row total of the dropless mode (capacity-factor buffers need none: saved activations take the capacity)."""
+        from ..ops import cuda as k
+        T, K = idx.shape
+        counts, work, ex = k.ep_plan_count(idx, E)
+        table = self._gather_counts(counts, as_int32=True)
+        cap = self.capacity(T, K, E)
+        if self._overflow_dev is None:
+            self._overflow_dev = torch.zeros((), dtype=torch.int32, device=idx.device)
+        slot_rank, slot_row, offsets = k.ep_plan_map(ex, (T, K), E, table, self.world, self.rank, PAD, cap, work,
+                                                     self._overflow_dev)
+        ops._count(4)
+        self.overflow = self._overflow_dev
+        rows = cap if self.capacity_factor > 0 else int(offsets[-1])
+        return EPPlan(None, None, None, None, slot_rank, slot_row, offsets,
+                      w.reshape(-1).to(torch.float32).contiguous(), rows)
+
+    def plan_from_table(self, idx: torch.Tensor, w: torch.Tensor, E: int, table: torch.Tensor) -> EPPlan:
+        """The same plan in plain tensor ops (library back end, CPU ranks, and the oracle of the plan kernels):
+        ``table (W, E)`` holds every rank's per-expert slot counts."""
         T, K = idx.shape
         dev = idx.device
         W, El = self.world, E // self.world
@@ -141,8 +174,7 @@ class ExpertParallel:
         n = flat.numel()
         order = torch.sort(flat, stable=True).indices
         e_sorted = flat[order]
-        counts = torch.zeros(E, dtype=torch.long, device=dev).index_add_(0, flat, torch.ones(n, dtype=torch.long, device=dev))
-        table = self._gather_counts(counts).long()                      # (W, E)
+        counts = table[self.rank]
         tot = table.sum(0)
         padded = (tot + PAD - 1) // PAD * PAD
         pr = padded.view(W, El)
@@ -206,14 +238,22 @@ class ExpertParallel:
             sc[:R].zero_()
         self._sync()                       # all receive buffers are clean and no one still reads the old contents
         from ..ops.cuda import _stream
-        n = plan.src_tok.numel()
-        rc = self.lib.ftb_ep_push_rows(c_void_p(x.data_ptr()), c_void_p(plan.src_tok.data_ptr()),
-                                       c_void_p(plan.dest_rank.data_ptr()), c_void_p(plan.dest_row.data_ptr()),
-                                       c_void_p(plan.w_sorted.data_ptr() if with_scalar else 0), buf.c_ptrs,
-                                       sbuf.c_ptrs if with_scalar else None, c_long(n), c_int(D), c_long(cap),
-                                       c_int(self.world), _stream())
+        if plan.src_tok is None:           # device-built plan: dispatch by (token, k) slot
+            Tn, K = plan.slot_rank.shape
+            rc = self.lib.ftb_ep_push_slots(c_void_p(x.data_ptr()), c_void_p(plan.slot_rank.data_ptr()),
+                                            c_void_p(plan.slot_row.data_ptr()),
+                                            c_void_p(plan.w_sorted.data_ptr() if with_scalar else 0), buf.c_ptrs,
+                                            sbuf.c_ptrs if with_scalar else None, c_long(Tn * K), c_int(K), c_int(D),
+                                            c_long(cap), c_int(self.world), _stream())
+        else:
+            n = plan.src_tok.numel()
+            rc = self.lib.ftb_ep_push_rows(c_void_p(x.data_ptr()), c_void_p(plan.src_tok.data_ptr()),
+                                           c_void_p(plan.dest_rank.data_ptr()), c_void_p(plan.dest_row.data_ptr()),
+                                           c_void_p(plan.w_sorted.data_ptr() if with_scalar else 0), buf.c_ptrs,
+                                           sbuf.c_ptrs if with_scalar else None, c_long(n), c_int(D), c_long(cap),
+                                           c_int(self.world), _stream())
         if rc != 0:
-            raise RuntimeError(f"ftb_ep_push_rows failed ({rc})")
+            raise RuntimeError(f"ftb_ep dispatch failed ({rc})")
         ops._count()
         self._sync()                       # every rank's rows have landed
         return recv, sc
@@ -286,11 +326,11 @@ class ExpertParallel:
         plan = self.plan(idx, w, c.num_experts)
         xs, _ = self.dispatch(h, plan, cap, "recv_a")
         R = max(plan.rows, PAD)
-        up = ops.grouped_gemm(xs[:R], params["w_up"], plan.offsets)
+        up = ops.grouped_gemm(xs[:R], moe.weight(params, "w_up"), plan.offsets)
         slot._t["x_up"] = up               # sized by the rows that arrived, not by the receive capacity
         slot._t["_ep_plan"] = plan
         act = ops.glu_fwd(up[:, F:], up[:, :F], c.kind)
-        y = ops.grouped_gemm(act, params["w_down"], plan.offsets)
+        y = ops.grouped_gemm(act, moe.weight(params, "w_down"), plan.offsets)
         return self.combine(y, plan, w, x_resid, cap, "ybuf")
 
     def moe_backward(self, moe, dx, h, w, idx, params, grads, slot):
@@ -304,8 +344,8 @@ class ExpertParallel:
         xs, dy_u, wrow = xs[:R], dy_u[:R], wrow[:R]
         up = slot._t.get("x_up")
         if up is None:
-            up = ops.grouped_gemm(xs, params["w_up"], plan.offsets)
-        dact_u = ops.grouped_gemm(dy_u, params["w_down"], plan.offsets, trans_w=False)
+            up = ops.grouped_gemm(xs, moe.weight(params, "w_up"), plan.offsets)
+        dact_u = ops.grouped_gemm(dy_u, moe.weight(params, "w_down"), plan.offsets, trans_w=False)
         dup = torch.empty_like(up)
         act_w, dw_rows = ops.glu_bwd_weighted(dact_u, up[:, F:], up[:, :F], wrow, c.kind, dgate=dup[:, F:],
                                               dup=dup[:, :F])
@@ -313,7 +353,9 @@ class ExpertParallel:
             ops.grouped_wgrad(dy_u, act_w, plan.offsets, grads["g_down"], pad=PAD)
         if "g_up" in grads:
             ops.grouped_wgrad(dup, xs, plan.offsets, grads["g_up"], pad=PAD)
-        dxs = ops.grouped_gemm(dup, params["w_up"], plan.offsets, trans_w=False)
+        moe.lora_wgrad("w_down", dy_u, act_w, plan.offsets, params, grads, PAD)
+        moe.lora_wgrad("w_up", dup, xs, plan.offsets, params, grads, PAD)
+        dxs = ops.grouped_gemm(dup, moe.weight(params, "w_up"), plan.offsets, trans_w=False)
         dh = self.combine(dxs, plan, None, None, cap, "ybuf")
         dw = self.pull_scalar(dw_rows, plan, cap, "dwbuf")
         return dh, dw
@@ -321,6 +363,8 @@ class ExpertParallel:
     def check(self) -> None:
         if self.overflow is not None and bool(self.overflow):
             self.overflow = None
+            if self._overflow_dev is not None:
+                self._overflow_dev.zero_()
             raise RuntimeError("expert-parallel receive capacity exceeded; raise capacity_factor")
         if self.backend == "p2p":
             self.group.check()

@@ -160,3 +160,43 @@ def test_moe_dump_and_diff(tmp_path, monkeypatch):
     assert all(r.get("max_abs", 0.0) == 0.0 for r in first if "max_abs" in r)          # layer 0 is untouched
     logits = [r["max_abs"] for r in moved if r["tensor"] == "router_logits"]
     assert sum(v > 0.1 for v in logits) == 2 and sum(v == 0.0 for v in logits) == 2     # layer 1's router moved, both chunks
+
+
+@pytest.mark.parametrize("arch", ["qwen3_moe", "olmoe"])
+def test_moe_per_expert_lora_gradients(arch):
+    """LoRA on the routed-expert stacks: one rank-r pair per expert (``w_up_lora_a (E, r, d)``, ``w_up_lora_b
+    (E, 2F, r)``, likewise for ``w_down``).  The engine merges the adapters into the expert weights with one grouped
+    GEMM and gets the rank-r gradients from the expert-major ``(x, dy)`` rows with grouped launches; autograd on the
+    naive model (``W[e] + s B[e] A[e]`` per token) is the oracle.  Base weights, router included, stay frozen."""
+    am = build_tiny(arch=arch, dims=MOE, max_seq_len=48, batch_tokens=96, lora_targets="all", lora_rank=4,
+                    lora_alpha=8.0, lora_adapter_compute_dtype=torch.float32, lora_adapter_master_dtype=torch.float32,
+                    lora_adapter_grad_dtype=torch.float32, lora_adapter_opt_state_dtype=torch.float32)
+    torch.manual_seed(0)
+    names = {n for _, _, n, _ in am.named_master_params()}
+    assert {"w_up_lora_a", "w_up_lora_b", "w_down_lora_a", "w_down_lora_b", "w_q_lora_a"} <= names
+    for scope, l, name, t in am.named_master_params():
+        if name.endswith("_lora_b"):
+            t.copy_(torch.randn_like(t) * 0.05)
+    E, F, d = MOE["num_routed_experts"], MOE["expert_dim"], MOE["d_model"]
+    assert am.buffers.params(0)["w_up_lora_a"].shape == (E, 4, d)
+    assert am.buffers.params(0)["w_down_lora_b"].shape == (E, d, 4)
+    seqs = ft.SyntheticTokenSource(512, 48, seed=3).get_sequences(96)
+    P = clone_params(am)
+    naive_loss(am, P, seqs).backward()
+    am.fwd_bwd(seqs)
+    for l in range(2):
+        g = am.buffers.grads(l)
+        assert "g_up" not in g and "g_down" not in g and "g_router" not in g, "base weights must be frozen under LoRA"
+        for name in ("w_up", "w_down", "w_q", "w_o"):
+            for ab in ("_lora_a", "_lora_b"):
+                want = P[("layer", l, name + ab)].grad
+                assert float(want.abs().max()) > 0
+                torch.testing.assert_close(g["g_" + name[2:] + ab].float(), want, rtol=3e-4, atol=3e-6,
+                                           msg=f"{l}/{name}{ab}")
+    before = {n: t.clone() for _, l, n, t in am.named_master_params() if l == 0}
+    assert am.step() == 0
+    after = {n: t for _, l, n, t in am.named_master_params() if l == 0}
+    assert not torch.equal(before["w_up_lora_a"], after["w_up_lora_a"])
+    assert torch.equal(before["w_up"], after["w_up"])
+    st = am.fwd_bwd(seqs)                       # the merged weights were rebuilt from the updated adapters
+    assert st.loss == st.loss

@@ -161,3 +161,37 @@ def test_multimodal_bf16_tracks_fp32(tmp_path):
         b = gpu.fwd_bwd(seqs); gpu.step()
         assert abs(a.loss - b.loss) < 0.05, (step, a.loss, b.loss)
     assert gpu.embed.last_summary.n_images == 3
+
+
+def test_lora_bf16_tracks_fp32_on_the_tensor_core_kernel(monkeypatch):
+    """LoRA r=16 on every linear of a tiny Llama: the merged weight, both rank-r gradient products and the adapter
+    update run on the hand-written GEMM (strict mode would raise on a library call); losses track the fp32 CPU run and
+    only the adapters move."""
+    from flextrain_b200 import ops
+    monkeypatch.setenv("FTB_STRICT", "1")
+    dims = dict(vocab_size=1024, n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, expert_dim=704,
+                ffn_dim=704, num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
+    kw = dict(lora_targets="all", lora_rank=16, lora_alpha=32.0, lora_adapter_opt_state_dtype=torch.float32)
+    cpu = build_tiny(dims=dims, lora_adapter_compute_dtype=torch.float32, lora_adapter_master_dtype=torch.float32,
+                     lora_adapter_grad_dtype=torch.float32, **kw)
+    gpu = build_tiny(dims=dims, device="cuda:0", dtype=torch.bfloat16,
+                     optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32), **kw)
+    _copy_weights(cpu, gpu)
+    base0 = {(s, l, n): t.clone() for s, l, n, t in gpu.named_master_params() if "_lora_" not in n}
+    src = ft.SyntheticTokenSource(1024, 128, seed=3)
+    ops.reset_backends_used()
+    for step in range(4):
+        seqs = src.get_sequences(256)
+        a = cpu.fwd_bwd(seqs); cpu.step()
+        b = gpu.fwd_bwd(seqs); gpu.step()
+        assert abs(a.loss - b.loss) < 0.03, (step, a.loss, b.loss)
+    assert ops.backends_used().get("gemm") == ["tcgen05"], ops.backends_used()
+    moved = 0.0
+    for s, l, n, t in gpu.named_master_params():
+        if "_lora_b" in n:
+            moved = max(moved, float(t.float().abs().max()))
+        elif "_lora_" not in n:
+            assert torch.equal(t, base0[(s, l, n)]), (s, l, n)
+    assert moved > 0
+    from flextrain_b200.ops import cuda as k
+    assert all(v == 0 for v in k.device_error_words().values())

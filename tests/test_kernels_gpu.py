@@ -344,3 +344,88 @@ def test_muon_newton_schulz_on_tcgen05(shape):
     cos = torch.nn.functional.cosine_similarity(step.flatten(), step_ref.flatten(), dim=0)
     assert float(cos) > 0.98, float(cos)
     assert _rel(p, p_ref) < 2e-2, _rel(p, p_ref)
+
+
+@pytest.mark.parametrize("case", ["merge", "dy_b", "x_at", "ga", "gb"])
+def test_gemm_rank16_lora_shapes(case):
+    """The five products of a rank-16 LoRA linear (N = r or K = r or M = r): tiles mostly outside the matrix,
+    filled with zeros by TMA.  All of them must run on the tensor-core kernel (strict mode raises otherwise)."""
+    import os
+    T, d_in, d_out, r = 1000, 512, 768, 16
+    x, dy = _rand(T, d_in), _rand(T, d_out)
+    A, B = _rand(r, d_in, scale=0.1), _rand(d_out, r, scale=0.1)
+    os.environ["FTB_STRICT"] = "1"
+    try:
+        if case == "merge":       # W' = W + s * B @ A   (K = r, beta = 1, MN-major B operand)
+            W = _rand(d_out, d_in)
+            got = ops.gemm(B, A, alpha=2.0, beta=1.0, out=W.clone())
+            want = W.float() + 2.0 * (B.float() @ A.float())
+        elif case == "dy_b":      # (T, out) @ (out, r): N = r
+            got, want = ops.gemm(dy, B), dy.float() @ B.float()
+        elif case == "x_at":      # (T, in) @ (r, in)^T: N = r
+            got, want = ops.gemm(x, A, trans_b=True), x.float() @ A.float().t()
+        elif case == "ga":        # (T, r)^T @ (T, in): M = r, accumulated
+            dyb = _rand(T, r)
+            g0 = _rand(r, d_in)
+            got = ops.gemm(dyb, x, trans_a=True, alpha=0.5, beta=1.0, out=g0.clone())
+            want = g0.float() + 0.5 * (dyb.float().t() @ x.float())
+        else:                     # (T, out)^T @ (T, r): N = r, accumulated
+            xa = _rand(T, r)
+            g0 = _rand(d_out, r)
+            got = ops.gemm(dy, xa, trans_a=True, alpha=0.5, beta=1.0, out=g0.clone())
+            want = g0.float() + 0.5 * (dy.float().t() @ xa.float())
+    finally:
+        os.environ["FTB_STRICT"] = "0"
+    assert _rel(got, want) < 6e-3, (case, _rel(got, want))
+    from flextrain_b200.ops import cuda as k
+    assert k.device_error_words().get("gemm_tcgen05", 0) == 0
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_beta_on_mn_major_layouts(ta, tb, out_dtype):
+    """alpha / beta accumulate with MN-major operands (the dgrad and wgrad layouts), one-SM and two-SM kernels."""
+    from flextrain_b200.ops import cuda as k
+    M, N, K = 640, 768, 520
+    a = _rand(K, M) if ta else _rand(M, K)
+    b = _rand(N, K) if tb else _rand(K, N)
+    c = _rand(M, N, dtype=out_dtype)
+    want = 0.25 * ref.gemm(a, b, trans_a=ta, trans_b=tb, out_dtype=torch.float32) + 1.5 * c.float()
+    for bn in (0, 256, 512):
+        out = k.gemm(a, b, trans_a=ta, trans_b=tb, alpha=0.25, beta=1.5, c=c, out_dtype=out_dtype, bn=bn)
+        assert _rel(out, want) < 6e-3, (ta, tb, bn, _rel(out, want))
+
+
+def test_grouped_gemm_ragged_experts():
+    """Expert row segments that are not multiples of the 128-row tile (the rows past a segment's end belong to the
+    next expert and must not be overwritten), including empty and one-row experts."""
+    from flextrain_b200.ops import cuda as k
+    E, K, N = 6, 192, 264
+    counts = [5, 0, 130, 1, 257, 64]
+    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    R = int(off[-1])
+    x = _rand(R, K)
+    w = _rand(E, N, K, scale=0.1)
+    y = k.grouped_gemm(x, w, off, trans_w=True)
+    want = ref.grouped_gemm(x, w, off, trans_w=True)
+    assert _rel(y, want) < 6e-3, _rel(y, want)
+    for e in range(E):                       # per expert, so a small expert's error cannot hide in the total
+        a, b = int(off[e]), int(off[e + 1])
+        if b > a:
+            assert _rel(y[a:b], want[a:b]) < 1e-2, (e, _rel(y[a:b], want[a:b]))
+
+
+def test_strict_mode_refuses_library_paths():
+    import os
+    os.environ["FTB_STRICT"] = "1"
+    try:
+        a, b = _rand(64, 64), _rand(64, 60)             # N = 60 is not a multiple of 8
+        with pytest.raises(ops.LibraryFallback):
+            ops.gemm(a, b)
+        ops.reset_backends_used()
+        ops.gemm(_rand(64, 64), _rand(64, 64))
+        assert ops.backends_used() == {"gemm": ["tcgen05"]}
+    finally:
+        os.environ["FTB_STRICT"] = "0"
+    ops.gemm(a, b)                                       # outside strict mode the library path still works
+    assert "library" in ops.backends_used()["gemm"]

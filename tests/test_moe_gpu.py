@@ -57,3 +57,52 @@ def test_moe_model_bf16_tracks_fp32(arch):
                                                                 gb[name].flatten().float().cpu(), dim=0)
                     assert cos > 0.98, (arch, l, name, float(cos))
         cpu.step(); gpu.step()
+
+
+@pytest.mark.parametrize("T,K,E,pad,skew", [(300, 2, 8, 128, False), (4096, 8, 128, 128, False), (5000, 8, 64, 128, True),
+                                            (16384, 8, 128, 128, True), (77, 4, 256, 64, False), (2049, 1, 60, 1, False)])
+def test_device_routing_plan_equals_stable_sort(T, K, E, pad, skew):
+    """The three plan kernels against the plain tensor-op statement (library stable sort + cumsum): identical row
+    layout, inverse map and padded offsets, also when a few experts take most slots or some take none."""
+    from flextrain_b200 import ops
+    from flextrain_b200.ops import reference as ref
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    if skew:
+        p = torch.ones(E, device="cuda"); p[:3] = 200.0; p[5] = 0.0
+        idx = torch.multinomial(p.expand(T, E), K, generator=g).to(torch.int32)
+    else:
+        idx = torch.randint(0, E, (T, K), device="cuda", generator=g, dtype=torch.int32)
+    got = ops.moe_plan(idx, E, pad)
+    want = ref.moe_plan(idx, E, pad)
+    assert got.rows == want.rows
+    assert torch.equal(got.offsets.long(), want.offsets.long())
+    assert torch.equal(got.inv.long(), want.inv.long())
+    assert torch.equal(got.row_src.long(), want.row_src.long())
+    assert ops.backends_used().get("moe_plan") == ["ftb"]
+
+
+@pytest.mark.parametrize("W,rank", [(2, 0), (4, 3), (8, 5)])
+def test_expert_parallel_plan_kernels_against_tensor_ops(W, rank):
+    """Expert-parallel destination rows on one GPU: the count table of the other ranks is made up, this rank's row is
+    the real count of its slots; the scan + map kernels must give the rows of ``ExpertParallel.plan_from_table``."""
+    from flextrain_b200.ops import cuda as k
+    from flextrain_b200.parallel.ep import PAD, ExpertParallel
+    T, K, E = 3000, 8, 64
+    g = torch.Generator(device="cuda").manual_seed(W * 10 + rank)
+    idx = torch.randint(0, E, (T, K), device="cuda", generator=g, dtype=torch.int32)
+    w = torch.rand(T, K, device="cuda", generator=g)
+    counts, work, ex = k.ep_plan_count(idx, E)
+    assert torch.equal(counts.long(), torch.bincount(idx.reshape(-1).long(), minlength=E))
+    table = torch.randint(0, 700, (W, E), device="cuda", generator=g, dtype=torch.int32)
+    table[rank] = counts
+    ep = ExpertParallel(rank, W, "cuda", None, backend="collective", capacity_factor=float(W))
+    want = ep.plan_from_table(idx, w, E, table.long())
+    cap = ep.capacity(T, K, E)
+    over = torch.zeros((), dtype=torch.int32, device="cuda")
+    slot_rank, slot_row, offs = k.ep_plan_map(ex, (T, K), E, table.contiguous(), W, rank, PAD, cap, work, over)
+    assert torch.equal(slot_rank, want.slot_rank) and torch.equal(slot_row, want.slot_row)
+    assert torch.equal(offs, want.offsets) and int(over) == 0
+    # a capacity that is too small is flagged, never silently accepted
+    small = int(want.slot_row.max()) - 5
+    k.ep_plan_map(ex, (T, K), E, table.contiguous(), W, rank, PAD, small, work, over)
+    assert int(over) == 1
