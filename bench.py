@@ -71,7 +71,7 @@ CONFIGS = {
                                expert_dim=28672, ffn_dim=28672, num_routed_experts=0, num_shared_experts=0, top_k=0,
                                is_causal=True),
                      seq_len=2048, global_batch=262144, hyper={"rope_theta": 500000.0, "norm_eps": 1e-5},
-                     scaling="strong", tp="world"),
+                     scaling="strong", tp="world", opt_state="host"),
 }
 PUBLISHED_TOK_S = 3733.0          # reference, RTX 5090, Llama-3.1-8B full FT (docs/verified_runs.md:160)
 METRIC = "train tokens/sec/box, Llama-3.1-8B full FT"
@@ -180,8 +180,14 @@ def run_ours(args):
     opt = ft.AdamW(lr=1e-4 if lora else 3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
                    state_dtype=torch.float32)
     extra = dict(lora_targets=lora["targets"], lora_rank=lora["rank"], lora_alpha=lora["alpha"]) if lora else {}
+    host_bytes = args.host_gib << 30
+    if cfg.get("opt_state") == "host" and not args.opt_state_device:
+        # fp32 AdamW state of the rank's slice lives in pinned host memory: give the planner this rank's share of it
+        import psutil
+        host_bytes = max(host_bytes, int(psutil.virtual_memory().available * 0.8) // max(world, 1))
+        extra["opt_state"] = "host"
     am = ft.from_dims(dims, arch=cfg["arch"], optimizer=opt, max_seq_len=seq_len, max_global_batch_tokens=gbatch,
-                      max_gpu_mem_bytes=int(free), max_host_mem_bytes=args.host_gib << 30, device=dev,
+                      max_gpu_mem_bytes=int(free), max_host_mem_bytes=host_bytes, device=dev,
                       hyperparams=cfg["hyper"], world_size=world, rank=rank,
                       dp_shard=args.shard, init_on_device=True, init_std=0.02, verbose=(rank == 0 and args.verbose),
                       max_chunk_size=args.chunk, head_chunk_size=args.head_chunk, **par, **extra)
@@ -292,7 +298,8 @@ def run_ours(args):
             "config": {"model": cfg["model"] + (" (SMALL DEBUG)" if args.small else ""), "global_batch": gbatch,
                        "seq_len": seq_len, "parallelism": (f"tp{world}" if par["tp"] > 1 else f"dp{world}" + (f"+ep{world}" if par["ep"] > 1 else ""))
                        + (f"-shard({am.ws.shard})" if world > 1 else ""),
-                       "optimizer": "AdamW fp32 state" + (f", state on {am.ws.opt_residency}" if hasattr(am.ws, "opt_residency") else ""),
+                       "optimizer": "AdamW fp32 state",
+                       "opt_state": "host" if am.ws.n_gpu_opt_layers is not None else "hbm",
                        "round_tokens": am.ws.target_round_tokens,
                        "chunk": am.ws.max_chunk_size, "rounds_per_step": am.ws.target_num_rounds,
                        "l2": "inputs larger than L2 (each step streams >100 GB of weights/activations)",
@@ -543,6 +550,8 @@ def main():
     ap.add_argument("--host-gib", type=int, default=64)
     ap.add_argument("--budget-s", type=float, default=800.0,
                     help="wall-clock budget of the whole process; timed steps are reduced to fit (0 = never)")
+    ap.add_argument("--opt-state-device", action="store_true",
+                    help="keep optimizer state in HBM even for a configuration that names host offload (llama70b)")
     ap.add_argument("--op-timing", default=None, metavar="FILE",
                     help="bracket every op with CUDA events and write the per-op time table of the timed steps to FILE "
                          "(diagnostic run: the throughput it prints is not a benchmark value)")

@@ -54,6 +54,7 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
                         max_host_mem_bytes, device, leeway_gpu_mem_bytes, leeway_host_mem_bytes, dt: DTypePolicy,
                         lora, hw_cost, force_saved_act_level, head_chunk_size, verbose, min_chunk_size,
                         max_chunk_size, ws: Optional[WorkingSetConfig], world_size, rank, dp_shard, tp, ep,
+                        opt_state: str = "auto",
                         process_group, model_dir=None, arch_key=None, host_backend=None,
                         plan_only: bool = False) -> ActiveModel:
     builder = _BLOCK_BUILDERS.get(arch_key) if arch_key else None
@@ -82,11 +83,14 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
             max_global_batch_tokens=max_global_batch_tokens, max_gpu_mem_bytes=max_gpu_mem_bytes,
             max_host_mem_bytes=max_host_mem_bytes, leeway_gpu_mem_bytes=leeway_gpu_mem_bytes,
             leeway_host_mem_bytes=leeway_host_mem_bytes, hw=hw, world_size=world_size, tp=tp, ep=ep, shard=dp_shard,
+            opt_state=opt_state,
             layers_are_local=True,
             min_chunk_size=min_chunk_size, max_chunk_size=max_chunk_size,
             force_saved_act_level=force_saved_act_level, verbose=verbose)
     if plan_only:
         return ws
+    if getattr(ws, "head_chunk_size", None):
+        head.head_chunk_size = min(head.head_chunk_size, ws.head_chunk_size)     # the planner needed the room
     dp = tp_group = ep_group = None
     if world_size > 1:
         from .parallel import build_parallel
@@ -173,6 +177,7 @@ def from_dims(dims: Mapping, *, arch: str = "llama", optimizer, max_seq_len: int
               min_chunk_size: Optional[int] = None, max_chunk_size: Optional[int] = None, moe_backend=None,
               working_set: Optional[WorkingSetConfig] = None, world_size: int = 1, rank: int = 0,
               dp_shard: Optional[str] = None, tp: int = 1, ep: int = 1, process_group=None, host_backend=None,
+              opt_state: str = "auto",
               init_weights: bool = True, init_on_device: bool = False, plan_only: bool = False) -> ActiveModel:
     """Build an :class:`ActiveModel` from a dims dict with deterministic random weights; bypasses HF entirely.
 
@@ -193,7 +198,7 @@ def from_dims(dims: Mapping, *, arch: str = "llama", optimizer, max_seq_len: int
                              dt=dt, lora=lora, hw_cost=hw_cost, force_saved_act_level=force_saved_act_level,
                              head_chunk_size=head_chunk_size, verbose=verbose, min_chunk_size=min_chunk_size,
                              max_chunk_size=max_chunk_size, ws=working_set, world_size=world_size, rank=rank,
-                             dp_shard=dp_shard, tp=tp, ep=ep, process_group=process_group, arch_key=arch,
+                             dp_shard=dp_shard, tp=tp, ep=ep, opt_state=opt_state, process_group=process_group, arch_key=arch,
                              host_backend=host_backend, plan_only=plan_only)
     if plan_only:
         return am
@@ -223,6 +228,7 @@ def from_pretrained(model_path: str, *, optimizer, max_seq_len: int, max_global_
                     enable_multimodal="auto", freeze_modality_encoders: bool = True,
                     working_set: Optional[WorkingSetConfig] = None, world_size: int = 1, rank: int = 0,
                     dp_shard: Optional[str] = None, tp: int = 1, ep: int = 1, process_group=None,
+                    opt_state: str = "auto",
                     host_backend=None) -> ActiveModel:
     """Build a configured :class:`ActiveModel` for an HF model directory and load its safetensors weights."""
     with open(os.path.join(model_path, "config.json")) as f:
@@ -242,7 +248,7 @@ def from_pretrained(model_path: str, *, optimizer, max_seq_len: int, max_global_
                              dt=dt, lora=lora, hw_cost=hw_cost, force_saved_act_level=force_saved_act_level,
                              head_chunk_size=head_chunk_size, verbose=verbose, min_chunk_size=min_chunk_size,
                              max_chunk_size=max_chunk_size, ws=working_set, world_size=world_size, rank=rank,
-                             dp_shard=dp_shard, tp=tp, ep=ep, process_group=process_group, model_dir=model_path,
+                             dp_shard=dp_shard, tp=tp, ep=ep, opt_state=opt_state, process_group=process_group, model_dir=model_path,
                              arch_key=archs[0], host_backend=host_backend)
     if enable_multimodal not in (False, None) and ("vision_config" in hf):
         from .nn.multimodal_input import attach_multimodal_input

@@ -1,7 +1,8 @@
 """Small, self-terminating kernel cases for profiling one kernel at a time.
 
     python -m flextrain_b200.bench.kernel_cases gemm_fwd|gemm_dgrad|gemm_wgrad|rmsnorm_bwd|softmax_ce|attn_fwd|attn_bwd|
-                                                  gdn_fwd|gdn_bwd|gdn_long_fwd
+                                                  attn_fwd_one_tile|attn_fwd_32k|attn_bwd_32k|gdn_fwd|gdn_bwd|
+                                                  gdn_long_fwd|rope
 
 Each case holds a few hundred MB on the device (inputs larger than the 126 MB L2), runs three warm-up launches and
 ten timed launches with CUDA events, and prints achieved TFLOP/s or GB/s.  They are the commands behind the
@@ -77,15 +78,18 @@ def main(case: str) -> None:
             d_o = torch.randn_like(o)
             ms = _time(lambda: la.gdn_bwd(q, kk, v, g, beta, cu, None, fin, r, d_o))
             print(f"{case}: {S} x {L} tokens, HV={HV} dk={dk} dv={dv}  {ms:.3f} ms  {2.2 * fl / ms / 1e9:.1f} TFLOP/s fp32")
-    elif case in ("attn_fwd", "attn_bwd"):
-        S, B, H, KV, hd = 1024, 16, 32, 8, 128
+    elif case in ("attn_fwd", "attn_bwd", "attn_fwd_one_tile", "attn_fwd_32k", "attn_bwd_32k"):
+        S, B, H, KV, hd = (32768, 1, 32, 8, 128) if case.endswith("_32k") else (1024, 16, 32, 8, 128)
+        if case == "attn_fwd_one_tile":          # the one-query-tile-per-CTA forward kernel, for an A/B on the same GPU
+            k.load("attention").ftb_attn_set_two_tiles(0)
+            case = "attn_fwd"
         T = S * B
         q = torch.randn(T, H, hd, device=dev, dtype=bf)
         kk = torch.randn(T, KV, hd, device=dev, dtype=bf)
         v = torch.randn(T, KV, hd, device=dev, dtype=bf)
         cu = torch.arange(0, T + 1, S, device=dev, dtype=torch.int32)
         fl = 4.0 * B * H * S * S * hd / 2
-        if case == "attn_fwd":
+        if case.startswith("attn_fwd"):
             ms = _time(lambda: ops.attention_fwd(q, kk, v, cu, cu, S, S, scale=hd ** -0.5))
             print(f"{case}: B={B} S={S} H={H} KV={KV} hd={hd}  {ms:.3f} ms  {fl / ms / 1e9:.0f} TFLOP/s (causal)")
         else:
@@ -93,6 +97,13 @@ def main(case: str) -> None:
             do = torch.randn_like(o)
             ms = _time(lambda: ops.attention_bwd(do, q, kk, v, o, lse, cu, cu, S, S, scale=hd ** -0.5))
             print(f"{case}: B={B} S={S} H={H} KV={KV} hd={hd}  {ms:.3f} ms  {2.5 * fl / ms / 1e9:.0f} TFLOP/s (causal)")
+    elif case == "rope":
+        T, H, hd = 16384, 32, 128
+        x = torch.randn(T, H, hd, device=dev, dtype=bf)
+        pos = torch.arange(T, device=dev, dtype=torch.int32) % 1024
+        inv = ops.rope_inv_freq(hd, 5e5).to(dev)
+        ms = _time(lambda: ops.rope(x, pos, inv))
+        print(f"{case}: T={T} H={H} hd={hd}  {ms:.3f} ms  {2.0 * T * H * hd * 2 / ms / 1e6:.0f} GB/s (1 read + 1 write)")
     else:
         raise SystemExit(f"unknown case {case}")
     print("device error words:", k.device_error_words())

@@ -114,6 +114,12 @@ class TransmissionScheduler:
         out = np.empty(T, dtype=np.int32)
         total = float(compute_ms.sum())
         tick = max(self.tick_ms, total / float(1 << 20))
+        # the table is T x window bytes: coarsen the tick until it stays under ~48 MB
+        if n_slots >= 2 and T > n_slots:
+            c = np.concatenate([[0.0], np.cumsum(compute_ms)])
+            span = n_slots - 2
+            window_ms = float((c[span + 1:] - c[1:T - span + 1]).max()) if span < T else total
+            tick = max(tick, window_ms * T / 48e6)
         p = lambda a, t: a.ctypes.data_as(ctypes.POINTER(t))
         best = self.lib.ftb_dp_solve(ctypes.c_int(T), ctypes.c_int(k), ctypes.c_int(n_slots),
                                      p(compute_ms, ctypes.c_double), p(dur_ms, ctypes.c_double),

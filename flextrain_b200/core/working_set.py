@@ -25,7 +25,10 @@ from .save_level import HardwareCost
 from .sizing import divisors
 
 GiB = 1 << 30
-SHARD_MODES = ("none", "opt", "opt+grad", "opt+grad+param")
+# Data-parallel state sharding.  There is no "optimizer state only" level: the gradient reduction of the peer-memory
+# path IS a reduce-scatter into an fp32 shard, so sharded gradients come for free with a sharded optimizer.
+SHARD_MODES = ("none", "opt+grad", "opt+grad+param")
+RING_DEPTHS = (2, 3, 4)       # GPU slots of a state class whose master copy lives in host memory
 
 
 @dataclass
@@ -55,6 +58,7 @@ class WorkingSetConfig:
     est_pcie_ms: float = 0.0
     est_nvlink_ms: float = 0.0
     healthy: bool = True
+    head_chunk_size: Optional[int] = None      # set when the planner had to shrink the head's logits micro-chunk
     report: List[str] = field(default_factory=list)
 
     @classmethod
@@ -85,6 +89,9 @@ class ModelMemory:
     act_tier_per_token: List[List[int]]  # [layer][tier]
     fwd_flops_per_token: float
     head_flops_per_token: float
+    # share of the layers' forward FLOPs that has to be recomputed in backward when only tiers <= k were saved,
+    # from every layer's ``ComputeCost.avoided_recompute_flops`` (index k; the last entry is 0: everything saved)
+    recompute_frac: List[float] = field(default_factory=lambda: [0.0])
 
     @property
     def n_layers(self) -> int:
@@ -95,22 +102,28 @@ def baseline_model_memory(layers, embed, head, optimizer, probe_tokens: int = 40
     from ..engine.buffers import LayerBuffers
     lp, lm, lg, lo, af, at = [], [], [], [], [], []
     flops = 0.0
+    n_tiers = max((l.activation_schema.max_tier for l in layers), default=0) + 1
+    redo = [0.0] * n_tiers
     for layer in layers:
         lb = LayerBuffers(layer.param_spec, optimizer)
         lp.append(lb.p_bytes); lm.append(lb.m_bytes); lg.append(lb.g_bytes); lo.append(lb.o_bytes)
         sch = layer.activation_schema
         af.append(math.ceil(sch.device_size_bytes(probe_tokens) / probe_tokens))
         at.append([math.ceil(sch.home_size_bytes(probe_tokens, L) / probe_tokens) for L in range(sch.max_tier + 1)])
-        flops += layer.compute_cost(probe_tokens, probe_tokens / 2).total_fwd_flops / probe_tokens
+        cost = layer.compute_cost(probe_tokens, probe_tokens / 2)
+        flops += cost.total_fwd_flops / probe_tokens
+        av = cost.avoided_recompute_flops
+        for k in range(n_tiers):
+            redo[k] += (av[-1] - av[min(k, len(av) - 1)]) / probe_tokens
     eh = 0
     for blk in (embed, head):
         lb = LayerBuffers(blk.param_spec, optimizer)
         eh += lb.p_bytes + lb.g_bytes + lb.o_bytes
     head_flops = 2.0 * head.vocab_size * head.d_model
-    return ModelMemory(lp, lm, lg, lo, eh, af, at, flops, head_flops)
+    return ModelMemory(lp, lm, lg, lo, eh, af, at, flops, head_flops, [r / max(flops, 1e-9) for r in redo])
 
 
-def _workspace_bytes(layers, head, chunk: int, act_bytes: int = 2) -> int:
+def _workspace_bytes(layers, head, chunk: int, act_bytes: int = 2, head_rows: Optional[int] = None) -> int:
     """Transient GPU memory while one chunk is in flight: residual stream in/out, the widest projection output
     and its gradient, attention workspace, and one head micro-chunk of logits."""
     widest = 0
@@ -127,7 +140,7 @@ def _workspace_bytes(layers, head, chunk: int, act_bytes: int = 2) -> int:
             w = max(w, 3 * c.moe.expert_dim * c.moe.top_k + 3 * c.moe.shared_dim)
         widest = max(widest, w)
     per_tok = (4 * d + 2 * widest) * act_bytes
-    head_ws = min(chunk, head.head_chunk_size) * head.vocab_size * act_bytes * 2
+    head_ws = min(chunk, head_rows or head.head_chunk_size) * head.vocab_size * act_bytes * 2
     return chunk * per_tok + head_ws + (256 << 20)
 
 
@@ -137,8 +150,13 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
                                  hw: Optional[HardwareCost] = None, world_size: int = 1, tp: int = 1, ep: int = 1,
                                  shard: Optional[str] = None, min_chunk_size: Optional[int] = None,
                                  max_chunk_size: Optional[int] = None, force_saved_act_level: Optional[int] = None,
-                                 verbose: bool = False, layers_are_local: bool = False) -> WorkingSetConfig:
+                                 verbose: bool = False, layers_are_local: bool = False,
+                                 opt_state: str = "auto") -> WorkingSetConfig:
+    """``opt_state``: ``"auto"`` lets the search decide where optimizer state lives, ``"host"`` restricts it to the
+    layouts that stream the state through pinned host memory, ``"device"`` to the ones that keep it in HBM."""
     hw = hw or HardwareCost()
+    if opt_state not in ("auto", "host", "device"):
+        raise ValueError(f"opt_state must be auto, host or device, not {opt_state!r}")
     log: List[str] = []
 
     def say(msg: str):
@@ -180,112 +198,160 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
     full_tok = sum(mm.act_full_per_token)
     tier0_tok = sum(a[0] for a in mm.act_tier_per_token)
 
+    n_tiers = len(mm.recompute_frac)
+    tier_tok = [sum(a[min(k, len(a) - 1)] for a in mm.act_tier_per_token) for k in range(n_tiers)]
+
+    # Host residency of a state class is what a single GPU does when HBM is short.  With several ranks the states are
+    # sharded over the ranks first; the one multi-rank layout that also streams optimizer state through the host is a
+    # model-parallel group that spans the job (each rank updates its own slice of every matrix from pinned host state,
+    # layer by layer) or the library-collective back end (which keeps the single-GPU rings).
+    import os as _os
+    multi_host_ok = world_size > 1 and (tp_group == world_size or _os.environ.get("FTB_DP_BACKEND") == "collective")
+
     best: Optional[Tuple[float, WorkingSetConfig]] = None
     # With dp > 1 the engine always reduce-scatters gradients into an fp32 shard and runs the optimizer on the
-    # shard ("opt+grad"); "opt+grad+param" additionally keeps only 1/dp of the parameters between uses.
+    # shard ("opt+grad"); "opt+grad+param" additionally defers the parameter all-gather to first use.
     modes = [shard] if shard is not None else (("opt+grad", "opt+grad+param") if dp > 1 else ("none",))
-    for mode in modes:
-        # "opt+grad+param" defers the parameter all-gather to the first GEMM that uses a layer (it overlaps the forward
-        # pass instead of closing the optimizer step); the arena stays full size, so memory equals "opt+grad"
-        p = P
-        # local bf16 gradients stay full-size while rounds accumulate; the reduced fp32 shard is 2x bytes / dp
-        g = G + (2 * G / dp if (dp > 1 and mode != "none") else 0)
-        o = O / dp if mode != "none" else O
-        # optimizer update traffic through HBM (params r/w, grads r, state r/w)
-        opt_ms = hw.bytes_to_ms((2 * P + G + 2 * O) / (dp if mode != "none" else 1), "hbm")
-        # NVLink traffic per step and rank: gradient reduce-scatter (+ all-gather of the reduced grads when not
-        # sharded), parameter all-gather after the sharded update, parameter all-gathers per pass when sharded
-        nv = 0.0
-        if dp > 1:
-            f = (dp - 1) / dp
-            nv += G * f                                   # reduce-scatter
-            nv += (G * f) if mode == "none" else (P * f)  # all-gather grads, or updated params
-            if mode == "opt+grad+param":
-                nv += 0.0                                 # same bytes as the eager push, moved under the forward pass
-        nv_ms = hw.bytes_to_ms(nv, "nvlink")
-        # ---- residency search: all resident, else offload opt → grads → params (least-touched first)
-        # Host residency of model states is the single-GPU mechanism; with more than one rank the states are sharded /
-        # partitioned over the ranks instead and stay in HBM (only activations may still go to the host).
-        for resid in (("all", "opt_host", "opt_grad_host", "all_host") if world_size == 1 else ("all",)):
-            n_p = n_g = n_o = None
-            host_state = 0.0
-            pcie = 0.0
-            states = p + g + o
-            if resid != "all":
-                n_o = 2
-                states = p + g + 2 * max(mm.layer_opt) / tp
-                host_state += o
-                pcie += 2 * o
-            if resid in ("opt_grad_host", "all_host"):
-                n_g = 2
-                states -= g - 2 * max(mm.layer_grad) / tp
-                host_state += g
-            if resid == "all_host":
-                n_p = 2
-                states -= p - 2 * max(mm.layer_param) / tp
-                host_state += p
-            if host_state > host_budget:
-                say(f"[{mode}/{resid}] host-bound: states need {host_state / GiB:.1f} GiB of host")
-                continue
-            fixed = states + mm.embed_head_resident
-            for chunk in _chunk_candidates(batch_per_rank, max_seq_len, lo_chunk, hi_chunk):
-                ws_b = _workspace_bytes(layers, head, chunk)
-                room = gpu_budget - fixed - ws_b
-                if room < full_tok * chunk / max(L, 1):
-                    continue
-                # rounds that fit entirely on the device at full tier
-                r_dev = int(room // max(full_tok, 1))
-                rounds_pcie = 0.0
-                # a sequence is never split across rounds: a round holds at least one whole (longest) sequence
-                seq_floor = min(batch_per_rank, math.ceil(max_seq_len / chunk) * chunk)
-                if r_dev >= max(seq_floor, min(batch_per_rank, max(chunk, tokens_compute_bound if resid == "all_host"
-                                                                  else chunk))):
-                    round_tokens = _round_down_to_multiple(min(r_dev, batch_per_rank), chunk, batch_per_rank)
-                    n_slots = 1 << 30
-                    host_act = 0
-                    recompute = 0.0
-                else:
-                    # activations go to the host at (at least) tier 0; the DP solver picks the tiers per round
-                    host_room = host_budget - host_state
-                    r_host = int(host_room // max(tier0_tok, 1))
-                    round_tokens = _round_down_to_multiple(min(batch_per_rank, max(r_host, 0)), chunk, batch_per_rank)
-                    if round_tokens < max(chunk, seq_floor):
-                        continue
-                    n_slots = int(room // max(full_tok * chunk / max(L, 1), 1))
-                    if n_slots < 2:
-                        continue
-                    host_act = int(min(host_room, full_tok * round_tokens))
-                    rounds_pcie = 2.0 * tier0_tok * batch_per_rank
-                    recompute = 0.35      # tiers above 0 that PCIe cannot carry are recomputed (≈ 1/3 of forward)
-                n_rounds = math.ceil(batch_per_rank / round_tokens)
-                if resid == "all_host":
-                    pcie_total = pcie + rounds_pcie + n_rounds * 2 * (p + g)
-                elif resid == "opt_grad_host":
-                    pcie_total = pcie + rounds_pcie + n_rounds * 2 * g
-                else:
-                    pcie_total = pcie + rounds_pcie
-                pcie_ms = hw.bytes_to_ms(pcie_total / 2, "pcie")      # both directions run concurrently
-                comp = compute_ms_step * (1 + recompute / 3)
-                # transfers overlap compute; what exceeds it is exposed
-                est = max(comp, pcie_ms, nv_ms) + 0.05 * (pcie_ms + nv_ms) + opt_ms + 2.0 * n_rounds
-                cfg = WorkingSetConfig(
-                    target_round_tokens=round_tokens, max_chunk_size=chunk,
-                    max_training_chunks=2 * math.ceil(round_tokens / chunk) + 2,
-                    max_total_round_tokens=max(round_tokens, max_seq_len), target_num_rounds=n_rounds,
-                    n_gpu_layers=n_p, n_gpu_grads=n_g, n_gpu_opt_layers=n_o, n_gpu_act_slots=n_slots,
-                    gpu_act_buffer_size=int(room), host_act_buffer_size=host_act, max_seq_len=max_seq_len,
-                    max_global_batch_tokens=max_global_batch_tokens, world_size=world_size, shard=mode, tp=tp_group, ep=ep,
-                    est_step_ms=est, est_compute_ms=comp, est_pcie_ms=pcie_ms, est_nvlink_ms=nv_ms,
-                    healthy=(n_slots >= 2))
-                say(f"[{mode}/{resid}] chunk {chunk} round {round_tokens} x{n_rounds} slots "
-                    f"{'all' if n_slots >= 1 << 29 else n_slots}: est {est:.0f} ms "
-                    f"(compute {comp:.0f}, pcie {pcie_ms:.0f}, nvlink {nv_ms:.0f})")
-                key = (est, SHARD_MODES.index(mode), -chunk)
-                if best is None or key < best[0]:
-                    best = (key, cfg)
-                break       # largest feasible chunk for this (mode, residency)
-            if best is not None and best[1].shard == mode and resid == "all" and best[1].n_gpu_opt_layers is None:
-                break       # fully resident fits: no reason to look at offloaded variants of this mode
+    # The head holds one micro-chunk of logits (rows x vocab) at a time.  On a tight budget that block is the largest
+    # transient: if nothing fits with the configured micro-chunk the search is repeated with 1024 rows (the
+    # reference's default, flextrain/nn/head.py:202-207) and the plan carries the smaller value.
+    head_rows_options = [None] + ([1024] if head.head_chunk_size > 1024 else [])
+    for head_rows in head_rows_options:
+      if best is not None:
+          break
+      for mode in modes:
+          # "opt+grad+param" defers the parameter all-gather to the first GEMM that uses a layer (it overlaps the forward
+          # pass instead of closing the optimizer step); the arena stays full size, so memory equals "opt+grad"
+          p = P
+          # local bf16 gradients stay full-size while rounds accumulate; the reduced fp32 shard is 2x bytes / dp
+          g = G + (2 * G / dp if (dp > 1 and mode != "none") else 0)
+          o = O / dp if mode != "none" else O
+          # optimizer update traffic through HBM (params r/w, grads r, state r/w)
+          opt_ms = hw.bytes_to_ms((2 * P + G + 2 * O) / (dp if mode != "none" else 1), "hbm")
+          # NVLink traffic per step and rank: gradient reduce-scatter (+ all-gather of the reduced grads when not
+          # sharded), parameter all-gather after the sharded update
+          nv = 0.0
+          if dp > 1:
+              f = (dp - 1) / dp
+              nv += G * f                                   # reduce-scatter
+              nv += (G * f) if mode == "none" else (P * f)  # all-gather grads, or updated params
+          nv_ms = hw.bytes_to_ms(nv, "nvlink")
+          # "opt+grad+param": the all-gather runs under the next forward pass, not at the end of the step
+          nv_exposed = 0.5 * nv_ms if mode == "opt+grad+param" else nv_ms
+          if world_size == 1:
+              residencies = ("all", "opt_host", "opt_grad_host", "all_host")
+          else:
+              residencies = ("all", "opt_host") if multi_host_ok else ("all",)
+        if opt_state == "host":
+            residencies = tuple(r for r in residencies if r != "all")
+            if not residencies:
+                raise ValueError("optimizer state in host memory needs one GPU, a model-parallel group that spans "
+                                 "the job, or the library-collective data-parallel back end")
+        elif opt_state == "device":
+            residencies = ("all",)
+          for resid in residencies:
+              for depth in ((0,) if resid == "all" else RING_DEPTHS):
+                  n_p = n_g = n_o = None
+                  host_state = 0.0
+                  pcie = 0.0
+                  states = p + g + o
+                  if resid != "all":
+                      n_o = depth
+                      states = p + g + depth * max(mm.layer_opt) / tp
+                      host_state += o
+                      pcie += 2 * o
+                  if resid in ("opt_grad_host", "all_host"):
+                      n_g = depth
+                      states -= g - depth * max(mm.layer_grad) / tp
+                      host_state += g
+                  if resid == "all_host":
+                      n_p = depth
+                      states -= p - depth * max(mm.layer_param) / tp
+                      host_state += p
+                  if host_state > host_budget:
+                      say(f"[{mode}/{resid}] host-bound: states need {host_state / GiB:.1f} GiB of host")
+                      break
+                  fixed = states + mm.embed_head_resident
+                  # a deeper ring hides more of a layer's transfer behind the layers before it
+                  exposure = 0.05 if depth == 0 else 0.10 / (depth - 1)
+                  for chunk in _chunk_candidates(batch_per_rank, max_seq_len, lo_chunk, hi_chunk):
+                      ws_b = _workspace_bytes(layers, head, chunk, head_rows=head_rows)
+                      room = gpu_budget - fixed - ws_b
+                      if room < full_tok * chunk / max(L, 1):
+                          continue
+                      # rounds that fit entirely on the device at full tier
+                      r_dev = int(room // max(full_tok, 1))
+                      rounds_pcie = 0.0
+                      # a sequence is never split across rounds: a round holds at least one whole (longest) sequence
+                      seq_floor = min(batch_per_rank, math.ceil(max_seq_len / chunk) * chunk)
+                      tier_note = ""
+                      if r_dev >= max(seq_floor, min(batch_per_rank, max(chunk, tokens_compute_bound if resid == "all_host"
+                                                                        else chunk))):
+                          round_tokens = _round_down_to_multiple(min(r_dev, batch_per_rank), chunk, batch_per_rank)
+                          n_slots = 1 << 30
+                          host_act = 0
+                          recompute = 0.0
+                      else:
+                          # activations go to the host; the DP solver picks the tier per (layer, chunk) at run time.  For
+                          # the estimate take the uniform tier with the smallest max(compute + recompute, PCIe): a higher
+                          # tier moves more bytes but recomputes less (``recompute_frac`` from the layers' ComputeCost).
+                          host_room = host_budget - host_state
+                          n_slots = int(room // max(full_tok * chunk / max(L, 1), 1))
+                          if n_slots < 2:
+                              continue
+                          pick = None
+                          for k in range(n_tiers):
+                              r_host = int(host_room // max(tier_tok[k], 1))
+                              rt = _round_down_to_multiple(min(batch_per_rank, max(r_host, 0)), chunk, batch_per_rank)
+                              if rt < max(chunk, seq_floor):
+                                  continue
+                              pc = 2.0 * tier_tok[k] * batch_per_rank
+                              # forward is 1/3 of a step's layer FLOPs: recomputing a share r of it costs r/3 of the step
+                              t_k = max(compute_ms_step * (1 + mm.recompute_frac[k] / 3), hw.bytes_to_ms(pc / 2, "pcie"))
+                              if pick is None or t_k < pick[0]:
+                                  pick = (t_k, k, rt, pc)
+                          if pick is None:
+                              continue
+                          _, k_sel, round_tokens, rounds_pcie = pick
+                          recompute = mm.recompute_frac[k_sel]
+                          host_act = int(min(host_room, tier_tok[-1] * round_tokens))
+                          tier_note = f" tier<={k_sel}"
+                      n_rounds = math.ceil(batch_per_rank / round_tokens)
+                      if resid == "all_host":
+                          pcie_total = pcie + rounds_pcie + n_rounds * 2 * (p + g)
+                      elif resid == "opt_grad_host":
+                          pcie_total = pcie + rounds_pcie + n_rounds * 2 * g
+                      else:
+                          pcie_total = pcie + rounds_pcie
+                      pcie_ms = hw.bytes_to_ms(pcie_total / 2, "pcie")      # both directions run concurrently
+                      # optimizer state streams through the host while the update runs, after the last backward: that
+                      # part of the traffic has no forward / backward compute to hide behind
+                      opt_stream_ms = hw.bytes_to_ms(pcie / 2, "pcie") if resid != "all" else 0.0
+                      # chunk-dependent efficiency: GEMMs below the arithmetic-intensity knee run memory-bound, and every
+                      # (layer, chunk) pays its launches
+                      n_chunks_step = math.ceil(batch_per_rank / chunk)
+                      comp = compute_ms_step * (1 + recompute / 3) * (1 + ai_floor / (4.0 * chunk)) \
+                          + 0.12 * n_chunks_step * L
+                      # transfers overlap compute; what exceeds it is exposed
+                      est = max(comp, pcie_ms - opt_stream_ms, nv_exposed) + exposure * pcie_ms + 0.05 * nv_ms \
+                          + max(opt_ms, opt_stream_ms) + 2.0 * n_rounds
+                      cfg = WorkingSetConfig(
+                          target_round_tokens=round_tokens, max_chunk_size=chunk,
+                          max_training_chunks=2 * math.ceil(round_tokens / chunk) + 2,
+                          max_total_round_tokens=max(round_tokens, max_seq_len), target_num_rounds=n_rounds,
+                          n_gpu_layers=n_p, n_gpu_grads=n_g, n_gpu_opt_layers=n_o, n_gpu_act_slots=n_slots,
+                          gpu_act_buffer_size=int(room), host_act_buffer_size=host_act, max_seq_len=max_seq_len,
+                          max_global_batch_tokens=max_global_batch_tokens, world_size=world_size, shard=mode, tp=tp_group,
+                          ep=ep, est_step_ms=est, est_compute_ms=comp, est_pcie_ms=pcie_ms, est_nvlink_ms=nv_ms,
+                          healthy=(n_slots >= 2), head_chunk_size=head_rows)
+                      say(f"[{mode}/{resid}{'' if depth == 0 else '/ring ' + str(depth)}] chunk {chunk} round "
+                          f"{round_tokens} x{n_rounds} slots {'all' if n_slots >= 1 << 29 else n_slots}{tier_note}: est "
+                          f"{est:.0f} ms (compute {comp:.0f}, pcie {pcie_ms:.0f}, nvlink {nv_ms:.0f})")
+                      key = (est, SHARD_MODES.index(mode), -chunk)
+                      if best is None or key < best[0]:
+                          best = (key, cfg)
+              if best is not None and best[1].shard == mode and resid == "all" and best[1].n_gpu_opt_layers is None:
+                  break       # fully resident fits: no reason to look at offloaded variants of this mode
     if best is None:
         need = (P + G + O) / max(dp, 1) + mm.embed_head_resident
         if need > gpu_budget and (P + G + O) > host_budget:

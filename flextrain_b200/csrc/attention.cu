@@ -331,6 +331,325 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   }
 }
 
+
+// =====================================================================================================
+// Forward, two query tiles per CTA (the default).  A CTA owns 256 consecutive query rows of one head as two 128-row
+// tiles that share every K / V tile (half the K / V traffic of one tile per CTA) and run in ping-pong: while the four
+// softmax warps of one tile work on their scores, the tensor core computes the other tile's S = Q·Kᵀ or O += P·V.
+//   warps 0-3   softmax of tile 0        warps 4-7   softmax of tile 1
+//   warp 8      TMA producer (Q tiles once, K / V through two-stage rings, no multicast)
+//   warp 9      MMA issuer
+// Tensor memory: S0 | S1 | O0 | O1 (4 x 128 columns).  The probabilities never touch shared memory: a softmax thread
+// writes its row of P as packed bf16 over the first 64 columns of its S (tcgen05.st; the write position trails the
+// read position of the second pass) and the P·V MMA takes its A operand from tensor memory.  O accumulates in tensor
+// memory across the K / V tiles; it is rescaled only when a row maximum has grown by more than 2^8 since the last
+// rescale (the probabilities are computed against that stale maximum, so they stay below 2^8 and the final division
+// by the row sum is exact), which for real score distributions happens on the first tiles of a row only.
+// =====================================================================================================
+constexpr int FA2_THREADS = 320;
+constexpr float FA2_RESCALE_LOG2 = 8.0f;
+
+__device__ __forceinline__ bool find_tile2(const int* cu_q, int num_seqs, int tile, int& seq, int& q0) {
+  int acc = 0;
+  for (int s = 0; s < num_seqs; ++s) {
+    const int len = cu_q[s + 1] - cu_q[s];
+    const int nt = (len + 2 * TQ - 1) / (2 * TQ);
+    if (tile < acc + nt) {
+      seq = s;
+      q0 = (tile - acc) * 2 * TQ;
+      return true;
+    }
+    acc += nt;
+  }
+  return false;
+}
+
+template <int HD, bool CAP>
+__global__ void __launch_bounds__(FA2_THREADS, 1)
+fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+  constexpr int KB = HD / 64;
+  constexpr int Q_BYTES = TQ * HD * 2;
+  constexpr int KV_BYTES = TK * HD * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                         // 2 tiles
+  uint8_t* sK = sQ + 2 * Q_BYTES;             // 2 stages
+  uint8_t* sV = sK + 2 * KV_BYTES;            // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * KV_BYTES);
+  uint64_t* q_full = bars;                    // 1
+  uint64_t* k_full = bars + 1;                // 2
+  uint64_t* k_empty = bars + 3;               // 2
+  uint64_t* v_full = bars + 5;                // 2
+  uint64_t* v_empty = bars + 7;               // 2
+  uint64_t* s_full = bars + 9;                // 2 (per query tile)
+  uint64_t* p_full = bars + 11;               // 2
+  uint64_t* o_full = bars + 13;               // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int kvh = head / (p.H / p.KV);
+  int seq = 0, q0 = 0;
+  if (!find_tile2(p.cu_q, p.num_seqs, blockIdx.x, seq, q0)) return;   // uniform for the CTA: nothing allocated yet
+  const int qs = p.cu_q[seq], len_q = p.cu_q[seq + 1] - qs;
+  const int ks = p.cu_k[seq], len_k = p.cu_k[seq + 1] - ks;
+  const int off = len_k - len_q;
+  int kv_lo = (p.causal && p.window > 0) ? max(0, q0 + off - p.window + 1) : 0;
+  kv_lo = (kv_lo / TK) * TK;
+  // per query tile: live rows and K / V tiles it has to visit (scalars: no indexed local arrays)
+  const int rows0 = max(0, min(TQ, len_q - q0)), rows1 = max(0, min(TQ, len_q - q0 - TQ));
+  const int hi0 = rows0 == 0 ? 0 : (p.causal ? min(len_k, q0 + rows0 + off) : len_k);
+  const int hi1 = rows1 == 0 ? 0 : (p.causal ? min(len_k, q0 + TQ + rows1 + off) : len_k);
+  const int nt0 = hi0 > kv_lo ? (hi0 - kv_lo + TK - 1) / TK : 0;
+  const int nt1 = hi1 > kv_lo ? (hi1 - kv_lo + TK - 1) / TK : 0;
+  const int n_max = max(nt0, nt1);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&o_full[i], 1);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------------- TMA producer
+    if (lane == 0 && n_max > 0) {
+      const int nq = rows1 > 0 ? 2 : 1;
+      mbar_expect_tx(q_full, nq * Q_BYTES);
+      for (int t = 0; t < nq; ++t)
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_3d(sQ + t * Q_BYTES + kb * (TQ * 128), &tmQ, q_full, kb * 64, head, qs + q0 + t * TQ);
+      bool ok = true;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int key0 = ks + kv_lo + j * TK;
+        if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, 140))) break;
+        mbar_expect_tx(&k_full[st], KV_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_3d(sK + st * KV_BYTES + kb * (TK * 128), &tmK, &k_full[st], kb * 64, kvh, key0);
+        if (!(ok = mbar_wait(&v_empty[st], ph ^ 1, abort_flag, 141))) break;
+        mbar_expect_tx(&v_full[st], KV_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_3d(sV + st * KV_BYTES + kb * (TK * 128), &tmV, &v_full[st], kb * 64, kvh, key0);
+      }
+    }
+  } else if (warp == 9) {
+    // --------------------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_max > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(TQ, TK, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(TQ, HD, 0, 1);
+      bool ok = mbar_wait(q_full, 0, abort_flag, 150);
+      // S_t(j) = Q_t · K_jᵀ into the tile's score columns (they are free: the tile's P·V of j-1 was issued before)
+      auto issue_s = [&](int t, int j) {
+        const uint32_t aQ = smem_u32(sQ + t * Q_BYTES), aK = smem_u32(sK + (j & 1) * KV_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16(tmem_base + t * TK, make_smem_desc(aQ + kb * (TQ * 128) + kk * 32, 16, 1024),
+                     make_smem_desc(aK + kb * (TK * 128) + kk * 32, 16, 1024), idesc_s, (kb | kk) != 0);
+        umma_commit(&s_full[t]);
+      };
+      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, 151);
+      if (ok) {
+        tc_fence_after();
+        if (nt0 > 0) issue_s(0, 0);
+        if (nt1 > 0) issue_s(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const bool more = j + 1 < n_max;
+        if (!(ok = mbar_wait(&v_full[st], ph, abort_flag, 152))) break;
+        if (more && !(ok = mbar_wait(&k_full[st ^ 1], ((j + 1) >> 1) & 1, abort_flag, 153))) break;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int nt = t ? nt1 : nt0;
+          if (!ok || j >= nt) continue;
+          if (!(ok = mbar_wait(&p_full[t], j & 1, abort_flag, 154 + t))) break;
+          tc_fence_after();
+          const uint32_t aV = smem_u32(sV + st * KV_BYTES);
+#pragma unroll
+          for (int s2 = 0; s2 < TK / 16; ++s2)       // P (tensor memory, 8 columns per 16 keys) times V
+            umma_f16_ts(tmem_base + 256 + t * HD, tmem_base + t * TK + s2 * 8,
+                        make_smem_desc(aV + s2 * (16 * 128), TK * 128, 1024), idesc_pv, (j | s2) != 0);
+          umma_commit(&o_full[t]);
+          if (j + 1 < nt) issue_s(t, j + 1);
+        }
+        if (!ok) break;
+        umma_commit(&v_empty[st]);
+        if (more) umma_commit(&k_empty[st ^ 1]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + output of tile t
+    const int t = warp >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;                 // query row inside the tile
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t tm_S = tmem_base + t * TK + lane_base;
+    const uint32_t tm_O = tmem_base + 256 + t * HD + lane_base;
+    const float c = p.scale * 1.4426950408889634f;  // scores are kept in log2 units
+    const float cap2 = p.softcap * 1.4426950408889634f;
+    const float soc = CAP ? p.scale / p.softcap : 0.f;
+    const int n_tiles = t ? nt1 : nt0;
+    const int rows = t ? rows1 : rows0;
+    const int tq0 = q0 + t * TQ;
+    const int qi = tq0 + r + off;                   // last key this row may see (causal)
+    float m = -INFINITY, l = 0.f;                   // m: the maximum the probabilities are currently scaled against
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int key0 = kv_lo + j * TK;
+      if (!(ok = mbar_wait(&s_full[t], j & 1, abort_flag, 160 + t))) break;
+      tc_fence_after();
+      // The whole score row of this tile goes into registers with one wait (four loads in flight), so tensor memory
+      // is read once.  Only tiles that cross the causal diagonal, the window edge or the end of the keys pay for
+      // masking (a masked score becomes -inf, whose exponential is 0); interior tiles run the bare
+      // max / multiply-add / exp2 / pack stream.
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) tmem_ld_32x32(tm_S + q4 * 32, sv[q4]);
+      tmem_ld_wait();
+      const bool edge = (key0 + TK > len_k) ||
+                        (p.causal && (key0 + TK - 1 > tq0 + off || (p.window > 0 && key0 <= tq0 + TQ - 1 + off - p.window)));
+      if (edge) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kj = key0 + q4 * 32 + i;
+            bool keep = kj < len_k;
+            if (p.causal) keep = keep && (kj <= qi) && (p.window <= 0 || kj > qi - p.window);
+            if (!keep) sv[q4][i] = 0xff800000u;          // -inf
+          }
+      }
+      float mx4[4];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float a = __uint_as_float(sv[q4][0]);
+#pragma unroll
+        for (int i = 1; i < 32; ++i) a = fmaxf(a, __uint_as_float(sv[q4][i]));
+        mx4[q4] = a;
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float m_new;
+      if constexpr (CAP) m_new = fmaxf(m, mx == -INFINITY ? mx : cap2 * tanh_fast(mx * soc));
+      else m_new = fmaxf(m, mx * c);
+      if (j == 0) {
+        m = m_new;
+      } else {
+        const bool grow = m_new > m + FA2_RESCALE_LOG2;
+        if (__any_sync(0xffffffffu, grow)) {
+          // the tile's previous P·V must have landed before its output rows are rescaled in tensor memory
+          if (!(ok = mbar_wait(&o_full[t], (j - 1) & 1, abort_flag, 162 + t))) break;
+          tc_fence_after();
+          const float alpha = grow ? exp2f(m - m_new) : 1.f;
+#pragma unroll 1
+          for (int cb = 0; cb < HD; cb += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tm_O + cb, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(tm_O + cb, v);
+          }
+          tmem_st_wait();
+          l *= alpha;
+          if (grow) m = m_new;
+        }
+      }
+      // probabilities against m -> packed bf16 over the first half of this tile's S columns; row sum
+      const float mref = (m == -INFINITY) ? 0.f : m;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0, p1;
+          // two textually separate forms: the plain one must stay a single multiply-add feeding the exponential
+          if constexpr (CAP) {
+            const float s0 = __uint_as_float(sv[q4][i]), s1 = __uint_as_float(sv[q4][i + 1]);
+            p0 = s0 == -INFINITY ? 0.f : exp2f(cap2 * tanh_fast(s0 * soc) - mref);
+            p1 = s1 == -INFINITY ? 0.f : exp2f(cap2 * tanh_fast(s1 * soc) - mref);
+          } else {
+            p0 = exp2f(__uint_as_float(sv[q4][i]) * c - mref);
+            p1 = exp2f(__uint_as_float(sv[q4][i + 1]) * c - mref);
+          }
+          sum4[q4] += p0 + p1;
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+          pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        tmem_st_32x16(tm_S + q4 * 16, pk);
+      }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      l += sum;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    if (ok && n_tiles > 0 && mbar_wait(&o_full[t], (n_tiles - 1) & 1, abort_flag, 164 + t)) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const size_t row = static_cast<size_t>(qs + tq0 + min(r, max(rows - 1, 0)));
+      __nv_bfloat16* dst = p.out + (row * p.H + head) * HD;
+#pragma unroll 1
+      for (int cb = 0; cb < HD; cb += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_O + cb, v);
+        tmem_ld_wait();
+        if (r < rows) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 o4;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              h2[e] = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * e]) * inv, __uint_as_float(v[i + 2 * e + 1]) * inv);
+            *reinterpret_cast<uint4*>(dst + cb + i) = o4;
+          }
+        }
+      }
+      // natural-log LSE of the scaled scores
+      if (r < rows)
+        p.lse[static_cast<size_t>(head) * p.total_q + row] = (l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    } else if (n_tiles == 0 && r < rows) {
+      // no visible key at all (cannot happen with causal bottom-right alignment, kept for completeness)
+      const size_t row = static_cast<size_t>(qs + tq0 + r);
+      __nv_bfloat16* dst = p.out + (row * p.H + head) * HD;
+      for (int i = 0; i < HD; i += 8) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0, 0, 0, 0);
+      p.lse[static_cast<size_t>(head) * p.total_q + row] = -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -379,11 +698,32 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
 }
 
+template <int HD, bool CAP>
+static int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
+                       int tiles, cudaStream_t s) {
+  constexpr int SMEM = 2 * TQ * HD * 2 + 4 * TK * HD * 2 + 256 + 1024;
+  auto kern = fa_fwd2_kernel<HD, CAP>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return -300 - static_cast<int>(e);
+    configured = true;
+  }
+  dim3 grid(tiles, p.H);
+  kern<<<grid, FA2_THREADS, SMEM, s>>>(tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
+}
+
 }  // namespace ftb
 
 using namespace ftb;
 
+static int g_fwd_two_tiles = 1;     // ftb_attn_set_two_tiles(0) selects the one-tile-per-CTA forward kernel
+
 extern "C" {
+
+void ftb_attn_set_two_tiles(int on) { g_fwd_two_tiles = on; }
 
 // q (Tq, H, hd), k / v (Tk, KV, hd) bf16 with token strides (elements) q_stride / k_stride / v_stride;
 // out (Tq, H, hd) contiguous; lse (H, Tq) fp32. cu_q / cu_k: device int32 (num_seqs + 1).
@@ -406,6 +746,14 @@ int ftb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* 
   p.cu_q = cu_q; p.cu_k = cu_k; p.num_seqs = num_seqs; p.H = H; p.KV = KV;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.total_q = total_q;
   p.scale = scale; p.softcap = softcap; p.causal = causal; p.window = window;
+  if (g_fwd_two_tiles) {
+    const int tiles2 = (total_q + 2 * TQ - 1) / (2 * TQ) + num_seqs;   // >= sum over sequences of ceil(len_q / 256)
+    if (softcap > 0.f)
+      return hd == 128 ? launch_fwd2<128, true>(tq, tk, tv, p, tiles2, stream)
+                       : launch_fwd2<64, true>(tq, tk, tv, p, tiles2, stream);
+    return hd == 128 ? launch_fwd2<128, false>(tq, tk, tv, p, tiles2, stream)
+                     : launch_fwd2<64, false>(tq, tk, tv, p, tiles2, stream);
+  }
   if (softcap > 0.f)
     return hd == 128 ? launch_fwd<128, true>(tq, tk, tv, p, max_tiles, stream)
                      : launch_fwd<64, true>(tq, tk, tv, p, max_tiles, stream);
@@ -468,8 +816,13 @@ __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ dout, long do_
   if (lane == 0) delta[(size_t)h * T + t] = s;
 }
 
+// Backward thread layout: warp 0 TMA, warp 1 MMA, warps 2-9 softmax / drain.  Warps w and w + 4 share a tensor-memory
+// lane quadrant (rows) and split the columns of every tile between them, so two warps per scheduler work on the
+// P / dS tile instead of one.
+constexpr int FAB_THREADS = 320;
+
 template <int HD, bool CAP>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FAB_THREADS, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
   constexpr int KB = HD / 64;
@@ -513,7 +866,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(dq_empty, 4); mbar_init(stage_bar, 4);
+    mbar_init(pds_full, 8); mbar_init(dq_full, 1); mbar_init(dq_empty, 8); mbar_init(stage_bar, 8);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
@@ -598,6 +951,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;               // which half of the columns this warp owns
     const int r = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const float c = p.scale * 1.4426950408889634f;
@@ -615,26 +969,38 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const float lse2 = vq ? p.lse[static_cast<size_t>(h) * p.total_q + grow] * 1.4426950408889634f : INFINITY;
       const float dl = vq ? p.delta[static_cast<size_t>(h) * p.total_q + grow] : 0.f;
       const int qi = i + off;
+      // a tile needs masking only if it touches the end of the queries / keys, the causal diagonal or the window edge
+      const bool edge = (qt + 128 > len_q) || (k0 + 128 > len_k) ||
+                        (p.causal && (k0 + 127 > qt + off || (p.window > 0 && k0 <= qt + 127 + off - p.window)));
       if (!(ok = mbar_wait(sdp_full, ph, abort_flag, 230))) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int cb = 0; cb < 128; cb += 32) {
+      for (int cb = half * 64; cb < half * 64 + 64; cb += 32) {
         uint32_t vs[32], vd[32];
         tmem_ld_32x32(tm_S + lane_base + cb, vs);
         tmem_ld_32x32(tm_dP + lane_base + cb, vd);
         tmem_ld_wait();
         float pr[32], ds[32];
+        if (edge || capped) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int kj = k0 + cb + e;
-          bool keep = vq && kj < len_k;
-          if (p.causal) keep = keep && (kj <= qi) && (p.window <= 0 || kj > qi - p.window);
-          const float raw = __uint_as_float(vs[e]);
-          const float th = capped ? tanh_fast(raw * soc) : 0.f;
-          const float pe = keep ? exp2f((capped ? cap2 * th : raw * c) - lse2) : 0.f;
-          pr[e] = pe;
-          // d(cap * tanh(scale * s / cap)) / ds = scale * (1 - tanh^2)
-          ds[e] = pe * (__uint_as_float(vd[e]) - dl) * p.scale * (1.f - th * th);
+          for (int e = 0; e < 32; ++e) {
+            const int kj = k0 + cb + e;
+            bool keep = vq && kj < len_k;
+            if (p.causal) keep = keep && (kj <= qi) && (p.window <= 0 || kj > qi - p.window);
+            const float raw = __uint_as_float(vs[e]);
+            const float th = capped ? tanh_fast(raw * soc) : 0.f;
+            const float pe = keep ? exp2f((capped ? cap2 * th : raw * c) - lse2) : 0.f;
+            pr[e] = pe;
+            // d(cap * tanh(scale * s / cap)) / ds = scale * (1 - tanh^2)
+            ds[e] = pe * (__uint_as_float(vd[e]) - dl) * p.scale * (1.f - th * th);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float pe = exp2f(__uint_as_float(vs[e]) * c - lse2);
+            pr[e] = pe;
+            ds[e] = pe * (__uint_as_float(vd[e]) - dl) * p.scale;
+          }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -659,10 +1025,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tc_fence_after();
       // dQ tile: TMEM -> registers -> shared (XOR-swizzled so both the row-per-lane writes and the column-per-lane
       // reads are conflict free) -> fp32 atomics that a warp issues on 32 consecutive addresses (one line each).
-      // The P / dS tiles are dead once dq_full has fired, so their 64 KB hold the fp32 tile.
+      // The P / dS tiles are dead once dq_full has fired, so their 64 KB hold the fp32 tile.  Each warp drains its own
+      // half of the columns of its 32 rows.
       float* sq = reinterpret_cast<float*>(sP);
+      constexpr int HC = HD / 2;
 #pragma unroll 1
-      for (int cb = 0; cb < HD; cb += 32) {
+      for (int cb = half * HC; cb < half * HC + HC; cb += 32) {
         uint32_t v[32];
         tmem_ld_32x32(tm_dQ + lane_base + cb, v);
         tmem_ld_wait();
@@ -678,20 +1046,21 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         float* dq_row = p.dq_acc + ((static_cast<size_t>(qs + ii)) * p.H + h) * HD;
         const float* srow = sq + (quad * 32 + rr) * HD;
 #pragma unroll
-        for (int cb = 0; cb < HD; cb += 32) atomicAdd(dq_row + cb + lane, srow[cb + (lane ^ rr)]);
+        for (int cb = half * HC; cb < half * HC + HC; cb += 32) atomicAdd(dq_row + cb + lane, srow[cb + (lane ^ rr)]);
       }
-      // all four warps must be done with the staging area before anyone writes the next P / dS (bounded wait)
+      // all eight warps must be done with the staging area before anyone writes the next P / dS (bounded wait)
       __syncwarp();
       if (lane == 0) mbar_arrive(stage_bar);
       if (!(ok = mbar_wait(stage_bar, ph, abort_flag, 232))) break;
     }
     // dK / dV of this key tile (thread = key row)
+    constexpr int HC2 = HD / 2;
     if (r < kr) {
       const size_t row = static_cast<size_t>(ks + k0 + r);
       __nv_bfloat16* dk_row = p.dk + (row * p.KV + kvh) * HD;
       __nv_bfloat16* dv_row = p.dv + (row * p.KV + kvh) * HD;
       if (n_iter == 0 || !ok) {
-        for (int cidx = 0; cidx < HD; cidx += 8) {
+        for (int cidx = half * HC2; cidx < half * HC2 + HC2; cidx += 8) {
           *reinterpret_cast<uint4*>(dk_row + cidx) = make_uint4(0, 0, 0, 0);
           *reinterpret_cast<uint4*>(dv_row + cidx) = make_uint4(0, 0, 0, 0);
         }
@@ -703,7 +1072,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       __nv_bfloat16* dk_row = p.dk + (row * p.KV + kvh) * HD;
       __nv_bfloat16* dv_row = p.dv + (row * p.KV + kvh) * HD;
 #pragma unroll 1
-      for (int cb = 0; cb < HD; cb += 32) {
+      for (int cb = half * HC2; cb < half * HC2 + HC2; cb += 32) {
         uint32_t a[32], b[32];
         tmem_ld_32x32(tm_dV + lane_base + cb, a);
         tmem_ld_32x32(tm_dK + lane_base + cb, b);
@@ -746,7 +1115,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUten
     configured = true;
   }
   dim3 grid(tiles, p.KV);
-  kern<<<grid, FA_THREADS, SMEM, s>>>(tq, tdo, tk, tv, p);
+  kern<<<grid, FAB_THREADS, SMEM, s>>>(tq, tdo, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
 }

@@ -15,7 +15,12 @@
 //
 // State s = ticks the channel stays busy after c_t (s >= 0).  Choosing L: finish = s + dur;
 // feasible iff finish <= deadline_t = c_{t+N-2} - c_t; next state s' = max(0, finish - compute[t+1]).
-// The window is bounded by the largest deadline, so the table is T x (W+1).
+// The window is bounded by the largest finite deadline (a backlog beyond it can never be paid off) plus what the
+// deadline-free tail can queue, so the table is T x (W+1) BYTES: only the chosen tier is stored per cell.  The
+// predecessor of a cell follows from the transition (s = s' - dur + gap) except for the cells that collapse to
+// s' = 0, which keep their arg-max source per task.  A round of a thousand tasks with a window of ten thousand
+// ticks needs ~10 MB (the reference re-centres a sliding buffer with memmove for the same purpose,
+// transmission_scheduler.c:25-209).
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
@@ -89,7 +94,8 @@ extern "C" {
 // Number of bytes of scratch the solver will allocate for (T, window) — exposed so callers can
 // refuse absurd problems up front (counterpart of compute_buf_size in the reference).
 int64_t ftb_dp_buf_size(int T, int window_ticks) {
-  return static_cast<int64_t>(T) * (window_ticks + 1) * 5 + 2 * static_cast<int64_t>(window_ticks + 1) * 4;
+  return static_cast<int64_t>(T) * (window_ticks + 1) + 2 * static_cast<int64_t>(window_ticks + 1) * 4 +
+         static_cast<int64_t>(T) * 8;
 }
 
 // compute_ms[T]; dur_ms[T*k]; value[T*k]; pinned[T] (0/1); n_slots = N; tick_ms > 0.
@@ -123,22 +129,35 @@ double ftb_dp_solve(int T, int k, int n_slots, const double* compute_ms, const d
     else deadline[t] = std::numeric_limits<int64_t>::max() / 4;
     if (deadline[t] < std::numeric_limits<int64_t>::max() / 8) W = std::max(W, deadline[t]);
   }
-  // tasks with no finite deadline can still queue behind others; cap their backlog by the total runtime
-  const int64_t total = cend(T - 1);
-  W = std::max<int64_t>(W, 1);
-  W = std::min<int64_t>(std::max(W, std::min<int64_t>(total, 1 << 20)), 1 << 22);
+  // tasks with no finite deadline (the tail of the round) can still queue behind each other: their backlog is at
+  // most the sum of their longest transfers
+  {
+    int64_t tail = 0;
+    for (int t = 0; t < T; ++t) {
+      if (pinned[t] || deadline[t] < std::numeric_limits<int64_t>::max() / 8) continue;
+      double dmax = 0;
+      for (int L = 0; L < valid_k[t]; ++L) dmax = std::max(dmax, dur_ms[t * k + L]);
+      tail += static_cast<int64_t>(std::ceil(dmax / tick_ms));
+    }
+    W = std::max<int64_t>(W, tail);
+  }
+  W = std::min<int64_t>(std::max<int64_t>(W, 1), 1 << 22);
   const int S = static_cast<int>(W) + 1;
 
   std::vector<float> cur(S, NEG), nxt(S, NEG);
   std::vector<uint8_t> choice(static_cast<size_t>(T) * S, 255);
-  std::vector<int32_t> prev(static_cast<size_t>(T) * S, -1);
+  std::vector<int32_t> prev(2 * static_cast<size_t>(S), -1);   // scratch rows for the relax kernels (not kept per task)
+  std::vector<int32_t> prev0(T, -1);                            // source state of the cell s' = 0, per task
+  std::vector<int64_t> gaps(T, 0);
   cur[0] = 0.f;
 
   for (int t = 0; t < T; ++t) {
     std::fill(nxt.begin(), nxt.end(), NEG);
     uint8_t* ch = choice.data() + static_cast<size_t>(t) * S;
-    int32_t* pv = prev.data() + static_cast<size_t>(t) * S;
+    int32_t* pv = prev.data();
+    pv[0] = -1;
     const int64_t gap = (t + 1 < T) ? (cend(t + 1) - cend(t)) : 0;   // compute time of task t+1 in ticks
+    gaps[t] = gap;
     if (pinned[t]) {
       double best = 0;
       for (int L = 0; L < valid_k[t]; ++L) best = std::max(best, value[t * k + L]);
@@ -172,6 +191,7 @@ double ftb_dp_solve(int T, int k, int n_slots, const double* compute_ms, const d
         relax(cur.data(), nxt.data(), ch, pv, lo, hi, static_cast<int>(sh), v, static_cast<uint8_t>(L), avx2);
       }
     }
+    prev0[t] = pv[0];
     cur.swap(nxt);
   }
   // best terminal state
@@ -180,8 +200,16 @@ double ftb_dp_solve(int T, int k, int n_slots, const double* compute_ms, const d
   if (arg < 0 || best <= NEG / 2) return -1.0;
   for (int t = T - 1; t >= 0; --t) {
     const uint8_t L = choice[static_cast<size_t>(t) * S + arg];
+    if (L == 255) return -1.0;
     out_choice[t] = (L == 254) ? -1 : static_cast<int32_t>(L);
-    arg = prev[static_cast<size_t>(t) * S + arg];
+    if (arg == 0) {
+      arg = prev0[t];                       // several source states collapse to 0: the arg-max one was recorded
+    } else {
+      // s' = s + dur - gap (pinned: s' = s - gap), so the source follows from the chosen tier
+      const int64_t d = (L == 254) ? 0 : static_cast<int64_t>(std::ceil(dur_ms[t * k + L] / tick_ms - 1e-9));
+      const int64_t src = static_cast<int64_t>(arg) - d + gaps[t];
+      arg = (src < 0 || src >= S) ? -1 : static_cast<int>(src);
+    }
     if (arg < 0) return -1.0;
   }
   return static_cast<double>(best);

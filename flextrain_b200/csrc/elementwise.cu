@@ -361,6 +361,44 @@ __global__ void rope_kernel(const bf16* __restrict__ x, long in_stride, bf16* __
   }
 }
 
+// Full-rotary fast path (one position axis, rot == hd, hd % 16 == 0, 16-byte aligned rows): one block per token.
+// The hd/2 (sin, cos) pairs of the token are computed once into shared memory and reused by every head; each thread
+// then rotates 8 pairs of one head with two 16-byte loads and two 16-byte stores.
+__global__ void rope_full_vec_kernel(const bf16* __restrict__ x, long in_stride, bf16* __restrict__ out, long out_stride,
+                                     const int* __restrict__ pos, const float* __restrict__ inv_freq, int T, int H,
+                                     int hd, int inverse) {
+  extern __shared__ float sc[];              // [half] sin, [half] cos
+  const int t = blockIdx.x;
+  const int half = hd >> 1;
+  const float pf = (float)pos[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    sincosf(pf * inv_freq[i], &sn, &cs);
+    sc[i] = inverse ? -sn : sn;
+    sc[half + i] = cs;
+  }
+  __syncthreads();
+  const int per_head = half >> 3;            // 8-pair chunks per head
+  const bf16* xr = x + (size_t)t * in_stride;
+  bf16* orow = out + (size_t)t * out_stride;
+  for (int idx = threadIdx.x; idx < H * per_head; idx += blockDim.x) {
+    const int h = idx / per_head, c = (idx - h * per_head) << 3;
+    const uint4 ua = *reinterpret_cast<const uint4*>(xr + (size_t)h * hd + c);
+    const uint4 ub = *reinterpret_cast<const uint4*>(xr + (size_t)h * hd + half + c);
+    float a[8], b[8], ra[8], rb[8];
+    unpack8(ua, a);
+    unpack8(ub, b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float sn = sc[c + e], cs = sc[half + c + e];
+      ra[e] = a[e] * cs - b[e] * sn;
+      rb[e] = b[e] * cs + a[e] * sn;
+    }
+    *reinterpret_cast<uint4*>(orow + (size_t)h * hd + c) = pack8(ra);
+    *reinterpret_cast<uint4*>(orow + (size_t)h * hd + half + c) = pack8(rb);
+  }
+}
+
 // ------------------------------------------------------------------------ SwiGLU / GeGLU
 __device__ __forceinline__ void act_and_grad(float g, int kind, float& a, float& da) {
   if (kind == 0) {
@@ -867,6 +905,14 @@ int ftb_rope(const void* x, long in_stride, void* out, long out_stride, const in
              int T, int H, int hd, int half_rot, int inverse, int pos_stride, int sec_h, int sec_w, cudaStream_t s) {
   if (T == 0) return 0;
   if (hd % 2 || 2 * half_rot > hd) return -2;
+  if (pos_stride == 1 && 2 * half_rot == hd && hd % 16 == 0 && in_stride % 8 == 0 && out_stride % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    int thr = H * (hd / 16);
+    thr = thr > 256 ? 256 : ((thr + 31) / 32) * 32;
+    rope_full_vec_kernel<<<T, thr, hd * sizeof(float), s>>>((const bf16*)x, in_stride, (bf16*)out, out_stride, pos,
+                                                            inv_freq, T, H, hd, inverse);
+    CHECK_LAUNCH();
+  }
   int threads = H * (hd / 2);
   threads = threads > 512 ? 512 : ((threads + 31) / 32) * 32;
   rope_kernel<<<T, threads, 0, s>>>((const bf16*)x, in_stride, (bf16*)out, out_stride, pos, inv_freq, T, H, hd,

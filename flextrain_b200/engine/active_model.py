@@ -99,6 +99,10 @@ class ActiveModel:
             host_act_bytes=ws.host_act_buffer_size, verbose=verbose, **(dp.buffer_kwargs() if dp is not None else {}))
         self.streams = StreamBundle.create(device, secondary=False)
         self.events = EventBook(self.streams)
+        # offloaded activations: how many (layer, chunk) slots ahead of the one in backward are being copied back
+        import os as _os
+        self.act_prefetch_depth = int(_os.environ.get("FTB_ACT_PREFETCH", "2"))
+        self._prefetched: Dict = {}
         self._ce = None                 # C++ copy engine, created on first host<->device transfer
         self._ce_key = 0
         self._scheduler = None
@@ -474,6 +478,14 @@ class ActiveModel:
         if not bm.params_resident:
             # the forward pass left the last n_p layers in the ring; everything else is re-fetched backwards
             pass
+        # Backward order of the (layer, chunk) slots, for the look-ahead fetch of offloaded activations: while chunk i
+        # computes, the host->device copy of the slots of the next ``act_prefetch_depth`` chunks in this order runs on
+        # the inbound stream (flextrain/engine/active_model.py:2036-2098 walks backwards the same way and refills the
+        # ring slot that was just freed).
+        order = [(l, c) for l in range(nL - 1, -1, -1) for g in sorted(groups, reverse=True) for c in reversed(groups[g])]
+        pos = {lc: i for i, lc in enumerate(order)}
+        depth = self.act_prefetch_depth if bm.host_act is not None else 0
+        self._prefetched = {}
         for l in range(nL - 1, -1, -1):
             layer = self.layers[l]
             with _nvtx(f"Layer {l}"):
@@ -495,6 +507,9 @@ class ActiveModel:
                     lin_d = {}
                     for c in reversed(chunk_ids):
                         meta = metas[c]
+                        i = pos[(l, c)]
+                        for nl, nc in order[i + 1: i + 1 + depth]:       # start the copies of the chunks that follow
+                            self._issue_fetch(slots, nl, nc)
                         slot = self._fetch_slot(slots.pop((l, c)), l, c)
                         ctx = self._ctx(ctx_base, meta)
                         if layer.gdn is not None:
@@ -524,6 +539,7 @@ class ActiveModel:
                         self._prefetch_params_bwd(nxt, after=("b", l))
                 if self.dp is not None and last_round:
                     self.dp.on_layer_grads_ready(l)
+        self._prefetched = {}
 
     def _prefetch_params_bwd(self, l: int, after=None):
         bm, st, ev = self.buffers, self.streams, self.events
@@ -553,17 +569,32 @@ class ActiveModel:
     def _peek_slot(self, slot):
         return slot
 
-    def _fetch_slot(self, slot: ActivationSlot, l: int, c: int) -> ActivationSlot:
-        """Bring an offloaded slot back into HBM at its saved level (stale higher tiers stay invisible)."""
-        bm, st, ev = self.buffers, self.streams, self.events
-        if slot.buffer is None or slot.buffer.device == self.device:
-            return slot
+    def _issue_fetch(self, slots, l: int, c: int) -> None:
+        """Start the host->device copy of an offloaded slot on the inbound stream without making compute wait for it
+        (look-ahead).  The device copy is parked in ``_prefetched`` until :meth:`_fetch_slot` picks it up; the host slot
+        stays in ``slots`` (the K/V window refresh and the recurrent-state hand-over of Gated DeltaNet read from it)."""
+        slot = slots.get((l, c))
+        if slot is None or (l, c) in self._prefetched or slot.buffer is None or slot.buffer.device == self.device:
+            return
+        st, ev = self.streams, self.events
         with st.use(st.inbound):
             ev.act_out.wait((l, c), st.inbound)
             pairs = []
             dev = fetch_home(slot, None, self.device, copy_fn=lambda d, s_: pairs.append((d, s_)))
             self._engine_copies(pairs, 0)
             ev.act_in.record((l, c), st.inbound)
+        self._prefetched[(l, c)] = dev
+
+    def _fetch_slot(self, slot: ActivationSlot, l: int, c: int) -> ActivationSlot:
+        """Bring an offloaded slot back into HBM at its saved level (stale higher tiers stay invisible).  If the copy
+        was started ahead of time by :meth:`_issue_fetch` only its completion is awaited."""
+        st, ev = self.streams, self.events
+        if slot.buffer is None or slot.buffer.device == self.device:
+            return slot
+        dev = self._prefetched.pop((l, c), None)
+        if dev is None:
+            self._issue_fetch({(l, c): slot}, l, c)
+            dev = self._prefetched.pop((l, c))
         ev.act_in.wait((l, c), st.compute)
         if st.is_cuda:
             # allocated while the inbound stream was current, consumed on the compute stream: the allocator must not
@@ -577,6 +608,7 @@ class ActiveModel:
         clear the dK/dV accumulators (flextrain/engine/active_model.py:1941-2034)."""
         w = self.buffers.kv_window
         st = self.streams
+        live = 0
         with st.use(st.inbound_fwd_context):
             st.inbound_fwd_context.wait_stream(st.compute)
             for c in chunk_ids:
@@ -584,13 +616,19 @@ class ActiveModel:
                 if not (m.has_prior or any(m.has_more_chunks)):
                     continue
                 P, L = m.prior_lens[0], m.seq_lens[0]
-                s = slots[(l, c)]
-                if self.events.act_out.has((l, c)):       # saved K/V live in the host arena: wait for their arrival
-                    self.events.act_out.wait((l, c), st.inbound_fwd_context)
+                s = self._prefetched.get((l, c))
+                if s is not None:                         # already on its way back to HBM: take K/V from that copy
+                    self.events.act_in.wait((l, c), st.inbound_fwd_context)
+                else:
+                    s = slots[(l, c)]
+                    if self.events.act_out.has((l, c)):   # saved K/V live in the host arena: wait for their arrival
+                        self.events.act_out.wait((l, c), st.inbound_fwd_context)
                 w.k[P:P + L].copy_(s._t["xk"], non_blocking=True)
                 w.v[P:P + L].copy_(s._t["xv"], non_blocking=True)
-            w.dk.zero_()
-            w.dv.zero_()
+                live = max(live, P + L)
+            # only the keys this group can see collect dK / dV: clear that range, not the whole window
+            w.dk[:live].zero_()
+            w.dv[:live].zero_()
         st.compute.wait_stream(st.inbound_fwd_context)
 
     # =============================================================================== step

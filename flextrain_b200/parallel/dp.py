@@ -160,16 +160,40 @@ class P2PDataParallel(_Base):
         n = max(off, 8)
         f32 = lambda: torch.zeros(n, dtype=torch.float32, device=self.device)
         self.grad_shard, self.m, self.v = f32(), f32(), f32()
-        # tensors owned by this rank alone keep an ordinary local optimizer with fp32 state
+        # tensors owned by this rank alone (its slice of every tensor- / expert-parallel matrix) keep an ordinary local
+        # optimizer with fp32 state.  When the planner could not fit that state into HBM (``n_gpu_opt_layers`` set: a
+        # 70B model over 8 tensor-parallel ranks carries 70 GB of it per rank) it lives in pinned host memory, one
+        # flat buffer per unit, and streams through ``opt_ring`` device buffers during ``step()``.
         self.local_names: Dict[object, List[str]] = {}
         self.local_state: Dict[object, Dict[str, torch.Tensor]] = {}
+        self.opt_on_host = getattr(am.ws, "n_gpu_opt_layers", None) is not None
+        self._state_layout: Dict[object, List] = {}
+        self._state_flat: Dict[object, torch.Tensor] = {}
         for key in keys:
             names = self.local_part_names(lbs[key].spec)
-            if names:
-                self.local_names[key] = names
-                self.local_state[key] = {
-                    s.key: torch.zeros(s.shape, dtype=torch.float32, device=self.device)
-                    for s in am.optimizer.state_specs(lbs[key].spec) if s.param in names}
+            if not names:
+                continue
+            self.local_names[key] = names
+            specs = [s for s in am.optimizer.state_specs(lbs[key].spec) if s.param in names]
+            if not self.opt_on_host:
+                self.local_state[key] = {s.key: torch.zeros(s.shape, dtype=torch.float32, device=self.device)
+                                         for s in specs}
+                continue
+            lay, n = [], 0
+            for s in specs:
+                cnt = 1
+                for d in s.shape:
+                    cnt *= d
+                lay.append((s.key, n, cnt, tuple(s.shape)))
+                n += (cnt + 63) // 64 * 64
+            flat = bm.host.alloc(max(n, 1) * 4).view(torch.float32)
+            flat.zero_()
+            self._state_layout[key], self._state_flat[key] = lay, flat
+            self.local_state[key] = {k2: flat[o:o + c].view(shp) for k2, o, c, shp in lay}    # host views (checkpoints)
+        if self.opt_on_host and self._state_flat:
+            depth = max(2, int(am.ws.n_gpu_opt_layers))
+            biggest = max(f.numel() for f in self._state_flat.values())
+            self.opt_ring = [torch.empty(biggest, dtype=torch.float32, device=self.device) for _ in range(depth)]
         # deferred parameter all-gather ("opt+grad+param"): bf16 segments of attention layers are gathered by the
         # layer's first GEMM; everything else (norm weights, embedding, head, other layer kinds) is pushed eagerly
         self.defer = getattr(am.ws, "shard", "") == "opt+grad+param"
@@ -269,7 +293,9 @@ class P2PDataParallel(_Base):
                     ops._count()
             if deferred:
                 self._stale.add(key)
-        if self.local_names:
+        if self.local_names and self.opt_on_host:
+            self._step_local_streamed(am, opt, step)
+        elif self.local_names:
             cs.wait_stream(am.streams.compute)
             with torch.cuda.stream(cs):
                 for key, names in self.local_names.items():
@@ -279,6 +305,46 @@ class P2PDataParallel(_Base):
         self.group.signal_wait(self.barrier_slot, self.group.next_epoch(), cs)
         am.streams.compute.wait_stream(cs)
         return 0
+
+    def _step_local_streamed(self, am, opt, step: int) -> None:
+        """Update this rank's own slices with their optimizer state streaming through the host: unit k's state is
+        copied into ring slot ``k % depth`` on the inbound stream while unit k-1 is updated on the comm stream and
+        unit k-2 is written back on the outbound stream (one coalesced copy per unit and direction; the single-GPU
+        pattern of flextrain/engine/active_model.py:428-658 applied to a model-parallel rank)."""
+        st, bm, cs = am.streams, am.buffers, self.comm_stream
+        keys = list(self.local_names)
+        depth = len(self.opt_ring)
+        cs.wait_stream(st.compute)
+        st.inbound.wait_stream(st.compute)
+        loaded = [torch.cuda.Event() for _ in keys]
+        updated = [torch.cuda.Event() for _ in keys]
+        stored = [torch.cuda.Event() for _ in keys]
+
+        def fetch(i: int) -> None:
+            flat = self._state_flat[keys[i]]
+            with torch.cuda.stream(st.inbound):
+                if i >= depth:
+                    st.inbound.wait_event(stored[i - depth])          # the slot's previous tenant is back on the host
+                self.opt_ring[i % depth][: flat.numel()].copy_(flat, non_blocking=True)
+                loaded[i].record(st.inbound)
+
+        for i in range(min(depth - 1, len(keys))):
+            fetch(i)
+        for i, key in enumerate(keys):
+            if i + depth - 1 < len(keys):
+                fetch(i + depth - 1)
+            dev = self.opt_ring[i % depth]
+            views = {k2: dev[o:o + c].view(shp) for k2, o, c, shp in self._state_layout[key]}
+            cs.wait_event(loaded[i])
+            with torch.cuda.stream(cs):
+                opt.step(bm.layers[key].spec, bm.params(key), bm.grads(key), views, step, only=set(self.local_names[key]))
+                updated[i].record(cs)
+            with torch.cuda.stream(st.outbound):
+                st.outbound.wait_event(updated[i])
+                flat = self._state_flat[key]
+                flat.copy_(dev[: flat.numel()], non_blocking=True)
+                stored[i].record(st.outbound)
+        cs.wait_stream(st.outbound)
 
     def first_gemm(self, layer: int, x: torch.Tensor, w: torch.Tensor):
         """``x @ w.T`` for the first projection of ``layer`` in a step, fused with the all-gather of the layer's

@@ -8,6 +8,8 @@ and reports the differences.  ``tp_ragged``: as ``tp`` with sequences of uneven 
 chunk), so chunk token counts are not multiples of the shard width and the scheduler has to pad them.
 ``ep_ragged``: as ``ep`` with uneven sequences split unevenly over the ranks, so the ranks' chunks differ in length
 and one rank has more rounds and more chunks than the other (it is padded with filler chunks).
+``tp_hostopt``: as ``tp`` with the optimizer state kept in host memory and streamed through a two-slot device ring
+during ``step()`` (what a 70B model over 8 tensor-parallel ranks needs); results must equal the resident run.
 ``tp_grid`` / ``ep_grid``: model-parallel groups of two ranks inside a larger job (a ``dp x tp`` / ``dp x ep`` grid over
 library collectives); every group trains on its share of the batch.
 """
@@ -40,7 +42,8 @@ def build(dev, dtype, world, rank, mode, backend):
     ws = ft.WorkingSetConfig.simple(max_seq_len=seq, max_global_batch_tokens=per_rank,
                                     chunk=256 if ragged else 512,
                                     round_tokens=512 if mode == "ep_ragged" else per_rank, world_size=world,
-                                    shard="opt+grad" if world > 1 else "none")
+                                    shard="opt+grad" if world > 1 else "none",
+                                    **({"n_gpu_opt_layers": 2} if mode == "tp_hostopt" and world > 1 else {}))
     par = {"ep": mp} if mode.startswith("ep") else {"tp": mp}
     lora = dict(lora_targets="all", lora_rank=4, lora_alpha=8.0, lora_adapter_compute_dtype=dtype,
                 lora_adapter_master_dtype=dtype, lora_adapter_grad_dtype=dtype,

@@ -293,6 +293,56 @@ def test_attention_tcgen05_fwd(hd, case):
     assert float((lse - lw).abs().max()) < 2e-2
 
 
+@pytest.mark.parametrize("two_tiles", [1, 0])
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attention_fwd_growing_row_maximum(hd, two_tiles):
+    """Scores that jump by far more than 2^8 from one key tile to the next (later keys are scaled up), so the
+    two-tile kernel has to rescale the output rows it keeps in tensor memory, next to rows whose maximum does not
+    move (their keys are scaled down); also a jump of less than 2^8, which must NOT be rescaled yet give the same
+    result.  The one-tile kernel (``ftb_attn_set_two_tiles(0)``) is checked on the same data."""
+    from flextrain_b200.ops import attention_cuda as fa
+    from flextrain_b200.ops import cuda as kk
+    lib = kk.load("attention")
+    H, KV, S = 4, 2, 640
+    cu = torch.tensor([0, S, 2 * S + 70], dtype=torch.int32, device=DEV)
+    T = 2 * S + 70
+    q, k, v = _rand(T, H, hd), _rand(T, KV, hd), _rand(T, KV, hd)
+    k = k.float()
+    k[128:256] *= 1.5          # small growth: stays under the rescale threshold for most rows
+    k[256:384] *= 8.0          # large growth
+    k[384:512] *= 0.2          # maximum does not move
+    k[512:S] *= 20.0           # large growth again
+    k = k.to(torch.bfloat16)
+    lib.ftb_attn_set_two_tiles(two_tiles)
+    try:
+        o, lse = fa.fwd(q, k, v, cu, cu, S + 70, S + 70, scale=hd ** -0.5)
+    finally:
+        lib.ftb_attn_set_two_tiles(1)
+    ow, lw = ref.attention_fwd(q, k, v, cu, cu, scale=hd ** -0.5)
+    assert kk.device_error_words().get("attention", 0) == 0
+    assert _rel(o, ow) < 1e-2, (hd, two_tiles, _rel(o, ow))
+    assert float((lse - lw).abs().max()) < 3e-2
+
+
+def test_attention_fwd_one_tile_kernel_still_matches():
+    """The one-query-tile-per-CTA forward kernel stays selectable; same ragged case as the default kernel's test."""
+    from flextrain_b200.ops import attention_cuda as fa
+    from flextrain_b200.ops import cuda as kk
+    lib = kk.load("attention")
+    H, KV, hd = 8, 2, 128
+    lens_q, lens_k = [100, 37, 300, 1], [100, 200, 300, 129]
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32, device=DEV)
+    q, k, v = _rand(sum(lens_q), H, hd), _rand(sum(lens_k), KV, hd), _rand(sum(lens_k), KV, hd)
+    lib.ftb_attn_set_two_tiles(0)
+    try:
+        o, lse = fa.fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), scale=hd ** -0.5)
+    finally:
+        lib.ftb_attn_set_two_tiles(1)
+    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, scale=hd ** -0.5)
+    assert _rel(o, ow) < 1e-2 and float((lse - lw).abs().max()) < 2e-2
+
+
 @pytest.mark.parametrize("hd", [128, 64])
 @pytest.mark.parametrize("case", ["equal", "prior_ctx", "ragged", "window", "softcap"])
 def test_attention_tcgen05_bwd(hd, case):

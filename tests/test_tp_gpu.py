@@ -43,3 +43,21 @@ def test_engine_tensor_parallel_p2p(tmp_path):
     assert all(v == 0 for v in res.pop("errors").values())
     assert res["local_rows"] == 256
     assert res["loss_diff"] < 2e-2 and res["param_diff"] < 2e-2, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_engine_tensor_parallel_p2p_with_host_resident_optimizer_state(tmp_path):
+    """The peer-memory tensor-parallel path with each rank's optimizer state in pinned host memory, streamed through a
+    two-slot device ring during ``step()`` (copy in / update / copy out on three streams): same result as the run
+    that keeps the state in HBM."""
+    import json
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "tph.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "p2p", "tp_hostopt",
+           out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert all(v == 0 for v in res.pop("errors").values())
+    assert res["loss_diff"] < 2e-2 and res["param_diff"] < 2e-2, res
