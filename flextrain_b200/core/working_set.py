@@ -216,142 +216,146 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
     # transient: if nothing fits with the configured micro-chunk the search is repeated with 1024 rows (the
     # reference's default, flextrain/nn/head.py:202-207) and the plan carries the smaller value.
     head_rows_options = [None] + ([1024] if head.head_chunk_size > 1024 else [])
+
+    def search(head_rows: Optional[int]) -> None:
+        nonlocal best
+        for mode in modes:
+            # "opt+grad+param" defers the parameter all-gather to the first GEMM that uses a layer (it overlaps the forward
+            # pass instead of closing the optimizer step); the arena stays full size, so memory equals "opt+grad"
+            p = P
+            # local bf16 gradients stay full-size while rounds accumulate; the reduced fp32 shard is 2x bytes / dp
+            g = G + (2 * G / dp if (dp > 1 and mode != "none") else 0)
+            o = O / dp if mode != "none" else O
+            # optimizer update traffic through HBM (params r/w, grads r, state r/w)
+            opt_ms = hw.bytes_to_ms((2 * P + G + 2 * O) / (dp if mode != "none" else 1), "hbm")
+            # NVLink traffic per step and rank: gradient reduce-scatter (+ all-gather of the reduced grads when not
+            # sharded), parameter all-gather after the sharded update
+            nv = 0.0
+            if dp > 1:
+                f = (dp - 1) / dp
+                nv += G * f                                   # reduce-scatter
+                nv += (G * f) if mode == "none" else (P * f)  # all-gather grads, or updated params
+            nv_ms = hw.bytes_to_ms(nv, "nvlink")
+            # "opt+grad+param": the all-gather runs under the next forward pass, not at the end of the step
+            nv_exposed = 0.5 * nv_ms if mode == "opt+grad+param" else nv_ms
+            if world_size == 1:
+                residencies = ("all", "opt_host", "opt_grad_host", "all_host")
+            else:
+                residencies = ("all", "opt_host") if multi_host_ok else ("all",)
+            if opt_state == "host":
+                residencies = tuple(r for r in residencies if r != "all")
+                if not residencies:
+                    raise ValueError("optimizer state in host memory needs one GPU, a model-parallel group that spans "
+                                     "the job, or the library-collective data-parallel back end")
+            elif opt_state == "device":
+                residencies = ("all",)
+            for resid in residencies:
+                for depth in ((0,) if resid == "all" else RING_DEPTHS):
+                    n_p = n_g = n_o = None
+                    host_state = 0.0
+                    pcie = 0.0
+                    states = p + g + o
+                    if resid != "all":
+                        n_o = depth
+                        states = p + g + depth * max(mm.layer_opt) / tp
+                        host_state += o
+                        pcie += 2 * o
+                    if resid in ("opt_grad_host", "all_host"):
+                        n_g = depth
+                        states -= g - depth * max(mm.layer_grad) / tp
+                        host_state += g
+                    if resid == "all_host":
+                        n_p = depth
+                        states -= p - depth * max(mm.layer_param) / tp
+                        host_state += p
+                    if host_state > host_budget:
+                        say(f"[{mode}/{resid}] host-bound: states need {host_state / GiB:.1f} GiB of host")
+                        break
+                    fixed = states + mm.embed_head_resident
+                    # a deeper ring hides more of a layer's transfer behind the layers before it
+                    exposure = 0.05 if depth == 0 else 0.10 / (depth - 1)
+                    for chunk in _chunk_candidates(batch_per_rank, max_seq_len, lo_chunk, hi_chunk):
+                        ws_b = _workspace_bytes(layers, head, chunk, head_rows=head_rows)
+                        room = gpu_budget - fixed - ws_b
+                        if room < full_tok * chunk / max(L, 1):
+                            continue
+                        # rounds that fit entirely on the device at full tier
+                        r_dev = int(room // max(full_tok, 1))
+                        rounds_pcie = 0.0
+                        # a sequence is never split across rounds: a round holds at least one whole (longest) sequence
+                        seq_floor = min(batch_per_rank, math.ceil(max_seq_len / chunk) * chunk)
+                        tier_note = ""
+                        if r_dev >= max(seq_floor, min(batch_per_rank, max(chunk, tokens_compute_bound if resid == "all_host"
+                                                                          else chunk))):
+                            round_tokens = _round_down_to_multiple(min(r_dev, batch_per_rank), chunk, batch_per_rank)
+                            n_slots = 1 << 30
+                            host_act = 0
+                            recompute = 0.0
+                        else:
+                            # activations go to the host; the DP solver picks the tier per (layer, chunk) at run time.  For
+                            # the estimate take the uniform tier with the smallest max(compute + recompute, PCIe): a higher
+                            # tier moves more bytes but recomputes less (``recompute_frac`` from the layers' ComputeCost).
+                            host_room = host_budget - host_state
+                            n_slots = int(room // max(full_tok * chunk / max(L, 1), 1))
+                            if n_slots < 2:
+                                continue
+                            pick = None
+                            for k in range(n_tiers):
+                                r_host = int(host_room // max(tier_tok[k], 1))
+                                rt = _round_down_to_multiple(min(batch_per_rank, max(r_host, 0)), chunk, batch_per_rank)
+                                if rt < max(chunk, seq_floor):
+                                    continue
+                                pc = 2.0 * tier_tok[k] * batch_per_rank
+                                # forward is 1/3 of a step's layer FLOPs: recomputing a share r of it costs r/3 of the step
+                                t_k = max(compute_ms_step * (1 + mm.recompute_frac[k] / 3), hw.bytes_to_ms(pc / 2, "pcie"))
+                                if pick is None or t_k < pick[0]:
+                                    pick = (t_k, k, rt, pc)
+                            if pick is None:
+                                continue
+                            _, k_sel, round_tokens, rounds_pcie = pick
+                            recompute = mm.recompute_frac[k_sel]
+                            host_act = int(min(host_room, tier_tok[-1] * round_tokens))
+                            tier_note = f" tier<={k_sel}"
+                        n_rounds = math.ceil(batch_per_rank / round_tokens)
+                        if resid == "all_host":
+                            pcie_total = pcie + rounds_pcie + n_rounds * 2 * (p + g)
+                        elif resid == "opt_grad_host":
+                            pcie_total = pcie + rounds_pcie + n_rounds * 2 * g
+                        else:
+                            pcie_total = pcie + rounds_pcie
+                        pcie_ms = hw.bytes_to_ms(pcie_total / 2, "pcie")      # both directions run concurrently
+                        # optimizer state streams through the host while the update runs, after the last backward: that
+                        # part of the traffic has no forward / backward compute to hide behind
+                        opt_stream_ms = hw.bytes_to_ms(pcie / 2, "pcie") if resid != "all" else 0.0
+                        # chunk-dependent efficiency: GEMMs below the arithmetic-intensity knee run memory-bound, and every
+                        # (layer, chunk) pays its launches
+                        n_chunks_step = math.ceil(batch_per_rank / chunk)
+                        comp = compute_ms_step * (1 + recompute / 3) * (1 + ai_floor / (4.0 * chunk)) \
+                            + 0.12 * n_chunks_step * L
+                        # transfers overlap compute; what exceeds it is exposed
+                        est = max(comp, pcie_ms - opt_stream_ms, nv_exposed) + exposure * pcie_ms + 0.05 * nv_ms \
+                            + max(opt_ms, opt_stream_ms) + 2.0 * n_rounds
+                        cfg = WorkingSetConfig(
+                            target_round_tokens=round_tokens, max_chunk_size=chunk,
+                            max_training_chunks=2 * math.ceil(round_tokens / chunk) + 2,
+                            max_total_round_tokens=max(round_tokens, max_seq_len), target_num_rounds=n_rounds,
+                            n_gpu_layers=n_p, n_gpu_grads=n_g, n_gpu_opt_layers=n_o, n_gpu_act_slots=n_slots,
+                            gpu_act_buffer_size=int(room), host_act_buffer_size=host_act, max_seq_len=max_seq_len,
+                            max_global_batch_tokens=max_global_batch_tokens, world_size=world_size, shard=mode, tp=tp_group,
+                            ep=ep, est_step_ms=est, est_compute_ms=comp, est_pcie_ms=pcie_ms, est_nvlink_ms=nv_ms,
+                            healthy=(n_slots >= 2), head_chunk_size=head_rows)
+                        say(f"[{mode}/{resid}{'' if depth == 0 else '/ring ' + str(depth)}] chunk {chunk} round "
+                            f"{round_tokens} x{n_rounds} slots {'all' if n_slots >= 1 << 29 else n_slots}{tier_note}: est "
+                            f"{est:.0f} ms (compute {comp:.0f}, pcie {pcie_ms:.0f}, nvlink {nv_ms:.0f})")
+                        key = (est, SHARD_MODES.index(mode), -chunk)
+                        if best is None or key < best[0]:
+                            best = (key, cfg)
+                if best is not None and best[1].shard == mode and resid == "all" and best[1].n_gpu_opt_layers is None:
+                    break       # fully resident fits: no reason to look at offloaded variants of this mode
+
     for head_rows in head_rows_options:
-      if best is not None:
-          break
-      for mode in modes:
-          # "opt+grad+param" defers the parameter all-gather to the first GEMM that uses a layer (it overlaps the forward
-          # pass instead of closing the optimizer step); the arena stays full size, so memory equals "opt+grad"
-          p = P
-          # local bf16 gradients stay full-size while rounds accumulate; the reduced fp32 shard is 2x bytes / dp
-          g = G + (2 * G / dp if (dp > 1 and mode != "none") else 0)
-          o = O / dp if mode != "none" else O
-          # optimizer update traffic through HBM (params r/w, grads r, state r/w)
-          opt_ms = hw.bytes_to_ms((2 * P + G + 2 * O) / (dp if mode != "none" else 1), "hbm")
-          # NVLink traffic per step and rank: gradient reduce-scatter (+ all-gather of the reduced grads when not
-          # sharded), parameter all-gather after the sharded update
-          nv = 0.0
-          if dp > 1:
-              f = (dp - 1) / dp
-              nv += G * f                                   # reduce-scatter
-              nv += (G * f) if mode == "none" else (P * f)  # all-gather grads, or updated params
-          nv_ms = hw.bytes_to_ms(nv, "nvlink")
-          # "opt+grad+param": the all-gather runs under the next forward pass, not at the end of the step
-          nv_exposed = 0.5 * nv_ms if mode == "opt+grad+param" else nv_ms
-          if world_size == 1:
-              residencies = ("all", "opt_host", "opt_grad_host", "all_host")
-          else:
-              residencies = ("all", "opt_host") if multi_host_ok else ("all",)
-        if opt_state == "host":
-            residencies = tuple(r for r in residencies if r != "all")
-            if not residencies:
-                raise ValueError("optimizer state in host memory needs one GPU, a model-parallel group that spans "
-                                 "the job, or the library-collective data-parallel back end")
-        elif opt_state == "device":
-            residencies = ("all",)
-          for resid in residencies:
-              for depth in ((0,) if resid == "all" else RING_DEPTHS):
-                  n_p = n_g = n_o = None
-                  host_state = 0.0
-                  pcie = 0.0
-                  states = p + g + o
-                  if resid != "all":
-                      n_o = depth
-                      states = p + g + depth * max(mm.layer_opt) / tp
-                      host_state += o
-                      pcie += 2 * o
-                  if resid in ("opt_grad_host", "all_host"):
-                      n_g = depth
-                      states -= g - depth * max(mm.layer_grad) / tp
-                      host_state += g
-                  if resid == "all_host":
-                      n_p = depth
-                      states -= p - depth * max(mm.layer_param) / tp
-                      host_state += p
-                  if host_state > host_budget:
-                      say(f"[{mode}/{resid}] host-bound: states need {host_state / GiB:.1f} GiB of host")
-                      break
-                  fixed = states + mm.embed_head_resident
-                  # a deeper ring hides more of a layer's transfer behind the layers before it
-                  exposure = 0.05 if depth == 0 else 0.10 / (depth - 1)
-                  for chunk in _chunk_candidates(batch_per_rank, max_seq_len, lo_chunk, hi_chunk):
-                      ws_b = _workspace_bytes(layers, head, chunk, head_rows=head_rows)
-                      room = gpu_budget - fixed - ws_b
-                      if room < full_tok * chunk / max(L, 1):
-                          continue
-                      # rounds that fit entirely on the device at full tier
-                      r_dev = int(room // max(full_tok, 1))
-                      rounds_pcie = 0.0
-                      # a sequence is never split across rounds: a round holds at least one whole (longest) sequence
-                      seq_floor = min(batch_per_rank, math.ceil(max_seq_len / chunk) * chunk)
-                      tier_note = ""
-                      if r_dev >= max(seq_floor, min(batch_per_rank, max(chunk, tokens_compute_bound if resid == "all_host"
-                                                                        else chunk))):
-                          round_tokens = _round_down_to_multiple(min(r_dev, batch_per_rank), chunk, batch_per_rank)
-                          n_slots = 1 << 30
-                          host_act = 0
-                          recompute = 0.0
-                      else:
-                          # activations go to the host; the DP solver picks the tier per (layer, chunk) at run time.  For
-                          # the estimate take the uniform tier with the smallest max(compute + recompute, PCIe): a higher
-                          # tier moves more bytes but recomputes less (``recompute_frac`` from the layers' ComputeCost).
-                          host_room = host_budget - host_state
-                          n_slots = int(room // max(full_tok * chunk / max(L, 1), 1))
-                          if n_slots < 2:
-                              continue
-                          pick = None
-                          for k in range(n_tiers):
-                              r_host = int(host_room // max(tier_tok[k], 1))
-                              rt = _round_down_to_multiple(min(batch_per_rank, max(r_host, 0)), chunk, batch_per_rank)
-                              if rt < max(chunk, seq_floor):
-                                  continue
-                              pc = 2.0 * tier_tok[k] * batch_per_rank
-                              # forward is 1/3 of a step's layer FLOPs: recomputing a share r of it costs r/3 of the step
-                              t_k = max(compute_ms_step * (1 + mm.recompute_frac[k] / 3), hw.bytes_to_ms(pc / 2, "pcie"))
-                              if pick is None or t_k < pick[0]:
-                                  pick = (t_k, k, rt, pc)
-                          if pick is None:
-                              continue
-                          _, k_sel, round_tokens, rounds_pcie = pick
-                          recompute = mm.recompute_frac[k_sel]
-                          host_act = int(min(host_room, tier_tok[-1] * round_tokens))
-                          tier_note = f" tier<={k_sel}"
-                      n_rounds = math.ceil(batch_per_rank / round_tokens)
-                      if resid == "all_host":
-                          pcie_total = pcie + rounds_pcie + n_rounds * 2 * (p + g)
-                      elif resid == "opt_grad_host":
-                          pcie_total = pcie + rounds_pcie + n_rounds * 2 * g
-                      else:
-                          pcie_total = pcie + rounds_pcie
-                      pcie_ms = hw.bytes_to_ms(pcie_total / 2, "pcie")      # both directions run concurrently
-                      # optimizer state streams through the host while the update runs, after the last backward: that
-                      # part of the traffic has no forward / backward compute to hide behind
-                      opt_stream_ms = hw.bytes_to_ms(pcie / 2, "pcie") if resid != "all" else 0.0
-                      # chunk-dependent efficiency: GEMMs below the arithmetic-intensity knee run memory-bound, and every
-                      # (layer, chunk) pays its launches
-                      n_chunks_step = math.ceil(batch_per_rank / chunk)
-                      comp = compute_ms_step * (1 + recompute / 3) * (1 + ai_floor / (4.0 * chunk)) \
-                          + 0.12 * n_chunks_step * L
-                      # transfers overlap compute; what exceeds it is exposed
-                      est = max(comp, pcie_ms - opt_stream_ms, nv_exposed) + exposure * pcie_ms + 0.05 * nv_ms \
-                          + max(opt_ms, opt_stream_ms) + 2.0 * n_rounds
-                      cfg = WorkingSetConfig(
-                          target_round_tokens=round_tokens, max_chunk_size=chunk,
-                          max_training_chunks=2 * math.ceil(round_tokens / chunk) + 2,
-                          max_total_round_tokens=max(round_tokens, max_seq_len), target_num_rounds=n_rounds,
-                          n_gpu_layers=n_p, n_gpu_grads=n_g, n_gpu_opt_layers=n_o, n_gpu_act_slots=n_slots,
-                          gpu_act_buffer_size=int(room), host_act_buffer_size=host_act, max_seq_len=max_seq_len,
-                          max_global_batch_tokens=max_global_batch_tokens, world_size=world_size, shard=mode, tp=tp_group,
-                          ep=ep, est_step_ms=est, est_compute_ms=comp, est_pcie_ms=pcie_ms, est_nvlink_ms=nv_ms,
-                          healthy=(n_slots >= 2), head_chunk_size=head_rows)
-                      say(f"[{mode}/{resid}{'' if depth == 0 else '/ring ' + str(depth)}] chunk {chunk} round "
-                          f"{round_tokens} x{n_rounds} slots {'all' if n_slots >= 1 << 29 else n_slots}{tier_note}: est "
-                          f"{est:.0f} ms (compute {comp:.0f}, pcie {pcie_ms:.0f}, nvlink {nv_ms:.0f})")
-                      key = (est, SHARD_MODES.index(mode), -chunk)
-                      if best is None or key < best[0]:
-                          best = (key, cfg)
-              if best is not None and best[1].shard == mode and resid == "all" and best[1].n_gpu_opt_layers is None:
-                  break       # fully resident fits: no reason to look at offloaded variants of this mode
+        if best is None:
+            search(head_rows)
     if best is None:
         need = (P + G + O) / max(dp, 1) + mm.embed_head_resident
         if need > gpu_budget and (P + G + O) > host_budget:

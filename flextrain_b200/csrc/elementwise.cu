@@ -1057,6 +1057,49 @@ __global__ void topk_route_bwd_kernel(const float* __restrict__ dw, const bf16* 
   }
 }
 
+// Load-balance auxiliary gradient added into dlogits (flextrain/ops/_kernels/moe.py:601-646):
+//   dl[t, e] += alpha * p[t, e] * (gvec[e] - sum_j p[t, j] gvec[j]),  p = softmax(logits[t, :]),
+//   gvec[e] = counts[e] / n_slots * E / total_tokens   (the routed fractions are constants of the step).
+// One warp per token, E <= 256.
+__global__ void load_balance_bwd_kernel(const bf16* __restrict__ logits, const int* __restrict__ counts,
+                                        float* __restrict__ dl, int T, int E, float alpha, float gscale) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int lane = threadIdx.x & 31;
+  float v[8], gv[8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = lane + j * 32;
+    v[j] = e < E ? __bfloat162float(logits[(size_t)t * E + e]) : -INFINITY;
+    gv[j] = e < E ? (float)counts[e] * gscale : 0.f;
+    mx = fmaxf(mx, v[j]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { v[j] = (lane + j * 32 < E) ? __expf(v[j] - mx) : 0.f; sum += v[j]; }
+  sum = warp_sum(sum);
+  float dot = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { v[j] /= sum; dot += v[j] * gv[j]; }
+  dot = warp_sum(dot);
+  float* out = dl + (size_t)t * E;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = lane + j * 32;
+    if (e < E) out[e] += alpha * v[j] * (gv[j] - dot);
+  }
+}
+
+int ftb_load_balance_bwd(const void* logits, const int* counts, float* dl, int T, int E, float alpha, float gscale,
+                         cudaStream_t s) {
+  if (T == 0) return 0;
+  if (E > 256) return -2;
+  load_balance_bwd_kernel<<<(T + 7) / 8, 256, 0, s>>>((const bf16*)logits, counts, dl, T, E, alpha, gscale);
+  CHECK_LAUNCH();
+}
+
 int ftb_topk_route_bwd(const float* dw, const void* logits, const float* w, const int* experts, float* dl, int T, int E,
                        int K, int mode, cudaStream_t s) {
   if (T == 0) return 0;

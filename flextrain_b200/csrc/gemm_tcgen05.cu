@@ -38,6 +38,9 @@ struct GemmParams {
   int num_groups;
   const int* offsets;
   int max_tiles;     // grouped: upper bound of tiles the grid walks
+  // split-K (plain mode only): the K range is cut into split_k slices of k_per_split elements; slice s of every output
+  // tile is a work item of its own and lands in D + s * M * ldd (an fp32 workspace), to be summed by splitk_reduce.
+  int split_k, k_per_split;
   // ---- tensor-parallel fused modes (comm_mode != 0); rows are split into `world` panels of `panel_rows`
   //  1  all-gather -> GEMM: A's row panel p lives on rank p.  Warps 6-7 of every CTA pull the remote panels
   //     from the peers' staging buffers into the local one (plain peer loads, each byte crosses NVLink once),
@@ -145,8 +148,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int lane = threadIdx.x & 31;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int tiles_m = (p.M + BM - 1) / BM;
-  const int num_tiles = GROUPED == 1 ? p.max_tiles : (GROUPED == 2 ? p.num_groups * tiles_m * tiles_n : tiles_m * tiles_n);
+  const int splits = (GROUPED == 0 && COMM == 0 && p.split_k > 1) ? p.split_k : 1;
+  const int num_tiles = GROUPED == 1 ? p.max_tiles
+                                     : (GROUPED == 2 ? p.num_groups * tiles_m * tiles_n : tiles_m * tiles_n * splits);
   int k_blocks = (p.K + BK - 1) / BK;
+  // k-blocks of split slice `sp` (all slices but the last are full)
+  auto split_blocks = [&](int sp) {
+    const int lo = sp * p.k_per_split;
+    return (min(p.K, lo + p.k_per_split) - lo + BK - 1) / BK;
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -226,7 +236,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
         } else {
-          tile_coords(tile, tiles_m, tiles_n, tm, tn);
+          if (splits > 1) {
+            const int sp = tile / (tiles_m * tiles_n);
+            tile_coords(tile - sp * tiles_m * tiles_n, tiles_m, tiles_n, tm, tn);
+            k_lo = sp * p.k_per_split;
+            k_blocks = split_blocks(sp);
+          } else {
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+          }
           row0 = tm * BM;
         }
         const int col0 = tn * BN;
@@ -289,6 +306,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           k_blocks = (p.offsets[g + 1] - p.offsets[g] + BK - 1) / BK;
           if (k_blocks == 0) continue;
         }
+        if (splits > 1) k_blocks = split_blocks(tile / (tiles_m * tiles_n));
         if (!(ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, 20))) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
@@ -411,7 +429,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           d_row_shift = static_cast<long>(panel) * p.panel_rows;
         }
       } else {
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        if (splits > 1) {
+          const int sp = tile / (tiles_m * tiles_n);
+          tile_coords(tile - sp * tiles_m * tiles_n, tiles_m, tiles_n, tm, tn);
+          d_base = reinterpret_cast<char*>(p.D) + static_cast<size_t>(sp) * p.M * p.ldd * 4;   // fp32 slice
+        } else {
+          tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        }
         row0 = tm * BM;
         rows = min(BM, p.M - row0);
       }
@@ -811,6 +835,41 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParam
   return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
 }
 
+// D[m, n] = sum_s ws[s][m, n] + beta * C[m, n] + bias[n], four columns per thread (N % 8 == 0).
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, void* __restrict__ D,
+                                     const void* __restrict__ C, const float* __restrict__ bias, int M, int N, int ldd,
+                                     int ldc, float beta, int d_fp32) {
+  const long i4 = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long total4 = (long)M * N / 4;
+  if (i4 >= total4) return;
+  const long e = i4 * 4;
+  const int m = (int)(e / N), n = (int)(e - (long)m * N);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sl = 0; sl < splits; ++sl) {
+    const float4 v = *reinterpret_cast<const float4*>(ws + (size_t)sl * M * N + e);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  if (bias != nullptr) { acc.x += bias[n]; acc.y += bias[n + 1]; acc.z += bias[n + 2]; acc.w += bias[n + 3]; }
+  if (d_fp32) {
+    if (beta != 0.f) {
+      const float4 c = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(C) + (size_t)m * ldc + n);
+      acc.x += beta * c.x; acc.y += beta * c.y; acc.z += beta * c.z; acc.w += beta * c.w;
+    }
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(D) + (size_t)m * ldd + n) = acc;
+  } else {
+    if (beta != 0.f) {
+      const uint2 c = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(C) + (size_t)m * ldc + n);
+      const float2 c0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&c.x));
+      const float2 c1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&c.y));
+      acc.x += beta * c0.x; acc.y += beta * c0.y; acc.z += beta * c1.x; acc.w += beta * c1.y;
+    }
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(acc.x, acc.y);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(D) + (size_t)m * ldd + n) = o;
+  }
+}
+
 template <int BN, int STAGES, int GROUPED>
 static int dispatch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                           int grid, cudaStream_t s) {
@@ -884,7 +943,7 @@ int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const fl
     p2.alpha = alpha; p2.beta = (C != nullptr) ? beta : 0.f;
     p2.D = D; p2.C = (C != nullptr) ? C : D; p2.bias = bias; p2.d_fp32 = d_fp32;
     p2.num_groups = 0; p2.offsets = nullptr; p2.max_tiles = 0;
-    p2.comm_mode = 0; p2.world = 1; p2.rank = 0; p2.panel_rows = 0;
+    p2.comm_mode = 0; p2.world = 1; p2.rank = 0; p2.panel_rows = 0; p2.split_k = 1; p2.k_per_split = 0;
     const int tiles2 = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN2 - 1) / BN2);
     int grid2 = sm_count() & ~1;
     if (max_ctas > 0 && max_ctas < grid2) grid2 = max_ctas & ~1;
@@ -927,7 +986,7 @@ int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const fl
   p.alpha = alpha; p.beta = (C != nullptr) ? beta : 0.f;
   p.D = D; p.C = (C != nullptr) ? C : D; p.bias = bias; p.d_fp32 = d_fp32;
   p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
-  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0; p.split_k = 1; p.k_per_split = 0;
   const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
@@ -937,6 +996,69 @@ int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const fl
 }
 
 void ftb_gemm_set_two_sm(int on) { g_use_2cta = on; }
+
+// Split-K variant for small outputs with a long reduction (the rank-r LoRA gradients: M or N = r, K = tokens): the K
+// range is cut into `splits` slices so that tiles x splits work items fill the GPU instead of a handful of CTAs each
+// walking the whole K.  Every slice writes alpha * partial into its own fp32 slab of `workspace` (splits x M x N
+// floats, supplied by the caller) and a second kernel adds the slabs (+ beta * C + bias) into D in the output type:
+// fixed summation order, no atomics.  Same operand rules as ftb_gemm_bf16; one-SM kernel only.
+int ftb_gemm_bf16_splitk(const void* A, const void* B, void* D, const void* C, const float* bias, int M, int N, int K,
+                         int a_mn_major, int b_mn_major, int lda, int ldb, int ldd, int ldc, float alpha, float beta,
+                         int d_fp32, int splits, float* workspace, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || splits < 2 || workspace == nullptr) return -1;
+  if ((lda & 7) || (ldb & 7) || (N & 7) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(D) & 15))
+    return -2;
+  const int bn = (N <= 128) ? 128 : 256;
+  int kps = ((K + splits - 1) / splits + BK - 1) / BK * BK;
+  splits = (K + kps - 1) / kps;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn_major) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {BK, BM};
+    rc = make_tmap(&ta, A, 2, dims, str, box);
+  } else {
+    uint64_t dims[2] = {(uint64_t)M, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_tmap(&ta, A, 2, dims, str, box);
+  }
+  if (rc) return rc;
+  if (!b_mn_major) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {BK, (uint32_t)bn};
+    rc = make_tmap(&tb, B, 2, dims, str, box);
+  } else {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_tmap(&tb, B, 2, dims, str, box);
+  }
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldd = N; p.ldc = N;
+  p.alpha = alpha; p.beta = 0.f;
+  p.D = workspace; p.C = workspace; p.bias = nullptr; p.d_fp32 = 1;
+  p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0;
+  p.split_k = splits; p.k_per_split = kps;
+  const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * splits;
+  int grid = sm_count();
+  if (tiles < grid) grid = tiles;
+  rc = (bn == 256) ? dispatch_major<256, 4, 0>(a_mn_major, b_mn_major, ta, tb, p, grid, stream)
+                   : dispatch_major<128, 6, 0>(a_mn_major, b_mn_major, ta, tb, p, grid, stream);
+  if (rc) return rc;
+  const long n4 = (long)M * N / 4;
+  splitk_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(workspace, splits, D, C != nullptr ? C : D,
+                                                                         bias, M, N, ldd, C != nullptr ? ldc : ldd,
+                                                                         C != nullptr ? beta : 0.f, d_fp32);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
+}
 
 // Grouped GEMM over expert-major rows:  D[rows_g, :] = alpha * A[rows_g, :] * op(B[g]) + beta * C[rows_g, :].
 //   A (total_rows, K) row-major; B (G, N, K) if b_mn_major = 0, (G, K, N) if 1; offsets (G+1) int32 on device.
@@ -973,7 +1095,7 @@ int ftb_grouped_gemm_bf16(const void* A, const void* B, void* D, const void* C, 
   p.alpha = alpha; p.beta = (C != nullptr) ? beta : 0.f;
   p.D = D; p.C = (C != nullptr) ? C : D; p.bias = nullptr; p.d_fp32 = d_fp32;
   p.num_groups = num_groups; p.offsets = offsets;
-  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0; p.split_k = 1; p.k_per_split = 0;
   const int tiles_n = (N + bn - 1) / bn;
   p.max_tiles = ((total_rows + BM - 1) / BM + num_groups) * tiles_n;
   int grid = sm_count();
@@ -1012,7 +1134,7 @@ int ftb_grouped_wgrad_bf16(const void* dY, const void* X, void* G, const int* of
   p.M = N; p.N = Kd; p.K = total_rows; p.ldd = Kd; p.ldc = Kd; p.alpha = alpha; p.beta = beta;
   p.D = G; p.C = G; p.bias = nullptr; p.d_fp32 = g_fp32;
   p.num_groups = num_groups; p.offsets = offsets; p.max_tiles = 0;
-  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0; p.split_k = 1; p.k_per_split = 0;
   const int tiles = num_groups * ((N + BM - 1) / BM) * ((Kd + bn - 1) / bn);
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
@@ -1061,7 +1183,7 @@ int ftb_gemm_bf16_tp(int mode, const void* A, void* const* a_peer, unsigned long
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldd; p.alpha = alpha; p.beta = 0.f;
   p.D = D; p.C = D; p.bias = nullptr; p.d_fp32 = d_fp32;
   p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
-  p.comm_mode = mode; p.world = world; p.rank = rank; p.panel_rows = panel_rows;
+  p.comm_mode = mode; p.world = world; p.rank = rank; p.panel_rows = panel_rows; p.split_k = 1; p.k_per_split = 0;
   p.a_local = const_cast<void*>(A); p.panel_bytes = (long)panel_rows * lda * 2; p.panel_counter = panel_counter;
   p.d_slot_stride = d_slot_stride;
   for (int i = 0; i < MAX_RANKS; ++i) {
@@ -1127,7 +1249,7 @@ int ftb_gemm_bf16_wgather(const void* A, const void* B, void* D, int M, int N, i
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldd; p.alpha = alpha; p.beta = 0.f;
   p.D = D; p.C = D; p.bias = nullptr; p.d_fp32 = 0;
   p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
-  p.comm_mode = 3; p.world = world; p.rank = rank; p.panel_rows = 0;
+  p.comm_mode = 3; p.world = world; p.rank = rank; p.panel_rows = 0; p.split_k = 1; p.k_per_split = 0;
   p.a_local = arena[rank]; p.panel_bytes = 0; p.panel_counter = counters; p.d_slot_stride = 0;
   for (int i = 0; i < MAX_RANKS; ++i) { p.a_peer[i] = i < world ? arena[i] : nullptr; p.d_peer[i] = nullptr; }
   p.n_pull = nseg;

@@ -292,7 +292,81 @@ __global__ void top_p_kernel(const bf16* __restrict__ logits, const float* __res
     return e_ == cudaSuccess ? 0 : -400 - (int)e_;     \
   } while (0)
 
+
+// ----------------------------------------------------------------------------------------- gate preparation
+// Gated DeltaNet gates from the fused [b | a] projection (flextrain/ops/_kernels/gate_prep.py:29-80):
+//   beta = sigmoid(b),   g = -exp(A_log) * softplus(a + dt_bias)          (per token and value head)
+// and their backward:  db = dbeta * beta (1 - beta),  da = dg * (-exp(A_log)) * sigmoid(a + dt_bias),
+//   dA_log[h] += sum_t dg * g,   d_dt_bias[h] += sum_t da.
+// ba is the bf16 GEMM output (T, 2*HV); beta / g are fp32 (T, HV); dba is bf16 (T, 2*HV).
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+
+__global__ void gate_prep_fwd_kernel(const __nv_bfloat16* __restrict__ ba, const float* __restrict__ dt_bias,
+                                     const float* __restrict__ a_log, float* __restrict__ beta, float* __restrict__ g,
+                                     long T, int HV) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * HV) return;
+  const long t = i / HV;
+  const int h = (int)(i - t * HV);
+  const float b = __bfloat162float(ba[t * 2 * HV + h]);
+  const float a = __bfloat162float(ba[t * 2 * HV + HV + h]) + dt_bias[h];
+  beta[i] = 1.f / (1.f + __expf(-b));
+  g[i] = -__expf(a_log[h]) * softplus_f(a);
+}
+
+// grid: blocks of 256 threads over heads x token slabs; each block reduces its slab's column sums in shared memory
+__global__ void gate_prep_bwd_kernel(const __nv_bfloat16* __restrict__ ba, const float* __restrict__ dt_bias,
+                                     const float* __restrict__ a_log, const float* __restrict__ g,
+                                     const float* __restrict__ dbeta, const float* __restrict__ dg,
+                                     __nv_bfloat16* __restrict__ dba, float* __restrict__ d_a_log,
+                                     float* __restrict__ d_dt_bias, long T, int HV, int rows_per_block) {
+  extern __shared__ float sh[];            // [2 * HV] column sums of this block
+  for (int j = threadIdx.x; j < 2 * HV; j += blockDim.x) sh[j] = 0.f;
+  __syncthreads();
+  const long t0 = (long)blockIdx.x * rows_per_block;
+  const long t1 = min(T, t0 + rows_per_block);
+  for (long i = t0 * HV + threadIdx.x; i < t1 * HV; i += blockDim.x) {
+    const long t = i / HV;
+    const int h = (int)(i - t * HV);
+    const float b = __bfloat162float(ba[t * 2 * HV + h]);
+    const float a = __bfloat162float(ba[t * 2 * HV + HV + h]) + dt_bias[h];
+    const float be = 1.f / (1.f + __expf(-b));
+    const float dgi = dg[i];
+    const float da = dgi * (-__expf(a_log[h])) * (1.f / (1.f + __expf(-a)));
+    dba[t * 2 * HV + h] = __float2bfloat16(dbeta[i] * be * (1.f - be));
+    dba[t * 2 * HV + HV + h] = __float2bfloat16(da);
+    atomicAdd(&sh[h], dgi * g[i]);
+    atomicAdd(&sh[HV + h], da);
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < HV; j += blockDim.x) {
+    if (d_a_log) atomicAdd(d_a_log + j, sh[j]);
+    if (d_dt_bias) atomicAdd(d_dt_bias + j, sh[HV + j]);
+  }
+}
+
 extern "C" {
+
+int ftb_gate_prep_fwd(const void* ba, const float* dt_bias, const float* a_log, float* beta, float* g, long T, int HV,
+                      cudaStream_t s) {
+  if (T == 0) return 0;
+  const long n = T * HV;
+  gate_prep_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)ba, dt_bias, a_log, beta, g, T, HV);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -400 - (int)e;
+}
+
+// d_a_log / d_dt_bias (HV fp32) are ACCUMULATED into (pass zeroed buffers for plain sums); either may be NULL.
+int ftb_gate_prep_bwd(const void* ba, const float* dt_bias, const float* a_log, const float* g, const float* dbeta,
+                      const float* dg, void* dba, float* d_a_log, float* d_dt_bias, long T, int HV, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (HV > 4096) return -2;
+  const int rows = 128;
+  gate_prep_bwd_kernel<<<(unsigned)((T + rows - 1) / rows), 256, 2 * HV * sizeof(float), s>>>(
+      (const __nv_bfloat16*)ba, dt_bias, a_log, g, dbeta, dg, (__nv_bfloat16*)dba, d_a_log, d_dt_bias, T, HV, rows);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -400 - (int)e;
+}
 
 int ftb_conv1d_fwd(const void* x, long ldx, const void* w, const void* init, const int* cu, int nseq, void* y, void* fin,
                    int T, int D, int W, int act, cudaStream_t s) {

@@ -369,8 +369,7 @@ class ActiveModel:
         if not bm.params_resident:
             # events of the previous round are stale; the ring may only be refilled once compute has left it
             ev.weights_in.clear(); ev.layer_out.clear(); ev.grads_in.clear()
-            if st.is_cuda:
-                st.inbound.wait_stream(st.compute)
+            st.wait_stream(st.inbound, st.compute)
             for l in range(min(bm.n_p, nL)):
                 self._prefetch_params(l)
         elif not bm.grads_resident:
@@ -379,6 +378,7 @@ class ActiveModel:
             with _nvtx(f"Layer {l}"):
                 if not bm.params_resident:
                     ev.weights_in.wait(l, st.compute)
+                    st.touch(("p", bm._slot("p", l)), "r", f"forward of layer {l}")
                 params = bm.params(l)
                 lin_state, lin_conv = {}, {}
                 for c, meta in enumerate(metas):
@@ -454,6 +454,7 @@ class ActiveModel:
             pairs = []
             host = send_home(slot, hbuf, level, copy_fn=lambda d, s_: pairs.append((d, s_)))
             self._engine_copies(pairs, 1)
+            st.touch(("hact", hbuf.data_ptr() - bm.host_act.data_ptr()), "w", f"offload of slot ({l}, {c})")
             ev.act_out.record((l, c), st.outbound)
         if st.is_cuda:
             for name in slot.names():
@@ -466,6 +467,7 @@ class ActiveModel:
             if after_layer is not None:
                 ev.layer_out.wait(after_layer, st.inbound)      # ring slot is free once its previous tenant finished
             bm.fetch_layer_params(l, self._ring_copier(0))
+            st.touch(("p", bm._slot("p", l)), "w", f"fetch of layer {l}'s parameters (forward)")
             ev.weights_in.record(l, st.inbound)
 
     # =========================================================================== backward
@@ -475,9 +477,12 @@ class ActiveModel:
         groups: Dict[int, List[int]] = {}
         for c, m in enumerate(metas):
             groups.setdefault(m.seq_group, []).append(c)
-        if not bm.params_resident:
-            # the forward pass left the last n_p layers in the ring; everything else is re-fetched backwards
-            pass
+        if not bm.grads_resident:
+            # The first layers of this backward pass reuse gradient slots whose last tenants were written back on the
+            # outbound stream by the PREVIOUS round (or step): nothing else orders the refill / zeroing of a slot after
+            # that copy, so both streams that may write the slot wait for the outbound stream once per pass.
+            st.wait_stream(st.compute, st.outbound)
+            st.wait_stream(st.inbound, st.outbound)
         # Backward order of the (layer, chunk) slots, for the look-ahead fetch of offloaded activations: while chunk i
         # computes, the host->device copy of the slots of the next ``act_prefetch_depth`` chunks in this order runs on
         # the inbound stream (flextrain/engine/active_model.py:2036-2098 walks backwards the same way and refills the
@@ -496,8 +501,10 @@ class ActiveModel:
                         ev.weights_in.wait(("b", l), st.compute)
                     else:
                         ev.weights_in.wait(l, st.compute)
+                    st.touch(("p", bm._slot("p", l)), "r", f"backward of layer {l}")
                 if not bm.grads_resident:
                     self._prepare_ring_grads(l)
+                    st.touch(("g", bm._slot("g", l)), "w", f"backward of layer {l} accumulates gradients")
                 params, grads = bm.params(l), bm.grads(l)
                 for g in sorted(groups, reverse=True):
                     chunk_ids = groups[g]
@@ -531,6 +538,7 @@ class ActiveModel:
                     with st.use(st.outbound):
                         ev.grads_ready.wait(l, st.outbound)
                         bm.offload_layer_grads(l, self._ring_copier(1))
+                        st.touch(("g", bm._slot("g", l)), "r", f"write-back of layer {l}'s gradients")
                         ev.layer_out.record(("g", l), st.outbound)
                 if not bm.params_resident:
                     ev.layer_out.record(("b", l), st.compute)
@@ -547,6 +555,7 @@ class ActiveModel:
             if after is not None:
                 ev.layer_out.wait(after, st.inbound)
             bm.fetch_layer_params(l, self._ring_copier(0))
+            st.touch(("p", bm._slot("p", l)), "w", f"fetch of layer {l}'s parameters (backward)")
             ev.weights_in.record(("b", l), st.inbound)
 
     def _prepare_ring_grads(self, l: int):
@@ -557,12 +566,14 @@ class ActiveModel:
             ev.layer_out.wait(("g", prev_tenant), st.compute)
         if self._grads_fresh.get(l, True):
             bm.zero_layer_grads(l)
+            st.touch(("g", bm._slot("g", l)), "w", f"zero of layer {l}'s gradient slot")
             self._grads_fresh[l] = False
         else:
             with st.use(st.inbound):
                 if ev.layer_out.has(("g", prev_tenant)):
                     ev.layer_out.wait(("g", prev_tenant), st.inbound)
                 bm.fetch_layer_grads(l, self._ring_copier(0))
+                st.touch(("g", bm._slot("g", l)), "w", f"fetch of layer {l}'s partial gradients")
                 ev.grads_in.record(l, st.inbound)
             ev.grads_in.wait(l, st.compute)
 
@@ -582,6 +593,9 @@ class ActiveModel:
             pairs = []
             dev = fetch_home(slot, None, self.device, copy_fn=lambda d, s_: pairs.append((d, s_)))
             self._engine_copies(pairs, 0)
+            if self.buffers.host_act is not None:
+                st.touch(("hact", slot.buffer.data_ptr() - self.buffers.host_act.data_ptr()), "r",
+                         f"fetch of slot ({l}, {c})")
             ev.act_in.record((l, c), st.inbound)
         self._prefetched[(l, c)] = dev
 
@@ -610,7 +624,8 @@ class ActiveModel:
         st = self.streams
         live = 0
         with st.use(st.inbound_fwd_context):
-            st.inbound_fwd_context.wait_stream(st.compute)
+            st.wait_stream(st.inbound_fwd_context, st.compute)
+            st.touch(("kv",), "w", f"K/V window refill for layer {l}")
             for c in chunk_ids:
                 m = metas[c]
                 if not (m.has_prior or any(m.has_more_chunks)):
@@ -629,7 +644,8 @@ class ActiveModel:
             # only the keys this group can see collect dK / dV: clear that range, not the whole window
             w.dk[:live].zero_()
             w.dv[:live].zero_()
-        st.compute.wait_stream(st.inbound_fwd_context)
+        st.wait_stream(st.compute, st.inbound_fwd_context)
+        st.touch(("kv",), "w", f"backward of layer {l} over the K/V window")
 
     # =============================================================================== step
     def _step_local(self, grad_scale: float = 1.0) -> int:
@@ -662,14 +678,21 @@ class ActiveModel:
                         ev.layer_out.wait(("s", k - n), st.inbound)
                 cp = self._ring_copier(0)
                 bm.fetch_layer_params(k, cp); bm.fetch_layer_grads(k, cp); bm.fetch_layer_opt(k, cp)
+                for kind, res in (("p", bm.params_resident), ("g", bm.grads_resident), ("o", bm.opt_resident)):
+                    if not res:
+                        st.touch((kind, bm._slot(kind, k)), "w", f"fetch of layer {k}'s {kind} state for the update")
                 ev.opt_in.record(k, st.inbound)
 
-        st.inbound.wait_stream(st.compute)
-        st.inbound.wait_stream(st.outbound)
+        st.wait_stream(st.inbound, st.compute)
+        st.wait_stream(st.inbound, st.outbound)
         for k in range(min(depth, nL)):
             fetch(k)
         for l, layer in enumerate(self.layers):
             ev.opt_in.wait(l, st.compute)
+            for kind, res, mode in (("p", bm.params_resident, "w"), ("g", bm.grads_resident, "r"),
+                                    ("o", bm.opt_resident, "w")):
+                if not res:
+                    st.touch((kind, bm._slot(kind, l)), mode, f"optimizer update of layer {l}")
             rc |= opt.step(layer.param_spec, bm.params(l), bm.grads(l), bm.opt_state(l), self.step_num, grad_scale)
             if rc:
                 break
@@ -679,6 +702,9 @@ class ActiveModel:
                 ev.layer_out.wait(("c", l), st.outbound)
                 bm.offload_layer_params(l, self._ring_copier(1))
                 bm.offload_layer_opt(l, self._ring_copier(1))
+                for kind, res in (("p", bm.params_resident), ("o", bm.opt_resident)):
+                    if not res:
+                        st.touch((kind, bm._slot(kind, l)), "r", f"write-back of layer {l}'s {kind} state")
                 ev.layer_out.record(("s", l), st.outbound)
             if l + depth < nL:
                 fetch(l + depth)
@@ -713,6 +739,12 @@ class ActiveModel:
 
     def synchronize(self) -> None:
         self.streams.synchronize_all()
+
+    def protocol_violations(self) -> List[str]:
+        """Ordering violations found by the host-side stream-protocol checker (``FTB_STREAM_CHECK=1``): every ring
+        slot, host-arena range or K/V-window access that is not ordered after the accesses it conflicts with."""
+        chk = self.streams.checker
+        return [] if chk is None else [str(v) for v in chk.violations]
 
     def check_health(self, error_words=None) -> None:
         """Raise if anything on the device gave up during the step that just ran.

@@ -29,6 +29,12 @@ def _name_stream(stream, name: str) -> None:
 
 
 class _NullStream:
+    """Stand-in for a CUDA stream on CPU.  Every role gets its own instance so the protocol checker can tell the
+    logical streams apart even though all work runs in program order."""
+
+    def __init__(self, name: str = "null"):
+        self.name = name
+
     def wait_stream(self, other): pass
     def wait_event(self, ev): pass
     def synchronize(self): pass
@@ -51,23 +57,57 @@ class StreamBundle:
     comm: object                       # peer traffic (fused collectives)
     secondary_compute: Optional[object] = None
     is_cuda: bool = False
+    checker: Optional[object] = None   # StreamProtocolChecker when FTB_STREAM_CHECK=1 / check=True
+
+    ROLES = ("compute", "inbound", "outbound", "inbound_fwd_context", "comm")
 
     @classmethod
-    def create(cls, device, secondary: bool = False) -> "StreamBundle":
+    def create(cls, device, secondary: bool = False, check: Optional[bool] = None) -> "StreamBundle":
+        import os
         dev = torch.device(device)
         if dev.type != "cuda":
-            n = _NullStream()
-            return cls(n, n, n, n, n, n if secondary else None, False)
-        with torch.cuda.device(dev):
-            compute = torch.cuda.current_stream(dev)
-            mk = lambda: torch.cuda.Stream(device=dev)
-            b = cls(compute, mk(), mk(), mk(), mk(), mk() if secondary else None, True)
-        for nm in ("inbound", "outbound", "inbound_fwd_context", "comm"):
-            _name_stream(getattr(b, nm), "ftb." + nm)
+            b = cls(*[_NullStream(r) for r in cls.ROLES], _NullStream("secondary_compute") if secondary else None, False)
+        else:
+            with torch.cuda.device(dev):
+                compute = torch.cuda.current_stream(dev)
+                mk = lambda: torch.cuda.Stream(device=dev)
+                b = cls(compute, mk(), mk(), mk(), mk(), mk() if secondary else None, True)
+            for nm in ("inbound", "outbound", "inbound_fwd_context", "comm"):
+                _name_stream(getattr(b, nm), "ftb." + nm)
+        b._names = {id(getattr(b, r)): r for r in cls.ROLES}
+        b._stack = []
+        if check if check is not None else os.environ.get("FTB_STREAM_CHECK", "0") == "1":
+            from .protocol_check import StreamProtocolChecker
+            b.checker = StreamProtocolChecker()
         return b
 
+    # ---- logical stream names (for the protocol checker)
+    def name_of(self, stream) -> str:
+        return self._names.get(id(stream), "other")
+
+    def current(self) -> str:
+        """Role of the stream that work issued now lands on (``use`` contexts nest; the default is compute)."""
+        return self._stack[-1] if self._stack else "compute"
+
+    @contextlib.contextmanager
     def use(self, stream):
-        return torch.cuda.stream(stream) if self.is_cuda else contextlib.nullcontext()
+        self._stack.append(self.name_of(stream))
+        try:
+            with (torch.cuda.stream(stream) if self.is_cuda else contextlib.nullcontext()):
+                yield
+        finally:
+            self._stack.pop()
+
+    def wait_stream(self, waiter, other) -> None:
+        """``waiter`` waits for everything queued on ``other`` so far (logged for the protocol checker)."""
+        waiter.wait_stream(other)
+        if self.checker is not None:
+            self.checker.wait_stream(self.name_of(waiter), self.name_of(other))
+
+    def touch(self, resource, mode: str, note: str = "", stream=None) -> None:
+        """Log a read (``"r"``) or write (``"w"``) of a tracked resource on ``stream`` (default: the current one)."""
+        if self.checker is not None:
+            self.checker.access(self.name_of(stream) if stream is not None else self.current(), resource, mode, note)
 
     def new_event(self):
         return torch.cuda.Event() if self.is_cuda else _NullEvent()
@@ -75,6 +115,8 @@ class StreamBundle:
     def synchronize_all(self) -> None:
         for s in (self.compute, self.inbound, self.outbound, self.inbound_fwd_context, self.comm):
             s.synchronize()
+        if self.checker is not None:
+            self.checker.host_sync(self.ROLES)
 
 
 class EventMap(Generic[K]):
@@ -88,12 +130,16 @@ class EventMap(Generic[K]):
         ev = self.bundle.new_event()
         ev.record(stream) if self.bundle.is_cuda else None
         self._ev[key] = ev
+        if self.bundle.checker is not None:
+            self.bundle.checker.record((self.name, key), self.bundle.name_of(stream))
 
     def wait(self, key: K, stream) -> None:
         if key not in self._ev:
             raise KeyError(f"{self.name}: wait on never-recorded event {key!r}")
         if self.bundle.is_cuda:
             stream.wait_event(self._ev[key])
+        if self.bundle.checker is not None:
+            self.bundle.checker.wait((self.name, key), self.bundle.name_of(stream))
 
     def has(self, key: K) -> bool:
         return key in self._ev

@@ -215,11 +215,8 @@ class MoEFFN:
         logits = ops.gemm(h, params["w_router"], trans_b=True)
         dlogits = ops.topk_route_bwd(dw, logits, w, idx, c.routing)
         if c.aux_loss_alpha > 0 and ctx.total_tokens_per_step > 0:
-            p = torch.softmax(logits.to(torch.float32), -1)
-            f = torch.zeros(E, dtype=torch.float32, device=h.device).index_add_(
-                0, idx.reshape(-1).long(), torch.ones(idx.numel(), dtype=torch.float32, device=h.device))
-            gvec = f / max(idx.numel(), 1) * E / ctx.total_tokens_per_step
-            dlogits = dlogits + c.aux_loss_alpha * p * (gvec - (p * gvec).sum(-1, keepdim=True))
+            dlogits = ops.load_balance_bwd_(dlogits.contiguous(), logits, idx, c.aux_loss_alpha,
+                                            ctx.total_tokens_per_step)
         dl = dlogits.to(h.dtype)
         dh = ops.gemm(dl, params["w_router"], beta=1.0, out=dh)
         if "g_router" in grads:

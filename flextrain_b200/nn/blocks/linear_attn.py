@@ -126,19 +126,18 @@ class GatedDeltaNetBlock:
         f32 = torch.float32
         cu = meta.cu_seqlens_q
         qkvz = ops.gemm(h, p["w_lin_qkvz"], trans_b=True)
-        ba = ops.gemm(h, p["w_lin_ba"], trans_b=True).to(f32)
+        ba = ops.gemm(h, p["w_lin_ba"], trans_b=True)
         qkv, z2d = qkvz[:, : c.conv_dim], qkvz[:, c.conv_dim:]
         qkv_c, conv_fin = la.conv1d_fwd(qkv, p["w_lin_conv"], cu, conv_in, activation=True)
         qn, q_rn = la.l2norm_heads_fwd(qkv_c[:, : c.key_dim], c.n_k_heads, c.head_k_dim)
         kn, k_rn = la.l2norm_heads_fwd(qkv_c[:, c.key_dim: 2 * c.key_dim], c.n_k_heads, c.head_k_dim)
         v = qkv_c[:, 2 * c.key_dim:].contiguous().view(T, c.n_v_heads, c.head_v_dim)
-        a_pre = ba[:, c.n_v_heads:] + p["w_lin_dt_bias"].to(f32)
-        beta = torch.sigmoid(ba[:, : c.n_v_heads]).contiguous()
-        g = (-torch.exp(p["w_lin_A_log"].to(f32)) * F.softplus(a_pre)).contiguous()
+        # gates in one launch straight from the bf16 projection (flextrain/ops/_kernels/gate_prep.py:29-80)
+        beta, g = la.gate_prep_fwd(ba.contiguous(), p["w_lin_dt_bias"].to(f32), p["w_lin_A_log"].to(f32))
         o, fin, r = la.gdn_fwd(qn, kn, v, g, beta, cu, state_in, want_r=want_r)
         z = z2d.contiguous().view(T * c.n_v_heads, c.head_v_dim)
         on = ops.gated_rmsnorm_fwd(o.view(T * c.n_v_heads, c.head_v_dim), z, p["w_lin_norm"].to(f32), c.norm_eps)
-        return dict(qkvz=qkvz, qkv_c=qkv_c, conv_fin=conv_fin, qn=qn, kn=kn, q_rn=q_rn, k_rn=k_rn, v=v, a_pre=a_pre,
+        return dict(qkvz=qkvz, qkv_c=qkv_c, conv_fin=conv_fin, qn=qn, kn=kn, q_rn=q_rn, k_rn=k_rn, v=v, ba=ba,
                     beta=beta, g=g, o=o, fin=fin, r=r, on=on.view(T, c.value_dim))
 
     def _fwd_cuda(self, h, x_resid, meta, params, slot, ctx):
@@ -183,12 +182,12 @@ class GatedDeltaNetBlock:
                                  ctx.lin_dconv_in, dqkvz[:, : c.conv_dim], dwc, want_dinit=ctx.lin_conv_in is not None)
         acc("g_lin_conv", dwc)
         # ---- gates:  beta = sigmoid(b);  g = -exp(A_log) * softplus(a + dt_bias)
-        beta, a_pre = s["beta"], s["a_pre"]
-        db = dbeta * beta * (1.0 - beta)
-        da = dg * (-torch.exp(params["w_lin_A_log"].to(f32))) * torch.sigmoid(a_pre)
-        acc("g_lin_A_log", (dg * s["g"]).sum(0))
-        acc("g_lin_dt_bias", da.sum(0))
-        dba = torch.cat([db, da], 1).to(h.dtype)
+        d_alog = torch.zeros(c.n_v_heads, dtype=f32, device=h.device)
+        d_dtb = torch.zeros(c.n_v_heads, dtype=f32, device=h.device)
+        dba = la.gate_prep_bwd(s["ba"].contiguous(), params["w_lin_dt_bias"].to(f32), params["w_lin_A_log"].to(f32),
+                               s["g"], dbeta, dg, d_alog, d_dtb)
+        acc("g_lin_A_log", d_alog)
+        acc("g_lin_dt_bias", d_dtb)
         # ---- input projections
         dh = ops.linear_dgrad(dqkvz, params["w_lin_qkvz"])
         dh = ops.linear_dgrad(dba, params["w_lin_ba"], out=dh, accumulate=True)

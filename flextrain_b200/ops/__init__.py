@@ -396,6 +396,26 @@ def topk_route_bwd(dw, logits, w, experts, mode="topk_then_softmax"):
 moe_sort = ref.moe_sort
 
 
+def load_balance_bwd_(dlogits, logits, experts, alpha: float, total_tokens_per_step: int, counts=None):
+    """Add the load-balance auxiliary gradient into ``dlogits (T, E)`` fp32 in place:
+    ``alpha * p * (gvec - sum(p * gvec))`` with ``p = softmax(logits)`` and ``gvec = counts / n_slots * E / total_tokens``
+    (flextrain/ops/_kernels/moe.py:601-646); ``counts`` are the per-expert slot counts of this chunk."""
+    T, E = logits.shape
+    n = experts.numel()
+    if _cuda_bf16(logits) and E <= 256 and dlogits.dtype == torch.float32 and dlogits.is_contiguous():
+        if counts is None:
+            counts = torch.bincount(experts.reshape(-1).long(), minlength=E)
+        _count()
+        return _kernels().load_balance_bwd_(dlogits, logits.contiguous(), counts.to(torch.int32).contiguous(),
+                                            float(alpha), float(E) / max(n, 1) / float(total_tokens_per_step))
+    p = torch.softmax(logits.to(torch.float32), -1)
+    f = torch.zeros(E, dtype=torch.float32, device=logits.device).index_add_(
+        0, experts.reshape(-1).long(), torch.ones(n, dtype=torch.float32, device=logits.device))
+    gvec = f / max(n, 1) * E / total_tokens_per_step
+    dlogits += alpha * p * (gvec - (p * gvec).sum(-1, keepdim=True))
+    return dlogits
+
+
 def moe_plan(experts, num_experts: int, pad: int = 1):
     """Expert-major row layout of one chunk's routed slots (``reference.MoEPlan``): a stable counting sort by expert
     with every expert's segment padded to ``pad`` rows.  On CUDA three small kernels build it without a host read
@@ -406,8 +426,8 @@ def moe_plan(experts, num_experts: int, pad: int = 1):
         R = ref.moe_rows_bound(T, K, num_experts, pad)
         _count(3)
         _used("moe_plan", "ftb")
-        row_src, inv, offsets, _ = _kernels().moe_plan(experts, num_experts, pad, R)
-        return ref.MoEPlan(row_src, inv, offsets, R)
+        row_src, inv, offsets, counts = _kernels().moe_plan(experts, num_experts, pad, R)
+        return ref.MoEPlan(row_src, inv, offsets, R, counts)
     if experts.is_cuda:
         _fallback("moe_plan", f"{num_experts} experts (the plan kernels take up to 1024)")
     return ref.moe_plan(experts, num_experts, pad)

@@ -132,6 +132,19 @@ def gemm(a, b, *, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, bia
         assert c.dtype == out.dtype and c.stride(1) == 1
     if bias is not None:
         assert bias.dtype == torch.float32
+    # small output, long reduction (rank-r LoRA gradients: M or N = r, K = tokens): a handful of tiles would each walk
+    # the whole K on a handful of SMs; split K so that tiles x slices fill the GPU (fp32 slabs + ordered reduce)
+    tiles = ((M + 127) // 128) * ((N + (127 if N <= 128 else 255)) // (128 if N <= 128 else 256))
+    if bn == 0 and tiles <= 40 and K >= 4096 and (N <= 128 or M < 512):
+        splits = max(2, min(148 // tiles, K // 512, 64))
+        ws = torch.empty(splits * M * N, dtype=torch.float32, device=a.device)
+        rc = lib.ftb_gemm_bf16_splitk(_ptr(a), _ptr(b), _ptr(out), _ptr(c), _ptr(bias), c_int(M), c_int(N), c_int(K),
+                                      c_int(1 if trans_a else 0), c_int(0 if trans_b else 1), c_int(a.stride(0)),
+                                      c_int(b.stride(0)), c_int(out.stride(0)), c_int(c.stride(0) if c is not None else 0),
+                                      c_float(alpha), c_float(beta), c_int(1 if out.dtype == torch.float32 else 0),
+                                      c_int(splits), _ptr(ws), _stream())
+        _check(rc, "ftb_gemm_bf16_splitk")
+        return out
     fast = fastcall()
     if fast is not None:
         rc = fast.gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), None if c is None else c.data_ptr(),
@@ -290,6 +303,15 @@ def topk_route_bwd(dw, logits, w, experts, mode="topk_then_softmax"):
                                 _ptr(dl), c_int(T), c_int(E), c_int(K), c_int(0 if mode == "topk_then_softmax" else 1),
                                 _stream())
     _check(rc, "ftb_topk_route_bwd")
+    return dl
+
+
+def load_balance_bwd_(dl, logits, counts, alpha: float, gscale: float):
+    lib = load("elementwise")
+    T, E = logits.shape
+    rc = lib.ftb_load_balance_bwd(_ptr(logits), _ptr(counts), _ptr(dl), c_int(T), c_int(E), c_float(alpha),
+                                  c_float(gscale), _stream())
+    _check(rc, "ftb_load_balance_bwd")
     return dl
 
 

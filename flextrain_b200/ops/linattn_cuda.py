@@ -99,6 +99,36 @@ def gated_rmsnorm_bwd(dy: torch.Tensor, o: torch.Tensor, z2d: torch.Tensor, w: t
 
 
 # ------------------------------------------------------------------------------------------ gated delta rule
+def gate_prep_fwd(ba: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``beta = sigmoid(b)``, ``g = -exp(A_log) * softplus(a + dt_bias)`` from the bf16 ``[b | a]`` projection
+    ``(T, 2*HV)`` in one launch; both fp32 ``(T, HV)``."""
+    lib = load("seqmix")
+    T, two_hv = ba.shape
+    HV = two_hv // 2
+    assert ba.dtype == torch.bfloat16 and ba.is_contiguous() and dt_bias.dtype == torch.float32 and a_log.dtype == torch.float32
+    beta = torch.empty(T, HV, dtype=torch.float32, device=ba.device)
+    g = torch.empty(T, HV, dtype=torch.float32, device=ba.device)
+    _check(lib.ftb_gate_prep_fwd(_ptr(ba), _ptr(dt_bias), _ptr(a_log), _ptr(beta), _ptr(g), c_long(T), c_int(HV),
+                                 _stream()), "ftb_gate_prep_fwd")
+    return beta, g
+
+
+def gate_prep_bwd(ba, dt_bias, a_log, g, dbeta, dg, d_a_log: Optional[torch.Tensor], d_dt_bias: Optional[torch.Tensor]
+                  ) -> torch.Tensor:
+    """Backward of :func:`gate_prep_fwd`: returns ``dba (T, 2*HV)`` bf16 and accumulates the two parameter gradients
+    (fp32 ``(HV,)`` buffers) in the same launch."""
+    lib = load("seqmix")
+    T, two_hv = ba.shape
+    HV = two_hv // 2
+    dba = torch.empty_like(ba)
+    for t in (d_a_log, d_dt_bias):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    _check(lib.ftb_gate_prep_bwd(_ptr(ba), _ptr(dt_bias), _ptr(a_log), _ptr(g.contiguous()), _ptr(dbeta.contiguous()),
+                                 _ptr(dg.contiguous()), _ptr(dba), _ptr(d_a_log), _ptr(d_dt_bias), c_long(T),
+                                 c_int(HV), _stream()), "ftb_gate_prep_bwd")
+    return dba
+
+
 def gdn_supported(dk: int, dv: int) -> bool:
     return dk in (16, 32, 64, 128) and dv % 8 == 0
 

@@ -590,10 +590,10 @@ class MoEPlan:
     ``inv (T,K)``: row of each slot; ``offsets (E+1,)``: start row of each expert (each expert's
     segment is padded to a multiple of ``pad`` so GEMM tiles never straddle two experts).
     """
-    __slots__ = ("row_src", "inv", "offsets", "rows")
+    __slots__ = ("row_src", "inv", "offsets", "rows", "counts")
 
-    def __init__(self, row_src, inv, offsets, rows):
-        self.row_src, self.inv, self.offsets, self.rows = row_src, inv, offsets, rows
+    def __init__(self, row_src, inv, offsets, rows, counts=None):
+        self.row_src, self.inv, self.offsets, self.rows, self.counts = row_src, inv, offsets, rows, counts
 
 
 def moe_rows_bound(T: int, K: int, E: int, pad: int) -> int:
@@ -622,7 +622,7 @@ def moe_plan(experts: torch.Tensor, num_experts: int, pad: int = 1) -> MoEPlan:
     row_src[rows] = order.to(torch.int32)
     inv = torch.empty(n, dtype=torch.int32, device=dev)
     inv[order] = rows.to(torch.int32)
-    return MoEPlan(row_src, inv.view(T, K), offsets.to(torch.int32), R)
+    return MoEPlan(row_src, inv.view(T, K), offsets.to(torch.int32), R, counts.to(torch.int32))
 
 
 def moe_row_weights(w: torch.Tensor, plan: MoEPlan) -> torch.Tensor:

@@ -166,3 +166,45 @@ def test_evaluate_is_forward_only(variant):
     b._zero_grad = True
     assert abs(a.evaluate(held_out).loss_sum - want.loss_sum) < 1e-3
     assert held_out[0].per_token_loss is not None
+
+
+# ------------------------------------------------------------------ stream-protocol checker
+RINGS = dict(n_gpu_layers=2, n_gpu_grads=2, n_gpu_opt_layers=2, chunk=96, round_tokens=128)
+
+
+def test_protocol_checker_passes_the_ring_schedules(monkeypatch):
+    """With ``FTB_STREAM_CHECK=1`` every ring-slot access of the weight / gradient / optimizer rings (forward,
+    backward over several rounds, streamed optimizer step) and of the K/V window of a sequence that spans chunks is
+    replayed through vector clocks: the engine's events must order every write after the accesses it conflicts with."""
+    monkeypatch.setenv("FTB_STREAM_CHECK", "1")
+    _, _, am = _run(RINGS)
+    chk = am.streams.checker
+    assert chk is not None and chk.n_accesses > 50
+    assert {k[0] for k in chk.history} >= {"p", "g", "o"}
+    assert am.protocol_violations() == []
+    _, _, am2 = _run(dict(chunk=64), seq_lens=(160, 96), max_seq=160)          # sequences that span chunks
+    assert ("kv",) in am2.streams.checker.history and am2.protocol_violations() == []
+
+
+@pytest.mark.parametrize("dropped", ["layer_out", "weights_in", "opt_in"])
+def test_protocol_checker_catches_a_missing_wait(monkeypatch, dropped):
+    """Take one class of waits out of the schedule (the copy that refills a ring slot no longer waits for the layer
+    that used it / compute no longer waits for its weights / the update no longer waits for its state): nothing
+    crashes, the run even finishes, and the checker names the unordered access."""
+    from flextrain_b200.engine import streams as S
+    monkeypatch.setenv("FTB_STREAM_CHECK", "1")
+    real = S.EventMap.wait
+
+    def wait(self, key, stream):
+        if self.name == dropped:
+            if key not in self._ev:
+                raise KeyError(key)
+            return None                      # the scheduling bug: the wait is simply not issued
+        return real(self, key, stream)
+
+    monkeypatch.setattr(S.EventMap, "wait", wait)
+    _, _, am = _run(RINGS, steps=1)
+    v = am.protocol_violations()
+    assert v, "a dropped wait must be reported"
+    kinds = {"layer_out": "write-after-read", "weights_in": "read-after-write", "opt_in": "after-write"}
+    assert any(kinds[dropped] in s for s in v), v[:3]

@@ -180,3 +180,27 @@ def test_top_p_sampler_stays_in_nucleus():
     assert bool((chosen_p >= smallest * 0.98).all())
     # top_p -> 0 degenerates to the arg-max
     assert torch.equal(la.top_p_sample(logits, 1e-6, 1.0, generator=g), p.argmax(-1))
+
+
+@pytest.mark.parametrize("T,HV", [(1000, 32), (77, 4), (4096, 48)])
+def test_gate_prep_fwd_bwd(T, HV):
+    """``beta = sigmoid(b)``, ``g = -exp(A_log) softplus(a + dt_bias)`` and their backward (incl. the two parameter
+    gradients, reduced inside the kernel) against autograd on the same bf16 projection output."""
+    import torch.nn.functional as F
+    from flextrain_b200.ops import linattn_cuda as la
+    torch.manual_seed(T)
+    ba = (torch.randn(T, 2 * HV, device="cuda") * 2).to(torch.bfloat16)
+    dtb = torch.randn(HV, device="cuda")
+    alog = torch.randn(HV, device="cuda") * 0.5
+    beta, g = la.gate_prep_fwd(ba, dtb, alog)
+    baf = ba.float().requires_grad_(True)
+    dtb_r, alog_r = dtb.clone().requires_grad_(True), alog.clone().requires_grad_(True)
+    beta_w = torch.sigmoid(baf[:, :HV])
+    g_w = -torch.exp(alog_r) * F.softplus(baf[:, HV:] + dtb_r)
+    assert _rel(beta, beta_w) < 1e-5 and _rel(g, g_w) < 1e-5
+    dbeta, dg = torch.randn(T, HV, device="cuda"), torch.randn(T, HV, device="cuda")
+    (beta_w * dbeta + g_w * dg).sum().backward()
+    d_alog, d_dtb = torch.zeros(HV, device="cuda"), torch.zeros(HV, device="cuda")
+    dba = la.gate_prep_bwd(ba, dtb, alog, g, dbeta, dg, d_alog, d_dtb)
+    assert _rel(dba, baf.grad) < 6e-3
+    assert _rel(d_alog, alog_r.grad) < 1e-4 and _rel(d_dtb, dtb_r.grad) < 1e-4

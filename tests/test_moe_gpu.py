@@ -106,3 +106,21 @@ def test_expert_parallel_plan_kernels_against_tensor_ops(W, rank):
     small = int(want.slot_row.max()) - 5
     k.ep_plan_map(ex, (T, K), E, table.contiguous(), W, rank, PAD, small, work, over)
     assert int(over) == 1
+
+
+@pytest.mark.parametrize("T,E,K", [(300, 8, 2), (2048, 128, 8), (77, 60, 4)])
+def test_load_balance_gradient_kernel(T, E, K):
+    """The auxiliary load-balance gradient added into dlogits by one kernel, against the tensor-op statement."""
+    from flextrain_b200 import ops
+    torch.manual_seed(E)
+    logits = (torch.randn(T, E, device="cuda") * 2).to(torch.bfloat16)
+    idx = torch.topk(logits.float(), K, dim=-1).indices.to(torch.int32)
+    dl0 = torch.randn(T, E, device="cuda")
+    alpha, total = 0.05, 4 * T
+    got = ops.load_balance_bwd_(dl0.clone(), logits, idx, alpha, total)
+    p = torch.softmax(logits.float(), -1)
+    f = torch.bincount(idx.reshape(-1).long(), minlength=E).float()
+    gvec = f / idx.numel() * E / total
+    want = dl0 + alpha * p * (gvec - (p * gvec).sum(-1, keepdim=True))
+    assert _rel(got, want) < 1e-5
+    assert _rel(got - dl0, want - dl0) < 2e-3
