@@ -399,12 +399,17 @@ def run_reference(args):
         # smaller chunk cap, then a smaller GPU budget, then the nominal link figure, then its default bf16
         # optimizer state; the first plan that builds is the one that runs, and the JSON line says which.
         am, errors, chosen = None, [], None
-        ladder = [(st, hw, g, m)
+        # state dtype (the configuration's fp32 first, the reference's own bf16 default last) x GPU budget (descending:
+        # the largest budget whose plan also survives the reference's own allocations wins) x link figure x chunk cap
+        ladder = [(st, g, hw, m)
                   for st in ("float32", "bfloat16")
+                  for g in (None, 160, 140, 120, 96, 64, 31)
                   for hw in ("probed", "nominal")
-                  for g in (None, 96, 64, 31)
                   for m in (None, 16384, 8192, 4096)]
-        for st, hw, g, m in ladder:
+        oom_at = set()                       # (state, gpu budget) whose plan ran out of device memory: skip its variants
+        for st, g, hw, m in ladder:
+            if (st, g) in oom_at:
+                continue
             opt = AdamW(AdamWHyperparams(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0),
                         state_dtype=getattr(torch, st))
             hwc, mbw = hw_probed if hw == "probed" else hw_nominal
@@ -417,8 +422,13 @@ def run_reference(args):
                 chosen = {"opt_state": st, "hw_cost": hw, "max_gpu_gib": g, "max_chunk_size": m}
                 break
             except (ValueError, RuntimeError, AssertionError, MemoryError) as e:
-                errors.append(f"{st}/{hw}/gpu={g}/chunk={m}: {type(e).__name__}: {str(e)[:160]}")
-                if isinstance(e, (RuntimeError, MemoryError)):
+                msg = f"{st}/gpu={g}/{hw}/chunk={m}: {type(e).__name__}: {str(e)[:160]}"
+                errors.append(msg)
+                print("[reference arm] attempt failed: " + msg.replace("\n", " "), file=sys.stderr, flush=True)
+                if not isinstance(e, ValueError):
+                    # an allocation of the reference's own plan failed (device or pinned memory): the other link / chunk
+                    # variants of this budget plan the same memory, go to the next smaller GPU budget
+                    oom_at.add((st, g))
                     import gc
                     gc.collect()
                     torch.cuda.empty_cache()
@@ -474,6 +484,13 @@ def run_reference(args):
                 dist.barrier()
             torch.cuda.synchronize()
 
+        def ref_loss(st):
+            """Mean loss of the whole job's batch from the reference's StepStats (sum of per-token losses)."""
+            t = torch.tensor([float(st.total_loss)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t)
+            return float(t) / gbatch
+
         loss_step1, warm_s = None, 0.0
         for i in range(args.warmup):
             barrier()
@@ -482,7 +499,7 @@ def run_reference(args):
             barrier()
             warm_s = time.perf_counter() - t0
             if i == 0:
-                loss_step1 = getattr(st, "loss", None)
+                loss_step1 = ref_loss(st)
         steps = _budget_steps(args, t_proc0, warm_s)
         if world > 1:
             tsteps = torch.tensor([steps], device=dev)
@@ -504,6 +521,7 @@ def run_reference(args):
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, e2e_ms = float(t[0]), float(t[1])
+        last_loss = ref_loss(st)
     except Exception as e:
         import traceback
         traceback.print_exc()
@@ -511,7 +529,6 @@ def run_reference(args):
     if rank == 0:
         ms_step = dev_ms / steps
         value = gbatch / (ms_step / 1e3)
-        loss = getattr(st, "loss", None)
         _emit({"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
                "steps": steps, "steps_requested": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
                "higher_is_better": True,
@@ -529,8 +546,7 @@ def run_reference(args):
                "clocks": clocks,
                "e2e": {"value": gbatch / (e2e_ms / steps / 1e3), "unit": "tokens/s",
                        "h2d_bytes_per_step": 16 * per_rank, "d2h_bytes_per_step": 4 * per_rank},
-               "loss": float(loss) if loss is not None else None,
-               "loss_step1": float(loss_step1) if loss_step1 is not None else None,
+               "loss": last_loss, "loss_step1": loss_step1,
                "gpu_launches": None})
     if world > 1:
         dist.destroy_process_group()

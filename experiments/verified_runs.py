@@ -42,6 +42,7 @@ if __name__ == "__main__":
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--out", default="runs/verified")
     ap.add_argument("--baseline", default=None)
+    ap.add_argument("--tok-s-tolerance", type=float, default=0.05, help="allowed relative throughput change vs --baseline")
     a, extra = ap.parse_known_args()
     os.makedirs(a.out, exist_ok=True)
     rows = [run_row(*r.split(":"), a.steps, a.read_step, a.seq_len, a.batch, a.gpus, extra) for r in a.rows.split(",")]
@@ -57,7 +58,7 @@ if __name__ == "__main__":
         for r in rows:
             o = old.get((r["model"], r["mode"]))
             if o and "loss" in o and "loss" in r:
-                if abs(o["loss"] - r["loss"]) > 5e-5 or abs(o["tok_s"] - r["tok_s"]) > 0.05 * o["tok_s"]:
+                if abs(o["loss"] - r["loss"]) > 5e-5 or abs(o["tok_s"] - r["tok_s"]) > a.tok_s_tolerance * o["tok_s"]:
                     print("DIFF", r["model"], r["mode"], o["loss"], r["loss"], o["tok_s"], r["tok_s"])
                     bad += 1
     print(open(os.path.join(a.out, "table.md")).read())

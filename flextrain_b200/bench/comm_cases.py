@@ -135,7 +135,13 @@ def main() -> None:
     w2 = (torch.randn(K, N, device=dev) * 0.05).to(torch.bfloat16)
     fl = 2.0 * world * Tl * K * N
     link = (world - 1) * Tl * K * 2
-    record("tp_ag_gemm", timeit(lambda: tp.ag_gemm(x, w)), timeit(lambda: base.ag_gemm(x, w)), fl, link)
+    t_lib = timeit(lambda: base.ag_gemm(x, w))
+    record("tp_ag_gemm", timeit(lambda: tp.ag_gemm(x, w)), t_lib, fl, link)
+    # the same kernel with the remote panels pulled by two warps of 16-byte loads instead of bulk copies (A/B switch)
+    from flextrain_b200.ops.cuda import load as _load_gemm
+    _load_gemm("gemm_tcgen05").ftb_gemm_set_tp_pull_threads(c_int(1))
+    record("tp_ag_gemm_thread_pull", timeit(lambda: tp.ag_gemm(x, w)), t_lib, fl, link)
+    _load_gemm("gemm_tcgen05").ftb_gemm_set_tp_pull_threads(c_int(0))
     record("tp_gemm_rs", timeit(lambda: tp.gemm_rs(xa, w2)), timeit(lambda: base.gemm_rs(xa, w2)), fl, link)
 
     # ------------------------------------------------------------------ (b) parameter all-gather -> first GEMM

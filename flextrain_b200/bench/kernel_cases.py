@@ -1,8 +1,8 @@
 """Small, self-terminating kernel cases for profiling one kernel at a time.
 
     python -m flextrain_b200.bench.kernel_cases gemm_fwd|gemm_dgrad|gemm_wgrad|rmsnorm_bwd|softmax_ce|attn_fwd|attn_bwd|
-                                                  attn_fwd_one_tile|attn_fwd_32k|attn_bwd_32k|gdn_fwd|gdn_bwd|
-                                                  gdn_long_fwd|rope
+                                                  attn_fwd_one_tile|attn_bwd_unordered|attn_fwd_32k|attn_bwd_32k|gdn_fwd|gdn_bwd|
+                                                  gdn_long_fwd|rope|ffn_glu_fwd|ffn_glu_bwd
 
 Each case holds a few hundred MB on the device (inputs larger than the 126 MB L2), runs three warm-up launches and
 ten timed launches with CUDA events, and prints achieved TFLOP/s or GB/s.  They are the commands behind the
@@ -78,7 +78,7 @@ def main(case: str) -> None:
             d_o = torch.randn_like(o)
             ms = _time(lambda: la.gdn_bwd(q, kk, v, g, beta, cu, None, fin, r, d_o))
             print(f"{case}: {S} x {L} tokens, HV={HV} dk={dk} dv={dv}  {ms:.3f} ms  {2.2 * fl / ms / 1e9:.1f} TFLOP/s fp32")
-    elif case in ("attn_fwd", "attn_bwd", "attn_fwd_one_tile", "attn_fwd_32k", "attn_bwd_32k"):
+    elif case in ("attn_fwd", "attn_bwd", "attn_bwd_unordered", "attn_fwd_one_tile", "attn_fwd_32k", "attn_bwd_32k"):
         S, B, H, KV, hd = (32768, 1, 32, 8, 128) if case.endswith("_32k") else (1024, 16, 32, 8, 128)
         if case == "attn_fwd_one_tile":          # the one-query-tile-per-CTA forward kernel, for an A/B on the same GPU
             k.load("attention").ftb_attn_set_two_tiles(0)
@@ -93,6 +93,9 @@ def main(case: str) -> None:
             ms = _time(lambda: ops.attention_fwd(q, kk, v, cu, cu, S, S, scale=hd ** -0.5))
             print(f"{case}: B={B} S={S} H={H} KV={KV} hd={hd}  {ms:.3f} ms  {fl / ms / 1e9:.0f} TFLOP/s (causal)")
         else:
+            import os
+            if case == "attn_bwd_unordered":       # dQ added in whatever order the CTAs arrive (not reproducible)
+                os.environ["FTB_ATTN_DETERMINISTIC"] = "0"
             o, lse = ops.attention_fwd(q, kk, v, cu, cu, S, S, scale=hd ** -0.5)
             do = torch.randn_like(o)
             ms = _time(lambda: ops.attention_bwd(do, q, kk, v, o, lse, cu, cu, S, S, scale=hd ** -0.5))
@@ -104,6 +107,30 @@ def main(case: str) -> None:
         inv = ops.rope_inv_freq(hd, 5e5).to(dev)
         ms = _time(lambda: ops.rope(x, pos, inv))
         print(f"{case}: T={T} H={H} hd={hd}  {ms:.3f} ms  {2.0 * T * H * hd * 2 / ms / 1e6:.0f} GB/s (1 read + 1 write)")
+    elif case in ("ffn_glu_fwd", "ffn_glu_bwd"):
+        # Llama-3.1-8B gated FFN on one 16,384-token chunk: fused GEMM + activation epilogue against GEMM then activation
+        M, K, F = 16384, 4096, 14336
+        x = torch.randn(M, K, device=dev, dtype=bf) * 0.5
+        w13 = torch.randn(2 * F, K, device=dev, dtype=bf) * K ** -0.5
+        w2 = torch.randn(K, F, device=dev, dtype=bf) * F ** -0.5
+        x13 = torch.empty(M, 2 * F, device=dev, dtype=bf)
+        if case == "ffn_glu_fwd":
+            fused = _time(lambda: k.gemm_glu_fwd(x, w13, "swiglu", x13=x13))
+            def two():
+                k.gemm(x, w13, trans_b=True, out=x13)
+                k.glu_fwd(x13[:, :F], x13[:, F:], "swiglu")
+            fl = 2.0 * M * K * 2 * F
+        else:
+            k.gemm(x, w13, trans_b=True, out=x13)
+            dx13 = torch.empty_like(x13)
+            fused = _time(lambda: k.gemm_glu_bwd(x, w2, x13, "swiglu", dx13=dx13))
+            def two():
+                dact = k.gemm(x, w2)
+                k.glu_bwd(dact, x13[:, :F], x13[:, F:], "swiglu", dgate=dx13[:, :F], dup=dx13[:, F:])
+            fl = 2.0 * M * K * F
+        sep = _time(two)
+        print(f"{case}: M={M} K={K} F={F}  fused {fused:.3f} ms ({fl / fused / 1e9:.0f} TFLOP/s)  "
+              f"GEMM + activation pass {sep:.3f} ms")
     else:
         raise SystemExit(f"unknown case {case}")
     print("device error words:", k.device_error_words())

@@ -13,7 +13,11 @@
 //
 // Backward, one CTA per (128-key tile, KV head): loops over the query heads of the group and over the query
 // tiles that see these keys; five MMAs per pair (S, dP, dV += Pᵀ·dO, dK += dSᵀ·Q, dQ += dS·K); dK / dV accumulate
-// in TMEM across the loop (deterministic), dQ is accumulated with fp32 atomics into a workspace and converted.
+// in TMEM across the loop (deterministic).  dQ goes into an fp32 workspace with vector reductions (red.v4.f32) issued
+// straight from the registers that hold the tile.  In deterministic mode the CTAs that add to the same (query tile,
+// head) take turns in DEscending key-tile order through a counter (the CTA of key tile j adds once the j_hi - j tiles
+// above it have added; those reach the query tile earlier in their own loops, so the wait is normally already
+// satisfied), which fixes the summation order and makes dQ bit-reproducible.
 #include "ptx.cuh"
 
 namespace ftb {
@@ -392,7 +396,10 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int head = blockIdx.y;
   const int kvh = head / (p.H / p.KV);
   int seq = 0, q0 = 0;
-  if (!find_tile2(p.cu_q, p.num_seqs, blockIdx.x, seq, q0)) return;   // uniform for the CTA: nothing allocated yet
+  // Blocks are handed out in increasing blockIdx; walking the tiles backwards puts the late query blocks of a sequence
+  // (the ones with the most K / V tiles under a causal mask) first and leaves the short ones for the tail of the grid.
+  if (!find_tile2(p.cu_q, p.num_seqs, static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x), seq, q0))
+    return;                                                            // uniform for the CTA: nothing allocated yet
   const int qs = p.cu_q[seq], len_q = p.cu_q[seq + 1] - qs;
   const int ks = p.cu_k[seq], len_k = p.cu_k[seq + 1] - ks;
   const int off = len_k - len_q;
@@ -533,15 +540,16 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const bool edge = (key0 + TK > len_k) ||
                         (p.causal && (key0 + TK - 1 > tq0 + off || (p.window > 0 && key0 <= tq0 + TQ - 1 + off - p.window)));
       if (edge) {
+        // visible columns of this row inside the tile: [lo, hi] (one subtract and one unsigned compare per element)
+        const int hi = (p.causal ? min(len_k - 1, qi) : len_k - 1) - key0;
+        const int lo = (p.causal && p.window > 0) ? max(0, qi - p.window + 1 - key0) : 0;
+        const unsigned span = hi >= lo ? static_cast<unsigned>(hi - lo) : 0u;
+        const bool none = hi < lo;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kj = key0 + q4 * 32 + i;
-            bool keep = kj < len_k;
-            if (p.causal) keep = keep && (kj <= qi) && (p.window <= 0 || kj > qi - p.window);
-            if (!keep) sv[q4][i] = 0xff800000u;          // -inf
-          }
+          for (int i = 0; i < 32; ++i)
+            if (none || static_cast<unsigned>(q4 * 32 + i - lo) > span) sv[q4][i] = 0xff800000u;   // -inf
       }
       float mx4[4];
 #pragma unroll
@@ -786,6 +794,7 @@ struct BwdParams {
   int num_seqs;
   int H, KV;
   float* dq_acc;            // (Tq, H, HD) fp32, zero-initialised by the caller
+  int* dq_sem;              // deterministic mode: one counter per (query tile, head), zeroed by the caller; else NULL
   __nv_bfloat16* dk;        // (Tk, KV, HD) contiguous
   __nv_bfloat16* dv;
   const float* lse;         // (H, Tq)
@@ -852,7 +861,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int kvh = blockIdx.y;
   const int rep = p.H / p.KV;
   int seq = 0, k0 = 0;
-  if (!find_tile(p.cu_k, p.num_seqs, blockIdx.x, seq, k0)) return;
+  // Blocks are handed out in increasing blockIdx.  Unordered dQ: ascending key tiles, so the causal key tiles with the
+  // most query tiles start first.  Ordered dQ: DEscending key tiles, so every CTA only ever waits for CTAs that were
+  // handed out before it (a CTA that waited for a later one could fill the GPU with waiters and starve it).
+  const int tile_x = p.dq_sem != nullptr ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)
+                                         : static_cast<int>(blockIdx.x);
+  if (!find_tile(p.cu_k, p.num_seqs, tile_x, seq, k0)) return;
   const int qs = p.cu_q[seq], len_q = p.cu_q[seq + 1] - qs;
   const int ks = p.cu_k[seq], len_k = p.cu_k[seq + 1] - ks;
   const int off = len_k - len_q;
@@ -862,6 +876,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   i_lo = (i_lo / 128) * 128;
   const int n_qt = i_hi > i_lo ? (i_hi - i_lo + 127) / 128 : 0;
   const int n_iter = n_qt * rep;
+  int qtile_base = 0;                                   // index of this sequence's first query tile (semaphores)
+  if (p.dq_sem != nullptr)
+    for (int s2 = 0; s2 < seq; ++s2) qtile_base += (p.cu_q[s2 + 1] - p.cu_q[s2] + 127) / 128;
+  const int n_kt = (len_k + 127) / 128;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -1023,35 +1041,52 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (lane == 0) mbar_arrive(pds_full);
       if (!(ok = mbar_wait(dq_full, ph, abort_flag, 231))) break;
       tc_fence_after();
-      // dQ tile: TMEM -> registers -> shared (XOR-swizzled so both the row-per-lane writes and the column-per-lane
-      // reads are conflict free) -> fp32 atomics that a warp issues on 32 consecutive addresses (one line each).
-      // The P / dS tiles are dead once dq_full has fired, so their 64 KB hold the fp32 tile.  Each warp drains its own
-      // half of the columns of its 32 rows.
-      float* sq = reinterpret_cast<float*>(sP);
+      // dQ tile: tensor memory -> registers -> vector reductions into the fp32 workspace, one row per thread (eight
+      // 16-byte red.v4 per 32 columns).  Each warp drains its own half of the columns of its 32 rows.
       constexpr int HC = HD / 2;
+      int* sem = nullptr;
+      if (p.dq_sem != nullptr) {
+        // deterministic order: wait until the key tiles above this one have added their share of this query tile
+        // (word 0 of the array is the give-up flag, the counters follow it)
+        sem = p.dq_sem + 1 + (static_cast<size_t>(qtile_base + qt / 128)) * p.H + h;
+        const int j_hi = p.causal ? min(n_kt - 1, (qt + 127 + off) / 128) : n_kt - 1;
+        const int expected = j_hi - k0 / 128;
+        if (lane == 0 && expected > 0) {
+          uint32_t spins = 0;
+          volatile int* gave_up = p.dq_sem;
+          while (!*gave_up && ld_acquire_gpu_s32(sem) < expected) {
+            // give up: the order is lost, not data.  The flag makes every later wait of this launch return at once,
+            // so one lost turn costs one time limit (about a second), not one per tile.
+            if (++spins > (1u << 21) || *abort_flag) { *gave_up = 1; set_error(4, 240); break; }
+            __nanosleep(32);
+          }
+        }
+        __syncwarp();
+      }
+      float* dq_row = p.dq_acc + ((static_cast<size_t>(qs + (vq ? i : 0))) * p.H + h) * HD;
 #pragma unroll 1
       for (int cb = half * HC; cb < half * HC + HC; cb += 32) {
         uint32_t v[32];
         tmem_ld_32x32(tm_dQ + lane_base + cb, v);
         tmem_ld_wait();
+        if (vq) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) sq[r * HD + cb + (e ^ lane)] = __uint_as_float(v[e]);
+          for (int e = 0; e < 32; e += 4)
+            red_add_v4_f32(dq_row + cb + e, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
+                           __uint_as_float(v[e + 3]));
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_empty);       // TMEM columns are free: the next S / dP may be issued now
-      for (int rr = 0; rr < 32; ++rr) {
-        const int ii = qt + quad * 32 + rr;
-        if (ii >= len_q) break;
-        float* dq_row = p.dq_acc + ((static_cast<size_t>(qs + ii)) * p.H + h) * HD;
-        const float* srow = sq + (quad * 32 + rr) * HD;
-#pragma unroll
-        for (int cb = half * HC; cb < half * HC + HC; cb += 32) atomicAdd(dq_row + cb + lane, srow[cb + (lane ^ rr)]);
+      if (sem != nullptr) {
+        // all eight warps' reductions must be visible before the next key tile in the order may add
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(stage_bar);
+        if (!(ok = mbar_wait(stage_bar, ph, abort_flag, 232))) break;
+        if (warp == 2 && lane == 0) red_release_gpu_add_s32(sem, 1);
       }
-      // all eight warps must be done with the staging area before anyone writes the next P / dS (bounded wait)
-      __syncwarp();
-      if (lane == 0) mbar_arrive(stage_bar);
-      if (!(ok = mbar_wait(stage_bar, ph, abort_flag, 232))) break;
     }
     // dK / dV of this key tile (thread = key row)
     constexpr int HC2 = HD / 2;
@@ -1127,8 +1162,11 @@ extern "C" {
 // dout / q / out (Tq, H, hd), k / v (Tk, KV, hd) bf16 with token strides; lse (H, Tq) from the forward.
 // Workspaces supplied by the caller: delta (H, Tq) fp32, dq_acc (Tq, H, hd) fp32 ZEROED.
 // Outputs: dq (bf16, converted from dq_acc), dk, dv (Tk, KV, hd) bf16 contiguous, every row written.
+// dq_sem: NULL, or 1 + (sum over sequences of ceil(len_q / 128)) x H int32 words, ZEROED (word 0 is the kernel's
+//   give-up flag, the rest one counter per (query tile, head)): makes the dQ summation order
+// fixed (bit-reproducible gradients) at the price of ordering the CTAs that share a query tile.
 int ftb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse,
-                 float* delta, float* dq_acc, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k,
+                 float* delta, float* dq_acc, int* dq_sem, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k,
                  int num_seqs, int total_q, int total_k, int H, int KV, int hd, long q_stride, long k_stride,
                  long v_stride, long do_stride, long o_stride, float scale, float softcap, int causal, int window,
                  int max_tiles, cudaStream_t stream) {
@@ -1152,7 +1190,7 @@ int ftb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, 
   if (rc) return rc;
   BwdParams p;
   p.cu_q = cu_q; p.cu_k = cu_k; p.num_seqs = num_seqs; p.H = H; p.KV = KV;
-  p.dq_acc = dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.lse = lse; p.delta = delta;
+  p.dq_acc = dq_acc; p.dq_sem = dq_sem; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.lse = lse; p.delta = delta;
   p.total_q = total_q; p.scale = scale; p.softcap = softcap; p.causal = causal; p.window = window;
   if (softcap > 0.f)
     rc = (hd == 128) ? launch_bwd<128, true>(tq, tdo, tk, tv, p, max_tiles, stream)

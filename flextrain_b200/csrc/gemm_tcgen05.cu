@@ -41,6 +41,12 @@ struct GemmParams {
   // split-K (plain mode only): the K range is cut into split_k slices of k_per_split elements; slice s of every output
   // tile is a work item of its own and lands in D + s * M * ldd (an fp32 workspace), to be summed by splitk_reduce.
   int split_k, k_per_split;
+  // gated-FFN epilogues of the two-SM kernel (EPI 1 / 2, see gemm2_kernel)
+  int glu_F, glu_kind;       // F = ffn width (columns of one half); kind 0 SwiGLU, 1 GeGLU(tanh)
+  void* glu_act;             // (M, F) bf16: activation output
+  int glu_ld_act;
+  const void* glu_x13;       // EPI 2: saved forward [gate | up] (M, 2F) bf16
+  int glu_ld_x13;
   // ---- tensor-parallel fused modes (comm_mode != 0); rows are split into `world` panels of `panel_rows`
   //  1  all-gather -> GEMM: A's row panel p lives on rank p.  Warps 6-7 of every CTA pull the remote panels
   //     from the peers' staging buffers into the local one (plain peer loads, each byte crosses NVLink once),
@@ -49,6 +55,7 @@ struct GemmParams {
   //     straight into the owner's staging slot for this rank (peer stores, tile by tile under the math);
   //     a small reduce kernel on the owner then sums the `world` slots.
   int comm_mode, world, rank, panel_rows;
+  int pull_threads;          // mode 1: 1 = pull with per-thread 16-byte loads (two warps) instead of bulk copies
   const void* a_peer[MAX_RANKS];
   void* a_local;
   long panel_bytes;
@@ -78,6 +85,8 @@ struct SmemLayout {
 
 // Reduce-scatter epilogue staging: 4 epilogue warps x (32 rows x 128 bf16 columns).
 constexpr int RS_STAGE_BYTES = 4 * 32 * 256;
+// All-gather mode: two shared-memory buffers of this size carry the remote panels (peer -> shared -> local staging).
+constexpr int PULL_CHUNK_BYTES = 16384;
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int per_group = GROUP_M * tiles_n;
@@ -167,6 +176,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 4);
+    }
+    if constexpr (COMM == 1) {           // completion barriers of the two peer-pull buffers
+      mbar_init(full_bar + 20, 1);
+      mbar_init(full_bar + 21, 1);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -370,6 +383,59 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
     if constexpr (COMM == 1) {
+      if (!p.pull_threads) {
+        // One thread streams this CTA's share of the remote panels through shared memory with bulk copies:
+        // peer memory -> 16 KB buffer (completion on an mbarrier) -> local staging buffer (bulk store).  Two buffers,
+        // so each CTA keeps two remote reads in flight (148 CTAs x 32 KB outstanding, enough to cover NVLink latency
+        // at full bandwidth) and the copy costs one issuing thread instead of two warps' load/store slots.
+        if (warp == 6 && lane == 0) {
+          constexpr long CH = PULL_CHUNK_BYTES;
+          uint8_t* pbuf = smem + L::BAR_OFFSET + 256;
+          uint64_t* pull_bar = full_bar + 20;
+          const long per_panel = (p.panel_bytes + CH - 1) / CH;
+          const long total = per_panel * (p.world - 1);
+          auto locate = [&](long g, int& pn, long& off, uint32_t& n) {
+            pn = (p.rank + 1 + static_cast<int>(g / per_panel)) % p.world;
+            off = (g % per_panel) * CH;
+            n = static_cast<uint32_t>(min(CH, p.panel_bytes - off));
+          };
+          auto issue = [&](long g, int buf) {
+            int pn; long off; uint32_t n;
+            locate(g, pn, off, n);
+            mbar_expect_tx(&pull_bar[buf], n);
+            bulk_load_g2s(pbuf + buf * CH, reinterpret_cast<const char*>(p.a_peer[pn]) + pn * p.panel_bytes + off, n,
+                          &pull_bar[buf]);
+          };
+          auto publish = [&](int pn, long moved) {
+            bulk_wait_all();                                   // the panel's stores have been written
+            asm volatile("fence.proxy.async;" ::: "memory");
+            __threadfence();
+            atomicAdd(p.panel_counter + pn, static_cast<unsigned long long>(moved));
+          };
+          long g = blockIdx.x, moved = 0;
+          int k = 0, cur = -1;
+          uint32_t phases = 0;
+          if (g < total) issue(g, 0);
+          for (; g < total; g += gridDim.x, ++k) {
+            const int buf = k & 1;
+            if (g + gridDim.x < total) {
+              bulk_wait_read_all();                            // the other buffer's last store has left shared memory
+              issue(g + gridDim.x, buf ^ 1);
+            }
+            if (!mbar_wait(&pull_bar[buf], (phases >> buf) & 1u, abort_flag, 30)) break;
+            phases ^= 1u << buf;
+            int pn; long off; uint32_t n;
+            locate(g, pn, off, n);
+            if (pn != cur && cur >= 0) { publish(cur, moved); moved = 0; }
+            cur = pn;
+            bulk_store_s2g(reinterpret_cast<char*>(p.a_local) + pn * p.panel_bytes + off, pbuf + buf * CH, n);
+            bulk_commit();
+            moved += n;
+          }
+          if (cur >= 0) publish(cur, moved);
+          bulk_wait_all();                                     // nothing of this thread's copies outlives the kernel
+        }
+      } else {
       const int t = threadIdx.x - 192;                       // 0..63
       const long stride = static_cast<long>(gridDim.x) * 64;
       const long n16 = p.panel_bytes >> 4;
@@ -393,6 +459,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) moved += __shfl_xor_sync(0xffffffffu, moved, o);
         if (lane == 0 && moved) atomicAdd(p.panel_counter + pn, static_cast<unsigned long long>(moved));
+      }
       }
     }
   } else {
@@ -604,7 +671,7 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, int GROUPED, int COMM = 0>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, GROUPED, COMM>;
-  constexpr int SMEM = L::TOTAL + (COMM == 2 ? RS_STAGE_BYTES : 0);
+  constexpr int SMEM = L::TOTAL + (COMM == 2 ? RS_STAGE_BYTES : 0) + (COMM == 1 ? 2 * PULL_CHUNK_BYTES : 0);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -629,7 +696,31 @@ constexpr int ST2 = 6;
 constexpr int STAGE2_BYTES = 2 * BM * BK * 2;   // A (128 x 64) + B half (128 x 64)
 constexpr int SMEM2_TOTAL = ST2 * STAGE2_BYTES + 256 + 1024;
 
-template <bool A_MN, bool B_MN>
+// act(g) and d act / d g of the gate activation (same formulas as the stand-alone SwiGLU / GeGLU kernels)
+__device__ __forceinline__ void glu_act_grad(float g, int kind, float& a, float& da) {
+  if (kind == 0) {
+    const float sg = 1.f / (1.f + __expf(-g));
+    a = g * sg;
+    da = sg * (1.f + g * (1.f - sg));
+  } else {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    const float t = tanhf(k0 * (g + k1 * g * g * g));
+    a = 0.5f * g * (1.f + t);
+    da = 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
+  }
+}
+
+// EPI selects the epilogue:
+//   0  D = alpha * acc + beta * C + bias
+//   1  gated-FFN forward.  B is the stacked [W_gate ; W_up] (2F x K, K-major).  A tile is 256 rows x (128 gate + 128 up)
+//      columns: CTA 0 of the pair stages the gate rows of B, CTA 1 the up rows F below them, so the pair's accumulator
+//      holds gate in columns 0..127 and up in 128..255.  The epilogue stores both halves into D (M x 2F, kept for the
+//      backward) and act = act_fn(gate) * up into glu_act (M x F): the separate activation pass and its re-read of
+//      the projection disappear (flextrain/ops/_kernels/swiglu.py:9-45 is that pass in the reference).
+//   2  gated-FFN backward.  The accumulator is dact = dy · W_down; the epilogue reads the saved gate / up values and
+//      writes dgate, dup into D (M x 2F) and the re-emitted activation into glu_act; dact never reaches memory
+//      (flextrain/ops/_kernels/swiglu.py:46-100 reads it back from HBM).
+template <bool A_MN, bool B_MN, int EPI = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -645,7 +736,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const uint32_t cta = cluster_ctarank();
   const bool leader = cta == 0;
   const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
-  const int tiles_n = (p.N + BN2 - 1) / BN2;
+  const int tiles_n = EPI == 1 ? p.glu_F / (BN2 / 2) : (p.N + BN2 - 1) / BN2;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + BK - 1) / BK;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
@@ -677,7 +768,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
         const int row0 = tm * 2 * BM + static_cast<int>(cta) * BM;      // this CTA's 128 rows of A
-        const int col0 = tn * BN2 + static_cast<int>(cta) * (BN2 / 2);  // this CTA's half of B's N rows
+        // this CTA's half of B's N rows (gated forward: 128 gate rows for CTA 0, the matching up rows for CTA 1)
+        const int col0 = EPI == 1 ? tn * (BN2 / 2) + static_cast<int>(cta) * p.glu_F
+                                  : tn * BN2 + static_cast<int>(cta) * (BN2 / 2);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 50))) break;
           uint8_t* sa = smem + stage * STAGE2_BYTES;
@@ -743,12 +836,106 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
       const int row0 = tm * 2 * BM + static_cast<int>(cta) * BM;
       const int rows = min(BM, p.M - row0);
-      if (!(ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 70))) break;
-      tc_fence_after();
       const int r_in = quad * 32 + lane;
       const bool row_ok = r_in < rows;
       const size_t row = static_cast<size_t>(row0 + r_in);
+      // gated-FFN backward: saved gate / up values of 32 columns, fetched one step ahead of their use (the first
+      // step is issued before the wait for the accumulator, it does not depend on the MMAs)
+      [[maybe_unused]] uint4 xg[4], xu[4];
+      [[maybe_unused]] auto fetch_x13 = [&](int col) {
+        const __nv_bfloat16* xrow = reinterpret_cast<const __nv_bfloat16*>(p.glu_x13) + row * p.glu_ld_x13;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (row_ok && col + 8 * q < p.N) {
+            xg[q] = __ldg(reinterpret_cast<const uint4*>(xrow + col + 8 * q));
+            xu[q] = __ldg(reinterpret_cast<const uint4*>(xrow + p.glu_F + col + 8 * q));
+          }
+        }
+      };
+      if constexpr (EPI == 2) fetch_x13(tn * BN2);
+      if (!(ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 70))) break;
+      tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN2;
+      if constexpr (EPI == 1) {
+        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + row * p.ldd;
+        __nv_bfloat16* arow = reinterpret_cast<__nv_bfloat16*>(p.glu_act) + row * p.glu_ld_act;
+#pragma unroll 1
+        for (int c = 0; c < BN2 / 2; c += 32) {
+          const int col = tn * (BN2 / 2) + c;
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(taddr + c, rg);
+          tmem_ld_32x32(taddr + BN2 / 2 + c, ru);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 og, ou, oa;
+              __nv_bfloat162* g2 = reinterpret_cast<__nv_bfloat162*>(&og);
+              __nv_bfloat162* u2 = reinterpret_cast<__nv_bfloat162*>(&ou);
+              __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&oa);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                g2[j] = __floats2bfloat162_rn(__uint_as_float(rg[i + 2 * j]), __uint_as_float(rg[i + 2 * j + 1]));
+                u2[j] = __floats2bfloat162_rn(__uint_as_float(ru[i + 2 * j]), __uint_as_float(ru[i + 2 * j + 1]));
+                // the activation is taken from the ROUNDED gate / up, exactly what the backward will read back
+                const float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
+                float a0, a1, d0, d1;
+                glu_act_grad(gf.x, p.glu_kind, a0, d0);
+                glu_act_grad(gf.y, p.glu_kind, a1, d1);
+                a2[j] = __floats2bfloat162_rn(a0 * uf.x, a1 * uf.y);
+              }
+              *reinterpret_cast<uint4*>(drow + col + i) = og;
+              *reinterpret_cast<uint4*>(drow + p.glu_F + col + i) = ou;
+              *reinterpret_cast<uint4*>(arow + col + i) = oa;
+            }
+          }
+        }
+      }
+      if constexpr (EPI == 2) {
+        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + row * p.ldd;
+        __nv_bfloat16* arow = reinterpret_cast<__nv_bfloat16*>(p.glu_act) + row * p.glu_ld_act;
+#pragma unroll 1
+        for (int c = 0; c < BN2; c += 32) {
+          const int col = tn * BN2 + c;
+          if (col >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          uint4 cg[4], cu[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) { cg[q] = xg[q]; cu[q] = xu[q]; }
+          if (c + 32 < BN2 && col + 32 < p.N) fetch_x13(col + 32);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int i = 8 * q;
+              if (col + i < p.N) {
+                const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&cg[q]);
+                const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&cu[q]);
+                uint4 odg, odu, oa;
+                __nv_bfloat162* dg2 = reinterpret_cast<__nv_bfloat162*>(&odg);
+                __nv_bfloat162* du2 = reinterpret_cast<__nv_bfloat162*>(&odu);
+                __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&oa);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
+                  const float da0 = __uint_as_float(r[i + 2 * j]) * p.alpha, da1 = __uint_as_float(r[i + 2 * j + 1]) * p.alpha;
+                  float a0, a1, d0, d1;
+                  glu_act_grad(gf.x, p.glu_kind, a0, d0);
+                  glu_act_grad(gf.y, p.glu_kind, a1, d1);
+                  a2[j] = __floats2bfloat162_rn(a0 * uf.x, a1 * uf.y);
+                  dg2[j] = __floats2bfloat162_rn(da0 * uf.x * d0, da1 * uf.y * d1);
+                  du2[j] = __floats2bfloat162_rn(da0 * a0, da1 * a1);
+                }
+                *reinterpret_cast<uint4*>(drow + col + i) = odg;
+                *reinterpret_cast<uint4*>(drow + p.glu_F + col + i) = odu;
+                *reinterpret_cast<uint4*>(arow + col + i) = oa;
+              }
+            }
+          }
+        }
+      }
+      if constexpr (EPI == 0) {
 #pragma unroll 1
       for (int c = 0; c < BN2; c += 32) {
         const int col = tn * BN2 + c;
@@ -805,6 +992,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&tempty_bar[acc]);   // 4 warps x 2 CTAs release the accumulator
@@ -821,9 +1009,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   }
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int EPI = 0>
 static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  auto kern = gemm2_kernel<A_MN, B_MN>;
+  auto kern = gemm2_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_TOTAL);
@@ -883,6 +1071,7 @@ static int dispatch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUten
 
 using namespace ftb;
 
+static int g_tp_pull_threads = 0;
 static int g_use_2cta = 1;    // ftb_gemm_set_two_sm(0) falls back to the one-SM kernel for every shape
 static int g_sm_count = 0;
 static int sm_count() {
@@ -996,6 +1185,90 @@ int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const fl
 }
 
 void ftb_gemm_set_two_sm(int on) { g_use_2cta = on; }
+// all-gather -> GEMM: 1 = remote panels pulled by two warps of 16-byte loads, 0 (default) = by bulk copies
+void ftb_gemm_set_tp_pull_threads(int on) { g_tp_pull_threads = on; }
+
+// Gated-FFN forward in one kernel (two-SM tiles):  [gate | up] = X (M, K) @ W13 (2F, K)^T  ->  x13 (M, 2F), and
+// act = act_fn(gate) * up -> act (M, F).  F must be a multiple of 128; X row-major with leading dimension lda,
+// W13 contiguous rows (ldb), x13 leading dimension ld13, act leading dimension ld_act; kind 0 SwiGLU, 1 GeGLU(tanh).
+int ftb_gemm_glu_fwd(const void* X, const void* W13, void* x13, void* act, int M, int F, int K, int lda, int ldb,
+                     int ld13, int ld_act, int kind, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return 0;
+  if (K <= 0) return -1;
+  if ((F % 128) || (lda & 7) || (ldb & 7) || (ld13 & 7) || (ld_act & 7) || (reinterpret_cast<uintptr_t>(X) & 15) ||
+      (reinterpret_cast<uintptr_t>(W13) & 15) || (reinterpret_cast<uintptr_t>(x13) & 15) ||
+      (reinterpret_cast<uintptr_t>(act) & 15))
+    return -2;
+  CUtensorMap ta, tb;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {BK, BM};
+    rc = make_tmap(&ta, X, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)(2 * F)};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {BK, BM};
+    rc = make_tmap(&tb, W13, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  GemmParams p;
+  p.M = M; p.N = 2 * F; p.K = K; p.ldd = ld13; p.ldc = ld13; p.alpha = 1.f; p.beta = 0.f;
+  p.D = x13; p.C = x13; p.bias = nullptr; p.d_fp32 = 0;
+  p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0; p.split_k = 1; p.k_per_split = 0;
+  p.glu_F = F; p.glu_kind = kind; p.glu_act = act; p.glu_ld_act = ld_act; p.glu_x13 = nullptr; p.glu_ld_x13 = 0;
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * (F / 128);
+  int grid = sm_count() & ~1;
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas & ~1;
+  if (2 * tiles < grid) grid = 2 * tiles;
+  if (grid < 2) grid = 2;
+  return launch2<false, false, 1>(ta, tb, p, grid, stream);
+}
+
+// Gated-FFN backward in one kernel:  dact = dY (M, K) @ W2 (K, F)  (never stored);  from the saved x13 = [gate | up]
+// the epilogue writes dx13 = [dgate | dup] (M, 2F) and the re-emitted activation act (M, F).  F a multiple of 8.
+int ftb_gemm_glu_bwd(const void* dY, const void* W2, const void* x13, void* dx13, void* act, int M, int F, int K,
+                     int lda, int ldb, int ld13, int ldd13, int ld_act, int kind, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return 0;
+  if (K <= 0) return -1;
+  if ((F & 7) || (lda & 7) || (ldb & 7) || (ld13 & 7) || (ldd13 & 7) || (ld_act & 7) ||
+      (reinterpret_cast<uintptr_t>(dY) & 15) || (reinterpret_cast<uintptr_t>(W2) & 15) ||
+      (reinterpret_cast<uintptr_t>(x13) & 15) || (reinterpret_cast<uintptr_t>(dx13) & 15) ||
+      (reinterpret_cast<uintptr_t>(act) & 15))
+    return -2;
+  CUtensorMap ta, tb;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {BK, BM};
+    rc = make_tmap(&ta, dY, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)F, (uint64_t)K};       // W2 (K = d_model rows, F columns): MN-major B
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_tmap(&tb, W2, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  GemmParams p;
+  p.M = M; p.N = F; p.K = K; p.ldd = ldd13; p.ldc = ldd13; p.alpha = 1.f; p.beta = 0.f;
+  p.D = dx13; p.C = dx13; p.bias = nullptr; p.d_fp32 = 0;
+  p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.panel_rows = 0; p.split_k = 1; p.k_per_split = 0;
+  p.glu_F = F; p.glu_kind = kind; p.glu_act = act; p.glu_ld_act = ld_act; p.glu_x13 = x13; p.glu_ld_x13 = ld13;
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((F + BN2 - 1) / BN2);
+  int grid = sm_count() & ~1;
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas & ~1;
+  if (2 * tiles < grid) grid = 2 * tiles;
+  if (grid < 2) grid = 2;
+  return launch2<false, true, 2>(ta, tb, p, grid, stream);
+}
 
 // Split-K variant for small outputs with a long reduction (the rank-r LoRA gradients: M or N = r, K = tokens): the K
 // range is cut into `splits` slices so that tiles x splits work items fill the GPU instead of a handful of CTAs each
@@ -1184,6 +1457,7 @@ int ftb_gemm_bf16_tp(int mode, const void* A, void* const* a_peer, unsigned long
   p.D = D; p.C = D; p.bias = nullptr; p.d_fp32 = d_fp32;
   p.num_groups = 0; p.offsets = nullptr; p.max_tiles = 0;
   p.comm_mode = mode; p.world = world; p.rank = rank; p.panel_rows = panel_rows; p.split_k = 1; p.k_per_split = 0;
+  p.pull_threads = g_tp_pull_threads;
   p.a_local = const_cast<void*>(A); p.panel_bytes = (long)panel_rows * lda * 2; p.panel_counter = panel_counter;
   p.d_slot_stride = d_slot_stride;
   for (int i = 0; i < MAX_RANKS; ++i) {

@@ -254,16 +254,15 @@ class ActiveModel:
         norm before scaling)."""
         self.step_num += 1
         grad_scale = 1.0
+        sharded = self.dp is not None and getattr(self.dp, "m", None) is not None      # reduced gradients live as shards
         if max_grad_norm is not None:
-            if self.dp is not None and getattr(self.dp, "m", None) is not None:
-                raise NotImplementedError("gradient clipping needs the whole gradient on every rank: use "
-                                          "FTB_DP_BACKEND=collective (the peer-memory path keeps reduced gradients "
-                                          "as shards)")
-            self.last_grad_norm = self.grad_norm()
+            self.last_grad_norm = self.dp.grad_norm(self) if sharded else self.grad_norm()
             if self.last_grad_norm > max_grad_norm:
                 grad_scale = max_grad_norm / (self.last_grad_norm + 1e-6)
         with _nvtx("Step"):
-            if self.dp is not None:
+            if sharded:
+                rc = self.dp.step(self, grad_scale)
+            elif self.dp is not None:
                 rc = self.dp.step(self) if grad_scale == 1.0 else self._step_local(grad_scale)
             else:
                 rc = self._step_local(grad_scale)

@@ -82,6 +82,9 @@ def save_training_state(am, out_dir: str, extra: Optional[dict] = None) -> str:
         for key, tensors in getattr(dp, "local_state", {}).items():
             for n, t in tensors.items():
                 state[f"dp.local.{key}.{n}"] = keep(t)
+        for key, tensors in getattr(dp, "owned_state", {}).items():       # Muon momentum of the tensors this rank owns
+            for n, t in tensors.items():
+                state[f"dp.owned.{key}.{n}"] = keep(t)
     else:
         owner = {s.key: s.param for _, _, spec in ([("embed", -1, am.embed.param_spec), ("head", -1, am.head.param_spec)]
                                                    + [("layer", l, la.param_spec) for l, la in enumerate(am.layers)])
@@ -147,6 +150,9 @@ def load_training_state(am, src_dir: str, strict: bool = True) -> dict:
         for key, tensors in getattr(dp, "local_state", {}).items():
             for n, t in tensors.items():
                 t.copy_(fetch(f"dp.local.{key}.{n}", True))
+        for key, tensors in getattr(dp, "owned_state", {}).items():
+            for n, t in tensors.items():
+                t.copy_(fetch(f"dp.owned.{key}.{n}", True))
     else:
         owner = {s.key: s.param for _, _, spec in ([("embed", -1, am.embed.param_spec), ("head", -1, am.head.param_spec)]
                                                    + [("layer", l, la.param_spec) for l, la in enumerate(am.layers)])

@@ -1,9 +1,10 @@
 """Dense gated FFN (SwiGLU / tanh-GeGLU) with hand-written forward / recompute / backward.
 
 ``w_1`` = gate, ``w_3`` = up, ``w_2`` = down (names as in flextrain/io/arch/llama.py:10-28).  Gate and
-up are one GEMM writing ``x13 (T, 2F) = [gate | up]`` (tier 3); the down projection adds the residual
-in its epilogue; the backward activation kernel re-emits ``act`` for the down-proj weight gradient
-(flextrain/nn/blocks/ffn_dense.py:58-304, fusions F1/F4).
+up are one GEMM writing ``x13 (T, 2F) = [gate | up]`` (tier 3) whose epilogue also emits the activation; the
+down projection adds the residual in its epilogue; in the backward the down projection's data gradient and the
+activation backward are one GEMM whose epilogue writes ``[dgate | dup]`` and re-emits ``act`` for the down-proj
+weight gradient (flextrain/nn/blocks/ffn_dense.py:58-304, fusions F1/F4, runs them as separate passes).
 """
 from __future__ import annotations
 
@@ -44,8 +45,11 @@ class GatedFFN:
 
     def fwd(self, h, x_resid, params, slot):
         F = self.cfg.ffn_dim
-        x13 = self.up.fwd(h, params, out=slot.out("x13", h.device))
-        act = ops.glu_fwd(x13[:, :F], x13[:, F:], self.cfg.kind)
+        if self.up.tp is None:
+            x13, act = ops.linear_glu_fwd(h, self.up.weight(params), self.cfg.kind, x13=slot.out("x13", h.device))
+        else:
+            x13 = self.up.fwd(h, params, out=slot.out("x13", h.device))
+            act = ops.glu_fwd(x13[:, :F], x13[:, F:], self.cfg.kind)
         return self.down.fwd(act, params, residual=x_resid)
 
     def recompute(self, h, params, slot) -> None:
@@ -56,9 +60,12 @@ class GatedFFN:
         """Returns ``(dh, dx13)``; the caller runs ``self.up.wgrad(dx13, h, ...)`` once ``h`` is re-emitted."""
         F = self.cfg.ffn_dim
         x13 = slot._t["x13"]
-        dact = self.down.dgrad(dx, params)
-        dx13 = torch.empty_like(x13)
-        _, _, act = ops.glu_bwd(dact, x13[:, :F], x13[:, F:], self.cfg.kind, dgate=dx13[:, :F], dup=dx13[:, F:])
+        if self.down.tp is None:
+            dx13, act = ops.linear_glu_bwd(dx, self.down.weight(params), x13, self.cfg.kind)
+        else:
+            dact = self.down.dgrad(dx, params)
+            dx13 = torch.empty_like(x13)
+            _, _, act = ops.glu_bwd(dact, x13[:, :F], x13[:, F:], self.cfg.kind, dgate=dx13[:, :F], dup=dx13[:, F:])
         self.down.wgrad(dx, act, params, grads)
         dh = self.up.dgrad(dx13, params)
         return dh, dx13

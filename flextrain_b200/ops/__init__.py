@@ -229,6 +229,53 @@ def glu_bwd(dact, gate, up, kind="swiglu", *, dgate=None, dup=None):
     return dg, du, act
 
 
+_GLU_FUSED = os.environ.get("FTB_GLU_FUSED", "1") == "1"
+
+
+def gemm_glu_fwd(x, w13, kind="swiglu", *, x13=None):
+    """The fused kernel itself (GPU only); ``linear_glu_fwd`` is the entry that falls back."""
+    return _kernels().gemm_glu_fwd(x, w13, kind, x13=x13)
+
+
+def gemm_glu_bwd(dy, w2, x13, kind="swiglu"):
+    return _kernels().gemm_glu_bwd(dy, w2, x13, kind)
+
+
+def _glu_fused_ok(x, w, F: int) -> bool:
+    if not (_GLU_FUSED and _cuda_bf16(x, w)):
+        return False
+    from . import cuda
+    return cuda.have("gemm_tcgen05") and cuda.gemm_glu_supported(x, w, F)
+
+
+def linear_glu_fwd(x, w13, kind="swiglu", *, x13=None):
+    """Gated-FFN up projection and activation: ``x13 = x @ w13^T`` (``w13 = [W_gate ; W_up]``), ``act = act_fn(gate) * up``.
+    On the GPU both come out of ONE two-SM tcgen05 GEMM (the activation is computed in the epilogue from the tile
+    that is being stored); elsewhere, or for shapes the kernel does not take, a GEMM followed by the activation pass.
+    Returns ``(x13, act)``."""
+    F = w13.shape[0] // 2
+    if _glu_fused_ok(x, w13, F):
+        _count()
+        _used("linear_glu_fwd", "ftb")
+        return gemm_glu_fwd(x, w13, kind, x13=x13)
+    x13 = linear_fwd(x, w13, out=x13)
+    return x13, glu_fwd(x13[:, :F], x13[:, F:], kind)
+
+
+def linear_glu_bwd(dy, w2, x13, kind="swiglu"):
+    """Backward of ``y = act(x13) @ w2^T`` down to ``x13``: returns ``(dx13 = [dgate | dup], act)``; ``act`` is re-emitted
+    for the down projection's weight gradient.  One fused GEMM on the GPU (``dact`` never reaches memory)."""
+    F = w2.shape[1]
+    if _glu_fused_ok(dy, w2, F) and x13.stride(1) == 1 and x13.stride(0) % 8 == 0 and x13.data_ptr() % 16 == 0:
+        _count()
+        _used("linear_glu_bwd", "ftb")
+        return gemm_glu_bwd(dy, w2, x13, kind)
+    dact = linear_dgrad(dy, w2)
+    dx13 = torch.empty_like(x13)
+    _, _, act = glu_bwd(dact, x13[:, :F], x13[:, F:], kind, dgate=dx13[:, :F], dup=dx13[:, F:])
+    return dx13, act
+
+
 def glu_bwd_weighted(dact_u, gate, up, w_row, kind="swiglu", *, dgate, dup):
     """Expert backward through the gated activation with the router weight folded in (one pass):
     ``dgate, dup`` from ``w_row * dact_u``; returns ``(act_w = w_row * act, dw_row = sum(dact_u * act, -1))``."""
@@ -537,7 +584,7 @@ rope_inv_freq = ref.rope_inv_freq
 # ``FTB_OP_TIMING=1`` brackets every leaf op of this module with CUDA events on the current stream and
 # ``timing_report()`` aggregates them by (op, shape): the per-kernel time table of a training step without a
 # profiler attached.  The events add host work, so a throughput number taken with it on is not a benchmark value.
-_TIMED_OPS = ("gemm", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "glu_fwd", "glu_bwd", "glu_bwd_weighted", "attention_fwd",
+_TIMED_OPS = ("gemm", "gemm_glu_fwd", "gemm_glu_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "glu_fwd", "glu_bwd", "glu_bwd_weighted", "attention_fwd",
               "attention_bwd", "softmax_ce_", "embedding_fwd", "embedding_bwd", "adamw_multi", "topk_route",
               "topk_route_bwd", "gather_rows", "moe_combine", "grouped_gemm", "grouped_wgrad", "l2norm_fwd",
               "gated_rmsnorm_fwd", "bias_grad")

@@ -36,8 +36,17 @@ def fwd(q, k, v, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, soft
     return out, lse
 
 
-def bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, softcap=0.0):
-    """Returns ``(dq, dk, dv)``; dk / dv cover all keys."""
+def deterministic_default() -> bool:
+    """``FTB_ATTN_DETERMINISTIC`` (default 1): fixed dQ summation order, as the reference asks of its flash back ends
+    (``deterministic=True``, flextrain/ops/_kernels/attention.py:227,302,378)."""
+    import os
+    return os.environ.get("FTB_ATTN_DETERMINISTIC", "1") != "0"
+
+
+def bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True, window=0, softcap=0.0,
+        deterministic=None):
+    """Returns ``(dq, dk, dv)``; dk / dv cover all keys.  ``deterministic`` (default: :func:`deterministic_default`)
+    orders the key tiles' additions to every query tile, so two runs give bit-identical dQ (dK / dV always are)."""
     lib = load("attention")
     if not hasattr(lib, "ftb_attn_bwd"):
         raise NotImplementedError
@@ -56,8 +65,10 @@ def bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, *, scale, causal=True
     delta = torch.empty(H, Tq, dtype=torch.float32, device=q.device)
     cu_q = cu_q.to(torch.int32)
     cu_k = cu_k.to(torch.int32)
+    det = deterministic_default() if deterministic is None else bool(deterministic)
+    sem = torch.zeros(1 + (Tq // 128 + nseq) * H, dtype=torch.int32, device=q.device) if det else None
     rc = lib.ftb_attn_bwd(_ptr(dout), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), _ptr(delta), _ptr(dq_acc),
-                          _ptr(dq), _ptr(dk), _ptr(dv), _ptr(cu_q), _ptr(cu_k), c_int(nseq), c_int(Tq), c_int(Tk),
+                          _ptr(sem), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(cu_q), _ptr(cu_k), c_int(nseq), c_int(Tq), c_int(Tk),
                           c_int(H), c_int(KV), c_int(hd), c_long(q.stride(0)), c_long(k.stride(0)),
                           c_long(v.stride(0)), c_long(dout.stride(0)), c_long(out.stride(0)), c_float(scale),
                           c_float(float(softcap or 0.0)), c_int(1 if causal else 0), c_int(int(window or 0)),

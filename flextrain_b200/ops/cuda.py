@@ -278,6 +278,52 @@ def glu_fwd(gate, up, kind="swiglu", out=None):
     return out
 
 
+def gemm_glu_supported(x, w, F: int, M_min: int = 512) -> bool:
+    """Shapes the two-SM gated-FFN kernels take: bf16, contiguous rows, F a multiple of 128, enough rows for 256-row
+    tiles to fill the GPU."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+            and x.stride(1) == 1 and w.stride(1) == 1 and F % 128 == 0 and x.shape[0] >= M_min
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_glu_fwd(x, w13, kind="swiglu", *, x13=None, act=None):
+    """``x13 = x @ w13^T`` (``w13`` = stacked ``[W_gate ; W_up]``, (2F, K)) and ``act = act_fn(gate) * up`` from the
+    same accumulator tile.  Returns ``(x13 (M, 2F), act (M, F))``."""
+    lib = load("gemm_tcgen05")
+    M, K = x.shape
+    F = w13.shape[0] // 2
+    assert w13.shape == (2 * F, K)
+    if x13 is None:
+        x13 = torch.empty(M, 2 * F, dtype=x.dtype, device=x.device)
+    if act is None:
+        act = torch.empty(M, F, dtype=x.dtype, device=x.device)
+    assert x13.shape == (M, 2 * F) and x13.stride(1) == 1 and act.shape == (M, F) and act.stride(1) == 1
+    rc = lib.ftb_gemm_glu_fwd(_ptr(x), _ptr(w13), _ptr(x13), _ptr(act), c_int(M), c_int(F), c_int(K),
+                              c_int(x.stride(0)), c_int(w13.stride(0)), c_int(x13.stride(0)), c_int(act.stride(0)),
+                              c_int(_KIND[kind]), c_int(GEMM_MAX_CTAS), _stream())
+    _check(rc, "ftb_gemm_glu_fwd")
+    return x13, act
+
+
+def gemm_glu_bwd(dy, w2, x13, kind="swiglu", *, dx13=None, act=None):
+    """Backward through the down projection's input and the gated activation in one kernel:
+    ``dact = dy @ w2`` (``w2`` (d, F)) stays in tensor memory; returns ``(dx13 = [dgate | dup] (M, 2F), act (M, F))``."""
+    lib = load("gemm_tcgen05")
+    M, K = dy.shape
+    F = w2.shape[1]
+    assert w2.shape[0] == K and x13.shape == (M, 2 * F) and x13.stride(1) == 1
+    if dx13 is None:
+        dx13 = torch.empty(M, 2 * F, dtype=dy.dtype, device=dy.device)
+    if act is None:
+        act = torch.empty(M, F, dtype=dy.dtype, device=dy.device)
+    rc = lib.ftb_gemm_glu_bwd(_ptr(dy), _ptr(w2), _ptr(x13), _ptr(dx13), _ptr(act), c_int(M), c_int(F), c_int(K),
+                              c_int(dy.stride(0)), c_int(w2.stride(0)), c_int(x13.stride(0)), c_int(dx13.stride(0)),
+                              c_int(act.stride(0)), c_int(_KIND[kind]), c_int(GEMM_MAX_CTAS), _stream())
+    _check(rc, "ftb_gemm_glu_bwd")
+    return dx13, act
+
+
 def glu_bwd(dact, gate, up, kind="swiglu", *, dgate=None, dup=None, emit_act=True):
     lib = load("elementwise")
     T, F = gate.shape

@@ -27,7 +27,7 @@ from __future__ import annotations
 
 from ctypes import c_float, c_int, c_long, c_uint, c_void_p
 from dataclasses import dataclass
-from typing import Dict, List
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
@@ -49,10 +49,14 @@ class Segment:
     begin: int = 0      # this rank's range
     count: int = 0
     shard_off: int = 0  # element offset in the rank's fp32 shard arrays
+    name: Optional[str] = None   # set for a tensor that one rank owns whole (matrix optimizers need the full gradient)
+    shape: Tuple[int, ...] = ()
+    owner: int = -1
 
 
-def build_segments(lb, p_base: int, g_base: int, no_decay_1d: bool = True) -> List[Segment]:
-    """Merge tensors that are adjacent in both buffers and share dtypes / decay into segments."""
+def build_segments(lb, p_base: int, g_base: int, no_decay_1d: bool = True, whole=()) -> List[Segment]:
+    """Merge tensors that are adjacent in both buffers and share dtypes / decay into segments.  Tensors named in
+    ``whole`` stay segments of their own (they are reduced to, and updated by, a single owner rank)."""
     segs: List[Segment] = []
     for t in lb.spec.trainable():
         if t.is_local_part:
@@ -61,7 +65,11 @@ def build_segments(lb, p_base: int, g_base: int, no_decay_1d: bool = True) -> Li
         go, gn, _, gdt = lb.g_layout[t.grad_name]
         decay = not (no_decay_1d and len(t.shape) == 1)
         s = Segment(p_base + po, g_base + go, t.numel, pdt, gdt, decay)
-        if segs:
+        if t.name in whole:
+            s.name, s.shape = t.name, tuple(t.shape)
+            segs.append(s)
+            continue
+        if segs and segs[-1].name is None:
             q = segs[-1]
             if (q.p_dtype == pdt and q.g_dtype == gdt and q.decay == decay
                     and q.p_off + q.numel * itemsize(pdt) == s.p_off and q.g_off + q.numel * itemsize(gdt) == s.g_off):
@@ -140,20 +148,41 @@ class P2PDataParallel(_Base):
         return {"device_alloc": lambda nbytes, tag: self.group.alloc(nbytes), "shard_opt": True}
 
     def attach(self, am) -> None:
-        from ..optim import AdamW
-        if not isinstance(am.optimizer, AdamW):
-            raise TypeError("the peer-memory data-parallel path implements sharded AdamW; use the collective "
-                            "backend for Muon / hybrid optimizers")
+        from ..optim import AdamW, HybridMuonAdamW, Muon, uses_muon
+        opt = am.optimizer
+        # Element-wise AdamW is sharded by element range.  Muon orthogonalises whole matrices, so each of its tensors is
+        # reduced to ONE owner rank (owners balanced by element count), updated there with the tcgen05 Newton-Schulz
+        # GEMMs and pushed to the peers' arenas by stores: the step's matrix work is split over the ranks instead of
+        # being repeated on each.
+        if isinstance(opt, AdamW):
+            self.adamw, self.muon, is_muon = opt, None, (lambda t: False)
+        elif isinstance(opt, Muon):
+            self.adamw, self.muon, is_muon = None, opt, (lambda t: True)
+        elif isinstance(opt, HybridMuonAdamW):
+            self.adamw, self.muon, is_muon = opt.adamw, opt.muon, uses_muon
+        else:
+            raise TypeError(f"the peer-memory data-parallel path knows AdamW, Muon and their hybrid, not {type(opt).__name__}")
         self.am = am
         bm = am.buffers
-        nd = am.optimizer.no_decay_1d
+        nd = self.adamw.no_decay_1d if self.adamw is not None else True
         off = 0
         keys = ["embed"] + list(range(len(am.layers))) + ["head"]
         lbs = {"embed": bm.embed, "head": bm.head, **{i: lb for i, lb in enumerate(bm.layers)}}
+        load = [0] * self.world
+        self.owned_state: Dict[object, Dict[str, torch.Tensor]] = {}     # Muon momentum of the tensors this rank owns
         for key in keys:
-            segs = build_segments(lbs[key], bm.p_off[key], bm.g_off[key], nd)
+            whole = {t.name for t in lbs[key].spec.trainable() if not t.is_local_part and is_muon(t)}
+            segs = build_segments(lbs[key], bm.p_off[key], bm.g_off[key], nd, whole)
             for s in segs:
-                s.begin, s.count = shard_range(s.numel, self.rank, self.world)
+                if s.name is not None:
+                    s.owner = min(range(self.world), key=lambda r: (load[r], r))
+                    load[s.owner] += s.numel
+                    s.begin, s.count = (0, s.numel) if s.owner == self.rank else (0, 0)
+                    if s.owner == self.rank:
+                        self.owned_state.setdefault(key, {})[s.name] = torch.zeros(
+                            s.shape, dtype=self.muon.state_dtype, device=self.device)
+                else:
+                    s.begin, s.count = shard_range(s.numel, self.rank, self.world)
                 s.shard_off = off
                 off += (s.count + 7) // 8 * 8
             self.units[key] = segs
@@ -196,7 +225,8 @@ class P2PDataParallel(_Base):
             self.opt_ring = [torch.empty(biggest, dtype=torch.float32, device=self.device) for _ in range(depth)]
         # deferred parameter all-gather ("opt+grad+param"): bf16 segments of attention layers are gathered by the
         # layer's first GEMM; everything else (norm weights, embedding, head, other layer kinds) is pushed eagerly
-        self.defer = getattr(am.ws, "shard", "") == "opt+grad+param"
+        # (element-range shards only: a matrix optimizer's owner pushes whole tensors right after its update)
+        self.defer = getattr(am.ws, "shard", "") == "opt+grad+param" and self.muon is None
         self.deferred_keys = set()
         if self.defer:
             for i, layer in enumerate(am.layers):
@@ -264,18 +294,44 @@ class P2PDataParallel(_Base):
         self._reduce("embed")
         self._reduce("head")
 
-    def step(self, am) -> int:
+    def grad_norm(self, am) -> float:
+        """Global L2 norm of the reduced gradient, from the shards: every rank squares its own fp32 range of each
+        replicated tensor (the alignment padding between ranges is never written and stays zero) plus its own slices
+        of tensor- / expert-parallel tensors, and one scalar all-reduce adds them up (one host read)."""
+        import torch.distributed as dist
+        cs = self.comm_stream
+        cs.wait_stream(am.streams.compute)
+        with torch.cuda.stream(cs):
+            sq = self.grad_shard.pow(2).sum()
+            for key, names in self.local_names.items():
+                bm = am.buffers
+                spec, grads = {"embed": (bm.embed.spec, bm.embed_grads()), "head": (bm.head.spec, bm.head_grads())}.get(
+                    key) or (bm.layers[key].spec, bm.grads(key))
+                for t in spec.trainable():
+                    if t.name in names and grads.get(t.grad_name) is not None:
+                        sq = sq + grads[t.grad_name].to(torch.float32).pow(2).sum()
+            dist.all_reduce(sq, group=self.pg)
+            out = float(sq.sqrt())
+        return out
+
+    def step(self, am, grad_scale: float = 1.0) -> int:
         from .. import ops
         opt = am.optimizer
         cs = self.comm_stream
         bm = am.buffers
         step = am.step_num
-        bc1, bc2 = 1.0 - opt.beta1 ** step, 1.0 - opt.beta2 ** step
+        if grad_scale != 1.0:                   # clipping: the reduced fp32 shard is what the sharded AdamW reads
+            with torch.cuda.stream(cs):
+                self.grad_shard.mul_(grad_scale)
+        ad = self.adamw
+        if ad is not None:
+            bc1, bc2 = 1.0 - ad.beta1 ** step, 1.0 - ad.beta2 ** step
         own_only = (c_void_p * 1)(bm.param_arena.c_ptrs[self.rank])       # a one-rank "group": no peer stores
         for key, segs in self.units.items():
             deferred = key in self.deferred_keys
-            groups = [([s for s in segs if not (deferred and s.p_dtype == torch.bfloat16)], False),
-                      ([s for s in segs if deferred and s.p_dtype == torch.bfloat16], True)]
+            elem = [s for s in segs if s.name is None]
+            groups = [([s for s in elem if not (deferred and s.p_dtype == torch.bfloat16)], False),
+                      ([s for s in elem if deferred and s.p_dtype == torch.bfloat16], True)]
             for glist, local in groups:
                 for i0 in range(0, len(glist), 16):
                     part = glist[i0:i0 + 16]
@@ -285,28 +341,44 @@ class P2PDataParallel(_Base):
                                                       cnt, ooff, dts, c_void_p(self.grad_shard.data_ptr()),
                                                       c_void_p(self.m.data_ptr()), c_void_p(self.v.data_ptr()),
                                                       c_int(1 if local else self.world), c_int(0 if local else self.rank),
-                                                      c_float(opt.lr), c_float(opt.beta1), c_float(opt.beta2),
-                                                      c_float(opt.eps), c_float(opt.weight_decay), c_float(bc1),
+                                                      c_float(ad.lr), c_float(ad.beta1), c_float(ad.beta2),
+                                                      c_float(ad.eps), c_float(ad.weight_decay), c_float(bc1),
                                                       c_float(bc2), c_uint(mask), c_void_p(cs.cuda_stream))
                     if rc != 0:
                         raise RuntimeError(f"ftb_comm_adamw_push failed ({rc})")
                     ops._count()
             if deferred:
                 self._stale.add(key)
+            mine = [s for s in segs if s.name is not None and s.owner == self.rank]
+            if mine:
+                mu = self.muon
+                pv = bm.embed_params() if key == "embed" else bm.head_params() if key == "head" else bm.params(key)
+                with torch.cuda.stream(cs):
+                    for s in mine:
+                        g = self.grad_shard[s.shard_off:s.shard_off + s.numel].view(s.shape)      # fp32, fully reduced
+                        ops.muon_step(pv[s.name], g, self.owned_state[key][s.name], lr=mu.lr, beta=mu.beta,
+                                      weight_decay=mu.weight_decay, ns_iters=mu.ns_iters, nesterov=mu.nesterov)
+                        nbytes = (s.numel * itemsize(s.p_dtype) + 15) // 16 * 16     # layout slots are padded past this
+                        rc = self.lib.ftb_comm_allgather_push(bm.param_arena.c_ptrs, c_long(s.p_off), c_long(nbytes),
+                                                              c_int(self.world), c_int(self.rank),
+                                                              c_void_p(cs.cuda_stream))
+                        if rc != 0:
+                            raise RuntimeError(f"ftb_comm_allgather_push failed ({rc})")
+                        ops._count()
         if self.local_names and self.opt_on_host:
-            self._step_local_streamed(am, opt, step)
+            self._step_local_streamed(am, opt, step, grad_scale)
         elif self.local_names:
             cs.wait_stream(am.streams.compute)
             with torch.cuda.stream(cs):
                 for key, names in self.local_names.items():
                     opt.step(bm.layers[key].spec, bm.params(key), bm.grads(key), self.local_state[key], step,
-                             only=set(names))
+                             grad_scale, only=set(names))
         # every peer's stores into my parameters have landed, and every peer is done reading my gradients
         self.group.signal_wait(self.barrier_slot, self.group.next_epoch(), cs)
         am.streams.compute.wait_stream(cs)
         return 0
 
-    def _step_local_streamed(self, am, opt, step: int) -> None:
+    def _step_local_streamed(self, am, opt, step: int, grad_scale: float = 1.0) -> None:
         """Update this rank's own slices with their optimizer state streaming through the host: unit k's state is
         copied into ring slot ``k % depth`` on the inbound stream while unit k-1 is updated on the comm stream and
         unit k-2 is written back on the outbound stream (one coalesced copy per unit and direction; the single-GPU
@@ -337,7 +409,8 @@ class P2PDataParallel(_Base):
             views = {k2: dev[o:o + c].view(shp) for k2, o, c, shp in self._state_layout[key]}
             cs.wait_event(loaded[i])
             with torch.cuda.stream(cs):
-                opt.step(bm.layers[key].spec, bm.params(key), bm.grads(key), views, step, only=set(self.local_names[key]))
+                opt.step(bm.layers[key].spec, bm.params(key), bm.grads(key), views, step, grad_scale,
+                         only=set(self.local_names[key]))
                 updated[i].record(cs)
             with torch.cuda.stream(st.outbound):
                 st.outbound.wait_event(updated[i])

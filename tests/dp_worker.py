@@ -15,6 +15,10 @@ def main():
     shard = "opt+grad"
     accum = backend.endswith("_accum")      # the step's batch in two fwd_bwd calls (gradient accumulation over calls)
     backend = backend.replace("_accum", "")
+    clip = 0.05 if backend.endswith("_clip") else None       # well below the norm of these gradients: every step clips
+    backend = backend.replace("_clip", "")
+    hybrid = backend.endswith("_muon")      # Muon for the hidden matrices, AdamW for the rest
+    backend = backend.replace("_muon", "")
     if backend == "p2p_param":              # peer-memory path with the parameter all-gather deferred into the QKV GEMM
         backend, shard = "p2p", "opt+grad+param"
     os.environ["FTB_DP_BACKEND"] = backend
@@ -25,14 +29,16 @@ def main():
     dims = dict(vocab_size=2048, n_layers=3, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, expert_dim=1408,
                 num_routed_experts=0, num_shared_experts=0, top_k=0, is_causal=True)
     gb = 4096
-    am = ft.from_dims(dims, arch="llama", optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32, weight_decay=0.01),
+    adamw = ft.AdamW(lr=1e-3, state_dtype=torch.float32, weight_decay=0.01)
+    am = ft.from_dims(dims, arch="llama",
+                      optimizer=ft.HybridMuonAdamW(muon=ft.Muon(lr=2e-3), adamw=adamw) if hybrid else adamw,
                       max_seq_len=256, max_global_batch_tokens=gb, max_gpu_mem_bytes=16 << 30,
                       max_host_mem_bytes=16 << 30, device=dev, world_size=world, rank=rank,
                       working_set=ft.WorkingSetConfig.simple(max_seq_len=256, max_global_batch_tokens=gb // world,
                                                              chunk=1024, round_tokens=1024, world_size=world,
                                                              shard=shard))
     src = ft.SyntheticTokenSource(2048, 256, seed=11)
-    losses = []
+    losses, norms = [], []
     for step in range(3):
         seqs = src.get_sequences(gb)[rank::world]
         if accum:
@@ -42,7 +48,9 @@ def main():
             st.loss_sum += st2.loss_sum
         else:
             st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / gb, total_tokens_per_step=gb)
-        assert am.step() == 0
+        assert am.step(max_grad_norm=clip) == 0
+        if clip is not None:
+            norms.append(am.last_grad_norm)
         t = torch.tensor([st.loss_sum], device=dev)
         dist.all_reduce(t)
         losses.append(float(t) / gb)
@@ -61,7 +69,7 @@ def main():
         same = all(torch.equal(allflat[0], f) for f in allflat)
         from flextrain_b200.ops import cuda as k
         torch.save({"params": flat, "losses": losses, "ranks_identical": same, "errors": k.device_error_words(),
-                    "libs": sorted(k._libs), "deferred_layers": deferred}, out_path)
+                    "libs": sorted(k._libs), "deferred_layers": deferred, "norms": norms}, out_path)
     dist.barrier()
     dist.destroy_process_group()
 

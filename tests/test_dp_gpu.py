@@ -67,3 +67,33 @@ def test_two_fwd_bwd_calls_per_step_match_one_call(tmp_path):
         assert abs(x - y) < 2e-3, (a["losses"], b["losses"])
     d = (a["params"] - b["params"]).abs()
     assert float(d.mean()) < 2e-5 and float(d.max()) < 5e-3, (float(d.mean()), float(d.max()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gradient_clipping_on_shards_matches_collective(tmp_path):
+    """``step(max_grad_norm=...)`` on the peer-memory path takes the norm from the reduced fp32 shards (one scalar
+    all-reduce) and scales the shard; the library-collective path clips whole replicated gradients."""
+    n = min(torch.cuda.device_count(), 4)
+    a = _run("p2p_clip", str(tmp_path / "p2p.pt"), n)
+    b = _run("collective_clip", str(tmp_path / "coll.pt"), n)
+    assert a["ranks_identical"] and all(v == 0 for v in a["errors"].values()), a["errors"]
+    assert len(a["norms"]) == 3 and all(x > 0.05 for x in a["norms"]), a["norms"]
+    for x, y in zip(a["norms"], b["norms"]):
+        assert abs(x - y) < 0.02 * y, (a["norms"], b["norms"])
+    d = (a["params"] - b["params"]).abs()
+    assert float(d.mean()) < 2e-4 and float(d.max()) < 2e-2, (float(d.mean()), float(d.max()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_hybrid_muon_on_peer_memory_path_matches_collective(tmp_path):
+    """Muon tensors are reduced to one owner rank each, updated there (Newton-Schulz on the tcgen05 GEMM) and pushed
+    to the peers by stores; AdamW tensors stay sharded by element range.  Against NCCL all-reduce + replicated step."""
+    n = min(torch.cuda.device_count(), 4)
+    a = _run("p2p_muon", str(tmp_path / "p2p.pt"), n)
+    b = _run("collective_muon", str(tmp_path / "coll.pt"), n)
+    assert a["ranks_identical"] and all(v == 0 for v in a["errors"].values()), a["errors"]
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 3e-2, (a["losses"], b["losses"])
+    d = (a["params"] - b["params"]).abs()
+    # Newton-Schulz in bf16 amplifies the bf16-vs-fp32 difference of the reduced gradient a little
+    assert float(d.mean()) < 5e-4 and float(d.max()) < 5e-2, (float(d.mean()), float(d.max()))

@@ -498,3 +498,73 @@ def test_gemm_split_k_small_outputs(M, N, K, ta, tb, out_dtype):
     assert _rel(got, want) < 6e-3, _rel(got, want)
     assert torch.equal(got, again)
     assert k.device_error_words().get("gemm_tcgen05", 0) == 0
+
+
+@pytest.mark.parametrize("case", ["causal_ragged", "prior_ctx_window"])
+def test_attention_bwd_deterministic_dq(case):
+    """With the key tiles' additions to each query tile ordered by the semaphore chain, two backward runs on the same
+    inputs give bit-identical dQ (dK / dV accumulate in tensor memory and always are); the unordered mode agrees with
+    it to fp32 round-off."""
+    from flextrain_b200.ops import attention_cuda as fa
+    from flextrain_b200.ops import cuda as kk
+    H, KV, hd = 8, 2, 128
+    if case == "causal_ragged":
+        lens_q, lens_k, window = [1024, 700, 333, 1], [1024, 700, 333, 129], 0
+    else:
+        lens_q, lens_k, window = [512, 384], [1152, 456], 300
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32, device=DEV)
+    q, k, v = _rand(sum(lens_q), H, hd), _rand(sum(lens_k), KV, hd), _rand(sum(lens_k), KV, hd)
+    do = _rand(sum(lens_q), H, hd)
+    kw = dict(scale=hd ** -0.5, window=window)
+    o, lse = fa.fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), **kw)
+    runs = [fa.bwd(do, q, k, v, o, lse, cu_q, cu_k, max(lens_q), max(lens_k), deterministic=True, **kw) for _ in range(3)]
+    for r in runs[1:]:
+        assert torch.equal(r[0], runs[0][0]) and torch.equal(r[1], runs[0][1]) and torch.equal(r[2], runs[0][2])
+    loose = fa.bwd(do, q, k, v, o, lse, cu_q, cu_k, max(lens_q), max(lens_k), deterministic=False, **kw)
+    assert _rel(loose[0], runs[0][0]) < 1e-3
+    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, **kw)
+    wq, wk, wv = ref.attention_bwd(do, q, k, v, ow, lw, cu_q, cu_k, **kw)
+    assert _rel(runs[0][0], wq) < 2e-2 and _rel(runs[0][1], wk) < 2e-2 and _rel(runs[0][2], wv) < 2e-2
+    assert kk.device_error_words().get("attention", 0) == 0
+
+
+def test_attention_bwd_deterministic_more_key_tiles_than_sms():
+    """One 24,576-token sequence: 192 key-tile CTAs per KV head, more than fit on the GPU at once.  The ordered mode
+    hands key tiles out from the last to the first, so a CTA only waits for CTAs that started before it: the run
+    finishes at the unordered kernel's pace, keeps its order (error word stays zero) and repeats bit for bit."""
+    from flextrain_b200.ops import attention_cuda as fa
+    from flextrain_b200.ops import cuda as kk
+    S, H, KV, hd = 24576, 2, 1, 128
+    cu = torch.tensor([0, S], dtype=torch.int32, device=DEV)
+    q, k, v, do = _rand(S, H, hd), _rand(S, KV, hd), _rand(S, KV, hd), _rand(S, H, hd)
+    o, lse = fa.fwd(q, k, v, cu, cu, S, S, scale=hd ** -0.5)
+    a = fa.bwd(do, q, k, v, o, lse, cu, cu, S, S, scale=hd ** -0.5, deterministic=True)
+    b = fa.bwd(do, q, k, v, o, lse, cu, cu, S, S, scale=hd ** -0.5, deterministic=True)
+    loose = fa.bwd(do, q, k, v, o, lse, cu, cu, S, S, scale=hd ** -0.5, deterministic=False)
+    torch.cuda.synchronize()
+    assert kk.device_error_words().get("attention", 0) == 0
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    assert _rel(loose[0], a[0]) < 1e-3 and _rel(loose[1], a[1]) < 1e-3
+
+
+@pytest.mark.parametrize("kind", ["swiglu", "geglu"])
+@pytest.mark.parametrize("M,K,F", [(512, 256, 128), (1000, 512, 640), (4096, 1024, 1792)])
+def test_gemm_glu_fused_forward_and_backward(kind, M, K, F):
+    """Gated-FFN GEMMs with the activation in the epilogue against the fp32 composition of GEMM and activation."""
+    from flextrain_b200.ops import cuda as k
+    x, w13, w2 = _rand(M, K, scale=0.5), _rand(2 * F, K, scale=K ** -0.5), _rand(K, F, scale=F ** -0.5)
+    x13, act = ops.linear_glu_fwd(x, w13, kind)
+    assert "ftb" in ops.backends_used().get("linear_glu_fwd", [])
+    want13 = x.float() @ w13.float().t()
+    assert _rel(x13, want13) < 5e-3
+    # the activation is defined on the stored (bf16) projection, which is what the backward reads back
+    want_act = ref.glu_fwd(x13[:, :F].float(), x13[:, F:].float(), kind)
+    assert _rel(act, want_act) < 5e-3
+    dy = _rand(M, K, scale=0.3)
+    dx13, act2 = ops.linear_glu_bwd(dy, w2, x13, kind)
+    assert "ftb" in ops.backends_used().get("linear_glu_bwd", [])
+    dact = dy.float() @ w2.float()
+    dg, du, a = ref.glu_bwd(dact, x13[:, :F].float(), x13[:, F:].float(), kind)
+    assert _rel(dx13[:, :F], dg) < 6e-3 and _rel(dx13[:, F:], du) < 6e-3 and _rel(act2, a) < 5e-3
+    assert k.device_error_words().get("gemm_tcgen05", 0) == 0
