@@ -369,7 +369,10 @@ def run_reference(args):
     except Exception as e:
         unavailable(f"reference import failed: {type(e).__name__}: {e}")
     try:
-        dims = {k: v for k, v in LLAMA31_8B.items() if k != "ffn_dim"}
+        # only the keys the reference's Llama adapter documents; its own defaults fill the rest (a dense FFN is
+        # "one shared expert" there: num_shared_experts = 1, flextrain/io/arch/llama.py:154-159)
+        dims = {k: LLAMA31_8B[k] for k in ("vocab_size", "n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim",
+                                           "expert_dim")}
         seq_len, gbatch = SEQ_LEN, GLOBAL_BATCH
         if args.small:
             dims["n_layers"] = 4
@@ -425,6 +428,18 @@ def run_reference(args):
                 msg = f"{st}/gpu={g}/{hw}/chunk={m}: {type(e).__name__}: {str(e)[:160]}"
                 errors.append(msg)
                 print("[reference arm] attempt failed: " + msg.replace("\n", " "), file=sys.stderr, flush=True)
+                if len(errors) == 1 and rank == 0 and isinstance(e, ValueError):
+                    # the planner's own trace of the first (preferred) attempt, so a log shows why it was refused
+                    import contextlib
+                    with contextlib.redirect_stdout(sys.stderr):
+                        try:
+                            ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len,
+                                          max_global_batch_tokens=per_rank, max_gpu_mem_bytes=int(free),
+                                          max_host_mem_bytes=host_budget, max_chunk_size=m, hw_cost=hwc,
+                                          mem_bw_gbps=mbw, device=dev, verbose=True,
+                                          hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5})
+                        except Exception:
+                            pass
                 if not isinstance(e, ValueError):
                     # an allocation of the reference's own plan failed (device or pinned memory): the other link / chunk
                     # variants of this budget plan the same memory, go to the next smaller GPU budget

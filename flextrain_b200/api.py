@@ -57,6 +57,10 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
                         opt_state: str = "auto",
                         process_group, model_dir=None, arch_key=None, host_backend=None,
                         plan_only: bool = False) -> ActiveModel:
+    if tp == "auto" or ep == "auto":
+        args = dict(locals())
+        args.pop("mc")
+        tp, ep = choose_layout(mc, args)
     builder = _BLOCK_BUILDERS.get(arch_key) if arch_key else None
     if tp > 1 and ep > 1:
         raise NotImplementedError("tensor and expert parallelism cannot be combined")
@@ -88,6 +92,7 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
             min_chunk_size=min_chunk_size, max_chunk_size=max_chunk_size,
             force_saved_act_level=force_saved_act_level, verbose=verbose)
     if plan_only:
+        ws.tp, ws.ep = tp, ep
         return ws
     if getattr(ws, "head_chunk_size", None):
         head.head_chunk_size = min(head.head_chunk_size, ws.head_chunk_size)     # the planner needed the room
@@ -102,9 +107,53 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
     am.model_config = mc
     am.is_causal = mc.is_causal
     am.rank, am.world_size = rank, world_size
+    am.tp_degree, am.ep_degree = tp, ep
     mp = tp_group or ep_group
     am.shard_group = getattr(mp, "group_pg", None) if mp is not None else None
     return am
+
+
+def layout_candidates(mc: ModelConfig, world_size: int, optimizer=None) -> list:
+    """``(tp, ep)`` layouts this model can run in on ``world_size`` GPUs, cheapest communication first: data parallel,
+    then expert parallel (MoE whose expert count divides), then tensor parallel (head / FFN widths divide, attention
+    layers only, element-wise optimizer).  Model-parallel groups span the whole job."""
+    out = [(1, 1)]
+    if world_size <= 1:
+        return out
+    if mc.num_experts > 0 and mc.num_experts % world_size == 0:
+        out.append((1, world_size))
+    muon = type(optimizer).__name__ in ("Muon", "HybridMuonAdamW")
+    linear = mc.gdn is not None or any(t == "linear" for t in (mc.layer_types or []))
+    if (not muon and not linear and mc.num_experts == 0 and mc.n_heads % world_size == 0
+            and mc.n_kv_heads % world_size == 0 and mc.ffn_dim % (world_size * 128) == 0):
+        out.append((world_size, 1))
+    return out
+
+
+def choose_layout(mc: ModelConfig, build_args: dict):
+    """Plan every candidate layout and return the ``(tp, ep)`` with the lowest estimated step time among those that
+    fit the budgets.  Data parallelism wins whenever it fits (no activation traffic between ranks); a model whose
+    state does not fit under it (70B-class dense models, large MoE) lands on tensor or expert parallelism."""
+    verbose = build_args.get("verbose")
+    tried, best = [], None
+    for t, e in layout_candidates(mc, build_args["world_size"], build_args.get("optimizer")):
+        try:
+            ws = _build_active_model(mc, **{**build_args, "tp": t, "ep": e, "plan_only": True, "ws": None,
+                                            "verbose": False})
+        except (ValueError, NotImplementedError) as err:
+            tried.append(f"tp={t} ep={e}: does not fit ({str(err)[:120]})")
+            continue
+        tried.append(f"tp={t} ep={e}: est {ws.est_step_ms:.0f} ms/step, shard {ws.shard}, "
+                     f"{'healthy' if ws.healthy else 'PCIe-exposed'}")
+        key = (not ws.healthy, ws.est_step_ms)
+        if best is None or key < best[0]:
+            best = (key, t, e)
+    if verbose:
+        for line in tried:
+            print(f"[Working Set Log] layout {line}")
+    if best is None:
+        raise ValueError("no parallel layout fits the budgets: " + "; ".join(tried))
+    return best[1], best[2]
 
 
 def _init_random_weights(am: ActiveModel, seed: int, std: float, on_device: bool = False) -> None:

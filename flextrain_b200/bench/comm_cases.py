@@ -194,11 +194,13 @@ def main() -> None:
     rows = max(plan.rows, 128)
     remote = T * Kt * D * 2 * (world - 1) / world         # bytes leaving (dispatch) / entering (combine) this GPU
     y = torch.randn(rows, D, device=dev).to(torch.bfloat16)
-    send = h[plan.src_tok.long()].contiguous()
+    # library baseline: gather the T x K routed rows into destination order, then one equal-split all-to-all
+    send_order = torch.argsort(idx.reshape(-1).long(), stable=True) // Kt
+    send = h[send_order].contiguous()
     recv_a2a = torch.empty_like(send)
 
     def nccl_dispatch():
-        dist.all_to_all_single(recv_a2a, h[plan.src_tok.long()])      # gather into send order + all-to-all
+        dist.all_to_all_single(recv_a2a, h[send_order])              # gather into send order + all-to-all
 
     def nccl_combine():
         dist.all_to_all_single(recv_a2a, send)

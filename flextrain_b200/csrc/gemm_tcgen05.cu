@@ -651,8 +651,53 @@ static EncodeTiledFn get_encode() {
 }
 
 // Tensor map over a row-major bf16 tensor (dims innermost-first). box = {box0, box1[, 1]}.
+// A training step launches the same few hundred (buffer, shape, tile) combinations tens of thousands of times (ring
+// slots and weight views recur every round), so encoded maps are kept in a small direct-mapped table keyed on
+// everything the encoding depends on: base address, extents, strides, box.  A map holds no data, only that
+// description, so an entry stays valid when the memory behind the address is freed and reused.  (The reference's
+// dispatcher keeps an exact-shape cache of its cuBLASLt plans for the same reason, helpers/matmul_dispatcher/src/
+// dispatch.cpp:23-57.)
+struct TmapKey {
+  const void* base;
+  uint64_t dims[3];
+  uint64_t strides[2];
+  uint32_t box[3];
+  int rank;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rank == o.rank && dims[0] == o.dims[0] && dims[1] == o.dims[1] && dims[2] == o.dims[2] &&
+           strides[0] == o.strides[0] && strides[1] == o.strides[1] && box[0] == o.box[0] && box[1] == o.box[1] &&
+           box[2] == o.box[2];
+  }
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used = false;
+};
+constexpr int TMAP_SLOTS = 4096;
+static int g_tmap_cache_on = 1;
+static unsigned long long g_tmap_hits = 0, g_tmap_misses = 0;
+
 static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                      const uint32_t* box) {
+  static thread_local TmapSlot* table = nullptr;
+  TmapKey key{};
+  key.base = base; key.rank = rank;
+  for (int i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+  for (int i = 0; i < rank - 1; ++i) key.strides[i] = strides_bytes[i];
+  TmapSlot* slot = nullptr;
+  if (g_tmap_cache_on) {
+    if (table == nullptr) table = new TmapSlot[TMAP_SLOTS];
+    uint64_t h = reinterpret_cast<uintptr_t>(base) * 0x9E3779B97F4A7C15ull;
+    h ^= (key.dims[0] * 0xC2B2AE3D27D4EB4Full) ^ (key.dims[1] * 0x165667B19E3779F9ull) ^ (key.strides[0] << 7) ^
+         (static_cast<uint64_t>(key.box[0]) << 40) ^ (static_cast<uint64_t>(key.box[1]) << 20) ^ key.dims[2];
+    slot = &table[(h >> 24) & (TMAP_SLOTS - 1)];
+    if (slot->used && slot->key == key) {
+      *out = slot->map;
+      ++g_tmap_hits;
+      return 0;
+    }
+  }
   EncodeTiledFn enc = get_encode();
   if (enc == nullptr) return -100;
   cuuint64_t gdim[3];
@@ -664,7 +709,10 @@ static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstr, bx, es,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -200 - static_cast<int>(r);
+  if (r != CUDA_SUCCESS) return -200 - static_cast<int>(r);
+  ++g_tmap_misses;
+  if (slot != nullptr) { slot->key = key; slot->map = *out; slot->used = true; }
+  return 0;
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, int GROUPED, int COMM = 0>
@@ -1185,6 +1233,11 @@ int ftb_gemm_bf16(const void* A, const void* B, void* D, const void* C, const fl
 }
 
 void ftb_gemm_set_two_sm(int on) { g_use_2cta = on; }
+// tensor-map cache: switch, and (hits, misses) since the library was loaded
+void ftb_gemm_set_tmap_cache(int on) { g_tmap_cache_on = on; }
+void ftb_gemm_tmap_cache_stats(unsigned long long* hits, unsigned long long* misses) {
+  *hits = g_tmap_hits; *misses = g_tmap_misses;
+}
 // all-gather -> GEMM: 1 = remote panels pulled by two warps of 16-byte loads, 0 (default) = by bulk copies
 void ftb_gemm_set_tp_pull_threads(int on) { g_tp_pull_threads = on; }
 

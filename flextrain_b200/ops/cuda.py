@@ -40,6 +40,10 @@ def load(name: str) -> ctypes.CDLL:
     _libs[name] = lib
     if name == "gemm_tcgen05" and os.environ.get("FTB_GEMM_TWO_SM", "1") == "0":
         lib.ftb_gemm_set_two_sm(c_int(0))   # one-SM tiles for every shape (A/B comparisons)
+    if name == "gemm_tcgen05" and os.environ.get("FTB_TMAP_CACHE", "1") == "0":
+        lib.ftb_gemm_set_tmap_cache(c_int(0))   # encode the tensor maps on every call
+    if name == "gemm_tcgen05" and os.environ.get("FTB_TP_PULL", "bulk") == "threads":
+        lib.ftb_gemm_set_tp_pull_threads(c_int(1))   # all-gather GEMM: pull remote panels with per-thread loads
     return lib
 
 
@@ -98,6 +102,14 @@ def device_error_words() -> dict:
 
 # ------------------------------------------------------------------------------- GEMM
 GEMM_MAX_CTAS = int(os.environ.get("FTB_GEMM_MAX_CTAS", "0"))
+
+
+def tmap_cache_stats() -> dict:
+    """``{"hits": n, "misses": n}`` of the GEMM library's tensor-map cache since it was loaded."""
+    lib = load("gemm_tcgen05")
+    h, m = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+    lib.ftb_gemm_tmap_cache_stats(ctypes.byref(h), ctypes.byref(m))
+    return {"hits": int(h.value), "misses": int(m.value)}
 
 
 def gemm_supported(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool, out_dtype) -> bool:

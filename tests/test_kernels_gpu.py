@@ -568,3 +568,21 @@ def test_gemm_glu_fused_forward_and_backward(kind, M, K, F):
     dg, du, a = ref.glu_bwd(dact, x13[:, :F].float(), x13[:, F:].float(), kind)
     assert _rel(dx13[:, :F], dg) < 6e-3 and _rel(dx13[:, F:], du) < 6e-3 and _rel(act2, a) < 5e-3
     assert k.device_error_words().get("gemm_tcgen05", 0) == 0
+
+
+def test_tensor_map_cache_reuses_encodings_and_keeps_results():
+    """Repeated GEMMs on the same buffers hit the tensor-map cache; a new shape at a cached address re-encodes."""
+    from flextrain_b200.ops import cuda as k
+    a, b = _rand(512, 256), _rand(384, 256)
+    out = torch.empty(512, 384, dtype=torch.bfloat16, device=DEV)
+    k.gemm(a, b, trans_b=True, out=out)
+    s0 = k.tmap_cache_stats()
+    for _ in range(5):
+        k.gemm(a, b, trans_b=True, out=out)
+    s1 = k.tmap_cache_stats()
+    assert s1["hits"] - s0["hits"] >= 10 and s1["misses"] == s0["misses"], (s0, s1)
+    assert _rel(out, a.float() @ b.float().t()) < 5e-3
+    a2 = a.view(-1)[: 256 * 256].view(256, 256)                 # same base address, different extent
+    out2 = k.gemm(a2, b, trans_b=True)
+    assert k.tmap_cache_stats()["misses"] > s1["misses"]
+    assert _rel(out2, a2.float() @ b.float().t()) < 5e-3

@@ -283,3 +283,26 @@ def test_dp_solver_large_round_stays_small_in_memory():
         start = max(busy, c[t + 1])
         busy = start + dur[t, sol[t]]
         assert busy <= c[t + N - 1] + 0.2 * (t + 1) ** 0 + 0.3, (t, busy, c[t + N - 1])
+
+
+def test_planner_chooses_parallel_layout_by_fit():
+    """``tp="auto"``: an 8B dense model on 8 GPUs stays data parallel; a 70B-class dense model whose replicated state
+    cannot fit 180 GB lands on tensor parallelism; a large MoE lands on expert parallelism."""
+    import json, os
+    import flextrain_b200 as ft
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    table = json.load(open(os.path.join(root, "flextrain_b200", "configs", "model_dims.json")))
+    opt = ft.AdamW(lr=1e-5, state_dtype=torch.float32)
+    kw = dict(optimizer=opt, max_seq_len=1024, max_gpu_mem_bytes=178 << 30, max_host_mem_bytes=100 << 30,
+              device="cpu", world_size=8, rank=0, plan_only=True, tp="auto", ep="auto")
+
+    def plan(name, batch):
+        d = dict(table[name]); arch = d.pop("arch", "llama"); hyper = d.pop("hyperparams", None)
+        return ft.from_dims(d, arch=arch, hyperparams=hyper, max_global_batch_tokens=batch, **kw)
+
+    ws = plan("llama3_1_8B", 524288)
+    assert (ws.tp, ws.ep) == (1, 1) and ws.shard != "none"
+    ws = plan("llama3_70B", 262144)
+    assert (ws.tp, ws.ep) == (8, 1), (ws.tp, ws.ep, ws.report[-3:])
+    ws = plan("qwen3_30B_A3B", 262144)
+    assert (ws.tp, ws.ep) == (1, 8), (ws.tp, ws.ep, ws.report[-3:])

@@ -103,8 +103,10 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--heartbeat-s", type=float, default=0.0,
                    help="multi-rank runs: raise on every rank when a peer has not finished a step for this many "
                         "seconds or has left (0 = off)")
-    p.add_argument("--tp", type=int, default=1)
-    p.add_argument("--ep", type=int, default=1)
+    _deg = lambda v: v if v == "auto" else int(v)
+    p.add_argument("--tp", type=_deg, default=1, help="tensor-parallel degree, or 'auto': plan data / expert / tensor "
+                   "parallel layouts for this model and budget and take the fastest that fits")
+    p.add_argument("--ep", type=_deg, default=1, help="expert-parallel degree, or 'auto' (see --tp)")
     return p
 
 
@@ -192,7 +194,8 @@ def main(argv=None) -> int:
     # ---- data
     # data-parallel ranks (also under expert parallelism) each take their share of the batch; the ranks of a
     # tensor-parallel group work on the SAME sequences, so they read identical data
-    data_ranks, data_rank = (world // args.tp, rank // args.tp) if args.tp > 1 else (world, rank)
+    tp_deg = getattr(am, "tp_degree", args.tp)
+    data_ranks, data_rank = (world // tp_deg, rank // tp_deg) if tp_deg > 1 else (world, rank)
     per_rank_tokens = args.max_global_batch_tokens // data_ranks
     def make_source(path, seed, loop=True):
         if args.data_source == "synthetic":
