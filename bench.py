@@ -132,7 +132,9 @@ def _dist_env():
 
 
 def _emit(obj):
-    print(json.dumps(obj), flush=True)
+    # the one JSON line goes to the process's real stdout; everything else either arm prints goes to stderr
+    sys.__stdout__.write(json.dumps(obj) + "\n")
+    sys.__stdout__.flush()
 
 
 def _budget_steps(args, t_proc0: float, warm_step_s: float, setup_reserve_s: float = 25.0) -> int:
@@ -343,6 +345,7 @@ def run_reference(args):
     t_proc0 = time.perf_counter()
     rank, world, local = _dist_env()
     ref_root = os.path.join(ROOT, "baseline", "_ref")
+    sys.stdout = sys.stderr          # the reference prints its planner notes to stdout: keep stdout for the JSON line
 
     def unavailable(why: str):
         if rank == 0:
