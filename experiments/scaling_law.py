@@ -43,15 +43,19 @@ def fit_parabola(ns, ls):
     return out
 
 
-def markov_source(vocab: int, branch: int = 8, seed: int = 0):
-    """Second-order source: the pair (a, b) hashes to ``branch`` candidate successors with fixed geometric weights.
-    Returns ``(successor table fn, entropy in nats per token)``."""
+def markov_source(vocab: int, branch: int = 8, seed: int = 0, context_classes: int = 64):
+    """Sparse second-order source: the pair (class of a, b) hashes to ``branch`` candidate successors with fixed
+    geometric weights, where ``class of a = a mod context_classes``.  A bigram model can only average over the classes;
+    the full table has ``context_classes * vocab * branch`` entries, so within a small compute budget a larger model
+    learns more of it per token while a smaller one sees more tokens: the IsoFLOP trade-off has something to act on.
+    Returns ``(successor fn, weights, entropy in nats per token)``."""
     w = 0.5 ** np.arange(1, branch + 1); w[-1] *= 2.0; w /= w.sum()
     ent = float(-(w * np.log(w)).sum())
     rng = np.random.default_rng(seed)
     mul = rng.integers(1, 2 ** 31 - 1, size=(branch, 2), dtype=np.int64) | 1
 
     def successors(a, b):
+        a = a % context_classes
         return ((a[:, None] * mul[None, :, 0] + b[:, None] * mul[None, :, 1] + np.arange(branch)[None, :] * 40503)
                 % 2147483647) % vocab
     return successors, w, ent
