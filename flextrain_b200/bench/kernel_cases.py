@@ -2,7 +2,7 @@
 
     python -m flextrain_b200.bench.kernel_cases gemm_fwd|gemm_dgrad|gemm_wgrad|rmsnorm_bwd|softmax_ce|attn_fwd|attn_bwd|
                                                   attn_fwd_one_tile|attn_bwd_unordered|attn_fwd_32k|attn_bwd_32k|gdn_fwd|gdn_bwd|
-                                                  gdn_long_fwd|rope|ffn_glu_fwd|ffn_glu_bwd|gdn_fla_fwd|gdn_fla_bwd
+                                                  gdn_long_fwd|rope|ffn_glu_fwd|ffn_glu_bwd|gdn_fla_fwd|gdn_fla_bwd|attn_fa2_fwd|attn_fa2_bwd|attn_fa2_fwd_32k|attn_fa2_bwd_32k
 
 Each case holds a few hundred MB on the device (inputs larger than the 126 MB L2), runs three warm-up launches and
 ten timed launches with CUDA events, and prints achieved TFLOP/s or GB/s.  They are the commands behind the
@@ -134,6 +134,30 @@ def main(case: str) -> None:
             do = torch.randn_like(o)
             ms = _time(lambda: ops.attention_bwd(do, q, kk, v, o, lse, cu, cu, S, S, scale=hd ** -0.5))
             print(f"{case}: B={B} S={S} H={H} KV={KV} hd={hd}  {ms:.3f} ms  {2.5 * fl / ms / 1e9:.0f} TFLOP/s (causal)")
+    elif case in ("attn_fa2_fwd", "attn_fa2_bwd", "attn_fa2_fwd_32k", "attn_fa2_bwd_32k"):
+        # Third-party bar: flash_attn 2.8 (the package in this image; mma.sync kernels recompiled for sm_100) on the same
+        # problems as attn_fwd / attn_bwd, deterministic backward as the reference asks of it.  A measurement only.
+        from flash_attn import flash_attn_varlen_func
+        S, B, H, KV, hd = (32768, 1, 32, 8, 128) if case.endswith("_32k") else (1024, 16, 32, 8, 128)
+        T = S * B
+        q = torch.randn(T, H, hd, device=dev, dtype=bf, requires_grad=True)
+        kk = torch.randn(T, KV, hd, device=dev, dtype=bf, requires_grad=True)
+        v = torch.randn(T, KV, hd, device=dev, dtype=bf, requires_grad=True)
+        cu = torch.arange(0, T + 1, S, device=dev, dtype=torch.int32)
+        fl = 4.0 * B * H * S * S * hd / 2
+        run = lambda: flash_attn_varlen_func(q, kk, v, cu, cu, S, S, causal=True, deterministic=True)
+        if "_fwd" in case:
+            with torch.no_grad():
+                ms = _time(run)
+            print(f"{case}: B={B} S={S} H={H} KV={KV} hd={hd}  {ms:.3f} ms  {fl / ms / 1e9:.0f} TFLOP/s (causal, flash_attn 2)")
+        else:
+            o = run()
+            do = torch.randn_like(o)
+            ms = _time(lambda: torch.autograd.grad(o, (q, kk, v), do, retain_graph=True))
+            print(f"{case}: B={B} S={S} H={H} KV={KV} hd={hd}  {ms:.3f} ms  {2.5 * fl / ms / 1e9:.0f} TFLOP/s "
+                  f"(causal, flash_attn 2 backward only)")
+        print("device error words: {}")
+        return
     elif case == "rope":
         T, H, hd = 16384, 32, 128
         x = torch.randn(T, H, hd, device=dev, dtype=bf)
