@@ -78,6 +78,9 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--master-dtype", choices=tuple(_DT), default="bfloat16")
     p.add_argument("--grad-dtype", choices=tuple(_DT), default="bfloat16")
     p.add_argument("--opt-state-dtype", choices=tuple(_DT), default=None)
+    p.add_argument("--opt-state", choices=("auto", "host", "device"), default="auto",
+                   help="where optimizer state lives: the planner decides, pinned host memory (streamed through a "
+                        "device ring during the step), or HBM")
     p.add_argument("--save", action="store_true")
     p.add_argument("--save-state-every", type=int, default=0,
                    help="every N steps (and at the end) write a full training state (weights, optimizer state, step) "
@@ -177,7 +180,7 @@ def main(argv=None) -> int:
                   lora_targets="all" if lora else None, lora_rank=args.lora_rank, lora_alpha=args.lora_alpha,
                   force_saved_act_level=args.force_save_level, min_chunk_size=args.min_chunk_size,
                   max_chunk_size=args.max_chunk_size, verbose=args.verbose and rank == 0, world_size=world, rank=rank,
-                  dp_shard=args.dp_shard, tp=args.tp, ep=args.ep)
+                  dp_shard=args.dp_shard, tp=args.tp, ep=args.ep, opt_state=args.opt_state)
     if kind == "dims":
         arch = model.pop("arch", "llama")
         hyper = model.pop("hyperparams", None)
