@@ -7,9 +7,10 @@ In-repo backends (always runnable on a GPU box with this image):
                       (``FTB_DP_BACKEND=collective FTB_GEMM_BACKEND=library``): the "NCCL + cuBLAS" baseline;
 * ``reference``       the unmodified reference engine installed under ``baseline/_ref`` (``bench.py --impl reference``);
 * ``hf_fsdp2``        HuggingFace ``transformers`` model + PyTorch FSDP2 (``baseline/backends/hf_fsdp2.py``).
+* ``torchtitan``      TorchTitan's Llama-3 model, FSDP2 and activation checkpointing (``baseline/backends/torchtitan_synthetic.py``).
 
 Third-party backends the reference project compares against (baseline/baseline_harness/backends.py in its tree):
-``trl_deepspeed``, ``trl_fsdp``, ``deepspeed_arctic``, ``megatrain``, ``torchtitan``, ``megatron``.  Their command
+``trl_deepspeed``, ``trl_fsdp``, ``deepspeed_arctic``, ``megatrain``, ``megatron``.  Their command
 lines are built the same way; a backend whose Python package is not importable reports ``available() == False`` and
 a sweep records it as skipped instead of failing.
 """
@@ -99,6 +100,15 @@ def _hf_fsdp2(spec: RunSpec):
     return _torchrun(spec, os.path.join(REPO_ROOT, "baseline", "backends", "hf_fsdp2.py"), args), {}
 
 
+def _torchtitan(spec: RunSpec):
+    args = ["--preset", spec.model_preset, "--seq-length", str(spec.seq_length),
+            "--micro-batch-size", str(spec.micro_batch_size),
+            "--gradient-accumulation-steps", str(spec.gradient_accumulation_steps),
+            "--num-steps", str(spec.num_steps), "--warmup-steps", str(spec.warmup_steps), "--seed", str(spec.seed)]
+    args += _flag_args(spec.extra, ("ac_mode", "cpu_offload", "n_layers"))
+    return _torchrun(spec, os.path.join(REPO_ROOT, "baseline", "backends", "torchtitan_synthetic.py"), args), {}
+
+
 # --------------------------------------------------------------------------------------------- third-party backends
 def _external(script_rel: str, allowed: Tuple[str, ...]):
     def build(spec: RunSpec):
@@ -126,8 +136,8 @@ BACKENDS: Dict[str, Backend] = {b.name: b for b in (
             _external("external.py", ("sequence_parallel_size", "zero_stage", "offload_optimizer", "tiled_mlp"))),
     Backend("megatrain", "MegaTrain CPU-master training", ("megatrain",),
             _external("external.py", ("grad_slab_gib", "activation_checkpointing"))),
-    Backend("torchtitan", "TorchTitan FSDP2", ("torchtitan",),
-            _external("external.py", ("data_parallel_shard_degree", "context_parallel_degree", "ac_mode"))),
+    Backend("torchtitan", "TorchTitan Llama-3 model + FSDP2 + activation checkpointing on synthetic tokens",
+            ("torch", "torchtitan"), _torchtitan),
     Backend("megatron", "Megatron-Core + TransformerEngine", ("megatron", "transformer_engine"),
             _external("external.py", ("tensor_model_parallel_size", "context_parallel_size", "recompute_granularity",
                                       "optimizer_cpu_offload"))),
