@@ -131,10 +131,27 @@ def _dist_env():
     return rank, world, local
 
 
+_JSON_FD = None
+
+
+def _claim_stdout() -> None:
+    """Keep file descriptor 1 for the one JSON line: a duplicate of it is kept for ``_emit`` and descriptor 1 itself is
+    pointed at stderr, so whatever else writes to stdout in this process (library banners such as NCCL's version line,
+    the reference's planner notes, C extensions) lands in the log instead of in front of the result."""
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
 def _emit(obj):
-    # the one JSON line goes to the process's real stdout; everything else either arm prints goes to stderr
-    sys.__stdout__.write(json.dumps(obj) + "\n")
-    sys.__stdout__.flush()
+    line = (json.dumps(obj) + "\n").encode()
+    if _JSON_FD is None:
+        sys.__stdout__.write(line.decode())
+        sys.__stdout__.flush()
+    else:
+        os.write(_JSON_FD, line)
 
 
 def _budget_steps(args, t_proc0: float, warm_step_s: float, setup_reserve_s: float = 25.0) -> int:
@@ -345,7 +362,6 @@ def run_reference(args):
     t_proc0 = time.perf_counter()
     rank, world, local = _dist_env()
     ref_root = os.path.join(ROOT, "baseline", "_ref")
-    sys.stdout = sys.stderr          # the reference prints its planner notes to stdout: keep stdout for the JSON line
 
     def unavailable(why: str):
         if rank == 0:
@@ -571,6 +587,7 @@ def run_reference(args):
 
 
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
