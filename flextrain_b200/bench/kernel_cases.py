@@ -1,8 +1,8 @@
 """Small, self-terminating kernel cases for profiling one kernel at a time.
 
     python -m flextrain_b200.bench.kernel_cases gemm_fwd|gemm_dgrad|gemm_wgrad|rmsnorm_bwd|softmax_ce|attn_fwd|attn_bwd|
-                                                  attn_fwd_one_tile|attn_bwd_unordered|attn_fwd_32k|attn_bwd_32k|gdn_fwd|gdn_bwd|
-                                                  gdn_long_fwd|rope|ffn_glu_fwd|ffn_glu_bwd|gdn_fla_fwd|gdn_fla_bwd|attn_fa2_fwd|attn_fa2_bwd|attn_fa2_fwd_32k|attn_fa2_bwd_32k
+                                                  attn_fwd_one_tile|attn_bwd_unordered|attn_bwd_thread_reds|attn_fwd_32k|attn_bwd_32k|attn_bwd_32k_thread_reds|gdn_fwd|gdn_bwd|
+                                                  gdn_long_fwd|rope|ffn_glu_fwd|ffn_glu_bwd|gdn_fla_fwd|attn_fa2_fwd|attn_fa2_bwd|attn_fa2_fwd_32k|attn_fa2_bwd_32k
 
 Each case holds a few hundred MB on the device (inputs larger than the 126 MB L2), runs three warm-up launches and
 ten timed launches with CUDA events, and prints achieved TFLOP/s or GB/s.  They are the commands behind the
@@ -55,10 +55,11 @@ def main(case: str) -> None:
         tgt = torch.randint(0, V, (T,), device=dev)
         ms = _time(lambda: k.softmax_ce_(z, tgt, grad_scale=1e-3))
         print(f"{case}: T={T} V={V}  {ms:.3f} ms  {3.0 * T * V * 2 / ms / 1e6:.0f} GB/s (2 reads + 1 write)")
-    elif case in ("gdn_fla_fwd", "gdn_fla_bwd"):
+    elif case == "gdn_fla_fwd":
         # Third-party bar for the Gated DeltaNet kernels: flash-linear-attention's chunked Triton kernels (the ones the
-        # reference calls, flextrain/nn/blocks/linear_attn.py:1036-1046) on the same shape as gdn_fwd / gdn_bwd.
-        # A measurement only: nothing in the package imports fla.
+        # reference calls, flextrain/nn/blocks/linear_attn.py:1036-1046) on the same shape as gdn_fwd.  A measurement
+        # only: nothing in the package imports fla.  (Forward only: FLA's backward raised a misaligned-address fault
+        # inside its own kernels on this hardware, so it is not run.)
         import torch.nn.functional as F
         from fla.ops.gated_delta_rule import chunk_gated_delta_rule
         HK, HV, dk, dv, S, L = 16, 32, 128, 128, 16, 1024
@@ -71,22 +72,9 @@ def main(case: str) -> None:
         beta = (torch.rand(1, T, HV, device=dev) * 0.9 + 0.05).to(bf).contiguous()
         cu = torch.arange(0, T + 1, L, device=dev, dtype=torch.long)
         fl = 2.0 * T * HV * dk * dv * 3
-        if case == "gdn_fla_fwd":
-            with torch.no_grad():
-                ms = _time(lambda: chunk_gated_delta_rule(q, kk, v, g, beta, cu_seqlens=cu, output_final_state=True))
-            print(f"{case}: {S} x {L} tokens, HV={HV} dk={dk} dv={dv}  {ms:.3f} ms (FLA chunked Triton forward)")
-        else:
-            leaves = [t.clone().requires_grad_(True) for t in (q, kk, v, g, beta)]
-            def fb():
-                o, _ = chunk_gated_delta_rule(*leaves, cu_seqlens=cu, output_final_state=True)
-                o.backward(d_o)
-                for t in leaves:
-                    t.grad = None
-            with torch.no_grad():
-                o0, _ = chunk_gated_delta_rule(q, kk, v, g, beta, cu_seqlens=cu, output_final_state=True)
-            d_o = torch.randn_like(o0)
-            ms = _time(fb)
-            print(f"{case}: {S} x {L} tokens, HV={HV} dk={dk} dv={dv}  {ms:.3f} ms (FLA chunked Triton forward + backward)")
+        with torch.no_grad():
+            ms = _time(lambda: chunk_gated_delta_rule(q, kk, v, g, beta, cu_seqlens=cu, output_final_state=True))
+        print(f"{case}: {S} x {L} tokens, HV={HV} dk={dk} dv={dv}  {ms:.3f} ms (FLA chunked Triton forward)")
         print("device error words: {}")
         return
     elif case in ("gdn_fwd", "gdn_bwd", "gdn_long_fwd"):
@@ -112,7 +100,11 @@ def main(case: str) -> None:
             d_o = torch.randn_like(o)
             ms = _time(lambda: la.gdn_bwd(q, kk, v, g, beta, cu, None, fin, r, d_o))
             print(f"{case}: {S} x {L} tokens, HV={HV} dk={dk} dv={dv}  {ms:.3f} ms  {2.2 * fl / ms / 1e9:.1f} TFLOP/s fp32")
-    elif case in ("attn_fwd", "attn_bwd", "attn_bwd_unordered", "attn_fwd_one_tile", "attn_fwd_32k", "attn_bwd_32k"):
+    elif case in ("attn_fwd", "attn_bwd", "attn_bwd_unordered", "attn_fwd_one_tile", "attn_fwd_32k", "attn_bwd_32k",
+                  "attn_bwd_thread_reds", "attn_bwd_32k_thread_reds"):
+        if case.endswith("_thread_reds"):      # dQ by per-thread 16-byte reductions (the earlier drain), same GPU
+            k.load("attention").ftb_attn_set_dq_bulk(0)
+            case = case[: -len("_thread_reds")]
         S, B, H, KV, hd = (32768, 1, 32, 8, 128) if case.endswith("_32k") else (1024, 16, 32, 8, 128)
         if case == "attn_fwd_one_tile":          # the one-query-tile-per-CTA forward kernel, for an A/B on the same GPU
             k.load("attention").ftb_attn_set_two_tiles(0)

@@ -783,6 +783,8 @@ int ftb_attn_error(void) {
 
 }  // extern "C"
 
+static int g_dq_bulk = 1;     // ftb_attn_set_dq_bulk(0): per-thread vector reductions (the earlier drain), for A/B runs
+
 // =====================================================================================================
 // Backward
 // =====================================================================================================
@@ -795,6 +797,7 @@ struct BwdParams {
   int H, KV;
   float* dq_acc;            // (Tq, H, HD) fp32, zero-initialised by the caller
   int* dq_sem;              // deterministic mode: one counter per (query tile, head), zeroed by the caller; else NULL
+  int dq_bulk;              // 1: dQ tiles leave through shared memory as tiled reduce-adds; 0: per-thread vector reductions
   __nv_bfloat16* dk;        // (Tk, KV, HD) contiguous
   __nv_bfloat16* dv;
   const float* lse;         // (H, Tq)
@@ -833,7 +836,8 @@ constexpr int FAB_THREADS = 320;
 template <int HD, bool CAP>
 __global__ void __launch_bounds__(FAB_THREADS, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
-              const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
+              const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+              const __grid_constant__ CUtensorMap tmDQ, const BwdParams p) {
   constexpr int KB = HD / 64;
   constexpr int T_BYTES = 128 * HD * 2;       // one Q / dO / K / V tile
   constexpr int P_BYTES = 128 * 128 * 2;
@@ -854,6 +858,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint64_t* dq_full = bars + 5;
   uint64_t* dq_empty = bars + 6;
   uint64_t* stage_bar = bars + 7;
+  uint64_t* drain_bar = bars + 9;          // (bars + 8 holds the tensor-memory slot and the abort flag)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -885,6 +890,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     *abort_flag = 0;
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
     mbar_init(pds_full, 8); mbar_init(dq_full, 1); mbar_init(dq_empty, 8); mbar_init(stage_bar, 8);
+    mbar_init(drain_bar, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
@@ -1041,9 +1047,66 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (lane == 0) mbar_arrive(pds_full);
       if (!(ok = mbar_wait(dq_full, ph, abort_flag, 231))) break;
       tc_fence_after();
+      constexpr int HC = HD / 2;
+      if (p.dq_bulk) {
+        // dQ tile: tensor memory -> registers -> fp32 staging in shared memory (the P / dS buffers, free now that the
+        // MMAs of this query tile are done; one 16 KB block of 128 rows x 32 columns per 32 columns, 128-byte
+        // swizzle) -> four (two at hd 64) tiled reduce-adds into the fp32 workspace.  L2 then sees whole 128-byte
+        // lines per reduction instead of one 16-byte piece per row and thread, which is what bounded this kernel.
+        // Rows past the end of the sequence hold exact zeros (their P and dS were masked), so adding them is harmless.
+        uint8_t* stg = sP;
+#pragma unroll 1
+        for (int cb = half * HC; cb < half * HC + HC; cb += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tm_dQ + lane_base + cb, v);
+          tmem_ld_wait();
+          uint8_t* rowp = stg + (cb >> 5) * (128 * 128) + r * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(rowp + ((j ^ (r & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+        tc_fence_before();
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(dq_empty);                  // TMEM columns are free: the next S / dP may be issued now
+          mbar_arrive(stage_bar);                 // this warp's rows are staged
+        }
+        if (warp == 2 && lane == 0) {
+          bool go = mbar_wait(stage_bar, ph, abort_flag, 232);
+          int* sem = nullptr;
+          if (go && p.dq_sem != nullptr) {
+            // deterministic order: wait until the key tiles above this one have added their share of this query tile
+            // (word 0 of the array is the give-up flag, the counters follow it)
+            sem = p.dq_sem + 1 + (static_cast<size_t>(qtile_base + qt / 128)) * p.H + h;
+            const int j_hi = p.causal ? min(n_kt - 1, (qt + 127 + off) / 128) : n_kt - 1;
+            const int expected = j_hi - k0 / 128;
+            uint32_t spins = 0;
+            volatile int* gave_up = p.dq_sem;
+            while (expected > 0 && !*gave_up && ld_acquire_gpu_s32(sem) < expected) {
+              if (++spins > (1u << 21) || *abort_flag) { *gave_up = 1; set_error(4, 240); break; }
+              __nanosleep(32);
+            }
+          }
+          if (go) {
+#pragma unroll
+            for (int q4 = 0; q4 < HD / 32; ++q4)
+              tma_reduce_add_2d(&tmDQ, stg + q4 * (128 * 128), h * HD + q4 * 32, qs + qt);
+            bulk_commit();
+            if (sem != nullptr) {
+              bulk_wait_all();                    // the additions have been performed: the next key tile may add
+              red_release_gpu_add_s32(sem, 1);
+            } else {
+              bulk_wait_read_all();               // the staging buffers have been read: P / dS may be rewritten
+            }
+          }
+          mbar_arrive(drain_bar);
+        }
+        if (!(ok = mbar_wait(drain_bar, ph, abort_flag, 233))) break;
+        continue;
+      }
       // dQ tile: tensor memory -> registers -> vector reductions into the fp32 workspace, one row per thread (eight
       // 16-byte red.v4 per 32 columns).  Each warp drains its own half of the columns of its 32 rows.
-      constexpr int HC = HD / 2;
       int* sem = nullptr;
       if (p.dq_sem != nullptr) {
         // deterministic order: wait until the key tiles above this one have added their share of this query tile
@@ -1088,6 +1151,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (warp == 2 && lane == 0) red_release_gpu_add_s32(sem, 1);
       }
     }
+    if (p.dq_bulk && warp == 2 && lane == 0) bulk_wait_all();   // none of this thread's reduce-adds outlives the kernel
     // dK / dV of this key tile (thread = key row)
     constexpr int HC2 = HD / 2;
     if (r < kr) {
@@ -1140,7 +1204,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
 template <int HD, bool CAP>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv,
-                      const BwdParams& p, int tiles, cudaStream_t s) {
+                      const CUtensorMap& tdq, const BwdParams& p, int tiles, cudaStream_t s) {
   constexpr int SMEM = 4 * 128 * HD * 2 + 2 * 128 * 128 * 2 + 256 + 1024;
   auto kern = fa_bwd_kernel<HD, CAP>;
   static bool configured = false;
@@ -1150,7 +1214,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUten
     configured = true;
   }
   dim3 grid(tiles, p.KV);
-  kern<<<grid, FAB_THREADS, SMEM, s>>>(tq, tdo, tk, tv, p);
+  kern<<<grid, FAB_THREADS, SMEM, s>>>(tq, tdo, tk, tv, tdq, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -400 - static_cast<int>(e);
 }
@@ -1188,17 +1252,33 @@ int ftb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, 
   if (rc) return rc;
   rc = make_tmap_3d(&tv, v, hd, KV, total_k, v_stride, 128);
   if (rc) return rc;
+  // fp32 workspace as a 2-D tensor (total_q rows of H * hd columns): boxes of 128 rows x 32 columns for the reduce-adds
+  CUtensorMap tdq;
+  {
+    EncodeTiledFn enc = get_encode();
+    if (enc == nullptr) return -100;
+    cuuint64_t gdim[2] = {(cuuint64_t)H * hd, (cuuint64_t)total_q};
+    cuuint64_t gstr[1] = {(cuuint64_t)H * hd * 4};
+    cuuint32_t box[2] = {32, 128};
+    cuuint32_t es[2] = {1, 1};
+    CUresult r = enc(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dq_acc, gdim, gstr, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -200 - static_cast<int>(r);
+  }
   BwdParams p;
-  p.cu_q = cu_q; p.cu_k = cu_k; p.num_seqs = num_seqs; p.H = H; p.KV = KV;
+  p.cu_q = cu_q; p.cu_k = cu_k; p.num_seqs = num_seqs; p.H = H; p.KV = KV; p.dq_bulk = g_dq_bulk;
   p.dq_acc = dq_acc; p.dq_sem = dq_sem; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.lse = lse; p.delta = delta;
   p.total_q = total_q; p.scale = scale; p.softcap = softcap; p.causal = causal; p.window = window;
   if (softcap > 0.f)
-    rc = (hd == 128) ? launch_bwd<128, true>(tq, tdo, tk, tv, p, max_tiles, stream)
-                     : launch_bwd<64, true>(tq, tdo, tk, tv, p, max_tiles, stream);
+    rc = (hd == 128) ? launch_bwd<128, true>(tq, tdo, tk, tv, tdq, p, max_tiles, stream)
+                     : launch_bwd<64, true>(tq, tdo, tk, tv, tdq, p, max_tiles, stream);
   else
-    rc = (hd == 128) ? launch_bwd<128, false>(tq, tdo, tk, tv, p, max_tiles, stream)
-                     : launch_bwd<64, false>(tq, tdo, tk, tv, p, max_tiles, stream);
+    rc = (hd == 128) ? launch_bwd<128, false>(tq, tdo, tk, tv, tdq, p, max_tiles, stream)
+                     : launch_bwd<64, false>(tq, tdo, tk, tv, tdq, p, max_tiles, stream);
   return rc;
 }
+
+// 1 (default): dQ leaves the SM as tiled reduce-adds from shared memory; 0: per-thread vector reductions
+void ftb_attn_set_dq_bulk(int on) { g_dq_bulk = on; }
 
 }  // extern "C"

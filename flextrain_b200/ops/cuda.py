@@ -40,6 +40,8 @@ def load(name: str) -> ctypes.CDLL:
     _libs[name] = lib
     if name == "gemm_tcgen05" and os.environ.get("FTB_GEMM_TWO_SM", "1") == "0":
         lib.ftb_gemm_set_two_sm(c_int(0))   # one-SM tiles for every shape (A/B comparisons)
+    if name == "attention" and os.environ.get("FTB_ATTN_DQ_BULK", "1") == "0":
+        lib.ftb_attn_set_dq_bulk(c_int(0))      # backward: dQ by per-thread vector reductions (A/B comparisons)
     if name == "gemm_tcgen05" and os.environ.get("FTB_TMAP_CACHE", "1") == "0":
         lib.ftb_gemm_set_tmap_cache(c_int(0))   # encode the tensor maps on every call
     if name == "gemm_tcgen05" and os.environ.get("FTB_TP_PULL", "bulk") == "threads":

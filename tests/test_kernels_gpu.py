@@ -586,3 +586,31 @@ def test_tensor_map_cache_reuses_encodings_and_keeps_results():
     out2 = k.gemm(a2, b, trans_b=True)
     assert k.tmap_cache_stats()["misses"] > s1["misses"]
     assert _rel(out2, a2.float() @ b.float().t()) < 5e-3
+
+
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attention_bwd_dq_drains_agree(hd):
+    """dQ leaves the SM either as tiled reduce-adds from shared memory (default) or as per-thread vector reductions;
+    with the ordered mode on, both add the same fp32 partial tiles in the same order, so dQ agrees bit for bit."""
+    from flextrain_b200.ops import attention_cuda as fa
+    from flextrain_b200.ops import cuda as kk
+    H, KV = 4, 2
+    lens_q, lens_k = [640, 300, 1], [640, 428, 129]
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32, device=DEV)
+    q, k, v = _rand(sum(lens_q), H, hd), _rand(sum(lens_k), KV, hd), _rand(sum(lens_k), KV, hd)
+    do = _rand(sum(lens_q), H, hd)
+    kw = dict(scale=hd ** -0.5)
+    o, lse = fa.fwd(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), **kw)
+    lib = kk.load("attention")
+    try:
+        a = fa.bwd(do, q, k, v, o, lse, cu_q, cu_k, max(lens_q), max(lens_k), deterministic=True, **kw)
+        lib.ftb_attn_set_dq_bulk(0)
+        b = fa.bwd(do, q, k, v, o, lse, cu_q, cu_k, max(lens_q), max(lens_k), deterministic=True, **kw)
+    finally:
+        lib.ftb_attn_set_dq_bulk(1)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    ow, lw = ref.attention_fwd(q, k, v, cu_q, cu_k, **kw)
+    wq, _, _ = ref.attention_bwd(do, q, k, v, ow, lw, cu_q, cu_k, **kw)
+    assert _rel(a[0], wq) < 2e-2
+    assert kk.device_error_words().get("attention", 0) == 0
