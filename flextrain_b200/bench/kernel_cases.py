@@ -2,7 +2,7 @@
 
     python -m flextrain_b200.bench.kernel_cases gemm_fwd|gemm_dgrad|gemm_wgrad|rmsnorm_bwd|softmax_ce|attn_fwd|attn_bwd|
                                                   attn_fwd_one_tile|attn_bwd_unordered|attn_bwd_thread_reds|attn_fwd_32k|attn_bwd_32k|attn_bwd_32k_thread_reds|gdn_fwd|gdn_bwd|
-                                                  gdn_long_fwd|rope|ffn_glu_fwd|ffn_glu_bwd|gdn_fla_fwd|attn_fa2_fwd|attn_fa2_bwd|attn_fa2_fwd_32k|attn_fa2_bwd_32k
+                                                  gdn_long_fwd|rope|ffn_glu_fwd|ffn_glu_bwd|moe_grouped_gemm|moe_grouped_wgrad|moe_plan|gdn_fla_fwd|attn_fa2_fwd|attn_fa2_bwd|attn_fa2_fwd_32k|attn_fa2_bwd_32k
 
 Each case holds a few hundred MB on the device (inputs larger than the 126 MB L2), runs three warm-up launches and
 ten timed launches with CUDA events, and prints achieved TFLOP/s or GB/s.  They are the commands behind the
@@ -157,6 +157,31 @@ def main(case: str) -> None:
         inv = ops.rope_inv_freq(hd, 5e5).to(dev)
         ms = _time(lambda: ops.rope(x, pos, inv))
         print(f"{case}: T={T} H={H} hd={hd}  {ms:.3f} ms  {2.0 * T * H * hd * 2 / ms / 1e6:.0f} GB/s (1 read + 1 write)")
+    elif case in ("moe_grouped_gemm", "moe_grouped_wgrad", "moe_plan"):
+        # Qwen3-30B-A3B expert shapes: 128 experts, d 2048, expert width 768, top-8 routing of one 16,384-token chunk
+        E, D, F, T, K = 128, 2048, 768, 16384, 8
+        torch.manual_seed(3)
+        logits = torch.randn(T, E, device=dev)
+        experts = logits.topk(K, dim=1).indices.to(torch.int32)
+        if case == "moe_plan":
+            ms = _time(lambda: ops.moe_plan(experts, E, 64))
+            print(f"{case}: T={T} K={K} E={E}  {ms:.3f} ms (histogram + scan + map kernels, no host read)")
+        else:
+            plan = ops.moe_plan(experts, E, 64)
+            R = int(plan.R)
+            x = torch.randn(R, D, device=dev, dtype=bf) * 0.5
+            w = torch.randn(E, 2 * F, D, device=dev, dtype=bf) * D ** -0.5
+            if case == "moe_grouped_gemm":
+                out = torch.empty(R, 2 * F, device=dev, dtype=bf)
+                ms = _time(lambda: k.grouped_gemm(x, w, plan.offsets, out=out))
+                print(f"{case}: rows={R} E={E} N={2 * F} K={D}  {ms:.3f} ms  {2.0 * T * K * 2 * F * D / ms / 1e9:.0f} "
+                      f"TFLOP/s (useful rows)")
+            else:
+                dy = torch.randn(R, 2 * F, device=dev, dtype=bf) * 0.1
+                gw = torch.zeros(E, 2 * F, D, device=dev, dtype=bf)
+                ms = _time(lambda: k.grouped_wgrad(dy, x, plan.offsets, gw))
+                print(f"{case}: rows={R} E={E} N={2 * F} K={D}  {ms:.3f} ms  {2.0 * T * K * 2 * F * D / ms / 1e9:.0f} "
+                      f"TFLOP/s (useful rows)")
     elif case in ("ffn_glu_fwd", "ffn_glu_bwd"):
         # Llama-3.1-8B gated FFN on one 16,384-token chunk: fused GEMM + activation epilogue against GEMM then activation
         M, K, F = 16384, 4096, 14336
