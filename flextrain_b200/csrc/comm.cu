@@ -166,6 +166,71 @@ __global__ void __launch_bounds__(RS_THREADS) reduce_scatter_kernel(PeerTable bu
   }
 }
 
+// The same reduce-scatter through the NVSwitch: `mc` is the multicast address of the symmetric gradient arena (every
+// rank's copy bound to one multicast object), so ONE `multimem.ld_reduce` returns the sum over all ranks, added inside
+// the switch with fp32 accumulation: this rank pulls count elements instead of world x count, and no SM adds anything.
+// bf16 segments come back as bf16 (the switch rounds the fp32 sum once), fp32 segments as fp32.  Ranges that are not
+// 16-byte aligned (never the case for ranges cut by shard_range) fall back to the peer-pointer loop.
+__global__ void __launch_bounds__(RS_THREADS) reduce_scatter_mc_kernel(const char* __restrict__ mc, PeerTable bufs,
+                                                                        const __grid_constant__ SegTable tab,
+                                                                        float* __restrict__ out, int world, float scale) {
+  const int k = find_seg(tab, blockIdx.x);
+  const Seg& sg = tab.s[k];
+  const long base = ((long)blockIdx.x - tab.block_start[k]) * RS_PER_BLOCK;
+  if (sg.dtype == 0) {
+    const long i0 = base + (long)threadIdx.x * 8;
+    if (i0 >= sg.count) return;
+    if (i0 + 8 <= sg.count && ((sg.begin + i0) & 7) == 0 && (sg.byte_off & 15) == 0) {
+      const char* a = mc + sg.byte_off + (sg.begin + i0) * 2;
+      uint4 u;
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                   : "l"(a)
+                   : "memory");
+      float f[8];
+      unpack8(u, f);
+      float4* o = reinterpret_cast<float4*>(out + sg.out_off + i0);
+      o[0] = make_float4(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
+      o[1] = make_float4(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
+    } else {
+      for (int e = 0; e < 8 && i0 + e < sg.count; ++e) {
+        float acc = 0.f;
+        for (int r = 0; r < world; ++r) {
+          const bf16* src = reinterpret_cast<const bf16*>(reinterpret_cast<const char*>(bufs.ptr[r]) + sg.byte_off);
+          acc += __bfloat162float(src[sg.begin + i0 + e]);
+        }
+        out[sg.out_off + i0 + e] = acc * scale;
+      }
+    }
+  } else {
+    // fp32 segments (norm gains): four elements per 16-byte in-switch reduction
+    const long i0 = base + (long)threadIdx.x * 8;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long i = i0 + 4 * h;
+      if (i >= sg.count) break;
+      if (i + 4 <= sg.count && ((sg.begin + i) & 3) == 0 && (sg.byte_off & 15) == 0) {
+        const char* a = mc + sg.byte_off + (sg.begin + i) * 4;
+        float4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "l"(a)
+                     : "memory");
+        *reinterpret_cast<float4*>(out + sg.out_off + i) = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+      } else {
+        for (int e = 0; e < 4 && i + e < sg.count; ++e) {
+          float acc = 0.f;
+          for (int r = 0; r < world; ++r) {
+            const float* src = reinterpret_cast<const float*>(reinterpret_cast<const char*>(bufs.ptr[r]) + sg.byte_off);
+            acc += src[sg.begin + i + e];
+          }
+          out[sg.out_off + i + e] = acc * scale;
+        }
+      }
+    }
+  }
+}
+
 struct AdamHyper {
   float lr, beta1, beta2, eps, wd, bc1, bc2;
 };
@@ -378,6 +443,24 @@ int ftb_comm_reduce_scatter(void* const* bufs, int n, const long* byte_off, cons
   if (rc) return rc;
   if (blocks == 0) return 0;
   reduce_scatter_kernel<<<(unsigned)blocks, RS_THREADS, 0, s>>>(t, tab, out, world, rank, scale);
+  CHECK_LAUNCH();
+}
+
+// `mc` = multicast address of the same symmetric buffer (see reduce_scatter_mc_kernel); `bufs` are the peer mappings
+// used for ranges that are not 16-byte aligned.
+int ftb_comm_reduce_scatter_mc(const void* mc, void* const* bufs, int n, const long* byte_off, const long* begin,
+                               const long* count, const long* out_off, const int* dtype, float* out, int world,
+                               float scale, cudaStream_t s) {
+  if (world > MAX_RANKS || mc == nullptr) return -2;
+  PeerTable t;
+  for (int i = 0; i < world; ++i) t.ptr[i] = bufs[i];
+  SegTable tab;
+  long blocks = 0;
+  int rc = fill_table(tab, n, byte_off, begin, count, out_off, dtype, &blocks);
+  if (rc) return rc;
+  if (blocks == 0) return 0;
+  reduce_scatter_mc_kernel<<<(unsigned)blocks, RS_THREADS, 0, s>>>(reinterpret_cast<const char*>(mc), t, tab, out, world,
+                                                                   scale);
   CHECK_LAUNCH();
 }
 

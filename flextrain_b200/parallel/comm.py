@@ -28,12 +28,13 @@ class _RawCudaBuffer:
 class SymmetricBuffer:
     """A buffer that exists at the same size on every rank; ``ptrs[r]`` is rank r's copy mapped here."""
 
-    def __init__(self, local: torch.Tensor, ptrs: List[int], owner=None):
+    def __init__(self, local: torch.Tensor, ptrs: List[int], owner=None, mc_ptr: int = 0):
         self.local = local
         self.ptrs = ptrs
         self.nbytes = local.numel()
         self._owner = owner
         self.c_ptrs = (c_void_p * len(ptrs))(*ptrs)
+        self.mc_ptr = mc_ptr          # NVSwitch multicast address of the buffer (0: none; see PeerGroup.alloc)
 
 
 class PeerGroup:
@@ -49,6 +50,7 @@ class PeerGroup:
         self.lib = load("comm")
         self.timeout_s = timeout_s
         self._bufs: List[SymmetricBuffer] = []
+        self._symm: List[SymmetricBuffer] = []
         self._raw: List[int] = []
         self.num_flag_slots = num_flag_slots
         self.flags = self.alloc(num_flag_slots * MAX_RANKS * 4)
@@ -56,12 +58,27 @@ class PeerGroup:
         self.epoch = 0
 
     # ---------------------------------------------------------------- allocation
-    def alloc(self, nbytes: int) -> SymmetricBuffer:
+    def alloc(self, nbytes: int, multicast: bool = False) -> SymmetricBuffer:
+        """``multicast=True`` allocates through ``torch.distributed._symmetric_memory`` (``cuMemCreate`` memory bound
+        to an NVSwitch multicast object) so that kernels can reduce or broadcast in the switch with ``multimem.*``
+        on ``buf.mc_ptr``; the peers' copies are mapped as well, so everything that works on ``ptrs`` still does.
+        Falls back to the plain peer mapping when the platform reports no multicast support."""
         nbytes = (max(int(nbytes), 16) + 255) // 256 * 256
         sizes = [None] * self.world
         self.dist.all_gather_object(sizes, nbytes, group=self.pg)
         if any(s != nbytes for s in sizes):
             raise RuntimeError(f"symmetric allocation sizes differ across ranks: {sizes}")
+        if multicast:
+            import torch.distributed._symmetric_memory as symm
+            with torch.cuda.device(self.device):
+                t = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+                hdl = symm.rendezvous(t, group=self.pg if self.pg is not None else self.dist.group.WORLD)
+            mc = int(hdl.multicast_ptr) if getattr(hdl, "has_multicast_support", lambda: True)() else 0
+            t.zero_()
+            buf = SymmetricBuffer(t, [int(p) for p in hdl.buffer_ptrs], (self, hdl), mc_ptr=mc)
+            self._symm.append(buf)                       # torch owns and frees these
+            self.dist.barrier(group=self.pg)
+            return buf
         with torch.cuda.device(self.device):
             p = c_void_p()
             rc = self.lib.ftb_comm_alloc(ctypes.byref(p), ctypes.c_size_t(nbytes))

@@ -145,7 +145,12 @@ class P2PDataParallel(_Base):
 
     # ------------------------------------------------------------------- set-up
     def buffer_kwargs(self) -> dict:
-        return {"device_alloc": lambda nbytes, tag: self.group.alloc(nbytes), "shard_opt": True}
+        # FTB_DP_MULTIMEM=1: the gradient arena is bound to an NVSwitch multicast object and the reduce-scatter pulls
+        # in-switch sums (multimem.ld_reduce) instead of reading every peer's copy
+        import os
+        mm = os.environ.get("FTB_DP_MULTIMEM", "0") == "1"
+        return {"device_alloc": lambda nbytes, tag: self.group.alloc(nbytes, multicast=(mm and tag == "grads")),
+                "shard_opt": True}
 
     def attach(self, am) -> None:
         from ..optim import AdamW, HybridMuonAdamW, Muon, uses_muon
@@ -255,11 +260,18 @@ class P2PDataParallel(_Base):
         from .. import ops
         segs = self.units[key]
         bm = self.am.buffers
+        mc = getattr(bm.grad_arena, "mc_ptr", 0)
         for i0 in range(0, len(segs), 16):
             n, boff, beg, cnt, ooff, dts = self._tables(segs[i0:i0 + 16], "grad")
-            rc = self.lib.ftb_comm_reduce_scatter(bm.grad_arena.c_ptrs, c_int(n), boff, beg, cnt, ooff, dts,
-                                                  c_void_p(self.grad_shard.data_ptr()), c_int(self.world),
-                                                  c_int(self.rank), c_float(scale), c_void_p(stream.cuda_stream))
+            if mc:
+                rc = self.lib.ftb_comm_reduce_scatter_mc(c_void_p(mc), bm.grad_arena.c_ptrs, c_int(n), boff, beg, cnt,
+                                                         ooff, dts, c_void_p(self.grad_shard.data_ptr()),
+                                                         c_int(self.world), c_float(scale),
+                                                         c_void_p(stream.cuda_stream))
+            else:
+                rc = self.lib.ftb_comm_reduce_scatter(bm.grad_arena.c_ptrs, c_int(n), boff, beg, cnt, ooff, dts,
+                                                      c_void_p(self.grad_shard.data_ptr()), c_int(self.world),
+                                                      c_int(self.rank), c_float(scale), c_void_p(stream.cuda_stream))
             if rc != 0:
                 raise RuntimeError(f"ftb_comm_reduce_scatter failed ({rc})")
             ops._count()

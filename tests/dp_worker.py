@@ -17,6 +17,9 @@ def main():
     backend = backend.replace("_accum", "")
     clip = 0.05 if backend.endswith("_clip") else None       # well below the norm of these gradients: every step clips
     backend = backend.replace("_clip", "")
+    if backend.endswith("_mm"):             # gradient reduce-scatter as in-switch reductions (multimem.ld_reduce)
+        os.environ["FTB_DP_MULTIMEM"] = "1"
+        backend = backend[:-3]
     hybrid = backend.endswith("_muon")      # Muon for the hidden matrices, AdamW for the rest
     backend = backend.replace("_muon", "")
     if backend == "p2p_param":              # peer-memory path with the parameter all-gather deferred into the QKV GEMM
@@ -69,7 +72,8 @@ def main():
         same = all(torch.equal(allflat[0], f) for f in allflat)
         from flextrain_b200.ops import cuda as k
         torch.save({"params": flat, "losses": losses, "ranks_identical": same, "errors": k.device_error_words(),
-                    "libs": sorted(k._libs), "deferred_layers": deferred, "norms": norms}, out_path)
+                    "libs": sorted(k._libs), "deferred_layers": deferred, "norms": norms,
+                    "multicast": bool(getattr(getattr(am.buffers, "grad_arena", None), "mc_ptr", 0))}, out_path)
     dist.barrier()
     dist.destroy_process_group()
 

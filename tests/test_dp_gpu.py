@@ -97,3 +97,20 @@ def test_hybrid_muon_on_peer_memory_path_matches_collective(tmp_path):
     d = (a["params"] - b["params"]).abs()
     # Newton-Schulz in bf16 amplifies the bf16-vs-fp32 difference of the reduced gradient a little
     assert float(d.mean()) < 5e-4 and float(d.max()) < 5e-2, (float(d.mean()), float(d.max()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_in_switch_gradient_reduction_matches_peer_loads(tmp_path):
+    """``FTB_DP_MULTIMEM=1``: the gradient arena is bound to an NVSwitch multicast object and every rank pulls the sum of
+    its range with ``multimem.ld_reduce`` (added inside the switch) instead of loading each peer's copy.  bf16 sums are
+    rounded once by the switch, so parameters agree with the peer-load path to bf16 round-off."""
+    n = min(torch.cuda.device_count(), 4)
+    a = _run("p2p_mm", str(tmp_path / "mm.pt"), n)
+    if not a["multicast"]:
+        pytest.skip("this platform reports no NVLink multicast support")
+    b = _run("p2p", str(tmp_path / "p2p.pt"), n)
+    assert a["ranks_identical"] and all(v == 0 for v in a["errors"].values()), a["errors"]
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 2e-2, (a["losses"], b["losses"])
+    d = (a["params"] - b["params"]).abs()
+    assert float(d.mean()) < 2e-4 and float(d.max()) < 2e-2, (float(d.mean()), float(d.max()))
