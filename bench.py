@@ -420,68 +420,6 @@ def run_reference(args):
         # (flextrain/core/working_set.py:1684-1736): when it rejects its own candidates on a 180 GB GPU, offer a
         # smaller chunk cap, then a smaller GPU budget, then the nominal link figure, then its default bf16
         # optimizer state; the first plan that builds is the one that runs, and the JSON line says which.
-        am, errors, chosen = None, [], None
-        # state dtype (the configuration's fp32 first, the reference's own bf16 default last) x GPU budget (descending:
-        # the largest budget whose plan also survives the reference's own allocations wins) x link figure x chunk cap
-        ladder = [(st, g, hw, m)
-                  for st in ("float32", "bfloat16")
-                  for g in (None, 160, 140, 120, 96, 64, 31)
-                  for hw in ("probed", "nominal")
-                  for m in (None, 16384, 8192, 4096)]
-        oom_at = set()                       # (state, gpu budget) whose plan ran out of device memory: skip its variants
-        for st, g, hw, m in ladder:
-            if (st, g) in oom_at:
-                continue
-            opt = AdamW(AdamWHyperparams(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0),
-                        state_dtype=getattr(torch, st))
-            hwc, mbw = hw_probed if hw == "probed" else hw_nominal
-            try:
-                am = ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len,
-                                   max_global_batch_tokens=per_rank,
-                                   max_gpu_mem_bytes=int(free) if g is None else min(int(free), g << 30),
-                                   max_host_mem_bytes=host_budget, max_chunk_size=m, hw_cost=hwc, mem_bw_gbps=mbw,
-                                   hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5}, device=dev)
-                chosen = {"opt_state": st, "hw_cost": hw, "max_gpu_gib": g, "max_chunk_size": m}
-                break
-            except (ValueError, RuntimeError, AssertionError, MemoryError) as e:
-                msg = f"{st}/gpu={g}/{hw}/chunk={m}: {type(e).__name__}: {str(e)[:160]}"
-                errors.append(msg)
-                print("[reference arm] attempt failed: " + msg.replace("\n", " "), file=sys.stderr, flush=True)
-                if len(errors) == 1 and rank == 0 and isinstance(e, ValueError):
-                    # the planner's own trace of the first (preferred) attempt, so a log shows why it was refused
-                    import contextlib
-                    with contextlib.redirect_stdout(sys.stderr):
-                        try:
-                            ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len,
-                                          max_global_batch_tokens=per_rank, max_gpu_mem_bytes=int(free),
-                                          max_host_mem_bytes=host_budget, max_chunk_size=m, hw_cost=hwc,
-                                          mem_bw_gbps=mbw, device=dev, verbose=True,
-                                          hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5})
-                        except Exception:
-                            pass
-                if not isinstance(e, ValueError):
-                    # an allocation of the reference's own plan failed (device or pinned memory): the other link / chunk
-                    # variants of this budget plan the same memory, go to the next smaller GPU budget
-                    oom_at.add((st, g))
-                    import gc
-                    gc.collect()
-                    torch.cuda.empty_cache()
-        if am is None:
-            for line in errors:
-                print("[reference arm] " + line, file=sys.stderr)
-            try:                                    # the planner's own trace for the last attempt
-                ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len, max_global_batch_tokens=per_rank,
-                              max_gpu_mem_bytes=int(free), max_host_mem_bytes=host_budget, hw_cost=hw_probed[0],
-                              mem_bw_gbps=hw_probed[1], device=dev, verbose=True,
-                              hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5})
-            except Exception:
-                pass
-            raise RuntimeError(f"no plan builds ({len(errors)} attempts); first: {errors[0]}; last: {errors[-1]}")
-        ws = am.working_set if hasattr(am, "working_set") else None
-        if rank == 0:
-            print(f"[reference arm] plan {chosen}: " + (f"round {ws.target_round_tokens} chunk {ws.max_chunk_size} "
-                  f"gpu layers {ws.n_gpu_layers}/{ws.n_gpu_grads}/{ws.n_gpu_opt_layers} host act "
-                  f"{ws.host_act_buffer_size / 2 ** 30:.1f} GiB" if ws is not None else ""), file=sys.stderr, flush=True)
         src = SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234)
 
         def next_batch():
@@ -525,8 +463,148 @@ def run_reference(args):
                 dist.all_reduce(t)
             return float(t) / gbatch
 
+        def agree(ok: bool) -> bool:
+            """True only if every rank says so (the ranks must walk the plan ladder in lock-step)."""
+            if world == 1:
+                return ok
+            t = torch.tensor([1 if ok else 0], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            return bool(int(t.item()))
+
+        def teardown(m) -> None:
+            """Give back what a reference engine holds: its buffers and its cudaHostRegister'ed host memory (the
+            reference's own process-wide clean-up, flextrain/engine/host_memory.py:215-233)."""
+            import gc
+            try:
+                b = getattr(m, "buffers", None)
+                if b is not None and hasattr(b, "destroy"):
+                    b.destroy()
+            except Exception:
+                pass
+            try:
+                from flextrain.engine import unregister_all_process_pinned_memory
+                unregister_all_process_pinned_memory()
+            except Exception:
+                pass
+            del m
+            gc.collect()
+            torch.cuda.empty_cache()
+
+        am, errors, chosen = None, [], None
+        trial = None                         # (StepStats, seconds) of the first warm-up step, run as part of the attempt
+        # state dtype (the configuration's fp32 first, the reference's own bf16 default last) x GPU budget (descending:
+        # the largest budget whose plan also survives the reference's own allocations wins) x link figure x chunk cap
+        ladder = [(st, g, hw, m)
+                  for st in ("float32", "bfloat16")
+                  for g in (None, 150, 120, 96, 64, 31)
+                  for hw in ("probed", "nominal")
+                  for m in (None, 16384, 8192, 4096)]
+        oom_at = set()                       # (state, gpu budget) whose plan ran out of device memory: skip its variants
+        for st, g, hw, m in ladder:
+            if (st, g) in oom_at:
+                continue
+            opt = AdamW(AdamWHyperparams(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0),
+                        state_dtype=getattr(torch, st))
+            hwc, mbw = hw_probed if hw == "probed" else hw_nominal
+            try:
+                am = ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len,
+                                   max_global_batch_tokens=per_rank,
+                                   max_gpu_mem_bytes=int(free) if g is None else min(int(free), g << 30),
+                                   max_host_mem_bytes=host_budget, max_chunk_size=m, hw_cost=hwc, mem_bw_gbps=mbw,
+                                   hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5}, device=dev)
+                chosen = {"opt_state": st, "hw_cost": hw, "max_gpu_gib": g, "max_chunk_size": m}
+            except (ValueError, RuntimeError, AssertionError, MemoryError) as e:
+                msg = f"{st}/gpu={g}/{hw}/chunk={m}: {type(e).__name__}: {str(e)[:160]}"
+                errors.append(msg)
+                print("[reference arm] attempt failed: " + msg.replace("\n", " "), file=sys.stderr, flush=True)
+                if len(errors) == 1 and rank == 0 and isinstance(e, ValueError):
+                    # the planner's own trace of the first (preferred) attempt, so a log shows why it was refused
+                    import contextlib
+                    with contextlib.redirect_stdout(sys.stderr):
+                        try:
+                            ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len,
+                                          max_global_batch_tokens=per_rank, max_gpu_mem_bytes=int(free),
+                                          max_host_mem_bytes=host_budget, max_chunk_size=m, hw_cost=hwc,
+                                          mem_bw_gbps=mbw, device=dev, verbose=True,
+                                          hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5})
+                        except Exception:
+                            pass
+                if not isinstance(e, ValueError):
+                    # an allocation of the reference's own plan failed (device or pinned memory): the other link / chunk
+                    # variants of this budget plan the same memory, go to the next smaller GPU budget
+                    oom_at.add((st, g))
+                    import gc
+                    del e
+                    gc.collect()
+                    torch.cuda.empty_cache()
+                am = None
+            if not agree(am is not None):
+                if am is not None:
+                    teardown(am)
+                    am = None
+                continue
+            # The plan built on every rank.  Its first warm-up step is part of the attempt: a plan that takes the whole
+            # GPU can still run out of device memory in the reference's own step-time allocations (seen at 8 ranks:
+            # round = chunk = 65,536 tokens, 23 layers resident); then the engine is given back and the next smaller
+            # GPU budget is planned.  The ranks agree before the gradient all-reduce and after the optimizer step, so
+            # no rank waits in a collective for one that gave up.
+            failed = None
+            if args.warmup >= 1:
+                barrier()
+                t0 = time.perf_counter()
+                st_trial = None
+                try:
+                    st_trial = am.fwd_bwd(next_batch(), loss_scale_factor=1.0 / gbatch, total_tokens_per_step=gbatch)
+                    torch.cuda.synchronize()
+                except (RuntimeError, MemoryError) as e:
+                    failed = f"{type(e).__name__}: {str(e)[:160]}"
+                    del e
+                if agree(failed is None):
+                    try:
+                        if world > 1:
+                            allreduce_grads()
+                        am.step()
+                        torch.cuda.synchronize()
+                    except (RuntimeError, MemoryError) as e:
+                        failed = f"{type(e).__name__}: {str(e)[:160]}"
+                        del e
+                    if not agree(failed is None):
+                        failed = failed or "another rank ran out of memory in the optimizer step"
+                else:
+                    failed = failed or "another rank ran out of memory in the first forward / backward"
+                if failed is None:
+                    barrier()
+                    trial = (st_trial, time.perf_counter() - t0)
+            if failed is not None:
+                msg = f"{st}/gpu={g}/{hw}/chunk={m}: first step: {failed}"
+                errors.append(msg)
+                print("[reference arm] attempt failed: " + msg.replace("\n", " "), file=sys.stderr, flush=True)
+                oom_at.add((st, g))
+                st_trial = None
+                teardown(am)
+                am = None
+                continue
+            break
+        if am is None:
+            for line in errors:
+                print("[reference arm] " + line, file=sys.stderr)
+            try:                                    # the planner's own trace for the last attempt
+                ref.from_dims(dims, arch="llama", optimizer=opt, max_seq_len=seq_len, max_global_batch_tokens=per_rank,
+                              max_gpu_mem_bytes=int(free), max_host_mem_bytes=host_budget, hw_cost=hw_probed[0],
+                              mem_bw_gbps=hw_probed[1], device=dev, verbose=True,
+                              hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5})
+            except Exception:
+                pass
+            raise RuntimeError(f"no plan builds ({len(errors)} attempts); first: {errors[0]}; last: {errors[-1]}")
+        ws = am.working_set if hasattr(am, "working_set") else None
+        if rank == 0:
+            print(f"[reference arm] plan {chosen}: " + (f"round {ws.target_round_tokens} chunk {ws.max_chunk_size} "
+                  f"gpu layers {ws.n_gpu_layers}/{ws.n_gpu_grads}/{ws.n_gpu_opt_layers} host act "
+                  f"{ws.host_act_buffer_size / 2 ** 30:.1f} GiB" if ws is not None else ""), file=sys.stderr, flush=True)
         loss_step1, warm_s = None, 0.0
-        for i in range(args.warmup):
+        if trial is not None:
+            loss_step1, warm_s = ref_loss(trial[0]), trial[1]
+        for i in range(1 if trial is not None else 0, args.warmup):
             barrier()
             t0 = time.perf_counter()
             st = one_step(next_batch())
