@@ -69,16 +69,9 @@ class PeerGroup:
         if any(s != nbytes for s in sizes):
             raise RuntimeError(f"symmetric allocation sizes differ across ranks: {sizes}")
         if multicast:
-            import torch.distributed._symmetric_memory as symm
-            with torch.cuda.device(self.device):
-                t = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
-                hdl = symm.rendezvous(t, group=self.pg if self.pg is not None else self.dist.group.WORLD)
-            mc = int(hdl.multicast_ptr) if getattr(hdl, "has_multicast_support", lambda: True)() else 0
-            t.zero_()
-            buf = SymmetricBuffer(t, [int(p) for p in hdl.buffer_ptrs], (self, hdl), mc_ptr=mc)
-            self._symm.append(buf)                       # torch owns and frees these
-            self.dist.barrier(group=self.pg)
-            return buf
+            buf = self._alloc_multicast(nbytes)
+            if buf is not None:
+                return buf
         with torch.cuda.device(self.device):
             p = c_void_p()
             rc = self.lib.ftb_comm_alloc(ctypes.byref(p), ctypes.c_size_t(nbytes))
@@ -104,6 +97,29 @@ class PeerGroup:
         buf = SymmetricBuffer(local, ptrs, self)
         self._bufs.append(buf)
         self._raw.append(p.value)
+        self.dist.barrier(group=self.pg)
+        return buf
+
+    def _alloc_multicast(self, nbytes: int):
+        """Symmetric buffer bound to an NVSwitch multicast object, or ``None`` when this platform / PyTorch build cannot
+        provide one (every rank then takes the plain peer mapping: the ranks agree on the outcome first)."""
+        buf, err = None, None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            with torch.cuda.device(self.device):
+                t = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+                hdl = symm.rendezvous(t, group=self.pg if self.pg is not None else self.dist.group.WORLD)
+            mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+            if mc:
+                t.zero_()
+                buf = SymmetricBuffer(t, [int(p) for p in hdl.buffer_ptrs], (self, hdl), mc_ptr=mc)
+        except Exception as e:                       # no symmetric-memory support in this build / on this fabric
+            err = e
+        oks = [None] * self.world
+        self.dist.all_gather_object(oks, buf is not None, group=self.pg)
+        if not all(oks):
+            return None
+        self._symm.append(buf)                       # torch owns and frees these
         self.dist.barrier(group=self.pg)
         return buf
 
