@@ -168,7 +168,7 @@ def main(case: str) -> None:
             print(f"{case}: T={T} K={K} E={E}  {ms:.3f} ms (histogram + scan + map kernels, no host read)")
         else:
             plan = ops.moe_plan(experts, E, 64)
-            R = int(plan.R)
+            R = int(plan.rows)
             x = torch.randn(R, D, device=dev, dtype=bf) * 0.5
             w = torch.randn(E, 2 * F, D, device=dev, dtype=bf) * D ** -0.5
             if case == "moe_grouped_gemm":
