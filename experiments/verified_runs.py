@@ -15,12 +15,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LINE = re.compile(r"\[step\s+(\d+)\].*loss ([\d.]+).*tok/s ([\d,]+) TFLOPS_eff ([\d.]+) TFLOPS_hw ([\d.]+) max_alloc ([\d.]+)")
 
 
-def run_row(model: str, mode: str, steps: int, read_step: int, seq_len: int, batch: int, gpus: int, extra):
+def run_row(model: str, mode: str, steps: int, read_step: int, seq_len: int, batch: int, gpus: int, extra, out_dir=None):
     base = [sys.executable] if gpus == 1 else [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                                                f"--nproc-per-node={gpus}", "--master-addr", "127.0.0.1"]
     cmd = base + [os.path.join(ROOT, "train.py"), "--model", f"dims:{model}" if not os.path.isdir(model) else model,
                   "--mode", mode, "--max-seq-len", str(seq_len), "--max-global-batch-tokens", str(batch), "--steps",
                   str(steps), "--data-source", "synthetic"] + list(extra)
+    if out_dir and "--output-dir" not in extra:        # keep each row's train.py outputs under this table's directory
+        cmd += ["--output-dir", os.path.join(out_dir, f"{os.path.basename(str(model))}_{mode}")]
     p = subprocess.run(cmd, capture_output=True, text=True)
     row = {"model": model, "mode": mode, "gpus": gpus, "rc": p.returncode}
     for m in LINE.finditer(p.stdout):
@@ -45,7 +47,8 @@ if __name__ == "__main__":
     ap.add_argument("--tok-s-tolerance", type=float, default=0.05, help="allowed relative throughput change vs --baseline")
     a, extra = ap.parse_known_args()
     os.makedirs(a.out, exist_ok=True)
-    rows = [run_row(*r.split(":"), a.steps, a.read_step, a.seq_len, a.batch, a.gpus, extra) for r in a.rows.split(",")]
+    rows = [run_row(*r.split(":"), a.steps, a.read_step, a.seq_len, a.batch, a.gpus, extra, a.out)
+            for r in a.rows.split(",")]
     json.dump(rows, open(os.path.join(a.out, "rows.json"), "w"), indent=1)
     with open(os.path.join(a.out, "table.md"), "w") as f:
         f.write("| model | mode | gpus | loss | tok/s | TFLOPS eff | TFLOPS hw | max alloc GiB |\n|---|---|---|---|---|---|---|---|\n")
