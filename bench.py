@@ -429,7 +429,8 @@ def run_reference(args):
         def allreduce_grads():
             # constructed multi-GPU wrapper: the reference has no distributed mode, so the ranks' host gradients
             # are summed with NCCL through a device staging buffer between fwd_bwd and step
-            bufs = []
+            torch.cuda.synchronize()        # the engine writes every layer's gradients back to the host on its own
+            bufs = []                       # outbound stream at the end of that layer's backward: let those copies land
             b = am.buffers
             for d in (getattr(b, "host_grads", None) or []):
                 bufs += list(d.values()) if isinstance(d, dict) else [d]
