@@ -306,3 +306,23 @@ def test_planner_chooses_parallel_layout_by_fit():
     assert (ws.tp, ws.ep) == (8, 1), (ws.tp, ws.ep, ws.report[-3:])
     ws = plan("qwen3_30B_A3B", 262144)
     assert (ws.tp, ws.ep) == (1, 8), (ws.tp, ws.ep, ws.report[-3:])
+
+
+def test_layout_candidates_follow_divisibility_and_optimizer():
+    import flextrain_b200 as ft
+    from flextrain_b200.api import layout_candidates
+    from flextrain_b200.io.arch.common import config_from_dims
+    import json, os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    table = json.load(open(os.path.join(root, "flextrain_b200", "configs", "model_dims.json")))
+
+    def mc(name):
+        d = dict(table[name]); arch = d.pop("arch", "llama"); hyper = d.pop("hyperparams", None) or {}
+        return config_from_dims(d, arch, hyper)
+
+    dense, moe = mc("llama3_1_8B"), mc("qwen3_30B_A3B")
+    assert layout_candidates(dense, 1) == [(1, 1)]
+    assert layout_candidates(dense, 8, ft.AdamW()) == [(1, 1), (8, 1)]
+    assert layout_candidates(dense, 8, ft.HybridMuonAdamW()) == [(1, 1)]        # Muon needs whole matrices
+    assert layout_candidates(dense, 3, ft.AdamW()) == [(1, 1)]                  # 32 heads / 8 KV heads do not split by 3
+    assert layout_candidates(moe, 8, ft.AdamW()) == [(1, 1), (1, 8)]            # 128 experts over 8 ranks; no tp for MoE
