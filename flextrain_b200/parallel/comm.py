@@ -113,7 +113,7 @@ class PeerGroup:
             if mc:
                 t.zero_()
                 buf = SymmetricBuffer(t, [int(p) for p in hdl.buffer_ptrs], (self, hdl), mc_ptr=mc)
-        except Exception as e:                       # no symmetric-memory support in this build / on this fabric
+        except Exception as e:                       # this PyTorch or this fabric has no symmetric-memory support
             err = e
         oks = [None] * self.world
         self.dist.all_gather_object(oks, buf is not None, group=self.pg)
