@@ -40,6 +40,29 @@ def test_verified_runs_table_and_regression_diff(tmp_path):
     assert p3.returncode != 0
 
 
+def test_verified_runs_subcommands(tmp_path):
+    """The reference's sub-command surface: run-one, report, compare."""
+    vr = os.path.join(ROOT, "experiments", "verified_runs.py")
+    out = tmp_path / "t"
+    p = subprocess.run([sys.executable, vr, "run-one", "--row", "tiny_llama:full", "--out", str(out), "--steps", "2",
+                        "--read-step", "2", "--seq-len", "64", "--batch", "512"], capture_output=True, text=True, cwd=ROOT)
+    assert p.returncode == 0, p.stderr[-800:]
+    assert (out / "tiny_llama_full" / "row.json").exists()
+    p = subprocess.run([sys.executable, vr, "report", "--runs-dir", str(out)], capture_output=True, text=True, cwd=ROOT)
+    assert p.returncode == 0 and "tiny_llama" in p.stdout and (out / "table.md").exists()
+    p = subprocess.run([sys.executable, vr, "compare", "--baseline", str(out), "--rerun", str(out)],
+                       capture_output=True, text=True, cwd=ROOT)
+    assert p.returncode == 0, p.stdout
+    rows = json.load(open(out / "rows.json"))
+    rows[0]["loss"] += 0.01
+    other = tmp_path / "u"
+    other.mkdir()
+    json.dump(rows, open(other / "rows.json", "w"))
+    p = subprocess.run([sys.executable, vr, "compare", "--baseline", str(out), "--rerun", str(other)],
+                       capture_output=True, text=True, cwd=ROOT)
+    assert p.returncode == 1 and "DIFF" in p.stdout
+
+
 def test_scaling_law_synthetic_grid(tmp_path):
     sl = _load("scaling_law")
     train, val, ent = sl.write_synthetic_corpus(str(tmp_path / "corpus"), 200_000, 512)
@@ -55,6 +78,22 @@ def test_scaling_law_synthetic_grid(tmp_path):
     best = {b: min(r["val_loss"] for r in res["rows"] if r["budget"] == b) for b in (2e10, 6e10)}
     assert best[6e10] < best[2e10]
     assert (tmp_path / "grid" / "table.md").exists()
+
+
+def test_scaling_law_subcommands(tmp_path):
+    """run-one adds a run directory; plot re-fits from what is on disk."""
+    sl = _load("scaling_law")
+    out = str(tmp_path / "g")
+    common = ["--synthetic-corpus", "100000", "--vocab-size", "512", "--batch-tokens", "2048", "--seq-len", "64",
+              "--peak-lr", "3e-3", "--device", "cpu", "--eval-tokens", "4096"]
+    for d, L in ((64, 1), (64, 2), (128, 2)):
+        sl.main(["run-one", "--d-model", str(d), "--n-layers", str(L), "--total-flops", "2e10", "--out", out] + common)
+    res = sl.main(["plot", "--runs-dir", out])
+    assert len(res["rows"]) == 3 and set(res["fits"]) == {"2e+10"}
+    assert os.path.exists(os.path.join(out, "table.md")) and os.path.exists(os.path.join(out, "fit.json"))
+    smoke = sl.main(["run-grid", "--out", str(tmp_path / "s"), "--smoke", "--budgets", "1e10,2e10,4e10", "--ladder",
+                     "64:1,64:2,128:2"] + common)
+    assert len(smoke["rows"]) == 4                         # 2 budgets x 2 sizes
 
 
 def test_parabola_fit_recovers_a_known_optimum():
