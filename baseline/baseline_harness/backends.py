@@ -41,6 +41,7 @@ class Backend:
 
     def command(self, spec: RunSpec) -> Tuple[List[str], Dict[str, str]]:
         cmd, env = self.build(spec)
+        cmd = list(cmd) + [str(a) for a in spec.extra.get("backend_extra_args", [])]     # raw pass-through arguments
         env = {"PYTHONPATH": REPO_ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), **env}
         return cmd, env
 

@@ -42,7 +42,45 @@ def parse_args(argv=None):
                     help="backend-specific knob (repeatable), e.g. --set dp_shard=opt+grad")
     ap.add_argument("--timeout", type=int, default=3600)
     ap.add_argument("--dry-run", action="store_true")
+    ap.add_argument("--seed", type=int, default=None)
+    ap.add_argument("--master-port", type=int, default=None)
+    # Named spellings of the backend knobs (the reference's launcher spells them out one by one,
+    # baseline/run_baseline.py there); each lands in the same dictionary as --set key=value, and a backend uses the
+    # ones it knows.
+    g = ap.add_argument_group("backend knobs (same as --set <name with underscores>=VALUE)")
+    for flag, kind in KNOB_FLAGS:
+        if kind is bool:
+            g.add_argument("--" + flag, action="store_true", default=None)
+        else:
+            g.add_argument("--" + flag, type=kind, default=None)
+    g.add_argument("--no-use-liger-kernel", dest="use_liger_kernel", action="store_false")
+    g.add_argument("--backend-extra-arg", action="append", default=[], metavar="ARG",
+                   help="raw argument appended to the backend's command line (repeatable)")
     return ap.parse_args(argv)
+
+
+KNOB_FLAGS = (("activation-checkpointing", bool), ("activation-checkpoint-fraction", float),
+              ("activation-checkpoint-interval", int), ("activation-checkpoint-selective-option", str),
+              ("activation-offload", bool), ("attn-implementation", str), ("context-parallel-size", int),
+              ("cpu-offloading-num-layers", int), ("fsdp-replicate-degree", int), ("fsdp-shard-degree", int),
+              ("learning-rate", float), ("weight-decay", float), ("liger-kernel", bool), ("use-liger-kernel", bool),
+              ("megatron-script", str), ("moe-kernel-backend", str), ("num-grad-slabs", int), ("offload-modules", str),
+              ("optimizer-offload", bool), ("param-offload", bool), ("pipeline-parallel-size", int),
+              ("recompute-granularity", str), ("recompute-method", str), ("recompute-modules", str),
+              ("recompute-num-layers", int), ("save-activation-layer-fraction", float), ("sequence-parallel-size", int),
+              ("tensor-parallel-size", int), ("tiled-loss-shards", int), ("tiled-mlp", bool),
+              ("torchtitan-config", str), ("torchtitan-module", str), ("zero-stage", int))
+
+
+def knob_extras(args) -> dict:
+    out = {}
+    for flag, _ in KNOB_FLAGS:
+        v = getattr(args, flag.replace("-", "_"), None)
+        if v is not None:
+            out[flag.replace("-", "_")] = v
+    if args.backend_extra_arg:
+        out["backend_extra_args"] = list(args.backend_extra_arg)
+    return out
 
 
 def _parse_sets(items):
@@ -108,7 +146,12 @@ def main(argv=None) -> int:
                    seq_length=args.seq_length, micro_batch_size=args.micro_batch_size,
                    gradient_accumulation_steps=args.gradient_accumulation_steps, num_steps=args.num_steps,
                    warmup_steps=args.warmup_steps, num_gpus=args.num_gpus or detect_num_gpus() or 1,
-                   output_dir=args.output_dir, run_name=args.run_name, extra=_parse_sets(args.set))
+                   output_dir=args.output_dir, run_name=args.run_name,
+                   extra={**knob_extras(args), **_parse_sets(args.set)})
+    if args.seed is not None:
+        spec.seed = args.seed
+    if args.master_port is not None:
+        spec.master_port = args.master_port
     spec.validate()
     rec = run_spec(spec, dry_run=args.dry_run, timeout=args.timeout)
     return 0 if rec["status"] in ("ok", "dry-run", "skipped") else 1

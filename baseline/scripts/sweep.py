@@ -67,7 +67,7 @@ def main(argv=None) -> int:
     ap.add_argument("--backends", default=None, help="comma-separated subset of the config's sections")
     ap.add_argument("--num-steps", type=int, default=None)
     ap.add_argument("--num-gpus", type=int, default=None)
-    ap.add_argument("--output-dir", default=None)
+    ap.add_argument("--output-dir", "--output-root", dest="output_dir", default=None)
     ap.add_argument("--timeout", type=int, default=3600)
     ap.add_argument("--dry-run", action="store_true")
     args = ap.parse_args(argv)

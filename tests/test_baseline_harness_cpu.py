@@ -87,3 +87,17 @@ def test_torchtitan_launcher_trains_a_tiny_model_on_cpu():
     a = tt.model_args_from_preset("llama3_1_8B", 1024)
     hidden = a.multiple_of * ((int(a.ffn_dim_multiplier * int(2 * 4 * a.dim / 3)) + a.multiple_of - 1) // a.multiple_of)
     assert (a.dim, a.n_layers, a.n_heads, a.n_kv_heads, hidden) == (4096, 32, 32, 8, 14336)
+
+
+def test_named_knob_flags_reach_the_backend_command(capsys):
+    """The launcher's named knobs (the reference's flag spellings) and raw pass-through arguments end up on the
+    backend's command line exactly like ``--set``."""
+    from baseline.run_baseline import main as run_main
+    rc = run_main(["--backend", "hf_fsdp2", "--dry-run", "--activation-checkpointing", "--attn-implementation", "eager",
+                   "--seed", "7", "--backend-extra-arg=--n-layers", "--backend-extra-arg", "2"])
+    out = capsys.readouterr().out
+    assert rc == 0 and "--activation-checkpointing" in out and "--attn-implementation eager" in out
+    assert "--seed 7" in out and out.strip().endswith("--n-layers 2")
+    rc = run_main(["--backend", "torchtitan", "--dry-run", "--set", "ac_mode=selective", "--zero-stage", "3"])
+    out = capsys.readouterr().out
+    assert rc == 0 and "--ac-mode selective" in out and "zero" not in out      # a knob the backend does not know is dropped
