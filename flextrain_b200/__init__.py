@@ -5,7 +5,7 @@ Public surface (mirrors flextrain/__init__.py:7-32):
 ``StepStats``, the optimizers, ``Sequence`` and the token sources, ``HardwareCost``,
 ``WorkingSetConfig``.
 """
-from .api import BuildContext, from_dims, from_pretrained, register_block_builder
+from .api import BlockBuilder, BuildContext, from_dims, from_pretrained, register_block_builder
 from .core.save_level import HardwareCost, SaveLevelPlan
 from .core.working_set import WorkingSetConfig, determine_working_set_config
 from .engine.active_model import ActiveModel, StepStats
@@ -18,7 +18,7 @@ from . import export  # noqa: E402  (``flextrain_b200.export.save_hf_full`` / ``
 __version__ = "0.1.0"
 
 __all__ = [
-    "from_pretrained", "from_dims", "register_block_builder", "BuildContext", "ActiveModel", "StepStats",
+    "from_pretrained", "from_dims", "register_block_builder", "BlockBuilder", "BuildContext", "ActiveModel", "StepStats",
     "AdamW", "Muon", "HybridMuonAdamW", "Sequence", "TokenSource", "SyntheticTokenSource", "RawTokenSource",
     "ShardTokenSource", "JsonSFTTokenSource", "CustomSchemaTokenSource", "HFTokenSource", "RankStridedSource", "MultimodalJsonSource",
     "HardwareCost",

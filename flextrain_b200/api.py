@@ -22,7 +22,10 @@ from .engine.active_model import ActiveModel
 from .io.arch import select_arch_module
 from .io.arch.common import DTypePolicy, ModelConfig, build_model_parts, config_from_dims, resolve_lora
 
-_BLOCK_BUILDERS: Dict[str, Callable] = {}
+# ``builder(layer_id, decoder_config, model_config) -> Layer`` (the reference's alias of the same name takes
+# ``(layer_id, BuildContext)``, flextrain/api.py:119)
+BlockBuilder = Callable[[int, object, object], object]
+_BLOCK_BUILDERS: Dict[str, BlockBuilder] = {}
 
 
 @dataclass
