@@ -62,3 +62,25 @@ class UnpinnedHostBackend:
 
 def default_backend(device) -> HostMemoryBackend:
     return LocalPinnedHostBackend() if torch.device(device).type == "cuda" else UnpinnedHostBackend()
+
+
+def default_host_backend(device="cuda") -> HostMemoryBackend:
+    """The reference's name for :func:`default_backend` (flextrain/engine/host_memory.py)."""
+    return default_backend(device)
+
+
+def unregister_all_process_pinned_memory() -> int:
+    """Undo every ``cudaHostRegister`` this process still holds through :class:`LocalPinnedHostBackend` (engines that
+    were dropped without ``destroy()`` leave registrations behind); returns how many were released
+    (flextrain/engine/host_memory.py:215-233)."""
+    n = 0
+    try:
+        rt = torch.cuda.cudart()
+    except Exception:
+        rt = None
+    for ptr in list(_REGISTERED):
+        if rt is not None:
+            rt.cudaHostUnregister(ptr)
+        _REGISTERED.pop(ptr, None)
+        n += 1
+    return n

@@ -32,6 +32,36 @@ def _suffix(name: str) -> str:
     return name[2:] if name.startswith(("w_", "b_")) and not name.startswith("b_") else name
 
 
+def state_key(state_tensor_name: str, param_name: str) -> str:
+    """Key of an optimizer-state tensor: ``<state name>_<parameter name without its w_ prefix>`` (``o_adam_m_q`` for
+    ``w_q``; flextrain/optim/base.py:78-87)."""
+    return f"{state_tensor_name}_{_suffix(param_name)}"
+
+
+@dataclass
+class AdamWHyperparams:
+    """Hyper-parameter record in the reference's spelling (flextrain/optim/adamw.py:25-37): ``AdamW(AdamWHyperparams(...),
+    state_dtype=...)`` builds the same optimizer as ``AdamW(lr=..., ...)``."""
+    lr: float = 1e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.001
+    check_error: bool = False
+
+
+@dataclass
+class MuonHyperparams:
+    """(flextrain/optim/muon.py:22-33; the Newton-Schulz coefficients are fixed in the kernels here.)"""
+    lr: float = 1e-3
+    beta: float = 0.95
+    eps: float = 1e-8
+    ns_iters: int = 5
+    weight_decay: float = 0.0
+    nesterov: bool = True
+    check_error: bool = False
+
+
 class Optimizer(Protocol):
     def state_specs(self, param_spec: ParamSpec) -> List[OptimizerStateSpec]: ...
     def step(self, param_spec: ParamSpec, params, grads, state, step_num: int, grad_scale: float = 1.0) -> int: ...
@@ -56,6 +86,16 @@ class AdamW:
     state_dtype: torch.dtype = torch.bfloat16
     check_error: bool = False
     no_decay_1d: bool = True
+
+    def __post_init__(self):
+        if isinstance(self.lr, AdamWHyperparams):            # AdamW(AdamWHyperparams(...), state_dtype=...)
+            hp = self.lr
+            self.lr, self.beta1, self.beta2, self.eps = hp.lr, hp.beta1, hp.beta2, hp.eps
+            self.weight_decay, self.check_error = hp.weight_decay, hp.check_error
+
+    @property
+    def hp(self) -> "AdamWHyperparams":
+        return AdamWHyperparams(self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.check_error)
 
     def state_specs(self, param_spec: ParamSpec) -> List[OptimizerStateSpec]:
         out = []
@@ -100,6 +140,12 @@ class Muon:
     nesterov: bool = True
     state_dtype: torch.dtype = torch.bfloat16
     check_error: bool = False
+
+    def __post_init__(self):
+        if isinstance(self.lr, MuonHyperparams):             # Muon(MuonHyperparams(...))
+            hp = self.lr
+            self.lr, self.beta, self.weight_decay = hp.lr, hp.beta, hp.weight_decay
+            self.ns_iters, self.nesterov, self.check_error = hp.ns_iters, hp.nesterov, hp.check_error
 
     def state_specs(self, param_spec: ParamSpec) -> List[OptimizerStateSpec]:
         return [OptimizerStateSpec(f"o_muon_{_suffix(t.name)}", t.shape, t.opt_state_dtype or self.state_dtype, t.name)

@@ -68,3 +68,22 @@ def test_run_config_from_yaml(tmp_path):
     argv = _train_argv(c)
     assert "--use-muon" in argv and argv[argv.index("--tp") + 1] == "2" and argv[argv.index("--save-state-every") + 1] == "3"
     assert RunConfig.from_dict({}).train.steps > 0                                  # defaults fill everything
+
+
+def test_reference_style_optimizer_constructors_and_package_exports():
+    """``AdamW(AdamWHyperparams(...), state_dtype=...)`` / ``Muon(MuonHyperparams(...))`` build the same optimizers as
+    the keyword form, and the sub-packages export the names a user of the reference imports from them."""
+    import torch
+    from flextrain_b200.optim import AdamW, AdamWHyperparams, Muon, MuonHyperparams, state_key
+    a = AdamW(AdamWHyperparams(lr=3e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0), state_dtype=torch.float32)
+    assert a == AdamW(lr=3e-5, weight_decay=0.0, state_dtype=torch.float32) and a.hp.lr == 3e-5
+    assert Muon(MuonHyperparams(lr=2e-3, ns_iters=3)).ns_iters == 3
+    assert state_key("o_adam_m", "w_q") == "o_adam_m_q"
+    from flextrain_b200.engine import (BufferManager, ChunkPolicy, EventBook, LocalPinnedHostBackend, StreamBundle,  # noqa: F401
+                                        default_host_backend, prepare_training_chunks, split_sequences,
+                                        unregister_all_process_pinned_memory)
+    from flextrain_b200.core import (ActivationSchema, ChunkMeta, HardwareCost, Layer, ParamSpec, SaveLevelPlan,  # noqa: F401
+                                      TensorSpec, build_dp_tables, probe_hardware)
+    from flextrain_b200.nn import IGNORE_INDEX, CrossEntropyLoss, LMHead, TokenEmbedLayer  # noqa: F401
+    from flextrain_b200.io import Sequence, ShardTokenSource, SyntheticTokenSource, TokenSource  # noqa: F401
+    assert IGNORE_INDEX == -100 and unregister_all_process_pinned_memory() == 0
