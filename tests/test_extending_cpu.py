@@ -61,3 +61,16 @@ def test_phi3_example_matches_transformers(tmp_path):
     assert not info["missing_keys"] and not info["unexpected_keys"], info
     with torch.no_grad():
         assert abs(hf_loss(m2) - want) / want < 2e-4
+
+
+def test_finetune_and_export_example_runs_on_cpu(tmp_path):
+    """``examples/finetune_and_export.py``: LoRA steps on the toy model, then the adapter / merged / base exports."""
+    import subprocess, sys, os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    p = subprocess.run([sys.executable, os.path.join(root, "examples", "finetune_and_export.py"), "--dims", "tiny_llama",
+                        "--steps", "2", "--out", str(tmp_path / "x")], capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert "exports written" in p.stdout
+    for sub, name in (("adapter", "adapter_model.safetensors"), ("merged", "config.json"), ("base_only", "config.json")):
+        assert os.path.exists(tmp_path / "x" / sub / name), (sub, os.listdir(tmp_path / "x" / sub))
