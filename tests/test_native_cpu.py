@@ -326,3 +326,37 @@ def test_layout_candidates_follow_divisibility_and_optimizer():
     assert layout_candidates(dense, 8, ft.HybridMuonAdamW()) == [(1, 1)]        # Muon needs whole matrices
     assert layout_candidates(dense, 3, ft.AdamW()) == [(1, 1)]                  # 32 heads / 8 KV heads do not split by 3
     assert layout_candidates(moe, 8, ft.AdamW()) == [(1, 1), (1, 8)]            # 128 experts over 8 ranks; no tp for MoE
+
+
+def test_planner_estimate_never_gets_worse_with_more_gpu_memory():
+    """For a fixed model and batch, a larger GPU budget never yields a slower estimated step (2 % slack for ties
+    between regimes), and every plan respects the invariants of its regime."""
+    import json, os
+    import flextrain_b200 as ft
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    table = json.load(open(os.path.join(root, "flextrain_b200", "configs", "model_dims.json")))
+    opt = ft.AdamW(lr=1e-5, state_dtype=torch.float32)
+
+    def plan(name, gpu_gib):
+        d = dict(table[name]); arch = d.pop("arch", "llama"); hyper = d.pop("hyperparams", None)
+        try:
+            return ft.from_dims(d, arch=arch, hyperparams=hyper, optimizer=opt, max_seq_len=2048,
+                                max_global_batch_tokens=65536, max_gpu_mem_bytes=gpu_gib << 30,
+                                max_host_mem_bytes=192 << 30, device="cpu", plan_only=True)
+        except ValueError:
+            return None
+
+    for name in ("llama3_1_8B", "llama3_2_1B", "olmoe_1B_7B"):
+        prev, seen_feasible = None, False
+        for g in (12, 16, 24, 32, 48, 64, 96, 128, 178):
+            ws = plan(name, g)
+            if ws is None:
+                assert not seen_feasible, f"{name}: feasible at a smaller budget but not at {g} GiB"
+                continue
+            seen_feasible = True
+            assert ws.max_chunk_size <= ws.target_round_tokens <= 65536 and ws.max_chunk_size % 128 == 0
+            assert ws.est_step_ms > 0 and ws.n_gpu_act_slots >= 1
+            if prev is not None:
+                assert ws.est_step_ms <= prev * 1.02, (name, g, ws.est_step_ms, prev)
+            prev = ws.est_step_ms
+        assert seen_feasible
