@@ -12,6 +12,7 @@ from __future__ import annotations
 import argparse
 import json
 import sys
+from dataclasses import dataclass
 
 import torch
 
@@ -62,6 +63,33 @@ def run_config(name: str, steps: int, device: str, lr: float = 5e-4, window: int
         diffs.append(abs(st.loss - float(loss.detach())))
     win = [sum(diffs[i:i + window]) / len(diffs[i:i + window]) for i in range(0, len(diffs), window)]
     return {"config": name, "max_windowed_abs_dloss": max(win), "final_engine": le[-1], "final_naive": ln[-1]}
+
+
+@dataclass
+class LossCurveParityConfig:
+    """One run of the harness (the reference's record of the same name, flextrain/bench/parity.py): which forced
+    working set (``CONFIGS`` key), how many steps, where."""
+    config: str = "A"
+    steps: int = 30
+    device: str = "cpu"
+    lr: float = 5e-4
+    window: int = 10
+    tolerance: float = 0.06              # bound on the windowed mean |engine loss - naive loss|
+
+
+@dataclass
+class LossCurveParityResult:
+    config: str
+    max_windowed_abs_dloss: float
+    final_engine: float
+    final_naive: float
+    passed: bool
+
+
+def run_loss_curve_parity(cfg: LossCurveParityConfig) -> LossCurveParityResult:
+    r = run_config(cfg.config, cfg.steps, cfg.device, cfg.lr, cfg.window)
+    return LossCurveParityResult(r["config"], r["max_windowed_abs_dloss"], r["final_engine"], r["final_naive"],
+                                 r["max_windowed_abs_dloss"] <= cfg.tolerance)
 
 
 class _CPUView:
