@@ -103,3 +103,43 @@ def test_lora_exports_against_transformers(name, tmp_path):
                                                                  output_loading_info=True)
     assert not info["missing_keys"] and not info["unexpected_keys"]
     assert abs(hf_loss(m2) - want) / want < 2e-4                                               # (3) merged
+
+
+def test_moe_lora_adapter_export_carries_the_expert_adapters(tmp_path):
+    """Per-expert adapters leave as one PEFT module per expert (gate / up share the expert's A and split B); base weight
+    + scale * B @ A equals the merged export for every expert projection."""
+    import json
+    import os
+    import flextrain_b200 as ft
+    from safetensors import safe_open
+    from flextrain_b200.export import save_hf_full, save_hf_merged, save_lora_adapter
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cat = json.load(open(os.path.join(root, "flextrain_b200", "configs", "model_dims.json")))
+    d = dict(cat["tiny_moe"]); arch = d.pop("arch"); hyper = d.pop("hyperparams", None)
+    f32 = torch.float32
+    am = ft.from_dims(d, arch=arch, hyperparams=hyper, optimizer=ft.AdamW(lr=1e-2, state_dtype=f32), max_seq_len=64,
+                      max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30, device="cpu",
+                      compute_dtype=f32, master_dtype=f32, grad_dtype=f32, lora_targets="all", lora_rank=4, lora_alpha=8.0)
+    src = ft.SyntheticTokenSource(d["vocab_size"], 64, seed=0, pin=False)
+    for _ in range(2):
+        am.fwd_bwd(src.get_sequences(256)); am.step()
+    save_lora_adapter(am, str(tmp_path / "a")); save_hf_full(am, str(tmp_path / "b")); save_hf_merged(am, str(tmp_path / "m"))
+
+    def load(p):
+        with safe_open(p, "pt") as f:
+            return {k: f.get_tensor(k) for k in f.keys()}
+
+    ad, base, merged = (load(str(tmp_path / n / fn)) for n, fn in (("a", "adapter_model.safetensors"),
+                                                                  ("b", "model.safetensors"), ("m", "model.safetensors")))
+    cfg = json.load(open(tmp_path / "a" / "adapter_config.json"))
+    assert {"gate_proj", "up_proj", "down_proj", "q_proj"} <= set(cfg["target_modules"])
+    scale = cfg["lora_alpha"] / cfg["r"]
+    checked = 0
+    for k in ad:
+        if ".experts." in k and k.endswith(".lora_A.weight"):
+            mod = k[len("base_model.model."):-len(".lora_A.weight")]
+            delta = scale * ad[k.replace("lora_A", "lora_B")] @ ad[k]
+            assert float(delta.abs().max()) > 0                      # the adapters did train
+            assert torch.allclose(base[mod + ".weight"].float() + delta, merged[mod + ".weight"].float(), atol=1e-6)
+            checked += 1
+    assert checked == d["n_layers"] * d["num_routed_experts"] * 3
