@@ -10,6 +10,8 @@ chunk), so chunk token counts are not multiples of the shard width and the sched
 and one rank has more rounds and more chunks than the other (it is padded with filler chunks).
 ``tp_hostopt``: as ``tp`` with the optimizer state kept in host memory and streamed through a two-slot device ring
 during ``step()`` (what a 70B model over 8 tensor-parallel ranks needs); results must equal the resident run.
+``ep_lora``: as ``ep`` with LoRA on every projection, including per-expert adapters on the sharded expert stacks; the
+merged weights (base + adapters, gathered) must match the unsharded run.
 ``tp_grid`` / ``ep_grid``: model-parallel groups of two ranks inside a larger job (a ``dp x tp`` / ``dp x ep`` grid over
 library collectives); every group trains on its share of the batch.
 """
@@ -47,7 +49,7 @@ def build(dev, dtype, world, rank, mode, backend):
     par = {"ep": mp} if mode.startswith("ep") else {"tp": mp}
     lora = dict(lora_targets="all", lora_rank=4, lora_alpha=8.0, lora_adapter_compute_dtype=dtype,
                 lora_adapter_master_dtype=dtype, lora_adapter_grad_dtype=dtype,
-                lora_adapter_opt_state_dtype=torch.float32) if mode == "tp_lora" else {}
+                lora_adapter_opt_state_dtype=torch.float32) if mode in ("tp_lora", "ep_lora") else {}
     hybrid = mode == "ep_hybrid"        # Gated DeltaNet + gated attention layers, routed + shared experts
     gemma = mode == "tp_gemma"          # sandwich norms, per-head QK-norm, sliding + global layers, tied scaled embedding
     hyper = {"sliding_window": 64, "layer_pattern": "SF"} if gemma else None
@@ -70,7 +72,7 @@ def train(am, rank, world, dev, mode):
     ragged = mode in ("tp_ragged", "ep_ragged")
     src = ft.SyntheticTokenSource(512, RAGGED if ragged else SEQ, seed=5)
     losses = []
-    for _ in range(4 if mode == "tp_lora" else STEPS):      # LoRA: B starts at zero, A only moves from step 2 on
+    for _ in range(4 if mode in ("tp_lora", "ep_lora") else STEPS):      # LoRA: B starts at zero, A only moves from step 2 on
         seqs = src.get_sequences(sum(RAGGED) if ragged else GB)
         if mode.startswith("ep"):
             seqs = seqs[rank::world]                  # data parallel: each rank takes its share of the batch
@@ -105,10 +107,10 @@ def main():
     losses = train(am, rank, world, dev, mode)
     if am.ep is not None:
         am.ep.check()
-    merge = mode == "tp_lora"                     # compare base + adapters, merged: the adapters are what trained
+    merge = mode in ("tp_lora", "ep_lora")        # compare base + adapters, merged: the adapters are what trained
     state = collect_hf_state(am, lora_merge=merge)      # collective: gathers the tensor- / expert-parallel parts
     adapters = {}
-    if mode == "tp_lora":                         # gather every adapter (collective) for a direct comparison
+    if mode in ("tp_lora", "ep_lora"):            # gather every adapter (collective) for a direct comparison
         from flextrain_b200.io.hf_weights import gather_local_parts
         for l, layer in enumerate(am.layers):
             for n, t in am.buffers.host_params(l).items():
@@ -116,7 +118,7 @@ def main():
                     spec = layer.param_spec.get(n)
                     adapters[(l, n)] = (gather_local_parts(t.detach(), spec, am) if spec.is_local_part else t.detach()).float().cpu()
     adapter_dir = out_path + ".adapter"
-    if mode == "tp_lora":
+    if mode in ("tp_lora", "ep_lora"):
         from flextrain_b200.export import save_lora_adapter
         save_lora_adapter(am, adapter_dir)        # collective gather of the sharded adapters; rank 0 writes
     res = None

@@ -78,3 +78,27 @@ def test_engine_expert_parallel_with_unequal_chunks_and_rounds(tmp_path):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     res = json.load(open(out))
     assert res["local_rows"] == 4 and res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
+
+
+def test_engine_expert_parallel_lora_with_per_expert_adapters(tmp_path):
+    """ep=2 with LoRA on every projection: each rank holds the adapters of its own experts (3-D ``A`` / ``B`` sliced like
+    the expert stacks), the dense adapters are replicated and reduced; the merged weights, gathered over the ranks, match
+    the unsharded run."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "epl.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective",
+           "ep_lora", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert res["local_rows"] == 4
+    assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
+    # every adapter (gathered over the ranks) equals the unsharded run's, the adapters did move, and the PEFT file
+    # written by rank 0 holds all 8 experts of layer 0 (4 of them live on the other rank)
+    assert res["adapter_diff"] < 1e-3 and res["adapter_moved"] > 0, res
+    shapes = res["adapter_file_shapes"]
+    experts = {k.split(".experts.")[1].split(".")[0] for k in shapes if ".experts." in k}
+    assert experts == {str(e) for e in range(8)}, sorted(experts)
+    assert shapes["base_model.model.model.layers.0.mlp.experts.7.gate_proj.lora_A.weight"] == [4, 128]
+    assert shapes["base_model.model.model.layers.0.mlp.experts.7.down_proj.lora_B.weight"] == [128, 4]
