@@ -35,7 +35,7 @@ def _run(am, src, steps):
     return out
 
 
-@pytest.mark.parametrize("variant", ["resident", "rings", "muon", "lora"])
+@pytest.mark.parametrize("variant", ["resident", "rings", "muon", "lora", "moe_lora"])
 def test_resume_is_exact(variant, tmp_path):
     kw = dict(dims=DIMS, max_seq_len=64, batch_tokens=128)
     if variant == "rings":
@@ -46,7 +46,10 @@ def test_resume_is_exact(variant, tmp_path):
                                              adamw=ft.AdamW(lr=2e-3, state_dtype=torch.float32))
     else:
         kw["optimizer"] = ft.AdamW(lr=2e-3, weight_decay=0.1, state_dtype=torch.float32)
-    if variant == "lora":
+    if variant == "moe_lora":            # per-expert adapters on the routed expert stacks
+        kw["dims"] = dict(DIMS, expert_dim=64, ffn_dim=64, num_routed_experts=4, top_k=2)
+        kw["arch"] = "qwen3_moe"
+    if variant in ("lora", "moe_lora"):
         f32 = torch.float32
         kw.update(lora_targets="all", lora_rank=4, lora_alpha=8.0, lora_adapter_compute_dtype=f32,
                   lora_adapter_master_dtype=f32, lora_adapter_grad_dtype=f32, lora_adapter_opt_state_dtype=f32)
