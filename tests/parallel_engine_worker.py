@@ -12,6 +12,8 @@ and one rank has more rounds and more chunks than the other (it is padded with f
 during ``step()`` (what a 70B model over 8 tensor-parallel ranks needs); results must equal the resident run.
 ``ep_lora``: as ``ep`` with LoRA on every projection, including per-expert adapters on the sharded expert stacks; the
 merged weights (base + adapters, gathered) must match the unsharded run.
+``ep_muon``: as ``ep`` with the hybrid optimizer: Muon orthogonalises each expert matrix of the local stack and the
+replicated hidden matrices (after their gradients were reduced), AdamW takes the rest.
 ``tp_grid`` / ``ep_grid``: model-parallel groups of two ranks inside a larger job (a ``dp x tp`` / ``dp x ep`` grid over
 library collectives); every group trains on its share of the batch.
 """
@@ -60,7 +62,9 @@ def build(dev, dtype, world, rank, mode, backend):
     return ft.from_dims(dims,
                         arch="qwen3_5_moe" if hybrid else "qwen3_moe" if mode.startswith("ep") else ("gemma3" if gemma else "llama"),
                         hyperparams=hyper,
-                        optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32),
+                        optimizer=(ft.HybridMuonAdamW(muon=ft.Muon(lr=1e-3, state_dtype=torch.float32),
+                                                      adamw=ft.AdamW(lr=1e-3, state_dtype=torch.float32))
+                                   if mode == "ep_muon" else ft.AdamW(lr=1e-3, state_dtype=torch.float32)),
                         max_seq_len=seq, max_global_batch_tokens=GB, max_gpu_mem_bytes=8 << 30,
                         max_host_mem_bytes=8 << 30, device=dev, compute_dtype=dtype, master_dtype=dtype,
                         grad_dtype=dtype, working_set=ws, world_size=world, rank=rank,

@@ -102,3 +102,18 @@ def test_engine_expert_parallel_lora_with_per_expert_adapters(tmp_path):
     assert experts == {str(e) for e in range(8)}, sorted(experts)
     assert shapes["base_model.model.model.layers.0.mlp.experts.7.gate_proj.lora_A.weight"] == [4, 128]
     assert shapes["base_model.model.model.layers.0.mlp.experts.7.down_proj.lora_B.weight"] == [128, 4]
+
+
+def test_engine_expert_parallel_with_hybrid_muon(tmp_path):
+    """ep=2 with Muon on the hidden matrices: a rank orthogonalises the expert matrices it owns (a stack is a batch of
+    matrices), replicated matrices are orthogonalised identically on both ranks after the gradient reduction; matches
+    the unsharded run."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "epm.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective",
+           "ep_muon", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert res["loss_diff"] < 1e-4 and res["param_diff"] < 2e-3, res
