@@ -12,6 +12,7 @@ and one rank has more rounds and more chunks than the other (it is padded with f
 during ``step()`` (what a 70B model over 8 tensor-parallel ranks needs); results must equal the resident run.
 ``ep_lora``: as ``ep`` with LoRA on every projection, including per-expert adapters on the sharded expert stacks; the
 merged weights (base + adapters, gathered) must match the unsharded run.
+``ep_clip``: as ``ep`` with global gradient-norm clipping (the norm sums the expert parts over the group).
 ``ep_muon``: as ``ep`` with the hybrid optimizer: Muon orthogonalises each expert matrix of the local stack and the
 replicated hidden matrices (after their gradients were reduced), AdamW takes the rest.
 ``tp_grid`` / ``ep_grid``: model-parallel groups of two ranks inside a larger job (a ``dp x tp`` / ``dp x ep`` grid over
@@ -83,7 +84,7 @@ def train(am, rank, world, dev, mode):
         elif mode == "tp_grid" and world > 1:
             seqs = seqs[rank // 2::world // 2]        # each tensor-parallel pair takes its share
         st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / GB, total_tokens_per_step=GB)
-        assert am.step() == 0
+        assert am.step(max_grad_norm=0.05 if mode == "ep_clip" else None) == 0      # 0.05: every step clips
         t = torch.tensor([st.loss_sum], device=dev, dtype=torch.float64 if dev == "cpu" else torch.float32)
         if world > 1:
             dist.all_reduce(t)

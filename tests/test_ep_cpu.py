@@ -117,3 +117,17 @@ def test_engine_expert_parallel_with_hybrid_muon(tmp_path):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     res = json.load(open(out))
     assert res["loss_diff"] < 1e-4 and res["param_diff"] < 2e-3, res
+
+
+def test_engine_expert_parallel_gradient_clipping(tmp_path):
+    """Global-norm clipping under ep=2: replicated tensors count once, the ranks' expert slices are summed over the
+    group, so both ranks scale by the same factor as the unsharded run."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "epc.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "parallel_engine_worker.py"), "collective",
+           "ep_clip", out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    assert res["loss_diff"] < 1e-4 and res["param_diff"] < 1e-3, res
