@@ -212,6 +212,12 @@ def test_train_lora_sft_on_an_hf_directory_learns_and_saves(tmp_path):
     losses = _steps(r.stdout)
     assert len(losses) == 12 and losses[-1] < losses[0] - 0.3, losses
     assert os.path.exists(os.path.join(out, "final.safetensors"))
+    # LoRA mode also leaves what was trained: a PEFT adapter whose B matrices moved away from their zero start
+    from safetensors.torch import load_file
+    cfg = json.load(open(os.path.join(out, "adapter", "adapter_config.json")))
+    assert cfg["r"] == 8 and cfg["lora_alpha"] == 16
+    ad = load_file(os.path.join(out, "adapter", "adapter_model.safetensors"))
+    assert any(k.endswith("lora_B.weight") and float(v.abs().max()) > 0 for k, v in ad.items())
 
 
 def test_train_from_yaml_with_state_checkpoint(tmp_path):

@@ -242,6 +242,12 @@ def main(argv=None) -> int:
         # gathering tensor- / expert-parallel parts is a collective: every rank takes part, rank 0 writes
         path = am.save_hf(out_dir, "final.safetensors")
         say(f"[save] {path}")
+        if args.mode == "lora":
+            # final.safetensors holds the (frozen) base weights; what was trained is the adapter
+            from flextrain_b200.export import save_lora_adapter
+            apath = save_lora_adapter(am, os.path.join(out_dir, "adapter"),
+                                      base_model_name_or_path=str(args.model))
+            say(f"[save] {apath}")
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
