@@ -356,6 +356,11 @@ def _host_memory_report() -> dict:
     return out
 
 
+def _device_of(local: int) -> str:
+    """Device string of this rank (one place, so a test can walk the reference arm's control flow on CPU ranks)."""
+    return f"cuda:{local}"
+
+
 def run_reference(args):
     """The unmodified reference engine (installed under baseline/_ref) through its own public API
     (``flextrain.from_dims`` -> ``fwd_bwd`` -> ``step``): same model, sequence length, batch and optimizer."""
@@ -375,7 +380,7 @@ def run_reference(args):
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local)
-        dev = f"cuda:{local}"
+        dev = _device_of(local)
         if world > 1:
             dist.init_process_group("nccl", device_id=torch.device(dev))
         import flextrain as ref
@@ -445,13 +450,6 @@ def run_reference(args):
                     t.copy_(g, non_blocking=True)
             torch.cuda.synchronize()
 
-        def one_step(seqs):
-            st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / gbatch, total_tokens_per_step=gbatch)
-            if world > 1:
-                allreduce_grads()
-            am.step()
-            return st
-
         def barrier():
             if world > 1:
                 dist.barrier()
@@ -472,10 +470,49 @@ def run_reference(args):
             dist.all_reduce(t, op=dist.ReduceOp.MIN)
             return bool(int(t.item()))
 
+        def worst_of(code: int) -> int:
+            """Largest code over the ranks."""
+            if world == 1:
+                return code
+            t = torch.tensor([code], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return int(t.item())
+
+        def checked_step(seqs, sync: bool = False):
+            """One optimisation step -> ``(StepStats, None)`` or ``(None, why)``.  The ranks tell one another whether
+            they got through forward / backward before the gradient all-reduce, and through the optimizer step after
+            it, so a rank whose engine raised (device memory, typically) never leaves the others in a collective."""
+            failed, st = None, None
+            try:
+                st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / gbatch, total_tokens_per_step=gbatch)
+                if sync:
+                    torch.cuda.synchronize()
+            except Exception as e:
+                failed = f"{type(e).__name__}: {str(e)[:160]}"
+                del e
+            if not agree(failed is None):
+                return None, failed or "another rank failed in forward / backward"
+            try:
+                if world > 1:
+                    allreduce_grads()
+                am.step()
+                if sync:
+                    torch.cuda.synchronize()
+            except Exception as e:
+                failed = f"{type(e).__name__}: {str(e)[:160]}"
+                del e
+            if not agree(failed is None):
+                return None, failed or "another rank failed in the optimizer step"
+            return st, None
+
         def teardown(m) -> None:
             """Give back what a reference engine holds: its buffers and its cudaHostRegister'ed host memory (the
             reference's own process-wide clean-up, flextrain/engine/host_memory.py:215-233)."""
             import gc
+            try:
+                torch.cuda.synchronize()        # no copy of the engine may still be in flight on its side streams
+            except Exception:
+                pass
             try:
                 b = getattr(m, "buffers", None)
                 if b is not None and hasattr(b, "destroy"):
@@ -492,7 +529,6 @@ def run_reference(args):
             torch.cuda.empty_cache()
 
         am, errors, chosen = None, [], None
-        trial = None                         # (StepStats, seconds) of the first warm-up step, run as part of the attempt
         # state dtype (the configuration's fp32 first, the reference's own bf16 default last) x GPU budget (descending:
         # the largest budget whose plan also survives the reference's own allocations wins) x link figure x chunk cap
         ladder = [(st, g, hw, m)
@@ -530,58 +566,49 @@ def run_reference(args):
                                           hyperparams={"rope_theta": 500000.0, "rms_norm_eps": 1e-5})
                         except Exception:
                             pass
+                status = 1                  # refused by the planner
                 if not isinstance(e, ValueError):
-                    # an allocation of the reference's own plan failed (device or pinned memory): the other link / chunk
-                    # variants of this budget plan the same memory, go to the next smaller GPU budget
-                    oom_at.add((st, g))
-                    import gc
+                    status = 2              # an allocation of the reference's own plan failed (device or pinned memory)
                     del e
-                    gc.collect()
-                    torch.cuda.empty_cache()
+                    teardown(None)          # also drops the host registrations of the half-built engine
                 am = None
-            if not agree(am is not None):
+            else:
+                status = 0
+            worst = worst_of(status)
+            if worst == 2:
+                # on some rank: the other link / chunk variants of this budget plan the same memory, so every rank goes
+                # to the next smaller GPU budget
+                oom_at.add((st, g))
+            if worst != 0:
                 if am is not None:
+                    errors.append(f"{st}/gpu={g}/{hw}/chunk={m}: built here, " +
+                                  ("refused" if worst == 1 else "out of memory") + " on another rank")
                     teardown(am)
                     am = None
                 continue
-            # The plan built on every rank.  Its first warm-up step is part of the attempt: a plan that takes the whole
-            # GPU can still run out of device memory in the reference's own step-time allocations (seen at 8 ranks:
-            # round = chunk = 65,536 tokens, 23 layers resident); then the engine is given back and the next smaller
-            # GPU budget is planned.  The ranks agree before the gradient all-reduce and after the optimizer step, so
-            # no rank waits in a collective for one that gave up.
-            failed = None
-            if args.warmup >= 1:
+            # The plan built on every rank.  The warm-up steps are part of the attempt: a plan that takes the whole GPU
+            # can still run out of device memory in the reference's own step-time allocations (seen at 8 ranks: round =
+            # chunk = 65,536 tokens, 23 layers resident); then the engine is given back and the next smaller GPU budget
+            # is planned.
+            src = SyntheticTokenSource(dims["vocab_size"], seq_len, seed=1234)      # every attempt sees the same batches
+            failed, st_first, warm_s = None, None, 0.0
+            for i in range(args.warmup):
                 barrier()
                 t0 = time.perf_counter()
-                st_trial = None
-                try:
-                    st_trial = am.fwd_bwd(next_batch(), loss_scale_factor=1.0 / gbatch, total_tokens_per_step=gbatch)
-                    torch.cuda.synchronize()
-                except Exception as e:
-                    failed = f"{type(e).__name__}: {str(e)[:160]}"
-                    del e
-                if agree(failed is None):
-                    try:
-                        if world > 1:
-                            allreduce_grads()
-                        am.step()
-                        torch.cuda.synchronize()
-                    except Exception as e:
-                        failed = f"{type(e).__name__}: {str(e)[:160]}"
-                        del e
-                    if not agree(failed is None):
-                        failed = failed or "another rank ran out of memory in the optimizer step"
-                else:
-                    failed = failed or "another rank ran out of memory in the first forward / backward"
-                if failed is None:
-                    barrier()
-                    trial = (st_trial, time.perf_counter() - t0)
+                st_i, failed = checked_step(next_batch(), sync=True)
+                if failed is not None:
+                    failed = f"warm-up step {i + 1}: {failed}"
+                    break
+                barrier()
+                warm_s = time.perf_counter() - t0
+                if i == 0:
+                    st_first = st_i
             if failed is not None:
-                msg = f"{st}/gpu={g}/{hw}/chunk={m}: first step: {failed}"
+                msg = f"{st}/gpu={g}/{hw}/chunk={m}: {failed}"
                 errors.append(msg)
                 print("[reference arm] attempt failed: " + msg.replace("\n", " "), file=sys.stderr, flush=True)
                 oom_at.add((st, g))
-                st_trial = None
+                st_i = st_first = None
                 teardown(am)
                 am = None
                 continue
@@ -602,17 +629,7 @@ def run_reference(args):
             print(f"[reference arm] plan {chosen}: " + (f"round {ws.target_round_tokens} chunk {ws.max_chunk_size} "
                   f"gpu layers {ws.n_gpu_layers}/{ws.n_gpu_grads}/{ws.n_gpu_opt_layers} host act "
                   f"{ws.host_act_buffer_size / 2 ** 30:.1f} GiB" if ws is not None else ""), file=sys.stderr, flush=True)
-        loss_step1, warm_s = None, 0.0
-        if trial is not None:
-            loss_step1, warm_s = ref_loss(trial[0]), trial[1]
-        for i in range(1 if trial is not None else 0, args.warmup):
-            barrier()
-            t0 = time.perf_counter()
-            st = one_step(next_batch())
-            barrier()
-            warm_s = time.perf_counter() - t0
-            if i == 0:
-                loss_step1 = ref_loss(st)
+        loss_step1 = ref_loss(st_first) if st_first is not None else None
         steps = _budget_steps(args, t_proc0, warm_s)
         if world > 1:
             tsteps = torch.tensor([steps], device=dev)
@@ -624,7 +641,10 @@ def run_reference(args):
         t0 = time.perf_counter()
         e0.record()
         for _ in range(steps):
-            st = one_step(next_batch())
+            st, failed = checked_step(next_batch())
+            if failed is not None:              # every rank is told, so all of them leave through the same door
+                sampler.stop()
+                raise RuntimeError(f"a timed step failed after {args.warmup} good warm-up steps: {failed}")
         e1.record()
         barrier()
         e2e_ms = (time.perf_counter() - t0) * 1e3
