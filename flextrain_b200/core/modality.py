@@ -21,6 +21,7 @@ class ImageInputCPU:
     grid_thw: Tuple[int, int, int]
     first_token: int = 0                 # index of the first placeholder token in the sequence
     kind: str = "image"                  # "image" | "video"
+    frame_prefix_ids: Optional[List[List[int]]] = None   # video: token ids written before each temporal patch's block
 
     def num_placeholders(self, merge: int) -> int:
         t, h, w = self.grid_thw

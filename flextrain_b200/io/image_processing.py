@@ -12,9 +12,15 @@ torch (so a training job needs neither PIL nor the processor classes on its hot 
 4. the result is cut into ``temporal_patch x patch x patch`` blocks, flattened channel-major, and ordered
    merge-block-major: the ``merge x merge`` patches that the vision tower's merger concatenates are consecutive rows.
 
+Video clips go the same way with three differences, each checked against ``transformers``' Qwen3-VL video processor:
+frames are sampled at a target rate (:func:`sample_frame_indices`), the pixel budget of the resize counts all frames
+(:func:`smart_resize_video`), and in the text every temporal patch is a block of its own, ``<T seconds>`` + vision
+start + its placeholders + vision end, with ``T`` the mean time of the frames in the patch (:func:`video_timestamps`).
+
 :class:`MultimodalProcessorBundle` reads the geometry and the special token ids from a model directory
-(``preprocessor_config.json`` / ``config.json``) and, when a tokenizer is there, turns chat-style rows with images
-into multimodal :class:`Sequence` objects; :func:`build_multimodal_sequence` does the token-level assembly."""
+(``preprocessor_config.json`` / ``video_preprocessor_config.json`` / ``config.json``) and, when a tokenizer is there,
+turns chat-style rows with images and videos into multimodal :class:`Sequence` objects;
+:func:`build_multimodal_sequence` does the token-level assembly."""
 from __future__ import annotations
 
 import json
@@ -49,6 +55,49 @@ def smart_resize(height: int, width: int, factor: int, min_pixels: int, max_pixe
     return max(h, factor), max(w, factor)
 
 
+def smart_resize_video(num_frames: int, height: int, width: int, temporal_factor: int, factor: int,
+                       min_pixels: int, max_pixels: int) -> Tuple[int, int]:
+    """Frame size of a clip: multiples of ``factor``, with frames x height x width inside the pixel budget."""
+    if height < factor or width < factor:
+        raise ValueError(f"a {height}x{width} frame is smaller than patch*merge = {factor}")
+    if max(height, width) / min(height, width) > 200:
+        raise ValueError(f"aspect ratio of a {height}x{width} frame is beyond 200")
+    h = round(height / factor) * factor
+    w = round(width / factor) * factor
+    t = math.ceil(num_frames / temporal_factor) * temporal_factor
+    if t * h * w > max_pixels:
+        beta = math.sqrt(num_frames * height * width / max_pixels)
+        h = max(factor, math.floor(height / beta / factor) * factor)
+        w = max(factor, math.floor(width / beta / factor) * factor)
+    elif t * h * w < min_pixels:
+        beta = math.sqrt(min_pixels / (num_frames * height * width))
+        h = math.ceil(height * beta / factor) * factor
+        w = math.ceil(width * beta / factor) * factor
+    return h, w
+
+
+def sample_frame_indices(total_frames: int, source_fps: float, target_fps: float = 2.0, min_frames: int = 4,
+                         max_frames: int = 768) -> List[int]:
+    """Which frames of a ``total_frames``-long clip recorded at ``source_fps`` to keep for ``target_fps`` frames per
+    second: evenly spaced, at least ``min_frames`` and at most ``max_frames`` (and never more than there are)."""
+    n = int(total_frames / source_fps * target_fps)
+    n = min(max(n, min_frames), max_frames, total_frames)
+    if n <= 1:
+        return [0] * max(n, 1)
+    step = (total_frames - 1) / (n - 1)
+    # round half to even, as numpy's rint does
+    return [int(round(i * step)) for i in range(n)]
+
+
+def video_timestamps(frame_indices: Seq[int], source_fps: float, temporal_patch: int = 2) -> List[float]:
+    """Seconds shown in front of each temporal patch: the mean of its first and last frame's time."""
+    idx = [int(i) for i in frame_indices]
+    if len(idx) % temporal_patch:
+        idx += [idx[-1]] * (temporal_patch - len(idx) % temporal_patch)
+    ts = [i / source_fps for i in idx]
+    return [(ts[i] + ts[i + temporal_patch - 1]) / 2 for i in range(0, len(ts), temporal_patch)]
+
+
 def _to_uint8_chw(img: Any) -> torch.Tensor:
     """PIL image, ``(H, W, 3)`` uint8 array, or ``(3, H, W)`` tensor (uint8, or float in [0, 1]) -> ``(3, H, W)`` float
     tensor holding 8-bit levels."""
@@ -79,20 +128,36 @@ class ImageGeometry:
     max_pixels: int = 16 * 16 * 4 * 4096
     mean: Tuple[float, float, float] = (0.5, 0.5, 0.5)
     std: Tuple[float, float, float] = (0.5, 0.5, 0.5)
+    # video clips: pixel budget over all frames of a clip, and the frame sampling rule
+    video_min_pixels: int = 128 * 32 * 32
+    video_max_pixels: int = 768 * 32 * 32
+    video_fps: float = 2.0
+    video_min_frames: int = 4
+    video_max_frames: int = 768
 
     @property
     def patch_dim(self) -> int:
         return 3 * self.temporal_patch * self.patch * self.patch
 
 
-def preprocess_frames(frames: Seq[Any], g: ImageGeometry, resize: bool = True) -> ImageInputCPU:
-    """One image (a single frame) or one video clip (several frames of equal size) -> :class:`ImageInputCPU`."""
+def preprocess_frames(frames: Seq[Any], g: ImageGeometry, resize: bool = True,
+                      video: Optional[bool] = None) -> ImageInputCPU:
+    """One image (a single frame) or one video clip (several frames of equal size) -> :class:`ImageInputCPU`.
+    ``video`` (default: more than one frame) selects the clip's resize rule and marks the result as a clip."""
+    if isinstance(frames, torch.Tensor) and frames.dim() == 4:                 # (F, H, W, 3) or (F, 3, H, W)
+        frames = list(frames)
     ts = [_to_uint8_chw(f) for f in frames]
+    video = len(ts) > 1 if video is None else bool(video)
     H, W = ts[0].shape[-2:]
+    if any(t.shape[-2:] != (H, W) for t in ts):
+        raise ValueError("the frames of a clip must have one size")
     x = torch.stack(ts, 0)                                                     # (F, 3, H, W), 8-bit levels
     q = g.patch * g.merge
     if resize:
-        Hn, Wn = smart_resize(H, W, q, g.min_pixels, g.max_pixels)
+        if video:
+            Hn, Wn = smart_resize_video(len(ts), H, W, g.temporal_patch, q, g.video_min_pixels, g.video_max_pixels)
+        else:
+            Hn, Wn = smart_resize(H, W, q, g.min_pixels, g.max_pixels)
         if (Hn, Wn) != (H, W):
             # on 8-bit data, as an image library does it (the two separable passes each saturate to 8 bits)
             x8 = x.round().clamp_(0, 255).to(torch.uint8)
@@ -110,7 +175,7 @@ def preprocess_frames(frames: Seq[Any], g: ImageGeometry, resize: bool = True) -
     m, p = g.merge, g.patch
     x = x.view(gt, tp, 3, gh // m, m, p, gw // m, m, p)
     x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8).reshape(gt * gh * gw, 3 * tp * p * p)
-    return ImageInputCPU(pixel_values=x.contiguous(), grid_thw=(gt, gh, gw), kind="image" if len(frames) == 1 else "video")
+    return ImageInputCPU(pixel_values=x.contiguous(), grid_thw=(gt, gh, gw), kind="video" if video else "image")
 
 
 def preprocess_images(images: Seq[Any], g: Optional[ImageGeometry] = None, resize: bool = True) -> List[ImageInputCPU]:
@@ -125,29 +190,63 @@ def patchify(img: torch.Tensor, patch: int = 16, temporal_patch: int = 2, merge:
 
 def build_multimodal_sequence(segments: Seq[Any], image_token_id: int, merge: int = 2, seq_id: int = 0,
                               vision_start_token_id: Optional[int] = None, vision_end_token_id: Optional[int] = None,
-                              train_on: Optional[Seq[bool]] = None) -> Sequence:
-    """Assemble token ids and images into one training sequence.
+                              train_on: Optional[Seq[bool]] = None, video_token_id: Optional[int] = None,
+                              video_start_token_id: Optional[int] = None,
+                              video_end_token_id: Optional[int] = None) -> Sequence:
+    """Assemble token ids, images and video clips into one training sequence.
 
     ``segments`` alternates freely between lists of token ids and :class:`ImageInputCPU` objects; every image expands
-    to ``[vision_start] + image_token * n + [vision_end]`` with ``n`` its merged patch count.  ``train_on[i]`` says
-    whether the tokens of text segment ``i`` (counting all segments) are targets; image tokens never are, and the
-    token before an image never predicts it."""
+    to ``[vision_start] + image_token * n + [vision_end]`` with ``n`` its merged patch count.  A clip
+    (``kind == "video"``) expands to one such block per temporal patch, made of ``video_token_id`` and wrapped in
+    ``video_start_token_id`` / ``video_end_token_id`` (default: the image's start / end ids), each preceded by the
+    clip's ``frame_prefix_ids`` entry (the ``<T seconds>`` text) when it has one; for the rotary positions every
+    block is a single-frame image.  ``train_on[i]`` says whether the tokens of text segment ``i`` (counting all
+    segments) are targets; placeholder and wrapper tokens never are, and the token before one never predicts it."""
     ids: List[int] = []
     learn: List[bool] = []
     images: List[ImageInputCPU] = []
     spans = []
+    v_start = vision_start_token_id if video_start_token_id is None else video_start_token_id
+    v_end = vision_end_token_id if video_end_token_id is None else video_end_token_id
+
+    def block(start_id, token, n, end_id, gh, gw):
+        if start_id is not None:
+            ids.append(start_id); learn.append(False)
+        first = len(ids)
+        spans.append((first, 1, gh // merge, gw // merge))
+        ids.extend([token] * n)
+        learn.extend([False] * n)
+        if end_id is not None:
+            ids.append(end_id); learn.append(False)
+        return first
+
     for si, seg in enumerate(segments):
         if isinstance(seg, ImageInputCPU):
             t, gh, gw = seg.grid_thw
-            n = seg.num_placeholders(merge)
-            if vision_start_token_id is not None:
-                ids.append(vision_start_token_id); learn.append(False)
-            seg.first_token = len(ids)
-            spans.append((len(ids), t, gh // merge, gw // merge))
-            ids += [image_token_id] * n
-            learn += [False] * n
-            if vision_end_token_id is not None:
-                ids.append(vision_end_token_id); learn.append(False)
+            per_frame = (gh // merge) * (gw // merge)
+            if seg.kind == "video":
+                if video_token_id is None:
+                    raise ValueError("a video clip needs video_token_id")
+                pre = seg.frame_prefix_ids
+                if pre is not None and len(pre) != t:
+                    raise ValueError(f"{len(pre)} frame prefixes for {t} temporal patches")
+                for f in range(t):
+                    if pre is not None:
+                        ids.extend(int(v) for v in pre[f]); learn.extend([False] * len(pre[f]))
+                    first = block(v_start, video_token_id, per_frame, v_end, gh, gw)
+                    if f == 0:
+                        seg.first_token = first
+            else:
+                if t != 1:                                     # a multi-frame "image": one block, t advances inside it
+                    if vision_start_token_id is not None:
+                        ids.append(vision_start_token_id); learn.append(False)
+                    seg.first_token = len(ids)
+                    spans.append((len(ids), t, gh // merge, gw // merge))
+                    ids.extend([image_token_id] * (t * per_frame)); learn.extend([False] * (t * per_frame))
+                    if vision_end_token_id is not None:
+                        ids.append(vision_end_token_id); learn.append(False)
+                else:
+                    seg.first_token = block(vision_start_token_id, image_token_id, per_frame, vision_end_token_id, gh, gw)
             images.append(seg)
         else:
             seg = [int(v) for v in seg]
@@ -199,6 +298,16 @@ class MultimodalProcessorBundle:
                 g.mean = tuple(float(v) for v in pc["image_mean"])
             if pc.get("image_std"):
                 g.std = tuple(float(v) for v in pc["image_std"])
+        vp = os.path.join(model_path, "video_preprocessor_config.json")
+        if os.path.exists(vp):
+            with open(vp) as f:
+                vpc = json.load(f)
+            size = vpc.get("size") or {}
+            g.video_min_pixels = int(size.get("shortest_edge", g.video_min_pixels))
+            g.video_max_pixels = int(size.get("longest_edge", g.video_max_pixels))
+            g.video_fps = float(vpc.get("fps") or g.video_fps)
+            g.video_min_frames = int(vpc.get("min_frames", g.video_min_frames))
+            g.video_max_frames = int(vpc.get("max_frames", g.video_max_frames))
         tok = None
         if load_tokenizer:
             try:
@@ -214,6 +323,31 @@ class MultimodalProcessorBundle:
     def process_images(self, images: Seq[Any]) -> List[ImageInputCPU]:
         return preprocess_images(images, self.geometry)
 
+    def process_video(self, frames: Seq[Any], source_fps: Optional[float] = None,
+                      frame_indices: Optional[Seq[int]] = None, sample: bool = True) -> ImageInputCPU:
+        """One clip -> :class:`ImageInputCPU` of kind ``"video"`` with its ``<T seconds>`` prefixes.
+
+        ``frames`` are the clip's frames in order (a ``(F, H, W, 3)`` / ``(F, 3, H, W)`` array or a list of images).
+        With ``source_fps`` and ``sample=True`` they are the whole recording and are thinned to the geometry's target
+        rate; otherwise they are taken as already sampled, ``frame_indices`` saying which frames of the recording
+        they were (default: consecutive, at 24 frames per second when ``source_fps`` is not given either)."""
+        n = len(frames)
+        g = self.geometry
+        if frame_indices is None:
+            if sample and source_fps is not None:
+                frame_indices = sample_frame_indices(n, source_fps, g.video_fps, g.video_min_frames, g.video_max_frames)
+                frames = [frames[i] for i in frame_indices]
+            else:
+                frame_indices = list(range(n))
+        elif len(frame_indices) != n:
+            raise ValueError(f"{len(frame_indices)} frame indices for {n} frames")
+        clip = preprocess_frames(frames, g, video=True)
+        if self.tokenizer is not None:
+            stamps = video_timestamps(frame_indices, source_fps or 24.0, g.temporal_patch)
+            clip.frame_prefix_ids = [self.tokenizer(f"<{t:.1f} seconds>", add_special_tokens=False)["input_ids"]
+                                     for t in stamps]
+        return clip
+
     def build(self, texts: Seq[str], images: Seq[Any], seq_id: int = 0, train_on: Optional[Seq[bool]] = None) -> Sequence:
         """``texts`` has one more entry than ``images``: text, image, text, image, ..., text.  ``train_on`` flags the
         text pieces (default: only the last one, the answer)."""
@@ -221,7 +355,8 @@ class MultimodalProcessorBundle:
             raise RuntimeError("this model directory has no tokenizer; use build_multimodal_sequence with token ids")
         if len(texts) != len(images) + 1:
             raise ValueError("need len(texts) == len(images) + 1")
-        ims = self.process_images(images)
+        # an entry that is already an ImageInputCPU (a clip from process_video, say) is used as it is
+        ims = [im if isinstance(im, ImageInputCPU) else preprocess_frames([im], self.geometry) for im in images]
         segs: List[Any] = []
         flags: List[bool] = []
         for i, t in enumerate(texts):
@@ -231,17 +366,21 @@ class MultimodalProcessorBundle:
                 segs.append(ims[i])
                 flags.append(False)
         return build_multimodal_sequence(segs, self.image_token_id, self.geometry.merge, seq_id,
-                                         self.vision_start_token_id, self.vision_end_token_id, flags)
+                                         self.vision_start_token_id, self.vision_end_token_id, flags,
+                                         video_token_id=self.video_token_id)
 
     def build_from_messages(self, messages: Seq[dict], images: Seq[Any], seq_id: int = 0,
-                            max_seq_len: Optional[int] = None) -> Optional[Sequence]:
+                            max_seq_len: Optional[int] = None, videos: Seq[Any] = ()) -> Optional[Sequence]:
         """Chat-style row -> multimodal sequence, through the tokenizer's own chat template.
 
         ``messages`` is the usual list of ``{"role", "content"}`` dicts whose ``content`` is a string or a list of
-        ``{"type": "text", "text": ...}`` / ``{"type": "image"}`` parts; the template must render every image part as
-        one image placeholder token, which is expanded here to the image's merged patch count.  Only the LAST
-        assistant message is trained on (everything the template renders before it is prompt).  Returns ``None`` when
-        ``max_seq_len`` is given and the result is longer."""
+        ``{"type": "text", "text": ...}`` / ``{"type": "image"}`` / ``{"type": "video"}`` parts; the template must
+        render every image part as one image placeholder token, which is expanded here to the image's merged patch
+        count, and every video part as one video placeholder token (between vision start / end tokens or bare), which
+        is replaced by the clip's per-temporal-patch blocks.  ``videos`` are clips from :meth:`process_video` or
+        frame lists (taken as already sampled).  Only the LAST assistant message is trained on (everything the
+        template renders before it is prompt).  Returns ``None`` when ``max_seq_len`` is given and the result is
+        longer."""
         if self.tokenizer is None or not hasattr(self.tokenizer, "apply_chat_template"):
             raise RuntimeError("this model directory has no tokenizer with a chat template")
         if not messages or messages[-1].get("role") != "assistant":
@@ -255,12 +394,32 @@ class MultimodalProcessorBundle:
         n_ph = sum(1 for t in full if t == self.image_token_id)
         if n_ph != len(ims):
             raise ValueError(f"the template rendered {n_ph} image placeholders for {len(ims)} images")
+        clips = [v if isinstance(v, ImageInputCPU) else self.process_video(v, sample=False) for v in videos]
+        n_vp = sum(1 for t in full if t == self.video_token_id) if self.video_token_id is not None else 0
+        if n_vp != len(clips):
+            raise ValueError(f"the template rendered {n_vp} video placeholders for {len(clips)} videos")
         segs: List[Any] = []
         flags: List[bool] = []
         cur: List[int] = []
-        cur_start, k = 0, 0
+        cur_start, k, kv, skip = 0, 0, 0, -1
         for pos, t in enumerate(full):
-            if t == self.image_token_id:
+            if pos == skip:                                    # the vision end token the template wrote after a video
+                cur_start = pos + 1
+                continue
+            if clips and t == self.video_token_id:
+                # every temporal patch gets its own start / end tokens: drop the pair the template wrote around
+                # the single placeholder
+                if cur and self.vision_start_token_id is not None and cur[-1] == self.vision_start_token_id:
+                    cur.pop()
+                if (self.vision_end_token_id is not None and pos + 1 < len(full)
+                        and full[pos + 1] == self.vision_end_token_id):
+                    skip = pos + 1
+                if cur:
+                    segs.append(cur); flags.append(cur_start >= len(prompt))
+                segs.append(clips[kv]); flags.append(False)
+                kv += 1
+                cur, cur_start = [], pos + 1
+            elif t == self.image_token_id:
                 if cur:
                     segs.append(cur); flags.append(cur_start >= len(prompt))
                 segs.append(ims[k]); flags.append(False)
@@ -276,7 +435,10 @@ class MultimodalProcessorBundle:
         if cur:
             segs.append(cur); flags.append(cur_start >= len(prompt))
         # the template already wrote the vision start / end tokens around each placeholder
-        seq = build_multimodal_sequence(segs, self.image_token_id, self.geometry.merge, seq_id, None, None, flags)
+        seq = build_multimodal_sequence(segs, self.image_token_id, self.geometry.merge, seq_id, None, None, flags,
+                                        video_token_id=self.video_token_id,
+                                        video_start_token_id=self.vision_start_token_id,
+                                        video_end_token_id=self.vision_end_token_id)
         if max_seq_len is not None and len(seq) > max_seq_len:
             return None
         return seq

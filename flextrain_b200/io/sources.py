@@ -86,9 +86,15 @@ class RankStridedSource(_QueueMixin):
 
 
 class MultimodalJsonSource(_QueueMixin):
-    """JSON / JSONL rows ``{"messages": [...], "images": [path, ...]}`` (chat parts of type ``image`` mark where each
-    image goes) -> multimodal sequences through a :class:`MultimodalProcessorBundle`; image paths are relative to the
-    file.  Rows that fail to load or exceed ``max_seq_len`` are skipped and counted in ``skipped``."""
+    """JSON / JSONL rows ``{"messages": [...], "images": [path, ...], "videos": [clip, ...]}`` (chat parts of type
+    ``image`` / ``video`` mark where each goes) -> multimodal sequences through a
+    :class:`MultimodalProcessorBundle`; paths are relative to the file.  A clip is a ``.npy`` file holding
+    ``(frames, H, W, 3)`` 8-bit pixels, a directory of frame images (read in name order), a list of frame image
+    paths, or ``{"path" | "frames": one of those, "fps": rate of the recording, "frame_indices": [...],
+    "sample": bool}``: with ``fps`` and no ``frame_indices`` the frames are the whole recording and are thinned to
+    the model's rate unless ``sample`` is false.  Rows that fail to load or exceed ``max_seq_len`` are skipped and
+    counted in ``skipped``."""
+    FRAME_SUFFIXES = (".png", ".jpg", ".jpeg", ".bmp", ".webp")
 
     def __init__(self, path: str, bundle, max_seq_len: int, loop: bool = True):
         self.path, self.bundle, self.max_seq_len, self.loop = path, bundle, max_seq_len, loop
@@ -99,6 +105,25 @@ class MultimodalJsonSource(_QueueMixin):
         self._init_queue()
         self._it = self._generate()
 
+    def _clip(self, spec, base: str):
+        from PIL import Image
+        opts = spec if isinstance(spec, dict) else {}
+        src = (opts.get("path") or opts.get("frames")) if isinstance(spec, dict) else spec
+        if src is None:
+            raise ValueError("a video entry needs 'path' or 'frames'")
+        full = lambda p: p if os.path.isabs(p) else os.path.join(base, p)
+        if isinstance(src, str) and src.endswith(".npy"):
+            frames = list(torch.from_numpy(np.load(full(src))))
+        else:
+            if isinstance(src, str):
+                d = full(src)
+                src = [os.path.join(d, n) for n in sorted(os.listdir(d)) if n.lower().endswith(self.FRAME_SUFFIXES)]
+            frames = [Image.open(full(p)).convert("RGB") for p in src]
+        if not frames:
+            raise ValueError("a video entry has no frames")
+        return self.bundle.process_video(frames, source_fps=opts.get("fps"), frame_indices=opts.get("frame_indices"),
+                                         sample=bool(opts.get("sample", True)))
+
     def _generate(self) -> Iterator[Sequence]:
         from PIL import Image
         base, sid = os.path.dirname(os.path.abspath(self.path)), 0
@@ -108,7 +133,9 @@ class MultimodalJsonSource(_QueueMixin):
                 try:
                     ims = [Image.open(p if os.path.isabs(p) else os.path.join(base, p)).convert("RGB")
                            for p in r.get("images", [])]
-                    seq = self.bundle.build_from_messages(r["messages"], ims, seq_id=sid, max_seq_len=self.max_seq_len)
+                    clips = [self._clip(v, base) for v in r.get("videos", [])]
+                    seq = self.bundle.build_from_messages(r["messages"], ims, seq_id=sid, max_seq_len=self.max_seq_len,
+                                                          videos=clips)
                 except (OSError, ValueError, KeyError):
                     seq = None
                 if seq is None:

@@ -257,10 +257,11 @@ def test_multimodal_training_follows_transformers_forward(tmp_path):
 
 
 def _chat_tokenizer(path):
-    """Character-level tokenizer with vision special tokens and a chat template that renders image parts as
-    ``<|vision_start|><|image_pad|><|vision_end|>`` (the shape of the Qwen-VL templates)."""
+    """Character-level tokenizer with vision special tokens and a chat template that renders image / video parts as
+    ``<|vision_start|><|image_pad|><|vision_end|>`` / ``...<|video_pad|>...`` (the shape of the Qwen-VL templates)."""
     from tokenizers import Tokenizer, models, pre_tokenizers
-    specials = ["<unk>", "</s>", "<|im_start|>", "<|im_end|>", "<|vision_start|>", "<|image_pad|>", "<|vision_end|>"]
+    specials = ["<unk>", "</s>", "<|im_start|>", "<|im_end|>", "<|vision_start|>", "<|image_pad|>", "<|vision_end|>",
+                "<|video_pad|>"]
     chars = specials + [chr(c) for c in range(32, 127)] + ["\n"]
     tok = Tokenizer(models.WordLevel({c: i for i, c in enumerate(chars)}, unk_token="<unk>"))
     tok.pre_tokenizer = pre_tokenizers.Split("", behavior="isolated")
@@ -269,7 +270,8 @@ def _chat_tokenizer(path):
     fast.chat_template = (
         "{% for m in messages %}<|im_start|>{{ m['role'] }}\n"
         "{% if m['content'] is string %}{{ m['content'] }}{% else %}{% for p in m['content'] %}"
-        "{% if p['type'] == 'image' %}<|vision_start|><|image_pad|><|vision_end|>{% else %}{{ p['text'] }}{% endif %}"
+        "{% if p['type'] == 'image' %}<|vision_start|><|image_pad|><|vision_end|>"
+        "{% elif p['type'] == 'video' %}<|vision_start|><|video_pad|><|vision_end|>{% else %}{{ p['text'] }}{% endif %}"
         "{% endfor %}{% endif %}<|im_end|>\n{% endfor %}"
         "{% if add_generation_prompt %}<|im_start|>assistant\n{% endif %}")
     fast.save_pretrained(path)
@@ -358,3 +360,189 @@ def test_train_py_on_image_chat_rows(tmp_path):
     assert r.returncode == 0, r.stderr[-3000:]
     losses = [float(m) for m in re.findall(r"\[step\s+\d+\].*? loss ([\d.]+)", r.stdout)]
     assert len(losses) == 8 and losses[-1] < losses[0] - 0.5, losses
+
+
+# ---------------------------------------------------------------------------------------------------------- video
+
+def test_video_preprocessing_matches_transformers():
+    """Frame sampling, the clip's resize rule, patch order and the per-patch time stamps against the Qwen3-VL video
+    processor / processor of ``transformers``."""
+    import numpy as np
+    from flextrain_b200.io.image_processing import sample_frame_indices, smart_resize_video, video_timestamps
+    vp_cls = getattr(transformers, "Qwen3VLVideoProcessor", None)
+    if vp_cls is None:
+        pytest.skip("this transformers has no Qwen3VLVideoProcessor")
+    from transformers.video_utils import VideoMetadata
+    size = {"shortest_edge": 4 * 64, "longest_edge": 6 * 1024}
+    proc = vp_cls(patch_size=4, temporal_patch_size=2, merge_size=2, image_mean=[0.5] * 3, image_std=[0.5] * 3,
+                  size=size, do_sample_frames=False)
+    g = ImageGeometry(patch=4, temporal_patch=2, merge=2, video_min_pixels=size["shortest_edge"],
+                      video_max_pixels=size["longest_edge"])
+    torch.manual_seed(0)
+    for F, H, W in [(4, 32, 48), (5, 24, 24), (3, 50, 37), (8, 90, 120), (2, 8, 8)]:
+        clip = torch.randint(0, 256, (F, 3, H, W), dtype=torch.uint8)
+        want = proc(videos=[clip], return_tensors="pt")
+        got = preprocess_frames(clip, g, video=True)
+        assert got.kind == "video" and list(got.grid_thw) == want["video_grid_thw"][0].tolist(), (F, H, W)
+        Hn, Wn = smart_resize_video(F, H, W, 2, 8, size["shortest_edge"], size["longest_edge"])
+        assert tuple(got.grid_thw) == (-(-F // 2), Hn // 4, Wn // 4)
+        tol = 1e-6 if (Hn, Wn) == (H, W) else 2.5 / 255 / 0.5
+        assert float((got.pixel_values - want["pixel_values_videos"]).abs().max()) <= tol, (F, H, W)
+    # which frames are kept
+    for total, src_fps, fps in [(240, 24.0, 2.0), (30, 30.0, 2.0), (1000, 25.0, 1.0), (7, 24.0, 2.0), (100000, 30.0, 2.0)]:
+        md = VideoMetadata(total_num_frames=total, fps=src_fps)
+        want = proc.sample_frames(md, fps=fps).tolist()
+        assert sample_frame_indices(total, src_fps, fps, proc.min_frames, proc.max_frames) == want, (total, src_fps)
+    # what time each temporal patch shows
+    from transformers.models.qwen3_vl.processing_qwen3_vl import Qwen3VLProcessor
+    for idx, fps in [([0, 12, 24, 36], 24.0), ([0, 10, 20, 30, 40], 30.0), ([3], 25.0)]:
+        want = Qwen3VLProcessor._calculate_timestamps(None, np.asarray(idx), fps, 2)
+        assert video_timestamps(idx, fps, 2) == pytest.approx(want)
+
+
+def _video_sequence(seq_id, seed):
+    """text, a three-patch clip with a two-token time stamp before each patch, text, an image, text."""
+    g = torch.Generator().manual_seed(seed)
+    clip = ImageInputCPU(torch.randn(3 * 4 * 6, 3 * 2 * 4 * 4, generator=g), (3, 4, 6), kind="video",
+                         frame_prefix_ids=[[200 + f, 210] for f in range(3)])
+    img = ImageInputCPU(torch.randn(1 * 4 * 4, 3 * 2 * 4 * 4, generator=g), (1, 4, 4))
+    text = lambda n: torch.randint(0, 200, (n,), generator=g).tolist()
+    segs = [text(6), clip, text(5), img, text(9)]
+    return build_multimodal_sequence(segs, IMG, merge=2, seq_id=seq_id, vision_start_token_id=VSTART,
+                                     vision_end_token_id=VEND, train_on=[True] * len(segs), video_token_id=VID)
+
+
+def test_video_sequence_layout_and_positions_match_transformers():
+    model = _hf_vl_model()
+    seq = _video_sequence(0, 11)
+    ids = seq.tokens
+    # three blocks of 2 x 3 merged patches, each after its two prefix tokens and between start / end tokens
+    first = [int(i) for i in (ids == VID).nonzero().flatten()[::6]]
+    assert int((ids == VID).sum()) == 18 and int((ids == IMG).sum()) == 4
+    for f, p in enumerate(first):
+        assert ids[p - 3:p].tolist() == [200 + f, 210, VSTART] and int(ids[p + 6]) == VEND
+    # placeholders, wrappers and time stamps are never predicted
+    assert not bool(torch.isin(seq.targets, torch.tensor([VID, IMG, VSTART, VEND, 200, 201, 202, 210])).any())
+    assert int((seq.targets != -100).sum()) == (6 - 1) + 5 + 9      # every text token but the very first
+    types = ((ids == IMG).to(torch.int32) + 2 * (ids == VID).to(torch.int32))[None]
+    want, _ = model.model.get_rope_index(ids[None], mm_token_type_ids=types, image_grid_thw=torch.tensor([[1, 4, 4]]),
+                                         video_grid_thw=torch.tensor([[3, 4, 6]]))
+    got = compute_mrope_position_ids(seq, 0, len(seq))
+    assert torch.equal(got.to(torch.int64).t(), want[:, 0])
+
+
+@pytest.mark.parametrize("chunk", [256, 16])
+def test_video_and_image_model_matches_transformers(tmp_path, chunk):
+    """Loss and gradients of a sequence with a clip and an image; ``chunk=16`` cuts inside the clip's blocks."""
+    model = _hf_vl_model()
+    _save_hub_layout(model, str(tmp_path))
+    seqs = [_video_sequence(0, 11), _mm_sequence(1, [(1, 4, 4)], 4, [11, 6])]
+    model.zero_grad()
+    total = 0.0
+    for s in seqs:
+        ids = s.tokens[None]
+        ims = s.modality_inputs["images"]
+        kw = dict(mm_token_type_ids=(ids == IMG).to(torch.int32) + 2 * (ids == VID).to(torch.int32))
+        stills = [im for im in ims if im.kind == "image"]
+        clips = [im for im in ims if im.kind == "video"]
+        if stills:
+            kw.update(pixel_values=torch.cat([im.pixel_values for im in stills]),
+                      image_grid_thw=torch.tensor([im.grid_thw for im in stills]))
+        if clips:
+            kw.update(pixel_values_videos=torch.cat([im.pixel_values for im in clips]),
+                      video_grid_thw=torch.tensor([im.grid_thw for im in clips]))
+        logits = model(input_ids=ids, **kw).logits[0].float()
+        total = total + torch.nn.functional.cross_entropy(logits, s.targets, ignore_index=-100, reduction="sum")
+    total.backward()
+    am = ft.from_pretrained(str(tmp_path), optimizer=ft.AdamW(lr=1e-3, state_dtype=torch.float32), max_seq_len=128,
+                            max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
+                            device="cpu", compute_dtype=torch.float32, master_dtype=torch.float32,
+                            grad_dtype=torch.float32, host_backend=UnpinnedHostBackend(), enable_multimodal=True,
+                            working_set=ft.WorkingSetConfig.simple(max_seq_len=128, max_global_batch_tokens=256,
+                                                                   chunk=chunk, round_tokens=256))
+    st = am.fwd_bwd(seqs, loss_scale_factor=1.0)
+    assert abs(st.loss_sum - float(total)) / float(total) < 2e-4, (st.loss_sum, float(total))
+    assert am.embed.last_summary.n_images == 3 and am.embed.last_summary.n_image_tokens == 18 + 4 + 4
+    sd = dict(model.named_parameters())
+    g_embed = am.buffers.embed_grads()["g_tok_embeddings"]
+    want = sd["model.language_model.embed_tokens.weight"].grad
+    assert float((g_embed - want).norm() / want.norm()) < 2e-3
+    assert float(g_embed[VID].abs().max()) == 0.0 and float(g_embed[IMG].abs().max()) == 0.0
+    g_o = am.buffers.grads(1)["g_o"]
+    want = sd["model.language_model.layers.1.self_attn.o_proj.weight"].grad
+    assert float((g_o - want).norm() / want.norm()) < 2e-3
+
+
+def test_chat_rows_with_videos_match_the_transformers_processor(tmp_path):
+    """A chat row with a clip and an image: the token ids are what ``transformers``' Qwen3-VL processor makes of the
+    same conversation (one ``<T seconds>`` + start + placeholders + end block per temporal patch); the JSON source
+    reads clips from a ``.npy`` file, a frame directory and a frame list."""
+    from PIL import Image
+    import numpy as np
+    vp_cls = getattr(transformers, "Qwen3VLVideoProcessor", None)
+    if vp_cls is None:
+        pytest.skip("this transformers has no Qwen3VLVideoProcessor")
+    from transformers.video_utils import VideoMetadata
+    d = str(tmp_path)
+    fast, ids = _chat_tokenizer(d)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump({"image_token_id": ids["<|image_pad|>"], "video_token_id": ids["<|video_pad|>"],
+                   "vision_start_token_id": ids["<|vision_start|>"], "vision_end_token_id": ids["<|vision_end|>"],
+                   "vision_config": {"patch_size": 4, "temporal_patch_size": 2, "spatial_merge_size": 2}}, f)
+    isize, vsize = {"shortest_edge": 64, "longest_edge": 4096}, {"shortest_edge": 256, "longest_edge": 8192}
+    with open(os.path.join(d, "preprocessor_config.json"), "w") as f:
+        json.dump({"patch_size": 4, "temporal_patch_size": 2, "merge_size": 2, "image_mean": [0.5] * 3,
+                   "image_std": [0.5] * 3, "size": isize}, f)
+    with open(os.path.join(d, "video_preprocessor_config.json"), "w") as f:
+        json.dump({"size": vsize, "fps": 2, "min_frames": 4, "max_frames": 16}, f)
+    b = MultimodalProcessorBundle.from_pretrained(d)
+    assert b.video_token_id == ids["<|video_pad|>"] and b.geometry.video_max_pixels == 8192
+    assert b.geometry.video_max_frames == 16
+    rng = np.random.default_rng(0)
+    recording = rng.integers(0, 255, (60, 24, 32, 3), dtype=np.uint8)            # 2.5 s at 24 frames per second
+    still = Image.fromarray(rng.integers(0, 255, (16, 16, 3), dtype=np.uint8))
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "what happens in "}, {"type": "video"},
+                                         {"type": "text", "text": " and in "}, {"type": "image"}]},
+            {"role": "assistant", "content": "it moves"}]
+    clip = b.process_video(torch.from_numpy(recording), source_fps=24.0)
+    assert clip.grid_thw == (3, 6, 8) and len(clip.frame_prefix_ids) == 3       # 5 of 60 frames -> 3 temporal patches
+    seq = b.build_from_messages(msgs, [still], videos=[clip])
+    # ---- the same conversation through transformers
+    ip = transformers.Qwen2VLImageProcessor(patch_size=4, temporal_patch_size=2, merge_size=2, image_mean=[0.5] * 3,
+                                            image_std=[0.5] * 3, size=isize)
+    vp = vp_cls(patch_size=4, temporal_patch_size=2, merge_size=2, image_mean=[0.5] * 3, image_std=[0.5] * 3,
+                size=vsize, fps=2, min_frames=4, max_frames=16)
+    proc = transformers.Qwen3VLProcessor(image_processor=ip, tokenizer=fast, video_processor=vp,
+                                         chat_template=fast.chat_template)
+    text = fast.apply_chat_template(msgs, tokenize=False, add_generation_prompt=False)
+    want = proc(text=[text], images=[still], videos=[torch.from_numpy(recording).permute(0, 3, 1, 2)],
+                video_metadata=[VideoMetadata(total_num_frames=60, fps=24.0)], return_tensors="pt")
+    assert seq.tokens.tolist() == want["input_ids"][0].tolist()
+    assert want["video_grid_thw"][0].tolist() == list(clip.grid_thw)
+    assert float((clip.pixel_values - want["pixel_values_videos"]).abs().max()) <= 2.5 / 255 / 0.5
+    rendered = fast.decode(seq.tokens.tolist()).replace(" ", "")               # the toy tokenizer spaces characters out
+    assert "<0.3seconds>" in rendered and "<1.5seconds>" in rendered and rendered.count("seconds>") == 3
+    scored = [int(t) for t in seq.targets.tolist() if t != -100]
+    answer = fast("it moves", add_special_tokens=False)["input_ids"]
+    assert scored[: len(answer)] == answer and len(scored) <= len(answer) + 2
+    # ---- the JSON source: three ways to name a clip
+    np.save(os.path.join(d, "rec.npy"), recording)
+    still.save(os.path.join(d, "still.png"))
+    os.makedirs(os.path.join(d, "frames"))
+    kept = [0, 15, 30, 44, 59]
+    for n, i in enumerate(kept):
+        Image.fromarray(recording[i]).save(os.path.join(d, "frames", f"f{n:03d}.png"))
+    rows = [{"messages": msgs, "images": ["still.png"], "videos": [{"path": "rec.npy", "fps": 24.0}]},
+            {"messages": msgs, "images": ["still.png"],
+             "videos": [{"path": "frames", "fps": 24.0, "frame_indices": kept}]},
+            {"messages": msgs, "images": ["still.png"],
+             "videos": [{"frames": [f"frames/f{n:03d}.png" for n in range(5)], "fps": 24.0, "frame_indices": kept}]},
+            {"messages": msgs, "images": ["still.png"], "videos": []}]            # skipped: a video part without a clip
+    with open(os.path.join(d, "mm.jsonl"), "w") as f:
+        f.write("\n".join(json.dumps(r) for r in rows))
+    src = ft.MultimodalJsonSource(os.path.join(d, "mm.jsonl"), b, max_seq_len=512, loop=False)
+    got = list(src.iter_sequences())
+    assert len(got) == 3 and src.skipped == 1
+    for s in got:
+        assert torch.equal(s.tokens, seq.tokens)
+        assert torch.equal(s.modality_inputs["pixel_values"], seq.modality_inputs["pixel_values"])
