@@ -1,4 +1,4 @@
-"""``python -m flextrain_b200 {info,train <yaml>,pretrain,init}`` (flextrain/cli.py:669-697)."""
+"""``python -m flextrain_b200 {info,check,train <yaml>,pretrain,init}`` (flextrain/cli.py:669-697)."""
 from __future__ import annotations
 
 import argparse
@@ -80,12 +80,18 @@ def main(argv=None) -> int:
     sub.add_parser("info", help="versions, devices, memory, architectures, native libraries")
     t = sub.add_parser("train", help="train from a YAML run config")
     t.add_argument("config")
+    c = sub.add_parser("check", help="build the native libraries and check tool chain, libraries, GPUs, peer access")
+    c.add_argument("--no-build", action="store_true")
+    c.add_argument("--json", action="store_true")
     from .scripts import init_hf, pretrain
     pretrain.add_subparser(sub)
     init_hf.add_subparser(sub)
     args = p.parse_args(argv)
     if args.cmd == "info":
         return _info(args)
+    if args.cmd == "check":
+        from .scripts import post_install
+        return post_install.main((["--no-build"] if args.no_build else []) + (["--json"] if args.json else []))
     if args.cmd == "train":
         return _train(args)
     return args.func(args)

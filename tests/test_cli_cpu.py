@@ -63,6 +63,25 @@ def test_info_lists_architectures():
     assert "architectures:" in out and "gemma4" in out and "qwen3_5_moe" in out
 
 
+def test_check_reports_tool_chain_libraries_and_no_gpu():
+    """``python -m flextrain_b200 check --json``: every native library is built, loads and exports its entry point;
+    without a GPU nothing is a problem (the report says so instead)."""
+    rep = json.loads(_run("check", "--json").strip().splitlines()[-1])
+    assert rep["problems"] == [] and rep["toolchain"]["sm_100a"] and rep["toolchain"]["nvcc"]
+    libs = rep["libraries"]
+    assert set(libs) >= {"gemm_tcgen05", "attention", "comm", "moe", "elementwise", "gdn", "seqmix", "noalloc",
+                         "dp_solver", "copy_engine", "fastcall"}
+    assert all(r["ok"] for r in libs.values())
+    assert rep["gpus"]["available"] is False and rep["gpus"]["devices"] == [] and rep["gpus"]["host_memory_gib"] > 0
+    # a missing entry point or a GPU of another generation is named
+    from flextrain_b200.scripts.post_install import problems
+    rep["libraries"]["attention"] = {"ok": False, "error": "entry point ftb_attn_fwd is missing"}
+    rep["gpus"]["devices"] = [{"index": 0, "cc": "9.0", "supported": False}]
+    rep["gpus"]["peer_access"] = False
+    bad = problems(rep)
+    assert len(bad) == 3 and "attention" in bad[0] and "9.0" in bad[1] and "peer access" in bad[2]
+
+
 def test_pretrain_with_reference_flags_then_skip(tmp_path):
     d, out = str(tmp_path / "data"), str(tmp_path / "run")
     _write_shards(d)
