@@ -9,7 +9,7 @@ import os
 from typing import Optional
 
 from ..io.arch import select_arch_module
-from ..io.hf_weights import collect_hf_state, is_export_writer
+from ..io.hf_weights import checkpoint_names, collect_hf_state, is_export_writer, passthrough_tensors
 from ._common import copy_aux_files, write_sharded_safetensors
 
 
@@ -18,8 +18,15 @@ def save_hf_full(am, out_dir: str, *, max_shard_bytes: int = 5 << 30, source_dir
     state = collect_hf_state(am, lora_merge=_merge_lora)          # collective under tensor / expert parallelism
     if not is_export_writer(am):
         return out_dir
-    write_sharded_safetensors(state, out_dir, max_shard_bytes)
     src = source_dir or am.model_dir
+    # a checkpoint that nests its decoder (vision-language wrappers) gets its own names back, and what the engine does
+    # not hold (vision tower, extra heads) is copied over from the source, so the directory loads where the source did
+    state = checkpoint_names(state, getattr(am, "hf_nested_prefix", None))
+    encoders = getattr(am.embed, "encoder_export_state", None)
+    if encoders is not None:
+        state.update(encoders())
+    passthrough_tensors(src, state)
+    write_sharded_safetensors(state, out_dir, max_shard_bytes)
     cfg = None
     if src and os.path.exists(os.path.join(src, "config.json")):
         with open(os.path.join(src, "config.json")) as f:

@@ -18,6 +18,22 @@ _MODULE = {"w_q": "self_attn.q_proj", "w_k": "self_attn.k_proj", "w_v": "self_at
            "w_1": "mlp.gate_proj", "w_3": "mlp.up_proj", "w_2": "mlp.down_proj"}
 
 
+def _wrapper_module_prefix(am):
+    """Adapter keys follow the MODULE tree of the class the base checkpoint loads as, not the tensor names in its
+    files: a vision-language wrapper (``...ForConditionalGeneration``) holds the decoder under the nested prefix the
+    checkpoint uses, while the family's causal-LM class has ``model.layers`` even when its files spell the nested
+    names.  Returns the nested prefix for the former, ``None`` otherwise."""
+    nested = getattr(am, "hf_nested_prefix", None)
+    if not nested or not getattr(am, "model_dir", None):
+        return None
+    try:
+        with open(os.path.join(am.model_dir, "config.json")) as f:
+            archs = json.load(f).get("architectures") or []
+    except OSError:
+        return None
+    return nested if any(a.endswith("ForConditionalGeneration") for a in archs) else None
+
+
 def save_lora_adapter(am, out_dir: str, base_model_name_or_path: str = "") -> str:
     from safetensors.torch import save_file
     from ..io.hf_weights import gather_local_parts, is_export_writer
@@ -70,6 +86,11 @@ def save_lora_adapter(am, out_dir: str, base_model_name_or_path: str = "") -> st
                 expert_targets.add("down_proj")
     if not is_export_writer(am):
         return out_dir
+    nested = _wrapper_module_prefix(am)
+    if nested:                      # vision-language wrappers: the decoder's modules live under the wrapper's prefix
+        head = "base_model.model.model."
+        state = {("base_model.model." + nested + k[len(head):] if k.startswith(head) else k): v
+                 for k, v in state.items()}
     os.makedirs(out_dir, exist_ok=True)
     save_file(state, os.path.join(out_dir, "adapter_model.safetensors"), metadata={"format": "pt"})
     cfg = {"peft_type": "LORA", "task_type": "CAUSAL_LM", "r": lora.rank, "lora_alpha": lora.alpha,

@@ -133,6 +133,13 @@ def load_hf_into_model(am, model_dir: str, strict: bool = False) -> None:
     bm = am.buffers
     by_name = lambda ps: {t.name: t for t in ps.tensors}
     _load_entries(spec.embed(mc), bm.embed_params(), src, "embed", strict, by_name(am.embed.param_spec))
+    # which prefix the checkpoint nests its decoder under (multimodal wrappers): the export writes the same names
+    am.hf_nested_prefix = None
+    for e in spec.embed(mc):
+        names = _peek(e, src)
+        if names:
+            am.hf_nested_prefix = next((pre for pre in _NESTED_PREFIXES if names[0].startswith(pre)), None)
+            break
     for i in range(len(am.layers)):
         _load_entries(spec.layer(i, mc), bm.host_params(i), src, f"layer {i}", strict,
                       by_name(am.layers[i].param_spec))
@@ -159,6 +166,34 @@ def _peek(entry: WeightMapEntry, src: SafetensorsDir):
         if all(src.has(n) for n in names):
             return names
     return None
+
+
+def checkpoint_names(state: Dict[str, torch.Tensor], nested_prefix: Optional[str]) -> Dict[str, torch.Tensor]:
+    """Tensor names as the source checkpoint spells them: ``model.X`` becomes ``<nested_prefix>X`` for a checkpoint
+    that nests its decoder (``model.language_model.`` in the vision-language wrappers)."""
+    if not nested_prefix:
+        return state
+    return {(nested_prefix + k[len("model."):] if k.startswith("model.") else k): v for k, v in state.items()}
+
+
+def passthrough_tensors(source_dir: Optional[str], state: Dict[str, torch.Tensor]) -> int:
+    """Add to ``state`` every tensor of the source checkpoint that the engine does not hold (vision tower,
+    multi-token-prediction heads, ...), unchanged, so that the exported directory is a complete checkpoint again
+    (flextrain/export/_hf_full.py:388-425).  ``lm_head.weight`` is left out when the export did not write one (tied
+    embeddings).  Returns how many tensors were added."""
+    if not source_dir or not os.path.isdir(source_dir):
+        return 0
+    try:
+        src = SafetensorsDir(source_dir)
+    except Exception:
+        return 0
+    n = 0
+    for k in sorted(src.where):
+        if k in state or k == "lm_head.weight" or "rotary_emb.inv_freq" in k:
+            continue
+        state[k] = src.get(k)
+        n += 1
+    return n
 
 
 def is_export_writer(am) -> bool:
@@ -229,13 +264,14 @@ def gather_local_parts(t: torch.Tensor, spec, am) -> torch.Tensor:
 
 
 def export_model_safetensors(am, out_dir: str, filename: str = "final.safetensors") -> str:
-    """Single-shard export in HF names (flextrain/io/hf_weights.py:491-530)."""
+    """Single-shard export of the tensors the engine holds, in the source checkpoint's names
+    (flextrain/io/hf_weights.py:491-530); :func:`flextrain_b200.export.save_hf_full` writes a complete directory."""
     from safetensors.torch import save_file
     os.makedirs(out_dir, exist_ok=True)
     if torch.device(am.device).type == "cuda":
         torch.cuda.synchronize()
     path = os.path.join(out_dir, filename)
-    state = collect_hf_state(am)
+    state = checkpoint_names(collect_hf_state(am), getattr(am, "hf_nested_prefix", None))
     if is_export_writer(am):
         save_file(state, path, metadata={"format": "pt"})
     return path

@@ -546,3 +546,94 @@ def test_chat_rows_with_videos_match_the_transformers_processor(tmp_path):
     for s in got:
         assert torch.equal(s.tokens, seq.tokens)
         assert torch.equal(s.modality_inputs["pixel_values"], seq.modality_inputs["pixel_values"])
+
+
+def test_vision_language_export_reloads_in_transformers(tmp_path):
+    """Fine-tune the text side of a vision-language checkpoint, export it, load the directory with ``transformers``
+    as a vision-language model: the decoder comes back under the wrapper's own names with the trained values, the
+    vision tower is passed through from the source, and the reloaded model's loss on image + text equals the
+    engine's."""
+    src_dir, out = str(tmp_path / "src"), str(tmp_path / "out")
+    model = _hf_vl_model()
+    _save_hub_layout(model, src_dir)
+    am = ft.from_pretrained(src_dir, optimizer=ft.AdamW(lr=1e-2, state_dtype=torch.float32), max_seq_len=128,
+                            max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
+                            device="cpu", compute_dtype=torch.float32, master_dtype=torch.float32,
+                            grad_dtype=torch.float32, host_backend=UnpinnedHostBackend(), enable_multimodal=True)
+    assert am.hf_nested_prefix == "model.language_model."
+    seqs = [_mm_sequence(0, [(1, 4, 6)], 3, [5, 9]), _video_sequence(1, 11)]
+    am.fwd_bwd(seqs, loss_scale_factor=1.0 / 64)
+    am.step()
+    ft.export.save_hf_full(am, out)
+    re = transformers.AutoModelForImageTextToText.from_pretrained(out, dtype=torch.float32)
+    re.config._attn_implementation = "eager"
+    sd0, sd1 = model.state_dict(), re.state_dict()
+    assert set(sd0) == set(sd1)
+    for k in sd0:
+        if ".visual." in k:
+            assert torch.equal(sd0[k], sd1[k]), k                      # passed through unchanged
+    moved = sd1["model.language_model.layers.1.self_attn.o_proj.weight"] - sd0["model.language_model.layers.1.self_attn.o_proj.weight"]
+    assert float(moved.abs().max()) > 1e-3                             # the step is in the exported weights
+    assert torch.allclose(sd1["model.language_model.layers.1.self_attn.o_proj.weight"], am.buffers.host_params(1)["w_o"])
+    want = 0.0
+    with torch.no_grad():
+        for s in seqs:
+            ids = s.tokens[None]
+            ims = s.modality_inputs["images"]
+            kw = dict(mm_token_type_ids=(ids == IMG).to(torch.int32) + 2 * (ids == VID).to(torch.int32))
+            stills = [im for im in ims if im.kind == "image"]
+            clips = [im for im in ims if im.kind == "video"]
+            if stills:
+                kw.update(pixel_values=torch.cat([im.pixel_values for im in stills]),
+                          image_grid_thw=torch.tensor([im.grid_thw for im in stills]))
+            if clips:
+                kw.update(pixel_values_videos=torch.cat([im.pixel_values for im in clips]),
+                          video_grid_thw=torch.tensor([im.grid_thw for im in clips]))
+            logits = re(input_ids=ids, **kw).logits[0].float()
+            want += float(torch.nn.functional.cross_entropy(logits, s.targets, ignore_index=-100, reduction="sum"))
+    got = am.evaluate(seqs)
+    assert abs(got.loss_sum - want) / want < 2e-4, (got.loss_sum, want)
+
+
+def test_vision_language_lora_adapter_names_the_wrapper_modules(tmp_path):
+    """The adapter of a vision-language checkpoint addresses the decoder where the wrapper class holds it
+    (``model.language_model.layers``); applied to the ``transformers`` model by the PEFT rule it gives the engine's
+    loss on image + text."""
+    from safetensors import safe_open
+    src_dir, ad = str(tmp_path / "src"), str(tmp_path / "adapter")
+    model = _hf_vl_model()
+    _save_hub_layout(model, src_dir)
+    f32 = torch.float32
+    am = ft.from_pretrained(src_dir, optimizer=ft.AdamW(lr=1e-2, state_dtype=f32), max_seq_len=128,
+                            max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
+                            device="cpu", compute_dtype=f32, master_dtype=f32, grad_dtype=f32,
+                            host_backend=UnpinnedHostBackend(), enable_multimodal=True, lora_targets="all",
+                            lora_rank=4, lora_alpha=8.0, lora_adapter_compute_dtype=f32,
+                            lora_adapter_master_dtype=f32, lora_adapter_grad_dtype=f32,
+                            lora_adapter_opt_state_dtype=f32)
+    torch.manual_seed(3)
+    for _, _, n, t in am.named_master_params():
+        if n.endswith("_lora_b"):
+            t.copy_(torch.randn_like(t) * 0.3)
+    seqs = [_mm_sequence(0, [(1, 4, 6)], 3, [5, 9])]
+    want = am.evaluate(seqs).loss_sum
+    ft.export.save_lora_adapter(am, ad)
+    scale = 8.0 / 4
+    sd = dict(model.named_parameters())
+    applied = 0
+    with safe_open(os.path.join(ad, "adapter_model.safetensors"), framework="pt") as f, torch.no_grad():
+        for k in f.keys():
+            assert k.startswith("base_model.model.model.language_model.layers."), k
+            if k.endswith("lora_A.weight"):
+                mod = k[len("base_model.model."): -len(".lora_A.weight")]
+                sd[mod + ".weight"].add_(scale * (f.get_tensor(k.replace("lora_A", "lora_B")) @ f.get_tensor(k)))
+                applied += 1
+    assert applied >= 7
+    s = seqs[0]
+    ids = s.tokens[None]
+    with torch.no_grad():
+        logits = model(input_ids=ids, pixel_values=s.modality_inputs["pixel_values"],
+                       image_grid_thw=torch.tensor(s.modality_inputs["grid_thw"]),
+                       mm_token_type_ids=(ids == IMG).to(torch.int32)).logits[0].float()
+    got = float(torch.nn.functional.cross_entropy(logits, s.targets, ignore_index=-100, reduction="sum"))
+    assert abs(got - want) / want < 2e-4, (got, want)
