@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import argparse
+import json
 import os
 import sys
 from typing import List
@@ -31,7 +32,15 @@ def _info(args) -> int:
 def _train_argv(cfg) -> List[str]:
     """Translate a RunConfig into train.py flags: both front ends drive the same loop."""
     m, o, t, h, d, io = cfg.model, cfg.optimizer, cfg.train, cfg.hardware, cfg.data, cfg.io
-    argv = ["--model", m.path or f"dims:{m.dims}", "--mode", m.mode, "--max-seq-len", str(t.max_seq_len),
+    model = m.path or f"dims:{m.dims}"
+    if not m.path and m.inline_dims:
+        # dimensions written out in the run file: handed to train.py as a dims file next to the run's outputs
+        os.makedirs(io.output_dir, exist_ok=True)
+        dims_file = os.path.join(io.output_dir, "model_dims.json")
+        with open(dims_file, "w") as f:
+            json.dump(dict(m.inline_dims, arch=m.arch, **({"hyperparams": m.hyperparams} if m.hyperparams else {})), f)
+        model = f"dims:{dims_file}"
+    argv = ["--model", model, "--mode", m.mode, "--max-seq-len", str(t.max_seq_len),
             "--max-global-batch-tokens", str(t.max_global_batch_tokens), "--steps", str(t.steps),
             "--data-source", d.source, "--lr", str(o.lr), "--lr-warmup-pct", str(o.warmup_pct),
             "--lr-cooldown-start-pct", str(o.cooldown_start_pct), "--lr-final-pct", str(o.final_pct),
@@ -50,11 +59,17 @@ def _train_argv(cfg) -> List[str]:
                       ("--max-chunk-size", t.max_chunk_size), ("--dp-shard", h.dp_shard),
                       ("--save-state-every", io.save_state_every or None), ("--resume-state", io.resume_state),
                       ("--eval-every", io.eval_every or None), ("--eval-tokens", io.eval_tokens if io.eval_every else None),
-                      ("--eval-dataset", d.eval_path), ("--max-grad-norm", o.max_grad_norm)):
+                      ("--eval-dataset", d.eval_path), ("--max-grad-norm", o.max_grad_norm),
+                      ("--device-id", h.device_id), ("--tokenizer", d.tokenizer), ("--min-seq-len", d.min_seq_len or None),
+                      ("--hf-subset", d.hf_subset), ("--shard-num-shards", d.shard_num_shards),
+                      ("--custom-factory", d.custom_factory)):
         if val is not None:
             argv += [flag, str(val)]
+    argv += ["--hf-split", d.hf_split, "--hf-text-field", d.hf_text_field, "--sft-prompt-field", d.prompt_field,
+             "--sft-response-field", d.response_field, "--sft-input-field", d.input_field or ""]
     for flag, on in (("--save", io.save), ("--apply-chat-template", d.apply_chat_template),
-                     ("--truncate-long", d.truncate_long)):
+                     ("--truncate-long", d.truncate_long), ("--no-hf-streaming", not d.hf_streaming),
+                     ("--shard-documents", d.shard_documents)):
         if on:
             argv.append(flag)
     return argv

@@ -43,15 +43,31 @@ def lr_schedule(step: int, *, max_lr: float, final_lr: float, warmup_steps: int,
 
 def build_arg_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="train.py")
-    p.add_argument("--model", required=True, help="HF model directory, or dims:<name> for a random-init catalogue model")
+    p.add_argument("--model", required=True, help="HF model directory, or dims:<name> (a random-init catalogue model) / dims:<file.json> (a dims dict)")
     p.add_argument("--mode", choices=("full", "lora"), required=True)
     p.add_argument("--max-seq-len", type=int, required=True)
     p.add_argument("--max-global-batch-tokens", type=int, required=True)
     p.add_argument("--truncate-long", action="store_true")
     p.add_argument("--apply-chat-template", action="store_true")
     p.add_argument("--steps", type=int, default=20)
-    p.add_argument("--data-source", choices=("json_sft", "synthetic", "shards", "mm_json"), default="json_sft",
-                   help="mm_json: chat rows with image files for a vision-language checkpoint (MultimodalJsonSource)")
+    p.add_argument("--data-source", choices=("json_sft", "synthetic", "shards", "mm_json", "hf", "raw", "custom"),
+                   default="json_sft",
+                   help="mm_json: chat rows with image / video files for a vision-language checkpoint; hf: a HuggingFace "
+                        "`datasets` id or directory in --dataset; raw: a .pt file of pre-tokenised sequences; custom: "
+                        "--custom-factory module:callable returning (records, extract)")
+    p.add_argument("--tokenizer", default=None, help="tokenizer directory / hub id (default: the model directory)")
+    p.add_argument("--min-seq-len", type=int, default=0, help="skip documents / records shorter than this")
+    p.add_argument("--hf-subset", default=None)
+    p.add_argument("--hf-split", default="train")
+    p.add_argument("--hf-text-field", default="text")
+    p.add_argument("--no-hf-streaming", action="store_true")
+    p.add_argument("--shard-documents", action="store_true",
+                   help="shards: one sequence per document (split at the end-of-text id) instead of fixed windows")
+    p.add_argument("--shard-num-shards", type=int, default=None)
+    p.add_argument("--sft-prompt-field", default="instruction")
+    p.add_argument("--sft-response-field", default="output")
+    p.add_argument("--sft-input-field", default="input")
+    p.add_argument("--custom-factory", default=None, metavar="MODULE:CALLABLE")
     p.add_argument("--dataset", default=os.path.join(ROOT, "flextrain_b200/configs/examples/data/tiny_math_sft.json"))
     p.add_argument("--synthetic-seq-len", type=int, default=None)
     p.add_argument("--output-dir", default=None)
@@ -122,6 +138,9 @@ def _resolve_model(args):
         with open(os.path.join(ROOT, "flextrain_b200/configs/model_dims.json")) as f:
             cat = json.load(f)
         name = args.model[5:]
+        if name.endswith(".json") and os.path.exists(name):        # {"arch": ..., "hyperparams": {...}, <dims keys>}
+            with open(name) as f:
+                return "dims", json.load(f)
         if name not in cat:
             raise SystemExit(f"unknown dims model {name!r}; known: {sorted(cat)}")
         return "dims", cat[name]
@@ -204,18 +223,39 @@ def main(argv=None) -> int:
         if args.data_source == "synthetic":
             return ft.SyntheticTokenSource(vocab, args.synthetic_seq_len or args.max_seq_len, seed=seed + data_rank,
                                            pin=use_cuda)
+        def tokenizer():
+            from transformers import AutoTokenizer
+            return AutoTokenizer.from_pretrained(args.tokenizer or (model if kind == "hf" else args.model))
+
         if args.data_source == "shards":
-            s = ft.ShardTokenSource(path, args.max_seq_len, loop=loop)
+            if args.shard_documents:
+                s = ft.ShardTokenSource(path, loop=loop, vocab_size=vocab, num_shards=args.shard_num_shards,
+                                        min_seq_len=args.min_seq_len, max_seq_len=args.max_seq_len)
+            else:
+                s = ft.ShardTokenSource(path, args.max_seq_len, loop=loop, num_shards=args.shard_num_shards)
+        elif args.data_source == "hf":
+            s = ft.HFTokenSource(path, tokenizer(), subset=args.hf_subset, split=args.hf_split,
+                                 text_field=args.hf_text_field, min_seq_len=args.min_seq_len,
+                                 max_seq_len=args.max_seq_len, streaming=not args.no_hf_streaming)
+        elif args.data_source == "raw":
+            s = ft.RawTokenSource(torch.load(path, map_location="cpu"), loop=loop)
+        elif args.data_source == "custom":
+            import importlib
+            mod_name, _, attr = (args.custom_factory or "").partition(":")
+            if not attr:
+                raise SystemExit("--data-source custom needs --custom-factory module:callable")
+            records, extract = getattr(importlib.import_module(mod_name), attr)()
+            s = ft.CustomSchemaTokenSource(records, extract, loop=loop)
         elif args.data_source == "mm_json":
             if kind != "hf":
                 raise SystemExit("--data-source mm_json needs an HF vision-language model directory (tokenizer, geometry)")
             from flextrain_b200.io.image_processing import MultimodalProcessorBundle
             s = ft.MultimodalJsonSource(path, MultimodalProcessorBundle.from_pretrained(model), args.max_seq_len, loop=loop)
         else:
-            from transformers import AutoTokenizer
-            tok = AutoTokenizer.from_pretrained(model if kind == "hf" else args.model)
-            s = ft.JsonSFTTokenSource(path, tok, args.max_seq_len, apply_chat_template=args.apply_chat_template,
-                                      truncate_long=args.truncate_long, loop=loop)
+            s = ft.JsonSFTTokenSource(path, tokenizer(), args.max_seq_len, apply_chat_template=args.apply_chat_template,
+                                      truncate_long=args.truncate_long, loop=loop, prompt_field=args.sft_prompt_field,
+                                      response_field=args.sft_response_field, input_field=args.sft_input_field,
+                                      min_seq_len=args.min_seq_len)
         # every rank opened the same files: data-parallel ranks each take every data_ranks-th sequence
         return ft.RankStridedSource(s, data_rank, data_ranks) if data_ranks > 1 else s
 
