@@ -39,9 +39,16 @@ class BuildContext:
     extra: dict = field(default_factory=dict)
 
 
-def register_block_builder(architecture: str, builder: Callable) -> None:
-    """Register ``builder(layer_id, decoder_config, model_config) -> Layer`` for an HF ``architectures`` name."""
-    _BLOCK_BUILDERS[architecture] = builder
+def register_block_builder(hf_arch_ids, builder: Callable) -> None:
+    """Register ``builder(layer_id, decoder_config, model_config) -> Layer`` for one HF ``architectures`` name or
+    several (a string or an iterable of strings).  Registering the same builder again is a no-op; a different builder
+    for a name that is taken raises (flextrain/api.py:123-137)."""
+    names = [hf_arch_ids] if isinstance(hf_arch_ids, str) else list(hf_arch_ids)
+    for name in names:
+        have = _BLOCK_BUILDERS.get(name)
+        if have is not None and have is not builder:
+            raise ValueError(f"a block builder for {name!r} is already registered ({have!r})")
+        _BLOCK_BUILDERS[name] = builder
 
 
 def _hw_cost(hw_cost, device) -> HardwareCost:

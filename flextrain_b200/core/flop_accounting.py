@@ -10,7 +10,18 @@ from __future__ import annotations
 from typing import Tuple
 
 
+def _sequence_fwd_flops(am, seq_len: int) -> float:
+    """Forward FLOPs of ONE sequence of ``seq_len`` tokens through every layer and the head: each layer's own
+    ``compute_cost`` at the causal mean context ``seq_len / 2`` (flextrain/core/flop_accounting.py:111-137)."""
+    n = int(seq_len)
+    return float(sum(layer.compute_cost(n, n / 2).total_fwd_flops for layer in am.layers)) + head_flops(am, n)
+
+
 def fwd_flops(am, stats) -> float:
+    """Forward FLOPs of what ``stats`` (a :class:`StepStats`) recorded, or, given a sequence length instead (the
+    reference's form), of one sequence of that length including the head."""
+    if isinstance(stats, (int, float)):
+        return _sequence_fwd_flops(am, int(stats))
     return float(stats.fwd_flops)
 
 
@@ -19,7 +30,16 @@ def head_flops(am, tokens: int) -> float:
 
 
 def bwd_flops(am, stats, mode: str = "full") -> float:
-    return (2.0 if mode == "full" else 1.0) * float(stats.fwd_flops)
+    if mode not in ("full", "lora"):
+        raise ValueError(f"mode must be 'full' or 'lora', got {mode!r}")
+    return (2.0 if mode == "full" else 1.0) * fwd_flops(am, stats)
+
+
+def step_flops(am, seq_lens, *, mode: str = "full") -> float:
+    """FLOPs of one optimizer step over sequences of the given lengths: forward + backward per sequence (the
+    attention term is not linear in length, so they are summed one by one) + the optimizer
+    (flextrain/core/flop_accounting.py:303-320)."""
+    return float(sum(fwd_flops(am, int(n)) + bwd_flops(am, int(n), mode) for n in seq_lens)) + opt_flops_per_step(am)
 
 
 def opt_flops_per_step(am) -> float:

@@ -12,7 +12,27 @@ import time
 
 import torch
 
+from dataclasses import dataclass
+
 from .save_level import HardwareCost
+
+
+@dataclass(frozen=True)
+class HardwareProbeResult(HardwareCost):
+    """What :func:`probe_hardware` measured.  It IS a :class:`HardwareCost` (pass it wherever one is wanted) and also
+    answers to the reference's record: ``.hw_cost``, ``.mem_bw_gbps``, the two halves of the GEMM run and the run
+    times (flextrain/core/hw_probe.py:40-66)."""
+    matmul_n: int = 0
+    matmul_total_seconds: float = 0.0
+    achieved_tflops_first_half: float = 0.0
+    achieved_tflops_second_half: float = 0.0
+    transfer_bytes: int = 0
+    mem_bw_total_seconds: float = 0.0
+
+    @property
+    def hw_cost(self) -> HardwareCost:
+        return HardwareCost(self.peak_tflops, self.pcie_bw_gbps, self.nvlink_bw_gbps, self.mem_bw_gbps,
+                            self.practical_efficiency_factor)
 
 
 def _timed(fn, seconds: float):
@@ -28,15 +48,21 @@ def _timed(fn, seconds: float):
             return n, dt
 
 
-def probe_matmul(device, seconds: float = 4.0, n: int = 8192) -> float:
+def probe_matmul_halves(device, seconds: float = 4.0, n: int = 8192):
+    """``(first-half TFLOP/s, second-half TFLOP/s)`` of an ``n``-cubed bf16 GEMM run for ``seconds``."""
     from .. import ops
     a = torch.randn(n, n, device=device, dtype=torch.bfloat16)
     b = torch.randn(n, n, device=device, dtype=torch.bfloat16)
     out = torch.empty(n, n, device=device, dtype=torch.bfloat16)
     fn = lambda: ops.gemm(a, b, trans_b=True, out=out)
-    _timed(fn, seconds / 2)
-    cnt, dt = _timed(fn, seconds / 2)
-    return 2.0 * n ** 3 * cnt / dt / 1e12
+    c0, t0 = _timed(fn, seconds / 2)
+    c1, t1 = _timed(fn, seconds / 2)
+    rate = lambda c, t: 2.0 * n ** 3 * c / t / 1e12
+    return rate(c0, t0), rate(c1, t1)
+
+
+def probe_matmul(device, seconds: float = 4.0, n: int = 8192) -> float:
+    return probe_matmul_halves(device, seconds, n)[1]
 
 
 def probe_hbm(device, seconds: float = 1.0, nbytes: int = 2 << 30) -> float:
@@ -63,14 +89,25 @@ def probe_pcie(device, seconds: float = 1.0, nbytes: int = 256 << 20) -> float:
     return nbytes * cnt / dt / 1e9       # per direction, with both directions busy
 
 
-def probe_hardware(device="cuda:0", seconds: float = 6.0, verbose: bool = False) -> HardwareCost:
+def probe_hardware(device="cuda:0", seconds: float = 6.0, verbose: bool = False, *, matmul_n: int = 8192,
+                   transfer_mib: int = 256, matmul_target_seconds: float = None, mem_bw_target_seconds: float = None,
+                   **_ignored) -> HardwareProbeResult:
+    """Sustained GEMM rate (second half of the run), HBM and PCIe bandwidth of ``device``.  ``seconds`` is the whole
+    probe's length, split 60 / 20 / 20; the reference's ``matmul_target_seconds`` / ``mem_bw_target_seconds`` set the
+    parts one by one (its remaining tuning keywords are accepted and have no counterpart here)."""
     dev = torch.device(device)
     if dev.type != "cuda":
-        return HardwareCost()
+        return HardwareProbeResult()
+    t_mm = matmul_target_seconds if matmul_target_seconds is not None else seconds * 0.6
+    t_bw = mem_bw_target_seconds if mem_bw_target_seconds is not None else seconds * 0.2
     with torch.cuda.device(dev):
-        tf = probe_matmul(dev, seconds * 0.6)
-        hbm = probe_hbm(dev, seconds * 0.2)
-        pcie = probe_pcie(dev, seconds * 0.2)
+        first, second = probe_matmul_halves(dev, t_mm, matmul_n)
+        hbm = probe_hbm(dev, t_bw)
+        pcie = probe_pcie(dev, seconds * 0.2, transfer_mib << 20)
     if verbose:
-        print(f"[hw probe] bf16 {tf:.0f} TFLOPS sustained, HBM {hbm:.0f} GB/s, PCIe {pcie:.1f} GB/s per direction")
-    return HardwareCost(peak_tflops=tf, pcie_bw_gbps=pcie, mem_bw_gbps=hbm)
+        print(f"[hw probe] bf16 {second:.0f} TFLOPS sustained ({first:.0f} in the first half), HBM {hbm:.0f} GB/s, "
+              f"PCIe {pcie:.1f} GB/s per direction")
+    return HardwareProbeResult(peak_tflops=second, pcie_bw_gbps=pcie, mem_bw_gbps=hbm, matmul_n=matmul_n,
+                               matmul_total_seconds=t_mm, achieved_tflops_first_half=first,
+                               achieved_tflops_second_half=second, transfer_bytes=transfer_mib << 20,
+                               mem_bw_total_seconds=t_bw)

@@ -12,9 +12,13 @@ import subprocess
 from typing import Optional
 
 
-def get_available_gpu_memory(device="cuda:0") -> int:
+def get_available_gpu_memory(device="cuda:0", *, device_id: Optional[int] = None) -> int:
+    """Free device memory in bytes; ``device`` is a device string / object or a bare index (``device_id`` is the
+    reference's keyword for the index)."""
     import torch
-    dev = torch.device(device)
+    if device_id is not None:
+        device = device_id
+    dev = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
     if dev.type != "cuda":
         return 8 << 30
     try:

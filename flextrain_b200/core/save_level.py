@@ -22,9 +22,19 @@ class HardwareCost:
     pcie_bw_gbps: float = 50.0             # host <-> HBM, per direction
     nvlink_bw_gbps: float = 770.0          # peer HBM <-> HBM, per direction
     mem_bw_gbps: float = 6546.0
+    practical_efficiency_factor: float = 1.0   # scales a nameplate peak down; 1.0 for a measured rate
+
+    @property
+    def effective_flops_per_ms(self) -> float:
+        return self.practical_efficiency_factor * self.peak_tflops * 1e12 / 1e3
+
+    @property
+    def pcie_bytes_per_ms(self) -> float:
+        return self.pcie_bw_gbps * 1e9 / 1e3
 
     def flops_to_ms(self, flops: float) -> float:
-        return flops / (self.peak_tflops * 1e12) * 1e3
+        rate = self.effective_flops_per_ms
+        return flops / rate if rate > 0 else 0.0
 
     def bytes_to_ms(self, nbytes: float, link: str = "pcie") -> float:
         bw = {"pcie": self.pcie_bw_gbps, "nvlink": self.nvlink_bw_gbps, "hbm": self.mem_bw_gbps}[link]
@@ -52,6 +62,14 @@ class SaveLevelPlan:
 
     def level(self, layer: int, chunk: int) -> int:
         return self.levels[(layer, chunk)]
+
+    # the reference's spellings (flextrain/core/save_level.py:88-132)
+    def level_for(self, layer_id: int, chunk_id: int) -> int:
+        return self.levels[(layer_id, chunk_id)]
+
+    @property
+    def choices(self) -> Dict[Tuple[int, int], int]:
+        return self.levels
 
     def histogram(self) -> Dict[int, int]:
         h: Dict[int, int] = {}

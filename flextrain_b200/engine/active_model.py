@@ -55,6 +55,19 @@ class StepStats:
     def loss(self) -> float:
         return self.loss_sum / max(self.active_tokens, 1)
 
+    # the reference's field names (flextrain/engine/active_model.py:125-129)
+    @property
+    def total_loss(self) -> float:
+        return self.loss_sum
+
+    @property
+    def total_tokens(self) -> int:
+        return self.tokens
+
+    @property
+    def rounds(self) -> int:
+        return self.n_rounds
+
 
 def _nvtx(name: str):
     if torch.cuda.is_available():
@@ -115,11 +128,27 @@ class ActiveModel:
             ep.attach(self)
 
     # ====================================================================== public API
-    def fwd_bwd(self, seqs: Seq[Sequence], loss_scale_factor: Optional[float] = None,
-                total_tokens_per_step: Optional[int] = None, loss_fn=None, forward_only: bool = False) -> StepStats:
+    def fwd_bwd(self, seqs: Optional[Seq[Sequence]] = None, loss_scale_factor: Optional[float] = None,
+                total_tokens_per_step: Optional[int] = None, loss_fn=None, forward_only: bool = False, *,
+                sequences: Optional[Seq[Sequence]] = None, verbose: Optional[bool] = None) -> StepStats:
         """Forward + backward over ``seqs``; gradients accumulate until :meth:`step`.  ``forward_only`` stops after the
-        loss (see :meth:`evaluate`): no gradient buffer is read or written."""
+        loss (see :meth:`evaluate`): no gradient buffer is read or written.  ``sequences`` is the reference's name for
+        the first argument; ``verbose`` overrides the engine's setting for this call."""
         t0 = time.perf_counter()
+        if seqs is None:
+            seqs = sequences
+        if seqs is None:
+            raise TypeError("fwd_bwd() needs the step's sequences")
+        seqs = list(seqs)
+        was_verbose = self.verbose
+        if verbose is not None:
+            self.verbose = bool(verbose)
+        try:
+            return self._fwd_bwd(seqs, loss_scale_factor, total_tokens_per_step, loss_fn, forward_only, t0)
+        finally:
+            self.verbose = was_verbose
+
+    def _fwd_bwd(self, seqs, loss_scale_factor, total_tokens_per_step, loss_fn, forward_only, t0) -> StepStats:
         ws = self.ws
         if loss_scale_factor is None:
             loss_scale_factor = 1.0 / max(sum(s.active_token_count for s in seqs), 1)
@@ -200,6 +229,31 @@ class ActiveModel:
         stats.elapsed_s = time.perf_counter() - t0
         return stats
 
+    # ---- the reference's attribute names (flextrain/engine/active_model.py:175-193)
+    @property
+    def backbone(self):
+        return self.layers
+
+    @property
+    def working_set(self) -> WorkingSetConfig:
+        return self.ws
+
+    @property
+    def hw_cost(self) -> HardwareCost:
+        return self.hw
+
+    @property
+    def step_count(self) -> int:
+        return self.step_num
+
+    @step_count.setter
+    def step_count(self, n: int) -> None:
+        self.step_num = int(n)
+
+    @property
+    def force_saved_act_level(self) -> Optional[int]:
+        return self.force_level
+
     def evaluate(self, seqs: Seq[Sequence], loss_fn=None) -> StepStats:
         """Loss of ``seqs`` under the current weights, forward only: gradients accumulated so far, optimizer state and
         the step counter are untouched (``stats.loss`` is the mean over active tokens; per-token losses are written
@@ -248,11 +302,12 @@ class ActiveModel:
             dist.all_reduce(part, group=group.pg)
         return float((rep + part).sqrt())
 
-    def step(self, max_grad_norm: Optional[float] = None) -> int:
+    def step(self, step_num: Optional[int] = None, *, max_grad_norm: Optional[float] = None) -> int:
         """Optimizer step over embed, head and every layer; returns 0, or the optimizer's error code.
-        ``max_grad_norm`` scales the gradients down when their global norm exceeds it (``last_grad_norm`` keeps the
-        norm before scaling)."""
-        self.step_num += 1
+        ``step_num`` is the update's number for AdamW's bias correction (default: one more than the last, as in
+        flextrain/engine/active_model.py:428-452); ``max_grad_norm`` scales the gradients down when their global norm
+        exceeds it (``last_grad_norm`` keeps the norm before scaling)."""
+        self.step_num = self.step_num + 1 if step_num is None else int(step_num)
         grad_scale = 1.0
         sharded = self.dp is not None and getattr(self.dp, "m", None) is not None      # reduced gradients live as shards
         if max_grad_norm is not None:
@@ -770,13 +825,19 @@ class ActiveModel:
                 grp.check()
 
     # --------------------------------------------------------------------- HF load / save
-    def load_hf(self, model_dir: str, strict: bool = False) -> None:
+    def load_hf(self, model_dir: Optional[str] = None, strict: bool = False, *, hf_path: Optional[str] = None,
+                arch=None) -> None:
+        """Fill the master weights from an HF directory.  ``hf_path`` is the reference's name for the directory; the
+        family's name map is found from the model's own configuration, so ``arch`` is accepted and not needed."""
         from ..io.hf_weights import load_hf_into_model
-        load_hf_into_model(self, model_dir, strict=strict)
+        load_hf_into_model(self, model_dir or hf_path, strict=strict)
 
-    def save_hf(self, out_dir: str, filename: str = "final.safetensors") -> str:
+    def save_hf(self, out_dir: str, filename: Optional[str] = None, *, out_filename: Optional[str] = None,
+                arch=None) -> str:
+        """One safetensors file of the weights the engine holds, in checkpoint names; returns its path
+        (flextrain/engine/active_model.py:795-840; ``out_filename`` is the reference's name for ``filename``)."""
         from ..io.hf_weights import export_model_safetensors
-        return export_model_safetensors(self, out_dir, filename)
+        return export_model_safetensors(self, out_dir, filename or out_filename or "final.safetensors")
 
     def save_training_state(self, out_dir: str, extra: Optional[dict] = None) -> str:
         """Weights + optimizer state + step counter (every rank calls it); see ``io/training_state.py``."""

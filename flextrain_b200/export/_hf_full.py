@@ -13,8 +13,13 @@ from ..io.hf_weights import checkpoint_names, collect_hf_state, is_export_writer
 from ._common import copy_aux_files, write_sharded_safetensors
 
 
-def save_hf_full(am, out_dir: str, *, max_shard_bytes: int = 5 << 30, source_dir: Optional[str] = None,
-                 _merge_lora: bool = False) -> str:
+def save_hf_full(am, out_dir: str, *, max_shard_bytes: Optional[int] = None, source_dir: Optional[str] = None,
+                 _merge_lora: bool = False, hf_source_dir: Optional[str] = None, shard_size_bytes: Optional[int] = None,
+                 arch=None) -> str:
+    """``hf_source_dir`` / ``shard_size_bytes`` are the reference's names for ``source_dir`` / ``max_shard_bytes``; the
+    family's name map comes from the model's own configuration, so ``arch`` is accepted and not needed."""
+    source_dir = source_dir or hf_source_dir
+    max_shard_bytes = max_shard_bytes or shard_size_bytes or (5 << 30)
     state = collect_hf_state(am, lora_merge=_merge_lora)          # collective under tensor / expert parallelism
     if not is_export_writer(am):
         return out_dir

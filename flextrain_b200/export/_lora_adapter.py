@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import json
 import os
+from typing import Optional
 
 import torch
 
@@ -34,7 +35,10 @@ def _wrapper_module_prefix(am):
     return nested if any(a.endswith("ForConditionalGeneration") for a in archs) else None
 
 
-def save_lora_adapter(am, out_dir: str, base_model_name_or_path: str = "") -> str:
+def save_lora_adapter(am, out_dir: str, base_model_name_or_path: Optional[str] = "", *, arch=None,
+                      rank: Optional[int] = None, alpha: Optional[float] = None, bias: str = "none") -> str:
+    """``rank`` / ``alpha`` override what ``adapter_config.json`` records (default: the values the model was built
+    with); ``bias`` is written through; ``arch`` is accepted and not needed (flextrain/export/_lora_adapter.py:198)."""
     from safetensors.torch import save_file
     from ..io.hf_weights import gather_local_parts, is_export_writer
     lora = am.layers[0].cfg.lora
@@ -93,8 +97,8 @@ def save_lora_adapter(am, out_dir: str, base_model_name_or_path: str = "") -> st
                  for k, v in state.items()}
     os.makedirs(out_dir, exist_ok=True)
     save_file(state, os.path.join(out_dir, "adapter_model.safetensors"), metadata={"format": "pt"})
-    cfg = {"peft_type": "LORA", "task_type": "CAUSAL_LM", "r": lora.rank, "lora_alpha": lora.alpha,
-           "lora_dropout": 0.0, "bias": "none", "fan_in_fan_out": False, "inference_mode": True,
+    cfg = {"peft_type": "LORA", "task_type": "CAUSAL_LM", "r": int(rank or lora.rank),
+           "lora_alpha": float(alpha if alpha is not None else lora.alpha), "lora_dropout": 0.0, "bias": bias, "fan_in_fan_out": False, "inference_mode": True,
            "target_modules": sorted({_MODULE[t].split(".")[-1] for t in lora.targets if t in _MODULE} | expert_targets),
            "base_model_name_or_path": base_model_name_or_path or (am.model_dir or "")}
     with open(os.path.join(out_dir, "adapter_config.json"), "w") as f:

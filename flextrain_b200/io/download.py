@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import json
 import os
+import sys
 from typing import Iterable, Optional
 
 DEFAULT_PATTERNS = ["*.json", "*.safetensors", "*.model", "*.txt", "*.jinja", "*.tiktoken"]
@@ -23,11 +24,21 @@ def _looks_complete(target: str) -> bool:
     return any(n.endswith(".safetensors") for n in os.listdir(target))
 
 
-def download_model(repo_id: str, target: str, revision: Optional[str] = None,
-                   allow_patterns: Optional[Iterable[str]] = None, force: bool = False) -> str:
-    """Mirror an HF model repository into ``target`` (explicit path, created if needed).  A target that already looks
-    complete is left alone unless ``force``."""
+def hf_checkpoint_is_complete(local_path) -> bool:
+    """True when ``local_path`` holds ``config.json`` and every weight file it needs (one ``model.safetensors`` or all
+    shards of the index), so an interrupted download is not mistaken for a model (flextrain/io/download.py:40-68)."""
+    return os.path.isdir(str(local_path)) and _looks_complete(str(local_path))
+
+
+def download_model(repo_id: str, target: Optional[str] = None, revision: Optional[str] = None,
+                   allow_patterns: Optional[Iterable[str]] = None, force: bool = False, *,
+                   target_dir: Optional[str] = None, verbose: bool = True) -> str:
+    """Mirror an HF model repository into ``target`` (explicit path, created if needed; ``target_dir`` is the
+    reference's name for it).  A target that already looks complete is left alone unless ``force``."""
+    target = str(target if target is not None else target_dir)
     if not force and os.path.isdir(target) and _looks_complete(target):
+        if verbose:
+            print(f"[download] {target} is complete; nothing to do", file=sys.stderr)
         return target
     try:
         from huggingface_hub import snapshot_download
@@ -42,9 +53,17 @@ def download_model(repo_id: str, target: str, revision: Optional[str] = None,
     return target
 
 
-def download_dataset(spec: str, target: str, split: str = "train", config: Optional[str] = None,
-                     force: bool = False, limit: Optional[int] = None) -> str:
-    """Write an SFT dataset (local JSON / JSONL file, or HF dataset id) as normalised JSONL at ``target``."""
+def download_dataset(spec: Optional[str] = None, target: Optional[str] = None, split: str = "train",
+                     config: Optional[str] = None, force: bool = False, limit: Optional[int] = None, *,
+                     dataset_spec: Optional[str] = None, target_path: Optional[str] = None, verbose: bool = True) -> str:
+    """Write an SFT dataset (local JSON / JSONL file, or HF dataset id) as normalised JSONL at ``target``
+    (``dataset_spec`` / ``target_path`` are the reference's names for the two arguments)."""
+    spec = spec if spec is not None else dataset_spec
+    target = str(target if target is not None else target_path)
+    if not force and os.path.exists(target) and os.path.getsize(target) > 0:
+        if verbose:
+            print(f"[download] {target} exists; nothing to do", file=sys.stderr)
+        return target
     if force and os.path.exists(target):
         os.remove(target)
     return materialize_sft_dataset(spec if os.path.exists(spec) or ":" in spec else f"{spec}:{split}", target, limit,
@@ -53,12 +72,13 @@ def download_dataset(spec: str, target: str, split: str = "train", config: Optio
 
 def normalise_sft_record(rec: dict) -> Optional[dict]:
     """Accepts ``instruction/output``, ``prompt/completion``, ``question/answer`` or chat ``messages``."""
-    for a, b in (("instruction", "output"), ("prompt", "completion"), ("question", "answer"), ("input", "output"),
-                 ("instruction", "response")):
+    for a, b, extra in (("instruction", "output", "input"), ("prompt", "completion", "input"),
+                        ("prompt", "response", "input"), ("question", "answer", "context"),
+                        ("query", "response", "context"), ("input", "output", None), ("instruction", "response", "input")):
         if a in rec and b in rec:
             ins = rec[a]
-            if a == "instruction" and rec.get("input"):
-                ins = f"{ins}\n{rec['input']}"
+            if extra and extra != a and rec.get(extra):
+                ins = f"{ins}\n{rec[extra]}"
             return {"instruction": str(ins), "response": str(rec[b])}
     msgs = rec.get("messages") or rec.get("conversations")
     if msgs:
@@ -68,6 +88,9 @@ def normalise_sft_record(rec: dict) -> Optional[dict]:
             return {"instruction": str(user[0].get("content", user[0].get("value", ""))),
                     "response": str(asst[0].get("content", asst[0].get("value", ""))), "messages": msgs}
     return None
+
+
+normalize_sft_record = normalise_sft_record          # the reference's spelling
 
 
 def maybe_download_hf_snapshot(repo_id: str, models_dir: str = "models") -> str:

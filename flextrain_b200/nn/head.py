@@ -11,7 +11,7 @@ import torch
 
 from .. import ops
 from ..core.layer import ChunkMeta, LossStats, ParamSpec, TensorSpec
-from .loss import CrossEntropyLoss, TokenSlice
+from .loss import CrossEntropyLoss, TokenSlice, apply_loss
 
 
 class LMHead:
@@ -44,7 +44,7 @@ class LMHead:
             sl = TokenSlice(meta.targets[a:b], meta.loss_mask[a:b] if meta.loss_mask is not None else None,
                             meta.extra.get("advantages")[a:b] if meta.extra.get("advantages") is not None else None,
                             meta.extra.get("ref_logprobs")[a:b] if meta.extra.get("ref_logprobs") is not None else None)
-            per_tok[a:b] = loss_fn(logits, sl, loss_scale, self.final_softcap)
+            per_tok[a:b] = apply_loss(loss_fn, logits, sl, loss_scale, self.final_softcap)
             if gW is not None:
                 ops.gemm(logits, hn, trans_a=True, beta=1.0, out=gW)
             if want_dx:

@@ -60,6 +60,27 @@ class MuonHyperparams:
     weight_decay: float = 0.0
     nesterov: bool = True
     check_error: bool = False
+    a: float = 3.4445                       # Newton-Schulz quintic coefficients: compiled into the kernels here,
+    b: float = -4.7750                      # so other values are refused rather than ignored
+    c: float = 2.0315
+
+    def __post_init__(self):
+        if (round(self.a, 4), round(self.b, 4), round(self.c, 4)) != (3.4445, -4.775, 2.0315):
+            raise ValueError("the Newton-Schulz coefficients are fixed at (3.4445, -4.7750, 2.0315)")
+
+
+@dataclass
+class HybridMuonAdamWHyperparams:
+    """(flextrain/optim/hybrid.py:147-153): the two optimizers' records; ``lr`` is the default of both."""
+    lr: float = 1e-3
+    adamw: Optional[AdamWHyperparams] = None
+    muon: Optional[MuonHyperparams] = None
+
+    def __post_init__(self):
+        if self.adamw is None:
+            self.adamw = AdamWHyperparams(lr=self.lr)
+        if self.muon is None:
+            self.muon = MuonHyperparams(lr=self.lr)
 
 
 class Optimizer(Protocol):
@@ -176,11 +197,24 @@ def uses_muon(t: TensorSpec) -> bool:
     return len(t.shape) in (2, 3) and not any(p in t.name for p in _ADAM_NAME_PARTS)
 
 
+def infer_optimizer_for_param(spec: TensorSpec, dims=None) -> str:
+    """``"muon"`` or ``"adamw"`` for one tensor, by :func:`uses_muon`'s rule (flextrain/optim/hybrid.py:60-89; shapes are
+    concrete here, so ``dims`` is not needed)."""
+    return "muon" if uses_muon(spec) else "adamw"
+
+
 @dataclass
 class HybridMuonAdamW:
     muon: Muon = field(default_factory=Muon)
     adamw: AdamW = field(default_factory=lambda: AdamW(lr=3e-4))
     check_error: bool = False
+
+    def __post_init__(self):
+        if isinstance(self.muon, HybridMuonAdamWHyperparams):       # HybridMuonAdamW(HybridMuonAdamWHyperparams(...))
+            hp = self.muon
+            self.muon = Muon(hp.muon)
+            self.adamw = AdamW(hp.adamw, state_dtype=torch.float32)   # the reference's hybrid keeps fp32 moments
+            self.check_error = bool(hp.adamw.check_error or hp.muon.check_error)
 
     @property
     def lr(self) -> float:
@@ -215,3 +249,20 @@ class HybridMuonAdamW:
 
     def flops_per_param(self) -> float:
         return 12.0
+
+
+def _accept_hp_keyword(cls) -> None:
+    """``Cls(hp=record)`` is the reference's spelling of ``Cls(record)``."""
+    plain = cls.__init__
+
+    def __init__(self, *args, hp=None, **kw):
+        if hp is not None:
+            args = (hp,) + args
+        plain(self, *args, **kw)
+
+    __init__.__doc__, __init__.__wrapped__ = plain.__doc__, plain
+    cls.__init__ = __init__
+
+
+for _cls in (AdamW, Muon, HybridMuonAdamW):
+    _accept_hp_keyword(_cls)

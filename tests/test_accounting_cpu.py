@@ -1,5 +1,7 @@
 """Book-keeping helpers: FLOP accounting of a step, parameter counts, batch-size divisors, memory probes and the YAML
 run configuration."""
+import json
+import os
 import pytest
 import torch
 
@@ -87,3 +89,98 @@ def test_reference_style_optimizer_constructors_and_package_exports():
     from flextrain_b200.nn import IGNORE_INDEX, CrossEntropyLoss, LMHead, TokenEmbedLayer  # noqa: F401
     from flextrain_b200.io import Sequence, ShardTokenSource, SyntheticTokenSource, TokenSource  # noqa: F401
     assert IGNORE_INDEX == -100 and unregister_all_process_pinned_memory() == 0
+
+
+def test_engine_surface_answers_to_the_reference_spellings(tmp_path):
+    """A training loop written against the reference runs unchanged: ``fwd_bwd(sequences=...)``, ``StepStats``'s
+    ``total_loss / total_tokens / rounds``, ``step(step_num)``, ``save_hf(out_filename=...)``, ``load_hf(hf_path=...)``,
+    ``am.working_set / backbone / step_count``, ``probe_hardware(...).hw_cost`` and ``register_block_builder`` with a
+    list of architecture names."""
+    import os
+    import pytest
+    import torch
+    import flextrain_b200 as ft
+    from conftest import build_tiny
+    from flextrain_b200.core.hw_probe import probe_hardware
+    am = build_tiny(batch_tokens=512)
+    src = ft.SyntheticTokenSource(vocab_size=1024, seq_lens=128, seed=0)
+    seqs = src.get_sequences(512)
+    st = am.fwd_bwd(sequences=seqs, loss_scale_factor=1.0 / 512, total_tokens_per_step=512, verbose=False)
+    assert st.total_tokens == 512 and st.rounds == st.n_rounds >= 1 and st.total_loss == st.loss_sum > 0
+    assert am.step(7) == 0 and am.step_count == 7 and am.step() == 0 and am.step_count == 8
+    assert am.working_set is am.ws and am.backbone is am.layers and am.hw_cost is am.hw
+    with pytest.raises(TypeError):
+        am.fwd_bwd()
+    path = am.save_hf(str(tmp_path), out_filename="weights.safetensors")
+    assert os.path.basename(path) == "weights.safetensors" and os.path.exists(path)
+    before = am.evaluate(seqs).total_loss
+    for _, _, _, t in am.named_master_params():
+        t.zero_()
+    am.load_hf(hf_path=str(tmp_path), strict=False)
+    assert abs(am.evaluate(seqs).total_loss - before) < 1e-3 * before
+    probe = probe_hardware(device="cpu", matmul_target_seconds=0.1, n_matmul_warmup=1)
+    assert isinstance(probe, ft.HardwareCost) and probe.hw_cost.peak_tflops == probe.peak_tflops and probe.mem_bw_gbps > 0
+    hw = ft.HardwareCost(peak_tflops=100.0, pcie_bw_gbps=10.0, practical_efficiency_factor=0.5)
+    assert hw.flops_to_ms(1e14) == 2000.0 and hw.pcie_bytes_per_ms == 1e7 and hw.effective_flops_per_ms == 5e10
+    plan = ft.SaveLevelPlan.uniform(2, 3, 1)
+    assert plan.level_for(1, 2) == 1 and plan.choices is plan.levels
+    b = lambda layer_id, dc, mc: None
+    ft.register_block_builder(["AForCausalLM", "BForCausalLM"], b)
+    ft.register_block_builder("AForCausalLM", b)                       # the same builder again: fine
+    with pytest.raises(ValueError):
+        ft.register_block_builder(["BForCausalLM"], lambda *a: None)
+
+
+def test_more_reference_spellings(tmp_path):
+    """Keyword names of the reference in the optimizers, exports, download helpers and FLOP helpers."""
+    import pytest
+    import torch
+    import flextrain_b200 as ft
+    from conftest import build_tiny
+    from flextrain_b200.core.flop_accounting import bwd_flops, fwd_flops, opt_flops_per_step, step_flops
+    from flextrain_b200.core.memory import get_available_gpu_memory
+    from flextrain_b200.io.download import download_dataset, hf_checkpoint_is_complete, normalize_sft_record
+    from flextrain_b200.optim import (AdamW, AdamWHyperparams, HybridMuonAdamW, HybridMuonAdamWHyperparams, Muon,
+                                      MuonHyperparams, infer_optimizer_for_param)
+    from flextrain_b200.core import TensorSpec
+    a = AdamW(hp=AdamWHyperparams(lr=2e-4), state_dtype=torch.float32)
+    assert a == AdamW(lr=2e-4, weight_decay=0.001, state_dtype=torch.float32)
+    assert Muon(hp=MuonHyperparams(lr=5e-3)).lr == 5e-3
+    h = HybridMuonAdamW(hp=HybridMuonAdamWHyperparams(lr=2e-3))
+    assert h.muon.lr == h.adamw.lr == 2e-3 and h.adamw.state_dtype == torch.float32
+    with pytest.raises(ValueError):
+        MuonHyperparams(a=3.0)
+    assert infer_optimizer_for_param(TensorSpec("w_q", (8, 8)), {}) == "muon"
+    assert infer_optimizer_for_param(TensorSpec("w_router", (8, 8)), {}) == "adamw"
+    assert infer_optimizer_for_param(TensorSpec("w_q", (8, 8), optimizer="adamw"), {}) == "adamw"
+    # exports
+    am = build_tiny(batch_tokens=512, lora_targets="all", lora_rank=4, lora_alpha=8.0)
+    out = ft.export.save_hf_full(am, str(tmp_path / "full"), hf_source_dir=None, arch=None, shard_size_bytes=1 << 20)
+    assert len([f for f in os.listdir(out) if f.endswith(".safetensors")]) > 1            # the small shard size took
+    ad = ft.export.save_lora_adapter(am, str(tmp_path / "ad"), base_model_name_or_path="base", rank=4, alpha=8.0, bias="none")
+    cfg = json.load(open(os.path.join(ad, "adapter_config.json")))
+    assert cfg["r"] == 4 and cfg["lora_alpha"] == 8.0 and cfg["base_model_name_or_path"] == "base"
+    for _, _, n, t in am.named_master_params():
+        if n.endswith("_lora_b"):
+            t.fill_(0.01)
+    ft.export.save_hf_merged(am, str(tmp_path / "m1"))
+    assert any(float(t.abs().max()) > 0 for _, _, n, t in am.named_master_params() if n.endswith("_lora_b"))
+    ft.export.save_hf_merged(am, str(tmp_path / "m2"), keep_lora_after_merge=False)
+    assert all(float(t.abs().max()) == 0 for _, _, n, t in am.named_master_params() if n.endswith("_lora_b"))
+    assert ft.export.merge_lora_into_base(am) > 0
+    # download helpers
+    assert not hf_checkpoint_is_complete(tmp_path) and hf_checkpoint_is_complete(out)
+    assert normalize_sft_record({"query": "q", "response": "r", "context": "c"}) == {"instruction": "q\nc", "response": "r"}
+    src = tmp_path / "d.json"
+    src.write_text(json.dumps([{"prompt": "p", "response": "r"}]))
+    got = download_dataset(dataset_spec=str(src), target_path=str(tmp_path / "d.jsonl"), verbose=False)
+    assert json.loads(open(got).readline())["instruction"] == "p"
+    # FLOP helpers with a sequence length instead of recorded statistics
+    plain = build_tiny(batch_tokens=512)
+    seqs = ft.SyntheticTokenSource(1024, 128, seed=0).get_sequences(512)
+    st = plain.fwd_bwd(seqs)
+    head = 2.0 * 512 * plain.head.vocab_size * plain.head.d_model
+    assert abs(4 * fwd_flops(plain, 128) - (st.fwd_flops + head)) < 1e-6 * st.fwd_flops
+    assert bwd_flops(plain, 128, mode="lora") == fwd_flops(plain, 128) and bwd_flops(plain, 128) == 2 * fwd_flops(plain, 128)
+    assert step_flops(plain, [128] * 4) == 12 * fwd_flops(plain, 128) + opt_flops_per_step(plain)
+    assert get_available_gpu_memory("cpu") == get_available_gpu_memory(device="cpu") > 0

@@ -75,3 +75,69 @@ def test_mse_loss_gradients():
     st = am.fwd_bwd(seqs, loss_scale_factor=1.0, loss_fn=MSELoss())
     assert abs(st.loss_sum - float(total)) < 1e-3 * max(1.0, abs(float(total)))
     _compare(am, P, total)
+
+
+class _RefStyleLabelSmoothing:
+    """A loss written against the reference's protocol: ``compute`` returns UNscaled ``dZ`` and fills
+    ``per_token_loss_out``; it reads ``token_slice.labels``."""
+
+    def __init__(self, eps):
+        self.eps = eps
+
+    def compute(self, logits, token_slice, *, loss_scale, per_token_loss_out):
+        z = logits.to(torch.float32)
+        labels = token_slice.labels
+        valid = labels != -100
+        logp = torch.log_softmax(z, -1)
+        V = z.shape[1]
+        target = torch.full_like(z, self.eps / V)
+        target.scatter_(1, labels.clamp(min=0).long().unsqueeze(1), 1.0 - self.eps + self.eps / V)
+        per_token_loss_out.copy_(-(target * logp).sum(-1) * valid)
+        dz = (torch.exp(logp) - target) * valid.unsqueeze(1)
+        return dz.to(logits.dtype), {"smoothing": self.eps}
+
+
+@pytest.mark.parametrize("softcap", [0.0, 5.0])
+def test_reference_style_loss_object_matches_autograd(softcap):
+    """A ``compute``-style loss (the reference's protocol) runs through the engine; with a final soft-cap the loss
+    sees capped logits and its gradient is carried back through the cap."""
+    am = build_tiny(dims=DIMS, max_seq_len=48, batch_tokens=96)
+    seqs = _seqs()
+    eps = 0.1
+    am.head.final_softcap = softcap
+    st = am.fwd_bwd(seqs, loss_scale_factor=0.5, loss_fn=_RefStyleLabelSmoothing(eps))
+    am.head.final_softcap = 0.0                      # the naive forward below applies the cap itself
+    P = clone_params(am)
+    total = 0.0
+    for s in seqs:
+        z = naive_forward(am, P, s.tokens).float()
+        if softcap:
+            z = softcap * torch.tanh(z / softcap)
+        logp = torch.log_softmax(z, -1)
+        valid = s.targets != -100
+        V = z.shape[1]
+        target = torch.full_like(z, eps / V)
+        target.scatter_(1, s.targets.clamp(min=0).unsqueeze(1), 1.0 - eps + eps / V)
+        total = total + (-(target * logp).sum(-1) * valid).sum()
+    assert abs(st.loss_sum - float(total)) < 1e-3 * float(total)
+    _compare(am, P, total * 0.5)
+
+
+def test_builtin_losses_answer_to_the_reference_call_and_names():
+    from flextrain_b200.nn.loss import CrossEntropyLoss, TokenContext, TokenSlice
+    torch.manual_seed(0)
+    z = torch.randn(6, 11)
+    labels = torch.tensor([1, 2, -100, 4, 5, 6])
+    ctx = TokenContext(labels=labels, advantages=torch.ones(6))
+    sl = ctx.slice_for(2, 4)
+    assert sl.offset == 2 and sl.size == 4 and sl.labels is sl.targets and sl.targets.tolist() == [-100, 4, 5, 6]
+    assert ctx.total_tokens == 6 and TokenSlice(labels=labels).targets is labels
+    out = torch.empty(6)
+    zz = z.clone()
+    dz, aux = CrossEntropyLoss(ignore_index=-100).compute(zz, TokenSlice(labels), loss_scale=0.25, per_token_loss_out=out)
+    want = torch.nn.functional.cross_entropy(z, labels, ignore_index=-100, reduction="none")
+    torch.testing.assert_close(out, want)
+    p = torch.softmax(z, -1)
+    onehot = torch.zeros_like(p).scatter_(1, labels.clamp(min=0).unsqueeze(1), 1.0)
+    torch.testing.assert_close(dz, (p - onehot) * (labels != -100).unsqueeze(1))       # unscaled, as the reference says
+    assert GRPOLoss(kl_coef=0.3).kl_beta == 0.3
