@@ -60,6 +60,17 @@ def _hw_cost(hw_cost, device) -> HardwareCost:
     return HardwareCost()
 
 
+def _dims_of(mc: ModelConfig) -> dict:
+    """The model's dimensions under the reference's keys (``am.dims["vocab_size"]`` and so on; ``expert_dim`` is the
+    FFN width of a dense model and the per-expert width of a routed one, as in its catalogue)."""
+    routed = mc.num_experts > 0
+    return {"vocab_size": mc.vocab_size, "n_layers": mc.n_layers, "d_model": mc.d_model, "n_heads": mc.n_heads,
+            "n_kv_heads": mc.n_kv_heads, "head_dim": mc.head_dim, "expert_dim": mc.expert_dim if routed else mc.ffn_dim,
+            "ffn_dim": mc.ffn_dim, "num_routed_experts": mc.num_experts, "top_k": mc.top_k,
+            "num_shared_experts": (1 if mc.shared_dim > 0 else 0) if routed else 1,
+            "shared_expert_dim": mc.shared_dim, "is_causal": mc.is_causal}
+
+
 def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_batch_tokens, max_gpu_mem_bytes,
                         max_host_mem_bytes, device, leeway_gpu_mem_bytes, leeway_host_mem_bytes, dt: DTypePolicy,
                         lora, hw_cost, force_saved_act_level, head_chunk_size, verbose, min_chunk_size,
@@ -112,7 +123,7 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
         dp, tp_group, ep_group = build_parallel(world_size=world_size, rank=rank, shard=ws.shard, tp=tp, ep=ep,
                                                 device=device, process_group=process_group)
     am = ActiveModel(embed=embed, layers=layers, head=head, optimizer=optimizer, ws=ws, device=device, hw_cost=hw,
-                     dims=None, arch=mc.arch, hf_config=mc.hf, force_saved_act_level=force_saved_act_level,
+                     dims=_dims_of(mc), arch=mc.arch, hf_config=mc.hf, force_saved_act_level=force_saved_act_level,
                      verbose=verbose, dp=dp, tp=tp_group, ep=ep_group, model_dir=model_dir, host_backend=host_backend)
     am.model_config = mc
     am.is_causal = mc.is_causal

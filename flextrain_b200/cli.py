@@ -13,7 +13,7 @@ def _info(args) -> int:
 
     import flextrain_b200 as ft
     from .build import CSRC, LIB
-    from .core.memory import get_available_gpu_memory, get_available_host_memory
+    from .core._memory import get_available_gpu_memory, get_available_host_memory
     from .io.arch import ARCH_MODULES
     print(f"flextrain_b200 {ft.__version__}")
     print(f"torch {torch.__version__}, CUDA available: {torch.cuda.is_available()}")

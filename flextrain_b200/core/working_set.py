@@ -22,7 +22,7 @@ from dataclasses import dataclass, field
 from typing import List, Optional, Tuple
 
 from .save_level import HardwareCost
-from .sizing import divisors
+from ._sizing import divisors
 
 GiB = 1 << 30
 # Data-parallel state sharding.  There is no "optimizer state only" level: the gradient reduction of the peer-memory

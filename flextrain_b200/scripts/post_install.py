@@ -80,7 +80,7 @@ def check_libraries(build: bool = True) -> Dict[str, Dict[str, object]]:
 
 def check_gpus() -> Dict[str, object]:
     import torch
-    from ..core.memory import get_available_host_memory
+    from ..core._memory import get_available_host_memory
     out: Dict[str, object] = {"available": torch.cuda.is_available(), "devices": [], "peer_access": None,
                               "host_memory_gib": round(get_available_host_memory() / 2 ** 30, 1)}
     if not out["available"]:

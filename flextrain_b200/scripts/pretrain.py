@@ -179,8 +179,8 @@ def run(args) -> int:
     import torch
 
     import flextrain_b200 as ft
-    from ..core.memory import get_available_gpu_memory, get_available_host_memory
-    from ..core.sizing import model_param_count
+    from ..core._memory import get_available_gpu_memory, get_available_host_memory
+    from ..core._sizing import model_param_count
     os.makedirs(args.out, exist_ok=True)
     final = os.path.join(args.out, "final.json")
     if os.path.exists(final):

@@ -8,8 +8,8 @@ import torch
 import flextrain_b200 as ft
 from flextrain_b200.config import RunConfig
 from flextrain_b200.core import flop_accounting as fa
-from flextrain_b200.core.memory import get_available_gpu_memory, get_available_host_memory
-from flextrain_b200.core.sizing import divisors, layer_param_count, matmul_flops_per_token, model_param_count, prev_high_div
+from flextrain_b200.core._memory import get_available_gpu_memory, get_available_host_memory
+from flextrain_b200.core._sizing import divisors, layer_param_count, matmul_flops_per_token, model_param_count, prev_high_div
 from conftest import build_tiny
 
 DIMS = dict(vocab_size=256, n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, expert_dim=128, ffn_dim=128,
@@ -109,6 +109,7 @@ def test_engine_surface_answers_to_the_reference_spellings(tmp_path):
     assert st.total_tokens == 512 and st.rounds == st.n_rounds >= 1 and st.total_loss == st.loss_sum > 0
     assert am.step(7) == 0 and am.step_count == 7 and am.step() == 0 and am.step_count == 8
     assert am.working_set is am.ws and am.backbone is am.layers and am.hw_cost is am.hw
+    assert am.dims["vocab_size"] == 1024 and am.dims["n_layers"] == len(am.backbone) and am.dims["expert_dim"] > 0
     with pytest.raises(TypeError):
         am.fwd_bwd()
     path = am.save_hf(str(tmp_path), out_filename="weights.safetensors")
@@ -138,7 +139,7 @@ def test_more_reference_spellings(tmp_path):
     import flextrain_b200 as ft
     from conftest import build_tiny
     from flextrain_b200.core.flop_accounting import bwd_flops, fwd_flops, opt_flops_per_step, step_flops
-    from flextrain_b200.core.memory import get_available_gpu_memory
+    from flextrain_b200.core._memory import get_available_gpu_memory
     from flextrain_b200.io.download import download_dataset, hf_checkpoint_is_complete, normalize_sft_record
     from flextrain_b200.optim import (AdamW, AdamWHyperparams, HybridMuonAdamW, HybridMuonAdamWHyperparams, Muon,
                                       MuonHyperparams, infer_optimizer_for_param)

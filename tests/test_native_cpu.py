@@ -207,7 +207,7 @@ def _catalogue():
 def test_every_packaged_model_plans(name):
     """Every entry of the packaged catalogue resolves to its family and gets a plan for one and for eight 180 GB GPUs
     (``plan_only``: nothing is allocated); models that cannot fit one GPU must say so with an error, not a crash."""
-    from flextrain_b200.core.sizing import model_param_count
+    from flextrain_b200.core._sizing import model_param_count
     dims = dict(_catalogue()[name])
     arch, hyper = dims.pop("arch"), dims.pop("hyperparams", None)
     kw = dict(arch=arch, hyperparams=hyper, optimizer=ft.AdamW(state_dtype=torch.float32), max_seq_len=1024,

@@ -24,7 +24,7 @@ sys.path.insert(0, ROOT)
 
 import flextrain_b200 as ft  # noqa: E402
 from flextrain_b200.core.flop_accounting import step_flops_breakdown  # noqa: E402
-from flextrain_b200.core.memory import get_available_gpu_memory, get_available_host_memory  # noqa: E402
+from flextrain_b200.core._memory import get_available_gpu_memory, get_available_host_memory  # noqa: E402
 from flextrain_b200.engine.schedule import split_sequences  # noqa: E402
 
 _DT = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}
