@@ -20,6 +20,7 @@ from .core.save_level import HardwareCost
 from .core.working_set import WorkingSetConfig, determine_working_set_config
 from .engine.active_model import ActiveModel
 from .io.arch import select_arch_module
+from .optim.base import as_engine_optimizer
 from .io.arch.common import DTypePolicy, ModelConfig, build_model_parts, config_from_dims, resolve_lora
 
 # ``builder(layer_id, decoder_config, model_config) -> Layer`` (the reference's alias of the same name takes
@@ -78,6 +79,7 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
                         opt_state: str = "auto",
                         process_group, model_dir=None, arch_key=None, host_backend=None,
                         plan_only: bool = False) -> ActiveModel:
+    optimizer = as_engine_optimizer(optimizer)
     if tp == "auto" or ep == "auto":
         args = dict(locals())
         args.pop("mc")

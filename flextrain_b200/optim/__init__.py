@@ -10,9 +10,10 @@ State keys follow flextrain/optim/base.py:77-87: ``o_adam_m_<suffix>``, ``o_adam
 NaN/Inf gradient, in which case nothing was updated.
 """
 from .adamw import AdamW, AdamWHyperparams
-from .base import Optimizer, OptimizerStateSpec, state_key
+from .base import Optimizer, OptimizerStateSpec, OptStateTensor, ReferenceStyleOptimizer, as_engine_optimizer, state_key
 from .hybrid import HybridMuonAdamW, HybridMuonAdamWHyperparams, infer_optimizer_for_param, uses_muon
 from .muon import Muon, MuonHyperparams
 
 __all__ = ["AdamW", "AdamWHyperparams", "HybridMuonAdamW", "HybridMuonAdamWHyperparams", "Muon", "MuonHyperparams",
-           "Optimizer", "OptimizerStateSpec", "infer_optimizer_for_param", "state_key", "uses_muon"]
+           "OptStateTensor", "Optimizer", "OptimizerStateSpec", "ReferenceStyleOptimizer", "as_engine_optimizer",
+           "infer_optimizer_for_param", "state_key", "uses_muon"]

@@ -185,3 +185,50 @@ def test_more_reference_spellings(tmp_path):
     assert bwd_flops(plain, 128, mode="lora") == fwd_flops(plain, 128) and bwd_flops(plain, 128) == 2 * fwd_flops(plain, 128)
     assert step_flops(plain, [128] * 4) == 12 * fwd_flops(plain, 128) + opt_flops_per_step(plain)
     assert get_available_gpu_memory("cpu") == get_available_gpu_memory(device="cpu") > 0
+
+
+def test_an_optimizer_written_to_the_reference_protocol_trains_the_model():
+    """``state_spec = OptimizerStateSpec(tensors=...)`` + ``step(..., *, step_num)``: SGD with momentum written that
+    way drives the engine and matches ``torch.optim.SGD`` on the naive model."""
+    import torch
+    import flextrain_b200 as ft
+    from conftest import build_tiny
+    from flextrain_b200.bench.naive import clone_params, naive_loss
+    from flextrain_b200.optim.base import Optimizer, OptimizerStateSpec, OptStateTensor  # noqa: F401
+
+    class MomentumSGD:
+        state_spec = OptimizerStateSpec(tensors=(OptStateTensor(name="o_buf", dtype=torch.float32),))
+
+        def __init__(self, lr, mu):
+            self.lr, self.mu, self.calls = lr, mu, []
+
+        def step(self, param_spec, master, grads, state, *, step_num):
+            self.calls.append(step_num)
+            for p in param_spec.tensors:
+                grad_key = "g_" + p.name[2:] if p.name.startswith("w_") else "g_" + p.name
+                buf = state[f"o_buf_{p.name[2:] if p.name.startswith('w_') else p.name}"]
+                buf.mul_(self.mu).add_(grads[grad_key].float())
+                master[p.name].add_(buf.to(master[p.name].dtype), alpha=-self.lr)
+            return 0
+
+    opt = MomentumSGD(lr=0.05, mu=0.9)
+    am = build_tiny(batch_tokens=256, optimizer=opt)
+    P = clone_params(am)
+    ref = torch.optim.SGD(list(P.values()), lr=0.05, momentum=0.9)
+    src = ft.SyntheticTokenSource(1024, 128, seed=5)
+    for step in range(3):
+        seqs = src.get_sequences(256)
+        st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / 256)
+        assert am.step() == 0
+        ref.zero_grad()
+        loss = naive_loss(am, P, seqs)                       # the mean over the 256 scored tokens
+        loss.backward()
+        ref.step()
+        assert abs(st.loss_sum / 256 - float(loss)) < 2e-4
+    assert opt.calls[:3] == [1, 1, 1] or opt.calls.count(3) >= 1          # called per unit, with the step number
+    bm = am.buffers
+    for (scope, l, name), p in P.items():
+        mine = {"embed": bm.embed_params(), "head": bm.head_params()}.get(scope) or bm.host_params(l)
+        torch.testing.assert_close(mine[name].float(), p.detach(), rtol=2e-4, atol=2e-5, msg=f"{scope}/{l}/{name}")
+    am.optimizer.lr = 0.01
+    assert opt.lr == 0.01
