@@ -30,7 +30,7 @@ from ..core.layer import ChunkMeta, LayerContext
 from ..core.save_level import (HardwareCost, SaveLevelPlan, TransmissionScheduler, build_dp_tables,
                                plan_from_solution)
 from ..core.working_set import WorkingSetConfig
-from ..io.sequence import Sequence
+from ..io.sequence import Sequence, as_sequence
 from .buffers import BufferManager
 from .schedule import ChunkPolicy, prepare_training_chunks, split_sequences
 from .streams import EventBook, StreamBundle
@@ -139,7 +139,8 @@ class ActiveModel:
             seqs = sequences
         if seqs is None:
             raise TypeError("fwd_bwd() needs the step's sequences")
-        seqs = list(seqs)
+        given = list(seqs)
+        seqs = [as_sequence(s) for s in given]                 # any object with ``tokens`` will do
         was_verbose = self.verbose
         if verbose is not None:
             self.verbose = bool(verbose)
@@ -147,6 +148,12 @@ class ActiveModel:
             return self._fwd_bwd(seqs, loss_scale_factor, total_tokens_per_step, loss_fn, forward_only, t0)
         finally:
             self.verbose = was_verbose
+            for mine, theirs in zip(seqs, given):              # per-token losses go back to the caller's own objects
+                if mine is not theirs and mine.per_token_loss is not None:
+                    try:
+                        theirs.per_token_loss = mine.per_token_loss
+                    except AttributeError:
+                        pass
 
     def _fwd_bwd(self, seqs, loss_scale_factor, total_tokens_per_step, loss_fn, forward_only, t0) -> StepStats:
         ws = self.ws

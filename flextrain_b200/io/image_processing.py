@@ -178,9 +178,26 @@ def preprocess_frames(frames: Seq[Any], g: ImageGeometry, resize: bool = True,
     return ImageInputCPU(pixel_values=x.contiguous(), grid_thw=(gt, gh, gw), kind="video" if video else "image")
 
 
-def preprocess_images(images: Seq[Any], g: Optional[ImageGeometry] = None, resize: bool = True) -> List[ImageInputCPU]:
+def _open_images(images: Seq[Any]) -> List[Any]:
+    out = []
+    for im in images:
+        if isinstance(im, (str, os.PathLike)):
+            from PIL import Image
+            im = Image.open(im).convert("RGB")
+        out.append(im)
+    return out
+
+
+def preprocess_images(images: Seq[Any], g: Any = None, resize: bool = True):
+    """Images (objects or paths) -> one :class:`ImageInputCPU` each.  Given a :class:`MultimodalProcessorBundle` in
+    place of the geometry (the reference's call, flextrain/io/image_processing.py:112-143) the result is the pair
+    ``(pixel_values, image_grid_thw)`` of all images instead."""
+    if hasattr(g, "geometry"):
+        ims = [preprocess_frames([im], g.geometry, resize=resize) for im in _open_images(images)]
+        return (torch.cat([im.pixel_values for im in ims], 0) if ims else torch.empty(0, g.geometry.patch_dim),
+                torch.tensor([list(im.grid_thw) for im in ims], dtype=torch.int64).reshape(-1, 3))
     g = g or ImageGeometry()
-    return [preprocess_frames([im], g, resize=resize) for im in images]
+    return [preprocess_frames([im], g, resize=resize) for im in _open_images(images)]
 
 
 def patchify(img: torch.Tensor, patch: int = 16, temporal_patch: int = 2, merge: int = 2) -> ImageInputCPU:
@@ -192,7 +209,8 @@ def build_multimodal_sequence(segments: Seq[Any], image_token_id: int, merge: in
                               vision_start_token_id: Optional[int] = None, vision_end_token_id: Optional[int] = None,
                               train_on: Optional[Seq[bool]] = None, video_token_id: Optional[int] = None,
                               video_start_token_id: Optional[int] = None,
-                              video_end_token_id: Optional[int] = None) -> Sequence:
+                              video_end_token_id: Optional[int] = None, targets: Optional[torch.Tensor] = None,
+                              loss_mask: Optional[torch.Tensor] = None) -> Sequence:
     """Assemble token ids, images and video clips into one training sequence.
 
     ``segments`` alternates freely between lists of token ids and :class:`ImageInputCPU` objects; every image expands
@@ -202,6 +220,10 @@ def build_multimodal_sequence(segments: Seq[Any], image_token_id: int, merge: in
     clip's ``frame_prefix_ids`` entry (the ``<T seconds>`` text) when it has one; for the rotary positions every
     block is a single-frame image.  ``train_on[i]`` says whether the tokens of text segment ``i`` (counting all
     segments) are targets; placeholder and wrapper tokens never are, and the token before one never predicts it."""
+    if isinstance(segments, str):             # the reference's call: (text, images, bundle, *, targets, loss_mask)
+        return build_multimodal_sequence_from_text(segments, image_token_id, merge, targets=targets, loss_mask=loss_mask)
+    if targets is not None or loss_mask is not None:
+        raise TypeError("targets / loss_mask belong to the text form; with segments use train_on")
     ids: List[int] = []
     learn: List[bool] = []
     images: List[ImageInputCPU] = []
@@ -262,6 +284,45 @@ def build_multimodal_sequence(segments: Seq[Any], image_token_id: int, merge: in
         mi = {"pixel_values": torch.cat([im.pixel_values for im in images], 0),
               "grid_thw": [tuple(im.grid_thw) for im in images], "image_spans": spans, "images": images}
     return Sequence(toks, targets=tgt, seq_id=seq_id, modality_inputs=mi)
+
+
+def build_multimodal_sequence_from_text(text: str, images: Seq[Any], bundle: "MultimodalProcessorBundle", *,
+                                        targets: Optional[torch.Tensor] = None,
+                                        loss_mask: Optional[torch.Tensor] = None) -> Sequence:
+    """The reference's text form (flextrain/io/image_processing.py:146-278): ``text`` is the rendered conversation
+    with ONE image placeholder per image (and the vision start / end markers around it); every placeholder is expanded
+    to its image's merged patch count.  ``targets`` / ``loss_mask``, when given, are for the expanded sequence;
+    by default every text token is a target and placeholders are not."""
+    if bundle.tokenizer is None:
+        raise RuntimeError("this model directory has no tokenizer; use build_multimodal_sequence with token ids")
+    ids = bundle._flat_ids(bundle.tokenizer(text, add_special_tokens=False))
+    ims = [preprocess_frames([im], bundle.geometry) for im in _open_images(images)]
+    if sum(1 for t in ids if t == bundle.image_token_id) != len(ims):
+        raise ValueError(f"the text has {sum(1 for t in ids if t == bundle.image_token_id)} image placeholders for "
+                         f"{len(ims)} images")
+    segs: List[Any] = []
+    cur: List[int] = []
+    k = 0
+    for t in ids:
+        if t == bundle.image_token_id:
+            if cur:
+                segs.append(cur)
+            segs.append(ims[k])
+            k, cur = k + 1, []
+        else:
+            cur.append(t)
+    if cur:
+        segs.append(cur)
+    seq = build_multimodal_sequence(segs, bundle.image_token_id, bundle.geometry.merge)
+    if targets is not None:
+        if len(targets) != len(seq):
+            raise ValueError(f"targets has {len(targets)} entries for {len(seq)} tokens")
+        seq.targets = torch.as_tensor(targets).to(torch.int64)
+    if loss_mask is not None:
+        if len(loss_mask) != len(seq):
+            raise ValueError(f"loss_mask has {len(loss_mask)} entries for {len(seq)} tokens")
+        seq.loss_mask = torch.as_tensor(loss_mask)
+    return seq
 
 
 @dataclass

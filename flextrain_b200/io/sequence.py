@@ -35,3 +35,18 @@ class Sequence:
                 a = a & (self.loss_mask > 0)
             self._active = int(a.sum())
         return self._active
+
+
+def as_sequence(obj) -> "Sequence":
+    """A :class:`Sequence` for anything that carries ``tokens`` (duck typing, as the reference's engine allows:
+    ``tokens``, optionally ``targets``, ``loss_mask``, ``advantages``, ``ref_logprobs``, ``modality_inputs``,
+    ``seq_id``).  A :class:`Sequence` is returned as it is."""
+    if isinstance(obj, Sequence):
+        return obj
+    if not hasattr(obj, "tokens"):
+        raise TypeError(f"{type(obj).__name__} is not a sequence: it has no 'tokens'")
+    pick = lambda name: getattr(obj, name, None)
+    as64 = lambda t: None if t is None else torch.as_tensor(t).to(torch.int64)
+    return Sequence(as64(obj.tokens), targets=as64(pick("targets")), loss_mask=pick("loss_mask"),
+                    advantages=pick("advantages"), ref_logprobs=pick("ref_logprobs"),
+                    modality_inputs=pick("modality_inputs"), seq_id=int(pick("seq_id") or 0))

@@ -232,3 +232,36 @@ def test_an_optimizer_written_to_the_reference_protocol_trains_the_model():
         torch.testing.assert_close(mine[name].float(), p.detach(), rtol=2e-4, atol=2e-5, msg=f"{scope}/{l}/{name}")
     am.optimizer.lr = 0.01
     assert opt.lr == 0.01
+
+
+def test_duck_typed_sequences_are_accepted():
+    """Any object with ``tokens`` (and optionally ``targets``, ``loss_mask``, ``seq_id``) is a sequence, as in the
+    reference; per-token losses are written back to the caller's own objects."""
+    import pytest
+    import torch
+    import flextrain_b200 as ft
+    from conftest import build_tiny
+
+    class Mine:
+        def __init__(self, tokens):
+            self.tokens = tokens
+            self.targets = torch.roll(tokens, -1)
+            self.per_token_loss = torch.zeros(len(tokens))
+            self.seq_id = 0
+
+        def __len__(self):
+            return len(self.tokens)
+
+    g = torch.Generator().manual_seed(0)
+    toks = [torch.randint(0, 1024, (100,), generator=g), torch.randint(0, 1024, (60,), generator=g)]
+    mine = [Mine(t) for t in toks]
+    mine[0].targets[:10] = -100
+    theirs = [ft.Sequence(t.clone(), targets=m.targets.clone()) for t, m in zip(toks, mine)]
+    a, b = build_tiny(batch_tokens=256), build_tiny(batch_tokens=256)
+    sa = a.fwd_bwd(mine, loss_scale_factor=1.0 / 150)
+    sb = b.fwd_bwd(theirs, loss_scale_factor=1.0 / 150)
+    assert sa.loss_sum == sb.loss_sum and sa.active_tokens == 150
+    assert float(mine[0].per_token_loss[:10].abs().max()) == 0 and float(mine[0].per_token_loss[10]) > 0
+    assert torch.equal(mine[1].per_token_loss, theirs[1].per_token_loss)
+    with pytest.raises(TypeError):
+        a.fwd_bwd([object()])

@@ -314,6 +314,18 @@ def test_chat_rows_with_images_become_sequences(tmp_path):
     answer = fast("first is wider", add_special_tokens=False)["input_ids"]
     assert scored[: len(answer)] == answer and len(scored) <= len(answer) + 2
     assert compute_mrope_position_ids(seq, 0, len(seq)).shape == (len(seq), 3)
+    # the reference's text form and its (pixel_values, grid) call
+    from flextrain_b200.io.image_processing import preprocess_images
+    text = fast.apply_chat_template(msgs, tokenize=False)
+    seq_t = build_multimodal_sequence(text, [os.path.join(d, "a.png"), os.path.join(d, "b.png")], b)
+    assert torch.equal(seq_t.tokens, seq.tokens)
+    assert torch.equal(seq_t.modality_inputs["pixel_values"], seq.modality_inputs["pixel_values"])
+    mask = torch.zeros(len(seq_t), dtype=torch.bool)
+    mask[-5:] = True
+    assert build_multimodal_sequence(text, [os.path.join(d, "a.png"), os.path.join(d, "b.png")], b,
+                                     loss_mask=mask).active_token_count <= 5
+    px, grid = preprocess_images([os.path.join(d, "a.png"), os.path.join(d, "b.png")], b)
+    assert grid.tolist() == [[1, 8, 12], [1, 4, 4]] and torch.equal(px, seq.modality_inputs["pixel_values"])
     # the JSON source
     rows = [{"messages": msgs, "images": ["a.png", "b.png"]},
             {"messages": msgs, "images": ["missing.png", "b.png"]},                       # skipped: unreadable
