@@ -241,3 +241,27 @@ def test_reference_run_files_train_with_synthetic_raw_and_custom_sources(tmp_pat
     '''))
     out = _train(tmp_path, _ref_cfg(tmp_path, "{custom_factory: 'my_data:build'}"))
     assert out.count("[step") == 3 and "tok/step 512" in out
+
+
+def test_reference_run_file_with_json_sft_and_a_tokenizer_directory(tmp_path):
+    """``io.tokenizer`` + ``io.data.json_sft_path`` with the record's own field names, on a model whose dimensions are
+    written out in the file: the prompt is masked (fewer scored tokens than tokens) and the loss falls."""
+    transformers = pytest.importorskip("transformers")
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    chars = ["<unk>", "</s>"] + [chr(c) for c in range(32, 127)] + ["\n"]
+    tok = Tokenizer(models.WordLevel({c: i for i, c in enumerate(chars)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Split("", behavior="isolated")
+    transformers.PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", eos_token="</s>").save_pretrained(
+        str(tmp_path / "tok"))
+    rows = [{"q": f"{a}+{b}=", "a": str(a + b)} for a in range(6) for b in range(6)]
+    (tmp_path / "rows.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    data = "{json_sft_path: rows.jsonl, json_sft_prompt_field: q, json_sft_response_field: a, json_sft_input_field: null}"
+    path = _ref_cfg(tmp_path, data, **{"vocab_size: 512": f"vocab_size: {len(chars)}", "total_steps: 3": "total_steps: 12",
+                                       "lr: 0.001": "lr: 0.01", "save_final_checkpoint: false":
+                                       "save_final_checkpoint: false\n  tokenizer: tok"})
+    cfg = RunConfig.from_yaml(path)
+    assert cfg.data.tokenizer == str(tmp_path / "tok") and cfg.data.prompt_field == "q" and cfg.data.input_field is None
+    out = _train(tmp_path, path)
+    import re
+    losses = [float(m) for m in re.findall(r"\[step\s+\d+\].*? loss ([\d.]+)", out)]
+    assert len(losses) == 12 and losses[-1] < losses[0] - 0.3, losses
