@@ -114,6 +114,7 @@ def _build_active_model(mc: ModelConfig, *, optimizer, max_seq_len, max_global_b
             layers_are_local=True,
             min_chunk_size=min_chunk_size, max_chunk_size=max_chunk_size,
             force_saved_act_level=force_saved_act_level, verbose=verbose)
+    ws.resolve_act_slots(layers)          # a hand-built configuration may give the activation ring in bytes only
     if plan_only:
         ws.tp, ws.ep = tp, ep
         return ws

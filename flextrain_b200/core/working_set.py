@@ -42,11 +42,11 @@ class WorkingSetConfig:
     n_gpu_layers: Optional[int]            # None = all layers resident
     n_gpu_grads: Optional[int]
     n_gpu_opt_layers: Optional[int]
-    n_gpu_act_slots: int
-    gpu_act_buffer_size: int
-    host_act_buffer_size: int
-    max_seq_len: int
-    max_global_batch_tokens: int
+    n_gpu_act_slots: Optional[int] = None  # (layer, chunk) activation sets kept in HBM; None = derived from the ring bytes
+    gpu_act_buffer_size: int = 0
+    host_act_buffer_size: int = 0
+    max_seq_len: int = 0
+    max_global_batch_tokens: Optional[int] = None          # None = target_round_tokens x target_num_rounds
     # parallel layout
     world_size: int = 1
     shard: str = "none"
@@ -60,6 +60,31 @@ class WorkingSetConfig:
     healthy: bool = True
     head_chunk_size: Optional[int] = None      # set when the planner had to shrink the head's logits micro-chunk
     report: List[str] = field(default_factory=list)
+    # what the plan was made for: informational, and what a hand-built configuration in the reference's form carries
+    # (flextrain/core/working_set.py:91-129)
+    available_gpu_memory_bytes: int = 0
+    available_host_memory_bytes: int = 0
+    leeway_gpu_memory_bytes: int = 0
+    leeway_host_memory_bytes: int = 0
+    hardware_env: Optional[dict] = None
+    raw: Optional[dict] = None
+
+    def __post_init__(self):
+        if self.max_global_batch_tokens is None:
+            self.max_global_batch_tokens = int(self.target_round_tokens) * max(int(self.target_num_rounds), 1)
+        if not self.max_seq_len:
+            self.max_seq_len = int(self.max_chunk_size)
+
+    def resolve_act_slots(self, layers) -> None:
+        """A hand-built configuration may give the activation ring in bytes only: turn it into a slot count with the
+        largest per-layer activation set at ``max_chunk_size`` (no ring bytes = everything stays in HBM)."""
+        if self.n_gpu_act_slots is not None:
+            return
+        per_slot = max((l.activation_schema.device_size_bytes(self.max_chunk_size) for l in layers), default=0)
+        if self.gpu_act_buffer_size <= 0 or per_slot <= 0:
+            self.n_gpu_act_slots = 1 << 30
+        else:
+            self.n_gpu_act_slots = max(2, int(self.gpu_act_buffer_size // per_slot))
 
     @classmethod
     def simple(cls, *, max_seq_len: int, max_global_batch_tokens: int, chunk: Optional[int] = None,
@@ -343,7 +368,11 @@ def determine_working_set_config(*, layers, embed, head, optimizer, max_seq_len:
                             gpu_act_buffer_size=int(room), host_act_buffer_size=host_act, max_seq_len=max_seq_len,
                             max_global_batch_tokens=max_global_batch_tokens, world_size=world_size, shard=mode, tp=tp_group,
                             ep=ep, est_step_ms=est, est_compute_ms=comp, est_pcie_ms=pcie_ms, est_nvlink_ms=nv_ms,
-                            healthy=(n_slots >= 2), head_chunk_size=head_rows)
+                            healthy=(n_slots >= 2), head_chunk_size=head_rows,
+                            available_gpu_memory_bytes=int(max_gpu_mem_bytes),
+                            available_host_memory_bytes=int(max_host_mem_bytes),
+                            leeway_gpu_memory_bytes=int(leeway_gpu_mem_bytes),
+                            leeway_host_memory_bytes=int(leeway_host_mem_bytes))
                         say(f"[{mode}/{resid}{'' if depth == 0 else '/ring ' + str(depth)}] chunk {chunk} round "
                             f"{round_tokens} x{n_rounds} slots {'all' if n_slots >= 1 << 29 else n_slots}{tier_note}: est "
                             f"{est:.0f} ms (compute {comp:.0f}, pcie {pcie_ms:.0f}, nvlink {nv_ms:.0f})")

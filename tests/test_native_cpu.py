@@ -360,3 +360,31 @@ def test_planner_estimate_never_gets_worse_with_more_gpu_memory():
                 assert ws.est_step_ms <= prev * 1.02, (name, g, ws.est_step_ms, prev)
             prev = ws.est_step_ms
         assert seen_feasible
+
+
+def test_hand_built_working_set_in_the_reference_form():
+    """``WorkingSetConfig(...)`` written field by field as the reference's documentation does (activation ring in
+    bytes, informational budget fields, no slot count) drives the engine: few ring bytes force host offload of
+    activations, and the loss equals the everything-resident run's."""
+    import torch
+    import flextrain_b200 as ft
+    from conftest import build_tiny
+    from flextrain_b200.core.working_set import WorkingSetConfig
+    ws = WorkingSetConfig(target_round_tokens=256, max_chunk_size=128, max_training_chunks=4, max_total_round_tokens=256,
+                          target_num_rounds=1, n_gpu_layers=2, n_gpu_grads=2, n_gpu_opt_layers=1,
+                          gpu_act_buffer_size=3 << 20, host_act_buffer_size=64 << 20,
+                          available_gpu_memory_bytes=24 << 30, available_host_memory_bytes=110 << 30,
+                          leeway_gpu_memory_bytes=0, leeway_host_memory_bytes=0, max_seq_len=128, hardware_env={}, raw={})
+    assert ws.n_gpu_act_slots is None and ws.max_global_batch_tokens == 256
+    am = build_tiny(batch_tokens=256, ws=ws)
+    assert 2 <= am.ws.n_gpu_act_slots < 8                       # derived from the ring bytes: not everything fits
+    seqs = ft.SyntheticTokenSource(1024, 128, seed=2).get_sequences(256)
+    st = am.fwd_bwd(seqs, loss_scale_factor=1.0 / 256)
+    want = build_tiny(batch_tokens=256).fwd_bwd(ft.SyntheticTokenSource(1024, 128, seed=2).get_sequences(256),
+                                                loss_scale_factor=1.0 / 256)
+    assert st.loss_sum == want.loss_sum and st.host_act_bytes > 0 and want.host_act_bytes == 0
+    plan = ft.from_dims(dict(vocab_size=1024, n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16,
+                             expert_dim=128), arch="llama", optimizer=ft.AdamW(), max_seq_len=128,
+                        max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=16 << 30,
+                        device="cpu", plan_only=True)
+    assert plan.available_gpu_memory_bytes == 8 << 30 and plan.available_host_memory_bytes == 16 << 30
