@@ -43,3 +43,10 @@ def select_arch_module(arch: str, model_type: Optional[str] = None):
 
 
 select_arch = select_arch_module
+get_arch_module = select_arch_module          # the reference's name (flextrain/io/arch/__init__.py:57-70)
+
+
+def expand_layer_pattern(pattern: str, n_layers: int) -> list:
+    """``"3L1F"`` and the like -> one layer type per layer (see :func:`.common.expand_layer_pattern`)."""
+    from .common import expand_layer_pattern as _expand
+    return _expand(pattern, n_layers)
