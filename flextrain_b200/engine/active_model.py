@@ -155,8 +155,31 @@ class ActiveModel:
                     except AttributeError:
                         pass
 
+    def _check_sequences(self, seqs) -> None:
+        """Host-side checks of what would otherwise be an out-of-range access on the device: a sequence longer than the
+        context window the buffers were sized for, a token id outside the embedding table, a target outside the
+        vocabulary that is not the ignore value."""
+        vocab, limit = int(self.embed.vocab_size), int(self.ws.max_seq_len)
+        for s in seqs:
+            n = len(s)
+            if n == 0:
+                raise ValueError(f"sequence {s.seq_id} is empty")
+            if n > limit:
+                raise ValueError(f"sequence {s.seq_id} has {n} tokens; the model was built with max_seq_len={limit}")
+            lo, hi = int(s.tokens.min()), int(s.tokens.max())
+            if lo < 0 or hi >= vocab:
+                raise ValueError(f"sequence {s.seq_id} has token id {lo if lo < 0 else hi}; the vocabulary has "
+                                 f"{vocab} entries")
+            t = s.targets
+            if t is not None and t.dtype in (torch.int64, torch.int32):
+                if len(t) != n:
+                    raise ValueError(f"sequence {s.seq_id}: {len(t)} targets for {n} tokens")
+                if bool(((t >= vocab) | ((t < 0) & (t != -100))).any()):
+                    raise ValueError(f"sequence {s.seq_id} has a target outside [0, {vocab}) that is not -100")
+
     def _fwd_bwd(self, seqs, loss_scale_factor, total_tokens_per_step, loss_fn, forward_only, t0) -> StepStats:
         ws = self.ws
+        self._check_sequences(seqs)
         if loss_scale_factor is None:
             loss_scale_factor = 1.0 / max(sum(s.active_token_count for s in seqs), 1)
         total_tokens_per_step = total_tokens_per_step or sum(len(s) for s in seqs)

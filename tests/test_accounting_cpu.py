@@ -265,3 +265,26 @@ def test_duck_typed_sequences_are_accepted():
     assert torch.equal(mine[1].per_token_loss, theirs[1].per_token_loss)
     with pytest.raises(TypeError):
         a.fwd_bwd([object()])
+
+
+def test_sequences_are_checked_on_the_host_before_anything_reaches_the_device():
+    """Too long for the context window, a token id outside the embedding table, a target that is neither a vocabulary
+    id nor the ignore value, an empty sequence: each is a ``ValueError`` at the call, not an out-of-range access later."""
+    import pytest
+    import torch
+    import flextrain_b200 as ft
+    from conftest import build_tiny
+    am = build_tiny(batch_tokens=256, max_seq_len=128)
+    ids = lambda n, v=0: torch.full((n,), v, dtype=torch.int64)
+    bad_target = ids(16)
+    bad_target[3] = -1
+    for seq, what in [(ft.Sequence(ids(200)), "max_seq_len=128"), (ft.Sequence(ids(16, 5000)), "token id 5000"),
+                      (ft.Sequence(ids(16, -1)), "token id -1"), (ft.Sequence(ids(16), targets=bad_target), "target outside"),
+                      (ft.Sequence(ids(16), targets=ids(16, 1024)), "target outside"), (ft.Sequence(ids(0)), "is empty"),
+                      (ft.Sequence(ids(16), targets=ids(8)), "8 targets for 16 tokens")]:
+        with pytest.raises(ValueError, match=what):
+            am.fwd_bwd([seq])
+        with pytest.raises(ValueError, match=what):
+            am.evaluate([seq])
+    ok = ft.Sequence(ids(16, 1023), targets=torch.full((16,), -100, dtype=torch.int64))
+    assert am.fwd_bwd([ok]).active_tokens == 0
