@@ -176,6 +176,10 @@ class ActiveModel:
                     raise ValueError(f"sequence {s.seq_id}: {len(t)} targets for {n} tokens")
                 if bool(((t >= vocab) | ((t < 0) & (t != -100))).any()):
                     raise ValueError(f"sequence {s.seq_id} has a target outside [0, {vocab}) that is not -100")
+            for name in ("loss_mask", "advantages", "ref_logprobs"):
+                extra = getattr(s, name, None)
+                if extra is not None and len(extra) != n:
+                    raise ValueError(f"sequence {s.seq_id}: {len(extra)} {name} entries for {n} tokens")
 
     def _fwd_bwd(self, seqs, loss_scale_factor, total_tokens_per_step, loss_fn, forward_only, t0) -> StepStats:
         ws = self.ws

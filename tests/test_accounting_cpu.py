@@ -281,7 +281,9 @@ def test_sequences_are_checked_on_the_host_before_anything_reaches_the_device():
     for seq, what in [(ft.Sequence(ids(200)), "max_seq_len=128"), (ft.Sequence(ids(16, 5000)), "token id 5000"),
                       (ft.Sequence(ids(16, -1)), "token id -1"), (ft.Sequence(ids(16), targets=bad_target), "target outside"),
                       (ft.Sequence(ids(16), targets=ids(16, 1024)), "target outside"), (ft.Sequence(ids(0)), "is empty"),
-                      (ft.Sequence(ids(16), targets=ids(8)), "8 targets for 16 tokens")]:
+                      (ft.Sequence(ids(16), targets=ids(8)), "8 targets for 16 tokens"),
+                      (ft.Sequence(ids(16), loss_mask=torch.ones(4)), "4 loss_mask entries"),
+                      (ft.Sequence(ids(16), advantages=torch.ones(20)), "20 advantages entries")]:
         with pytest.raises(ValueError, match=what):
             am.fwd_bwd([seq])
         with pytest.raises(ValueError, match=what):
