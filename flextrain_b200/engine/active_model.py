@@ -225,7 +225,7 @@ class ActiveModel:
                                     param_gather=(self.dp.first_gemm if getattr(self.dp, "defer", False) else None))
                     with _nvtx("Setup Round"):
                         if hasattr(self.embed, "setup_round"):           # multimodal: encode the round's images once
-                            self.embed.setup_round(rseqs, metas, self.device)
+                            self.embed.setup_round(rseqs, metas, self.device, train=not forward_only)
                         transitions, slots = self._setup_round(metas)
                     with _nvtx("Forward"):
                         self._forward_pass(metas, plan, transitions, slots, ctx_base, stats)
@@ -320,6 +320,9 @@ class ActiveModel:
         for l, layer in enumerate(self.layers):
             g = bm.grads(l) if bm.grads_resident else _views(bm.host_g[l], bm.layers[l].g_layout)
             units.append((layer.param_spec, g))
+        if getattr(self.embed, "train_encoders", False):       # a trainable vision tower: replicated, counted once
+            for g in self.embed.encoder_grads().values():
+                rep += g.to(torch.float32).pow(2).sum().to(dev)
         for spec, grads in units:
             for t in spec.trainable():
                 g = grads.get(t.grad_name)
@@ -357,6 +360,12 @@ class ActiveModel:
                 rc = self._step_local(grad_scale)
             if getattr(self.head, "tied", False) and "g_tok_embeddings" in self.buffers.embed_grads():
                 self.buffers.head_params()["w_head_proj"].copy_(self.buffers.embed_params()["w_tok_embeddings"])
+            if getattr(self.embed, "train_encoders", False):
+                pg = None
+                if int(getattr(self, "world_size", 1) or 1) > 1:
+                    import torch.distributed as dist
+                    pg = dist.group.WORLD                   # data parallel over the whole job (no tp / ep with a tower)
+                rc |= self.embed.step_encoders(self.optimizer, self.step_num, grad_scale, pg)
         for l, layer in enumerate(self.layers):
             if self.buffers.params_resident:
                 layer.end_of_step(self.buffers.params(l))
@@ -806,6 +815,8 @@ class ActiveModel:
         bm = self.buffers
         bm.embed_g.zero_()
         bm.head_g.zero_()
+        if getattr(self.embed, "train_encoders", False):
+            self.embed.zero_encoder_grads()
         if bm.grads_resident:
             for b in bm.gpu_g:
                 b.zero_()

@@ -93,6 +93,8 @@ def save_training_state(am, out_dir: str, extra: Optional[dict] = None) -> str:
             for n, t in views.items():
                 if rank == 0 or local.get((scope, l, owner.get(n, "")), False):
                     state[f"o.{scope}.{l}.{n}"] = keep(t)
+    if rank == 0 and getattr(am.embed, "train_encoders", False):          # a trainable vision tower: replicated
+        state.update({k: keep(v) for k, v in am.embed.encoder_state_dict().items()})
     save_file(state, os.path.join(out_dir, f"state_rank{rank:05d}.safetensors"), metadata={"format": "pt"})
     if rank == 0:
         opt = am.optimizer
@@ -161,6 +163,11 @@ def load_training_state(am, src_dir: str, strict: bool = True) -> dict:
             for n, t in views.items():
                 src = fetch(f"o.{scope}.{l}.{n}", local.get((scope, l, owner.get(n, "")), False))
                 t.copy_(src.to(t.dtype).reshape(t.shape))
+    if getattr(am.embed, "train_encoders", False):
+        enc_keys = [k for k in keys[0] if k.startswith("enc.")]
+        if strict and not any(k.startswith("enc.master.") for k in enc_keys):
+            raise KeyError("the checkpoint has no vision-tower state but the tower is trainable in this job")
+        am.embed.load_encoder_state_dict({k: handles[0].get_tensor(k) for k in enc_keys})
     am.step_num = int(meta["step"])
     am._zero_grad = True
     if dp is not None:

@@ -18,7 +18,7 @@ tcgen05 attention kernel's 64 / 128)."""
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.nn.functional as F
@@ -78,6 +78,9 @@ class QwenVLViT:
     def __init__(self, cfg: ViTConfig, device="cpu", dtype=torch.float32):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.w: Dict[str, torch.Tensor] = {}
+        self.master: Optional[Dict[str, torch.Tensor]] = None      # fp32 leaves when the tower trains
+        self._ckpt_shapes: Dict[str, tuple] = {}                   # shapes as the checkpoint stores them (conv kernels)
+        self.loaded_prefix = self.PREFIXES[0]                      # where the checkpoint keeps the tower
 
     # ------------------------------------------------------------------ parameters
     def param_shapes(self) -> Dict[str, tuple]:
@@ -122,6 +125,7 @@ class QwenVLViT:
         """``state`` uses the tower's own names (no prefix); convolution kernels are flattened to matrices."""
         for n, shp in self.param_shapes().items():
             t = state[n]
+            self._ckpt_shapes[n] = tuple(t.shape)
             if t.dim() > 2:
                 t = t.reshape(t.shape[0], -1)
             if tuple(t.shape) != tuple(shp):
@@ -135,6 +139,7 @@ class QwenVLViT:
         for pre in prefixes:
             if reader.has(pre + probe):
                 self.load_state({n: reader.get(pre + n) for n in self.param_shapes()})
+                self.loaded_prefix = pre
                 return
         raise KeyError(f"no vision tower found under any of {prefixes}")
 
@@ -154,9 +159,9 @@ class QwenVLViT:
         ang = torch.cat([rows.to(torch.float32)[:, None] * inv, cols.to(torch.float32)[:, None] * inv], -1)
         return ang.repeat(t, 1)
 
-    def _pos_embed(self, t: int, h: int, w: int) -> torch.Tensor:
+    def _pos_embed(self, t: int, h: int, w: int, table: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Bilinear interpolation of the square position table to ``h x w``, in merge-block-major order."""
-        table = self.w["pos_embed.weight"]
+        table = self.w["pos_embed.weight"] if table is None else table
         side = int(round(self.cfg.num_pos ** 0.5))
         hi = torch.linspace(0, side - 1, h, device=self.device)
         wi = torch.linspace(0, side - 1, w, device=self.device)
@@ -181,18 +186,54 @@ class QwenVLViT:
         return (xf * cos + rot * sin).to(x.dtype)
 
     # ----------------------------------------------------------------------- forward
+    # ---------------------------------------------------------------------- training
+    def enable_training(self) -> None:
+        """Make the tower trainable: fp32 master copies become autograd leaves (their ``.grad`` accumulates over the
+        rounds of a step); the compute-dtype copies in ``self.w`` are refreshed after every update."""
+        self.master = {n: t.detach().to(torch.float32).clone().requires_grad_(True) for n, t in self.w.items()}
+
+    @property
+    def trainable(self) -> bool:
+        return self.master is not None
+
+    def param_spec(self):
+        """The tower's tensors as a :class:`ParamSpec` (fp32 master and gradient), for the engine's optimizer."""
+        from ...core.layer import ParamSpec, TensorSpec
+        return ParamSpec([TensorSpec(n, tuple(t.shape), self.dtype, master_dtype=torch.float32, grad_dtype=torch.float32,
+                                     opt_state_dtype=torch.float32) for n, t in self.w.items()])
+
+    def sync_compute(self) -> None:
+        for n, m in (self.master or {}).items():
+            self.w[n] = m.detach().to(self.dtype)
+
+    def encode_train(self, pixel_values: torch.Tensor, grid_thw: Sequence[Sequence[int]]) -> torch.Tensor:
+        """Like :meth:`encode`, with the autograd graph kept: ``rows.backward(d_rows)`` adds into ``master[n].grad``."""
+        if self.master is None:
+            raise RuntimeError("enable_training() first")
+        with torch.enable_grad():
+            return self._forward({n: m.to(self.dtype) for n, m in self.master.items()}, pixel_values, grid_thw, False)
+
+    def export_state(self) -> Dict[str, torch.Tensor]:
+        """Current weights under the tower's own names, in the checkpoint's shapes (conv kernels un-flattened)."""
+        src = self.master if self.master is not None else self.w
+        return {n: t.detach().to("cpu", self.w[n].dtype).reshape(self._ckpt_shapes.get(n, tuple(t.shape))).contiguous()
+                for n, t in src.items()}
+
     @torch.inference_mode()
     def encode(self, pixel_values: torch.Tensor, grid_thw: Sequence[Sequence[int]], return_hidden: bool = False):
         """``pixel_values (n_patches, C*tp*p*p)`` of all images, ``grid_thw`` = ``(t, h, w)`` per image (in patches).
         Returns the merged rows ``(n_patches / merge**2, out_hidden)`` in image order."""
-        c, W = self.cfg, self.w
+        return self._forward(self.w, pixel_values, grid_thw, return_hidden)
+
+    def _forward(self, W: Dict[str, torch.Tensor], pixel_values: torch.Tensor, grid_thw, return_hidden: bool):
+        c = self.cfg
         grids = [tuple(int(v) for v in g) for g in (grid_thw.tolist() if torch.is_tensor(grid_thw) else grid_thw)]
         n_expected = sum(t * h * w for t, h, w in grids)
         if pixel_values.shape[0] != n_expected or pixel_values.shape[1] != c.patch_dim:
             raise ValueError(f"pixel_values {tuple(pixel_values.shape)} does not match grids {grids} "
                              f"(expected ({n_expected}, {c.patch_dim}))")
         x = F.linear(pixel_values.to(self.device, self.dtype), W["patch_embed.proj.weight"], W["patch_embed.proj.bias"])
-        x = x + torch.cat([self._pos_embed(t, h, w) for t, h, w in grids], 0)
+        x = x + torch.cat([self._pos_embed(t, h, w, W["pos_embed.weight"]) for t, h, w in grids], 0)
         ang = torch.cat([self._rotary_angles(t, h, w) for t, h, w in grids], 0)
         ang = torch.cat([ang, ang], -1)
         cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]

@@ -43,6 +43,11 @@ class MultimodalInputLayer:
         self.vocab_size, self.d_model, self.scale = text.vocab_size, text.d_model, text.scale
         self._embeds: Optional[ImageEmbeddings] = None
         self.last_summary = InputsSummary()
+        # a trainable tower: the round's encoder output with its graph, and the gradient that flows back into it
+        self._rows_live: Optional[torch.Tensor] = None
+        self._d_rows: Optional[torch.Tensor] = None
+        self._opt_state: Dict[str, torch.Tensor] = {}
+        self.encoder_prefix = "model.visual."                  # where the checkpoint keeps the tower's tensors
 
     @property
     def placeholder_ids(self) -> List[int]:
@@ -53,8 +58,14 @@ class MultimodalInputLayer:
         return enc.cfg.depth if enc is not None else 0
 
     # ------------------------------------------------------------------ per round
-    def setup_round(self, seqs, metas: List[ChunkMeta], device) -> InputsSummary:
-        """Encode every image of the round once and attach the splice maps to the chunks."""
+    @property
+    def train_encoders(self) -> bool:
+        enc = self.encoders.get("image")
+        return enc is not None and getattr(enc, "trainable", False)
+
+    def setup_round(self, seqs, metas: List[ChunkMeta], device, train: bool = True) -> InputsSummary:
+        """Encode every image of the round once and attach the splice maps to the chunks.  With a trainable tower
+        and ``train`` the encoder's graph is kept until :meth:`finalize_round` sends the round's gradient through it."""
         enc = self.encoders.get("image")
         images, owner, row_offset, acc = [], [], {}, 0
         merge = enc.cfg.merge if enc is not None else 1
@@ -77,7 +88,14 @@ class MultimodalInputLayer:
         if not images:
             return summary
         batch = ImageInputs.pack(images, owner, enc.device, enc.dtype, pin=True)
-        rows = enc.encode(batch.pixel_values, batch.grid_thw)
+        self._rows_live = self._d_rows = None
+        if train and self.train_encoders:
+            rows = enc.encode_train(batch.pixel_values, batch.grid_thw)
+            self._rows_live = rows
+            self._d_rows = torch.zeros(rows.shape, dtype=torch.float32, device=rows.device)
+            rows = rows.detach()
+        else:
+            rows = enc.encode(batch.pixel_values, batch.grid_thw)
         self._embeds = ImageEmbeddings(rows.to(device), enc.rows_per_image(batch.grid_thw))
         maps = build_splice_maps(seqs, [m.extra["pieces"] for m in metas], self.placeholder_ids, row_offset)
         for i in row_offset:                                   # every image row must be consumed exactly once
@@ -92,7 +110,78 @@ class MultimodalInputLayer:
         return summary
 
     def finalize_round(self) -> None:
+        if self._rows_live is not None:
+            # every chunk of the round has handed its placeholder rows' gradient back: one backward through the tower
+            self._rows_live.backward(self._d_rows.to(self._rows_live.dtype))
+        self._rows_live = self._d_rows = None
         self._embeds = None
+
+    # ------------------------------------------------------------------ trainable tower: gradients, update, state
+    def encoder_grads(self) -> Dict[str, torch.Tensor]:
+        """``{"g_" + name: fp32 gradient}`` of the tower's tensors (zeros where nothing has flowed yet)."""
+        enc = self.encoders.get("image")
+        if not self.train_encoders:
+            return {}
+        out = {}
+        for n, m in enc.master.items():
+            if m.grad is None:
+                m.grad = torch.zeros_like(m)
+            out["g_" + n] = m.grad
+        return out
+
+    def zero_encoder_grads(self) -> None:
+        for g in self.encoder_grads().values():
+            g.zero_()
+
+    def step_encoders(self, optimizer, step_num: int, grad_scale: float = 1.0, process_group=None) -> int:
+        """Update the tower with the engine's optimizer (state allocated on first use, fp32); the data-parallel ranks
+        average nothing here: like every other gradient the tower's is a sum over the job's tokens."""
+        enc = self.encoders.get("image")
+        if not self.train_encoders:
+            return 0
+        grads = self.encoder_grads()
+        if process_group is not None:
+            import torch.distributed as dist
+            for g in grads.values():
+                dist.all_reduce(g, group=process_group)
+        spec = enc.param_spec()
+        if not self._opt_state:
+            for st in optimizer.state_specs(spec):
+                self._opt_state[st.key] = torch.zeros(st.shape, dtype=st.dtype, device=enc.device)
+        with torch.no_grad():
+            rc = optimizer.step(spec, {n: m.data for n, m in enc.master.items()}, grads, self._opt_state, step_num,
+                                grad_scale)
+        enc.sync_compute()
+        return int(rc or 0)
+
+    def encoder_export_state(self) -> Dict[str, torch.Tensor]:
+        """The tower's tensors under checkpoint names, for the exports (only when it trains: a frozen tower is passed
+        through from the source directory)."""
+        enc = self.encoders.get("image")
+        if not self.train_encoders:
+            return {}
+        return {self.encoder_prefix + n: t for n, t in enc.export_state().items()}
+
+    def encoder_state_dict(self) -> Dict[str, torch.Tensor]:
+        """Masters and optimizer state of a trainable tower, for training-state checkpoints."""
+        enc = self.encoders.get("image")
+        if not self.train_encoders:
+            return {}
+        out = {"enc.master." + n: m.detach().cpu() for n, m in enc.master.items()}
+        out.update({"enc.opt." + k: v.detach().cpu() for k, v in self._opt_state.items()})
+        return out
+
+    def load_encoder_state_dict(self, state: Dict[str, torch.Tensor]) -> None:
+        enc = self.encoders.get("image")
+        if not self.train_encoders:
+            return
+        with torch.no_grad():
+            for n, m in enc.master.items():
+                if "enc.master." + n in state:
+                    m.copy_(state["enc.master." + n])
+        self._opt_state = {k[len("enc.opt."):]: v.to(enc.device).clone() for k, v in state.items()
+                           if k.startswith("enc.opt.")}
+        enc.sync_compute()
 
     # ------------------------------------------------------------------ per chunk
     def forward(self, meta: ChunkMeta, params) -> torch.Tensor:
@@ -105,7 +194,11 @@ class MultimodalInputLayer:
     def backward(self, dx, meta: ChunkMeta, params, grads) -> None:
         rows = meta.extra.get("mm_rows")
         if rows is not None:
-            dx, _ = splice_backward(dx, rows)
+            want = self._d_rows is not None
+            dx, d_enc = splice_backward(dx, rows, want_encoder_grad=want)
+            if want:
+                self._d_rows.index_add_(0, meta.extra["mm_src"].to(self._d_rows.device),
+                                        d_enc.to(self._d_rows.device, torch.float32))
         self.text.backward(dx, meta, params, grads)
 
 
@@ -118,8 +211,6 @@ def attach_multimodal_input(am, hf: dict, model_dir: str, freeze: bool = True, r
         if required:
             raise ValueError("enable_multimodal=True but config.json has no vision_config")
         return
-    if not freeze:
-        raise NotImplementedError("the vision tower is frozen in this phase (freeze_modality_encoders=False)")
     if am.tp is not None:
         raise NotImplementedError("multimodal input with tensor parallelism is not supported")
     vit = QwenVLViT(ViTConfig.from_hf(vc), device=am.device,
@@ -130,5 +221,10 @@ def attach_multimodal_input(am, hf: dict, model_dir: str, freeze: bool = True, r
         if required:
             raise
         return
+    if not freeze:
+        if getattr(am, "dp", None) is not None and getattr(am.dp, "m", None) is not None:
+            raise NotImplementedError("a trainable vision tower runs on one GPU or with FTB_DP_BACKEND=collective")
+        vit.enable_training()
     am.embed = MultimodalInputLayer(am.embed, {"image": vit}, int(hf.get("image_token_id", -1)),
                                     hf.get("video_token_id"))
+    am.embed.encoder_prefix = vit.loaded_prefix

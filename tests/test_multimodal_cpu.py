@@ -649,3 +649,83 @@ def test_vision_language_lora_adapter_names_the_wrapper_modules(tmp_path):
                        mm_token_type_ids=(ids == IMG).to(torch.int32)).logits[0].float()
     got = float(torch.nn.functional.cross_entropy(logits, s.targets, ignore_index=-100, reduction="sum"))
     assert abs(got - want) / want < 2e-4, (got, want)
+
+
+def test_trainable_vision_tower_matches_transformers(tmp_path):
+    """``freeze_modality_encoders=False``: the gradient that reaches the placeholder rows flows on through the tower
+    (one backward per round, images and a clip, sequences cut across chunks); the tower's gradients equal
+    ``transformers``' autograd, an optimizer step moves it, the export carries the new tower and an exact-resume
+    checkpoint restores it."""
+    src_dir, out = str(tmp_path / "src"), str(tmp_path / "out")
+    model = _hf_vl_model()
+    _save_hub_layout(model, src_dir)
+    build = lambda: ft.from_pretrained(
+        src_dir, optimizer=ft.AdamW(lr=1e-2, state_dtype=torch.float32), max_seq_len=128, max_global_batch_tokens=256,
+        max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30, device="cpu", compute_dtype=torch.float32,
+        master_dtype=torch.float32, grad_dtype=torch.float32, host_backend=UnpinnedHostBackend(), enable_multimodal=True,
+        freeze_modality_encoders=False,
+        working_set=ft.WorkingSetConfig.simple(max_seq_len=128, max_global_batch_tokens=256, chunk=32, round_tokens=128))
+    am = build()
+    assert am.embed.train_encoders
+    seqs = [_mm_sequence(0, [(1, 4, 6), (1, 8, 4)], 3, [5, 7, 9]), _video_sequence(1, 11), _mm_sequence(2, [], 5, [40])]
+    model.zero_grad()
+    total = 0.0
+    for s in seqs:
+        ids = s.tokens[None]
+        kw = dict(mm_token_type_ids=(ids == IMG).to(torch.int32) + 2 * (ids == VID).to(torch.int32)) if s.modality_inputs else {}
+        ims = (s.modality_inputs or {}).get("images", [])
+        stills, clips = [im for im in ims if im.kind == "image"], [im for im in ims if im.kind == "video"]
+        if stills:
+            kw.update(pixel_values=torch.cat([im.pixel_values for im in stills]),
+                      image_grid_thw=torch.tensor([im.grid_thw for im in stills]))
+        if clips:
+            kw.update(pixel_values_videos=torch.cat([im.pixel_values for im in clips]),
+                      video_grid_thw=torch.tensor([im.grid_thw for im in clips]))
+        logits = model(input_ids=ids, **kw).logits[0].float()
+        total = total + torch.nn.functional.cross_entropy(logits, s.targets, ignore_index=-100, reduction="sum")
+    total.backward()
+    st = am.fwd_bwd(seqs, loss_scale_factor=1.0)               # two rounds: the tower's gradient accumulates over them
+    assert st.n_rounds >= 2 and abs(st.loss_sum - float(total)) / float(total) < 2e-4
+    sd = dict(model.named_parameters())
+    grads = am.embed.encoder_grads()
+    checked = 0
+    for n, g in grads.items():
+        want = sd["model.visual." + n[2:]].grad
+        want = want.reshape(g.shape)
+        assert float((g - want).norm()) <= 2e-3 * float(want.norm()) + 1e-7, n
+        checked += 1
+    assert checked == len(am.embed.encoders["image"].w) and checked > 20
+    before = {n: t.clone() for n, t in am.embed.encoders["image"].w.items()}
+    gn = am.grad_norm()
+    assert gn > float(torch.sqrt(sum(g.pow(2).sum() for g in grads.values())))      # the tower is part of the norm
+    assert am.step() == 0
+    moved = [n for n, t in am.embed.encoders["image"].w.items() if not torch.equal(t, before[n])]
+    assert len(moved) == len(before)
+    loss1 = am.evaluate(seqs).loss_sum
+    assert loss1 < st.loss_sum
+    # export: the trained tower, in the checkpoint's shapes; reload in transformers gives the engine's loss
+    ft.export.save_hf_full(am, out)
+    re = transformers.AutoModelForImageTextToText.from_pretrained(out, dtype=torch.float32)
+    rsd = re.state_dict()
+    assert rsd["model.visual.patch_embed.proj.weight"].shape == model.state_dict()["model.visual.patch_embed.proj.weight"].shape
+    assert not torch.equal(rsd["model.visual.blocks.0.attn.qkv.weight"], model.state_dict()["model.visual.blocks.0.attn.qkv.weight"])
+    assert torch.allclose(rsd["model.visual.blocks.0.attn.qkv.weight"], am.embed.encoders["image"].w["blocks.0.attn.qkv.weight"])
+    # exact resume: tower masters and optimizer state travel with the training state
+    am.save_training_state(str(tmp_path / "state"))
+    am.fwd_bwd(seqs, loss_scale_factor=1.0)
+    am.step()
+    want_w = {n: t.clone() for n, t in am.embed.encoders["image"].w.items()}
+    bm = build()
+    bm.load_training_state(str(tmp_path / "state"))
+    bm.fwd_bwd(seqs, loss_scale_factor=1.0)
+    bm.step()
+    for n, t in bm.embed.encoders["image"].w.items():
+        assert torch.equal(t, want_w[n]), n
+    # a frozen tower stays put and the evaluation path keeps no graph
+    fz = ft.from_pretrained(src_dir, optimizer=ft.AdamW(lr=1e-2), max_seq_len=128, max_global_batch_tokens=256,
+                            max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30, device="cpu",
+                            compute_dtype=torch.float32, master_dtype=torch.float32, grad_dtype=torch.float32,
+                            host_backend=UnpinnedHostBackend(), enable_multimodal=True)
+    assert not fz.embed.train_encoders and fz.embed.encoder_grads() == {}
+    am.evaluate(seqs)
+    assert am.embed._rows_live is None

@@ -55,6 +55,8 @@ def build_arg_parser() -> argparse.ArgumentParser:
                    help="mm_json: chat rows with image / video files for a vision-language checkpoint; hf: a HuggingFace "
                         "`datasets` id or directory in --dataset; raw: a .pt file of pre-tokenised sequences; custom: "
                         "--custom-factory module:callable returning (records, extract)")
+    p.add_argument("--train-vision-tower", action="store_true",
+                   help="vision-language checkpoints: update the vision tower too (default: frozen)")
     p.add_argument("--tokenizer", default=None, help="tokenizer directory / hub id (default: the model directory)")
     p.add_argument("--min-seq-len", type=int, default=0, help="skip documents / records shorter than this")
     p.add_argument("--hf-subset", default=None)
@@ -206,7 +208,7 @@ def main(argv=None) -> int:
         am = ft.from_dims(model, arch=arch, hyperparams=hyper, init_on_device=use_cuda, **common)
         vocab = model["vocab_size"]
     else:
-        am = ft.from_pretrained(model, **common)
+        am = ft.from_pretrained(model, freeze_modality_encoders=not args.train_vision_tower, **common)
         if os.environ.get("FLEXTRAIN_RANDOMIZE_WEIGHTS") == "1":
             from flextrain_b200.api import _init_random_weights
             _init_random_weights(am, int(os.environ.get("FLEXTRAIN_RANDOMIZE_WEIGHTS_SEED", "0")),
