@@ -272,6 +272,9 @@ def export_model_safetensors(am, out_dir: str, filename: str = "final.safetensor
         torch.cuda.synchronize()
     path = os.path.join(out_dir, filename)
     state = checkpoint_names(collect_hf_state(am), getattr(am, "hf_nested_prefix", None))
+    encoders = getattr(am.embed, "encoder_export_state", None)
+    if encoders is not None:
+        state.update(encoders())                    # a vision tower that was trained belongs to the weights
     if is_export_writer(am):
         save_file(state, path, metadata={"format": "pt"})
     return path

@@ -710,6 +710,10 @@ def test_trainable_vision_tower_matches_transformers(tmp_path):
     assert rsd["model.visual.patch_embed.proj.weight"].shape == model.state_dict()["model.visual.patch_embed.proj.weight"].shape
     assert not torch.equal(rsd["model.visual.blocks.0.attn.qkv.weight"], model.state_dict()["model.visual.blocks.0.attn.qkv.weight"])
     assert torch.allclose(rsd["model.visual.blocks.0.attn.qkv.weight"], am.embed.encoders["image"].w["blocks.0.attn.qkv.weight"])
+    from safetensors import safe_open
+    with safe_open(am.save_hf(str(tmp_path / "single"), out_filename="w.safetensors"), framework="pt") as f:
+        assert torch.allclose(f.get_tensor("model.visual.blocks.0.attn.qkv.weight"),
+                              am.embed.encoders["image"].w["blocks.0.attn.qkv.weight"])
     # exact resume: tower masters and optimizer state travel with the training state
     am.save_training_state(str(tmp_path / "state"))
     am.fwd_bwd(seqs, loss_scale_factor=1.0)
