@@ -321,7 +321,7 @@ class ActiveModel:
             g = bm.grads(l) if bm.grads_resident else _views(bm.host_g[l], bm.layers[l].g_layout)
             units.append((layer.param_spec, g))
         if getattr(self.embed, "train_encoders", False):       # a trainable vision tower: replicated, counted once
-            for g in self.embed.encoder_grads().values():
+            for g in self.embed.reduced_encoder_grads(self._encoder_group()).values():
                 rep += g.to(torch.float32).pow(2).sum().to(dev)
         for spec, grads in units:
             for t in spec.trainable():
@@ -338,6 +338,14 @@ class ActiveModel:
             import torch.distributed as dist
             dist.all_reduce(part, group=group.pg)
         return float((rep + part).sqrt())
+
+    def _encoder_group(self):
+        """Process group over which a trainable vision tower's gradient is summed: the whole job (data parallel; a
+        tower does not combine with tensor parallelism), or ``None`` on one rank."""
+        if int(getattr(self, "world_size", 1) or 1) <= 1:
+            return None
+        import torch.distributed as dist
+        return dist.group.WORLD
 
     def step(self, step_num: Optional[int] = None, *, max_grad_norm: Optional[float] = None) -> int:
         """Optimizer step over embed, head and every layer; returns 0, or the optimizer's error code.
@@ -361,11 +369,7 @@ class ActiveModel:
             if getattr(self.head, "tied", False) and "g_tok_embeddings" in self.buffers.embed_grads():
                 self.buffers.head_params()["w_head_proj"].copy_(self.buffers.embed_params()["w_tok_embeddings"])
             if getattr(self.embed, "train_encoders", False):
-                pg = None
-                if int(getattr(self, "world_size", 1) or 1) > 1:
-                    import torch.distributed as dist
-                    pg = dist.group.WORLD                   # data parallel over the whole job (no tp / ep with a tower)
-                rc |= self.embed.step_encoders(self.optimizer, self.step_num, grad_scale, pg)
+                rc |= self.embed.step_encoders(self.optimizer, self.step_num, grad_scale, self._encoder_group())
         for l, layer in enumerate(self.layers):
             if self.buffers.params_resident:
                 layer.end_of_step(self.buffers.params(l))

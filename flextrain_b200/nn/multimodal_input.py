@@ -48,6 +48,7 @@ class MultimodalInputLayer:
         self._d_rows: Optional[torch.Tensor] = None
         self._opt_state: Dict[str, torch.Tensor] = {}
         self.encoder_prefix = "model.visual."                  # where the checkpoint keeps the tower's tensors
+        self._reduced: Optional[Dict[str, torch.Tensor]] = None
 
     @property
     def placeholder_ids(self) -> List[int]:
@@ -113,6 +114,7 @@ class MultimodalInputLayer:
         if self._rows_live is not None:
             # every chunk of the round has handed its placeholder rows' gradient back: one backward through the tower
             self._rows_live.backward(self._d_rows.to(self._rows_live.dtype))
+            self._reduced = None                               # the local gradient moved: any summed copy is stale
         self._rows_live = self._d_rows = None
         self._embeds = None
 
@@ -132,6 +134,21 @@ class MultimodalInputLayer:
     def zero_encoder_grads(self) -> None:
         for g in self.encoder_grads().values():
             g.zero_()
+        self._reduced = None
+
+    def reduced_encoder_grads(self, process_group=None) -> Dict[str, torch.Tensor]:
+        """The tower's gradient summed over the data-parallel ranks (a copy, made once per accumulated gradient: the
+        local ``.grad`` tensors keep accumulating untouched, so a norm taken between two ``fwd_bwd`` calls does not
+        disturb the sum).  Every rank calls it at the same points (``grad_norm`` / ``step``)."""
+        local = self.encoder_grads()
+        if process_group is None or not local:
+            return local
+        if getattr(self, "_reduced", None) is None:
+            import torch.distributed as dist
+            self._reduced = {k: g.clone() for k, g in local.items()}
+            for k in sorted(self._reduced):                    # one fixed order on every rank
+                dist.all_reduce(self._reduced[k], group=process_group)
+        return self._reduced
 
     def step_encoders(self, optimizer, step_num: int, grad_scale: float = 1.0, process_group=None) -> int:
         """Update the tower with the engine's optimizer (state allocated on first use, fp32); the data-parallel ranks
@@ -139,11 +156,7 @@ class MultimodalInputLayer:
         enc = self.encoders.get("image")
         if not self.train_encoders:
             return 0
-        grads = self.encoder_grads()
-        if process_group is not None:
-            import torch.distributed as dist
-            for g in grads.values():
-                dist.all_reduce(g, group=process_group)
+        grads = self.reduced_encoder_grads(process_group)
         spec = enc.param_spec()
         if not self._opt_state:
             for st in optimizer.state_specs(spec):

@@ -733,3 +733,64 @@ def test_trainable_vision_tower_matches_transformers(tmp_path):
     assert not fz.embed.train_encoders and fz.embed.encoder_grads() == {}
     am.evaluate(seqs)
     assert am.embed._rows_live is None
+
+
+def _tower_rank(rank, world, port, src_dir, out):
+    import torch.distributed as dist
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        am = ft.from_pretrained(src_dir, optimizer=ft.AdamW(lr=1e-2, state_dtype=torch.float32), max_seq_len=128,
+                                max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
+                                device="cpu", compute_dtype=torch.float32, master_dtype=torch.float32,
+                                grad_dtype=torch.float32, host_backend=UnpinnedHostBackend(), enable_multimodal=True,
+                                freeze_modality_encoders=False, world_size=world, rank=rank)
+        seqs = _tower_batch()
+        am.fwd_bwd(seqs[rank::world], loss_scale_factor=1.0 / 64)
+        norm = am.grad_norm()
+        assert am.step(max_grad_norm=0.5 * norm) == 0
+        w = am.embed.encoders["image"].w
+        out.put((rank, norm, {n: t.numpy() for n, t in w.items()}))
+    finally:
+        dist.destroy_process_group()
+
+
+def _tower_batch():
+    return [_mm_sequence(0, [(1, 4, 6)], 3, [5, 9]), _video_sequence(1, 11), _mm_sequence(2, [(1, 4, 4)], 4, [11, 6]),
+            _mm_sequence(3, [], 5, [40])]
+
+
+def test_trainable_vision_tower_on_two_data_parallel_ranks(tmp_path):
+    """Two CPU ranks, each with half of the sequences: the tower's gradient is summed over the ranks before the norm
+    and the update, so norm and updated tower equal the single-process run on all sequences."""
+    import socket
+    import torch.multiprocessing as mp
+    src_dir = str(tmp_path / "src")
+    _save_hub_layout(_hf_vl_model(), src_dir)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_tower_rank, args=(r, 2, port, src_dir, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=600) for _ in range(2)], key=lambda x: x[0])
+    for p in procs:
+        p.join(60)
+    am = ft.from_pretrained(src_dir, optimizer=ft.AdamW(lr=1e-2, state_dtype=torch.float32), max_seq_len=128,
+                            max_global_batch_tokens=256, max_gpu_mem_bytes=8 << 30, max_host_mem_bytes=8 << 30,
+                            device="cpu", compute_dtype=torch.float32, master_dtype=torch.float32,
+                            grad_dtype=torch.float32, host_backend=UnpinnedHostBackend(), enable_multimodal=True,
+                            freeze_modality_encoders=False)
+    am.fwd_bwd(_tower_batch(), loss_scale_factor=1.0 / 64)
+    norm = am.grad_norm()
+    assert am.step(max_grad_norm=0.5 * norm) == 0
+    assert abs(res[0][1] - norm) < 1e-4 * norm and abs(res[1][1] - norm) < 1e-4 * norm
+    for n, t in am.embed.encoders["image"].w.items():
+        for r in range(2):
+            # AdamW's first step is sign-like: an element whose gradient is at rounding level may move the other way,
+            # so compare in the mean and bound the share of elements that differ
+            d = (torch.from_numpy(res[r][2][n]) - t).abs()
+            assert float(d.mean()) < 2e-4 and float((d > 1e-3).float().mean()) < 0.02, (r, n, float(d.mean()))
+    assert all((res[0][2][n] == res[1][2][n]).all() for n in res[0][2])            # the ranks stay identical
