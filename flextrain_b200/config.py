@@ -108,6 +108,13 @@ class RunConfig:
     def from_dict(d: dict, config_dir: Optional[str] = None) -> "RunConfig":
         if is_reference_schema(d):
             d = translate_reference_schema(d, config_dir)
+        sections = {"model": ModelConfig, "optimizer": OptimizerConfig, "train": TrainConfig, "hardware": HardwareConfig,
+                    "data": DataConfig, "io": IOConfig}
+        unknown = [k for k in d if k not in sections]
+        unknown += [f"{sec}.{k}" for sec, cls in sections.items() for k in (d.get(sec) or {})
+                    if k not in cls.__dataclass_fields__]
+        if unknown:
+            raise ValueError(f"run file keys that are not understood: {unknown}")
         mk = lambda cls, key: cls(**{k: v for k, v in (d.get(key) or {}).items() if k in cls.__dataclass_fields__})
         return RunConfig(mk(ModelConfig, "model"), mk(OptimizerConfig, "optimizer"), mk(TrainConfig, "train"),
                          mk(HardwareConfig, "hardware"), mk(DataConfig, "data"), mk(IOConfig, "io"))

@@ -61,7 +61,7 @@ def test_run_config_from_yaml(tmp_path):
     p = tmp_path / "c.yaml"
     p.write_text("model: {dims: tiny_llama, mode: lora, lora_rank: 4}\noptimizer: {name: muon, lr: 2.0e-3}\n"
                  "train: {steps: 7, max_seq_len: 64, max_global_batch_tokens: 256}\nhardware: {tp: 2}\n"
-                 "data: {source: synthetic}\nio: {output_dir: out, save_state_every: 3}\nunknown_section: {x: 1}\n")
+                 "data: {source: synthetic}\nio: {output_dir: out, save_state_every: 3}\n")
     c = RunConfig.from_yaml(str(p))
     assert (c.model.dims, c.model.mode, c.model.lora_rank) == ("tiny_llama", "lora", 4)
     assert c.optimizer.name == "muon" and c.optimizer.lr == 2e-3 and c.train.steps == 7 and c.hardware.tp == 2
@@ -70,6 +70,9 @@ def test_run_config_from_yaml(tmp_path):
     argv = _train_argv(c)
     assert "--use-muon" in argv and argv[argv.index("--tp") + 1] == "2" and argv[argv.index("--save-state-every") + 1] == "3"
     assert RunConfig.from_dict({}).train.steps > 0                                  # defaults fill everything
+    for bad in ({"unknown_section": {"x": 1}}, {"train": {"stepz": 3}}):            # a typo is refused, not ignored
+        with pytest.raises(ValueError, match="not understood"):
+            RunConfig.from_dict(bad)
 
 
 def test_reference_style_optimizer_constructors_and_package_exports():
